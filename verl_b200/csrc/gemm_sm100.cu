@@ -1,0 +1,549 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a built directly on tcgen05:
+//   warp 0      : TMA producer (per-CTA 2-D tiled loads, 128-byte swizzle)
+//   warp 1      : TMEM allocator + single-thread tcgen05.mma issuer
+//   warps 2..5  : epilogue (tcgen05.ld from TMEM, one accumulator row per thread)
+// The accumulator is double-buffered in TMEM (2 x BN fp32 columns) so the epilogue
+// of tile i overlaps the main loop of tile i+1.
+//
+// One main loop serves several epilogues:
+//   EPI_STORE   C = A.B^T (+bias) in bf16, or fp32 with optional C += (weight-gradient accumulation)
+//   EPI_LSE     fused lm_head -> online-softmax statistics per row (no logits in memory);
+//               role of verl/utils/kernel/kernels.py:183-343 (efficient_entropy_kernel_general_mainloop)
+//   EPI_DLOGITS recompute the logits tile and emit d_logits in bf16;
+//               role of verl/utils/kernel/kernels.py:1213-1509
+//
+// Operand layouts: an operand is "K-major" when the contraction index is contiguous
+// in memory ([rows, K] row-major) and "MN-major" when the row index is contiguous
+// ([K, rows] row-major). The forward pass of a Linear uses K-major/K-major, the data
+// gradient K-major/MN-major, the weight gradient MN-major/MN-major; no transposes are
+// materialised.
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace vb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 8;
+
+enum Epi : int { EPI_STORE = 0, EPI_LSE = 1, EPI_DLOGITS = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  // EPI_STORE
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;  // optional, length N
+  int out_fp32;
+  int accumulate;  // fp32 only: C += result
+  // EPI_LSE / EPI_DLOGITS
+  const long long* labels;  // [M]
+  float inv_temperature;
+  int num_splits;       // LSE: vocab splits per row block
+  int nblk_per_split;   // LSE: N blocks per split
+  float* partials;      // LSE: [M, num_splits, 4] = (max, sumexp, sum exp*logit, label logit)
+  const float* row_lse;     // DLOGITS: [M] log-sum-exp of scaled logits
+  const float* row_mean;    // DLOGITS: [M] E_p[logit]
+  const float* g_logprob;   // DLOGITS: [M] dL/dlogprob
+  const float* g_entropy;   // DLOGITS: [M] dL/dentropy (may be null)
+  int n_offset;             // DLOGITS: vocab offset of this chunk (for label compare)
+  int* status;
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort flag
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
+};
+
+// Map a linear work index to (m block, first n block, number of n blocks).
+struct Sched {
+  int num_m, num_n, num_units, nblk_per_split, num_splits;
+  bool lse;
+  __device__ Sched(const GemmParams& p, int BN, bool lse_) : lse(lse_) {
+    num_m = (p.M + BM - 1) / BM;
+    num_n = (p.N + BN - 1) / BN;
+    if (lse) {
+      nblk_per_split = p.nblk_per_split;
+      num_splits = p.num_splits;
+      num_units = num_m * num_splits;
+    } else {
+      nblk_per_split = 1;
+      num_splits = num_n;
+      num_units = num_m * num_n;
+    }
+  }
+  __device__ void get(int u, int& m_blk, int& n_first, int& n_count, int& split) const {
+    const int per_group = GROUP_M * num_splits;
+    const int g = u / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsize = min(num_m - first_m, GROUP_M);
+    const int r = u - g * per_group;
+    m_blk = first_m + r % gsize;
+    split = r / gsize;
+    n_first = split * nblk_per_split;
+    n_count = min(nblk_per_split, num_n - n_first);
+  }
+};
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using L = SmemLayout<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smemA = smem;
+  uint8_t* smemB = smem + L::STAGES * L::A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty = full + L::STAGES;
+  uint64_t* tfull = empty + L::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const Sched sched(p, BN, EPI == EPI_LSE);
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; ok && u < sched.num_units; u += gridDim.x) {
+        int m_blk, n_first, n_count, split;
+        sched.get(u, m_blk, n_first, n_count, split);
+        for (int nb = n_first; ok && nb < n_first + n_count; ++nb) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (*abort_flag || !mbar_wait(&empty[s], phase ^ 1)) {
+              report_error(p.status, ERR_WAIT_EMPTY, kb);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(&full[s], L::STAGE_BYTES);
+            uint8_t* a_dst = smemA + s * L::A_BYTES;
+            uint8_t* b_dst = smemB + s * L::B_BYTES;
+            if (A_MN) {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                tma_load_2d(a_dst + j * (BK * 128), &tmA, &full[s], m_blk * BM + j * 64, kb * BK);
+            } else {
+              tma_load_2d(a_dst, &tmA, &full[s], kb * BK, m_blk * BM);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(b_dst + j * (BK * 128), &tmB, &full[s], nb * BN + j * 64, kb * BK);
+            } else {
+              tma_load_2d(b_dst, &tmB, &full[s], kb * BK, nb * BN);
+            }
+            if (++s == L::STAGES) {
+              s = 0;
+              phase ^= 1;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
+      int s = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; ok && u < sched.num_units; u += gridDim.x) {
+        int m_blk, n_first, n_count, split;
+        sched.get(u, m_blk, n_first, n_count, split);
+        for (int nb = n_first; ok && nb < n_first + n_count; ++nb) {
+          if (*abort_flag || !mbar_wait(&tempty[acc], acc_phase ^ 1)) {
+            report_error(p.status, ERR_WAIT_TMEM_EMPTY, nb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (*abort_flag || !mbar_wait(&full[s], phase)) {
+              report_error(p.status, ERR_WAIT_FULL, kb);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(smemA + s * L::A_BYTES);
+            const uint32_t b_addr = smem_u32(smemB + s * L::B_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t a_desc = A_MN ? umma_smem_desc(a_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                                           : umma_smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
+              const uint64_t b_desc = B_MN ? umma_smem_desc(b_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                                           : umma_smem_desc(b_addr + k * (UMMA_K * 2), 16, 1024);
+              tc_mma_f16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            tc_commit(&empty[s]);  // frees the stage once these MMAs have read it
+            if (++s == L::STAGES) {
+              s = 0;
+              phase ^= 1;
+            }
+          }
+          if (!ok) break;
+          tc_commit(&tfull[acc]);
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1;
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; ok && u < sched.num_units; u += gridDim.x) {
+      int m_blk, n_first, n_count, split;
+      sched.get(u, m_blk, n_first, n_count, split);
+      const int row = m_blk * BM + row_in_tile;
+      const bool row_ok = row < p.M;
+
+      // per-row state for the fused epilogues
+      float run_max = -INFINITY, run_sum = 0.f, run_dot = 0.f, label_logit = 0.f;
+      long long label = -1;
+      float r_lse = 0.f, r_mean = 0.f, r_glp = 0.f, r_gent = 0.f;
+      if (EPI == EPI_LSE || EPI == EPI_DLOGITS) {
+        if (row_ok) label = p.labels[row];
+      }
+      if (EPI == EPI_DLOGITS) {
+        if (row_ok) {
+          r_lse = p.row_lse[row];
+          r_mean = p.row_mean[row];
+          r_glp = p.g_logprob[row];
+          r_gent = p.g_entropy ? p.g_entropy[row] : 0.f;
+        }
+      }
+
+      for (int nb = n_first; ok && nb < n_first + n_count; ++nb) {
+        if (*abort_flag || !mbar_wait(&tfull[acc], acc_phase)) {
+          report_error(p.status, ERR_WAIT_TMEM_FULL, nb);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = nb * BN + c * 32;
+          if (EPI == EPI_STORE) {
+            if (row_ok && col0 < p.N) {
+              if (p.bias != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  if (col0 + i < p.N) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[col0 + i]));
+                }
+              }
+              if (p.out_fp32) {
+                float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+                if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                           __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                    if (p.accumulate) {
+                      float4 o = reinterpret_cast<float4*>(dst)[i];
+                      v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                    }
+                    reinterpret_cast<float4*>(dst)[i] = v;
+                  }
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    if (col0 + i < p.N) {
+                      float v = __uint_as_float(r[i]);
+                      if (p.accumulate) v += dst[i];
+                      dst[i] = v;
+                    }
+                  }
+                }
+              } else {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+                if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    uint4 v;
+                    v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+                    v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                    v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                    v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                    reinterpret_cast<uint4*>(dst)[i] = v;
+                  }
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    if (col0 + i < p.N) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
+                }
+              }
+            }
+          } else if (EPI == EPI_LSE) {
+            if (col0 < p.N) {
+              float cmax = -INFINITY;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                float x = __uint_as_float(r[i]) * p.inv_temperature;
+                x = (col0 + i < p.N) ? x : -INFINITY;
+                if ((long long)(col0 + i) == label) label_logit = x;
+                r[i] = __float_as_uint(x);
+                cmax = fmaxf(cmax, x);
+              }
+              const float new_max = fmaxf(run_max, cmax);
+              const float scale = __expf(run_max - new_max);  // exp(-inf) = 0 on the first chunk
+              float csum = 0.f, cdot = 0.f;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float x = __uint_as_float(r[i]);
+                const float e = __expf(x - new_max);  // exp(-inf) = 0 for masked columns
+                csum += e;
+                cdot += (col0 + i < p.N) ? e * x : 0.f;
+              }
+              run_sum = run_sum * scale + csum;
+              run_dot = run_dot * scale + cdot;
+              run_max = new_max;
+            }
+          } else {  // EPI_DLOGITS
+            if (row_ok && col0 < p.N) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+              const long long rel = label - (long long)p.n_offset - col0;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float x = __uint_as_float(r[i]) * p.inv_temperature;
+                const float pr = __expf(x - r_lse);
+                float g = r_glp * (((long long)i == rel ? 1.f : 0.f) - pr) - r_gent * pr * (x - r_mean);
+                r[i] = __float_as_uint(g * p.inv_temperature);
+              }
+              if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  uint4 v;
+                  v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+                  v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                  v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                  v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                  reinterpret_cast<uint4*>(dst)[i] = v;
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < p.N) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
+              }
+            }
+          }
+        }
+        // release this accumulator buffer to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+      if (EPI == EPI_LSE) {
+        if (ok && row_ok) {
+          float4 out = make_float4(run_max, run_sum, run_dot, label_logit);
+          reinterpret_cast<float4*>(p.partials)[(long long)row * p.num_splits + split] = out;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// Merge the per-split statistics of the fused lm_head kernel.
+// Role of verl/utils/kernel/kernels.py:346-435 (efficient_entropy_triton_kernel_epilogue).
+__global__ void lse_merge_kernel(const float4* __restrict__ partials, int M, int num_splits,
+                                 float* __restrict__ logprob, float* __restrict__ entropy, float* __restrict__ lse_out,
+                                 float* __restrict__ mean_out) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float m = -INFINITY, s = 0.f, d = 0.f, ll = 0.f;
+  for (int i = 0; i < num_splits; ++i) {
+    const float4 v = partials[(long long)row * num_splits + i];
+    const float nm = fmaxf(m, v.x);
+    const float a = __expf(m - nm), b = __expf(v.x - nm);
+    s = s * a + v.y * b;
+    d = d * a + v.z * b;
+    m = nm;
+    ll += v.w;
+  }
+  const float lse = m + logf(s);
+  const float mean = d / s;
+  if (logprob) logprob[row] = ll - lse;
+  if (entropy) entropy[row] = lse - mean;
+  if (lse_out) lse_out[row] = lse;
+  if (mean_out) mean_out[row] = mean;
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+static int launch_gemm(const void* A, const void* B, long long lda, long long ldb, const GemmParams& p,
+                       cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (A_MN) rc = vb_make_tmap_2d(&tmA, A, 2, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)lda * 2, 64, BK);
+  else rc = vb_make_tmap_2d(&tmA, A, 2, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)lda * 2, BK, BM);
+  if (rc) return rc;
+  if (B_MN) rc = vb_make_tmap_2d(&tmB, B, 2, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)ldb * 2, 64, BK);
+  else rc = vb_make_tmap_2d(&tmB, B, 2, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldb * 2, BK, BN);
+  if (rc) return rc;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    VB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    attr_set = true;
+  }
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int units = (EPI == EPI_LSE) ? num_m * p.num_splits : num_m * num_n;
+  if (units <= 0) return 0;
+  const int grid = units < vb_num_sms() ? units : vb_num_sms();
+  kern<<<grid, NUM_THREADS, L::DYN_BYTES, stream>>>(tmA, tmB, p);
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+}  // namespace vb
+
+using namespace vb;
+
+// C[M,N] = A . B^T, bf16 inputs, fp32 accumulation.
+//   a_mn = 0: A is [M,K] row-major (lda elements per row); a_mn = 1: A is stored [K,M] row-major.
+//   b_mn = 0: B is [N,K] row-major;                         b_mn = 1: B is stored [K,N] row-major.
+//   out_fp32 = 0: C bf16; 1: C fp32, and accumulate != 0 adds into C.
+// Requirements: lda, ldb multiples of 8; pointers 16-byte aligned.
+extern "C" int vb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32,
+                            int accumulate, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7)) return -3;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.out_fp32 = out_fp32; p.accumulate = accumulate; p.status = status;
+  const bool small_n = N <= 128;
+  if (!a_mn && !b_mn) {
+    return small_n ? launch_gemm<128, false, false, EPI_STORE>(A, B, lda, ldb, p, stream)
+                   : launch_gemm<256, false, false, EPI_STORE>(A, B, lda, ldb, p, stream);
+  } else if (!a_mn && b_mn) {
+    return small_n ? launch_gemm<128, false, true, EPI_STORE>(A, B, lda, ldb, p, stream)
+                   : launch_gemm<256, false, true, EPI_STORE>(A, B, lda, ldb, p, stream);
+  } else if (a_mn && b_mn) {
+    return small_n ? launch_gemm<128, true, true, EPI_STORE>(A, B, lda, ldb, p, stream)
+                   : launch_gemm<256, true, true, EPI_STORE>(A, B, lda, ldb, p, stream);
+  } else {
+    return small_n ? launch_gemm<128, true, false, EPI_STORE>(A, B, lda, ldb, p, stream)
+                   : launch_gemm<256, true, false, EPI_STORE>(A, B, lda, ldb, p, stream);
+  }
+}
+
+// Number of vocab splits the fused lm_head kernel uses for (T, V); the caller sizes
+// the scratch as T * splits * 4 floats.
+extern "C" int vb_lmhead_num_splits(int T, int V) {
+  const int num_m = (T + BM - 1) / BM;
+  const int num_n = (V + 255) / 256;
+  int splits = (2 * vb_num_sms() + num_m - 1) / num_m;
+  if (splits < 1) splits = 1;
+  if (splits > num_n) splits = num_n;
+  const int per = (num_n + splits - 1) / splits;
+  return (num_n + per - 1) / per;
+}
+
+// Fused lm_head forward: logits = hidden . weight^T * inv_temperature are never written.
+//   hidden [T,H] bf16, weight [V,H] bf16, labels [T] int64.
+//   scratch: T * vb_lmhead_num_splits(T,V) * 4 floats.
+//   outputs (fp32, each [T], any may be null): logprob of label, entropy, lse, mean logit under p.
+extern "C" int vb_lmhead_logprob_fwd(const void* hidden, const void* weight, const long long* labels, int T, int H,
+                                     int V, float inv_temperature, float* scratch, float* logprob, float* entropy,
+                                     float* lse, float* mean, int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H & 7) return -3;
+  GemmParams p{};
+  p.M = T; p.N = V; p.K = H;
+  p.labels = labels; p.inv_temperature = inv_temperature;
+  const int num_n = (V + 255) / 256;
+  p.num_splits = vb_lmhead_num_splits(T, V);
+  p.nblk_per_split = (num_n + p.num_splits - 1) / p.num_splits;
+  p.partials = scratch; p.status = status;
+  int rc = launch_gemm<256, false, false, EPI_LSE>(hidden, weight, H, H, p, stream);
+  if (rc) return rc;
+  lse_merge_kernel<<<(T + 127) / 128, 128, 0, stream>>>(reinterpret_cast<const float4*>(scratch), T, p.num_splits,
+                                                        logprob, entropy, lse, mean);
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+// d_logits chunk for the fused lm_head backward: recomputes logits[T, n_offset : n_offset+Vc]
+// and writes d_logits (bf16, [T, ldc]) given per-row lse / mean and upstream gradients.
+//   weight_chunk points at weight[n_offset, 0].
+extern "C" int vb_lmhead_dlogits(const void* hidden, const void* weight_chunk, const long long* labels, int T, int H,
+                                 int Vc, int n_offset, float inv_temperature, const float* lse, const float* mean,
+                                 const float* g_logprob, const float* g_entropy, void* dlogits, long long ldc,
+                                 int* status, cudaStream_t stream) {
+  if (T <= 0 || Vc <= 0) return 0;
+  if (H & 7) return -3;
+  GemmParams p{};
+  p.M = T; p.N = Vc; p.K = H;
+  p.C = dlogits; p.ldc = ldc;
+  p.labels = labels; p.inv_temperature = inv_temperature;
+  p.row_lse = lse; p.row_mean = mean; p.g_logprob = g_logprob; p.g_entropy = g_entropy;
+  p.n_offset = n_offset; p.status = status;
+  return launch_gemm<256, false, false, EPI_DLOGITS>(hidden, weight_chunk, H, H, p, stream);
+}
