@@ -1,0 +1,319 @@
+"""Numerics of every hand-written CUDA kernel against a plain PyTorch fp32 reference of the same op.
+
+Tolerances: outputs stored in bf16 are compared with rtol ~ 2 bf16 ulps of the reference magnitude;
+fp32 outputs (log-probs, entropy, optimizer state) with the tolerances the reference uses for its
+fused kernels (tests/utils/test_linear_cross_entropy.py: logprob atol 1e-3 / rtol 2e-4, entropy atol 5e-3).
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf16_close(got, ref, scale=None, ulps=4.0):
+    got, ref = got.float(), ref.float()
+    scale = ref.abs().max().item() if scale is None else scale
+    err = (got - ref).abs().max().item()
+    assert err <= ulps * 2 ** -8 * scale + 1e-6, f"max err {err} vs scale {scale}"
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    from verl_b200.ops import _lib
+
+    _lib.load()
+    yield
+    code, blk, detail = _lib.read_status()
+    assert code == 0, f"kernel status word reports error {code} (block {blk}, detail {detail})"
+
+
+@pytest.mark.parametrize("mode", ["tn", "nn", "wg", "an"])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (200, 264, 136), (1024, 3584, 3584), (777, 128, 1000),
+                                   (8, 1024, 512), (384, 72, 256)])
+def test_gemm_layouts(mode, shape):
+    from verl_b200.ops import gemm
+
+    torch.manual_seed(0)
+    M, N, K = shape
+    a_mn, b_mn = {"tn": (False, False), "nn": (False, True), "wg": (True, True), "an": (True, False)}[mode]
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operand needs a row stride that is a multiple of 8")
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    out = gemm(A.t().contiguous() if a_mn else A, B.t().contiguous() if b_mn else B, a_mn=a_mn, b_mn=b_mn)
+    _bf16_close(out, ref)
+
+
+def test_gemm_fp32_accumulate_and_bias():
+    from verl_b200.ops import gemm
+
+    torch.manual_seed(1)
+    M, N, K = 256, 520, 384
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    C = torch.full((M, N), 3.0, device="cuda")
+    gemm(A, B, out=C, accumulate=True)
+    torch.testing.assert_close(C, A.float() @ B.float().t() + 3.0, atol=1e-3, rtol=1e-5)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    _bf16_close(gemm(A, B, bias=bias), A.float() @ B.float().t() + bias.float())
+
+
+def test_gemm_deterministic():
+    from verl_b200.ops import gemm
+
+    A = torch.randn(512, 1024, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(768, 1024, device="cuda", dtype=torch.bfloat16)
+    assert torch.equal(gemm(A, B), gemm(A, B))
+
+
+def test_linear_autograd_matches_torch():
+    from verl_b200 import ops
+
+    torch.manual_seed(2)
+    x = torch.randn(300, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(264, 512, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    b = torch.randn(264, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn(300, 264, device="cuda", dtype=torch.bfloat16)
+    ops.linear(x, w, b).backward(dy)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    torch.nn.functional.linear(xr, wr, br).backward(dy.float())
+    _bf16_close(x.grad, xr.grad)
+    _bf16_close(w.grad, wr.grad)
+    _bf16_close(b.grad, br.grad)
+    # fused accumulation into an fp32 main_grad
+    w2 = w.detach().clone().requires_grad_(True)
+    w2.main_grad = torch.ones(w2.shape, device="cuda")
+    ops.linear(x.detach(), w2, None).backward(dy)
+    assert w2.grad is None
+    torch.testing.assert_close(w2.main_grad, wr.grad + 1.0, atol=2e-3, rtol=1e-4)
+
+
+@pytest.mark.parametrize("T,H,V,temp", [(300, 256, 2048, 1.0), (1937, 3584, 152064, 0.7), (129, 1024, 32000, 1.5)])
+def test_fused_lmhead_forward_backward(T, H, V, temp):
+    from verl_b200 import ops
+
+    torch.manual_seed(3)
+    hid = torch.randn(T, H, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(V, H, device="cuda") * 0.02).bfloat16().requires_grad_(True)
+    labels = torch.randint(0, V, (T,), device="cuda")
+    lp, ent = ops.lmhead_logprob_entropy(hid, w, labels, temp)
+    hr, wr = hid.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    logits = (hr @ wr.t()) / temp
+    lse = torch.logsumexp(logits, -1)
+    lp_ref = logits.gather(1, labels[:, None])[:, 0] - lse
+    ent_ref = lse - (torch.softmax(logits, -1) * logits).sum(-1)
+    torch.testing.assert_close(lp, lp_ref, atol=1e-3, rtol=2e-4)
+    torch.testing.assert_close(ent, ent_ref, atol=5e-3, rtol=1e-3)
+    g_lp = torch.randn(T, device="cuda")
+    g_ent = torch.randn(T, device="cuda") * 0.1
+    (lp * g_lp + ent * g_ent).sum().backward()
+    (lp_ref * g_lp + ent_ref * g_ent).sum().backward()
+    _bf16_close(hid.grad, hr.grad, ulps=8)
+    _bf16_close(w.grad, wr.grad, ulps=8)
+
+
+def test_rmsnorm_forward_backward():
+    from verl_b200 import ops
+
+    torch.manual_seed(4)
+    rows, H = 1000, 3584
+    x = torch.randn(rows, H, device="cuda").bfloat16().requires_grad_(True)
+    res = torch.randn(rows, H, device="cuda").bfloat16().requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16().requires_grad_(True)
+    y, h = ops.rmsnorm(x, w, 1e-6, res)
+    dy, dh = torch.randn_like(y), torch.randn_like(h)
+    torch.autograd.backward([y, h], [dy, dh])
+    xr, rr, wr = (t.detach().float().requires_grad_(True) for t in (x, res, w))
+    hr = (xr + rr).bfloat16().float() + ((xr + rr) - (xr + rr).detach())  # same rounding, full gradient
+    yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    torch.autograd.backward([yr, hr], [dy.float(), dh.float()])
+    _bf16_close(y, yr)
+    _bf16_close(h, hr)
+    _bf16_close(x.grad, xr.grad)
+    _bf16_close(res.grad, rr.grad)
+    _bf16_close(w.grad, wr.grad, ulps=8)
+
+
+def test_swiglu_and_rope():
+    from verl_b200 import ops
+
+    torch.manual_seed(5)
+    gu = torch.randn(512, 2 * 1184, device="cuda").bfloat16().requires_grad_(True)
+    do = torch.randn(512, 1184, device="cuda").bfloat16()
+    out = ops.swiglu(gu)
+    out.backward(do)
+    gr = gu.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.silu(gr[:, :1184]) * gr[:, 1184:]
+    ref.backward(do.float())
+    _bf16_close(out, ref)
+    _bf16_close(gu.grad, gr.grad)
+
+    T, Hq, Hk, D = 333, 28, 4, 128
+    qkv = torch.randn(T, (Hq + 2 * Hk) * D, device="cuda").bfloat16()
+    pos = torch.randint(0, 4096, (T,), device="cuda")
+    cos_t, sin_t = ops.rope_tables(D, 4096, 1e6, "cuda")
+    ref = ops.rope_qkv(qkv.cpu().float(), pos.cpu(), cos_t.cpu(), sin_t.cpu(), Hq, Hk, D)
+    src = qkv.clone().requires_grad_(True)
+    got = ops.rope_qkv(src * 1.0, pos, cos_t, sin_t, Hq, Hk, D)
+    _bf16_close(got, ref)
+    # backward is the transpose rotation: <rope(x), g> == <x, rope^T(g)>
+    g = torch.randn_like(got)
+    got.backward(g)
+    lhs = (got.float() * g.float()).sum()
+    rhs = (qkv.float() * src.grad.float()).sum()
+    assert abs(lhs.item() - rhs.item()) <= 2e-2 * abs(lhs.item()) + 1.0
+
+
+def test_embedding_and_adamw_and_norms():
+    from verl_b200 import ops
+
+    torch.manual_seed(6)
+    W = torch.randn(5000, 512, device="cuda").bfloat16().requires_grad_(True)
+    ids = torch.randint(0, 5000, (777,), device="cuda")
+    out = ops.embedding(ids, W)
+    assert torch.equal(out, W[ids])
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    ref = torch.zeros(5000, 512, device="cuda").index_add_(0, ids, dy.float())
+    _bf16_close(W.grad, ref)
+
+    n = 1_000_003
+    p32, g = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    pr = torch.nn.Parameter(p32.clone())
+    opt = torch.optim.AdamW([pr], lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    for step in (1, 2, 3):
+        pr.grad = g.clone()
+        opt.step()
+        ops.adamw_step(p32, g, m, v, p16, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, step=step)
+    torch.testing.assert_close(p32, pr.data, atol=2e-6, rtol=1e-5)
+    _bf16_close(p16, pr.data)
+    ss = torch.zeros(1, device="cuda")
+    ops.sumsq_into(g, ss)
+    torch.testing.assert_close(ss[0], g.pow(2).sum(), rtol=1e-4, atol=0)
+    scale, skip, norm = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda", dtype=torch.int32), torch.zeros(1, device="cuda")
+    ops.clip_coef(ss, 1.0, 0.5, scale, skip, norm)
+    gn = g.norm().item() * 0.5
+    assert abs(norm.item() - gn) < 1e-2 and skip.item() == 0 and abs(scale.item() - 0.5 / (gn + 1e-6)) < 1e-6
+
+
+def test_ppo_loss_fused_matches_torch():
+    from verl_b200 import ops
+    from verl_b200.trainer.ppo import core_algos
+
+    torch.manual_seed(7)
+    B, T = 16, 200
+    logp = (torch.randn(B, T, device="cuda") * 0.5 - 2).requires_grad_(True)
+    old = logp.detach() + torch.randn(B, T, device="cuda") * 0.3
+    ref_lp = logp.detach() + torch.randn(B, T, device="cuda") * 0.2
+    adv = torch.randn(B, T, device="cuda")
+    mask = (torch.rand(B, T, device="cuda") > 0.3).float()
+    ent = torch.rand(B, T, device="cuda").requires_grad_(True)
+    loss, sums = ops.ppo_loss_fused(logp, old, adv, mask, entropy=ent, ref_logp=ref_lp, clip_low=0.2, clip_high=0.28,
+                                    clip_c=3.0, kl_coef=0.01, kl_type="low_var_kl", entropy_coeff=0.001)
+    loss.backward()
+    lr, er = logp.detach().clone().requires_grad_(True), ent.detach().clone().requires_grad_(True)
+    pg, clipfrac, ppo_kl, clipfrac_lower = core_algos.compute_policy_loss_vanilla(
+        old, lr, adv, mask, loss_agg_mode="token-mean", clip_ratio_low=0.2, clip_ratio_high=0.28, clip_ratio_c=3.0)
+    kld = core_algos.kl_penalty(lr, ref_lp, "low_var_kl")
+    kl_loss = core_algos.agg_loss(kld, mask, "token-mean")
+    ent_loss = core_algos.agg_loss(er, mask, "token-mean")
+    ref_loss = pg - 0.001 * ent_loss + 0.01 * kl_loss
+    ref_loss.backward()
+    torch.testing.assert_close(loss, ref_loss, atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(logp.grad, lr.grad, atol=1e-7, rtol=1e-3)
+    torch.testing.assert_close(ent.grad, er.grad, atol=1e-8, rtol=1e-3)
+    n = sums[6]
+    torch.testing.assert_close(sums[1] / n, clipfrac, atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(sums[2] / n, ppo_kl, atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(sums[3] / n, clipfrac_lower, atol=1e-5, rtol=1e-4)
+
+
+def test_gae_and_grpo_match_core_algos():
+    from verl_b200 import ops
+    from verl_b200.trainer.ppo import core_algos
+
+    torch.manual_seed(8)
+    B, T = 37, 129
+    r, v = torch.randn(B, T, device="cuda"), torch.randn(B, T, device="cuda")
+    mk = (torch.rand(B, T, device="cuda") > 0.2).float()
+    adv, ret = ops.gae(r, v, mk, 0.99, 0.95)
+    adv_ref, ret_ref = core_algos.compute_gae_advantage_return(r.cpu(), v.cpu(), mk.cpu(), 0.99, 0.95, whiten=False)
+    torch.testing.assert_close(adv.cpu(), adv_ref, atol=1e-4, rtol=1e-4)
+    torch.testing.assert_close(ret.cpu(), ret_ref, atol=1e-4, rtol=1e-4)
+
+    import numpy as np
+
+    scores_tok = torch.zeros(B, T)
+    scores = torch.randn(B)
+    lens = mk.cpu().sum(-1).long().clamp(min=1)
+    gid = torch.randint(0, 9, (B,))
+    gid[0] = 20  # singleton group
+    for b in range(B):
+        scores_tok[b, 0] = scores[b]
+    ref, _ = core_algos.compute_grpo_outcome_advantage(scores_tok, mk.cpu(), np.array(gid.tolist()))
+    got = ops.grpo_advantage(scores.cuda(), gid.cuda(), mk, 21)
+    torch.testing.assert_close(got.cpu(), ref, atol=1e-4, rtol=1e-4)
+
+
+def test_sampler_distribution_and_modes():
+    from verl_b200 import ops
+
+    torch.manual_seed(9)
+    V, n = 1000, 4096
+    logits = torch.randn(1, V, device="cuda").repeat(n, 1).contiguous()
+    step = torch.zeros(1, device="cuda", dtype=torch.long)
+    tok, lp = ops.sample(logits, seed=1234, step=step)
+    p = torch.softmax(logits[0], -1)
+    freq = torch.bincount(tok, minlength=V).float() / n
+    assert (freq - p).abs().sum().item() / 2 < 0.25
+    torch.testing.assert_close(lp, torch.log(p)[tok], atol=1e-5, rtol=1e-5)
+    tok2, _ = ops.sample(logits, seed=1234, step=step)
+    assert torch.equal(tok, tok2)  # same seed and step -> same draw
+    step += 1
+    tok3, _ = ops.sample(logits, seed=1234, step=step)
+    assert not torch.equal(tok, tok3)
+    tok, _ = ops.sample(logits, temperature=torch.zeros(n, device="cuda"), seed=1, step=step)
+    assert bool((tok == logits[0].argmax()).all())
+    tok, lp = ops.sample(logits, top_k=torch.full((n,), 5, device="cuda", dtype=torch.int32), seed=7, step=step)
+    top5 = logits[0].topk(5)
+    assert set(tok.unique().tolist()) <= set(top5.indices.tolist())
+    torch.testing.assert_close(lp, torch.log_softmax(top5.values, -1)[(tok[:, None] == top5.indices[None]).float().argmax(-1)],
+                               atol=1e-4, rtol=1e-4)
+    tok, _ = ops.sample(logits, top_p=torch.full((n,), 0.5, device="cuda"), seed=7, step=step)
+    sp, si = p.sort(descending=True)
+    kk = int((sp.cumsum(0) < 0.5).sum().item()) + 1
+    assert set(tok.unique().tolist()) <= set(si[:kk].tolist())
+    # bf16 logits
+    tok, _ = ops.sample(logits.bfloat16(), temperature=torch.zeros(n, device="cuda"), seed=1, step=step)
+    assert bool((tok == logits[0].bfloat16().float().argmax()).all())
+
+
+@pytest.mark.parametrize("B,Hq,Hk,D,bs,maxlen", [(5, 28, 4, 128, 16, 700), (3, 4, 2, 64, 16, 300), (2, 32, 4, 128, 32, 3000),
+                                                 (4, 40, 8, 128, 16, 150)])
+def test_paged_decode_attention(B, Hq, Hk, D, bs, maxlen):
+    from verl_b200 import ops
+
+    torch.manual_seed(10)
+    lens = torch.randint(1, maxlen, (B,), dtype=torch.int32)
+    lens[0] = maxlen
+    nblk_per = (maxlen + bs - 1) // bs
+    NB = B * nblk_per + 3
+    kc = torch.zeros(NB, Hk, bs, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    table = torch.randperm(NB)[: B * nblk_per].reshape(B, nblk_per).int().cuda()
+    # fill through the cache-write kernel
+    for b in range(B):
+        L = int(lens[b])
+        k_new = torch.randn(L, Hk, D, device="cuda").bfloat16()
+        v_new = torch.randn(L, Hk, D, device="cuda").bfloat16()
+        pos = torch.arange(L, device="cuda")
+        slots = table[b].long()[pos // bs] * bs + pos % bs
+        ops.kv_cache_write(k_new, v_new, slots, kc, vc)
+    q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+    ref = ops.paged_decode_attention(q.cpu().float(), kc.cpu().float(), vc.cpu().float(), table.cpu(), lens)
+    for splits in (1, ops.decode_workspace(B, Hq, Hk, D, maxlen, "cuda")[0]):
+        out = ops.paged_decode_attention(q, kc, vc, table, lens.cuda(), num_splits=splits)
+        _bf16_close(out, ref, ulps=4)

@@ -1,0 +1,172 @@
+"""Architecture description shared by the training engine, the rollout engine and the
+checkpoint code. Mirrors the HF ``config.json`` fields of the supported families
+(Llama, Qwen2/2.5, Qwen3, Qwen3-MoE); the reference gets these models from
+``transformers`` (verl/utils/model.py:103-127)."""
+
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+from typing import Any
+
+_ARCH_TO_TYPE = {
+    "LlamaForCausalLM": "llama",
+    "MistralForCausalLM": "llama",
+    "Qwen2ForCausalLM": "qwen2",
+    "Qwen3ForCausalLM": "qwen3",
+    "Qwen3MoeForCausalLM": "qwen3_moe",
+    "LlamaForTokenClassification": "llama",
+    "Qwen2ForTokenClassification": "qwen2",
+    "Qwen3ForTokenClassification": "qwen3",
+}
+_TYPE_TO_ARCH = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
+                 "qwen3_moe": "Qwen3MoeForCausalLM"}
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "qwen2"
+    vocab_size: int = 152064
+    hidden_size: int = 3584
+    intermediate_size: int = 18944
+    num_hidden_layers: int = 28
+    num_attention_heads: int = 28
+    num_key_value_heads: int = 4
+    head_dim: int | None = None
+    rope_theta: float = 1e6
+    rms_norm_eps: float = 1e-6
+    max_position_embeddings: int = 32768
+    tie_word_embeddings: bool = False
+    attention_bias: bool | None = None  # None -> family default (qwen2: True)
+    qk_norm: bool | None = None  # None -> family default (qwen3*: True)
+    # MoE (qwen3_moe)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    router_aux_loss_coef: float = 0.0
+    # token-classification / value head
+    num_labels: int = 0
+    bos_token_id: int | None = None
+    eos_token_id: int | None = 2
+    pad_token_id: int | None = None
+    extra: dict = field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        if self.attention_bias is None:
+            self.attention_bias = self.model_type == "qwen2"
+        if self.qk_norm is None:
+            self.qk_norm = self.model_type in ("qwen3", "qwen3_moe")
+
+    # ------------------------------------------------------------------ derived
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    def num_parameters(self, include_embedding: bool = True) -> int:
+        H, L = self.hidden_size, self.num_hidden_layers
+        attn = H * (self.q_size + 2 * self.kv_size) + self.q_size * H
+        if self.attention_bias:
+            attn += self.q_size + 2 * self.kv_size
+        if self.qk_norm:
+            attn += 2 * self.head_dim
+        if self.is_moe:
+            mlp = self.num_experts * 3 * H * self.moe_intermediate_size + H * self.num_experts
+        else:
+            mlp = 3 * H * self.intermediate_size
+        total = L * (attn + mlp + 2 * H) + H
+        if include_embedding:
+            total += self.vocab_size * H * (1 if self.tie_word_embeddings else 2)
+        return total
+
+    # --------------------------------------------------------------- (de)serialise
+    @classmethod
+    def from_hf_dict(cls, d: dict[str, Any]) -> "ModelConfig":
+        mt = d.get("model_type")
+        if mt is None:
+            archs = d.get("architectures") or ["Qwen2ForCausalLM"]
+            mt = _ARCH_TO_TYPE.get(archs[0], "qwen2")
+        known = {f for f in cls.__dataclass_fields__}
+        kw = {k: v for k, v in d.items() if k in known and k != "extra"}
+        kw["model_type"] = mt
+        if "num_local_experts" in d and "num_experts" not in d:
+            kw["num_experts"] = d["num_local_experts"]
+        eos = kw.get("eos_token_id")
+        if isinstance(eos, list):
+            kw["eos_token_id"] = eos[0]
+        cfg = cls(**kw)
+        cfg.extra = {k: v for k, v in d.items() if k not in known}
+        return cfg
+
+    @classmethod
+    def from_pretrained(cls, path: str | Path) -> "ModelConfig":
+        p = Path(path)
+        if p.is_dir():
+            p = p / "config.json"
+        return cls.from_hf_dict(json.loads(p.read_text()))
+
+    def to_hf_dict(self) -> dict[str, Any]:
+        d = asdict(self)
+        extra = d.pop("extra")
+        arch = _TYPE_TO_ARCH.get(self.model_type, "Qwen2ForCausalLM")
+        if self.num_labels:
+            arch = arch.replace("ForCausalLM", "ForTokenClassification")
+        d["architectures"] = [arch]
+        d["torch_dtype"] = "bfloat16"
+        if not self.is_moe:
+            for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob",
+                      "router_aux_loss_coef"):
+                d.pop(k)
+        if not self.num_labels:
+            d.pop("num_labels")
+        d.update({k: v for k, v in extra.items() if k not in d})
+        return d
+
+    def save_pretrained(self, path: str | Path) -> None:
+        p = Path(path)
+        p.mkdir(parents=True, exist_ok=True)
+        (p / "config.json").write_text(json.dumps(self.to_hf_dict(), indent=2))
+
+
+# Named architectures used by the benchmarks and tests (random-init, no download needed).
+PRESETS: dict[str, dict] = {
+    "tiny-qwen2": dict(model_type="qwen2", vocab_size=2048, hidden_size=256, intermediate_size=688,
+                       num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, rope_theta=1e6,
+                       tie_word_embeddings=True, eos_token_id=2),
+    "qwen2.5-0.5b": dict(model_type="qwen2", vocab_size=151936, hidden_size=896, intermediate_size=4864,
+                         num_hidden_layers=24, num_attention_heads=14, num_key_value_heads=2, rope_theta=1e6,
+                         tie_word_embeddings=True, eos_token_id=151645),
+    "qwen2.5-7b": dict(model_type="qwen2", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+                       num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6,
+                       eos_token_id=151645),
+    "qwen2.5-32b": dict(model_type="qwen2", vocab_size=152064, hidden_size=5120, intermediate_size=27648,
+                        num_hidden_layers=64, num_attention_heads=40, num_key_value_heads=8, rope_theta=1e6,
+                        eos_token_id=151645),
+    "qwen3-30b-a3b": dict(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                          num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                          rope_theta=1e6, num_experts=128, num_experts_per_tok=8, moe_intermediate_size=768,
+                          eos_token_id=151645),
+    "tiny-qwen3-moe": dict(model_type="qwen3_moe", vocab_size=2048, hidden_size=256, intermediate_size=512,
+                           num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                           num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, eos_token_id=2),
+    "llama-3-8b": dict(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+                       num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, rope_theta=5e5,
+                       rms_norm_eps=1e-5, eos_token_id=128001),
+}
+
+
+def preset(name: str, **overrides) -> ModelConfig:
+    kw = dict(PRESETS[name])
+    kw.update(overrides)
+    return ModelConfig(**kw)

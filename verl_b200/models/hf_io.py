@@ -1,0 +1,142 @@
+"""HuggingFace checkpoint compatibility: parameter-name mapping between the HF layout
+(separate q/k/v and gate/up projections, per-expert MoE tensors) and this framework's fused
+layout, plus safetensors import/export.
+
+The reference loads/saves HF models directly through ``transformers``
+(verl/utils/checkpoint/fsdp_checkpoint_manager.py:303-348) and regroups fused tensors for
+inference engines in verl/utils/megatron_utils.py:846 (default_tp_concat_fn).
+"""
+
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Iterable, Iterator
+
+import torch
+
+from .config import ModelConfig
+
+
+def hf_to_native_state_dict(cfg: ModelConfig, hf_sd: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """Fuse an HF state dict into native parameter names/shapes."""
+    out: dict[str, torch.Tensor] = {}
+    g = lambda k: hf_sd[k]  # noqa: E731
+    out["embed_tokens.weight"] = g("model.embed_tokens.weight")
+    out["norm.weight"] = g("model.norm.weight")
+    if "lm_head.weight" in hf_sd and not cfg.tie_word_embeddings:
+        out["lm_head.weight"] = g("lm_head.weight")
+    if "score.weight" in hf_sd:
+        out["score.weight"] = g("score.weight")
+    for i in range(cfg.num_hidden_layers):
+        p, n = f"model.layers.{i}.", f"layers.{i}."
+        out[n + "input_layernorm.weight"] = g(p + "input_layernorm.weight")
+        out[n + "post_attention_layernorm.weight"] = g(p + "post_attention_layernorm.weight")
+        out[n + "self_attn.qkv_proj.weight"] = torch.cat(
+            [g(p + f"self_attn.{x}_proj.weight") for x in "qkv"], dim=0)
+        if cfg.attention_bias:
+            out[n + "self_attn.qkv_proj.bias"] = torch.cat([g(p + f"self_attn.{x}_proj.bias") for x in "qkv"], dim=0)
+        out[n + "self_attn.o_proj.weight"] = g(p + "self_attn.o_proj.weight")
+        if cfg.qk_norm:
+            out[n + "self_attn.q_norm.weight"] = g(p + "self_attn.q_norm.weight")
+            out[n + "self_attn.k_norm.weight"] = g(p + "self_attn.k_norm.weight")
+        if cfg.is_moe:
+            out[n + "mlp.gate.weight"] = g(p + "mlp.gate.weight")
+            out[n + "mlp.gate_up_proj"] = torch.stack([
+                torch.cat([g(p + f"mlp.experts.{e}.gate_proj.weight"), g(p + f"mlp.experts.{e}.up_proj.weight")], 0)
+                for e in range(cfg.num_experts)])
+            out[n + "mlp.down_proj"] = torch.stack(
+                [g(p + f"mlp.experts.{e}.down_proj.weight") for e in range(cfg.num_experts)])
+        else:
+            out[n + "mlp.gate_up_proj.weight"] = torch.cat(
+                [g(p + "mlp.gate_proj.weight"), g(p + "mlp.up_proj.weight")], dim=0)
+            out[n + "mlp.down_proj.weight"] = g(p + "mlp.down_proj.weight")
+    return out
+
+
+def native_to_hf_items(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tensor]]) -> Iterator[tuple[str, torch.Tensor]]:
+    """Stream (hf_name, tensor) pairs from native (name, tensor) pairs, splitting fused tensors.
+    Works one parameter at a time so it can drive a weight-sync generator."""
+    for name, t in named:
+        if name == "embed_tokens.weight":
+            yield "model.embed_tokens.weight", t
+        elif name == "norm.weight":
+            yield "model.norm.weight", t
+        elif name in ("lm_head.weight", "score.weight"):
+            yield name, t
+        elif name.startswith("layers."):
+            _, idx, rest = name.split(".", 2)
+            p = f"model.layers.{idx}."
+            if rest == "self_attn.qkv_proj.weight" or rest == "self_attn.qkv_proj.bias":
+                kind = rest.rsplit(".", 1)[1]
+                q, k, v = t.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=0)
+                yield p + f"self_attn.q_proj.{kind}", q
+                yield p + f"self_attn.k_proj.{kind}", k
+                yield p + f"self_attn.v_proj.{kind}", v
+            elif rest == "mlp.gate_up_proj.weight":
+                gte, up = t.chunk(2, dim=0)
+                yield p + "mlp.gate_proj.weight", gte
+                yield p + "mlp.up_proj.weight", up
+            elif rest == "mlp.gate_up_proj":
+                for e in range(t.shape[0]):
+                    gte, up = t[e].chunk(2, dim=0)
+                    yield p + f"mlp.experts.{e}.gate_proj.weight", gte
+                    yield p + f"mlp.experts.{e}.up_proj.weight", up
+            elif rest == "mlp.down_proj":
+                for e in range(t.shape[0]):
+                    yield p + f"mlp.experts.{e}.down_proj.weight", t[e]
+            else:
+                yield p + rest, t
+        else:
+            yield name, t
+
+
+def native_to_hf_state_dict(cfg: ModelConfig, sd: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    return {k: v for k, v in native_to_hf_items(cfg, sd.items())}
+
+
+def save_hf_checkpoint(cfg: ModelConfig, native_sd: dict[str, torch.Tensor], path: str | Path,
+                       dtype: torch.dtype = torch.bfloat16, max_shard_bytes: int = 5 * 1024**3) -> None:
+    """Write ``config.json`` + sharded ``model-xxxxx-of-xxxxx.safetensors`` (+ index) in HF layout."""
+    from safetensors.torch import save_file
+
+    path = Path(path)
+    path.mkdir(parents=True, exist_ok=True)
+    cfg.save_pretrained(path)
+    shards, cur, cur_bytes = [], {}, 0
+    for k, v in native_to_hf_items(cfg, native_sd.items()):
+        t = v.detach().to(dtype).cpu().contiguous()
+        nbytes = t.numel() * t.element_size()
+        if cur and cur_bytes + nbytes > max_shard_bytes:
+            shards.append(cur)
+            cur, cur_bytes = {}, 0
+        cur[k] = t
+        cur_bytes += nbytes
+    if cur:
+        shards.append(cur)
+    if len(shards) == 1:
+        save_file(shards[0], str(path / "model.safetensors"), metadata={"format": "pt"})
+        return
+    index = {"metadata": {"total_size": 0}, "weight_map": {}}
+    for i, sh in enumerate(shards):
+        fname = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+        save_file(sh, str(path / fname), metadata={"format": "pt"})
+        for k, t in sh.items():
+            index["weight_map"][k] = fname
+            index["metadata"]["total_size"] += t.numel() * t.element_size()
+    (path / "model.safetensors.index.json").write_text(json.dumps(index, indent=2))
+
+
+def load_hf_checkpoint(path: str | Path) -> tuple[ModelConfig, dict[str, torch.Tensor]]:
+    """Read an HF directory (safetensors, single or sharded) into a native state dict."""
+    from safetensors.torch import load_file
+
+    path = Path(path)
+    cfg = ModelConfig.from_pretrained(path)
+    hf_sd: dict[str, torch.Tensor] = {}
+    files = sorted(path.glob("*.safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no safetensors files under {path}")
+    for f in files:
+        hf_sd.update(load_file(str(f)))
+    return cfg, hf_to_native_state_dict(cfg, hf_sd)

@@ -1,0 +1,277 @@
+"""Decoder-only transformer (Llama / Qwen2 / Qwen3 / Qwen3-MoE families) written against
+:mod:`verl_b200.ops`, operating on packed (remove-padding) token streams.
+
+The reference takes these models from HF ``transformers`` and monkey-patches attention and the
+lm_head (verl/models/transformers/monkey_patch.py:286-493, dense_common.py:72-193). Here the
+layer is a short sequence of native ops:
+
+    rmsnorm(+residual) -> qkv GEMM(+bias) -> [q/k norm] -> RoPE -> varlen causal GQA attention
+    -> o GEMM -> rmsnorm(+residual) -> gate|up GEMM -> SwiGLU -> down GEMM
+
+q/k/v and gate/up weights are stored fused ([q;k;v] rows, [gate;up] rows); HF checkpoints are
+split/merged by :mod:`verl_b200.models.hf_io`.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from .config import ModelConfig
+
+
+@dataclass
+class PackedBatch:
+    """Inputs of one packed forward: T tokens from B sequences."""
+
+    input_ids: torch.Tensor  # [T] int64
+    position_ids: torch.Tensor  # [T] int64
+    cu_seqlens: torch.Tensor  # [B+1] int32
+    max_seqlen: int
+
+    @classmethod
+    def from_padded(cls, input_ids: torch.Tensor, attention_mask: torch.Tensor, position_ids: torch.Tensor | None = None):
+        """Remove padding from [B,S] inputs. Returns (batch, flat_indices) where flat_indices are the
+        positions of the kept tokens in the flattened [B*S] layout (for scattering outputs back)."""
+        mask = attention_mask.bool()
+        seqlens = mask.sum(-1).int()
+        idx = torch.nonzero(mask.flatten(), as_tuple=False).flatten()
+        ids = input_ids.flatten()[idx]
+        if position_ids is None:
+            position_ids = (torch.cumsum(mask.long(), -1) - 1).clamp(min=0)
+        pos = position_ids.flatten()[idx]
+        cu = torch.zeros(seqlens.numel() + 1, dtype=torch.int32, device=input_ids.device)
+        cu[1:] = torch.cumsum(seqlens, 0)
+        return cls(ids, pos, cu, int(seqlens.max().item()) if seqlens.numel() else 0), idx
+
+
+class Linear(nn.Module):
+    def __init__(self, in_f: int, out_f: int, bias: bool, dtype, device, std: float = 0.02):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(out_f, in_f, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_f, dtype=dtype, device=device)) if bias else None
+        self._std = std
+
+    def reset_parameters(self, generator=None):
+        with torch.no_grad():
+            self.weight.copy_(
+                torch.empty(self.weight.shape, dtype=torch.float32, device=self.weight.device).normal_(
+                    0.0, self._std, generator=generator))
+            if self.bias is not None:
+                self.bias.zero_()
+
+    def forward(self, x):
+        return ops.linear(x, self.weight, self.bias)
+
+
+class RMSNormWeight(nn.Module):
+    def __init__(self, dim: int, dtype, device):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
+
+
+class DenseMLP(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.gate_up_proj = Linear(cfg.hidden_size, 2 * cfg.intermediate_size, False, dtype, device)
+        self.down_proj = Linear(cfg.intermediate_size, cfg.hidden_size, False, dtype, device)
+
+    def forward(self, x):
+        return self.down_proj(ops.swiglu(self.gate_up_proj(x)))
+
+
+class MoEMLP(nn.Module):
+    """Top-k routed experts (Qwen3-MoE): softmax router, top-k, optional renormalisation.
+
+    Tokens are sorted by expert and each expert's slice goes through the GEMM kernels;
+    ``last_routing`` keeps (top-k ids, weights) of the latest forward for router replay
+    (verl/utils/megatron/router_replay_utils.py)."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.E, self.k = cfg.num_experts, cfg.num_experts_per_tok
+        self.norm_topk = cfg.norm_topk_prob
+        I, H = cfg.moe_intermediate_size, cfg.hidden_size
+        self.gate = Linear(H, self.E, False, dtype, device)
+        self.gate_up_proj = nn.Parameter(torch.empty(self.E, 2 * I, H, dtype=dtype, device=device))
+        self.down_proj = nn.Parameter(torch.empty(self.E, H, I, dtype=dtype, device=device))
+        self.last_routing = None
+        self.replay_routing = None
+
+    def reset_parameters(self, generator=None):
+        self.gate.reset_parameters(generator)
+        with torch.no_grad():
+            for p in (self.gate_up_proj, self.down_proj):
+                p.copy_(torch.empty(p.shape, dtype=torch.float32, device=p.device).normal_(0.0, 0.02, generator=generator))
+
+    def forward(self, x):
+        T, H = x.shape
+        logits = self.gate(x).float()
+        probs = torch.softmax(logits, dim=-1)
+        if self.replay_routing is not None:
+            top_i = self.replay_routing
+            top_w = probs.gather(-1, top_i)
+        else:
+            top_w, top_i = torch.topk(probs, self.k, dim=-1)
+        if self.norm_topk:
+            top_w = top_w / top_w.sum(-1, keepdim=True)
+        self.last_routing = top_i.detach()
+        flat_e = top_i.flatten()
+        order = torch.argsort(flat_e, stable=True)
+        tok = order // self.k
+        counts = torch.bincount(flat_e, minlength=self.E).tolist()
+        xs = x[tok]
+        outs = torch.empty(xs.shape[0], H, dtype=x.dtype, device=x.device)
+        start = 0
+        pieces = []
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            seg = xs[start : start + n]
+            # pad the slice to a multiple of 8 rows so the transposed (weight-gradient) operand stays 16-byte aligned
+            h = ops.swiglu(ops.linear(seg, self.gate_up_proj[e]))
+            pieces.append(ops.linear(h, self.down_proj[e]))
+            start += n
+        outs = torch.cat(pieces, dim=0) if pieces else outs
+        w = top_w.flatten()[order].to(x.dtype).unsqueeze(-1)
+        y = torch.zeros(T, H, dtype=x.dtype, device=x.device)
+        y.index_add_(0, tok, outs * w)
+        return y
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        self.qkv_proj = Linear(cfg.hidden_size, cfg.q_size + 2 * cfg.kv_size, cfg.attention_bias, dtype, device)
+        self.o_proj = Linear(cfg.q_size, cfg.hidden_size, False, dtype, device)
+        if cfg.qk_norm:
+            self.q_norm = RMSNormWeight(cfg.head_dim, dtype, device)
+            self.k_norm = RMSNormWeight(cfg.head_dim, dtype, device)
+
+    def forward(self, x, batch: PackedBatch, rope):
+        cfg = self.cfg
+        Hq, Hk, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        T = x.shape[0]
+        qkv = self.qkv_proj(x)
+        if cfg.qk_norm:
+            q, k, v = qkv.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=-1)
+            q, _ = ops.rmsnorm(q.reshape(T * Hq, D), self.q_norm.weight, cfg.rms_norm_eps)
+            k, _ = ops.rmsnorm(k.reshape(T * Hk, D), self.k_norm.weight, cfg.rms_norm_eps)
+            qkv = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v], dim=-1)
+        qkv = ops.rope_qkv(qkv, batch.position_ids, rope[0], rope[1], Hq, Hk, D)
+        q = qkv[:, : cfg.q_size].view(T, Hq, D)
+        k = qkv[:, cfg.q_size : cfg.q_size + cfg.kv_size].view(T, Hk, D)
+        v = qkv[:, cfg.q_size + cfg.kv_size :].view(T, Hk, D)
+        o = ops.attention_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, causal=True)
+        return self.o_proj(o.reshape(T, cfg.q_size))
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        self.input_layernorm = RMSNormWeight(cfg.hidden_size, dtype, device)
+        self.self_attn = Attention(cfg, dtype, device)
+        self.post_attention_layernorm = RMSNormWeight(cfg.hidden_size, dtype, device)
+        self.mlp = MoEMLP(cfg, dtype, device) if cfg.is_moe else DenseMLP(cfg, dtype, device)
+
+    def forward(self, hidden, residual, batch: PackedBatch, rope):
+        """(hidden, residual) -> (hidden, residual); the residual add is fused into the next norm."""
+        eps = self.cfg.rms_norm_eps
+        normed, residual = ops.rmsnorm(hidden, self.input_layernorm.weight, eps, residual)
+        attn = self.self_attn(normed, batch, rope)
+        normed, residual = ops.rmsnorm(attn, self.post_attention_layernorm.weight, eps, residual)
+        return self.mlp(normed), residual
+
+
+class CausalLM(nn.Module):
+    """Packed-sequence causal LM with an lm_head (policy / reference) or a value head (critic)."""
+
+    def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", value_head: bool = False):
+        super().__init__()
+        self.cfg = cfg
+        self.value_head = value_head or cfg.num_labels == 1
+        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers)])
+        self.norm = RMSNormWeight(cfg.hidden_size, dtype, device)
+        if self.value_head:
+            self.score = Linear(cfg.hidden_size, 1, False, dtype, device)
+            self.lm_head = None
+        elif cfg.tie_word_embeddings:
+            self.lm_head = None
+        else:
+            self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, False, dtype, device)
+        self.gradient_checkpointing = False
+
+    # ------------------------------------------------------------------ init
+    def init_weights(self, seed: int = 0):
+        gen = torch.Generator(device=self.embed_tokens.weight.device)
+        gen.manual_seed(seed)
+        with torch.no_grad():
+            w = self.embed_tokens.weight
+            w.copy_(torch.empty(w.shape, dtype=torch.float32, device=w.device).normal_(0.0, 0.02, generator=gen))
+        for m in self.modules():
+            if isinstance(m, (Linear, MoEMLP)):
+                m.reset_parameters(gen)
+        return self
+
+    @property
+    def lm_head_weight(self) -> torch.Tensor:
+        return self.embed_tokens.weight if self.lm_head is None else self.lm_head.weight
+
+    def rope(self, device) -> tuple[torch.Tensor, torch.Tensor]:
+        c = self.cfg
+        return ops.rope_tables(c.head_dim, c.max_position_embeddings, c.rope_theta, device)
+
+    # --------------------------------------------------------------- forward
+    def embed(self, batch: PackedBatch) -> torch.Tensor:
+        return ops.embedding(batch.input_ids, self.embed_tokens.weight)
+
+    def final_norm(self, hidden, residual) -> torch.Tensor:
+        out, _ = ops.rmsnorm(hidden, self.norm.weight, self.cfg.rms_norm_eps, residual)
+        return out
+
+    def forward_hidden(self, batch: PackedBatch) -> torch.Tensor:
+        """Final-norm hidden states [T,H] of a packed batch."""
+        hidden = self.embed(batch)
+        residual = None
+        rope = self.rope(hidden.device)
+        for layer in self.layers:
+            if self.gradient_checkpointing and torch.is_grad_enabled():
+                hidden, residual = torch.utils.checkpoint.checkpoint(layer, hidden, residual, batch, rope,
+                                                                     use_reentrant=False)
+            else:
+                hidden, residual = layer(hidden, residual, batch, rope)
+        return self.final_norm(hidden, residual)
+
+    def logprob_entropy(self, hidden: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0):
+        """Per-token log-prob of ``labels`` and entropy from final hidden states (fused, no logits)."""
+        return ops.lmhead_logprob_entropy(hidden, self.lm_head_weight, labels, temperature)
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        return ops.linear(hidden, self.lm_head_weight)
+
+    def values(self, hidden: torch.Tensor) -> torch.Tensor:
+        # the value head is a 1-row matrix: a dot product per token (bandwidth-bound, no tensor-core tile)
+        return (hidden.float() @ self.score.weight.float().t()).squeeze(-1)
+
+    def forward(self, batch: PackedBatch, labels: Optional[torch.Tensor] = None, temperature: float = 1.0):
+        hidden = self.forward_hidden(batch)
+        if self.value_head:
+            return self.values(hidden)
+        if labels is None:
+            return self.logits(hidden)
+        return self.logprob_entropy(hidden, labels, temperature)
+
+
+def build_model(cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", value_head: bool = False, seed: int = 0,
+                init: bool = True) -> CausalLM:
+    m = CausalLM(cfg, dtype=dtype, device=device, value_head=value_head)
+    if init:
+        m.init_weights(seed)
+    return m

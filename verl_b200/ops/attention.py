@@ -1,0 +1,104 @@
+"""Attention entry points.
+
+* :func:`attention_varlen` — causal GQA attention over packed (remove-padding) sequences for
+  training and prefill. On CUDA this currently calls the ``flash_attn`` varlen kernels (library
+  code, as the reference does through HF ``attn_implementation=flash_attention_2``,
+  verl/workers/fsdp_workers.py:331); on CPU a per-sequence SDPA loop.
+* :func:`paged_decode_attention` / :func:`kv_cache_write` — the hand-written paged-KV decode
+  path of the native rollout engine.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+_flash = None
+
+
+def _flash_varlen():
+    global _flash
+    if _flash is None:
+        from flash_attn import flash_attn_varlen_func  # library kernel
+
+        _flash = flash_attn_varlen_func
+    return _flash
+
+
+def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int,
+                     causal: bool = True, softmax_scale: float | None = None) -> torch.Tensor:
+    """q [T,Hq,D], k/v [T,Hk,D] packed; cu_seqlens int32 [B+1]. Returns [T,Hq,D]."""
+    D = q.shape[-1]
+    scale = softmax_scale if softmax_scale is not None else D ** -0.5
+    if q.is_cuda:
+        return _flash_varlen()(q, k, v, cu_seqlens, cu_seqlens, max_seqlen, max_seqlen, softmax_scale=scale,
+                               causal=causal)
+    out = torch.empty_like(q)
+    G = q.shape[1] // k.shape[1]
+    bounds = cu_seqlens.tolist()
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        qs = q[s:e].transpose(0, 1).unsqueeze(0)
+        ks = k[s:e].repeat_interleave(G, dim=1).transpose(0, 1).unsqueeze(0)
+        vs = v[s:e].repeat_interleave(G, dim=1).transpose(0, 1).unsqueeze(0)
+        o = F.scaled_dot_product_attention(qs, ks, vs, is_causal=causal, scale=scale)
+        out[s:e] = o.squeeze(0).transpose(0, 1)
+    return out
+
+
+def kv_cache_write(k: torch.Tensor, v: torch.Tensor, slots: torch.Tensor, k_cache: torch.Tensor,
+                   v_cache: torch.Tensor) -> None:
+    """Scatter new keys/values [T,Hk,D] into the paged caches [NB,Hk,BS,D] at flat ``slots`` (int64, <0 skips)."""
+    T, Hk, D = k.shape
+    BS = k_cache.shape[2]
+    if k.is_cuda:
+        rc = _lib.fn("vb_kv_cache_write")(k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0), slots.data_ptr(),
+                                          k_cache.data_ptr(), v_cache.data_ptr(), T, Hk, D, BS, _lib.stream())
+        _lib.check(rc, "vb_kv_cache_write")
+        return
+    ok = slots >= 0
+    blk, off = slots[ok] // BS, slots[ok] % BS
+    k_cache[blk, :, off] = k[ok]
+    v_cache[blk, :, off] = v[ok]
+
+
+def decode_workspace(B: int, Hq: int, Hk: int, D: int, max_seq_len: int, device) -> tuple[int, torch.Tensor | None]:
+    """Split count and fp32 scratch for :func:`paged_decode_attention` at these sizes."""
+    if torch.device(device).type != "cuda":
+        return 1, None
+    splits = _lib.fn("vb_decode_num_splits")(B, Hk, max_seq_len)
+    work = torch.empty(B * Hq * splits * (D + 2), dtype=torch.float32, device=device) if splits > 1 else None
+    return splits, work
+
+
+def paged_decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                           seq_lens: torch.Tensor, scale: float | None = None, num_splits: int = 1,
+                           work: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One query token per sequence. q [B,Hq,D]; caches [NB,Hk,BS,D]; block_table int32 [B,max_blocks];
+    seq_lens int32 [B] (including the current token, already written to the cache)."""
+    B, Hq, D = q.shape
+    Hk, BS = k_cache.shape[1], k_cache.shape[2]
+    scale = scale if scale is not None else D ** -0.5
+    if out is None:
+        out = torch.empty_like(q)
+    if q.is_cuda:
+        if num_splits > 1 and work is None:
+            work = torch.empty(B * Hq * num_splits * (D + 2), dtype=torch.float32, device=q.device)
+        rc = _lib.fn("vb_paged_decode")(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                                        block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(), B, Hq, Hk,
+                                        D, BS, scale, num_splits, out.data_ptr(), out.stride(0), _lib.ptr(work),
+                                        _lib.stream())
+        _lib.check(rc, "vb_paged_decode")
+        return out
+    G = Hq // Hk
+    for b in range(B):
+        L = int(seq_lens[b])
+        nb = (L + BS - 1) // BS
+        blocks = block_table[b, :nb].long()
+        kk = k_cache[blocks].permute(1, 0, 2, 3).reshape(Hk, -1, D)[:, :L].float()
+        vv = v_cache[blocks].permute(1, 0, 2, 3).reshape(Hk, -1, D)[:, :L].float()
+        qq = q[b].float().reshape(Hk, G, D)
+        s = torch.einsum("hgd,hld->hgl", qq, kk) * scale
+        out[b] = torch.einsum("hgl,hld->hgd", torch.softmax(s, -1), vv).reshape(Hq, D).to(q.dtype)
+    return out

@@ -1,0 +1,204 @@
+"""Model ops (RMSNorm, RoPE, SwiGLU, embedding) as autograd functions over the native kernels.
+
+CUDA tensors always go to the hand-written kernels (bf16 storage, fp32 math); CPU tensors
+use an equivalent plain-torch path so the same model code runs in the CPU test tier.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+
+# --------------------------------------------------------------------------- RMSNorm
+def _rmsnorm_ref(x, w, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+
+
+class _RMSNormFn(torch.autograd.Function):
+    """y = rmsnorm(x + residual) * w; also returns the new residual stream (x + residual)."""
+
+    @staticmethod
+    def forward(ctx, x, residual, weight, eps):
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H)
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        if residual is not None:
+            r2 = residual.reshape(-1, H)
+            h = torch.empty_like(x2)
+            rc = _lib.fn("vb_rmsnorm_fwd")(x2.data_ptr(), r2.data_ptr(), weight.data_ptr(), y.data_ptr(), h.data_ptr(),
+                                           rstd.data_ptr(), rows, H, eps, _lib.stream())
+        else:
+            h = x2
+            rc = _lib.fn("vb_rmsnorm_fwd")(x2.data_ptr(), None, weight.data_ptr(), y.data_ptr(), None,
+                                           rstd.data_ptr(), rows, H, eps, _lib.stream())
+        _lib.check(rc, "vb_rmsnorm_fwd")
+        ctx.save_for_backward(h, weight, rstd)
+        ctx.has_res = residual is not None
+        ctx.shape = x.shape
+        if residual is not None:
+            return y.reshape(x.shape), h.reshape(x.shape)
+        return y.reshape(x.shape), x
+
+    @staticmethod
+    def backward(ctx, dy, dh):
+        h, weight, rstd = ctx.saved_tensors
+        H = h.shape[-1]
+        rows = h.shape[0]
+        dy2 = dy.reshape(-1, H).contiguous()
+        dres = dh.reshape(-1, H).contiguous() if dh is not None else None
+        dx = torch.empty_like(h)
+        parts = _lib.fn("vb_rmsnorm_bwd_parts")(rows)
+        dwp = torch.empty(parts, H, dtype=torch.float32, device=h.device)
+        main_grad = getattr(weight, "main_grad", None)
+        if main_grad is not None:
+            dw_buf, acc = main_grad, 1
+        else:
+            dw_buf, acc = torch.empty(H, dtype=torch.float32, device=h.device), 0
+        rc = _lib.fn("vb_rmsnorm_bwd")(dy2.data_ptr(), h.data_ptr(), weight.data_ptr(), rstd.data_ptr(),
+                                       _lib.ptr(dres), dx.data_ptr(), dwp.data_ptr(), dw_buf.data_ptr(), acc, rows, H,
+                                       _lib.stream())
+        _lib.check(rc, "vb_rmsnorm_bwd")
+        dx = dx.reshape(ctx.shape)
+        dw = None if main_grad is not None else dw_buf.to(weight.dtype)
+        # the gradient of the residual stream flows to both x and residual
+        return dx, (dx if ctx.has_res else None), dw, None
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: torch.Tensor | None = None):
+    """Returns ``(normed, new_residual)`` where ``new_residual = x + residual`` (or ``x``)."""
+    if x.is_cuda:
+        if residual is None and not torch.is_grad_enabled():
+            pass
+        return _RMSNormFn.apply(x.contiguous(), None if residual is None else residual.contiguous(), weight, eps)
+    h = x if residual is None else x + residual
+    return _rmsnorm_ref(h, weight, eps), h
+
+
+# ------------------------------------------------------------------------------ RoPE
+_rope_cache: dict = {}
+
+
+def rope_tables(head_dim: int, max_pos: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    key = (head_dim, max_pos, float(theta), str(device))
+    if key not in _rope_cache:
+        inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+        ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None]
+        _rope_cache[key] = (ang.cos().contiguous(), ang.sin().contiguous())
+    return _rope_cache[key]
+
+
+def _rope_ref(t, pos, cos_t, sin_t, n_heads, D, sign=1.0):
+    T = t.shape[0]
+    tf = t.float().reshape(T, n_heads, D)
+    c = cos_t[pos][:, None, :]
+    s = sin_t[pos][:, None, :] * sign
+    a, b = tf[..., : D // 2], tf[..., D // 2 :]
+    return torch.cat([a * c - b * s, b * c + a * s], -1).reshape(T, n_heads * D).to(t.dtype)
+
+
+class _RopeFn(torch.autograd.Function):
+    """In-place rotary embedding on the q and k slices of a packed qkv activation [T, (Hq+2Hk)*D]."""
+
+    @staticmethod
+    def forward(ctx, qkv, pos, cos_t, sin_t, Hq, Hk, D):
+        T = qkv.shape[0]
+        q = qkv[:, : Hq * D]
+        k = qkv[:, Hq * D : (Hq + Hk) * D]
+        rc = _lib.fn("vb_rope")(q.data_ptr(), k.data_ptr(), qkv.stride(0), qkv.stride(0), pos.data_ptr(),
+                                cos_t.data_ptr(), sin_t.data_ptr(), T, Hq, Hk, D, 0, _lib.stream())
+        _lib.check(rc, "vb_rope")
+        ctx.save_for_backward(pos, cos_t, sin_t)
+        ctx.dims = (Hq, Hk, D)
+        ctx.mark_dirty(qkv)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, dqkv):
+        pos, cos_t, sin_t = ctx.saved_tensors
+        Hq, Hk, D = ctx.dims
+        dqkv = dqkv.contiguous().clone() if not dqkv.is_contiguous() else dqkv.clone()
+        T = dqkv.shape[0]
+        q = dqkv[:, : Hq * D]
+        k = dqkv[:, Hq * D : (Hq + Hk) * D]
+        rc = _lib.fn("vb_rope")(q.data_ptr(), k.data_ptr(), dqkv.stride(0), dqkv.stride(0), pos.data_ptr(),
+                                cos_t.data_ptr(), sin_t.data_ptr(), T, Hq, Hk, D, 1, _lib.stream())
+        _lib.check(rc, "vb_rope")
+        return dqkv, None, None, None, None, None, None
+
+
+def rope_qkv(qkv: torch.Tensor, pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor, Hq: int, Hk: int, D: int):
+    """Apply rotate-half RoPE to the q and k parts of packed ``qkv`` ([T, (Hq+2Hk)*D]); v is untouched."""
+    if qkv.is_cuda:
+        return _RopeFn.apply(qkv, pos, cos_t, sin_t, Hq, Hk, D)
+    q = _rope_ref(qkv[:, : Hq * D], pos, cos_t, sin_t, Hq, D)
+    k = _rope_ref(qkv[:, Hq * D : (Hq + Hk) * D], pos, cos_t, sin_t, Hk, D)
+    return torch.cat([q, k, qkv[:, (Hq + Hk) * D :]], dim=-1)
+
+
+# ---------------------------------------------------------------------------- SwiGLU
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        T, I2 = gu.shape
+        out = torch.empty(T, I2 // 2, dtype=gu.dtype, device=gu.device)
+        rc = _lib.fn("vb_swiglu_fwd")(gu.data_ptr(), out.data_ptr(), T, I2 // 2, _lib.stream())
+        _lib.check(rc, "vb_swiglu_fwd")
+        ctx.save_for_backward(gu)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        T, I2 = gu.shape
+        dgu = torch.empty_like(gu)
+        rc = _lib.fn("vb_swiglu_bwd")(gu.data_ptr(), dout.contiguous().data_ptr(), dgu.data_ptr(), T, I2 // 2,
+                                      _lib.stream())
+        _lib.check(rc, "vb_swiglu_bwd")
+        return dgu
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up = [gate | up]`` along the last dim."""
+    if gate_up.is_cuda:
+        shape = gate_up.shape
+        out = _SwiGLUFn.apply(gate_up.reshape(-1, shape[-1]).contiguous())
+        return out.reshape(*shape[:-1], shape[-1] // 2)
+    g, u = gate_up.chunk(2, dim=-1)
+    return F.silu(g) * u
+
+
+# ------------------------------------------------------------------------- Embedding
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, weight):
+        T = ids.numel()
+        H = weight.shape[1]
+        out = torch.empty(T, H, dtype=weight.dtype, device=weight.device)
+        rc = _lib.fn("vb_embedding_fwd")(ids.data_ptr(), weight.data_ptr(), out.data_ptr(), T, H, _lib.stream())
+        _lib.check(rc, "vb_embedding_fwd")
+        ctx.save_for_backward(ids, weight)
+        return out.reshape(*ids.shape, H)
+
+    @staticmethod
+    def backward(ctx, dy):
+        ids, weight = ctx.saved_tensors
+        T = ids.numel()
+        H = weight.shape[1]
+        main_grad = getattr(weight, "main_grad", None)
+        buf = main_grad if main_grad is not None else torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+        rc = _lib.fn("vb_embedding_bwd")(ids.data_ptr(), dy.reshape(T, H).contiguous().data_ptr(), buf.data_ptr(), T, H,
+                                         _lib.stream())
+        _lib.check(rc, "vb_embedding_bwd")
+        return None, (None if main_grad is not None else buf.to(weight.dtype))
+
+
+def embedding(ids: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    if weight.is_cuda:
+        return _EmbeddingFn.apply(ids.contiguous(), weight)
+    return F.embedding(ids, weight)
