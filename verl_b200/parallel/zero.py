@@ -1,0 +1,330 @@
+"""ZeRO-3 parameter sharding with per-unit gather / recompute / reduce-scatter.
+
+This is the engine-side replacement for torch FSDP1/FSDP2 as the reference uses them
+(verl/workers/fsdp_workers.py:529-564, verl/utils/fsdp_utils.py:507-551). One *unit* is a group of
+parameters that is gathered and released together (a decoder layer, the embedding, the head).
+
+Storage (per rank, flat):
+  * ``master`` fp32, ``exp_avg`` fp32, ``exp_avg_sq`` fp32, ``grad`` fp32 — 1/W of every unit
+  * ``shard16`` — the working-dtype copy of ``master`` that feeds the all-gather
+Every unit's padded flat parameter vector is split into W equal contiguous shards, so the
+all-gather output is the flat vector itself and parameters are views into it.
+
+With W == 1 the gathered buffer *is* ``shard16`` and the gradient buffer *is* ``grad``: no copies,
+weight-gradient GEMMs accumulate straight into the optimizer's gradient (``param.main_grad``).
+
+:func:`unit_call` runs a unit's computation under activation checkpointing: forward gathers,
+computes without saving activations and releases; backward gathers again, recomputes with autograd,
+back-propagates, reduce-scatters the unit's gradient into the fp32 shard and releases.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+
+@dataclass
+class ZeroUnit:
+    name: str
+    params: list  # nn.Parameter objects
+    names: list  # fully-qualified names
+    numel: int = 0
+    padded: int = 0
+    shard: int = 0
+    offset: int = 0  # offset of this unit's shard inside the rank-flat buffers
+    offsets: list = field(default_factory=list)  # per-parameter offsets inside the unit's flat vector
+    full: Optional[torch.Tensor] = None  # gathered working-dtype buffer (None when released)
+    full_grad: Optional[torch.Tensor] = None  # unit-sized fp32 gradient buffer during backward (W > 1)
+    gather_count: int = 0
+
+
+class ZeroShardedParams:
+    """Owns the sharded state of a model and the gather / reduce-scatter mechanics."""
+
+    def __init__(self, units: Sequence[tuple[str, nn.Module | list]], *, group=None, work_dtype=torch.bfloat16,
+                 device="cuda", trainable: bool = True, align: int = 256, comm=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.work_dtype = work_dtype
+        self.device = torch.device(device)
+        self.trainable = trainable
+        self.comm = comm  # optional accelerated collectives (peer-memory kernels); falls back to torch.distributed
+        self.units: list[ZeroUnit] = []
+        self._anchor = None
+        seen: set[int] = set()
+        off = 0
+        for name, mod in units:
+            named = list(mod.named_parameters()) if isinstance(mod, nn.Module) else list(mod)
+            named = [(n, p) for n, p in named if id(p) not in seen]
+            seen.update(id(p) for _, p in named)
+            u = ZeroUnit(name=name, params=[p for _, p in named], names=[f"{name}.{n}" if name else n for n, _ in named])
+            cur = 0
+            for p in u.params:
+                u.offsets.append(cur)
+                cur += (p.numel() + 7) // 8 * 8  # keep every tensor 16-byte aligned in bf16
+            u.numel = cur
+            quantum = align * self.world
+            u.padded = (cur + quantum - 1) // quantum * quantum
+            u.shard = u.padded // self.world
+            u.offset = off
+            off += u.shard
+            self.units.append(u)
+        self.total_shard = off
+        dev = self.device
+        self.shard16 = torch.zeros(off, dtype=work_dtype, device=dev)
+        if trainable:
+            self.master = torch.zeros(off, dtype=torch.float32, device=dev)
+            self.exp_avg = torch.zeros(off, dtype=torch.float32, device=dev)
+            self.exp_avg_sq = torch.zeros(off, dtype=torch.float32, device=dev)
+            self.grad = torch.zeros(off, dtype=torch.float32, device=dev)
+        else:
+            self.master = self.exp_avg = self.exp_avg_sq = self.grad = None
+        self._load_from_params()
+        if self.world == 1:
+            for u in self.units:
+                self._bind(u, self.shard16[u.offset : u.offset + u.shard],
+                           self.grad[u.offset : u.offset + u.shard] if trainable else None)
+                u.full = self.shard16[u.offset : u.offset + u.shard]
+        else:
+            for u in self.units:
+                self._unbind(u)
+
+    # ------------------------------------------------------------- initial load
+    @torch.no_grad()
+    def _load_from_params(self):
+        """Copy the module's current parameter values (identical on all ranks) into this rank's shards."""
+        for u in self.units:
+            lo, hi = self.rank * u.shard, (self.rank + 1) * u.shard
+            for p, o in zip(u.params, u.offsets):
+                s, e = max(o, lo), min(o + p.numel(), hi)
+                if s >= e:
+                    continue
+                src = p.detach().reshape(-1)[s - o : e - o]
+                dst = slice(u.offset + s - lo, u.offset + e - lo)
+                if self.trainable:
+                    self.master[dst].copy_(src.float())
+                self.shard16[dst].copy_(src.to(self.work_dtype))
+
+    def _bind(self, u: ZeroUnit, full: torch.Tensor, full_grad: Optional[torch.Tensor]):
+        for p, o in zip(u.params, u.offsets):
+            p.data = full[o : o + p.numel()].view(p.shape)
+            if full_grad is not None and p.requires_grad:
+                p.main_grad = full_grad[o : o + p.numel()].view(p.shape)
+
+    def _unbind(self, u: ZeroUnit):
+        empty = torch.empty(0, dtype=self.work_dtype, device=self.device)
+        for p in u.params:
+            p.data = empty
+            if hasattr(p, "main_grad"):
+                del p.main_grad
+
+    # ---------------------------------------------------------- gather / release
+    def gather(self, u: ZeroUnit, for_backward: bool = False):
+        u.gather_count += 1
+        if self.world == 1:
+            return
+        if u.full is None:
+            full = torch.empty(u.padded, dtype=self.work_dtype, device=self.device)
+            src = self.shard16[u.offset : u.offset + u.shard]
+            if self.comm is not None:
+                self.comm.all_gather(full, src)
+            else:
+                dist.all_gather_into_tensor(full, src, group=self.group)
+            u.full = full
+        if for_backward and self.trainable and u.full_grad is None:
+            u.full_grad = torch.zeros(u.padded, dtype=torch.float32, device=self.device)
+        self._bind(u, u.full, u.full_grad if for_backward else None)
+
+    def release(self, u: ZeroUnit):
+        u.gather_count -= 1
+        if self.world == 1 or u.gather_count > 0:
+            return
+        self._unbind(u)
+        u.full = None
+        u.full_grad = None
+
+    def fold_param_grads(self, u: ZeroUnit):
+        """Gradients that autograd left in ``p.grad`` (ops without a fused accumulate) go to ``main_grad``."""
+        for p in u.params:
+            if p.grad is not None:
+                if hasattr(p, "main_grad"):
+                    p.main_grad.add_(p.grad.float())
+                p.grad = None
+
+    def reduce_grads(self, u: ZeroUnit):
+        """Sum the unit's gradient over ranks and add this rank's slice into the fp32 gradient shard."""
+        self.fold_param_grads(u)
+        if self.world == 1 or not self.trainable or u.full_grad is None:
+            return
+        dst = self.grad[u.offset : u.offset + u.shard]
+        if self.comm is not None:
+            self.comm.reduce_scatter_add(dst, u.full_grad)
+        elif dist.get_backend(self.group) == "gloo":
+            dist.all_reduce(u.full_grad, group=self.group)
+            dst.add_(u.full_grad[self.rank * u.shard : (self.rank + 1) * u.shard])
+        else:
+            tmp = torch.empty(u.shard, dtype=torch.float32, device=self.device)
+            dist.reduce_scatter_tensor(tmp, u.full_grad, group=self.group)
+            dst.add_(tmp)
+        u.full_grad = None
+
+    # ------------------------------------------------------------ whole-model views
+    def gather_all(self):
+        for u in self.units:
+            self.gather(u)
+
+    def release_all(self):
+        for u in self.units:
+            self.release(u)
+
+    def full_tensor(self, u: ZeroUnit, idx: int, dtype=None) -> torch.Tensor:
+        """One full parameter of a (currently gathered) unit."""
+        p, o = u.params[idx], u.offsets[idx]
+        t = u.full[o : o + p.numel()].view(p.shape)
+        return t if dtype is None else t.to(dtype)
+
+    def named_full_tensors(self, dtype=None):
+        """Generator of (name, full tensor), gathering one unit at a time (weight export / sync).
+        Role of ``get_per_tensor_param`` (verl/workers/engine/fsdp/transformer_impl.py:635-671)."""
+        for u in self.units:
+            self.gather(u)
+            try:
+                for i, name in enumerate(u.names):
+                    yield name, self.full_tensor(u, i, dtype)
+            finally:
+                self.release(u)
+
+    @torch.no_grad()
+    def load_full_state(self, state: dict[str, torch.Tensor], strict: bool = True):
+        """Set parameters (and fp32 masters) from full tensors keyed by parameter name."""
+        missing = []
+        for u in self.units:
+            lo, hi = self.rank * u.shard, (self.rank + 1) * u.shard
+            for name, p, o in zip(u.names, u.params, u.offsets):
+                if name not in state:
+                    missing.append(name)
+                    continue
+                s, e = max(o, lo), min(o + p.numel(), hi)
+                if s >= e:
+                    continue
+                src = state[name].reshape(-1)[s - o : e - o].to(self.device)
+                dst = slice(u.offset + s - lo, u.offset + e - lo)
+                if self.trainable:
+                    self.master[dst].copy_(src.float())
+                self.shard16[dst].copy_(src.to(self.work_dtype))
+        if strict and missing:
+            raise KeyError(f"missing parameters: {missing[:5]}{'...' if len(missing) > 5 else ''}")
+        return missing
+
+    def zero_grad(self):
+        if self.trainable:
+            self.grad.zero_()
+
+    # ------------------------------------------------------------ sharded state io
+    def shard_state(self) -> dict:
+        """This rank's shard of model / optimizer state plus the layout needed to re-assemble it."""
+        layout = [{"name": u.name, "names": u.names, "shapes": [tuple(p.shape) for p in u.params], "offsets": u.offsets,
+                   "numel": u.numel, "padded": u.padded, "shard": u.shard, "offset": u.offset} for u in self.units]
+        out = {"layout": layout, "world_size": self.world, "rank": self.rank, "shard16": self.shard16.cpu()}
+        if self.trainable:
+            out.update(master=self.master.cpu(), exp_avg=self.exp_avg.cpu(), exp_avg_sq=self.exp_avg_sq.cpu())
+        return out
+
+    @torch.no_grad()
+    def load_shard_state(self, st: dict, load_optimizer: bool = True):
+        assert st["world_size"] == self.world, f"checkpoint world size {st['world_size']} != {self.world}"
+        self.shard16.copy_(st["shard16"].to(self.device))
+        if self.trainable and "master" in st:
+            self.master.copy_(st["master"].to(self.device))
+            if load_optimizer:
+                self.exp_avg.copy_(st["exp_avg"].to(self.device))
+                self.exp_avg_sq.copy_(st["exp_avg_sq"].to(self.device))
+
+    # ------------------------------------------------------------------ offload
+    def offload(self, params: bool = True, optimizer: bool = True):
+        """Move shards to pinned host memory (param_offload / optimizer_offload)."""
+        def to_host(t):
+            if t is None or not t.is_cuda:
+                return t
+            h = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+            h.copy_(t, non_blocking=True)
+            return h
+
+        if params and self.world > 1:
+            self.shard16 = to_host(self.shard16)
+        if optimizer and self.trainable:
+            self.master, self.exp_avg, self.exp_avg_sq = map(to_host, (self.master, self.exp_avg, self.exp_avg_sq))
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+
+    def reload(self):
+        dev = self.device
+        for name in ("shard16", "master", "exp_avg", "exp_avg_sq"):
+            t = getattr(self, name)
+            if t is not None and t.device != dev:
+                setattr(self, name, t.to(dev, non_blocking=True))
+
+
+class _UnitFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, zero: ZeroShardedParams, unit: ZeroUnit, fn: Callable, mask: tuple, *tensors):
+        ctx.zero, ctx.unit, ctx.fn, ctx.mask = zero, unit, fn, mask
+        tensors = tensors[:-1]  # the last input is the graph anchor (see unit_call)
+        zero.gather(unit)
+        try:
+            with torch.no_grad():
+                outs = fn(*_expand(mask, tensors))
+        finally:
+            zero.release(unit)
+        ctx.save_for_backward(*tensors)
+        ctx.single = not isinstance(outs, tuple)
+        return outs
+
+    @staticmethod
+    def backward(ctx, *grads):
+        zero, unit = ctx.zero, ctx.unit
+        inputs = [t.detach().requires_grad_(t.is_floating_point()) for t in ctx.saved_tensors]
+        zero.gather(unit, for_backward=True)
+        try:
+            with torch.enable_grad():
+                outs = ctx.fn(*_expand(ctx.mask, inputs))
+            outs = (outs,) if ctx.single else outs
+            pairs = [(o, g) for o, g in zip(outs, grads) if g is not None and isinstance(o, torch.Tensor) and o.requires_grad]
+            if pairs:
+                torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+            zero.reduce_grads(unit)
+        finally:
+            zero.release(unit)
+        return (None, None, None, None) + tuple(t.grad if t.requires_grad else None for t in inputs) + (None,)
+
+
+def _expand(mask, tensors):
+    it = iter(tensors)
+    return [next(it) if m else None for m in mask]
+
+
+def unit_call(zero: ZeroShardedParams, unit: ZeroUnit, fn: Callable, *args):
+    """Run ``fn(*args)`` (tensor or None arguments) with the unit's parameters gathered. With grad enabled
+    the call is checkpointed: activations are recomputed in backward, and the unit's gradients are
+    reduce-scattered right after its backward."""
+    mask = tuple(a is not None for a in args)
+    tensors = [a for a in args if a is not None]
+    if torch.is_grad_enabled() and zero.trainable:
+        # a unit whose inputs carry no gradient (the embedding: integer ids) must still get a backward
+        # call for its parameters, so every call is anchored on a scalar that requires grad
+        if zero._anchor is None:
+            zero._anchor = torch.zeros(1, device=zero.device, requires_grad=True)
+        return _UnitFn.apply(zero, unit, fn, mask, *tensors, zero._anchor)
+    zero.gather(unit)
+    try:
+        with torch.no_grad():
+            return fn(*args)
+    finally:
+        zero.release(unit)

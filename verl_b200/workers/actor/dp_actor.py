@@ -1,0 +1,175 @@
+"""PPO actor on the native engine: ``compute_log_prob`` and ``update_policy``.
+
+Semantics follow ``DataParallelPPOActor`` (verl/workers/actor/dp_actor.py:113-669): mini-batch /
+micro-batch loops, dynamic batching by token budget, on-policy shortcut, policy-loss registry, KL and
+entropy terms, one optimizer step per mini-batch, metric names ``actor/*``.
+
+Loss normalisation is global: every micro-batch loss is divided by the token (or sequence) count of
+the whole mini-batch summed over data-parallel ranks, and gradients are *summed* across ranks by the
+engine's reduce-scatter, so the optimiser sees the gradient of the global mean regardless of how
+tokens are spread over ranks and micro-batches.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ... import ops
+from ...protocol import DataProto
+from ...trainer.ppo import core_algos
+from ...trainer.ppo.core_algos import agg_loss, get_policy_loss_fn, kl_penalty
+from ...utils.py_functional import append_to_dict
+from ...utils.seqlen_balancing import prepare_dynamic_batch, restore_dynamic_batch
+from ..engine.native import NativeEngine, _cfg
+
+__all__ = ["DataParallelPPOActor"]
+
+
+class DataParallelPPOActor:
+    def __init__(self, config, engine: NativeEngine):
+        self.config = config
+        self.engine = engine
+        self.device = engine.device
+        self.use_fused_loss = self.device.type == "cuda"
+
+    # ------------------------------------------------------------------ forward
+    def _forward_micro_batch(self, micro: DataProto, temperature: float, calculate_entropy: bool):
+        """Returns (log_probs [b,R], entropy [b,R]) for the response part of a micro-batch."""
+        b = micro.batch
+        input_ids = b["input_ids"].to(self.device)
+        mask = b["attention_mask"].to(self.device)
+        pos = b["position_ids"].to(self.device) if "position_ids" in b else None
+        if pos is not None and pos.dim() == 3:  # mrope layouts carry [b, 3|4, S]; text positions are row 0
+            pos = pos[:, 0]
+        R = b["responses"].shape[-1]
+        packed, rows, labels, bj = NativeEngine.response_rows(input_ids, mask, R, pos)
+        lp, ent = self.engine.forward_logprob(packed, rows, labels, temperature)
+        B = input_ids.shape[0]
+        log_probs = torch.zeros(B, R, dtype=torch.float32, device=self.device)
+        entropy = torch.zeros(B, R, dtype=torch.float32, device=self.device)
+        log_probs = log_probs.index_put((bj[:, 0], bj[:, 1]), lp)
+        if calculate_entropy:
+            entropy = entropy.index_put((bj[:, 0], bj[:, 1]), ent)
+        return log_probs, (entropy if calculate_entropy else None)
+
+    def _micro_batches(self, data: DataProto, max_token_len: Optional[int], micro_bsz: Optional[int], use_dyn: bool):
+        if use_dyn:
+            return prepare_dynamic_batch(data, max_token_len=max_token_len, dp_group=self.engine.group
+                                         if self.engine.world > 1 else None)
+        return data.split(micro_bsz or len(data)), None
+
+    # -------------------------------------------------------------- log-prob only
+    @torch.no_grad()
+    def compute_log_prob(self, data: DataProto, calculate_entropy: bool = False):
+        """data.batch: responses, input_ids, attention_mask, position_ids; meta: temperature,
+        micro_batch_size | (max_token_len, use_dynamic_bsz). Returns (log_probs [B,R], entropys | None)."""
+        temperature = data.meta_info["temperature"]
+        use_dyn = data.meta_info.get("use_dynamic_bsz", False)
+        sel = data.select(batch_keys=[k for k in ("responses", "input_ids", "attention_mask", "position_ids")
+                                      if k in data.batch.keys()])
+        micros, idx = self._micro_batches(sel, data.meta_info.get("max_token_len"),
+                                          data.meta_info.get("micro_batch_size"), use_dyn)
+        lps, ents = [], []
+        for mb in micros:
+            lp, ent = self._forward_micro_batch(mb, temperature, calculate_entropy)
+            lps.append(lp)
+            if calculate_entropy:
+                ents.append(ent)
+        log_probs = torch.cat(lps, dim=0)
+        entropys = torch.cat(ents, dim=0) if calculate_entropy else None
+        if use_dyn:
+            log_probs = restore_dynamic_batch(log_probs, idx)
+            if calculate_entropy:
+                entropys = restore_dynamic_batch(entropys, idx)
+        return log_probs, entropys
+
+    # -------------------------------------------------------------------- update
+    def _global_counts(self, mini: DataProto):
+        mask = mini.batch["response_mask"]
+        t = torch.tensor([float(mask.sum()), float((mask.sum(-1) > 0).sum())], dtype=torch.float64, device=self.device)
+        if self.engine.world > 1:
+            dist.all_reduce(t, group=self.engine.group)
+        return max(t[0].item(), 1.0), max(t[1].item(), 1.0)
+
+    def update_policy(self, data: DataProto) -> dict:
+        cfg = self.config
+        temperature = data.meta_info["temperature"]
+        keys = ["responses", "response_mask", "input_ids", "attention_mask", "position_ids", "old_log_probs", "advantages"]
+        for opt_key in ("ref_log_prob", "rollout_is_weights", "rollout_log_probs"):
+            if opt_key in data.batch.keys():
+                keys.append(opt_key)
+        keys = [k for k in keys if k in data.batch.keys()]
+        data = data.select(batch_keys=keys)
+        mini_bsz = min(int(cfg.ppo_mini_batch_size), len(data))
+        mini_batches = data.split(mini_bsz)
+        on_policy = len(mini_batches) == 1 and cfg.ppo_epochs == 1
+        loss_mode = _cfg(cfg.policy_loss, "loss_mode", "vanilla")
+        entropy_coeff = float(cfg.entropy_coeff)
+        calc_entropy = entropy_coeff != 0 or bool(_cfg(cfg, "calculate_entropy", False))
+        use_kl = bool(cfg.use_kl_loss)
+        metrics: dict = {}
+        engine = self.engine
+        for _ in range(cfg.ppo_epochs):
+            for mini in mini_batches:
+                n_tok, n_seq = self._global_counts(mini)
+                micros, _ = self._micro_batches(mini, int(cfg.ppo_max_token_len_per_gpu),
+                                                cfg.ppo_micro_batch_size_per_gpu, bool(cfg.use_dynamic_bsz))
+                engine.optimizer_zero_grad()
+                acc = {"actor/pg_loss": 0.0, "actor/kl_loss": 0.0}
+                for mb in micros:
+                    b = mb.batch
+                    mask = b["response_mask"].to(self.device).float()
+                    adv = b["advantages"].to(self.device)
+                    log_prob, entropy = self._forward_micro_batch(mb, temperature, calc_entropy)
+                    old = log_prob.detach() if on_policy else b["old_log_probs"].to(self.device)
+                    ref = b["ref_log_prob"].to(self.device) if use_kl else None
+                    isw = b["rollout_is_weights"].to(self.device) if "rollout_is_weights" in b else None
+                    fused_ok = (self.use_fused_loss and loss_mode == "vanilla" and cfg.loss_agg_mode == "token-mean")
+                    if fused_ok:
+                        loss, sums = ops.ppo_loss_fused(
+                            log_prob, old, adv, mask, entropy=entropy, ref_logp=ref, is_weight=isw,
+                            clip_low=_cfg(cfg, "clip_ratio_low", cfg.clip_ratio), clip_high=_cfg(cfg, "clip_ratio_high", cfg.clip_ratio),
+                            clip_c=_cfg(cfg, "clip_ratio_c", 3.0), kl_coef=float(cfg.kl_loss_coef) if use_kl else 0.0,
+                            kl_type=cfg.kl_loss_type.rstrip("+"), entropy_coeff=entropy_coeff, denom=n_tok)
+                        loss.backward()
+                        s = sums.tolist()
+                        n_local = max(s[6], 1.0)
+                        acc["actor/pg_loss"] += s[0] / n_tok
+                        if use_kl:
+                            acc["actor/kl_loss"] += s[4] / n_tok
+                        mb_metrics = {"actor/pg_clipfrac": s[1] / n_local, "actor/ppo_kl": s[2] / n_local,
+                                      "actor/pg_clipfrac_lower": s[3] / n_local}
+                        if calc_entropy:
+                            mb_metrics["actor/entropy"] = s[5] / n_local
+                    else:
+                        info = {"dp_size": 1, "batch_num_tokens": n_tok, "global_batch_size": n_seq,
+                                "loss_scale_factor": _cfg(cfg, "loss_scale_factor", None)}
+                        object.__setattr__(cfg, "global_batch_info", info) if not isinstance(cfg, dict) else cfg.update(
+                            global_batch_info=info)
+                        fn = get_policy_loss_fn(loss_mode)
+                        pg_loss, mb_metrics = fn(old_log_prob=old, log_prob=log_prob, advantages=adv, response_mask=mask,
+                                                 loss_agg_mode=cfg.loss_agg_mode, config=cfg, rollout_is_weights=isw)
+                        loss = pg_loss
+                        acc["actor/pg_loss"] += pg_loss.detach().item()
+                        if calc_entropy:
+                            ent_agg = agg_loss(entropy, mask, cfg.loss_agg_mode, **info)
+                            mb_metrics["actor/entropy"] = (entropy.detach() * mask).sum().item() / max(mask.sum().item(), 1.0)
+                            if entropy_coeff != 0:
+                                loss = loss - entropy_coeff * ent_agg
+                        if use_kl:
+                            kld = kl_penalty(log_prob, ref, cfg.kl_loss_type)
+                            kl_loss = agg_loss(kld, mask, cfg.loss_agg_mode, **info)
+                            loss = loss + float(cfg.kl_loss_coef) * kl_loss
+                            acc["actor/kl_loss"] += kl_loss.detach().item()
+                            mb_metrics["actor/kl_coef"] = float(cfg.kl_loss_coef)
+                        loss.backward()
+                    append_to_dict(metrics, mb_metrics)
+                grad_norm = engine.optimizer_step()
+                mini_metrics = {"actor/grad_norm": float(grad_norm), "actor/pg_loss": acc["actor/pg_loss"]}
+                if use_kl:
+                    mini_metrics["actor/kl_loss"] = acc["actor/kl_loss"]
+                append_to_dict(metrics, mini_metrics)
+        return metrics

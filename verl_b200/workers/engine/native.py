@@ -1,0 +1,325 @@
+"""The native training engine: packed-sequence transformer on hand-written kernels, ZeRO-3
+sharding with per-layer gather / recompute / reduce-scatter, fused AdamW on fp32 master shards.
+
+It fills the role of ``FSDPEngine`` / ``FSDPEngineWithLMHead`` / ``FSDPEngineWithValueHead``
+(verl/workers/engine/fsdp/transformer_impl.py:77-1057) and of the FSDP parts of
+``ActorRolloutRefWorker._build_model_optimizer`` (verl/workers/fsdp_workers.py:275-611).
+
+Differences by design:
+  * inputs are always packed (remove-padding) and only the positions that predict response tokens go
+    through the lm_head, which is fused with log-softmax / entropy (no logits tensor);
+  * mixed precision = bf16 working weights + fp32 master / moments / gradient shards;
+    weight-gradient GEMMs accumulate in fp32 directly into the gradient shard on one GPU;
+  * activation checkpointing and parameter gathering are the same mechanism (``unit_call``).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+from contextlib import contextmanager
+from pathlib import Path
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from ... import ops
+from ...models import CausalLM, ModelConfig, PackedBatch
+from ...models.hf_io import native_to_hf_items
+from ...parallel.zero import ZeroShardedParams, unit_call
+from .base import BaseEngine, EngineRegistry
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           "float16": torch.float16, "fp16": torch.float16}
+
+
+def _cfg(obj, key, default=None):
+    if obj is None:
+        return default
+    if isinstance(obj, dict):
+        v = obj.get(key, default)
+    else:
+        v = getattr(obj, key, default)
+    return default if v is None else v
+
+
+class NativeEngine(BaseEngine):
+    def __init__(self, model_config: ModelConfig, engine_config=None, optimizer_config=None, *, value_head: bool = False,
+                 device: Optional[str] = None, trainable: bool = True, group=None, seed: int = 0,
+                 state_dict: Optional[dict] = None, comm=None, gradient_checkpointing: bool = True):
+        self.model_config = model_config
+        self.engine_config = engine_config
+        self.optimizer_config = optimizer_config
+        self.value_head = value_head
+        if device is None:
+            device = f"cuda:{torch.cuda.current_device()}" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        self.trainable = trainable and not _cfg(engine_config, "forward_only", False)
+        self.group = group
+        self.seed = seed
+        self._init_state = state_dict
+        self.comm = comm
+        self.gradient_checkpointing = gradient_checkpointing
+        self.work_dtype = _DTYPES[_cfg(engine_config, "dtype", "bfloat16")] if self.device.type == "cuda" else torch.float32
+        self.step_count = 0
+        self.lr_step = 0
+        self.model: Optional[CausalLM] = None
+        self.zero: Optional[ZeroShardedParams] = None
+        self._offloaded = False
+
+    # ------------------------------------------------------------------- build
+    def initialize(self):
+        cfg = self.model_config
+        self.model = CausalLM(cfg, dtype=self.work_dtype, device=self.device, value_head=self.value_head)
+        self.model.init_weights(self.seed)
+        if self._init_state is not None:
+            missing, unexpected = self.model.load_state_dict(
+                {k: v.to(self.work_dtype) for k, v in self._init_state.items()}, strict=False)
+            self._init_state = None
+        m = self.model
+        tied = m.lm_head is None and not m.value_head
+        units = []
+        if tied:
+            units.append(("", [("embed_tokens.weight", m.embed_tokens.weight), ("norm.weight", m.norm.weight)]))
+        else:
+            units.append(("", [("embed_tokens.weight", m.embed_tokens.weight)]))
+        for i, layer in enumerate(m.layers):
+            units.append((f"layers.{i}", layer))
+        if not tied:
+            head = [("norm.weight", m.norm.weight)]
+            if m.value_head:
+                head.append(("score.weight", m.score.weight))
+            else:
+                head.append(("lm_head.weight", m.lm_head.weight))
+            units.append(("", head))
+        self.zero = ZeroShardedParams(units, group=self.group, work_dtype=self.work_dtype, device=self.device,
+                                      trainable=self.trainable, comm=self.comm)
+        self._embed_unit = self.zero.units[0]
+        self._layer_units = self.zero.units[1 : 1 + cfg.num_hidden_layers]
+        self._head_unit = self.zero.units[0] if tied else self.zero.units[-1]
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+        if self.trainable:
+            dev = self.device
+            self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+            self._scale = torch.ones(1, dtype=torch.float32, device=dev)
+            self._skip = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        return self
+
+    @property
+    def world(self) -> int:
+        return self.zero.world
+
+    def get_data_parallel_size(self) -> int:
+        return self.zero.world
+
+    def get_data_parallel_rank(self) -> int:
+        return self.zero.rank
+
+    def get_data_parallel_group(self):
+        return self.group
+
+    # -------------------------------------------------------------- mode / offload
+    @contextmanager
+    def train_mode(self, **kwargs):
+        self._enter_mode("train")
+        try:
+            yield self
+        finally:
+            self._exit_mode("train")
+
+    @contextmanager
+    def eval_mode(self, **kwargs):
+        self._enter_mode("eval")
+        try:
+            yield self
+        finally:
+            self._exit_mode("eval")
+
+    def _enter_mode(self, mode, **kwargs):
+        if self._offloaded:
+            self.to(str(self.device))
+
+    def _exit_mode(self, mode):
+        if _cfg(self.engine_config, "param_offload", False) or _cfg(self.engine_config, "optimizer_offload", False):
+            self.to("cpu", model=_cfg(self.engine_config, "param_offload", False),
+                    optimizer=_cfg(self.engine_config, "optimizer_offload", False))
+
+    def to(self, device: str, model: bool = True, optimizer: bool = True, grad: bool = True):
+        if torch.device(device).type == "cpu" and self.device.type == "cuda":
+            self.zero.offload(params=model, optimizer=optimizer)
+            self._offloaded = True
+        else:
+            self.zero.reload()
+            self._offloaded = False
+
+    # ------------------------------------------------------------------ forward
+    def _forward_hidden_rows(self, batch: PackedBatch, rows: Optional[torch.Tensor]):
+        """Final-norm input pieces (hidden, residual) restricted to ``rows`` of the packed stream."""
+        m, z = self.model, self.zero
+        rope = m.rope(self.device)
+        hidden = unit_call(z, self._embed_unit, lambda: m.embed(batch))
+        residual = None
+        ckpt = self.gradient_checkpointing or z.world > 1
+        for layer, unit in zip(m.layers, self._layer_units):
+            if ckpt or not torch.is_grad_enabled():
+                hidden, residual = unit_call(z, unit, lambda h, r, layer=layer: layer(h, r, batch, rope), hidden, residual)
+            else:
+                hidden, residual = layer(hidden, residual, batch, rope)
+        if rows is not None:
+            hidden, residual = hidden[rows], residual[rows]
+        return hidden, residual
+
+    def forward_logprob(self, batch: PackedBatch, rows: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0):
+        """Log-prob of ``labels[i]`` predicted at packed position ``rows[i]`` (+ entropy), both fp32."""
+        m, z = self.model, self.zero
+        hidden, residual = self._forward_hidden_rows(batch, rows)
+
+        def head(h, r):
+            return m.logprob_entropy(m.final_norm(h, r), labels, temperature)
+
+        return unit_call(z, self._head_unit, head, hidden, residual)
+
+    def forward_values(self, batch: PackedBatch, rows: torch.Tensor):
+        m, z = self.model, self.zero
+        hidden, residual = self._forward_hidden_rows(batch, rows)
+        return unit_call(z, self._head_unit, lambda h, r: m.values(m.final_norm(h, r)), hidden, residual)
+
+    def forward_logits(self, batch: PackedBatch, rows: Optional[torch.Tensor] = None):
+        m, z = self.model, self.zero
+        hidden, residual = self._forward_hidden_rows(batch, rows)
+        return unit_call(z, self._head_unit, lambda h, r: m.logits(m.final_norm(h, r)), hidden, residual)
+
+    # --------------------------------------------------------- response bookkeeping
+    @staticmethod
+    def response_rows(input_ids: torch.Tensor, attention_mask: torch.Tensor, response_length: int,
+                      position_ids: Optional[torch.Tensor] = None):
+        """Pack a left-padded-prompt / right-padded-response batch and locate, for every existing
+        response token, the packed row that predicts it.
+
+        Returns (packed batch, rows [N], labels [N], (b, j) coordinates of the N response tokens)."""
+        B, S = input_ids.shape
+        P = S - response_length
+        packed, idx = PackedBatch.from_padded(input_ids, attention_mask, position_ids)
+        inv = torch.full((B * S,), -1, dtype=torch.long, device=input_ids.device)
+        inv[idx] = torch.arange(idx.numel(), device=input_ids.device)
+        resp_exists = attention_mask[:, P:].bool()
+        bj = torch.nonzero(resp_exists, as_tuple=False)
+        src_flat = bj[:, 0] * S + (P - 1) + bj[:, 1]
+        rows = inv[src_flat]
+        labels = input_ids[:, P:][resp_exists]
+        return packed, rows, labels, bj
+
+    # ---------------------------------------------------------------- optimizer
+    def optimizer_zero_grad(self):
+        self.zero.zero_grad()
+
+    def _lr(self) -> float:
+        oc = self.optimizer_config
+        base = float(_cfg(oc, "lr", 1e-6))
+        total = int(_cfg(oc, "total_training_steps", -1))
+        warm = int(_cfg(oc, "lr_warmup_steps", -1))
+        if warm < 0:
+            warm = int(float(_cfg(oc, "lr_warmup_steps_ratio", 0.0)) * max(total, 0))
+        step = self.lr_step
+        kind = _cfg(oc, "lr_scheduler_type", "constant")
+        if step < warm:
+            return base * step / max(1, warm)
+        if kind == "cosine" and total > 0:
+            import math
+
+            min_ratio = float(_cfg(oc, "min_lr_ratio", 0.0) or 0.0)
+            prog = (step - warm) / max(1, total - warm)
+            cyc = float(_cfg(oc, "num_cycles", 0.5))
+            coef = (1 - min_ratio) * 0.5
+            return base * max(min_ratio, math.cos(math.pi * cyc * 2.0 * prog) * coef + (1 + min_ratio) * 0.5)
+        return base
+
+    def lr_scheduler_step(self):
+        self.lr_step += 1
+        return self._lr()
+
+    def optimizer_step(self) -> float:
+        """Global grad-norm, clip, fused AdamW on the shards. Returns the (pre-clip) gradient norm; a
+        non-finite norm skips the update (verl/workers/actor/dp_actor.py:391-415)."""
+        z, oc = self.zero, self.optimizer_config
+        clip = float(_cfg(oc, "clip_grad", 1.0))
+        lr = self._lr()
+        betas = tuple(_cfg(oc, "betas", (0.9, 0.999)))
+        wd = float(_cfg(oc, "weight_decay", 0.01))
+        eps = float(_cfg(oc, "eps", 1e-8))
+        self.step_count += 1
+        if self.device.type == "cuda":
+            self._sumsq.zero_()
+            ops.sumsq_into(z.grad, self._sumsq)
+            if z.world > 1:
+                dist.all_reduce(self._sumsq, group=self.group)
+            ops.clip_coef(self._sumsq, clip, 1.0, self._scale, self._skip, self._norm)
+            ops.adamw_step(z.master, z.grad, z.exp_avg, z.exp_avg_sq, z.shard16, lr=lr, betas=betas, eps=eps,
+                           weight_decay=wd, step=self.step_count, scale=self._scale, skip=self._skip)
+            norm = self._norm
+        else:
+            sq = z.grad.double().pow(2).sum().reshape(1)
+            if z.world > 1:
+                dist.all_reduce(sq, group=self.group)
+            norm = sq.sqrt().float()
+            if torch.isfinite(norm).all():
+                coef = min(1.0, clip / (norm.item() + 1e-6)) if clip > 0 else 1.0
+                g = z.grad * coef
+                b1, b2 = betas
+                z.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
+                z.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+                bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
+                z.master.mul_(1 - lr * wd)
+                z.master.addcdiv_(z.exp_avg / bc1, (z.exp_avg_sq / bc2).sqrt() + eps, value=-lr)
+                z.shard16.copy_(z.master.to(z.shard16.dtype))
+            else:
+                self.step_count -= 1
+        z.zero_grad()
+        return norm
+
+    # --------------------------------------------------------------- weights out
+    def get_per_tensor_param(self, dtype: Optional[torch.dtype] = None):
+        """Generator of (HF parameter name, full tensor): one unit is gathered at a time."""
+        if self._offloaded:
+            self.to(str(self.device))
+        return native_to_hf_items(self.model_config, self.zero.named_full_tensors(dtype))
+
+    def native_named_tensors(self):
+        return self.zero.named_full_tensors()
+
+    def full_state_dict(self, dtype=torch.bfloat16, to_cpu: bool = True) -> dict:
+        out = {}
+        for k, v in self.zero.named_full_tensors():
+            t = v.detach().to(dtype)
+            out[k] = t.cpu() if to_cpu else t.clone()
+        return out
+
+    # ---------------------------------------------------------------- checkpoint
+    def save_checkpoint(self, local_path: str, hdfs_path=None, global_step: int = 0, max_ckpt_to_keep=None,
+                        save_contents=("model", "optimizer", "extra"), **kwargs):
+        """verl FSDP layout: ``model_world_size_{W}_rank_{r}.pt``, ``optim_...``, ``extra_state_...``,
+        ``fsdp_config.json``, ``huggingface/`` (verl/utils/checkpoint/fsdp_checkpoint_manager.py:56-362)."""
+        from ...utils.checkpoint.native_checkpoint import save_engine_checkpoint
+
+        save_engine_checkpoint(self, local_path, global_step=global_step, save_contents=save_contents)
+
+    def load_checkpoint(self, local_path: str, hdfs_path=None, del_local_after_load: bool = False,
+                        load_contents=("model", "optimizer", "extra"), **kwargs):
+        from ...utils.checkpoint.native_checkpoint import load_engine_checkpoint
+
+        load_engine_checkpoint(self, local_path, load_contents=load_contents)
+
+
+@EngineRegistry.register(model_type="language_model", backend=["fsdp", "fsdp2", "native"], device=["cuda", "cpu"])
+class NativeEngineWithLMHead(NativeEngine):
+    pass
+
+
+@EngineRegistry.register(model_type="value_model", backend=["fsdp", "fsdp2", "native"], device=["cuda", "cpu"])
+class NativeEngineWithValueHead(NativeEngine):
+    def __init__(self, *args, **kwargs):
+        kwargs["value_head"] = True
+        super().__init__(*args, **kwargs)
