@@ -57,7 +57,7 @@ struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : (BN == 64) ? 8 : 10;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort flag
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
@@ -478,20 +478,30 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.out_fp32 = out_fp32; p.accumulate = accumulate; p.status = status;
-  const bool small_n = N <= 128;
-  if (!a_mn && !b_mn) {
-    return small_n ? launch_gemm<128, false, false, EPI_STORE>(A, B, lda, ldb, p, stream)
-                   : launch_gemm<256, false, false, EPI_STORE>(A, B, lda, ldb, p, stream);
-  } else if (!a_mn && b_mn) {
-    return small_n ? launch_gemm<128, false, true, EPI_STORE>(A, B, lda, ldb, p, stream)
-                   : launch_gemm<256, false, true, EPI_STORE>(A, B, lda, ldb, p, stream);
-  } else if (a_mn && b_mn) {
-    return small_n ? launch_gemm<128, true, true, EPI_STORE>(A, B, lda, ldb, p, stream)
-                   : launch_gemm<256, true, true, EPI_STORE>(A, B, lda, ldb, p, stream);
-  } else {
-    return small_n ? launch_gemm<128, true, false, EPI_STORE>(A, B, lda, ldb, p, stream)
-                   : launch_gemm<256, true, false, EPI_STORE>(A, B, lda, ldb, p, stream);
+  // Tile width: the widest BN that still yields about one tile per SM. Skinny problems (decode: M <= 128)
+  // fall to BN = 64 / 32 so that the weight matrix is streamed by (nearly) all SMs.
+  const int num_m = (M + BM - 1) / BM;
+  const int want = vb_num_sms() * 4 / 5;
+  auto tiles = [&](int bn) { return num_m * ((N + bn - 1) / bn); };
+  int bn = 256;
+  if (N <= 128 || tiles(256) < want) bn = 128;
+  const bool kk = !a_mn && !b_mn;
+  if (kk && bn == 128 && tiles(128) < want) bn = 64;
+  if (kk && bn == 64 && tiles(64) < want) bn = 32;
+  if (N <= 32 && kk) bn = 32;
+  else if (N <= 64 && kk) bn = bn < 64 ? bn : 64;
+#define VB_DISPATCH(AMN, BMN)                                                              \
+  (bn == 256 ? launch_gemm<256, AMN, BMN, EPI_STORE>(A, B, lda, ldb, p, stream)             \
+             : launch_gemm<128, AMN, BMN, EPI_STORE>(A, B, lda, ldb, p, stream))
+  if (kk) {
+    if (bn == 64) return launch_gemm<64, false, false, EPI_STORE>(A, B, lda, ldb, p, stream);
+    if (bn == 32) return launch_gemm<32, false, false, EPI_STORE>(A, B, lda, ldb, p, stream);
+    return VB_DISPATCH(false, false);
   }
+  if (!a_mn && b_mn) return VB_DISPATCH(false, true);
+  if (a_mn && b_mn) return VB_DISPATCH(true, true);
+  return VB_DISPATCH(true, false);
+#undef VB_DISPATCH
 }
 
 // Number of vocab splits the fused lm_head kernel uses for (T, V); the caller sizes

@@ -1,0 +1,582 @@
+"""Native continuous-batching rollout engine with a paged KV cache.
+
+Replaces the vLLM / SGLang servers the reference launches (verl/workers/rollout/vllm_rollout/
+vllm_async_server.py, sglang_rollout/*). The scheduler and block manager are C++
+(``csrc/scheduler.cpp``); the model runner executes the same transformer weights as the training
+engine with the hand-written kernels: prefill = packed varlen attention + KV-cache write, decode =
+paged-KV attention, one CUDA graph per padded batch size, sampling fused into one kernel that also
+returns the log-prob of the sampled token (what the trainer stores as ``rollout_log_probs``).
+
+Token-in / token-out API: :meth:`add_request`, :meth:`step`, :meth:`generate`, :meth:`abort_request`,
+:meth:`sleep` / :meth:`wake_up` (drop / re-create the KV cache), :meth:`update_weights`.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import time
+from dataclasses import dataclass, field
+from typing import Iterable, Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..models import CausalLM, ModelConfig
+from ..models.hf_io import hf_to_native_state_dict
+from ..ops import _lib
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_k: int = -1
+    top_p: float = 1.0
+    max_tokens: int = 512
+    logprobs: bool = True
+    ignore_eos: bool = False
+    stop_token_ids: tuple = ()
+    n: int = 1
+
+    @classmethod
+    def from_dict(cls, d: Optional[dict]) -> "SamplingParams":
+        d = dict(d or {})
+        if "max_new_tokens" in d and "max_tokens" not in d:
+            d["max_tokens"] = d.pop("max_new_tokens")
+        if d.get("logprobs") is None:
+            d.pop("logprobs", None)
+        elif not isinstance(d["logprobs"], bool):
+            d["logprobs"] = d["logprobs"] not in (0, False)
+        known = {f for f in cls.__dataclass_fields__}
+        return cls(**{k: v for k, v in d.items() if k in known})
+
+
+@dataclass
+class TokenOutput:
+    """Result of one request (verl/workers/rollout/replica.py:32)."""
+
+    token_ids: list
+    log_probs: Optional[list] = None
+    routed_experts: Optional[object] = None
+    stop_reason: Optional[str] = None  # completed | aborted | length
+    num_preempted: int = 0
+    request_id: Optional[str] = None
+
+
+@dataclass
+class _Request:
+    rid: str
+    sid: int
+    params: SamplingParams
+    prompt_len: int
+    logprobs: list = field(default_factory=list)
+    done: bool = False
+    stop_reason: Optional[str] = None
+
+
+def _sched_lib():
+    lib = _lib.load()
+    if not getattr(lib, "_sched_bound", False):
+        c = ctypes
+        P, I, L = c.c_void_p, c.c_int, c.c_longlong
+        lib.vb_sched_create.argtypes, lib.vb_sched_create.restype = [I, I, I, I, I, I], P
+        lib.vb_sched_destroy.argtypes, lib.vb_sched_destroy.restype = [P], None
+        lib.vb_sched_add.argtypes, lib.vb_sched_add.restype = [P, L, P, I, I], I
+        lib.vb_sched_step.argtypes, lib.vb_sched_step.restype = [P], I
+        lib.vb_sched_get_step.argtypes, lib.vb_sched_get_step.restype = [P] * 10 + [I], I
+        lib.vb_sched_commit.argtypes, lib.vb_sched_commit.restype = [P, P, P, P], None
+        lib.vb_sched_output.argtypes, lib.vb_sched_output.restype = [P, L, P, I], I
+        lib.vb_sched_preempt_count.argtypes, lib.vb_sched_preempt_count.restype = [P, L], I
+        lib.vb_sched_remove.argtypes, lib.vb_sched_remove.restype = [P, L], I
+        lib.vb_sched_reset_prefix_cache.argtypes, lib.vb_sched_reset_prefix_cache.restype = [P], None
+        lib.vb_sched_stats.argtypes, lib.vb_sched_stats.restype = [P, P], None
+        lib._sched_bound = True
+    return lib
+
+
+class Scheduler:
+    """Thin Python handle on the C++ scheduler."""
+
+    def __init__(self, num_blocks, block_size, max_num_seqs, max_batched_tokens, max_model_len, prefix_caching=True):
+        self.lib = _sched_lib()
+        self.h = self.lib.vb_sched_create(num_blocks, block_size, max_num_seqs, max_batched_tokens, max_model_len,
+                                          int(prefix_caching))
+        self.block_size = block_size
+        self.max_blocks = (max_model_len + block_size - 1) // block_size
+        cap_s, cap_t = max_num_seqs + 8, max_batched_tokens + max_num_seqs + 8
+        self.seq_ids = np.zeros(cap_s, np.int64)
+        self.seq_ntok = np.zeros(cap_s, np.int32)
+        self.seq_start = np.zeros(cap_s, np.int32)
+        self.seq_prefill = np.zeros(cap_s, np.int32)
+        self.seq_total = np.zeros(cap_s, np.int32)
+        self.tokens = np.zeros(cap_t, np.int64)
+        self.positions = np.zeros(cap_t, np.int64)
+        self.slots = np.zeros(cap_t, np.int64)
+        self.block_tables = np.zeros((cap_s, self.max_blocks), np.int32)
+        self.done = np.zeros(cap_s, np.int32)
+
+    def __del__(self):
+        try:
+            if self.h:
+                self.lib.vb_sched_destroy(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+    def add(self, sid: int, prompt: list[int], max_new_tokens: int) -> int:
+        arr = np.asarray(prompt, dtype=np.int32)
+        return self.lib.vb_sched_add(self.h, sid, arr.ctypes.data, len(arr), max_new_tokens)
+
+    def step(self) -> tuple[int, int]:
+        n = self.lib.vb_sched_step(self.h)
+        if n == 0:
+            return 0, 0
+        p = lambda a: a.ctypes.data  # noqa: E731
+        t = self.lib.vb_sched_get_step(self.h, p(self.seq_ids), p(self.seq_ntok), p(self.seq_start), p(self.seq_prefill),
+                                       p(self.seq_total), p(self.tokens), p(self.positions), p(self.slots),
+                                       p(self.block_tables), self.max_blocks)
+        return n, t
+
+    def commit(self, new_tokens: np.ndarray, finished: np.ndarray) -> np.ndarray:
+        n = len(new_tokens)
+        self.lib.vb_sched_commit(self.h, new_tokens.ctypes.data, finished.ctypes.data, self.done.ctypes.data)
+        return self.done[:n]
+
+    def output(self, sid: int, cap: int) -> list[int]:
+        buf = np.zeros(max(cap, 1), np.int32)
+        n = self.lib.vb_sched_output(self.h, sid, buf.ctypes.data, len(buf))
+        return buf[: max(n, 0)].tolist()
+
+    def preempt_count(self, sid: int) -> int:
+        return self.lib.vb_sched_preempt_count(self.h, sid)
+
+    def remove(self, sid: int) -> bool:
+        return bool(self.lib.vb_sched_remove(self.h, sid))
+
+    def reset_prefix_cache(self):
+        self.lib.vb_sched_reset_prefix_cache(self.h)
+
+    def stats(self) -> dict:
+        out = np.zeros(6, np.int64)
+        self.lib.vb_sched_stats(self.h, out.ctypes.data)
+        return dict(zip(("waiting", "running", "free_pages", "preempted", "prefix_hits", "prefix_queries"), out.tolist()))
+
+
+class NativeRolloutEngine:
+    def __init__(self, model: CausalLM, *, max_num_seqs: int = 256, max_model_len: int = 2048,
+                 max_num_batched_tokens: int = 8192, block_size: int = 16, num_blocks: Optional[int] = None,
+                 gpu_memory_utilization: float = 0.5, enable_prefix_caching: bool = True, enforce_eager: bool = False,
+                 seed: int = 0, eos_token_id: Optional[int] = None, cudagraph_capture_sizes: Optional[list] = None):
+        self.model = model
+        self.cfg: ModelConfig = model.cfg
+        self.device = model.embed_tokens.weight.device
+        self.dtype = model.embed_tokens.weight.dtype
+        self.on_gpu = self.device.type == "cuda"
+        self.max_num_seqs = max_num_seqs
+        self.max_model_len = max_model_len
+        self.max_num_batched_tokens = max(max_num_batched_tokens, 16)
+        self.block_size = block_size
+        self.enable_prefix_caching = enable_prefix_caching
+        self.enforce_eager = enforce_eager or not self.on_gpu or self.cfg.is_moe
+        self.seed = seed
+        self.eos = self.cfg.eos_token_id if eos_token_id is None else eos_token_id
+        self.gpu_memory_utilization = gpu_memory_utilization
+        self._num_blocks_arg = num_blocks
+        self.k_cache: list = []
+        self.v_cache: list = []
+        self.sched: Optional[Scheduler] = None
+        self.requests: dict[int, _Request] = {}
+        self.by_rid: dict[str, int] = {}
+        self._next_sid = 0
+        self._graphs: dict[int, tuple] = {}
+        self._capture_sizes = cudagraph_capture_sizes
+        self.step_counter = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0}
+        self.wake_up()
+
+    # ----------------------------------------------------------------- memory
+    def _page_bytes(self) -> int:
+        c = self.cfg
+        return 2 * c.num_hidden_layers * c.num_key_value_heads * self.block_size * c.head_dim * 2
+
+    def wake_up(self, tags: Optional[list] = None):
+        """(Re-)create the KV cache and scheduler state. ``tags`` may name "kv_cache" / "weights" as in the
+        reference's multi-stage wake-up; weights are owned by the caller, so only "kv_cache" acts here."""
+        if tags is not None and "kv_cache" not in tags:
+            return
+        if self.sched is not None and self.k_cache:
+            return
+        if self._num_blocks_arg is not None:
+            nb = self._num_blocks_arg
+        elif self.on_gpu:
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = int(min(free * 0.9, total * self.gpu_memory_utilization))
+            nb = max(budget // self._page_bytes(), 64)
+            nb = min(nb, self.max_num_seqs * ((self.max_model_len + self.block_size - 1) // self.block_size) + 64)
+        else:
+            nb = self.max_num_seqs * ((self.max_model_len + self.block_size - 1) // self.block_size) + 8
+        self.num_blocks = int(nb)
+        c = self.cfg
+        shape = (self.num_blocks, c.num_key_value_heads, self.block_size, c.head_dim)
+        self.k_cache = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in range(c.num_hidden_layers)]
+        self.v_cache = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in range(c.num_hidden_layers)]
+        self.sched = Scheduler(self.num_blocks, self.block_size, self.max_num_seqs, self.max_num_batched_tokens,
+                               self.max_model_len, self.enable_prefix_caching)
+        self._graphs = {}
+
+    def sleep(self):
+        """Free the KV cache (and captured graphs). Running requests must have been drained or aborted."""
+        self.abort_all_requests()
+        self.k_cache, self.v_cache, self._graphs = [], [], {}
+        self.sched = None
+        if self.on_gpu:
+            torch.cuda.empty_cache()
+
+    def clear_kv_cache(self):
+        if self.sched is not None:
+            self.sched.reset_prefix_cache()
+
+    # ---------------------------------------------------------------- weights
+    @torch.no_grad()
+    def update_weights(self, weights: Iterable[tuple[str, torch.Tensor]], **kwargs):
+        """Load HF-named tensors into the engine's (fused-layout) parameters. When the engine shares its
+        module with the trainer on the same device this is unnecessary; it serves separate replicas."""
+        hf = {k: v for k, v in weights}
+        native = hf_to_native_state_dict(self.cfg, hf)
+        own = dict(self.model.named_parameters())
+        for k, v in native.items():
+            if k in own:
+                own[k].data.copy_(v.to(own[k].dtype))
+        self.clear_kv_cache()
+
+    # --------------------------------------------------------------- requests
+    def add_request(self, request_id: str, prompt_ids: list[int], sampling_params=None) -> None:
+        if self.sched is None:
+            self.wake_up()
+        sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
+        max_new = min(sp.max_tokens, self.max_model_len - len(prompt_ids))
+        sid = self._next_sid
+        self._next_sid += 1
+        rc = self.sched.add(sid, list(prompt_ids), max_new)
+        if rc != 0:
+            raise ValueError(f"request {request_id}: prompt of {len(prompt_ids)} tokens does not fit (code {rc})")
+        self.requests[sid] = _Request(request_id, sid, sp, len(prompt_ids))
+        self.by_rid[request_id] = sid
+
+    def _finish(self, sid: int, reason: str) -> TokenOutput:
+        req = self.requests.pop(sid)
+        self.by_rid.pop(req.rid, None)
+        toks = self.sched.output(sid, self.max_model_len)
+        pre = self.sched.preempt_count(sid)
+        self.sched.remove(sid)
+        lps = req.logprobs[: len(toks)] if req.params.logprobs else None
+        return TokenOutput(token_ids=toks, log_probs=lps, stop_reason=reason, num_preempted=max(pre, 0), request_id=req.rid)
+
+    def abort_request(self, request_id: str) -> Optional[TokenOutput]:
+        """Stop a request; the partial output is returned with ``stop_reason="aborted"``."""
+        sid = self.by_rid.get(request_id)
+        if sid is None:
+            return None
+        return self._finish(sid, "aborted")
+
+    def abort_all_requests(self) -> list[TokenOutput]:
+        if self.sched is None:
+            return []
+        return [self._finish(sid, "aborted") for sid in list(self.requests.keys())]
+
+    def has_unfinished(self) -> bool:
+        return bool(self.requests)
+
+    # ------------------------------------------------------------ model pieces
+    def _layer_attn_in(self, layer, x, positions):
+        c = self.cfg
+        att = layer.self_attn
+        qkv = ops.gemm(x, att.qkv_proj.weight, bias=att.qkv_proj.bias) if self.on_gpu else torch.nn.functional.linear(
+            x, att.qkv_proj.weight, att.qkv_proj.bias)
+        T = x.shape[0]
+        if c.qk_norm:
+            q, k, v = qkv.split([c.q_size, c.kv_size, c.kv_size], dim=-1)
+            q, _ = ops.rmsnorm(q.reshape(T * c.num_attention_heads, c.head_dim).contiguous(), att.q_norm.weight, c.rms_norm_eps)
+            k, _ = ops.rmsnorm(k.reshape(T * c.num_key_value_heads, c.head_dim).contiguous(), att.k_norm.weight, c.rms_norm_eps)
+            qkv = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v], dim=-1)
+        rope = self.model.rope(self.device)
+        qkv = ops.rope_qkv(qkv, positions, rope[0], rope[1], c.num_attention_heads, c.num_key_value_heads, c.head_dim)
+        q = qkv[:, : c.q_size].view(T, c.num_attention_heads, c.head_dim)
+        k = qkv[:, c.q_size : c.q_size + c.kv_size].view(T, c.num_key_value_heads, c.head_dim)
+        v = qkv[:, c.q_size + c.kv_size :].view(T, c.num_key_value_heads, c.head_dim)
+        return q, k, v
+
+    def _mm(self, x, w):
+        return ops.gemm(x, w) if self.on_gpu else x @ w.t()
+
+    def _layer_rest(self, layer, attn_out, residual):
+        c = self.cfg
+        o = self._mm(attn_out.reshape(attn_out.shape[0], c.q_size), layer.self_attn.o_proj.weight)
+        x, residual = ops.rmsnorm(o, layer.post_attention_layernorm.weight, c.rms_norm_eps, residual)
+        if c.is_moe:
+            h = layer.mlp(x)
+        else:
+            h = self._mm(ops.swiglu(self._mm(x, layer.mlp.gate_up_proj.weight)), layer.mlp.down_proj.weight)
+        return h, residual
+
+    def _final_logits(self, hidden, residual):
+        c = self.cfg
+        x, _ = ops.rmsnorm(hidden, self.model.norm.weight, c.rms_norm_eps, residual)
+        w = self.model.lm_head_weight
+        if self.on_gpu:
+            return ops.gemm(x, w, out_dtype=torch.float32)
+        return x.float() @ w.float().t()
+
+    # ------------------------------------------------------------------ decode
+    @torch.no_grad()
+    def _decode_forward(self, ids, positions, slots, block_table, seq_lens, splits, work):
+        c = self.cfg
+        h = ops.embedding(ids, self.model.embed_tokens.weight)
+        residual = None
+        for li, layer in enumerate(self.model.layers):
+            x, residual = ops.rmsnorm(h, layer.input_layernorm.weight, c.rms_norm_eps, residual)
+            q, k, v = self._layer_attn_in(layer, x, positions)
+            ops.kv_cache_write(k, v, slots, self.k_cache[li], self.v_cache[li])
+            attn = ops.paged_decode_attention(q, self.k_cache[li], self.v_cache[li], block_table, seq_lens,
+                                              num_splits=splits, work=work)
+            h, residual = self._layer_rest(layer, attn, residual)
+        return self._final_logits(h, residual)
+
+    def _graph_sizes(self):
+        if self._capture_sizes:
+            return sorted(self._capture_sizes)
+        sizes, b = [], 1
+        while b < self.max_num_seqs:
+            sizes.append(b)
+            b *= 2
+        sizes.append(self.max_num_seqs)
+        return sizes
+
+    def _get_graph(self, B: int):
+        """Static buffers + captured graph for a padded decode batch of B sequences."""
+        if B in self._graphs:
+            return self._graphs[B]
+        dev, c = self.device, self.cfg
+        mb = self.sched.max_blocks
+        st = {
+            "ids": torch.zeros(B, dtype=torch.long, device=dev),
+            "pos": torch.zeros(B, dtype=torch.long, device=dev),
+            "slots": torch.full((B,), -1, dtype=torch.long, device=dev),
+            "bt": torch.zeros(B, mb, dtype=torch.int32, device=dev),
+            "lens": torch.ones(B, dtype=torch.int32, device=dev),
+            "temp": torch.ones(B, dtype=torch.float32, device=dev),
+            "topk": torch.full((B,), -1, dtype=torch.int32, device=dev),
+            "topp": torch.ones(B, dtype=torch.float32, device=dev),
+            "tok": torch.zeros(B, dtype=torch.long, device=dev),
+            "lp": torch.zeros(B, dtype=torch.float32, device=dev),
+        }
+        splits, work = ops.decode_workspace(B, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
+                                            self.max_model_len, dev)
+        st["splits"], st["work"] = splits, work
+
+        def run():
+            logits = self._decode_forward(st["ids"], st["pos"], st["slots"], st["bt"], st["lens"], splits, work)
+            ops.sample(logits, temperature=st["temp"], top_k=st["topk"], top_p=st["topp"], seed=self.seed,
+                       step=self.step_counter, out_tokens=st["tok"], out_logprobs=st["lp"])
+            self.step_counter.add_(1)
+
+        graph = None
+        if not self.enforce_eager:
+            s = torch.cuda.Stream(device=dev)
+            s.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(s):
+                run()  # warm-up (also sets func attributes, fills caches)
+            torch.cuda.current_stream(dev).wait_stream(s)
+            torch.cuda.synchronize(dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                run()
+        self._graphs[B] = (st, graph, run)
+        return self._graphs[B]
+
+    def _pad_batch(self, n: int) -> int:
+        for b in self._graph_sizes():
+            if b >= n:
+                return b
+        return n
+
+    # ----------------------------------------------------------------- prefill
+    @torch.no_grad()
+    def _prefill_forward(self, seq_idx: list[int], tok_lo: list[int]):
+        """Run the scheduled prefill chunks. Returns logits [num_prefill_seqs, V] at each chunk's last token."""
+        sc, c, dev = self.sched, self.cfg, self.device
+        ids_l, pos_l, slot_l, cu, ctx_lens = [], [], [], [0], []
+        for i, lo in zip(seq_idx, tok_lo):
+            n = int(sc.seq_ntok[i])
+            ids_l.append(sc.tokens[lo : lo + n])
+            pos_l.append(sc.positions[lo : lo + n])
+            slot_l.append(sc.slots[lo : lo + n])
+            cu.append(cu[-1] + n)
+            ctx_lens.append(int(sc.seq_start[i]))
+        ids = torch.from_numpy(np.concatenate(ids_l)).to(dev)
+        pos = torch.from_numpy(np.concatenate(pos_l)).to(dev)
+        slots = torch.from_numpy(np.concatenate(slot_l)).to(dev)
+        T = ids.numel()
+        cu_q = torch.tensor(cu, dtype=torch.int32, device=dev)
+        max_q = max(b - a for a, b in zip(cu[:-1], cu[1:]))
+        has_ctx = any(x > 0 for x in ctx_lens)
+        if has_ctx:
+            # gather indices of the cached context (block, offset) and the order that interleaves
+            # [context | new tokens] per sequence for the key/value side
+            blk_l, off_l, order, cu_k = [], [], [], [0]
+            n_ctx_total = sum(ctx_lens)
+            ctx_off = 0
+            for j, (i, ctx) in enumerate(zip(seq_idx, ctx_lens)):
+                if ctx:
+                    p = np.arange(ctx)
+                    blk_l.append(sc.block_tables[i, p // self.block_size])
+                    off_l.append(p % self.block_size)
+                    order.append(np.arange(ctx_off, ctx_off + ctx))
+                    ctx_off += ctx
+                order.append(n_ctx_total + np.arange(cu[j], cu[j + 1]))
+                cu_k.append(cu_k[-1] + ctx + cu[j + 1] - cu[j])
+            blk = torch.from_numpy(np.concatenate(blk_l).astype(np.int64)).to(dev)
+            off = torch.from_numpy(np.concatenate(off_l).astype(np.int64)).to(dev)
+            order_t = torch.from_numpy(np.concatenate(order)).to(dev)
+            cu_k_t = torch.tensor(cu_k, dtype=torch.int32, device=dev)
+            max_k = max(b - a for a, b in zip(cu_k[:-1], cu_k[1:]))
+        h = ops.embedding(ids, self.model.embed_tokens.weight)
+        residual = None
+        for li, layer in enumerate(self.model.layers):
+            x, residual = ops.rmsnorm(h, layer.input_layernorm.weight, c.rms_norm_eps, residual)
+            q, k, v = self._layer_attn_in(layer, x, pos)
+            ops.kv_cache_write(k, v, slots, self.k_cache[li], self.v_cache[li])
+            if not has_ctx:
+                attn = ops.attention_varlen(q, k, v, cu_q, max_q, causal=True)
+            else:
+                k_all = torch.cat([self.k_cache[li][blk, :, off], k], dim=0)[order_t]
+                v_all = torch.cat([self.v_cache[li][blk, :, off], v], dim=0)[order_t]
+                attn = _varlen_attention_kv(q, k_all, v_all, cu_q, cu_k_t, max_q, max_k)
+            h, residual = self._layer_rest(layer, attn, residual)
+        last = torch.tensor([b - 1 for b in cu[1:]], dtype=torch.long, device=dev)
+        return self._final_logits(h[last], residual[last])
+
+    # -------------------------------------------------------------------- step
+    @torch.no_grad()
+    def step(self) -> list[TokenOutput]:
+        """One scheduler iteration. Returns the requests that finished in it."""
+        sc = self.sched
+        n, _ = sc.step()
+        if n == 0:
+            return []
+        self.stats["steps"] += 1
+        lo, tok_lo = 0, []
+        for i in range(n):
+            tok_lo.append(lo)
+            lo += int(sc.seq_ntok[i])
+        dec = [i for i in range(n) if not sc.seq_prefill[i]]
+        pre = [i for i in range(n) if sc.seq_prefill[i]]
+        new_tokens = np.full(n, -1, np.int64)
+        new_lps = np.zeros(n, np.float32)
+        dev = self.device
+        if dec:
+            nd = len(dec)
+            B = self._pad_batch(nd)
+            st, graph, run = self._get_graph(B)
+            di = np.asarray(dec)
+            t_idx = np.asarray([tok_lo[i] for i in dec])
+
+            def fill(name, arr, pad):
+                buf = np.full((B,) + arr.shape[1:], pad, dtype=arr.dtype)
+                buf[:nd] = arr
+                st[name].copy_(torch.from_numpy(buf), non_blocking=True)
+
+            fill("ids", sc.tokens[t_idx], 0)
+            fill("pos", sc.positions[t_idx], 0)
+            fill("slots", sc.slots[t_idx], -1)
+            fill("bt", sc.block_tables[di], 0)
+            fill("lens", sc.seq_total[di], 1)
+            sps = [self.requests[int(sc.seq_ids[i])].params for i in dec]
+            fill("temp", np.asarray([p.temperature for p in sps], np.float32), 1.0)
+            fill("topk", np.asarray([p.top_k for p in sps], np.int32), -1)
+            fill("topp", np.asarray([p.top_p for p in sps], np.float32), 1.0)
+            if graph is not None:
+                graph.replay()
+            else:
+                run()
+            new_tokens[di] = st["tok"][:nd].cpu().numpy()
+            new_lps[di] = st["lp"][:nd].cpu().numpy()
+            self.stats["decode_tokens"] += nd
+        if pre:
+            logits = self._prefill_forward(pre, [tok_lo[i] for i in pre])
+            # only chunks that complete their sequence sample a token
+            sps = [self.requests[int(sc.seq_ids[i])].params for i in pre]
+            temp = torch.tensor([p.temperature for p in sps], dtype=torch.float32, device=dev)
+            topk = torch.tensor([p.top_k for p in sps], dtype=torch.int32, device=dev)
+            topp = torch.tensor([p.top_p for p in sps], dtype=torch.float32, device=dev)
+            tok, lp = ops.sample(logits, temperature=temp, top_k=topk, top_p=topp, seed=self.seed, step=self.step_counter)
+            self.step_counter.add_(1)
+            new_tokens[np.asarray(pre)] = tok.cpu().numpy()
+            new_lps[np.asarray(pre)] = lp.cpu().numpy()
+            self.stats["prefill_tokens"] += int(sum(sc.seq_ntok[i] for i in pre))
+        # stop criteria
+        finished = np.zeros(n, np.int32)
+        reasons = {}
+        for i in range(n):
+            sid = int(sc.seq_ids[i])
+            req = self.requests[sid]
+            t = int(new_tokens[i])
+            if not req.params.ignore_eos and (t == self.eos or t in req.params.stop_token_ids):
+                finished[i] = 1
+                reasons[sid] = "completed"
+        done = sc.commit(new_tokens, finished).copy()
+        outs = []
+        for i in range(n):
+            sid = int(sc.seq_ids[i])
+            req = self.requests[sid]
+            if new_tokens[i] >= 0 and self._was_sampled(i):
+                req.logprobs.append(float(new_lps[i]))
+            if done[i]:
+                outs.append(self._finish(sid, reasons.get(sid, "length")))
+        return outs
+
+    def _was_sampled(self, i: int) -> bool:
+        """False for a partial prefill chunk: its sampled token is discarded by the scheduler."""
+        return int(self.sched.seq_prefill[i]) != 2
+
+    # ---------------------------------------------------------------- generate
+    def generate(self, prompts: list[list[int]], sampling_params=None, request_ids: Optional[list[str]] = None):
+        """Blocking batch generation. ``sampling_params``: one for all or a list. Returns TokenOutputs in order."""
+        n = len(prompts)
+        sps = sampling_params if isinstance(sampling_params, list) else [sampling_params] * n
+        rids = request_ids or [f"gen-{self._next_sid + i}-{time.monotonic_ns()}" for i in range(n)]
+        for rid, p, sp in zip(rids, prompts, sps):
+            self.add_request(rid, p, sp)
+        results: dict[str, TokenOutput] = {}
+        want = set(rids)
+        idle = 0
+        while want - results.keys():
+            outs = self.step()
+            if not outs and not self.requests:
+                break
+            idle = idle + 1 if not outs and self.sched.stats()["running"] == 0 else 0
+            if idle > 1000:
+                raise RuntimeError("rollout engine made no progress (KV cache too small for the waiting requests?)")
+            for o in outs:
+                results[o.request_id] = o
+        return [results[r] for r in rids]
+
+
+def _varlen_attention_kv(q, k, v, cu_q, cu_k, max_q, max_k):
+    """Causal attention where each sequence's queries are the last ``len_q`` positions of its keys."""
+    if q.is_cuda:
+        from flash_attn import flash_attn_varlen_func  # library kernel (prefix-cache prefill only)
+
+        return flash_attn_varlen_func(q, k, v, cu_q, cu_k, max_q, max_k, causal=True)
+    out = torch.empty_like(q)
+    G = q.shape[1] // k.shape[1]
+    for (qs, qe), (ks, ke) in zip(zip(cu_q[:-1].tolist(), cu_q[1:].tolist()), zip(cu_k[:-1].tolist(), cu_k[1:].tolist())):
+        lq, lk = qe - qs, ke - ks
+        qq = q[qs:qe].transpose(0, 1).float()
+        kk = k[ks:ke].repeat_interleave(G, 1).transpose(0, 1).float()
+        vv = v[ks:ke].repeat_interleave(G, 1).transpose(0, 1).float()
+        s = qq @ kk.transpose(1, 2) * q.shape[-1] ** -0.5
+        mask = torch.arange(lk)[None, :] <= (torch.arange(lq)[:, None] + (lk - lq))
+        s = s.masked_fill(~mask, float("-inf"))
+        out[qs:qe] = (torch.softmax(s, -1) @ vv).transpose(0, 1).to(q.dtype)
+    return out
