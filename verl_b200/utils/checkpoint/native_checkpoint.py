@@ -1,0 +1,163 @@
+"""Sharded checkpoints in the verl FSDP layout plus HuggingFace export.
+
+Directory layout written / read (verl/utils/checkpoint/fsdp_checkpoint_manager.py:56-362,
+docs/advance/checkpoint.rst:20-62):
+
+    <dir>/model_world_size_{W}_rank_{r}.pt        this rank's parameter shard
+    <dir>/optim_world_size_{W}_rank_{r}.pt        this rank's optimizer shard (fp32 master + Adam moments)
+    <dir>/extra_state_world_size_{W}_rank_{r}.pt  lr-scheduler step + RNG state
+    <dir>/fsdp_config.json                        {"FSDP_version": 2, "world_size": W}
+    <dir>/huggingface/                            config.json (always) + safetensors when "hf_model" is saved
+
+The reference stores ``DTensor`` shards produced by torch FSDP. This engine shards flat per-layer vectors
+instead, so the model file holds, per parameter, the slice of the flattened tensor this rank owns together
+with (global shape, start offset, length); :func:`merge_sharded_checkpoint` re-assembles full tensors from
+the W files (the job of ``python -m verl.model_merger merge --backend fsdp``).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import random
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ...models.hf_io import save_hf_checkpoint
+
+
+def _rng_state() -> dict:
+    st = {"cpu": torch.get_rng_state(), "numpy": np.random.get_state(), "random": random.getstate()}
+    if torch.cuda.is_available():
+        st["cuda"] = torch.cuda.get_rng_state()
+    return st
+
+
+def _load_rng_state(st: dict) -> None:
+    torch.set_rng_state(st["cpu"])
+    np.random.set_state(st["numpy"])
+    random.setstate(st["random"])
+    if torch.cuda.is_available() and "cuda" in st:
+        torch.cuda.set_rng_state(st["cuda"])
+
+
+def _param_slices(zero, flat: torch.Tensor) -> dict:
+    """{param name: {"shape", "start", "data"}} — the part of each flattened parameter held by this rank."""
+    out = {}
+    for u in zero.units:
+        lo, hi = zero.rank * u.shard, (zero.rank + 1) * u.shard
+        for name, p_shape, o in zip(u.names, [tuple(p.shape) for p in u.params], u.offsets):
+            n = int(np.prod(p_shape)) if len(p_shape) else 1
+            s, e = max(o, lo), min(o + n, hi)
+            if s >= e:
+                out[name] = {"shape": p_shape, "start": 0, "data": flat.new_empty(0)}
+                continue
+            out[name] = {"shape": p_shape, "start": s - o,
+                         "data": flat[u.offset + s - lo : u.offset + e - lo].detach().cpu().clone()}
+    return out
+
+
+def save_engine_checkpoint(engine, local_path: str, global_step: int = 0,
+                           save_contents=("model", "optimizer", "extra")) -> None:
+    z = engine.zero
+    path = Path(local_path)
+    if z.rank == 0:
+        path.mkdir(parents=True, exist_ok=True)
+    if dist.is_initialized():
+        dist.barrier()
+    W, r = z.world, z.rank
+    if "model" in save_contents:
+        src = z.master if z.trainable else z.shard16
+        torch.save({"format": "verl_b200.flat_shard.v1", "world_size": W, "rank": r, "params": _param_slices(z, src)},
+                   path / f"model_world_size_{W}_rank_{r}.pt")
+    if "optimizer" in save_contents and z.trainable:
+        torch.save({"format": "verl_b200.flat_shard.v1", "world_size": W, "rank": r, "step": engine.step_count,
+                    "exp_avg": _param_slices(z, z.exp_avg), "exp_avg_sq": _param_slices(z, z.exp_avg_sq)},
+                   path / f"optim_world_size_{W}_rank_{r}.pt")
+    if "extra" in save_contents:
+        torch.save({"lr_scheduler": {"lr_step": engine.lr_step, "step_count": engine.step_count}, "rng": _rng_state(),
+                    "global_step": global_step}, path / f"extra_state_world_size_{W}_rank_{r}.pt")
+    if r == 0:
+        (path / "fsdp_config.json").write_text(json.dumps({"FSDP_version": 2, "world_size": W}, indent=4))
+        hf_dir = path / "huggingface"
+        hf_dir.mkdir(exist_ok=True)
+        engine.model_config.save_pretrained(hf_dir)
+    if "hf_model" in save_contents:
+        sd = {}
+        for k, v in z.named_full_tensors():  # collective: every rank takes part in the gathers
+            if r == 0:
+                sd[k] = v.detach().to(torch.bfloat16).cpu()
+        if r == 0:
+            save_hf_checkpoint(engine.model_config, sd, path / "huggingface")
+    if dist.is_initialized():
+        dist.barrier()
+
+
+def _restore(zero, dst: torch.Tensor, slices: dict) -> None:
+    for u in zero.units:
+        lo, hi = zero.rank * u.shard, (zero.rank + 1) * u.shard
+        for name, o in zip(u.names, u.offsets):
+            ent = slices[name]
+            data = ent["data"]
+            if data.numel() == 0:
+                continue
+            s = o + ent["start"]
+            dst[u.offset + s - lo : u.offset + s - lo + data.numel()].copy_(data.to(dst.device, dst.dtype))
+
+
+def load_engine_checkpoint(engine, local_path: str, load_contents=("model", "optimizer", "extra")) -> None:
+    z = engine.zero
+    path = Path(local_path)
+    W, r = z.world, z.rank
+    mfile = path / f"model_world_size_{W}_rank_{r}.pt"
+    if "model" in load_contents:
+        if mfile.exists():
+            st = torch.load(mfile, map_location="cpu", weights_only=False)
+            assert st["world_size"] == W
+            if z.trainable:
+                _restore(z, z.master, st["params"])
+                z.shard16.copy_(z.master.to(z.shard16.dtype))
+            else:
+                _restore(z, z.shard16, st["params"])
+        else:  # a different world size (or an HF export): rebuild from full tensors
+            full = merge_sharded_checkpoint(path)
+            z.load_full_state(full)
+    ofile = path / f"optim_world_size_{W}_rank_{r}.pt"
+    if "optimizer" in load_contents and z.trainable and ofile.exists():
+        st = torch.load(ofile, map_location="cpu", weights_only=False)
+        _restore(z, z.exp_avg, st["exp_avg"])
+        _restore(z, z.exp_avg_sq, st["exp_avg_sq"])
+        engine.step_count = int(st.get("step", 0))
+    efile = path / f"extra_state_world_size_{W}_rank_{r}.pt"
+    if "extra" in load_contents and efile.exists():
+        st = torch.load(efile, map_location="cpu", weights_only=False)
+        engine.lr_step = int(st["lr_scheduler"]["lr_step"])
+        engine.step_count = int(st["lr_scheduler"].get("step_count", engine.step_count))
+        _load_rng_state(st["rng"])
+
+
+def merge_sharded_checkpoint(local_path: str | Path) -> dict:
+    """Re-assemble full (native-named) tensors from all ``model_world_size_*_rank_*.pt`` files of a directory."""
+    path = Path(local_path)
+    cfg = json.loads((path / "fsdp_config.json").read_text())
+    W = int(cfg["world_size"])
+    full: dict = {}
+    for r in range(W):
+        st = torch.load(path / f"model_world_size_{W}_rank_{r}.pt", map_location="cpu", weights_only=False)
+        for name, ent in st["params"].items():
+            n = int(np.prod(ent["shape"])) if len(ent["shape"]) else 1
+            if name not in full:
+                full[name] = torch.zeros(n, dtype=ent["data"].dtype if ent["data"].numel() else torch.float32)
+            d = ent["data"]
+            if d.numel():
+                if full[name].dtype != d.dtype:
+                    full[name] = full[name].to(d.dtype)
+                full[name][ent["start"] : ent["start"] + d.numel()] = d
+            full[name + "//shape"] = ent["shape"]
+    out = {}
+    for k in [k for k in full if not k.endswith("//shape")]:
+        out[k] = full[k].view(full[k + "//shape"])
+    return out

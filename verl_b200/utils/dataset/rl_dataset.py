@@ -1,0 +1,143 @@
+"""Prompt datasets for RL (verl/utils/dataset/rl_dataset.py:39-362): parquet / json(l) rows with a chat
+``prompt``, ``data_source``, ``reward_model{ground_truth,style}`` and ``extra_info``; items carry
+``raw_prompt`` plus tokenised, left-padded ``input_ids / attention_mask / position_ids``. Also a synthetic
+token-prompt dataset for benchmarks without any files.
+"""
+
+from __future__ import annotations
+
+import copy
+import json
+import os
+from collections import defaultdict
+from typing import Optional
+
+import numpy as np
+import torch
+from torch.utils.data import Dataset
+
+from .. import torch_functional as F_
+
+
+def collate_fn(data_list: list[dict]) -> dict:
+    """Stack tensors; everything else becomes an object array (one entry per sample)."""
+    tensors, others = defaultdict(list), defaultdict(list)
+    for d in data_list:
+        for k, v in d.items():
+            (tensors if isinstance(v, torch.Tensor) else others)[k].append(v)
+    out = {k: torch.stack(v, dim=0) for k, v in tensors.items()}
+    for k, v in others.items():
+        arr = np.empty(len(v), dtype=object)
+        arr[:] = v
+        out[k] = arr
+    return out
+
+
+def _read_rows(path: str) -> list[dict]:
+    path = os.path.expanduser(path)
+    if path.endswith(".parquet"):
+        import pyarrow.parquet as pq
+
+        return pq.read_table(path).to_pylist()
+    if path.endswith(".jsonl"):
+        with open(path) as f:
+            return [json.loads(line) for line in f if line.strip()]
+    if path.endswith(".json"):
+        with open(path) as f:
+            return json.load(f)
+    raise ValueError(f"unsupported data file {path}")
+
+
+class RLHFDataset(Dataset):
+    def __init__(self, data_files, tokenizer, config, processor=None, max_samples: int = -1):
+        if not isinstance(data_files, (list, tuple)):
+            data_files = [data_files]
+        self.data_files = list(copy.deepcopy(data_files))
+        self.tokenizer, self.processor, self.config = tokenizer, processor, config
+        g = config.get
+        self.prompt_key = g("prompt_key", "prompt")
+        self.max_prompt_length = g("max_prompt_length", 1024)
+        self.return_raw_chat = g("return_raw_chat", True)
+        self.return_full_prompt = g("return_full_prompt", False)
+        self.truncation = g("truncation", "error")
+        self.filter_overlong_prompts = g("filter_overlong_prompts", False)
+        self.apply_chat_template_kwargs = dict(g("apply_chat_template_kwargs", {}) or {})
+        self.need_tools_kwargs = g("need_tools_kwargs", False)
+        self.shuffle, self.seed = g("shuffle", False), g("seed", None)
+        self.rows: list[dict] = []
+        for f in self.data_files:
+            self.rows.extend(_read_rows(f))
+        if max_samples is not None and 0 < max_samples < len(self.rows):
+            if self.shuffle:
+                rng = np.random.default_rng(self.seed)
+                keep = rng.choice(len(self.rows), size=max_samples, replace=False)
+                self.rows = [self.rows[i] for i in keep.tolist()]
+            else:
+                self.rows = self.rows[:max_samples]
+        if self.filter_overlong_prompts:
+            self.rows = [r for r in self.rows if len(self._tokenize(r[self.prompt_key])) <= self.max_prompt_length]
+        print(f"dataset len: {len(self.rows)}")
+
+    def _tokenize(self, messages) -> list[int]:
+        if isinstance(messages, str):
+            return self.tokenizer.encode(messages, add_special_tokens=False)
+        if isinstance(messages, np.ndarray):
+            messages = messages.tolist()
+        if len(messages) and isinstance(messages[0], (int, np.integer)):
+            return [int(t) for t in messages]
+        return list(self.tokenizer.apply_chat_template(messages, add_generation_prompt=True, tokenize=True,
+                                                       **self.apply_chat_template_kwargs))
+
+    def __len__(self):
+        return len(self.rows)
+
+    def __getitem__(self, item):
+        row = dict(self.rows[item])
+        messages = row.pop(self.prompt_key)
+        ids = torch.tensor([self._tokenize(messages)], dtype=torch.long)
+        mask = torch.ones_like(ids)
+        pad = getattr(self.tokenizer, "pad_token_id", 0) or 0
+        ids, mask = F_.postprocess_data(ids, mask, self.max_prompt_length, pad, left_pad=True, truncation=self.truncation)
+        row["input_ids"], row["attention_mask"] = ids[0], mask[0]
+        row["position_ids"] = F_.compute_position_id_with_mask(mask)[0]
+        row["raw_prompt_ids"] = ids[0][mask[0].bool()].tolist()
+        if self.return_raw_chat:
+            row["raw_prompt"] = messages
+        extra = row.get("extra_info") or {}
+        row["index"] = extra.get("index", item) if isinstance(extra, dict) else item
+        row["tools_kwargs"] = extra.get("tools_kwargs", {}) if isinstance(extra, dict) else {}
+        row["interaction_kwargs"] = extra.get("interaction_kwargs", {}) if isinstance(extra, dict) else {}
+        row.setdefault("data_source", "unknown")
+        return row
+
+    def resume_dataset_state(self):
+        pass
+
+    def __getstate__(self):
+        return self.__dict__.copy()
+
+
+class SyntheticPromptDataset(Dataset):
+    """Uniform-random token prompts: lengths in [min_len, max_len], ids in [id_lo, id_hi), fixed seed.
+    Rows look like RLHFDataset rows so the same trainer, reward manager and collate function apply."""
+
+    def __init__(self, num_prompts: int, min_len: int, max_len: int, id_lo: int, id_hi: int, max_prompt_length: int,
+                 seed: int = 0, data_source: str = "synthetic/even_fraction", pad_token_id: int = 0, ground_truth=None):
+        g = torch.Generator().manual_seed(seed)
+        self.items = []
+        for i in range(num_prompts):
+            n = int(torch.randint(min_len, max_len + 1, (1,), generator=g))
+            toks = torch.randint(id_lo, id_hi, (n,), generator=g)
+            ids = torch.full((max_prompt_length,), pad_token_id, dtype=torch.long)
+            mask = torch.zeros(max_prompt_length, dtype=torch.long)
+            ids[-n:], mask[-n:] = toks, 1
+            self.items.append({"input_ids": ids, "attention_mask": mask,
+                               "position_ids": F_.compute_position_id_with_mask(mask), "data_source": data_source,
+                               "reward_model": {"ground_truth": ground_truth, "style": "rule"}, "extra_info": {"index": i},
+                               "index": i, "raw_prompt_ids": toks.tolist()})
+
+    def __len__(self):
+        return len(self.items)
+
+    def __getitem__(self, i):
+        return dict(self.items[i])

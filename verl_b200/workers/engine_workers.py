@@ -1,0 +1,426 @@
+"""SPMD workers: the hybrid actor / rollout / reference worker, the critic worker and a
+reward-model worker, all on the native engines.
+
+RPC surface and semantics follow ``ActorRolloutRefWorker`` / ``CriticWorker`` / ``RewardModelWorker``
+(verl/workers/fsdp_workers.py:140-1981, verl/workers/engine_workers.py:371-636): ``init_model,
+generate_sequences, compute_log_prob, compute_ref_log_prob, update_actor, update_weights,
+compute_values, update_critic, compute_rm_score, save_checkpoint, load_checkpoint``.
+
+Hybrid engine on one box: the rollout engine runs on the same GPU as the trainer. With one rank it
+reads the trainer's bf16 weights in place (weight sync is a no-op); with several ranks every rank
+keeps a rollout copy that ``update_weights`` refreshes from the ZeRO shards over NVLink.
+"""
+
+from __future__ import annotations
+
+import os
+import time
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..models import CausalLM, ModelConfig, preset
+from ..models.hf_io import load_hf_checkpoint
+from ..protocol import DataProto
+from ..single_controller.base import Dispatch, Worker, register
+from ..single_controller.base.decorator import make_nd_compute_dataproto_dispatch_fn
+from ..utils.config import omega_conf_to_dataclass
+from ..utils.py_functional import append_to_dict
+from .actor.dp_actor import DataParallelPPOActor
+from .critic.dp_critic import DataParallelPPOCritic
+from .engine.native import NativeEngine, _cfg
+
+__all__ = ["ActorRolloutRefWorker", "AsyncActorRolloutRefWorker", "CriticWorker", "RewardModelWorker",
+           "resolve_model_config"]
+
+
+def resolve_model_config(model_cfg) -> tuple[ModelConfig, Optional[dict]]:
+    """Model architecture (and weights, if the path holds any) from ``model.path``: an HF directory, a
+    preset name (``preset:qwen2.5-7b``) for random-init runs, or ``override_config`` on top of either."""
+    path = os.path.expanduser(str(_cfg(model_cfg, "path", "")))
+    override = dict(_cfg(model_cfg, "override_config", {}) or {})
+    override = dict(override.get("model_config", override))
+    state = None
+    if path.startswith("preset:"):
+        cfg = preset(path[len("preset:"):], **override)
+        return cfg, None
+    if os.path.isdir(path):
+        if any(f.endswith(".safetensors") for f in os.listdir(path)):
+            cfg, state = load_hf_checkpoint(path)
+        else:
+            cfg = ModelConfig.from_pretrained(path)
+        for k, v in override.items():
+            setattr(cfg, k, v)
+        return cfg, state
+    raise FileNotFoundError(f"model path {path!r}: expected an HF directory or 'preset:<name>'")
+
+
+def _init_dist(device_name: str, timeout_s: int = 600):
+    if dist.is_initialized():
+        return
+    if int(os.environ.get("WORLD_SIZE", 1)) <= 1 and "MASTER_ADDR" not in os.environ:
+        return
+    from datetime import timedelta
+
+    backend = "nccl" if device_name == "cuda" and torch.cuda.is_available() else "gloo"
+    if backend == "nccl":
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    dist.init_process_group(backend=backend, timeout=timedelta(seconds=timeout_s))
+
+
+class _WorkerBase(Worker):
+    def __init__(self, config, device_name: Optional[str] = None):
+        super().__init__()
+        self.config = config
+        self.device_name = device_name or ("cuda" if torch.cuda.is_available() else "cpu")
+        _init_dist(self.device_name, int(_cfg(config, "nccl_timeout", 600)))
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.dp_rank = dist.get_rank() if dist.is_initialized() else 0
+        if self.device_name == "cuda":
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        else:
+            self.device = torch.device("cpu")
+
+    def _norm_batch(self, cfg, mini_key="ppo_mini_batch_size", micro_key="ppo_micro_batch_size", n: int = 1):
+        """YAML batch sizes are global prompt counts; workers use per-rank sample counts
+        (verl/workers/fsdp_workers.py:239-273)."""
+        mini = int(getattr(cfg, mini_key)) * n // self.world
+        assert mini > 0, f"{mini_key} {getattr(cfg, mini_key)} * n {n} must be >= world size {self.world}"
+        object.__setattr__(cfg, mini_key, mini)
+        micro = getattr(cfg, micro_key, None)
+        if micro is not None:
+            per = max(int(micro) // self.world, 1)
+            object.__setattr__(cfg, micro_key + "_per_gpu", per)
+        per_gpu = getattr(cfg, micro_key + "_per_gpu", None)
+        if per_gpu is not None and not getattr(cfg, "use_dynamic_bsz", False):
+            assert mini % per_gpu == 0, f"normalized {mini_key} {mini} should be divisible by {micro_key}_per_gpu {per_gpu}"
+
+
+class ActorRolloutRefWorker(_WorkerBase):
+    """role in {"actor", "rollout", "ref", "actor_rollout", "actor_rollout_ref"}."""
+
+    def __init__(self, config, role: str = "actor_rollout_ref", device_name: Optional[str] = None, **kwargs):
+        super().__init__(config, device_name)
+        self.role = role
+        assert role in ("actor", "rollout", "ref", "actor_rollout", "actor_rollout_ref")
+        self._is_actor = role in ("actor", "actor_rollout", "actor_rollout_ref")
+        self._is_rollout = role in ("rollout", "actor_rollout", "actor_rollout_ref")
+        self._is_ref = role in ("ref", "actor_rollout_ref")
+        self.actor_cfg = omega_conf_to_dataclass(config.actor) if self._is_actor else None
+        self.ref_cfg = omega_conf_to_dataclass(config.ref) if self._is_ref and config.get("ref") is not None else None
+        self.rollout_cfg = omega_conf_to_dataclass(config.rollout) if self._is_rollout else None
+        n = int(_cfg(config.get("rollout", {}), "n", 1))
+        if self._is_actor:
+            self._norm_batch(self.actor_cfg, n=n)
+        self._register_dispatch_collect_info("actor", dp_rank=self.dp_rank, is_collect=True)
+        self._register_dispatch_collect_info("ref", dp_rank=self.dp_rank, is_collect=True)
+        self._register_dispatch_collect_info("rollout", dp_rank=self.dp_rank, is_collect=True)
+        self.actor_engine = self.ref_engine = None
+        self.actor = self.ref_policy = None
+        self.rollout_engine = None
+        self.rollout_model = None
+        self._rollout_flat = None
+        self.timing = {}
+
+    # ------------------------------------------------------------------ build
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def init_model(self):
+        model_cfg, state = resolve_model_config(self.config.model)
+        self.model_config = model_cfg
+        gc = bool(_cfg(self.config.model, "enable_gradient_checkpointing", True))
+        seed = int(_cfg(_cfg(self.actor_cfg, "fsdp_config", None), "seed", 42)) if self.actor_cfg else 42
+        group = dist.group.WORLD if dist.is_initialized() and self.world > 1 else None
+        comm = self._make_comm()
+        if self._is_actor:
+            self.actor_engine = NativeEngine(model_cfg, self.actor_cfg.fsdp_config, self.actor_cfg.optim,
+                                             device=str(self.device), group=group, seed=seed, state_dict=state,
+                                             comm=comm, gradient_checkpointing=gc).initialize()
+            self.actor = DataParallelPPOActor(self.actor_cfg, self.actor_engine)
+        if self._is_ref:
+            ref_eng_cfg = self.ref_cfg.fsdp_config if self.ref_cfg is not None else None
+            self.ref_engine = NativeEngine(model_cfg, ref_eng_cfg, None, device=str(self.device), group=group, seed=seed,
+                                           state_dict=state, trainable=False, comm=comm).initialize()
+            self.ref_policy = DataParallelPPOActor(self.ref_cfg or self.actor_cfg, self.ref_engine)
+        if self._is_rollout:
+            self._build_rollout(model_cfg, state, seed)
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    def _make_comm(self):
+        if self.device.type != "cuda" or self.world <= 1 or os.environ.get("VERL_B200_DISABLE_PEER_COMM"):
+            return None
+        try:
+            from ..parallel.peer_comm import PeerComm
+
+            return PeerComm(dist.group.WORLD)
+        except Exception as e:  # peer memory not available: plain NCCL collectives
+            if self.dp_rank == 0:
+                print(f"[verl_b200] peer-memory collectives unavailable ({type(e).__name__}: {e}); using NCCL")
+            return None
+
+    def _build_rollout(self, model_cfg: ModelConfig, state, seed: int):
+        from ..rollout import NativeRolloutEngine
+
+        rc = self.rollout_cfg
+        if self._is_actor and self.world == 1:
+            self.rollout_model = self.actor_engine.model  # same tensors: weight sync is free
+        else:
+            dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            self.rollout_model = CausalLM(model_cfg, dtype=dtype, device=self.device)
+            if self._is_actor:
+                self._bind_rollout_to_flat()
+            elif state is not None:
+                self.rollout_model.load_state_dict({k: v.to(dtype) for k, v in state.items()}, strict=False)
+            else:
+                self.rollout_model.init_weights(seed)
+        max_len = rc.max_model_len or (rc.prompt_length + rc.response_length)
+        kw = dict(_cfg(rc.engine_kwargs, "native", {}) or {})
+        self.rollout_engine = NativeRolloutEngine(
+            self.rollout_model, max_num_seqs=rc.max_num_seqs, max_model_len=max_len,
+            max_num_batched_tokens=max(rc.max_num_batched_tokens, rc.prompt_length),
+            gpu_memory_utilization=rc.gpu_memory_utilization, enable_prefix_caching=rc.enable_prefix_caching,
+            enforce_eager=rc.enforce_eager, seed=seed + 1000 * self.dp_rank, cudagraph_capture_sizes=rc.cudagraph_capture_sizes,
+            **kw)
+        if rc.free_cache_engine:
+            self.rollout_engine.sleep()
+
+    def _bind_rollout_to_flat(self):
+        """Rollout parameters become views into per-unit flat buffers laid out exactly like the trainer's
+        gathered units, so a weight sync is one all-gather per unit straight into the rollout weights."""
+        z = self.actor_engine.zero
+        own = dict(self.rollout_model.named_parameters())
+        self._rollout_flat = []
+        for u in z.units:
+            buf = torch.zeros(u.padded, dtype=z.work_dtype, device=self.device)
+            self._rollout_flat.append(buf)
+            for name, p, o in zip(u.names, u.params, u.offsets):
+                if name in own:
+                    n = own[name].numel()
+                    own[name].data = buf[o : o + n].view(own[name].shape)
+        self._sync_rollout_weights()
+
+    @torch.no_grad()
+    def _sync_rollout_weights(self):
+        z = self.actor_engine.zero
+        for u, buf in zip(z.units, self._rollout_flat):
+            src = z.shard16[u.offset : u.offset + u.shard]
+            if z.comm is not None:
+                z.comm.all_gather(buf, src)
+            else:
+                dist.all_gather_into_tensor(buf, src, group=z.group)
+
+    # ---------------------------------------------------------------- rollout
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("rollout"))
+    def generate_sequences(self, prompts: DataProto) -> DataProto:
+        """prompts.batch: input_ids / attention_mask / position_ids (left-padded). Returns prompts + responses
+        in the reference's layout (``prompts, responses, input_ids, attention_mask, position_ids,
+        response_mask, rollout_log_probs``)."""
+        from ..rollout import SamplingParams
+        from ..rollout.postprocess import assemble_rollout_batch
+
+        rc = self.rollout_cfg
+        eng = self.rollout_engine
+        t0 = time.perf_counter()
+        eng.wake_up()
+        meta = prompts.meta_info
+        validate = meta.get("validate", False)
+        do_sample = meta.get("do_sample", rc.do_sample if not validate else rc.val_kwargs.do_sample)
+        temp = meta.get("temperature", rc.val_kwargs.temperature if validate else rc.temperature)
+        sp = SamplingParams(temperature=float(temp) if do_sample else 0.0,
+                            top_k=int(meta.get("top_k", rc.val_kwargs.top_k if validate else rc.top_k)),
+                            top_p=float(meta.get("top_p", rc.val_kwargs.top_p if validate else rc.top_p)),
+                            max_tokens=int(meta.get("response_length", rc.response_length)), ignore_eos=rc.ignore_eos)
+        ids, mask = prompts.batch["input_ids"], prompts.batch["attention_mask"]
+        prompt_lists = [row[m.bool()].tolist() for row, m in zip(ids.cpu(), mask.cpu())]
+        outs = eng.generate(prompt_lists, sp)
+        out = assemble_rollout_batch(ids.cpu(), mask.cpu(), outs, rc.response_length, pad_token_id=meta.get("pad_token_id", 0),
+                                     with_logprobs=True)
+        gen_time = time.perf_counter() - t0
+        out.non_tensor_batch.update(prompts.non_tensor_batch)
+        n_tok = int(out.batch["response_mask"].sum())
+        out.meta_info["timing"] = {"generate_sequences": gen_time}
+        out.meta_info["metrics"] = {"rollout/num_preempted": float(sum(o.num_preempted for o in outs)),
+                                    "rollout/tokens_per_s": n_tok / max(gen_time, 1e-9)}
+        if rc.free_cache_engine and not meta.get("keep_cache", False):
+            eng.sleep()
+        return out
+
+    # ---------------------------------------------------------------- log-probs
+    def _lp_meta(self, data: DataProto, cfg, prefix="log_prob_"):
+        data.meta_info.setdefault("micro_batch_size", _cfg(cfg, prefix + "micro_batch_size_per_gpu", None))
+        data.meta_info.setdefault("max_token_len", _cfg(cfg, prefix + "max_token_len_per_gpu", 16384))
+        data.meta_info.setdefault("use_dynamic_bsz", bool(_cfg(cfg, prefix + "use_dynamic_bsz", False)))
+        data.meta_info.setdefault("temperature", _cfg(self.config.get("rollout", {}), "temperature", 1.0))
+
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
+    def compute_log_prob(self, data: DataProto) -> DataProto:
+        assert self._is_actor
+        self._lp_meta(data, self.rollout_cfg if self.rollout_cfg is not None else self.config.rollout)
+        with self.actor_engine.eval_mode():
+            lp, ent = self.actor.compute_log_prob(data, calculate_entropy=True)
+        out = DataProto.from_dict(tensors={"old_log_probs": lp.cpu(), "entropys": ent.cpu()},
+                                  meta_info={"temperature": data.meta_info["temperature"]})
+        return out
+
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("ref"))
+    def compute_ref_log_prob(self, data: DataProto) -> DataProto:
+        assert self._is_ref
+        self._lp_meta(data, self.ref_cfg or self.config.ref)
+        with self.ref_engine.eval_mode():
+            lp, _ = self.ref_policy.compute_log_prob(data, calculate_entropy=False)
+        return DataProto.from_dict(tensors={"ref_log_prob": lp.cpu()})
+
+    # ------------------------------------------------------------------ update
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
+    def update_actor(self, data: DataProto) -> DataProto:
+        assert self._is_actor
+        data.meta_info.setdefault("temperature", _cfg(self.config.get("rollout", {}), "temperature", 1.0))
+        t0 = time.perf_counter()
+        with self.actor_engine.train_mode():
+            metrics = self.actor.update_policy(data)
+        dt = time.perf_counter() - t0
+        lr = self.actor_engine._lr()
+        self.actor_engine.lr_scheduler_step()
+        metrics["actor/lr"] = lr
+        tokens = data.meta_info.get("global_token_num")
+        if tokens is not None:
+            from ..utils.flops_counter import FlopsCounter
+
+            est, promised = FlopsCounter(self.model_config).estimate_flops(tokens, dt)
+            metrics["perf/mfu/actor"] = est * self.actor_cfg.ppo_epochs / promised / self.world
+        return DataProto(meta_info={"metrics": metrics})
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL, blocking=False)
+    def update_weights(self, global_steps: Optional[int] = None):
+        """Push the trainer's current weights into the rollout engine."""
+        t0 = time.perf_counter()
+        if self._is_actor and self._is_rollout and self._rollout_flat is not None:
+            self._sync_rollout_weights()
+        if self.rollout_engine is not None:
+            self.rollout_engine.clear_kv_cache()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        return {"resync_s": time.perf_counter() - t0}
+
+    # -------------------------------------------------------------- checkpoint
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def save_checkpoint(self, local_path, hdfs_path=None, global_step=0, max_ckpt_to_keep=None):
+        assert self._is_actor
+        contents = tuple(_cfg(self.actor_cfg.checkpoint, "save_contents", ("model", "optimizer", "extra")))
+        self.actor_engine.save_checkpoint(local_path, hdfs_path, global_step, max_ckpt_to_keep, save_contents=contents)
+        if dist.is_initialized():
+            dist.barrier()
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=False):
+        assert self._is_actor
+        contents = tuple(_cfg(self.actor_cfg.checkpoint, "load_contents", ("model", "optimizer", "extra")))
+        self.actor_engine.load_checkpoint(local_path, hdfs_path, del_local_after_load, load_contents=contents)
+        if self._rollout_flat is not None:
+            self._sync_rollout_weights()
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def start_profile(self, **kwargs):
+        from ..utils.profiler.profile import DistProfiler
+
+        self._profiler = DistProfiler(self.dp_rank, _cfg(self.actor_cfg or self.rollout_cfg, "profiler", None))
+        self._profiler.start(**kwargs)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def stop_profile(self):
+        if getattr(self, "_profiler", None) is not None:
+            self._profiler.stop()
+
+
+class AsyncActorRolloutRefWorker(ActorRolloutRefWorker):
+    """Same worker; kept as a distinct name because the reference selects it for ``rollout.mode=async``."""
+
+
+class CriticWorker(_WorkerBase):
+    def __init__(self, config, device_name: Optional[str] = None, **kwargs):
+        super().__init__(config, device_name)
+        self.critic_cfg = omega_conf_to_dataclass(config)
+        self._norm_batch(self.critic_cfg, n=int(_cfg(self.critic_cfg, "rollout_n", 1)))
+        self._register_dispatch_collect_info("critic", dp_rank=self.dp_rank, is_collect=True)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def init_model(self):
+        model_cfg, state = resolve_model_config(self.critic_cfg.model)
+        model_cfg.num_labels = 1
+        if state is not None:
+            state = {k: v for k, v in state.items() if not k.startswith("lm_head")}
+        group = dist.group.WORLD if dist.is_initialized() and self.world > 1 else None
+        eng_cfg = _cfg(self.critic_cfg.model, "fsdp_config", None)
+        self.engine = NativeEngine(model_cfg, eng_cfg, self.critic_cfg.optim, value_head=True, device=str(self.device),
+                                   group=group, seed=int(_cfg(eng_cfg, "seed", 42)), state_dict=state,
+                                   gradient_checkpointing=bool(_cfg(self.critic_cfg.model, "enable_gradient_checkpointing", True))
+                                   ).initialize()
+        self.critic = DataParallelPPOCritic(self.critic_cfg, self.engine)
+        self.model_config = model_cfg
+
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("critic"))
+    def compute_values(self, data: DataProto) -> DataProto:
+        c = self.critic_cfg
+        data.meta_info.setdefault("micro_batch_size", c.forward_micro_batch_size_per_gpu or c.ppo_micro_batch_size_per_gpu)
+        data.meta_info.setdefault("max_token_len", c.forward_max_token_len_per_gpu)
+        data.meta_info.setdefault("use_dynamic_bsz", c.use_dynamic_bsz)
+        with self.engine.eval_mode():
+            values = self.critic.compute_values(data)
+        return DataProto.from_dict(tensors={"values": values.cpu()})
+
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("critic"))
+    def update_critic(self, data: DataProto) -> DataProto:
+        with self.engine.train_mode():
+            metrics = self.critic.update_critic(data)
+        metrics["critic/lr"] = self.engine._lr()
+        self.engine.lr_scheduler_step()
+        return DataProto(meta_info={"metrics": metrics})
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def save_checkpoint(self, local_path, hdfs_path=None, global_step=0, max_ckpt_to_keep=None):
+        self.engine.save_checkpoint(local_path, hdfs_path, global_step, max_ckpt_to_keep)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def load_checkpoint(self, local_path, hdfs_path=None, del_local_after_load=True):
+        self.engine.load_checkpoint(local_path, hdfs_path, del_local_after_load)
+
+
+class RewardModelWorker(_WorkerBase):
+    """Discriminative reward model: a value-head transformer whose score at the last valid response token is
+    the sequence reward (verl/workers/fsdp_workers.py:1626-1981)."""
+
+    def __init__(self, config, device_name: Optional[str] = None, **kwargs):
+        super().__init__(config, device_name)
+        self._register_dispatch_collect_info("reward", dp_rank=self.dp_rank, is_collect=True)
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def init_model(self):
+        model_cfg, state = resolve_model_config(self.config.model)
+        model_cfg.num_labels = 1
+        if state is not None:
+            state = {k: v for k, v in state.items() if not k.startswith("lm_head")}
+        group = dist.group.WORLD if dist.is_initialized() and self.world > 1 else None
+        self.engine = NativeEngine(model_cfg, None, None, value_head=True, device=str(self.device), group=group,
+                                   trainable=False, state_dict=state).initialize()
+
+    @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("reward"))
+    def compute_rm_score(self, data: DataProto) -> DataProto:
+        from ..models import PackedBatch
+
+        ids, mask = data.batch["input_ids"].to(self.device), data.batch["attention_mask"].to(self.device)
+        R = data.batch["responses"].shape[-1]
+        micro = int(_cfg(self.config, "micro_batch_size_per_gpu", None) or len(data))
+        scores = []
+        with torch.no_grad():
+            for s in range(0, len(data), micro):
+                i, m = ids[s : s + micro], mask[s : s + micro]
+                packed, _ = PackedBatch.from_padded(i, m)
+                last_rows = packed.cu_seqlens[1:].long() - 1
+                scores.append(self.engine.forward_values(packed, last_rows))
+        score = torch.cat(scores).float().cpu()
+        resp_len = data.batch["attention_mask"][:, -R:].sum(-1).clamp(min=1)
+        rm = torch.zeros(len(data), R)
+        rm[torch.arange(len(data)), resp_len - 1] = score
+        return DataProto.from_dict(tensors={"rm_scores": rm})
