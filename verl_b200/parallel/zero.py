@@ -39,6 +39,8 @@ class ZeroUnit:
     shard: int = 0
     offset: int = 0  # offset of this unit's shard inside the rank-flat buffers
     offsets: list = field(default_factory=list)  # per-parameter offsets inside the unit's flat vector
+    shapes: list = field(default_factory=list)  # parameter shapes (parameters are emptied while released)
+    numels: list = field(default_factory=list)
     full: Optional[torch.Tensor] = None  # gathered working-dtype buffer (None when released)
     full_grad: Optional[torch.Tensor] = None  # unit-sized fp32 gradient buffer during backward (W > 1)
     gather_count: int = 0
@@ -68,6 +70,8 @@ class ZeroShardedParams:
             cur = 0
             for p in u.params:
                 u.offsets.append(cur)
+                u.shapes.append(tuple(p.shape))
+                u.numels.append(p.numel())
                 cur += (p.numel() + 7) // 8 * 8  # keep every tensor 16-byte aligned in bf16
             u.numel = cur
             quantum = align * self.world
@@ -113,10 +117,10 @@ class ZeroShardedParams:
                 self.shard16[dst].copy_(src.to(self.work_dtype))
 
     def _bind(self, u: ZeroUnit, full: torch.Tensor, full_grad: Optional[torch.Tensor]):
-        for p, o in zip(u.params, u.offsets):
-            p.data = full[o : o + p.numel()].view(p.shape)
+        for p, o, shape, n in zip(u.params, u.offsets, u.shapes, u.numels):
+            p.data = full[o : o + n].view(shape)
             if full_grad is not None and p.requires_grad:
-                p.main_grad = full_grad[o : o + p.numel()].view(p.shape)
+                p.main_grad = full_grad[o : o + n].view(shape)
 
     def _unbind(self, u: ZeroUnit):
         empty = torch.empty(0, dtype=self.work_dtype, device=self.device)
@@ -186,8 +190,8 @@ class ZeroShardedParams:
 
     def full_tensor(self, u: ZeroUnit, idx: int, dtype=None) -> torch.Tensor:
         """One full parameter of a (currently gathered) unit."""
-        p, o = u.params[idx], u.offsets[idx]
-        t = u.full[o : o + p.numel()].view(p.shape)
+        o = u.offsets[idx]
+        t = u.full[o : o + u.numels[idx]].view(u.shapes[idx])
         return t if dtype is None else t.to(dtype)
 
     def named_full_tensors(self, dtype=None):
@@ -207,11 +211,11 @@ class ZeroShardedParams:
         missing = []
         for u in self.units:
             lo, hi = self.rank * u.shard, (self.rank + 1) * u.shard
-            for name, p, o in zip(u.names, u.params, u.offsets):
+            for name, n, o in zip(u.names, u.numels, u.offsets):
                 if name not in state:
                     missing.append(name)
                     continue
-                s, e = max(o, lo), min(o + p.numel(), hi)
+                s, e = max(o, lo), min(o + n, hi)
                 if s >= e:
                     continue
                 src = state[name].reshape(-1)[s - o : e - o].to(self.device)
@@ -230,7 +234,7 @@ class ZeroShardedParams:
     # ------------------------------------------------------------ sharded state io
     def shard_state(self) -> dict:
         """This rank's shard of model / optimizer state plus the layout needed to re-assemble it."""
-        layout = [{"name": u.name, "names": u.names, "shapes": [tuple(p.shape) for p in u.params], "offsets": u.offsets,
+        layout = [{"name": u.name, "names": u.names, "shapes": list(u.shapes), "offsets": u.offsets,
                    "numel": u.numel, "padded": u.padded, "shard": u.shard, "offset": u.offset} for u in self.units]
         out = {"layout": layout, "world_size": self.world, "rank": self.rank, "shard16": self.shard16.cpu()}
         if self.trainable:

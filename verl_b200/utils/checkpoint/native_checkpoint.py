@@ -49,7 +49,7 @@ def _param_slices(zero, flat: torch.Tensor) -> dict:
     out = {}
     for u in zero.units:
         lo, hi = zero.rank * u.shard, (zero.rank + 1) * u.shard
-        for name, p_shape, o in zip(u.names, [tuple(p.shape) for p in u.params], u.offsets):
+        for name, p_shape, o in zip(u.names, u.shapes, u.offsets):
             n = int(np.prod(p_shape)) if len(p_shape) else 1
             s, e = max(o, lo), min(o + n, hi)
             if s >= e:

@@ -7,12 +7,18 @@ service, and the two synthetic token rules used by the benchmark configs.
 
 from __future__ import annotations
 
-from . import geo3k, gsm8k, math_dapo, math_reward, search_r1_like_qa_em
+from . import geo3k, gsm8k, math_dapo, math_reward, search_r1_like_qa_em, synthetic
 
 
 def default_compute_score(data_source, solution_str, ground_truth, extra_info=None, sandbox_fusion_url=None,
                           concurrent_semaphore=None, memory_limit_mb=None, **kwargs):
-    if data_source == "openai/gsm8k":
+    if data_source == "synthetic/even_fraction":
+        res = synthetic.even_fraction(solution_str, ground_truth, extra_info)
+    elif data_source == "synthetic/even_fraction_threshold":
+        res = synthetic.even_fraction(solution_str, ground_truth, extra_info, threshold=0.5)
+    elif data_source == "synthetic/contains_token":
+        res = synthetic.contains_token(solution_str, ground_truth, extra_info)
+    elif data_source == "openai/gsm8k":
         res = gsm8k.compute_score(solution_str, ground_truth)
     elif data_source in ("lighteval/MATH", "DigitalLearningGmbH/MATH-lighteval", "HuggingFaceH4/MATH-500"):
         res = math_reward.compute_score(solution_str, ground_truth)

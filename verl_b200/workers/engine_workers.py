@@ -195,10 +195,9 @@ class ActorRolloutRefWorker(_WorkerBase):
         for u in z.units:
             buf = torch.zeros(u.padded, dtype=z.work_dtype, device=self.device)
             self._rollout_flat.append(buf)
-            for name, p, o in zip(u.names, u.params, u.offsets):
+            for name, shape, n, o in zip(u.names, u.shapes, u.numels, u.offsets):
                 if name in own:
-                    n = own[name].numel()
-                    own[name].data = buf[o : o + n].view(own[name].shape)
+                    own[name].data = buf[o : o + n].view(shape)
         self._sync_rollout_weights()
 
     @torch.no_grad()
@@ -240,8 +239,8 @@ class ActorRolloutRefWorker(_WorkerBase):
         gen_time = time.perf_counter() - t0
         out.non_tensor_batch.update(prompts.non_tensor_batch)
         n_tok = int(out.batch["response_mask"].sum())
-        out.meta_info["timing"] = {"generate_sequences": gen_time}
-        out.meta_info["metrics"] = {"rollout/num_preempted": float(sum(o.num_preempted for o in outs)),
+        out.meta_info["metrics"] = {"rollout/generate_sequences_s": gen_time,
+                                    "rollout/num_preempted": float(sum(o.num_preempted for o in outs)),
                                     "rollout/tokens_per_s": n_tok / max(gen_time, 1e-9)}
         if rc.free_cache_engine and not meta.get("keep_cache", False):
             eng.sleep()
