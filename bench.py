@@ -1,0 +1,285 @@
+"""Headline benchmark: end-to-end GRPO step throughput (tokens/s over the whole job) on the
+Qwen2.5-7B architecture, random-init weights, synthetic prompts.
+
+    python bench.py --gpus 1 --steps 2 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus 8 --steps 2 --warmup 3
+
+One step = rollout (n samples per prompt, paged-KV engine) -> reward -> old log-probs -> reference log-probs ->
+GRPO advantages -> actor update (fwd + bwd + optimizer) -> weight sync to the rollout engine, all through
+``RayPPOTrainer.train_step`` in SPMD mode (one controller replica per GPU). Weak scaling: every GPU gets
+``--prompts-per-gpu`` prompts (128 prompts x 8 samples at 8 GPUs).
+
+Rank 0 prints one JSON line. ``value`` is device-timed (CUDA events, max over ranks) over exactly K steps;
+``e2e`` times K further steps with the host clock, each including the pinned-host -> device copy of the step's
+prompts and a device -> host read of the step's loss.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen2.5-7b")
+    ap.add_argument("--prompts-per-gpu", type=int, default=16)
+    ap.add_argument("--n", type=int, default=8)
+    ap.add_argument("--min-prompt", type=int, default=256)
+    ap.add_argument("--max-prompt", type=int, default=512)
+    ap.add_argument("--max-response", type=int, default=1024)
+    ap.add_argument("--max-token-len", type=int, default=16384)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run as reduced)")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def reference_arm(args):
+    """The reference installs only with --no-deps and cannot be imported: ``import verl`` needs ray, tensordict,
+    hydra-core, omegaconf, peft, codetiming and accelerate, none of which is installable offline here."""
+    ref = os.path.join(REPO, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref, "verl")):
+        why = "baseline/_ref is absent: pip install of /root/reference did not run on this box"
+    else:
+        probe = subprocess.run([sys.executable, "-c", "import sys; sys.path.insert(0, sys.argv[1]); import verl",
+                                ref], capture_output=True, text=True, cwd=tempfile.gettempdir())
+        if probe.returncode != 0:
+            last = (probe.stderr.strip().splitlines() or ["import failed"])[-1]
+            why = f"import verl fails offline ({last}); its dependencies ray/tensordict/hydra-core/omegaconf are not in the wheelhouse"
+        else:
+            why = "reference imports but its stock main_ppo path needs a Ray cluster and vLLM workers that were not validated here"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of this process's GPU in the background (read-only queries)."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.path = os.path.join(tempfile.gettempdir(), f"verl_b200_clocks_{os.getpid()}.csv")
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(5)
+        except Exception:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_config(args, world: int):
+    from verl_b200.utils.config import compose
+
+    per_gpu = args.prompts_per_gpu
+    global_prompts = per_gpu * world
+    ov = [
+        f"actor_rollout_ref.model.path=preset:{args.model}", "trainer.device=cuda", f"trainer.n_gpus_per_node={world}",
+        "trainer.nnodes=1", "trainer.logger=[]", "trainer.val_before_train=false", "trainer.save_freq=-1", "trainer.test_freq=-1",
+        "trainer.balance_batch=false", "trainer.resume_mode=disable", "trainer.total_epochs=1000",
+        f"data.train_files=synthetic:{global_prompts * 4}:{args.min_prompt}:{args.max_prompt}:100:151000:0:synthetic/contains_token:4242",
+        "data.val_files=null", f"data.train_batch_size={global_prompts}", f"data.max_prompt_length={args.max_prompt}",
+        f"data.max_response_length={args.max_response}", "data.shuffle=false",
+        "algorithm.adv_estimator=grpo", f"actor_rollout_ref.rollout.n={args.n}", "actor_rollout_ref.rollout.temperature=1.0",
+        f"actor_rollout_ref.rollout.max_num_seqs={max(per_gpu * args.n, 8)}", "actor_rollout_ref.rollout.max_num_batched_tokens=8192",
+        "actor_rollout_ref.rollout.tensor_model_parallel_size=1", "actor_rollout_ref.rollout.gpu_memory_utilization=0.12",
+        "actor_rollout_ref.rollout.log_prob_use_dynamic_bsz=true", f"actor_rollout_ref.rollout.log_prob_max_token_len_per_gpu={2 * args.max_token_len}",
+        "actor_rollout_ref.ref.log_prob_use_dynamic_bsz=true", f"actor_rollout_ref.ref.log_prob_max_token_len_per_gpu={2 * args.max_token_len}",
+        f"actor_rollout_ref.actor.ppo_mini_batch_size={global_prompts}", "actor_rollout_ref.actor.use_dynamic_bsz=true",
+        f"actor_rollout_ref.actor.ppo_max_token_len_per_gpu={args.max_token_len}", "actor_rollout_ref.actor.use_kl_loss=true",
+        "actor_rollout_ref.actor.kl_loss_coef=0.001", "actor_rollout_ref.actor.optim.lr=1e-6",
+    ]
+    if args.layers:
+        ov.append(f"+actor_rollout_ref.model.override_config.num_hidden_layers={args.layers}")
+    return compose("ppo_trainer", ov)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) == 0:
+            reference_arm(args)
+        return
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl")
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    os.environ["VERL_B200_SPMD"] = "1"
+
+    from verl_b200.ops import _lib
+    from verl_b200.single_controller.spmd import SPMDResourcePool, SPMDWorkerGroup
+    from verl_b200.trainer.main_ppo import build_tokenizer, create_rl_dataset, create_rl_sampler
+    from verl_b200.trainer.ppo.ray_trainer import RayPPOTrainer, ResourcePoolManager
+    from verl_b200.trainer.ppo.reward import load_reward_manager
+    from verl_b200.trainer.ppo.utils import Role
+    from verl_b200.workers.engine_workers import ActorRolloutRefWorker
+
+    _lib.load(build_if_missing=False)
+    cfg = build_config(args, world)
+    tok = build_tokenizer(cfg)
+    ds = create_rl_dataset(cfg.data.train_files, cfg.data, tok)
+    rpm = ResourcePoolManager({"global_pool": [1]}, {Role.ActorRollout: "global_pool"}, pool_cls=SPMDResourcePool)
+    trainer = RayPPOTrainer(config=cfg, tokenizer=tok, role_worker_mapping={Role.ActorRollout: ActorRolloutRefWorker},
+                            resource_pool_manager=rpm, ray_worker_group_cls=SPMDWorkerGroup,
+                            reward_fn=load_reward_manager(cfg, tok), val_reward_fn=None, train_dataset=ds,
+                            train_sampler=create_rl_sampler(cfg.data, ds), device_name="cuda")
+    trainer.init_workers()
+
+    def batches():
+        while True:
+            for b in trainer.train_dataloader:
+                yield b
+
+    it = batches()
+    dev = torch.device("cuda", local)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_e2e(batch_dict):
+        """The user-facing call with explicit staging: prompts start in pinned host memory and are copied to the
+        device, the step's loss is read back to the host."""
+        h2d = 0
+        staged = {}
+        for k, v in batch_dict.items():
+            if isinstance(v, torch.Tensor):
+                pinned = v.pin_memory()
+                staged[k] = pinned.to(dev, non_blocking=True)
+                h2d += pinned.numel() * pinned.element_size()
+        torch.cuda.current_stream().synchronize()
+        m = trainer.train_step(batch_dict)
+        loss = torch.tensor([m.get("actor/pg_loss", 0.0), m.get("actor/kl_loss", 0.0)], device=dev)
+        host = loss.cpu()
+        return m, h2d // max(world, 1) * world, host.numel() * host.element_size()
+
+    for _ in range(args.warmup):
+        trainer.train_step(next(it))
+
+    # ---- device-timed region: exactly K steps ----
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    tokens = 0
+    last = {}
+    for _ in range(args.steps):
+        last = trainer.train_step(next(it))
+        tokens += int(last["perf/total_num_tokens"])
+    ev1.record()
+    barrier()
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    launches = torch.tensor([float(_lib.launch_count() - launches0)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(launches)
+    clocks = sampler.stop() if rank == 0 else {}
+    total_ms = ms.item()
+
+    e2e = None
+    if not args.no_e2e:
+        barrier()
+        t0 = time.perf_counter()
+        e_tokens, h2d, d2h = 0, 0, 0
+        for _ in range(args.steps):
+            m, hi, do = step_e2e(next(it))
+            e_tokens += int(m["perf/total_num_tokens"])
+            h2d, d2h = hi, do
+        barrier()
+        dt = torch.tensor([time.perf_counter() - t0], device=dev)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e = {"value": e_tokens / dt.item(), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "timer": "host clock around K steps incl. pinned H2D of prompts and D2H of the loss"}
+
+    if rank == 0:
+        c = trainer.actor_rollout_wg.worker.worker_dict["actor_rollout"].model_config
+        out = {
+            "metric": "RL step tokens/s/box (GRPO, rollout+logprob+ref+update+resync)", "value": tokens / (total_ms / 1e3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic prompts (uniform ids), random-init weights", "impl": "ours",
+            "config": {"model": args.model if not args.layers else f"{args.model}-REDUCED-{args.layers}L",
+                       "layers": c.num_hidden_layers, "hidden": c.hidden_size, "vocab": c.vocab_size,
+                       "global_batch": args.prompts_per_gpu * world * args.n, "prompts": args.prompts_per_gpu * world,
+                       "n_samples": args.n, "seq_len": args.max_prompt + args.max_response,
+                       "prompt_len": [args.min_prompt, args.max_prompt], "max_response": args.max_response,
+                       "parallelism": f"zero3-dp{world}, rollout tp1 x {world} replicas",
+                       "cache": "inputs larger than L2 (15 GB of weights streamed per pass)",
+                       "timer": "CUDA events on the step stream, max over ranks"},
+            "clocks": clocks, "gpu_launches": int(launches.item()),
+            "breakdown_s": {k.split("/", 1)[1]: round(v, 3) for k, v in last.items() if k.startswith("timing_s/")},
+            "rollout_tokens_per_s_per_gpu": last.get("rollout/tokens_per_s"),
+            "resync_ms": 1e3 * last.get("timing_s/resync", 0.0),
+            "mfu_actor": last.get("perf/mfu/actor"),
+        }
+        if e2e is not None:
+            out["e2e"] = e2e
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
