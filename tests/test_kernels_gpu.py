@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _bf16_close(got, ref, scale=None, ulps=4.0):
-    got, ref = got.float(), ref.float()
+    got, ref = got.float(), ref.float().to(got.device)
     scale = ref.abs().max().item() if scale is None else scale
     err = (got - ref).abs().max().item()
     assert err <= ulps * 2 ** -8 * scale + 1e-6, f"max err {err} vs scale {scale}"
@@ -215,8 +215,9 @@ def test_ppo_loss_fused_matches_torch():
                                     clip_c=3.0, kl_coef=0.01, kl_type="low_var_kl", entropy_coeff=0.001)
     loss.backward()
     lr, er = logp.detach().clone().requires_grad_(True), ent.detach().clone().requires_grad_(True)
-    pg, clipfrac, ppo_kl, clipfrac_lower = core_algos.compute_policy_loss_vanilla(
-        old, lr, adv, mask, loss_agg_mode="token-mean", clip_ratio_low=0.2, clip_ratio_high=0.28, clip_ratio_c=3.0)
+    pg, clipfrac, ppo_kl, clipfrac_lower = core_algos.compute_policy_loss(
+        old, lr, adv, mask, cliprange=0.2, cliprange_low=0.2, cliprange_high=0.28, clip_ratio_c=3.0,
+        loss_agg_mode="token-mean")
     kld = core_algos.kl_penalty(lr, ref_lp, "low_var_kl")
     kl_loss = core_algos.agg_loss(kld, mask, "token-mean")
     ent_loss = core_algos.agg_loss(er, mask, "token-mean")

@@ -1,0 +1,252 @@
+// Collectives over NVLink peer memory, written as kernels (no NCCL on these paths).
+//
+// Every rank maps every peer's symmetric buffers (allocation and handle exchange are done by the
+// host through torch's symmetric-memory allocator); kernels then read peers with plain ld.global
+// over NVLink or, where a multicast mapping exists, with multimem.ld_reduce through NVSwitch.
+// No TMA is issued on peer memory and no cluster-wide broadcast loads are used anywhere.
+//
+// Synchronisation: one signal pad per rank, `world` 32-bit slots per channel. A barrier writes a
+// monotonically increasing epoch into slot [my rank] of every peer's pad and waits until all slots
+// of its own pad reach the epoch. Waits are bounded (VB_WAIT_LIMIT_NS): on expiry the kernel
+// records ERR_WAIT_FLAG in the status word and returns, so a missing peer never hangs the GPU.
+//
+// Kernels:
+//   peer_barrier            all ranks arrive / depart (also orders prior writes: release/acquire at system scope)
+//   peer_all_gather         out[p*shard : (p+1)*shard] = peer p's shard (replaces NCCL all-gather in ZeRO-3)
+//   peer_reduce_scatter_add dst[i] += scale * sum_p peer p's full[rank*shard + i]  (fp32; grad reduce-scatter
+//                           fused with the scale and the accumulation into the optimizer's gradient shard)
+//   nvls_reduce_scatter_add same through multimem.ld_reduce (in-switch add)
+//   peer_segment_copy       table-driven gather of byte ranges from peers into a local buffer: the
+//                           train -> rollout weight reshard (FSDP shards -> TP/EP layout) in one launch
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace vb {
+
+constexpr int MAX_RANKS = 16;
+
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// Block 0 performs the cross-rank handshake; the other blocks of the grid are released through a
+// local flag in global memory (grid-local, same bounded wait).
+__device__ bool barrier_all_ranks(const PeerPtrs& pads, int rank, int world, int channel, uint32_t epoch,
+                                  int* status) {
+  // each thread t < world handles peer t
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  __threadfence_system();
+  if ((int)threadIdx.x < world) {
+    uint32_t* remote = reinterpret_cast<uint32_t*>(pads.p[threadIdx.x]) + channel * MAX_RANKS + rank;
+    st_release_sys(remote, epoch);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(pads.p[rank]) + channel * MAX_RANKS + threadIdx.x;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    // epochs only grow; signed difference tolerates wrap-around
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > VB_WAIT_LIMIT_NS) {
+        report_error(status, ERR_WAIT_FLAG, (int)threadIdx.x);
+        ok_s = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+__global__ void peer_barrier_kernel(PeerPtrs pads, int rank, int world, int channel, uint32_t epoch, int* status) {
+  barrier_all_ranks(pads, rank, world, channel, epoch, status);
+}
+
+// grid-wide: block 0 does the handshake, then publishes `epoch` in *gate; other blocks wait on *gate.
+__device__ bool grid_enter(const PeerPtrs& pads, int rank, int world, int channel, uint32_t epoch, uint32_t* gate,
+                           int* status) {
+  __shared__ int ok_b;
+  if (blockIdx.x == 0) {
+    bool ok = barrier_all_ranks(pads, rank, world, channel, epoch, status);
+    if (threadIdx.x == 0) {
+      st_release_sys(gate, ok ? epoch : (epoch | 0x80000000u));
+      ok_b = ok ? 1 : 0;
+    }
+  } else if (threadIdx.x == 0) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0, v;
+    ok_b = 1;
+    while (((v = ld_acquire_sys(gate)) & 0x7fffffffu) != (epoch & 0x7fffffffu)) {
+      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > 2 * VB_WAIT_LIMIT_NS) {
+        report_error(status, ERR_WAIT_FLAG, 1000 + (int)blockIdx.x);
+        ok_b = 0;
+        break;
+      }
+    }
+    if (ok_b && (v & 0x80000000u)) ok_b = 0;
+  }
+  __syncthreads();
+  return ok_b != 0;
+}
+
+// out (local) <- all peers' shards. srcs.p[r] = base of rank r's symmetric buffer; the shard sits at byte
+// offset src_off in every rank's buffer. Units of 16 bytes.
+__global__ void peer_all_gather_kernel(PeerPtrs srcs, PeerPtrs pads, long long src_off16, uint4* __restrict__ out,
+                                       long long shard16, int rank, int world, int channel, uint32_t epoch,
+                                       uint32_t* gate, int* status) {
+  if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
+  const long long total = shard16 * world;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += stride) {
+    // start each rank on a different peer so the links are used evenly
+    const long long j = (i + (long long)rank * shard16) % total;
+    const int p = (int)(j / shard16);
+    const long long k = j - (long long)p * shard16;
+    const uint4* src = reinterpret_cast<const uint4*>(srcs.p[p]) + src_off16 + k;
+    out[j] = __ldg(src);
+  }
+}
+
+// dst[i] += scale * sum_p full_p[rank*shard + i], i in [0, shard). fulls.p[r] = base of rank r's symmetric
+// gradient buffer (the unit's full gradient at float offset full_off). float4 granularity.
+__global__ void peer_reduce_scatter_add_kernel(PeerPtrs fulls, PeerPtrs pads, long long full_off4,
+                                               float4* __restrict__ dst, long long shard4, float scale, int rank,
+                                               int world, int channel, uint32_t epoch, uint32_t* gate, int* status) {
+  if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < shard4; i += stride) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = 0; q < world; ++q) {
+      const int p = (rank + q) % world;
+      const float4 v = __ldg(reinterpret_cast<const float4*>(fulls.p[p]) + full_off4 + (long long)rank * shard4 + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float4 d = dst[i];
+    d.x += scale * acc.x; d.y += scale * acc.y; d.z += scale * acc.z; d.w += scale * acc.w;
+    dst[i] = d;
+  }
+}
+
+// Same reduction through the NVSwitch: one multimem.ld_reduce returns the sum over all ranks' copies.
+__global__ void nvls_reduce_scatter_add_kernel(const float* mc_base, PeerPtrs pads, long long full_off4,
+                                               float4* __restrict__ dst, long long shard4, float scale, int rank,
+                                               int world, int channel, uint32_t epoch, uint32_t* gate, int* status) {
+  if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const float4* src = reinterpret_cast<const float4*>(mc_base) + full_off4 + (long long)rank * shard4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < shard4; i += stride) {
+    float4 acc;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(acc.x), "=f"(acc.y), "=f"(acc.z), "=f"(acc.w)
+                 : "l"(src + i)
+                 : "memory");
+    float4 d = dst[i];
+    d.x += scale * acc.x; d.y += scale * acc.y; d.z += scale * acc.z; d.w += scale * acc.w;
+    dst[i] = d;
+  }
+}
+
+struct Segment {
+  long long src_off;  // bytes from the base of the source rank's symmetric buffer (16-byte aligned)
+  long long dst_off;  // bytes from dst_base (16-byte aligned)
+  long long nbytes;   // multiple of 16
+  int src_rank;
+  int pad;
+};
+
+// One block walks whole segments (grid-stride over the table); large segments are split by the planner.
+__global__ void peer_segment_copy_kernel(PeerPtrs srcs, PeerPtrs pads, const Segment* __restrict__ segs, int nseg,
+                                         uint8_t* __restrict__ dst_base, int rank, int world, int channel,
+                                         uint32_t epoch, uint32_t* gate, int* status) {
+  if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
+  for (int s = blockIdx.x; s < nseg; s += gridDim.x) {
+    const Segment sg = segs[s];
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(srcs.p[sg.src_rank]) + sg.src_off);
+    uint4* dst = reinterpret_cast<uint4*>(dst_base + sg.dst_off);
+    const long long n16 = sg.nbytes >> 4;
+    for (long long i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldg(src + i);
+  }
+}
+
+static PeerPtrs make_ptrs(const void* const* arr, int world) {
+  PeerPtrs pp{};
+  for (int i = 0; i < world && i < MAX_RANKS; ++i) pp.p[i] = const_cast<void*>(arr[i]);
+  return pp;
+}
+
+}  // namespace vb
+
+using namespace vb;
+
+extern "C" int vb_peer_max_ranks() { return MAX_RANKS; }
+
+extern "C" int vb_peer_barrier(const void* const* pads, int rank, int world, int channel, unsigned epoch, int* status,
+                               cudaStream_t stream) {
+  if (world > MAX_RANKS) return -3;
+  peer_barrier_kernel<<<1, 32, 0, stream>>>(make_ptrs(pads, world), rank, world, channel, epoch, status);
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+// All byte counts / offsets must be multiples of 16. `gate` is a device uint32 owned by the caller (per channel).
+extern "C" int vb_peer_all_gather(const void* const* srcs, const void* const* pads, long long src_off_bytes, void* out,
+                                  long long shard_bytes, int rank, int world, int channel, unsigned epoch,
+                                  unsigned* gate, int* status, cudaStream_t stream) {
+  if (world > MAX_RANKS || (src_off_bytes & 15) || (shard_bytes & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return -3;
+  const long long total16 = (shard_bytes >> 4) * world;
+  long long blocks = (total16 + 255) / 256;
+  const int cap = vb_num_sms();  // all blocks must be co-resident with block 0: at most one wave
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  peer_all_gather_kernel<<<(int)blocks, 256, 0, stream>>>(make_ptrs(srcs, world), make_ptrs(pads, world),
+                                                          src_off_bytes >> 4, reinterpret_cast<uint4*>(out),
+                                                          shard_bytes >> 4, rank, world, channel, epoch, gate, status);
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vb_peer_reduce_scatter_add(const void* const* fulls, const void* const* pads, const void* mc_base,
+                                          long long full_off_bytes, float* dst, long long shard_floats, float scale,
+                                          int rank, int world, int channel, unsigned epoch, unsigned* gate, int* status,
+                                          cudaStream_t stream) {
+  if (world > MAX_RANKS || (full_off_bytes & 15) || (shard_floats & 3) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -3;
+  const long long shard4 = shard_floats >> 2;
+  long long blocks = (shard4 + 255) / 256;
+  const int cap = vb_num_sms();
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  if (mc_base != nullptr) {
+    nvls_reduce_scatter_add_kernel<<<(int)blocks, 256, 0, stream>>>(
+        reinterpret_cast<const float*>(mc_base), make_ptrs(pads, world), full_off_bytes >> 4,
+        reinterpret_cast<float4*>(dst), shard4, scale, rank, world, channel, epoch, gate, status);
+  } else {
+    peer_reduce_scatter_add_kernel<<<(int)blocks, 256, 0, stream>>>(
+        make_ptrs(fulls, world), make_ptrs(pads, world), full_off_bytes >> 4, reinterpret_cast<float4*>(dst), shard4,
+        scale, rank, world, channel, epoch, gate, status);
+  }
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+// segs: device array of {int64 src_off, int64 dst_off, int64 nbytes, int32 src_rank, int32 pad} (32 bytes each).
+extern "C" int vb_peer_segment_copy(const void* const* srcs, const void* const* pads, const void* segs, int nseg,
+                                    void* dst_base, int rank, int world, int channel, unsigned epoch, unsigned* gate,
+                                    int* status, cudaStream_t stream) {
+  if (world > MAX_RANKS) return -3;
+  if (nseg <= 0) return 0;
+  int blocks = nseg < vb_num_sms() ? nseg : vb_num_sms();
+  peer_segment_copy_kernel<<<blocks, 512, 0, stream>>>(make_ptrs(srcs, world), make_ptrs(pads, world),
+                                                       reinterpret_cast<const Segment*>(segs), nseg,
+                                                       reinterpret_cast<uint8_t*>(dst_base), rank, world, channel, epoch,
+                                                       gate, status);
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}

@@ -80,9 +80,10 @@ class _LinearFn(torch.autograd.Function):
     def forward(ctx, x, weight, bias):
         ctx.save_for_backward(x, weight)
         ctx.has_bias = bias is not None
-        x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, weight, bias=bias, out_dtype=x.dtype if x.is_cuda else x.dtype)
-        return y.reshape(*x.shape[:-1], weight.shape[0])
+        x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+        y = gemm(x2, weight, bias=bias, out_dtype=x.dtype)
+        # a 2-D input returns the freshly allocated result itself (not a view), so callers may update it in place
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, dy):

@@ -1,0 +1,183 @@
+"""Peer-memory collectives for one NVSwitch domain (kernels in ``csrc/comm.cu``).
+
+Buffers that peers must read (parameter shards, per-unit gradient buffers, signal pads) are allocated from
+torch's symmetric-memory allocator, which maps every rank's allocation into every process and, where the
+fabric supports it, creates an NVLS multicast mapping. That is the only service taken from the library: the
+data movement and the synchronisation are this package's own kernels (plain peer loads or
+``multimem.ld_reduce``; never NCCL, never TMA on peer memory).
+
+In the reference all of this is NCCL inside torch FSDP (all-gather / reduce-scatter per layer) and NCCL /
+CUDA-IPC copies for weight sync (verl/workers/fsdp_workers.py:677-756).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+_SIGS_BOUND = False
+
+
+def _bind():
+    global _SIGS_BOUND
+    lib = _lib.load()
+    if _SIGS_BOUND:
+        return lib
+    c = ctypes
+    P, I, L, U, F = c.c_void_p, c.c_int, c.c_longlong, c.c_uint, c.c_float
+    lib.vb_peer_max_ranks.argtypes, lib.vb_peer_max_ranks.restype = [], I
+    lib.vb_peer_barrier.argtypes, lib.vb_peer_barrier.restype = [P, I, I, I, U, P, P], I
+    lib.vb_peer_all_gather.argtypes, lib.vb_peer_all_gather.restype = [P, P, L, P, L, I, I, I, U, P, P, P], I
+    lib.vb_peer_reduce_scatter_add.argtypes = [P, P, P, L, P, L, F, I, I, I, U, P, P, P]
+    lib.vb_peer_reduce_scatter_add.restype = I
+    lib.vb_peer_segment_copy.argtypes, lib.vb_peer_segment_copy.restype = [P, P, P, I, P, I, I, I, U, P, P, P], I
+    _SIGS_BOUND = True
+    return lib
+
+
+class _Alloc:
+    """One symmetric allocation: the local tensor plus every rank's base pointer."""
+
+    def __init__(self, tensor: torch.Tensor, ptrs: list[int], multicast_ptr: int):
+        self.tensor = tensor
+        self.base = tensor.data_ptr()
+        self.nbytes = tensor.numel() * tensor.element_size()
+        self.ptrs = (ctypes.c_void_p * len(ptrs))(*ptrs)
+        self.multicast_ptr = multicast_ptr
+
+    def offset_of(self, t: torch.Tensor) -> Optional[int]:
+        off = t.data_ptr() - self.base
+        if 0 <= off and off + t.numel() * t.element_size() <= self.nbytes:
+            return off
+        return None
+
+
+class PeerComm:
+    CH_GATHER, CH_REDUCE, CH_COPY, CH_BARRIER = 0, 1, 2, 3
+
+    def __init__(self, group=None, use_nvls: Optional[bool] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.symm_mem = symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.lib = _bind()
+        assert self.world <= self.lib.vb_peer_max_ranks()
+        if use_nvls is None:
+            use_nvls = os.environ.get("VERL_B200_NVLS", "1") != "0"
+        self.use_nvls = use_nvls
+        self.allocs: list[_Alloc] = []
+        self.epochs = [0, 0, 0, 0]
+        self.gates = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.pads = self.alloc(1024, torch.int32, zero=True)
+        self.pad_alloc = self.allocs[-1]
+        self._grad_bufs: list[torch.Tensor] = []
+        self._grad_next = 0
+        self.barrier()
+
+    # -------------------------------------------------------------- allocation
+    def alloc(self, numel: int, dtype: torch.dtype, zero: bool = True) -> torch.Tensor:
+        """Symmetric allocation (collective: every rank must call it with the same size, in the same order)."""
+        sm = self.symm_mem
+        group_name = self.group.group_name
+        try:
+            sm.enable_symm_mem_for_group(group_name)
+        except Exception:
+            pass
+        t = sm.empty(int(numel), dtype=dtype, device=self.device)
+        if zero:
+            t.zero_()
+        torch.cuda.synchronize(self.device)
+        hdl = sm.rendezvous(t, group_name)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        self.allocs.append(_Alloc(t, ptrs, mc))
+        self._handles = getattr(self, "_handles", []) + [hdl]
+        return t
+
+    def _find(self, t: torch.Tensor) -> tuple[_Alloc, int]:
+        for a in self.allocs:
+            off = a.offset_of(t)
+            if off is not None:
+                return a, off
+        raise ValueError("tensor is not inside a symmetric allocation of this communicator")
+
+    def is_symmetric(self, t: torch.Tensor) -> bool:
+        return any(a.offset_of(t) is not None for a in self.allocs)
+
+    def reserve_grad_buffers(self, numel: int):
+        """Two alternating fp32 buffers for per-unit gradients. While one is being reduced by slower peers the
+        next unit's backward writes the other; a buffer is reused only after a later reduce's entry barrier
+        proved that every peer finished reading it."""
+        if self._grad_bufs and self._grad_bufs[0].numel() >= numel:
+            return
+        self._grad_bufs = [self.alloc(numel, torch.float32), self.alloc(numel, torch.float32)]
+
+    def grad_buffer(self, numel: int) -> torch.Tensor:
+        assert self._grad_bufs and self._grad_bufs[0].numel() >= numel, "reserve_grad_buffers() first"
+        buf = self._grad_bufs[self._grad_next][:numel]
+        self._grad_next ^= 1
+        buf.zero_()
+        return buf
+
+    # -------------------------------------------------------------- collectives
+    def _epoch(self, ch: int) -> int:
+        self.epochs[ch] += 1
+        return self.epochs[ch]
+
+    def _gate(self, ch: int) -> int:
+        return self.gates.data_ptr() + 4 * ch
+
+    def _status(self) -> int:
+        return _lib.status_word(self.device).data_ptr()
+
+    def barrier(self):
+        rc = self.lib.vb_peer_barrier(self.pad_alloc.ptrs, self.rank, self.world, self.CH_BARRIER,
+                                      self._epoch(self.CH_BARRIER), self._status(), _lib.stream())
+        _lib.check(rc, "vb_peer_barrier")
+
+    def all_gather(self, out: torch.Tensor, src: torch.Tensor):
+        """out[r * n : (r+1) * n] = rank r's ``src`` (n = src.numel()); ``src`` must be symmetric memory."""
+        a, off = self._find(src)
+        nbytes = src.numel() * src.element_size()
+        assert out.numel() * out.element_size() == nbytes * self.world
+        rc = self.lib.vb_peer_all_gather(a.ptrs, self.pad_alloc.ptrs, off, out.data_ptr(), nbytes, self.rank, self.world,
+                                         self.CH_GATHER, self._epoch(self.CH_GATHER), self._gate(self.CH_GATHER),
+                                         self._status(), _lib.stream())
+        _lib.check(rc, "vb_peer_all_gather")
+
+    def reduce_scatter_add(self, dst: torch.Tensor, full: torch.Tensor, scale: float = 1.0):
+        """dst += scale * sum over ranks of full[rank * n : (rank+1) * n]  (fp32; ``full`` symmetric)."""
+        a, off = self._find(full)
+        n = dst.numel()
+        assert full.numel() == n * self.world and dst.dtype == torch.float32 and full.dtype == torch.float32
+        mc = a.multicast_ptr if self.use_nvls else 0
+        rc = self.lib.vb_peer_reduce_scatter_add(a.ptrs, self.pad_alloc.ptrs, ctypes.c_void_p(mc) if mc else None, off,
+                                                 dst.data_ptr(), n, float(scale), self.rank, self.world, self.CH_REDUCE,
+                                                 self._epoch(self.CH_REDUCE), self._gate(self.CH_REDUCE), self._status(),
+                                                 _lib.stream())
+        _lib.check(rc, "vb_peer_reduce_scatter_add")
+
+    def segment_copy(self, dst: torch.Tensor, src_alloc_tensor: torch.Tensor, seg_table: torch.Tensor, nseg: int):
+        """Table-driven gather from peers' copies of ``src_alloc_tensor`` into ``dst`` (see :mod:`.reshard`)."""
+        a, off0 = self._find(src_alloc_tensor)
+        assert off0 == 0, "pass the allocation's base tensor"
+        rc = self.lib.vb_peer_segment_copy(a.ptrs, self.pad_alloc.ptrs, seg_table.data_ptr(), int(nseg), dst.data_ptr(),
+                                           self.rank, self.world, self.CH_COPY, self._epoch(self.CH_COPY),
+                                           self._gate(self.CH_COPY), self._status(), _lib.stream())
+        _lib.check(rc, "vb_peer_segment_copy")
+
+    def check(self):
+        """Synchronising read of the status word; raises if a bounded wait ran out."""
+        code, blk, detail = _lib.read_status(self.device)
+        if code != 0:
+            _lib.clear_status(self.device)
+            raise RuntimeError(f"peer collective timed out (code {code}, block {blk}, peer/detail {detail})")
