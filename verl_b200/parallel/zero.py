@@ -82,7 +82,13 @@ class ZeroShardedParams:
             self.units.append(u)
         self.total_shard = off
         dev = self.device
-        self.shard16 = torch.zeros(off, dtype=work_dtype, device=dev)
+        if comm is not None and self.world > 1:
+            # peers read this shard directly over NVLink: it lives in symmetric memory
+            self.shard16 = comm.alloc(off, work_dtype)
+            if trainable:
+                comm.reserve_grad_buffers(max(u.padded for u in self.units))
+        else:
+            self.shard16 = torch.zeros(off, dtype=work_dtype, device=dev)
         if trainable:
             self.master = torch.zeros(off, dtype=torch.float32, device=dev)
             self.exp_avg = torch.zeros(off, dtype=torch.float32, device=dev)
@@ -143,7 +149,10 @@ class ZeroShardedParams:
                 dist.all_gather_into_tensor(full, src, group=self.group)
             u.full = full
         if for_backward and self.trainable and u.full_grad is None:
-            u.full_grad = torch.zeros(u.padded, dtype=torch.float32, device=self.device)
+            if self.comm is not None:
+                u.full_grad = self.comm.grad_buffer(u.padded)
+            else:
+                u.full_grad = torch.zeros(u.padded, dtype=torch.float32, device=self.device)
         self._bind(u, u.full, u.full_grad if for_backward else None)
 
     def release(self, u: ZeroUnit):
@@ -261,7 +270,7 @@ class ZeroShardedParams:
             h.copy_(t, non_blocking=True)
             return h
 
-        if params and self.world > 1:
+        if params and self.world > 1 and self.comm is None:
             self.shard16 = to_host(self.shard16)
         if optimizer and self.trainable:
             self.master, self.exp_avg, self.exp_avg_sq = map(to_host, (self.master, self.exp_avg, self.exp_avg_sq))

@@ -187,28 +187,16 @@ class ActorRolloutRefWorker(_WorkerBase):
             self.rollout_engine.sleep()
 
     def _bind_rollout_to_flat(self):
-        """Rollout parameters become views into per-unit flat buffers laid out exactly like the trainer's
-        gathered units, so a weight sync is one all-gather per unit straight into the rollout weights."""
-        z = self.actor_engine.zero
-        own = dict(self.rollout_model.named_parameters())
-        self._rollout_flat = []
-        for u in z.units:
-            buf = torch.zeros(u.padded, dtype=z.work_dtype, device=self.device)
-            self._rollout_flat.append(buf)
-            for name, shape, n, o in zip(u.names, u.shapes, u.numels, u.offsets):
-                if name in own:
-                    own[name].data = buf[o : o + n].view(shape)
+        """Rollout parameters become views into one destination buffer; a weight sync executes a precomputed
+        copy table (trainer shards on all ranks -> this rank's rollout layout) in a single kernel launch."""
+        from ..parallel.reshard import RolloutWeights
+
+        self._rollout_flat = RolloutWeights(self.model_config, self.actor_engine.zero, self.rollout_model)
         self._sync_rollout_weights()
 
     @torch.no_grad()
     def _sync_rollout_weights(self):
-        z = self.actor_engine.zero
-        for u, buf in zip(z.units, self._rollout_flat):
-            src = z.shard16[u.offset : u.offset + u.shard]
-            if z.comm is not None:
-                z.comm.all_gather(buf, src)
-            else:
-                dist.all_gather_into_tensor(buf, src, group=z.group)
+        self._rollout_flat.sync()
 
     # ---------------------------------------------------------------- rollout
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("rollout"))
