@@ -125,7 +125,7 @@ def test_rmsnorm_forward_backward():
     dy, dh = torch.randn_like(y), torch.randn_like(h)
     torch.autograd.backward([y, h], [dy, dh])
     xr, rr, wr = (t.detach().float().requires_grad_(True) for t in (x, res, w))
-    hr = (xr + rr).bfloat16().float() + ((xr + rr) - (xr + rr).detach())  # same rounding, full gradient
+    hr = (xr + rr) + ((xr + rr).bfloat16().float() - (xr + rr)).detach()  # bf16-rounded value, identity gradient
     yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
     torch.autograd.backward([yr, hr], [dy.float(), dh.float()])
     _bf16_close(y, yr)

@@ -49,6 +49,13 @@ int vb_make_tmap_2d(CUtensorMap* out, const void* ptr, int elem_bytes, uint64_t 
                                                            : CU_TENSOR_MAP_SWIZZLE_NONE;
   CUresult r = fn(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT || r == CUDA_ERROR_NOT_INITIALIZED) {
+    // a thread that has made no runtime call yet (e.g. an autograd worker) has no current context:
+    // binding the primary context of the current device is enough
+    cudaFree(0);
+    r = fn(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   return r == CUDA_SUCCESS ? 0 : -(100 + (int)r);
 }
 

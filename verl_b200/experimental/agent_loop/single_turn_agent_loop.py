@@ -1,0 +1,28 @@
+"""Single-turn agent loop: one prompt, one completion (verl/experimental/agent_loop/single_turn_agent_loop.py)."""
+
+from __future__ import annotations
+
+import time
+from typing import Any
+from uuid import uuid4
+
+from .agent_loop import AgentLoopBase, AgentLoopMetrics, AgentLoopOutput, register
+
+
+@register("single_turn_agent")
+class SingleTurnAgentLoop(AgentLoopBase):
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        rc = self.config.actor_rollout_ref.rollout
+        self.prompt_length, self.response_length = int(rc.prompt_length), int(rc.response_length)
+
+    async def run(self, sampling_params: dict[str, Any], **kwargs) -> AgentLoopOutput:
+        prompt_ids = await self.apply_chat_template(kwargs["raw_prompt"])
+        t0 = time.perf_counter()
+        out = await self.server_manager.generate(uuid4().hex, prompt_ids=prompt_ids, sampling_params=sampling_params)
+        dt = time.perf_counter() - t0
+        ids = out.token_ids[: self.response_length]
+        return AgentLoopOutput(prompt_ids=prompt_ids, response_ids=ids, response_mask=[1] * len(ids),
+                               response_logprobs=out.log_probs[: self.response_length] if out.log_probs else None,
+                               routed_experts=out.routed_experts, num_turns=2,
+                               metrics=AgentLoopMetrics(generate_sequences=dt, num_preempted=out.num_preempted))

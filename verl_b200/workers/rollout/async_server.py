@@ -1,0 +1,216 @@
+"""Asynchronous token-in / token-out server around the native rollout engine.
+
+Contract of the reference's ``vLLMHttpServer`` (verl/workers/rollout/vllm_rollout/vllm_async_server.py:445-682):
+``generate(prompt_ids, sampling_params, request_id) -> TokenOutput`` as a coroutine, ``wake_up / sleep``,
+``clear_kv_cache``, ``wait_for_requests_to_drain``, ``abort_all_requests`` (aborted requests still deliver their
+partial output with ``stop_reason="aborted"``), ``abort_request``, ``start_profile / stop_profile``.
+
+The engine steps in a dedicated thread; coroutines wait on futures that the step loop resolves. An optional
+FastAPI app exposes ``/generate``, ``/health`` and an OpenAI-style ``/v1/completions`` for token ids.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import threading
+import time
+import uuid
+from concurrent.futures import Future
+from typing import Any, Optional
+
+from ...rollout import NativeRolloutEngine, SamplingParams, TokenOutput
+
+
+class NativeAsyncServer:
+    def __init__(self, engine: NativeRolloutEngine, response_length: int = 512, prompt_length: int = 512):
+        self.engine = engine
+        self.response_length, self.prompt_length = response_length, prompt_length
+        self._lock = threading.Lock()
+        self._pending: dict[str, Future] = {}
+        self._inbox: list = []
+        self._aborts: list[str] = []
+        self._wake = threading.Event()
+        self._stop = False
+        self._paused = False
+        self._idle = threading.Event()
+        self._idle.set()
+        self._thread = threading.Thread(target=self._loop, daemon=True, name="rollout-engine")
+        self._thread.start()
+
+    # ------------------------------------------------------------ engine thread
+    def _loop(self):
+        eng = self.engine
+        while not self._stop:
+            with self._lock:
+                inbox, self._inbox = self._inbox, []
+                aborts, self._aborts = self._aborts, []
+            for rid, prompt, sp in inbox:
+                try:
+                    eng.add_request(rid, prompt, sp)
+                except Exception as e:
+                    fut = self._pending.pop(rid, None)
+                    if fut is not None:
+                        fut.set_exception(e)
+            for rid in aborts:
+                out = eng.abort_request(rid)
+                fut = self._pending.pop(rid, None)
+                if fut is not None and out is not None:
+                    fut.set_result(out)
+            if self._paused or not eng.has_unfinished():
+                self._idle.set()
+                self._wake.wait(timeout=0.05)
+                self._wake.clear()
+                continue
+            self._idle.clear()
+            try:
+                outs = eng.step()
+            except Exception as e:  # fail every waiter rather than hang them
+                with self._lock:
+                    pend, self._pending = self._pending, {}
+                for fut in pend.values():
+                    if not fut.done():
+                        fut.set_exception(e)
+                eng.abort_all_requests()
+                continue
+            for o in outs:
+                fut = self._pending.pop(o.request_id, None)
+                if fut is not None and not fut.done():
+                    fut.set_result(o)
+
+    # ------------------------------------------------------------------ public
+    def submit(self, prompt_ids: list[int], sampling_params: Optional[dict] = None, request_id: Optional[str] = None) -> Future:
+        sp = dict(sampling_params or {})
+        if "max_tokens" not in sp and "max_new_tokens" not in sp:
+            sp["max_tokens"] = self.response_length + self.prompt_length - len(prompt_ids)
+        max_new = sp.get("max_tokens", sp.get("max_new_tokens"))
+        sp["max_tokens"] = max(0, min(int(max_new), self.engine.max_model_len - len(prompt_ids)))
+        sp.pop("max_new_tokens", None)
+        rid = request_id or uuid.uuid4().hex
+        fut: Future = Future()
+        with self._lock:
+            self._pending[rid] = fut
+            self._inbox.append((rid, list(prompt_ids), SamplingParams.from_dict(sp)))
+        self._wake.set()
+        return fut
+
+    async def generate(self, prompt_ids: list[int], sampling_params: Optional[dict] = None, request_id: Optional[str] = None,
+                       image_data=None, video_data=None, priority: int = 0) -> TokenOutput:
+        fut = self.submit(prompt_ids, sampling_params, request_id)
+        return await asyncio.wrap_future(fut)
+
+    async def abort_request(self, request_id: str, reset_prefix_cache: bool = False) -> dict[str, Any]:
+        known = request_id in self._pending
+        with self._lock:
+            self._aborts.append(request_id)
+        self._wake.set()
+        return {"aborted": known, "request_id": request_id}
+
+    async def abort_all_requests(self, reset_prefix_cache: bool = True) -> dict[str, Any]:
+        with self._lock:
+            ids = list(self._pending.keys())
+            self._aborts.extend(ids)
+        self._wake.set()
+        await self.wait_for_requests_to_drain()
+        if reset_prefix_cache:
+            self.engine.clear_kv_cache()
+        return {"aborted_count": len(ids), "request_ids": ids}
+
+    async def wait_for_requests_to_drain(self, timeout: float = 600.0):
+        t0 = time.monotonic()
+        while (self._pending or self._inbox) and time.monotonic() - t0 < timeout:
+            await asyncio.sleep(0.005)
+
+    async def resume_all_requests(self):
+        self._paused = False
+        self._wake.set()
+
+    async def pause(self):
+        self._paused = True
+
+    async def wake_up(self, tags: Optional[list[str]] = None):
+        self.engine.wake_up(tags)
+
+    async def sleep(self):
+        await self.wait_for_requests_to_drain()
+        self._idle.wait(5.0)
+        self.engine.sleep()
+
+    async def clear_kv_cache(self):
+        self.engine.clear_kv_cache()
+
+    async def start_profile(self, **kwargs):
+        import torch
+
+        if torch.cuda.is_available():
+            torch.cuda.profiler.start()
+
+    async def stop_profile(self):
+        import torch
+
+        if torch.cuda.is_available():
+            torch.cuda.profiler.stop()
+
+    def shutdown(self):
+        self._stop = True
+        self._wake.set()
+        self._thread.join(2.0)
+
+    # ------------------------------------------------------------------- HTTP
+    def build_app(self):
+        """FastAPI app with token-level endpoints (served with uvicorn by :func:`run_unvicorn`)."""
+        from fastapi import FastAPI
+
+        app = FastAPI()
+        server = self
+
+        @app.get("/health")
+        async def health():
+            return {"status": "ok", **server.engine.sched.stats()} if server.engine.sched else {"status": "sleeping"}
+
+        @app.post("/generate")
+        async def generate(body: dict):
+            out = await server.generate(body["prompt_ids"], body.get("sampling_params"), body.get("request_id"))
+            return {"token_ids": out.token_ids, "log_probs": out.log_probs, "stop_reason": out.stop_reason,
+                    "num_preempted": out.num_preempted}
+
+        @app.post("/v1/completions")
+        async def completions(body: dict):
+            prompt = body["prompt"]
+            assert isinstance(prompt, list), "prompt must be a list of token ids"
+            sp = {"temperature": body.get("temperature", 1.0), "top_p": body.get("top_p", 1.0),
+                  "max_tokens": body.get("max_tokens", 16), "logprobs": bool(body.get("logprobs"))}
+            out = await server.generate(prompt, sp)
+            return {"id": f"cmpl-{uuid.uuid4().hex}", "object": "text_completion",
+                    "choices": [{"index": 0, "token_ids": out.token_ids, "logprobs": out.log_probs,
+                                 "finish_reason": "stop" if out.stop_reason == "completed" else "length"}]}
+
+        @app.post("/abort_request")
+        async def abort(body: dict):
+            return await server.abort_request(body["request_id"])
+
+        return app
+
+
+async def run_unvicorn(app, server_args=None, server_address: str = "127.0.0.1", max_retries: int = 5):
+    """Start uvicorn on a free port, retrying on clashes (verl/workers/rollout/utils.py:38-58). Returns (port, task)."""
+    import socket
+
+    import uvicorn
+
+    last = None
+    for _ in range(max_retries):
+        with socket.socket() as s:
+            s.bind((server_address, 0))
+            port = s.getsockname()[1]
+        try:
+            cfg = uvicorn.Config(app, host=server_address, port=port, log_level="warning")
+            srv = uvicorn.Server(cfg)
+            task = asyncio.create_task(srv.serve())
+            for _ in range(100):
+                if srv.started:
+                    return port, task
+                await asyncio.sleep(0.05)
+            return port, task
+        except OSError as e:
+            last = e
+    raise RuntimeError(f"could not start the HTTP server: {last}")
