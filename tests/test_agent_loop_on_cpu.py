@@ -1,0 +1,149 @@
+"""Async server, abort semantics and agent loops (single turn + tool calling) against the native engine on CPU."""
+import asyncio
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from verl_b200 import DataProto
+from verl_b200.experimental.agent_loop import AgentLoopManager, AsyncLLMServerManager
+from verl_b200.experimental.agent_loop.tool_parser import HermesToolParser
+from verl_b200.models import build_model, preset
+from verl_b200.rollout import NativeRolloutEngine
+from verl_b200.utils.config import compose
+from verl_b200.utils.tokenizer import IntTokenizer
+from verl_b200.workers.rollout.async_server import NativeAsyncServer
+
+
+@pytest.fixture(scope="module")
+def server():
+    torch.manual_seed(0)
+    m = build_model(preset("tiny-qwen2"), dtype=torch.float32)
+    eng = NativeRolloutEngine(m, max_num_seqs=8, max_model_len=160, max_num_batched_tokens=128, num_blocks=96)
+    s = NativeAsyncServer(eng, response_length=32, prompt_length=64)
+    yield s
+    s.shutdown()
+
+
+def _cfg(extra=()):
+    return compose("ppo_trainer", ["actor_rollout_ref.model.path=preset:tiny-qwen2", "data.max_prompt_length=64",
+                                   "data.max_response_length=32", "actor_rollout_ref.rollout.agent.num_workers=2"] + list(extra))
+
+
+def test_generate_and_abort(server):
+    async def go():
+        fut = [server.generate(list(range(10, 30)), {"temperature": 0.0, "max_tokens": 8}) for _ in range(3)]
+        outs = await asyncio.gather(*fut)
+        assert all(len(o.token_ids) == 8 and o.stop_reason in ("length", "completed") for o in outs)
+        assert outs[0].token_ids == outs[1].token_ids  # greedy
+        long = asyncio.ensure_future(server.generate(list(range(10, 40)), {"temperature": 1.0, "max_tokens": 100}, request_id="victim"))
+        await asyncio.sleep(0.05)
+        res = await server.abort_all_requests()
+        out = await long
+        assert out.stop_reason == "aborted" and len(out.token_ids) < 100 and "victim" in res["request_ids"]
+
+    asyncio.run(go())
+
+
+def test_load_balancer_is_sticky_and_least_loaded():
+    class H:
+        def __init__(self, i):
+            self.i, self.calls = i, 0
+
+        async def generate(self, **kw):
+            self.calls += 1
+            return self.i
+
+    hs = [H(i) for i in range(3)]
+    mgr = AsyncLLMServerManager(None, hs)
+
+    async def go():
+        first = await mgr.generate("conv", prompt_ids=[1], sampling_params={})
+        again = await mgr.generate("conv", prompt_ids=[1, 2], sampling_params={})
+        assert first == again
+        for k in range(6):
+            await mgr.generate(f"r{k}", prompt_ids=[1], sampling_params={})
+        # 7 distinct conversations over 3 servers: assignments differ by at most one (the sticky call adds one more)
+        assert sum(h.calls for h in hs) == 8 and min(h.calls for h in hs) >= 2
+
+    asyncio.run(go())
+
+
+def test_single_turn_agent_loop_batch(server):
+    cfg = _cfg()
+    tok = IntTokenizer(2048)
+    mgr = AgentLoopManager(cfg, server_handles=[server], tokenizer=tok)
+    prompts = np.empty(5, dtype=object)
+    prompts[:] = [list(range(20, 20 + n)) for n in (12, 30, 7, 18, 25)]
+    batch = DataProto.from_dict(tensors={"dummy": torch.zeros(5)}, non_tensors={"raw_prompt": prompts})
+    out = mgr.generate_sequences(batch)
+    assert out.batch["prompts"].shape == (5, 64) and out.batch["responses"].shape == (5, 32)
+    assert out.batch["input_ids"].shape == (5, 96)
+    assert (out.batch["attention_mask"][:, :64].sum(-1) == torch.tensor([12, 30, 7, 18, 25])).all()
+    assert (out.batch["prompts"][1, -30:] == torch.arange(20, 50)).all()
+    assert "rollout_log_probs" in out.batch.keys() and "agent_loop/generate_sequences/mean" in out.meta_info["timing"]
+    assert (out.non_tensor_batch["__num_turns__"] == 2).all()
+
+
+class _Tok(IntTokenizer):
+    """Integer tokenizer whose decode can be made to contain a tool call."""
+
+    def decode(self, ids, skip_special_tokens=True):
+        ids = [int(t) for t in ids]
+        if getattr(self, "emit_call", 0) > 0 and ids:
+            self.emit_call -= 1
+            return '<tool_call>{"name": "echo", "arguments": {"text": "hi"}}</tool_call>'
+        return super().decode(ids, skip_special_tokens)
+
+
+def test_tool_agent_loop_masks_tool_tokens(server, tmp_path):
+    tools_yaml = tmp_path / "tools.yaml"
+    tools_yaml.write_text(json.dumps({"tools": [{
+        "class_name": "tests_tool_helpers.EchoTool", "config": {"type": "native"},
+        "tool_schema": {"type": "function", "function": {"name": "echo", "description": "echo",
+                                                         "parameters": {"type": "object", "properties": {"text": {"type": "string"}}, "required": ["text"]}}}}]}))
+    import sys
+    import types
+
+    from verl_b200.tools import BaseTool, ToolResponse
+
+    mod = types.ModuleType("tests_tool_helpers")
+
+    class EchoTool(BaseTool):
+        async def execute(self, instance_id, parameters, **kw):
+            return ToolResponse(text="7 8 9"), 0.5, {}
+
+    mod.EchoTool = EchoTool
+    sys.modules["tests_tool_helpers"] = mod
+    cfg = _cfg([f"actor_rollout_ref.rollout.multi_turn.tool_config_path={tools_yaml}",
+                "actor_rollout_ref.rollout.multi_turn.max_assistant_turns=3",
+                "actor_rollout_ref.rollout.agent.default_agent_loop=tool_agent", "actor_rollout_ref.rollout.agent.num_workers=1"])
+    tok = _Tok(2048)
+    tok.emit_call = 1
+    mgr = AgentLoopManager(cfg, server_handles=[server], tokenizer=tok)
+    prompts = np.empty(1, dtype=object)
+    prompts[:] = [[{"role": "user", "content": "30 31 32 33"}]]
+    batch = DataProto.from_dict(tensors={"dummy": torch.zeros(1)}, non_tensors={"raw_prompt": prompts})
+    # make the first assistant turn one token long: greedy decoding, and that token is declared EOS
+    first = asyncio.run(server.generate([30, 31, 32, 33], {"temperature": 0.0, "max_tokens": 1})).token_ids[0]
+    old_eos, server.engine.eos = server.engine.eos, first
+    batch.meta_info["validate"] = True
+    try:
+        out = mgr.generate_sequences(batch)
+    finally:
+        server.engine.eos = old_eos
+    rm, am = out.batch["response_mask"][0], out.batch["attention_mask"][0, 64:]
+    assert am.sum() > rm.sum() > 0  # some response tokens are tool tokens (mask 0)
+    assert int(out.non_tensor_batch["__num_turns__"][0]) >= 3
+    assert out.non_tensor_batch["tool_rewards"][0] == [0.5]
+
+
+def test_hermes_parser():
+    class T:
+        def decode(self, ids, **kw):
+            return 'think <tool_call>{"name": "f", "arguments": {"a": 1}}</tool_call> and <tool_call>not json</tool_call>'
+
+    text, calls = asyncio.run(HermesToolParser(T()).extract_tool_calls([1]))
+    assert len(calls) == 1 and calls[0].name == "f" and json.loads(calls[0].arguments) == {"a": 1}
+    assert "<tool_call>" not in text
