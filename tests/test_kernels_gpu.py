@@ -59,6 +59,29 @@ def test_gemm_fp32_accumulate_and_bias():
     _bf16_close(gemm(A, B, bias=bias), A.float() @ B.float().t() + bias.float())
 
 
+@pytest.mark.parametrize("M,N,K,mode", [(128, 3584, 18944, "tn"), (64, 4608, 3584, "tn"), (7, 520, 2048, "tn"),
+                                        (128, 1024, 4096, "nn"), (200, 640, 8192, "tn")])
+def test_gemm_split_k(M, N, K, mode):
+    """Skinny problems take the split-K path (fp32 slices + last-arriver reduction): same numbers as the
+    fp32 reference, bit-identical between calls, bias / accumulate handled by the reducing CTA."""
+    from verl_b200.ops import gemm, _lib
+
+    torch.manual_seed(3)
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    Bm = B.t().contiguous() if mode == "nn" else B
+    o1 = gemm(A, Bm, b_mn=(mode == "nn"), bias=bias)
+    o2 = gemm(A, Bm, b_mn=(mode == "nn"), bias=bias)
+    assert _lib.read_status("cuda")[0] == 0
+    _bf16_close(o1, ref + bias.float())
+    assert torch.equal(o1, o2)
+    C = torch.full((M, N), 2.0, device="cuda")
+    gemm(A, Bm, b_mn=(mode == "nn"), out=C, accumulate=True)
+    torch.testing.assert_close(C, ref + 2.0, atol=2e-2, rtol=1e-4)
+
+
 def test_gemm_deterministic():
     from verl_b200.ops import gemm
 
@@ -293,7 +316,8 @@ def test_sampler_distribution_and_modes():
 
 
 @pytest.mark.parametrize("B,Hq,Hk,D,bs,maxlen", [(5, 28, 4, 128, 16, 700), (3, 4, 2, 64, 16, 300), (2, 32, 4, 128, 32, 3000),
-                                                 (4, 40, 8, 128, 16, 150)])
+                                                 (4, 40, 8, 128, 16, 150), (3, 32, 2, 128, 128, 1000),
+                                                 (2, 8, 8, 128, 8, 260)])
 def test_paged_decode_attention(B, Hq, Hk, D, bs, maxlen):
     from verl_b200 import ops
 
@@ -315,6 +339,14 @@ def test_paged_decode_attention(B, Hq, Hk, D, bs, maxlen):
         ops.kv_cache_write(k_new, v_new, slots, kc, vc)
     q = torch.randn(B, Hq, D, device="cuda").bfloat16()
     ref = ops.paged_decode_attention(q.cpu().float(), kc.cpu().float(), vc.cpu().float(), table.cpu(), lens)
-    for splits in (1, ops.decode_workspace(B, Hq, Hk, D, maxlen, "cuda")[0]):
-        out = ops.paged_decode_attention(q, kc, vc, table, lens.cuda(), num_splits=splits)
-        _bf16_close(out, ref, ulps=4)
+    from verl_b200.ops import _lib
+
+    impls = ["simt"] if Hq // Hk <= 8 else []
+    if _lib.fn("vb_paged_decode_tc_supported")(Hq, Hk, D, bs):
+        impls.append("tc")
+    assert impls
+    for impl in impls:
+        for splits in sorted({1, 3, ops.decode_workspace(B, Hq, Hk, D, maxlen, "cuda")[0]}):
+            out = ops.paged_decode_attention(q, kc, vc, table, lens.cuda(), num_splits=splits, impl=impl)
+            assert _lib.read_status("cuda")[0] == 0
+            _bf16_close(out, ref, ulps=4)

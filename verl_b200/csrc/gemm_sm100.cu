@@ -49,6 +49,12 @@ struct GemmParams {
   const float* g_logprob;   // DLOGITS: [M] dL/dlogprob
   const float* g_entropy;   // DLOGITS: [M] dL/dentropy (may be null)
   int n_offset;             // DLOGITS: vocab offset of this chunk (for label compare)
+  // EPI_STORE split-K (k_splits > 1): every (tile, k slice) unit writes an fp32 partial tile to ws, the unit
+  // that arrives last at the tile's ticket counter sums the slices in slice order and writes C
+  int k_splits;
+  int kb_per_split;
+  float* ws;        // [k_splits, num_m * BM, num_n * BN] fp32
+  int* counters;    // one per tile, zero before the launch and zero again after it
   int* status;
 };
 
@@ -66,11 +72,14 @@ struct SmemLayout {
 
 // Map a linear work index to (m block, first n block, number of n blocks).
 struct Sched {
-  int num_m, num_n, num_units, nblk_per_split, num_splits;
+  int num_m, num_n, num_units, nblk_per_split, num_splits, k_splits, kb_per_split, num_kb;
   bool lse;
   __device__ Sched(const GemmParams& p, int BN, bool lse_) : lse(lse_) {
     num_m = (p.M + BM - 1) / BM;
     num_n = (p.N + BN - 1) / BN;
+    num_kb = (p.K + BK - 1) / BK;
+    k_splits = (!lse_ && p.k_splits > 1) ? p.k_splits : 1;
+    kb_per_split = k_splits > 1 ? p.kb_per_split : num_kb;
     if (lse) {
       nblk_per_split = p.nblk_per_split;
       num_splits = p.num_splits;
@@ -78,10 +87,17 @@ struct Sched {
     } else {
       nblk_per_split = 1;
       num_splits = num_n;
-      num_units = num_m * num_n;
+      num_units = num_m * num_n * k_splits;
     }
   }
+  // k-block range [kb0, kb1) and k slice of unit u (the k slice is the fastest-varying part of u)
+  __device__ void k_range(int u, int& ks, int& kb0, int& kb1) const {
+    ks = u % k_splits;
+    kb0 = ks * kb_per_split;
+    kb1 = min(num_kb, kb0 + kb_per_split);
+  }
   __device__ void get(int u, int& m_blk, int& n_first, int& n_count, int& split) const {
+    u /= k_splits;
     const int per_group = GROUP_M * num_splits;
     const int g = u / per_group;
     const int first_m = g * GROUP_M;
@@ -93,6 +109,57 @@ struct Sched {
     n_count = min(nblk_per_split, num_n - n_first);
   }
 };
+
+// Final store of 32 consecutive columns of one output row (bias, fp32 accumulate or bf16 pack).
+__device__ __forceinline__ void epi_store_chunk(const GemmParams& p, int row, int col0, uint32_t (&r)[32]) {
+                if (p.bias != nullptr) {
+  #pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    if (col0 + i < p.N) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[col0 + i]));
+                  }
+                }
+                if (p.out_fp32) {
+                  float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+                  if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
+  #pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                      float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                             __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                      if (p.accumulate) {
+                        float4 o = reinterpret_cast<float4*>(dst)[i];
+                        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                      }
+                      reinterpret_cast<float4*>(dst)[i] = v;
+                    }
+                  } else {
+  #pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                      if (col0 + i < p.N) {
+                        float v = __uint_as_float(r[i]);
+                        if (p.accumulate) v += dst[i];
+                        dst[i] = v;
+                      }
+                    }
+                  }
+                } else {
+                  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+                  if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
+  #pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                      uint4 v;
+                      v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+                      v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                      v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                      v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                      reinterpret_cast<uint4*>(dst)[i] = v;
+                    }
+                  } else {
+  #pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                      if (col0 + i < p.N) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
+                  }
+                }
+}
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -108,11 +175,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* ticket_s = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const Sched sched(p, BN, EPI == EPI_LSE);
-  const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; ++s) {
@@ -146,8 +213,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int u = blockIdx.x; ok && u < sched.num_units; u += gridDim.x) {
         int m_blk, n_first, n_count, split;
         sched.get(u, m_blk, n_first, n_count, split);
+        int ks, kb0, kb1;
+        sched.k_range(u, ks, kb0, kb1);
         for (int nb = n_first; ok && nb < n_first + n_count; ++nb) {
-          for (int kb = 0; kb < num_kb; ++kb) {
+          for (int kb = kb0; kb < kb1; ++kb) {
             if (*abort_flag || !mbar_wait(&empty[s], phase ^ 1)) {
               report_error(p.status, ERR_WAIT_EMPTY, kb);
               *abort_flag = 1;
@@ -191,6 +260,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int u = blockIdx.x; ok && u < sched.num_units; u += gridDim.x) {
         int m_blk, n_first, n_count, split;
         sched.get(u, m_blk, n_first, n_count, split);
+        int ks, kb0, kb1;
+        sched.k_range(u, ks, kb0, kb1);
         for (int nb = n_first; ok && nb < n_first + n_count; ++nb) {
           if (*abort_flag || !mbar_wait(&tempty[acc], acc_phase ^ 1)) {
             report_error(p.status, ERR_WAIT_TMEM_EMPTY, nb);
@@ -200,7 +271,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * BN;
-          for (int kb = 0; kb < num_kb; ++kb) {
+          for (int kb = kb0; kb < kb1; ++kb) {
             if (*abort_flag || !mbar_wait(&full[s], phase)) {
               report_error(p.status, ERR_WAIT_FULL, kb);
               *abort_flag = 1;
@@ -216,7 +287,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                            : umma_smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
               const uint64_t b_desc = B_MN ? umma_smem_desc(b_addr + k * (UMMA_K * 128), BK * 128, 1024)
                                            : umma_smem_desc(b_addr + k * (UMMA_K * 2), 16, 1024);
-              tc_mma_f16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+              tc_mma_f16(d_tmem, a_desc, b_desc, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
             }
             tc_commit(&empty[s]);  // frees the stage once these MMAs have read it
             if (++s == L::STAGES) {
@@ -243,6 +314,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     for (int u = blockIdx.x; ok && u < sched.num_units; u += gridDim.x) {
       int m_blk, n_first, n_count, split;
       sched.get(u, m_blk, n_first, n_count, split);
+      int ks, kb0, kb1;
+      sched.k_range(u, ks, kb0, kb1);
       const int row = m_blk * BM + row_in_tile;
       const bool row_ok = row < p.M;
 
@@ -278,54 +351,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           tmem_ld_wait();
           const int col0 = nb * BN + c * 32;
           if (EPI == EPI_STORE) {
-            if (row_ok && col0 < p.N) {
-              if (p.bias != nullptr) {
+            if (sched.k_splits > 1) {
+              // fp32 partial tile (the workspace is padded to whole tiles: no bounds checks)
+              float4* dst = reinterpret_cast<float4*>(p.ws + ((long long)ks * sched.num_m * BM + row) * ((long long)sched.num_n * BN) + col0);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                  if (col0 + i < p.N) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[col0 + i]));
-                }
-              }
-              if (p.out_fp32) {
-                float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
-                if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                           __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-                    if (p.accumulate) {
-                      float4 o = reinterpret_cast<float4*>(dst)[i];
-                      v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                    }
-                    reinterpret_cast<float4*>(dst)[i] = v;
-                  }
-                } else {
-#pragma unroll
-                  for (int i = 0; i < 32; ++i) {
-                    if (col0 + i < p.N) {
-                      float v = __uint_as_float(r[i]);
-                      if (p.accumulate) v += dst[i];
-                      dst[i] = v;
-                    }
-                  }
-                }
-              } else {
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
-                if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    uint4 v;
-                    v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
-                    v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-                    v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-                    v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-                    reinterpret_cast<uint4*>(dst)[i] = v;
-                  }
-                } else {
-#pragma unroll
-                  for (int i = 0; i < 32; ++i)
-                    if (col0 + i < p.N) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
-                }
-              }
+              for (int i = 0; i < 8; ++i)
+                __stcg(dst + i, make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                            __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])));
+            } else if (row_ok && col0 < p.N) {
+              epi_store_chunk(p, row, col0, r);
             }
           } else if (EPI == EPI_LSE) {
             if (col0 < p.N) {
@@ -390,6 +424,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           acc_phase ^= 1;
         }
       }
+      if (EPI == EPI_STORE) {
+        if (sched.k_splits > 1) {
+          // ticket: the unit that arrives last at this tile reduces the slices (fixed order: deterministic)
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int tile = m_blk * sched.num_n + n_first;
+          if (threadIdx.x == 64) *ticket_s = atomicAdd(&p.counters[tile], 1);
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const bool last = ok && (*ticket_s == sched.k_splits - 1);
+          asm volatile("bar.sync 1, 128;" ::: "memory");  // ticket_s read by all before the next unit writes it
+          if (last) {
+            __threadfence();
+            const long long ldw = (long long)sched.num_n * BN;
+            const long long slice = (long long)sched.num_m * BM * ldw;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              const int col0 = n_first * BN + c * 32;
+              if (!row_ok || col0 >= p.N) continue;
+              const float4* src = reinterpret_cast<const float4*>(p.ws + (long long)row * ldw + col0);
+              uint32_t r[32];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 v = __ldcg(src + i);
+                r[4 * i] = __float_as_uint(v.x); r[4 * i + 1] = __float_as_uint(v.y);
+                r[4 * i + 2] = __float_as_uint(v.z); r[4 * i + 3] = __float_as_uint(v.w);
+              }
+              for (int sp = 1; sp < sched.k_splits; ++sp) {
+                const float4* s2 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + sp * slice);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float4 v = __ldcg(s2 + i);
+                  r[4 * i] = __float_as_uint(__uint_as_float(r[4 * i]) + v.x);
+                  r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) + v.y);
+                  r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) + v.z);
+                  r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) + v.w);
+                }
+              }
+              epi_store_chunk(p, row, col0, r);
+            }
+            if (threadIdx.x == 64) p.counters[tile] = 0;
+          }
+        }
+      }
       if (EPI == EPI_LSE) {
         if (ok && row_ok) {
           float4 out = make_float4(run_max, run_sum, run_dot, label_logit);
@@ -452,7 +529,7 @@ static int launch_gemm(const void* A, const void* B, long long lda, long long ld
   }
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int units = (EPI == EPI_LSE) ? num_m * p.num_splits : num_m * num_n;
+  const int units = (EPI == EPI_LSE) ? num_m * p.num_splits : num_m * num_n * (p.k_splits > 1 ? p.k_splits : 1);
   if (units <= 0) return 0;
   const int grid = units < vb_num_sms() ? units : vb_num_sms();
   kern<<<grid, NUM_THREADS, L::DYN_BYTES, stream>>>(tmA, tmB, p);
@@ -469,15 +546,46 @@ using namespace vb;
 //   b_mn = 0: B is [N,K] row-major;                         b_mn = 1: B is stored [K,N] row-major.
 //   out_fp32 = 0: C bf16; 1: C fp32, and accumulate != 0 adds into C.
 // Requirements: lda, ldb multiples of 8; pointers 16-byte aligned.
-extern "C" int vb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
-                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32,
-                            int accumulate, int* status, cudaStream_t stream) {
+//
+// ws / counters (optional): fp32 workspace of ws_bytes and num_counters zeroed ints that enable split-K for
+// problems with too few output tiles to occupy the GPU (decode-time projections: M <= 128, large K). Calls
+// that share a workspace must be ordered on one stream. The counters are left at zero.
+extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                               long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32,
+                               int accumulate, float* ws, long long ws_bytes, int* counters, int num_counters,
+                               int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7)) return -3;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.out_fp32 = out_fp32; p.accumulate = accumulate; p.status = status;
+  p.k_splits = 1;
+  if (ws != nullptr && counters != nullptr) {
+    // split-K on 128-wide tiles when even those leave most SMs idle and K is deep enough to cut
+    const int nm = (M + BM - 1) / BM, nn = (N + 127) / 128, nkb = (K + BK - 1) / BK;
+    const int tiles128 = nm * nn;
+    int splits = vb_num_sms() / (tiles128 > 0 ? tiles128 : 1);
+    if (splits > nkb / 4) splits = nkb / 4;
+    if (splits > 16) splits = 16;
+    if (N > 128 && splits >= 2 && tiles128 <= num_counters) {
+      const int per = (nkb + splits - 1) / splits;
+      splits = (nkb + per - 1) / per;
+      const long long need = (long long)splits * nm * BM * nn * 128 * 4;
+      if (splits >= 2 && need <= ws_bytes) {
+        p.k_splits = splits;
+        p.kb_per_split = per;
+        p.ws = ws;
+        p.counters = counters;
+#define VB_SPLITK(AMN, BMN) launch_gemm<128, AMN, BMN, EPI_STORE>(A, B, lda, ldb, p, stream)
+        if (!a_mn && !b_mn) return VB_SPLITK(false, false);
+        if (!a_mn && b_mn) return VB_SPLITK(false, true);
+        if (a_mn && b_mn) return VB_SPLITK(true, true);
+        return VB_SPLITK(true, false);
+#undef VB_SPLITK
+      }
+    }
+  }
   // Tile width: the widest BN that still yields about one tile per SM. Skinny problems (decode: M <= 128)
   // fall to BN = 64 / 32 so that the weight matrix is streamed by (nearly) all SMs.
   const int num_m = (M + BM - 1) / BM;
@@ -502,6 +610,13 @@ extern "C" int vb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   if (a_mn && b_mn) return VB_DISPATCH(true, true);
   return VB_DISPATCH(true, false);
 #undef VB_DISPATCH
+}
+
+extern "C" int vb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32,
+                            int accumulate, int* status, cudaStream_t stream) {
+  return vb_gemm_bf16_ws(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, nullptr, 0, nullptr,
+                         0, status, stream);
 }
 
 // Number of vocab splits the fused lm_head kernel uses for (T, V); the caller sizes

@@ -243,6 +243,14 @@ extern "C" int vb_decode_num_splits(int B, int Hk, int max_seq_len) {
   return s;
 }
 
+// Merge of the per-split partial results (head_dim 128), shared with the tensor-core decode kernel.
+int vb_decode_merge_128(const float* o_part, const float* ml_part, int B, int Hq, int num_splits, void* out,
+                        long long out_stride, cudaStream_t stream) {
+  decode_merge_kernel<128><<<dim3(B, Hq), 128, 0, stream>>>(o_part, ml_part, Hq, num_splits, (__nv_bfloat16*)out,
+                                                            out_stride);
+  return (int)cudaGetLastError();
+}
+
 // work: fp32 scratch of B * Hq * num_splits * (D + 2) floats (unused when num_splits == 1).
 extern "C" int vb_paged_decode(const void* q, long long q_stride, const void* kc, const void* vc,
                                const int* block_table, int max_blocks, const int* seq_lens, int B, int Hq, int Hk,

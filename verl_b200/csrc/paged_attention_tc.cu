@@ -1,0 +1,387 @@
+// Paged-KV decode attention on tcgen05 (head_dim 128, up to 16 query heads per KV head).
+//
+// One CTA per (sequence, KV head, split). Work is transposed so that all 128 epilogue threads are busy
+// although a decode step has only G = Hq/Hk query rows:
+//     S^T[keys x heads]  = K_chunk[128 keys x 128 dims] . Q^T          (M = 128 keys,  N = 16 heads, K = 128 dims)
+//     O^T[dims x heads] += V_chunk^T[128 dims x 128 keys] . P[keys x heads]  (M = 128 dims, N = 16 heads, K = 128 keys)
+// TMEM lane i of S^T is key i of the chunk, lane i of O^T is output dim i: every thread of warps 0..3 owns
+// one key during the softmax and one output dimension during accumulation (16 fp32 values each).
+//
+//   warps 0..3 : softmax over the chunk (max / sum across the 128 key-threads), write P^T (bf16) into shared
+//                memory in the 128-byte-swizzled K-major layout, then fold O^T of the chunk into the running
+//                output held in registers (flash-decoding rescale)
+//   warp 4     : TMA producer: the pages of a chunk are fetched with per-CTA 2-D tiled loads straight from
+//                the paged cache ([num_blocks, Hk, block_size, 128]) into a 3-stage ring (K and V, 64 KB / stage)
+//   warp 5     : TMEM allocation + single-thread tcgen05.mma issue
+//
+// V needs no transpose: [keys, dims] with dims contiguous is exactly an "MN-major" A operand.
+// All waits are bounded; on expiry the status word is set and the CTA leaves through its teardown.
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace vb {
+
+constexpr int TC_CHUNK = 128;   // keys per chunk
+constexpr int TC_D = 128;       // head dim
+constexpr int TC_NH = 16;       // padded number of query heads per KV head (UMMA N)
+constexpr int TC_STAGES = 3;
+constexpr int TC_THREADS = 192;
+constexpr int KV_TILE_BYTES = TC_CHUNK * TC_D * 2;        // 32 KB (two 64-wide halves of 16 KB)
+constexpr int STAGE_BYTES_TC = 2 * KV_TILE_BYTES;         // K + V
+constexpr int Q_BYTES = TC_NH * TC_D * 2;                 // 4 KB: two 64-dim k-blocks of 2 KB
+constexpr int P_BYTES = TC_NH * TC_CHUNK * 2;             // 4 KB: two 64-key k-blocks of 2 KB
+constexpr int TC_BAR_OFF = TC_STAGES * STAGE_BYTES_TC + Q_BYTES + 2 * P_BYTES;
+constexpr int TC_SMEM = TC_BAR_OFF + 16 * 8 + 64 + 1024;
+
+struct DecodeTcParams {
+  const __nv_bfloat16* q;
+  long long q_stride;
+  const int* block_table;
+  int max_blocks;
+  const int* seq_lens;
+  int Hq, Hk, block_size;
+  float scale;
+  int num_splits;
+  __nv_bfloat16* out;
+  long long out_stride;
+  float* o_part;
+  float* ml_part;
+  int* status;
+};
+
+// byte offset of element (row r, col k) inside a K-major, 128-byte-swizzled operand of `rows` rows whose
+// k extent is split in 64-element blocks of rows*128 bytes
+__device__ __forceinline__ uint32_t sw128_off(int r, int k, int rows) {
+  const int kb = k >> 6, c16 = (k & 63) >> 3;
+  return (uint32_t)(kb * rows * 128 + (r >> 3) * 1024 + (r & 7) * 128 + ((c16 ^ (r & 7)) << 4) + (k & 7) * 2);
+}
+
+__device__ __forceinline__ void bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// barrier over the 128 softmax threads that also and-reduces a predicate, so that all of them leave the
+// chunk loop in the same iteration
+__device__ __forceinline__ bool bar_and_128(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                       const DecodeTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage0 = smem;
+  uint8_t* q_s = smem + TC_STAGES * STAGE_BYTES_TC;
+  uint8_t* p_s = q_s + Q_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + TC_BAR_OFF);
+  uint64_t* empty = full + TC_STAGES;
+  uint64_t* s_full = empty + TC_STAGES;
+  uint64_t* p_ready = s_full + 2;
+  uint64_t* o_full = p_ready + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ float red_s[TC_NH][4];
+
+  const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+  const int G = p.Hq / p.Hk;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int seq_len = p.seq_lens[b];
+  const int chunks_total = (seq_len + TC_CHUNK - 1) / TC_CHUNK;
+  const int per_split = (chunks_total + p.num_splits - 1) / p.num_splits;
+  const int c_begin = split * per_split;
+  const int c_end = min(chunks_total, c_begin + per_split);
+  const int n_chunks = max(c_end - c_begin, 0);
+
+  if (tid == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_ready[i], 4);
+      mbar_init(&o_full[i], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  // Q^T operand: [16 heads x 128 dims], rows >= G are zero. P buffers start zeroed (rows >= G stay zero).
+  for (int i = tid; i < (Q_BYTES + 2 * P_BYTES) / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  for (int i = tid; i < G * TC_D; i += TC_THREADS) {
+    const int g = i / TC_D, d = i % TC_D;
+    const __nv_bfloat16 v = p.q[(long long)b * p.q_stride + (long long)(h * G + g) * TC_D + d];
+    *reinterpret_cast<__nv_bfloat16*>(q_s + sw128_off(g, d, TC_NH)) = v;
+  }
+  fence_proxy_async_smem();
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 64);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0 && n_chunks > 0) {
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      const int pages_per_chunk = TC_CHUNK / p.block_size;
+      const int* bt = p.block_table + (long long)b * p.max_blocks;
+      const int n_pages = (seq_len + p.block_size - 1) / p.block_size;
+      for (int c = 0; c < n_chunks; ++c) {
+        const int s = c % TC_STAGES;
+        const uint32_t par = ((c / TC_STAGES) & 1) ^ 1;
+        if (*abort_flag || !mbar_wait(&empty[s], par)) {
+          report_error(p.status, ERR_WAIT_EMPTY, c);
+          *abort_flag = 1;
+          break;
+        }
+        mbar_arrive_expect_tx(&full[s], STAGE_BYTES_TC);
+        uint8_t* k_dst = stage0 + s * STAGE_BYTES_TC;
+        uint8_t* v_dst = k_dst + KV_TILE_BYTES;
+        const int page0 = (c_begin + c) * pages_per_chunk;
+        for (int pg = 0; pg < pages_per_chunk; ++pg) {
+          // pages past the end of the sequence re-read the sequence's last page: finite data, masked later
+          const int pi = min(page0 + pg, n_pages - 1);
+          const int row = (bt[pi] * p.Hk + h) * p.block_size;
+          const int off = pg * p.block_size * 128;
+          tma_load_2d(k_dst + off, &tmK, &full[s], 0, row);
+          tma_load_2d(k_dst + 16384 + off, &tmK, &full[s], 64, row);
+          tma_load_2d(v_dst + off, &tmV, &full[s], 0, row);
+          tma_load_2d(v_dst + 16384 + off, &tmV, &full[s], 64, row);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // -------------------------------- MMA issuer --------------------------------
+    if (lane == 0 && n_chunks > 0) {
+      constexpr uint32_t idesc_qk = umma_idesc(1, 1, 0, 0, 128, TC_NH);  // A = K (K-major), B = Q^T (K-major)
+      constexpr uint32_t idesc_pv = umma_idesc(1, 1, 1, 0, 128, TC_NH);  // A = V (MN-major), B = P^T (K-major)
+      const uint32_t q_addr = smem_u32(q_s);
+      bool ok = true;
+      auto issue_qk = [&](int c) -> bool {
+        const int s = c % TC_STAGES;
+        if (*abort_flag || !mbar_wait(&full[s], (c / TC_STAGES) & 1)) {
+          report_error(p.status, ERR_WAIT_FULL, c);
+          *abort_flag = 1;
+          return false;
+        }
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(stage0 + s * STAGE_BYTES_TC);
+        const uint32_t d_tmem = tmem_base + (c & 1) * TC_NH;
+#pragma unroll
+        for (int k = 0; k < TC_D / 16; ++k) {
+          const uint64_t a = umma_smem_desc(k_addr + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          const uint64_t bq = umma_smem_desc(q_addr + (k >> 2) * (TC_NH * 128) + (k & 3) * 32, 16, 1024);
+          tc_mma_f16(d_tmem, a, bq, idesc_qk, k != 0);
+        }
+        tc_commit(&s_full[c & 1]);
+        return true;
+      };
+      ok = issue_qk(0);
+      for (int c = 0; ok && c < n_chunks; ++c) {
+        if (c + 1 < n_chunks) ok = issue_qk(c + 1);
+        if (!ok) break;
+        if (*abort_flag || !mbar_wait(&p_ready[c & 1], (c >> 1) & 1)) {
+          report_error(p.status, ERR_WAIT_TMEM_EMPTY, c);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const int s = c % TC_STAGES;
+        const uint32_t v_addr = smem_u32(stage0 + s * STAGE_BYTES_TC + KV_TILE_BYTES);
+        const uint32_t p_addr = smem_u32(p_s + (c & 1) * P_BYTES);
+        const uint32_t d_tmem = tmem_base + 32 + (c & 1) * TC_NH;
+#pragma unroll
+        for (int k = 0; k < TC_CHUNK / 16; ++k) {
+          // A: dims are the M side (two 64-dim halves 16 KB apart), 16 keys per step = 16 rows of 128 bytes
+          const uint64_t a = umma_smem_desc(v_addr + k * 2048, 16384, 1024);
+          const uint64_t bp = umma_smem_desc(p_addr + (k >> 2) * (TC_NH * 128) + (k & 3) * 32, 16, 1024);
+          tc_mma_f16(d_tmem, a, bp, idesc_pv, k != 0);
+        }
+        tc_commit(&o_full[c & 1]);
+        tc_commit(&empty[s]);
+      }
+    }
+  } else {
+    // ----------------------- softmax + accumulation (128 threads) -----------------------
+    float m_run[TC_NH], l_run[TC_NH], o_acc[TC_NH];
+#pragma unroll
+    for (int g = 0; g < TC_NH; ++g) {
+      m_run[g] = -INFINITY;
+      l_run[g] = 0.f;
+      o_acc[g] = 0.f;
+    }
+    const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
+    bool ok = true;
+    for (int c = 0; ok && c < n_chunks; ++c) {
+      const int i = c & 1;
+      const uint32_t par = (c >> 1) & 1;
+      if (*abort_flag || !mbar_wait(&s_full[i], par)) {
+        report_error(p.status, ERR_WAIT_TMEM_FULL, c);
+        *abort_flag = 1;
+        ok = false;
+      }
+      // every thread of the 4 warps must reach the named barriers: on failure fall through with zeros
+      uint32_t sr[16];
+      if (ok) {
+        tc_fence_after();
+        tmem_ld_32x16(tmem_base + lane_base + i * TC_NH, sr);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int g = 0; g < 16; ++g) sr[g] = 0;
+      }
+      const int key = (c_begin + c) * TC_CHUNK + tid;
+      const bool valid = key < seq_len;
+      float sc[TC_NH];
+#pragma unroll
+      for (int g = 0; g < TC_NH; ++g) {
+        sc[g] = valid ? __uint_as_float(sr[g]) * p.scale : -INFINITY;
+        if (g < G) {
+          const float wm = warp_reduce_max(sc[g]);
+          if (lane == 0) red_s[g][warp] = wm;
+        }
+      }
+      bar_sync_128();
+      float alpha[TC_NH], pv[TC_NH];
+#pragma unroll
+      for (int g = 0; g < TC_NH; ++g) {
+        alpha[g] = 1.f;
+        pv[g] = 0.f;
+        if (g < G) {
+          const float cm = fmaxf(fmaxf(red_s[g][0], red_s[g][1]), fmaxf(red_s[g][2], red_s[g][3]));
+          const float nm = fmaxf(m_run[g], cm);
+          alpha[g] = __expf(m_run[g] - nm);
+          pv[g] = valid ? __expf(sc[g] - nm) : 0.f;
+          m_run[g] = nm;
+        }
+      }
+      bar_sync_128();  // red_s consumed
+      // P^T[g][key] in bf16, swizzled K-major (row = head, k = key within the chunk)
+      uint8_t* pbuf = p_s + i * P_BYTES;
+#pragma unroll
+      for (int g = 0; g < TC_NH; ++g) {
+        if (g < G) {
+          *reinterpret_cast<__nv_bfloat16*>(pbuf + sw128_off(g, tid, TC_NH)) = __float2bfloat16(pv[g]);
+          const float ws = warp_reduce_sum(pv[g]);
+          if (lane == 0) red_s[g][warp] = ws;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[i]);
+      bar_sync_128();
+#pragma unroll
+      for (int g = 0; g < TC_NH; ++g)
+        if (g < G) l_run[g] = l_run[g] * alpha[g] + red_s[g][0] + red_s[g][1] + red_s[g][2] + red_s[g][3];
+      // O^T of this chunk: lane = output dim
+      if (ok && (*abort_flag || !mbar_wait(&o_full[i], par))) {
+        report_error(p.status, ERR_WAIT_TMEM_FULL, 1000 + c);
+        *abort_flag = 1;
+        ok = false;
+      }
+      if (ok) {
+        tc_fence_after();
+        uint32_t orr[16];
+        tmem_ld_32x16(tmem_base + lane_base + 32 + i * TC_NH, orr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < TC_NH; ++g)
+          if (g < G) o_acc[g] = o_acc[g] * alpha[g] + __uint_as_float(orr[g]);
+      }
+      ok = bar_and_128(ok);  // red_s reused by the next chunk; one failed wait ends the loop for all
+    }
+    if (ok) {
+      const int d = tid;
+#pragma unroll
+      for (int g = 0; g < TC_NH; ++g) {
+        if (g < G) {
+          const int hq = h * G + g;
+          if (p.num_splits == 1) {
+            p.out[(long long)b * p.out_stride + (long long)hq * TC_D + d] =
+                __float2bfloat16(l_run[g] > 0.f ? o_acc[g] / l_run[g] : 0.f);
+          } else {
+            const long long base = ((long long)b * p.Hq + hq) * p.num_splits + split;
+            p.o_part[base * TC_D + d] = o_acc[g];
+            if (d == 0) {
+              p.ml_part[base * 2] = m_run[g];
+              p.ml_part[base * 2 + 1] = l_run[g];
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 64);
+  }
+}
+
+}  // namespace vb
+
+using namespace vb;
+
+// Returns 1 if the tensor-core decode kernel supports this configuration.
+extern "C" int vb_paged_decode_tc_supported(int Hq, int Hk, int D, int block_size) {
+  return (D == TC_D && Hk > 0 && Hq % Hk == 0 && Hq / Hk <= TC_NH && block_size >= 8 && block_size <= 128 &&
+          TC_CHUNK % block_size == 0)
+             ? 1
+             : 0;
+}
+
+int vb_decode_merge_128(const float* o_part, const float* ml_part, int B, int Hq, int num_splits, void* out,
+                        long long out_stride, cudaStream_t stream);
+
+// Same contract as vb_paged_decode (caches [NB, Hk, block_size, 128] bf16, partial results merged here);
+// num_blocks is needed to describe the cache to TMA, status receives the code of a wait that ran out.
+extern "C" int vb_paged_decode_tc(const void* q, long long q_stride, const void* kc, const void* vc, int num_blocks,
+                                  const int* block_table, int max_blocks, const int* seq_lens, int B, int Hq, int Hk,
+                                  int block_size, float scale, int num_splits, void* out, long long out_stride,
+                                  float* work, int* status, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (!vb_paged_decode_tc_supported(Hq, Hk, TC_D, block_size)) return -3;
+  CUtensorMap tmK, tmV;
+  const uint64_t rows = (uint64_t)num_blocks * Hk * block_size;
+  int rc = vb_make_tmap_2d(&tmK, kc, 2, TC_D, rows, TC_D * 2, 64, block_size);
+  if (rc) return rc;
+  rc = vb_make_tmap_2d(&tmV, vc, 2, TC_D, rows, TC_D * 2, 64, block_size);
+  if (rc) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    VB_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
+    attr_set = true;
+  }
+  DecodeTcParams p{};
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q);
+  p.q_stride = q_stride;
+  p.block_table = block_table;
+  p.max_blocks = max_blocks;
+  p.seq_lens = seq_lens;
+  p.Hq = Hq; p.Hk = Hk; p.block_size = block_size;
+  p.scale = scale;
+  p.num_splits = num_splits;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.out_stride = out_stride;
+  p.o_part = work;
+  p.ml_part = work ? work + (long long)B * Hq * num_splits * TC_D : nullptr;
+  p.status = status;
+  dim3 grid(B, Hk, num_splits);
+  paged_decode_tc_kernel<<<grid, TC_THREADS, TC_SMEM, stream>>>(tmK, tmV, p);
+  vb_count_launch(num_splits > 1 ? 2 : 1);
+  rc = (int)cudaGetLastError();
+  if (rc || num_splits == 1) return rc;
+  return vb_decode_merge_128(p.o_part, p.ml_part, B, Hq, num_splits, out, out_stride, stream);
+}

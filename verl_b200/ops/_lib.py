@@ -26,6 +26,7 @@ _SIGS = {
     "vb_launch_count_reset": ([], None),
     # gemm
     "vb_gemm_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, I, I, P, P], I),
+    "vb_gemm_bf16_ws": ([P, P, P, P, I, I, I, L, L, L, I, I, I, I, P, L, P, I, P, P], I),
     "vb_lmhead_num_splits": ([I, I], I),
     "vb_lmhead_logprob_fwd": ([P, P, P, I, I, I, F, P, P, P, P, P, P, P], I),
     "vb_lmhead_dlogits": ([P, P, P, I, I, I, I, F, P, P, P, P, P, L, P, P], I),
@@ -49,6 +50,8 @@ _SIGS = {
     "vb_sample": ([P, I, L, I, I, P, P, P, U, P, P, P, P], I),
     # attention
     "vb_decode_num_splits": ([I, I, I], I),
+    "vb_paged_decode_tc_supported": ([I, I, I, I], I),
+    "vb_paged_decode_tc": ([P, L, P, P, I, P, I, P, I, I, I, I, F, I, P, L, P, P, P], I),
     "vb_paged_decode": ([P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, L, P, P], I),
     "vb_kv_cache_write": ([P, P, L, L, P, P, P, L, I, I, I, P], I),
 }

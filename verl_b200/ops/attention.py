@@ -74,9 +74,13 @@ def decode_workspace(B: int, Hq: int, Hk: int, D: int, max_seq_len: int, device)
 
 def paged_decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                            seq_lens: torch.Tensor, scale: float | None = None, num_splits: int = 1,
-                           work: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+                           work: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                           impl: str = "auto") -> torch.Tensor:
     """One query token per sequence. q [B,Hq,D]; caches [NB,Hk,BS,D]; block_table int32 [B,max_blocks];
-    seq_lens int32 [B] (including the current token, already written to the cache)."""
+    seq_lens int32 [B] (including the current token, already written to the cache).
+
+    ``impl``: "tc" = tcgen05 kernel (head_dim 128, <= 16 query heads per KV head, block size a power of two in
+    8..128), "simt" = CUDA-core kernel, "auto" = "tc" wherever it applies."""
     B, Hq, D = q.shape
     Hk, BS = k_cache.shape[1], k_cache.shape[2]
     scale = scale if scale is not None else D ** -0.5
@@ -85,6 +89,17 @@ def paged_decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     if q.is_cuda:
         if num_splits > 1 and work is None:
             work = torch.empty(B * Hq * num_splits * (D + 2), dtype=torch.float32, device=q.device)
+        tc_ok = bool(_lib.fn("vb_paged_decode_tc_supported")(Hq, Hk, D, BS)) and k_cache.is_contiguous() and v_cache.is_contiguous()
+        if impl == "tc" and not tc_ok:
+            raise ValueError(f"tensor-core decode does not support Hq={Hq} Hk={Hk} D={D} block_size={BS}")
+        if tc_ok and impl != "simt":
+            rc = _lib.fn("vb_paged_decode_tc")(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                                               k_cache.shape[0], block_table.data_ptr(), block_table.stride(0),
+                                               seq_lens.data_ptr(), B, Hq, Hk, BS, scale, num_splits, out.data_ptr(),
+                                               out.stride(0), _lib.ptr(work), _lib.status_word(q.device).data_ptr(),
+                                               _lib.stream())
+            _lib.check(rc, "vb_paged_decode_tc")
+            return out
         rc = _lib.fn("vb_paged_decode")(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
                                         block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(), B, Hq, Hk,
                                         D, BS, scale, num_splits, out.data_ptr(), out.stride(0), _lib.ptr(work),

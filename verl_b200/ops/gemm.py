@@ -63,13 +63,43 @@ def gemm(
         raise TypeError("out must be bf16 or fp32 with unit inner stride")
     if accumulate and out.dtype != torch.float32:
         raise TypeError("accumulate requires an fp32 output")
-    rc = _lib.fn("vb_gemm_bf16")(
+    stream = _lib.stream()
+    ws, counters = _splitk_workspace(a.device, stream) if M <= _SPLITK_MAX_M else (None, None)
+    rc = _lib.fn("vb_gemm_bf16_ws")(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K,
         a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn),
-        int(out.dtype == torch.float32), int(accumulate), _lib.status_word(a.device).data_ptr(), _lib.stream(),
+        int(out.dtype == torch.float32), int(accumulate),
+        _lib.ptr(ws), ws.numel() * 4 if ws is not None else 0, _lib.ptr(counters), _SPLITK_COUNTERS if ws is not None else 0,
+        _lib.status_word(a.device).data_ptr(), stream,
     )
     _lib.check(rc, "vb_gemm_bf16")
     return out
+
+
+# Split-K scratch for skinny problems (decode-time projections). One workspace per (device, stream): calls that
+# share one are ordered by the stream. Launches recorded under graph capture share one more workspace per device
+# (created by the first eager call, kept for the life of the process so that replays find it): graphs that
+# contain split-K GEMMs must therefore not be replayed concurrently with each other.
+_SPLITK_MAX_M = 256
+_SPLITK_BYTES = 32 << 20
+_SPLITK_COUNTERS = 4096
+_splitk_ws: dict = {}
+
+
+def _splitk_workspace(device, stream):
+    capturing = torch.cuda.is_current_stream_capturing()
+    key = (device.index, "capture" if capturing else stream)
+    got = _splitk_ws.get(key)
+    if got is None:
+        if capturing:
+            # allocating under capture would put the buffers in the graph's private pool
+            return None, None
+        for k in (key, (device.index, "capture")):
+            if k not in _splitk_ws:
+                _splitk_ws[k] = (torch.empty(_SPLITK_BYTES // 4, dtype=torch.float32, device=device),
+                                 torch.zeros(_SPLITK_COUNTERS, dtype=torch.int32, device=device))
+        got = _splitk_ws[key]
+    return got
 
 
 class _LinearFn(torch.autograd.Function):
