@@ -116,6 +116,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* d
       : "memory");
 }
 
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes).
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* desc, uint64_t* bar, int x, int y,
                                             int z) {
   asm volatile(

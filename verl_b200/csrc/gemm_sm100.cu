@@ -65,8 +65,8 @@ struct SmemLayout {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : (BN == 64) ? 8 : 10;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort flag
-  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], split-K reduce[2], tmem slot, abort flag, ticket
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 6) * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
 };
 
@@ -161,6 +161,41 @@ __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, int row, in
                 }
 }
 
+// Final store of 4 consecutive columns of one output row (split-K reduction).
+__device__ __forceinline__ void epi_store4(const GemmParams& p, int row, int col, float4 v) {
+  float x[4] = {v.x, v.y, v.z, v.w};
+  const bool full = col + 4 <= p.N;
+  if (p.bias != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (col + i < p.N) x[i] += __bfloat162float(p.bias[col + i]);
+  }
+  if (p.out_fp32) {
+    float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+    if (full && (p.ldc & 3) == 0) {
+      float4 o = make_float4(x[0], x[1], x[2], x[3]);
+      if (p.accumulate) {
+        const float4 old = *reinterpret_cast<const float4*>(dst);
+        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+      }
+      *reinterpret_cast<float4*>(dst) = o;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (col + i < p.N) dst[i] = p.accumulate ? dst[i] + x[i] : x[i];
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+    if (full && (p.ldc & 3) == 0) {
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (col + i < p.N) dst[i] = __float2bfloat16(x[i]);
+    }
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -173,7 +208,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* empty = full + L::STAGES;
   uint64_t* tfull = empty + L::STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* rbar = tempty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rbar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* ticket_s = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -189,6 +225,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
       mbar_init(&tempty[a], 4);
+      mbar_init(&rbar[a], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -352,8 +389,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int col0 = nb * BN + c * 32;
           if (EPI == EPI_STORE) {
             if (sched.k_splits > 1) {
-              // fp32 partial tile (the workspace is padded to whole tiles: no bounds checks)
-              float4* dst = reinterpret_cast<float4*>(p.ws + ((long long)ks * sched.num_m * BM + row) * ((long long)sched.num_n * BN) + col0);
+              // fp32 partial tile, tile-contiguous in the workspace: [tile][k slice][BM][BN]
+              float4* dst = reinterpret_cast<float4*>(
+                  p.ws + (((long long)(m_blk * sched.num_n + nb) * sched.k_splits + ks) * BM + row_in_tile) * BN + c * 32);
 #pragma unroll
               for (int i = 0; i < 8; ++i)
                 __stcg(dst + i, make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
@@ -434,34 +472,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           asm volatile("bar.sync 1, 128;" ::: "memory");
           const bool last = ok && (*ticket_s == sched.k_splits - 1);
           asm volatile("bar.sync 1, 128;" ::: "memory");  // ticket_s read by all before the next unit writes it
-          if (last) {
+          if (BN == 128 && last) {
+            // The slices come back through bulk async copies (no registers, full L2 bandwidth) into the pipeline
+            // stages, which are idle: a split-K launch gives every CTA exactly one unit. Four bands of 32 rows,
+            // double-buffered; slices are summed in slice order, so the result does not depend on arrival order.
             __threadfence();
-            const long long ldw = (long long)sched.num_n * BN;
-            const long long slice = (long long)sched.num_m * BM * ldw;
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            const int et = threadIdx.x - 64;
+            const int S = sched.k_splits;
+            constexpr int BAND_ROWS = 32, BAND_BYTES = BAND_ROWS * 128 * 4, BUF_BYTES = 6 * BAND_BYTES;
+            const float* ws_tile = p.ws + (long long)tile * S * (BM * 128);
+            auto issue = [&](int band) {
+              uint64_t* bar = &rbar[band & 1];
+              mbar_arrive_expect_tx(bar, (uint32_t)(S * BAND_BYTES));
+              for (int sp = 0; sp < S; ++sp)
+                bulk_load(smem + (band & 1) * BUF_BYTES + sp * BAND_BYTES,
+                          ws_tile + ((long long)sp * BM + band * BAND_ROWS) * 128, BAND_BYTES, bar);
+            };
+            if (et == 0) {
+              issue(0);
+              issue(1);
+            }
+            bool rok = true;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-              const int col0 = n_first * BN + c * 32;
-              if (!row_ok || col0 >= p.N) continue;
-              const float4* src = reinterpret_cast<const float4*>(p.ws + (long long)row * ldw + col0);
-              uint32_t r[32];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float4 v = __ldcg(src + i);
-                r[4 * i] = __float_as_uint(v.x); r[4 * i + 1] = __float_as_uint(v.y);
-                r[4 * i + 2] = __float_as_uint(v.z); r[4 * i + 3] = __float_as_uint(v.w);
+            for (int band = 0; band < BM / BAND_ROWS; ++band) {
+              if (!mbar_wait(&rbar[band & 1], (band >> 1) & 1)) {
+                report_error(p.status, ERR_WAIT_FULL, 2000 + band);
+                rok = false;
               }
-              for (int sp = 1; sp < sched.k_splits; ++sp) {
-                const float4* s2 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + sp * slice);
+              const uint8_t* buf = smem + (band & 1) * BUF_BYTES;
+              const int g = et & 31, rs = et >> 5;
+              const int col = n_first * 128 + g * 4;
+              if (rok) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float4 v = __ldcg(s2 + i);
-                  r[4 * i] = __float_as_uint(__uint_as_float(r[4 * i]) + v.x);
-                  r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) + v.y);
-                  r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) + v.z);
-                  r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) + v.w);
+                for (int j = 0; j < BAND_ROWS / 4; ++j) {
+                  const int rb = rs + 4 * j;
+                  float4 acc = *reinterpret_cast<const float4*>(buf + rb * 512 + g * 16);
+                  for (int sp = 1; sp < S; ++sp) {
+                    const float4 v = *reinterpret_cast<const float4*>(buf + sp * BAND_BYTES + rb * 512 + g * 16);
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                  }
+                  const int orow = m_blk * BM + band * BAND_ROWS + rb;
+                  if (orow < p.M && col < p.N) epi_store4(p, orow, col, acc);
                 }
               }
-              epi_store_chunk(p, row, col0, r);
+              asm volatile("bar.sync 1, 128;" ::: "memory");  // the buffer is free again
+              if (et == 0 && rok && band + 2 < BM / BAND_ROWS) issue(band + 2);
             }
             if (threadIdx.x == 64) p.counters[tile] = 0;
           }
@@ -567,7 +623,7 @@ extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void
     const int tiles128 = nm * nn;
     int splits = vb_num_sms() / (tiles128 > 0 ? tiles128 : 1);
     if (splits > nkb / 4) splits = nkb / 4;
-    if (splits > 16) splits = 16;
+    if (splits > 6) splits = 6;  // the reducing CTA stages 6 slices x 32 rows per buffer
     if (N > 128 && splits >= 2 && tiles128 <= num_counters) {
       const int per = (nkb + splits - 1) / splits;
       splits = (nkb + per - 1) / per;

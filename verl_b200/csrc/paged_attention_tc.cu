@@ -31,7 +31,9 @@ constexpr int STAGE_BYTES_TC = 2 * KV_TILE_BYTES;         // K + V
 constexpr int Q_BYTES = TC_NH * TC_D * 2;                 // 4 KB: two 64-dim k-blocks of 2 KB
 constexpr int P_BYTES = TC_NH * TC_CHUNK * 2;             // 4 KB: two 64-key k-blocks of 2 KB
 constexpr int TC_BAR_OFF = TC_STAGES * STAGE_BYTES_TC + Q_BYTES + 2 * P_BYTES;
-constexpr int TC_SMEM = TC_BAR_OFF + 16 * 8 + 64 + 1024;
+constexpr int TC_BT_OFF = TC_BAR_OFF + 16 * 8 + 64;
+constexpr int TC_BT_MAX = 1024;  // block-table entries of this CTA's key range staged in shared memory
+constexpr int TC_SMEM = TC_BT_OFF + TC_BT_MAX * 4 + 1024;
 
 struct DecodeTcParams {
   const __nv_bfloat16* q;
@@ -84,6 +86,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   uint64_t* o_full = p_ready + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* bt_s = reinterpret_cast<int*>(smem + TC_BT_OFF);
   __shared__ float red_s[TC_NH][4];
 
   const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
@@ -109,6 +112,15 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     *abort_flag = 0;
     mbar_fence_init();
   }
+  // block-table entries of this CTA's pages: the producer must not chase global loads between its copies
+  const int pages_per_chunk = TC_CHUNK / p.block_size;
+  const int n_pages = (seq_len + p.block_size - 1) / p.block_size;
+  const int page_base = c_begin * pages_per_chunk;
+  {
+    const int* bt = p.block_table + (long long)b * p.max_blocks;
+    const int cnt = min(min(n_chunks * pages_per_chunk, n_pages - page_base), TC_BT_MAX);
+    for (int i = tid; i < cnt; i += TC_THREADS) bt_s[i] = bt[page_base + i];
+  }
   // Q^T operand: [16 heads x 128 dims], rows >= G are zero. P buffers start zeroed (rows >= G stay zero).
   for (int i = tid; i < (Q_BYTES + 2 * P_BYTES) / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
@@ -132,9 +144,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     if (lane == 0 && n_chunks > 0) {
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
-      const int pages_per_chunk = TC_CHUNK / p.block_size;
       const int* bt = p.block_table + (long long)b * p.max_blocks;
-      const int n_pages = (seq_len + p.block_size - 1) / p.block_size;
       for (int c = 0; c < n_chunks; ++c) {
         const int s = c % TC_STAGES;
         const uint32_t par = ((c / TC_STAGES) & 1) ^ 1;
@@ -150,7 +160,9 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         for (int pg = 0; pg < pages_per_chunk; ++pg) {
           // pages past the end of the sequence re-read the sequence's last page: finite data, masked later
           const int pi = min(page0 + pg, n_pages - 1);
-          const int row = (bt[pi] * p.Hk + h) * p.block_size;
+          const int rel = pi - page_base;
+          const int blk = rel < TC_BT_MAX ? bt_s[rel] : bt[pi];
+          const int row = (blk * p.Hk + h) * p.block_size;
           const int off = pg * p.block_size * 128;
           tma_load_2d(k_dst + off, &tmK, &full[s], 0, row);
           tma_load_2d(k_dst + 16384 + off, &tmK, &full[s], 64, row);
