@@ -728,3 +728,52 @@ extern "C" int vb_lmhead_dlogits(const void* hidden, const void* weight_chunk, c
   p.n_offset = n_offset; p.status = status;
   return launch_gemm<256, false, false, EPI_DLOGITS>(hidden, weight_chunk, H, H, p, stream);
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant of the fused lm_head forward (declared in lmhead_static.h).
+#include "lmhead_static.h"
+
+#include <cstdio>
+#include <mutex>
+
+static __device__ __align__(256) float g_lmhead_static_scratch[VB_LMHEAD_STATIC_SCRATCH_FLOATS];
+
+extern "C" int vb_lmhead_static_scratch_floats(void) { return VB_LMHEAD_STATIC_SCRATCH_FLOATS; }
+
+extern "C" int vb_lmhead_logprob_fwd_static(const void* hidden, const void* weight, const long long* labels, int T,
+                                            int H, int V, float inv_temperature, float* logprob, float* entropy,
+                                            float* lse, float* mean, int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (V <= 0 || H <= 0 || (H & 7)) return -3;
+  const long long need = (long long)T * vb_lmhead_num_splits(T, V) * 4;
+  if (need > (long long)VB_LMHEAD_STATIC_SCRATCH_FLOATS) {
+    fprintf(stderr,
+            "vb_lmhead_logprob_fwd_static: T=%d V=%d needs %lld scratch floats, the static array holds %d; "
+            "use vb_lmhead_logprob_fwd with caller-provided scratch\n",
+            T, V, need, VB_LMHEAD_STATIC_SCRATCH_FLOATS);
+    return -4;
+  }
+  // per-device address of the array, resolved once
+  static std::mutex mu;
+  static float* scratch_of[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return -5;
+  float* ptr = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (scratch_of[dev] == nullptr) {
+      float* p = nullptr;
+      e = cudaGetSymbolAddress((void**)&p, g_lmhead_static_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        fprintf(stderr, "vb_lmhead_logprob_fwd_static: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+        return -5;
+      }
+      scratch_of[dev] = p;
+    }
+    ptr = scratch_of[dev];
+  }
+  return vb_lmhead_logprob_fwd(hidden, weight, labels, T, H, V, inv_temperature, ptr, logprob, entropy, lse, mean,
+                               status, stream);
+}
