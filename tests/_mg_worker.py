@@ -1,0 +1,134 @@
+"""Child process of tests/test_multigpu.py (one rank per GPU, launched through torch.distributed.run)."""
+
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def check_comm(comm, rank, world, dev):
+    from verl_b200.ops import _lib
+
+    for it in range(3):
+        n = 4096 * 3 + 8 * it
+        src = comm.alloc(n, torch.bfloat16)
+        src.copy_((torch.arange(n, device=dev) % 251 + rank * 7 + it).to(torch.bfloat16))
+        out = torch.empty(n * world, dtype=torch.bfloat16, device=dev)
+        comm.all_gather(out, src)
+        exp = torch.cat([(torch.arange(n, device=dev) % 251 + r * 7 + it).to(torch.bfloat16) for r in range(world)])
+        assert torch.equal(out, exp), f"all_gather mismatch (iteration {it})"
+
+        shard = 1024 * 5 + 4 * it
+        full = comm.alloc(shard * world, torch.float32)
+        g = torch.Generator(device="cpu").manual_seed(100 * it + rank)
+        full.copy_(torch.randn(shard * world, generator=g).to(dev))
+        dst = torch.full((shard,), 0.5, device=dev)
+        want = torch.zeros(shard)
+        for r in range(world):
+            gr = torch.Generator(device="cpu").manual_seed(100 * it + r)
+            want += torch.randn(shard * world, generator=gr)[rank * shard : (rank + 1) * shard]
+        for nvls in (False, True):
+            comm.use_nvls = nvls
+            d = dst.clone()
+            comm.reduce_scatter_add(d, full, scale=0.25)
+            torch.testing.assert_close(d.cpu(), 0.5 + 0.25 * want, atol=1e-5, rtol=1e-5)
+        comm.barrier()
+    comm.check()
+    assert _lib.read_status(dev)[0] == 0
+
+
+def _packed(ids, lens, dev):
+    from verl_b200.models.transformer import PackedBatch
+
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32, device=dev)
+    cu[1:] = torch.cumsum(torch.tensor(lens, device=dev), 0)
+    pos = torch.cat([torch.arange(n, device=dev) for n in lens])
+    return PackedBatch(ids, pos, cu, max(lens))
+
+
+def check_reshard(comm, rank, world, dev):
+    """ZeRO shards -> full rollout weights (TP = 1) through the one-launch segment copy."""
+    from verl_b200.models import preset
+    from verl_b200.models.transformer import CausalLM
+    from verl_b200.parallel.reshard import RolloutWeights
+    from verl_b200.workers.engine.native import NativeEngine
+
+    cfg = preset("tiny-qwen2")
+    ref_model = CausalLM(cfg, dtype=torch.bfloat16, device=dev)
+    ref_model.init_weights(7)
+    ref_state = {k: v.detach().clone() for k, v in ref_model.named_parameters()}
+    eng = NativeEngine(cfg, None, None, device=str(dev), group=dist.group.WORLD, seed=7, trainable=False,
+                       comm=comm).initialize()
+    roll = CausalLM(cfg, dtype=torch.bfloat16, device=dev)
+    roll.init_weights(8)
+    rw = RolloutWeights(cfg, eng.zero, roll, tp_rank=0, tp_size=1)
+    rw.sync()
+    torch.cuda.synchronize()
+    comm.check()
+    n = 0
+    for k, v in roll.named_parameters():
+        assert torch.equal(v, ref_state[k]), f"reshard mismatch in {k}"
+        n += 1
+    assert n > 0
+
+
+def check_zero_step(rank, world, dev, comm):
+    """One optimizer step of the native engine: peer-memory collectives vs NCCL collectives give the same weights."""
+    from verl_b200.models import preset
+    from verl_b200.workers.engine.native import NativeEngine
+
+    class C(dict):
+        __getattr__ = dict.get
+
+    cfg = preset("tiny-qwen2")
+    optim = C(lr=1e-2, weight_decay=0.01, betas=(0.9, 0.95), clip_grad=1.0, lr_warmup_steps=0, total_training_steps=10)
+    outs = []
+    for use_comm in (True, False):
+        eng = NativeEngine(cfg, C(), optim, device=str(dev), group=dist.group.WORLD, seed=3,
+                           comm=comm if use_comm else None).initialize()
+        g = torch.Generator().manual_seed(50 + rank)
+        lens = [37, 64, 21]
+        ids = torch.randint(0, cfg.vocab_size, (sum(lens),), generator=g).to(dev)
+        batch = _packed(ids, lens, dev)
+        labels = torch.roll(ids, -1)
+        rows = torch.arange(ids.numel(), device=dev)
+        with eng.train_mode():
+            eng.optimizer_zero_grad()
+            lp, ent = eng.forward_logprob(batch, rows, labels, 1.0)
+            (-lp.mean()).backward()
+            gn = eng.optimizer_step()
+        outs.append((float(gn), eng.zero.shard16.clone().float(), float(lp.mean())))
+    (gn_a, w_a, l_a), (gn_b, w_b, l_b) = outs
+    assert abs(l_a - l_b) < 1e-3, (l_a, l_b)
+    assert abs(gn_a - gn_b) <= 2e-3 * max(1.0, abs(gn_b)), (gn_a, gn_b)
+    torch.testing.assert_close(w_a, w_b, atol=2e-2, rtol=2e-2)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    from verl_b200.parallel.peer_comm import PeerComm
+
+    comm = PeerComm(dist.group.WORLD)
+    what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if what in ("comm", "all"):
+        check_comm(comm, rank, world, dev)
+    if what in ("reshard", "all"):
+        check_reshard(comm, rank, world, dev)
+    if what in ("zero", "all"):
+        check_zero_step(rank, world, dev, comm)
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 0:
+        print(f"MG_WORKER_OK {what}")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,26 @@
+"""Multi-GPU tests: peer-memory collectives, the one-launch reshard and a ZeRO step on >= 2 GPUs."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(what: str, nproc: int = 2, timeout: int = 600):
+    port = 29000 + (os.getpid() % 500)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "_mg_worker.py"), what]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0 and f"MG_WORKER_OK {what}" in r.stdout, (r.stdout[-3000:], r.stderr[-6000:])
+
+
+@pytest.mark.parametrize("what", ["comm", "reshard", "zero"])
+def test_two_ranks(what):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _run(what, 2)

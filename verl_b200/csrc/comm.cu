@@ -111,7 +111,7 @@ __global__ void peer_all_gather_kernel(PeerPtrs srcs, PeerPtrs pads, long long s
     const int p = (int)(j / shard16);
     const long long k = j - (long long)p * shard16;
     const uint4* src = reinterpret_cast<const uint4*>(srcs.p[p]) + src_off16 + k;
-    out[j] = __ldg(src);
+    out[j] = *src;
   }
 }
 
@@ -126,7 +126,7 @@ __global__ void peer_reduce_scatter_add_kernel(PeerPtrs fulls, PeerPtrs pads, lo
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int q = 0; q < world; ++q) {
       const int p = (rank + q) % world;
-      const float4 v = __ldg(reinterpret_cast<const float4*>(fulls.p[p]) + full_off4 + (long long)rank * shard4 + i);
+      const float4 v = *(reinterpret_cast<const float4*>(fulls.p[p]) + full_off4 + (long long)rank * shard4 + i);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     float4 d = dst[i];
@@ -172,7 +172,7 @@ __global__ void peer_segment_copy_kernel(PeerPtrs srcs, PeerPtrs pads, const Seg
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(srcs.p[sg.src_rank]) + sg.src_off);
     uint4* dst = reinterpret_cast<uint4*>(dst_base + sg.dst_off);
     const long long n16 = sg.nbytes >> 4;
-    for (long long i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldg(src + i);
+    for (long long i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
   }
 }
 

@@ -11,7 +11,9 @@
 //                memory in the 128-byte-swizzled K-major layout, then fold O^T of the chunk into the running
 //                output held in registers (flash-decoding rescale)
 //   warp 4     : TMA producer: the pages of a chunk are fetched with per-CTA 2-D tiled loads straight from
-//                the paged cache ([num_blocks, Hk, block_size, 128]) into a 3-stage ring (K and V, 64 KB / stage)
+//                the paged cache ([num_blocks, Hk, block_size, 128]) into a ring of three 32 KB slots that
+//                alternates K and V tiles; shared memory stays near 111 KB so that two CTAs share an SM and
+//                one CTA's softmax chain overlaps the other's loads and MMAs
 //   warp 5     : TMEM allocation + single-thread tcgen05.mma issue
 //
 // V needs no transpose: [keys, dims] with dims contiguous is exactly an "MN-major" A operand.
@@ -24,16 +26,17 @@ namespace vb {
 constexpr int TC_CHUNK = 128;   // keys per chunk
 constexpr int TC_D = 128;       // head dim
 constexpr int TC_NH = 16;       // padded number of query heads per KV head (UMMA N)
-constexpr int TC_STAGES = 3;
+constexpr int TC_STAGES = 3;    // ring slots of one 32 KB tile each; tiles alternate K(0), V(0), K(1), V(1), ...
 constexpr int TC_THREADS = 192;
 constexpr int KV_TILE_BYTES = TC_CHUNK * TC_D * 2;        // 32 KB (two 64-wide halves of 16 KB)
-constexpr int STAGE_BYTES_TC = 2 * KV_TILE_BYTES;         // K + V
+constexpr int STAGE_BYTES_TC = KV_TILE_BYTES;
 constexpr int Q_BYTES = TC_NH * TC_D * 2;                 // 4 KB: two 64-dim k-blocks of 2 KB
 constexpr int P_BYTES = TC_NH * TC_CHUNK * 2;             // 4 KB: two 64-key k-blocks of 2 KB
 constexpr int TC_BAR_OFF = TC_STAGES * STAGE_BYTES_TC + Q_BYTES + 2 * P_BYTES;
 constexpr int TC_BT_OFF = TC_BAR_OFF + 16 * 8 + 64;
-constexpr int TC_BT_MAX = 1024;  // block-table entries of this CTA's key range staged in shared memory
-constexpr int TC_SMEM = TC_BT_OFF + TC_BT_MAX * 4 + 1024;
+constexpr int TC_BT_MAX = 256;  // block-table entries of this CTA's key range staged in shared memory
+constexpr int TC_RED_OFF = TC_BT_OFF + TC_BT_MAX * 4;
+constexpr int TC_SMEM = TC_RED_OFF + 2 * TC_NH * 4 * 4 + 1024;  // about 111 KB: two CTAs per SM
 
 struct DecodeTcParams {
   const __nv_bfloat16* q;
@@ -71,7 +74,7 @@ __device__ __forceinline__ bool bar_and_128(bool pred) {
   return r != 0;
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, 2)
 paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const DecodeTcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -87,7 +90,8 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* bt_s = reinterpret_cast<int*>(smem + TC_BT_OFF);
-  __shared__ float red_s[TC_NH][4];
+  float (*red_s)[4] = reinterpret_cast<float (*)[4]>(smem + TC_RED_OFF);           // per-warp chunk maxima
+  float (*red2_s)[4] = reinterpret_cast<float (*)[4]>(smem + TC_RED_OFF + TC_NH * 16);  // per-warp chunk sums
 
   const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
   const int G = p.Hq / p.Hk;
@@ -145,18 +149,18 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       const int* bt = p.block_table + (long long)b * p.max_blocks;
-      for (int c = 0; c < n_chunks; ++c) {
-        const int s = c % TC_STAGES;
-        const uint32_t par = ((c / TC_STAGES) & 1) ^ 1;
+      for (int t = 0; t < 2 * n_chunks; ++t) {
+        const int s = t % TC_STAGES;
+        const uint32_t par = ((t / TC_STAGES) & 1) ^ 1;
         if (*abort_flag || !mbar_wait(&empty[s], par)) {
-          report_error(p.status, ERR_WAIT_EMPTY, c);
+          report_error(p.status, ERR_WAIT_EMPTY, t);
           *abort_flag = 1;
           break;
         }
         mbar_arrive_expect_tx(&full[s], STAGE_BYTES_TC);
-        uint8_t* k_dst = stage0 + s * STAGE_BYTES_TC;
-        uint8_t* v_dst = k_dst + KV_TILE_BYTES;
-        const int page0 = (c_begin + c) * pages_per_chunk;
+        uint8_t* dst = stage0 + s * STAGE_BYTES_TC;
+        const CUtensorMap* tm = (t & 1) ? &tmV : &tmK;
+        const int page0 = (c_begin + (t >> 1)) * pages_per_chunk;
         for (int pg = 0; pg < pages_per_chunk; ++pg) {
           // pages past the end of the sequence re-read the sequence's last page: finite data, masked later
           const int pi = min(page0 + pg, n_pages - 1);
@@ -164,10 +168,8 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
           const int blk = rel < TC_BT_MAX ? bt_s[rel] : bt[pi];
           const int row = (blk * p.Hk + h) * p.block_size;
           const int off = pg * p.block_size * 128;
-          tma_load_2d(k_dst + off, &tmK, &full[s], 0, row);
-          tma_load_2d(k_dst + 16384 + off, &tmK, &full[s], 64, row);
-          tma_load_2d(v_dst + off, &tmV, &full[s], 0, row);
-          tma_load_2d(v_dst + 16384 + off, &tmV, &full[s], 64, row);
+          tma_load_2d(dst + off, tm, &full[s], 0, row);
+          tma_load_2d(dst + 16384 + off, tm, &full[s], 64, row);
         }
       }
     }
@@ -179,9 +181,9 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       const uint32_t q_addr = smem_u32(q_s);
       bool ok = true;
       auto issue_qk = [&](int c) -> bool {
-        const int s = c % TC_STAGES;
-        if (*abort_flag || !mbar_wait(&full[s], (c / TC_STAGES) & 1)) {
-          report_error(p.status, ERR_WAIT_FULL, c);
+        const int t = 2 * c, s = t % TC_STAGES;
+        if (*abort_flag || !mbar_wait(&full[s], (t / TC_STAGES) & 1)) {
+          report_error(p.status, ERR_WAIT_FULL, t);
           *abort_flag = 1;
           return false;
         }
@@ -195,20 +197,26 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
           tc_mma_f16(d_tmem, a, bq, idesc_qk, k != 0);
         }
         tc_commit(&s_full[c & 1]);
+        tc_commit(&empty[s]);
         return true;
       };
       ok = issue_qk(0);
       for (int c = 0; ok && c < n_chunks; ++c) {
         if (c + 1 < n_chunks) ok = issue_qk(c + 1);
         if (!ok) break;
+        const int t = 2 * c + 1, s = t % TC_STAGES;
+        if (*abort_flag || !mbar_wait(&full[s], (t / TC_STAGES) & 1)) {
+          report_error(p.status, ERR_WAIT_FULL, t);
+          *abort_flag = 1;
+          break;
+        }
         if (*abort_flag || !mbar_wait(&p_ready[c & 1], (c >> 1) & 1)) {
           report_error(p.status, ERR_WAIT_TMEM_EMPTY, c);
           *abort_flag = 1;
           break;
         }
         tc_fence_after();
-        const int s = c % TC_STAGES;
-        const uint32_t v_addr = smem_u32(stage0 + s * STAGE_BYTES_TC + KV_TILE_BYTES);
+        const uint32_t v_addr = smem_u32(stage0 + s * STAGE_BYTES_TC);
         const uint32_t p_addr = smem_u32(p_s + (c & 1) * P_BYTES);
         const uint32_t d_tmem = tmem_base + 32 + (c & 1) * TC_NH;
 #pragma unroll
@@ -233,10 +241,11 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     }
     const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
     bool ok = true;
-    for (int c = 0; ok && c < n_chunks; ++c) {
+    float alpha_cur[TC_NH], alpha_nxt[TC_NH];
+    // softmax of chunk c: S^T -> P^T (bf16, shared memory), running max / sum, rescale factor of this chunk
+    auto softmax_chunk = [&](int c, float (&alpha)[TC_NH]) {
       const int i = c & 1;
-      const uint32_t par = (c >> 1) & 1;
-      if (*abort_flag || !mbar_wait(&s_full[i], par)) {
+      if (*abort_flag || !mbar_wait(&s_full[i], (c >> 1) & 1)) {
         report_error(p.status, ERR_WAIT_TMEM_FULL, c);
         *abort_flag = 1;
         ok = false;
@@ -263,28 +272,20 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         }
       }
       bar_sync_128();
-      float alpha[TC_NH], pv[TC_NH];
+      uint8_t* pbuf = p_s + i * P_BYTES;
 #pragma unroll
       for (int g = 0; g < TC_NH; ++g) {
         alpha[g] = 1.f;
-        pv[g] = 0.f;
         if (g < G) {
           const float cm = fmaxf(fmaxf(red_s[g][0], red_s[g][1]), fmaxf(red_s[g][2], red_s[g][3]));
           const float nm = fmaxf(m_run[g], cm);
           alpha[g] = __expf(m_run[g] - nm);
-          pv[g] = valid ? __expf(sc[g] - nm) : 0.f;
+          const float pv = valid ? __expf(sc[g] - nm) : 0.f;
           m_run[g] = nm;
-        }
-      }
-      bar_sync_128();  // red_s consumed
-      // P^T[g][key] in bf16, swizzled K-major (row = head, k = key within the chunk)
-      uint8_t* pbuf = p_s + i * P_BYTES;
-#pragma unroll
-      for (int g = 0; g < TC_NH; ++g) {
-        if (g < G) {
-          *reinterpret_cast<__nv_bfloat16*>(pbuf + sw128_off(g, tid, TC_NH)) = __float2bfloat16(pv[g]);
-          const float ws = warp_reduce_sum(pv[g]);
-          if (lane == 0) red_s[g][warp] = ws;
+          // P^T[g][key] in bf16, swizzled K-major (row = head, k = key within the chunk)
+          *reinterpret_cast<__nv_bfloat16*>(pbuf + sw128_off(g, tid, TC_NH)) = __float2bfloat16(pv);
+          const float ws = warp_reduce_sum(pv);
+          if (lane == 0) red2_s[g][warp] = ws;
         }
       }
       fence_proxy_async_smem();
@@ -294,9 +295,18 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       bar_sync_128();
 #pragma unroll
       for (int g = 0; g < TC_NH; ++g)
-        if (g < G) l_run[g] = l_run[g] * alpha[g] + red_s[g][0] + red_s[g][1] + red_s[g][2] + red_s[g][3];
+        if (g < G) l_run[g] = l_run[g] * alpha[g] + red2_s[g][0] + red2_s[g][1] + red2_s[g][2] + red2_s[g][3];
+    };
+    if (n_chunks > 0) {
+      softmax_chunk(0, alpha_cur);
+      ok = bar_and_128(ok);  // all 128 threads enter (or skip) the loop together
+    }
+    for (int c = 0; ok && c < n_chunks; ++c) {
+      const int i = c & 1;
+      // the next chunk's softmax runs while the tensor core works on P.V of this one
+      if (c + 1 < n_chunks) softmax_chunk(c + 1, alpha_nxt);
       // O^T of this chunk: lane = output dim
-      if (ok && (*abort_flag || !mbar_wait(&o_full[i], par))) {
+      if (ok && (*abort_flag || !mbar_wait(&o_full[i], (c >> 1) & 1))) {
         report_error(p.status, ERR_WAIT_TMEM_FULL, 1000 + c);
         *abort_flag = 1;
         ok = false;
@@ -308,9 +318,11 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < TC_NH; ++g)
-          if (g < G) o_acc[g] = o_acc[g] * alpha[g] + __uint_as_float(orr[g]);
+          if (g < G) o_acc[g] = o_acc[g] * alpha_cur[g] + __uint_as_float(orr[g]);
       }
-      ok = bar_and_128(ok);  // red_s reused by the next chunk; one failed wait ends the loop for all
+#pragma unroll
+      for (int g = 0; g < TC_NH; ++g) alpha_cur[g] = alpha_nxt[g];
+      ok = bar_and_128(ok);  // one failed wait ends the loop for all
     }
     if (ok) {
       const int d = tid;
