@@ -358,18 +358,36 @@ class NativeRolloutEngine:
             return self._graphs[B]
         dev, c = self.device, self.cfg
         mb = self.sched.max_blocks
-        st = {
-            "ids": torch.zeros(B, dtype=torch.long, device=dev),
-            "pos": torch.zeros(B, dtype=torch.long, device=dev),
-            "slots": torch.full((B,), -1, dtype=torch.long, device=dev),
-            "bt": torch.zeros(B, mb, dtype=torch.int32, device=dev),
-            "lens": torch.ones(B, dtype=torch.int32, device=dev),
-            "temp": torch.ones(B, dtype=torch.float32, device=dev),
-            "topk": torch.full((B,), -1, dtype=torch.int32, device=dev),
-            "topp": torch.ones(B, dtype=torch.float32, device=dev),
-            "tok": torch.zeros(B, dtype=torch.long, device=dev),
-            "lp": torch.zeros(B, dtype=torch.float32, device=dev),
-        }
+        # All per-step inputs live in ONE device buffer that is filled by ONE copy from a pinned host mirror, the
+        # two outputs in one more buffer that comes back in one copy: a decode step costs two small transfers.
+        fields = [("ids", np.int64, (B,), 0), ("pos", np.int64, (B,), 0), ("slots", np.int64, (B,), -1),
+                  ("lens", np.int32, (B,), 1), ("temp", np.float32, (B,), 1.0), ("topk", np.int32, (B,), -1),
+                  ("topp", np.float32, (B,), 1.0), ("bt", np.int32, (B, mb), 0)]
+        off, layout = 0, {}
+        for name, dt, shape, _ in fields:
+            nb = int(np.prod(shape)) * np.dtype(dt).itemsize
+            layout[name] = (off, nb)
+            off = (off + nb + 255) // 256 * 256
+        pin = dev.type == "cuda"
+        host = torch.zeros(off, dtype=torch.uint8, pin_memory=pin)
+        devbuf = torch.zeros(off, dtype=torch.uint8, device=dev)
+        out_dev = torch.zeros(B * 12, dtype=torch.uint8, device=dev)
+        out_host = torch.zeros(B * 12, dtype=torch.uint8, pin_memory=pin)
+        tdt = {np.int64: torch.int64, np.int32: torch.int32, np.float32: torch.float32}
+        st = {"host": {}, "pad": {}, "host_buf": host, "dev_buf": devbuf, "out_dev": out_dev, "out_host": out_host,
+              "sig": None}
+        hnp = host.numpy()
+        for name, dt, shape, pad in fields:
+            o, nb = layout[name]
+            st[name] = devbuf[o : o + nb].view(tdt[dt]).view(shape)
+            st["host"][name] = hnp[o : o + nb].view(dt).reshape(shape)
+            st["host"][name][...] = pad
+            st["pad"][name] = pad
+        devbuf.copy_(host)
+        st["tok"] = out_dev[: B * 8].view(torch.int64)
+        st["lp"] = out_dev[B * 8 :].view(torch.float32)
+        st["host_tok"] = out_host.numpy()[: B * 8].view(np.int64)
+        st["host_lp"] = out_host.numpy()[B * 8 :].view(np.float32)
         splits, work = ops.decode_workspace(B, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
                                             self.max_model_len, dev)
         st["splits"], st["work"] = splits, work
@@ -480,27 +498,31 @@ class NativeRolloutEngine:
             st, graph, run = self._get_graph(B)
             di = np.asarray(dec)
             t_idx = np.asarray([tok_lo[i] for i in dec])
-
-            def fill(name, arr, pad):
-                buf = np.full((B,) + arr.shape[1:], pad, dtype=arr.dtype)
-                buf[:nd] = arr
-                st[name].copy_(torch.from_numpy(buf), non_blocking=True)
-
-            fill("ids", sc.tokens[t_idx], 0)
-            fill("pos", sc.positions[t_idx], 0)
-            fill("slots", sc.slots[t_idx], -1)
-            fill("bt", sc.block_tables[di], 0)
-            fill("lens", sc.seq_total[di], 1)
-            sps = [self.requests[int(sc.seq_ids[i])].params for i in dec]
-            fill("temp", np.asarray([p.temperature for p in sps], np.float32), 1.0)
-            fill("topk", np.asarray([p.top_k for p in sps], np.int32), -1)
-            fill("topp", np.asarray([p.top_p for p in sps], np.float32), 1.0)
+            hp, pad = st["host"], st["pad"]
+            sig = (nd, sc.seq_ids[di].tobytes())
+            fresh = st["sig"] != sig  # batch membership changed: rewrite the padding and the sampling parameters
+            for name, arr in (("ids", sc.tokens[t_idx]), ("pos", sc.positions[t_idx]), ("slots", sc.slots[t_idx]),
+                              ("bt", sc.block_tables[di]), ("lens", sc.seq_total[di])):
+                hp[name][:nd] = arr
+                if fresh:
+                    hp[name][nd:] = pad[name]
+            if fresh:
+                sps = [self.requests[int(sid)].params for sid in sc.seq_ids[di]]
+                for name, vals in (("temp", [p.temperature for p in sps]), ("topk", [p.top_k for p in sps]),
+                                   ("topp", [p.top_p for p in sps])):
+                    hp[name][:nd] = vals
+                    hp[name][nd:] = pad[name]
+                st["sig"] = sig
+            st["dev_buf"].copy_(st["host_buf"], non_blocking=True)
             if graph is not None:
                 graph.replay()
             else:
                 run()
-            new_tokens[di] = st["tok"][:nd].cpu().numpy()
-            new_lps[di] = st["lp"][:nd].cpu().numpy()
+            st["out_host"].copy_(st["out_dev"], non_blocking=True)
+            if dev.type == "cuda":
+                torch.cuda.current_stream(dev).synchronize()
+            new_tokens[di] = st["host_tok"][:nd]
+            new_lps[di] = st["host_lp"][:nd]
             self.stats["decode_tokens"] += nd
         if pre:
             logits = self._prefill_forward(pre, [tok_lo[i] for i in pre])
@@ -517,22 +539,24 @@ class NativeRolloutEngine:
         # stop criteria
         finished = np.zeros(n, np.int32)
         reasons = {}
-        for i in range(n):
-            sid = int(sc.seq_ids[i])
-            req = self.requests[sid]
-            t = int(new_tokens[i])
-            if not req.params.ignore_eos and (t == self.eos or t in req.params.stop_token_ids):
+        sids = sc.seq_ids[:n].tolist()
+        reqs = [self.requests[sid] for sid in sids]
+        toks = new_tokens.tolist()
+        eos = self.eos
+        for i, (req, t) in enumerate(zip(reqs, toks)):
+            prm = req.params
+            if not prm.ignore_eos and (t == eos or (prm.stop_token_ids and t in prm.stop_token_ids)):
                 finished[i] = 1
-                reasons[sid] = "completed"
-        done = sc.commit(new_tokens, finished).copy()
+                reasons[sids[i]] = "completed"
+        done = sc.commit(new_tokens, finished).tolist()
+        partial = (sc.seq_prefill[:n] == 2).tolist()  # partial prefill chunk: its sampled token is discarded
+        lps = new_lps.tolist()
         outs = []
-        for i in range(n):
-            sid = int(sc.seq_ids[i])
-            req = self.requests[sid]
-            if new_tokens[i] >= 0 and self._was_sampled(i):
-                req.logprobs.append(float(new_lps[i]))
+        for i, req in enumerate(reqs):
+            if toks[i] >= 0 and not partial[i]:
+                req.logprobs.append(lps[i])
             if done[i]:
-                outs.append(self._finish(sid, reasons.get(sid, "length")))
+                outs.append(self._finish(sids[i], reasons.get(sids[i], "length")))
         return outs
 
     def _was_sampled(self, i: int) -> bool:
