@@ -82,6 +82,30 @@ def test_gemm_split_k(M, N, K, mode):
     torch.testing.assert_close(C, ref + 2.0, atol=2e-2, rtol=1e-4)
 
 
+@pytest.mark.parametrize("mode", ["tn", "nn", "wg", "an"])
+def test_gemm_cta_pair_path(mode):
+    """Large problems run on CTA pairs (256 x 256 tiles, one MMA for two SMs). Odd 128-row block count, ragged N and
+    K, every operand layout, bias and fp32 accumulation."""
+    from verl_b200.ops import gemm, _lib
+
+    torch.manual_seed(4)
+    M, N, K = 4224, 2632, 584
+    a_mn, b_mn = {"tn": (False, False), "nn": (False, True), "wg": (True, True), "an": (True, False)}[mode]
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    Am = A.t().contiguous() if a_mn else A
+    Bm = B.t().contiguous() if b_mn else B
+    out = gemm(Am, Bm, a_mn=a_mn, b_mn=b_mn, bias=bias)
+    assert _lib.read_status("cuda")[0] == 0
+    _bf16_close(out, ref + bias.float())
+    assert torch.equal(out, gemm(Am, Bm, a_mn=a_mn, b_mn=b_mn, bias=bias))
+    C = torch.full((M, N), -1.0, device="cuda")
+    gemm(Am, Bm, a_mn=a_mn, b_mn=b_mn, out=C, accumulate=True)
+    torch.testing.assert_close(C, ref - 1.0, atol=2e-2, rtol=1e-4)
+
+
 def test_gemm_deterministic():
     from verl_b200.ops import gemm
 

@@ -18,6 +18,7 @@
 // gradient K-major/MN-major, the weight gradient MN-major/MN-major; no transposes are
 // materialised.
 #include "common.cuh"
+#include <cstdlib>
 #include "host_utils.h"
 
 namespace vb {
@@ -565,6 +566,269 @@ __global__ void lse_merge_kernel(const float4* __restrict__ partials, int M, int
   if (mean_out) mean_out[row] = mean;
 }
 
+// ---------------------------------------------------------------------------------------------------
+// CTA-pair GEMM (cta_group::2): a cluster of two CTAs owns a 256 x 256 output tile. Each CTA stages its own
+// 128 rows of A and its own 128 of the 256 columns' rows of B (32 KB per stage instead of 48 KB, six stages),
+// CTA 0 issues one 256 x 256 x 16 MMA for both, and each CTA drains its 128 accumulator rows from its own TMEM.
+// Barrier protocol (all barriers at the same shared-memory offset in both CTAs):
+//   full[s]    lives in CTA 0, count 2: each CTA's producer arrives with its own byte count; both CTAs' TMA
+//              loads report their bytes there
+//   empty[s]   CTA 0: arrived by tcgen05.commit; CTA 1: arrived by CTA 0's producer after it saw that commit
+//   tfull[a]   CTA 0: tcgen05.commit after the last k block; CTA 1: relayed by CTA 0's first epilogue warp
+//   tempty[a]  lives in CTA 0, count 8: the four epilogue warps of both CTAs
+// No load in this kernel is shared between CTAs: every CTA fetches exactly the bytes it owns.
+constexpr int P_BN = 256;
+constexpr int P_STAGES = 6;
+constexpr int P_A_BYTES = BM * BK * 2;          // 16 KB
+constexpr int P_B_BYTES = (P_BN / 2) * BK * 2;  // 16 KB
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_BAR_OFFSET = P_STAGES * P_STAGE_BYTES;
+constexpr int P_DYN_BYTES = P_BAR_OFFSET + (2 * P_STAGES + 4) * 8 + 16 + 1024;
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smemA = smem;
+  uint8_t* smemB = smem + P_STAGES * P_A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + P_BAR_OFFSET);
+  uint64_t* empty = full + P_STAGES;
+  uint64_t* tfull = empty + P_STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 issues the MMAs
+  const int num_m2 = (p.M + 2 * BM - 1) / (2 * BM);
+  const int num_n = (p.N + P_BN - 1) / P_BN;
+  const int num_units = num_m2 * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int first_unit = (int)cluster_id_x();
+  const int unit_stride = (int)cluster_nctaid_x();
+  // unit -> (256-row block, 256-column block); row blocks grouped so that neighbouring clusters share B in L2
+  auto unit_coords = [&](int u, int& m2, int& nb) {
+    const int per_group = GROUP_M * num_n;
+    const int g = u / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsize = min(num_m2 - first_m, GROUP_M);
+    const int r = u - g * per_group;
+    m2 = first_m + r % gsize;
+    nb = r / gsize;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&full[s], 2);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 2 * P_BN);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised and both allocations are done
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int s = 0;
+      uint32_t phase = 0;
+      int round = 0;
+      bool ok = true;
+      for (int u = first_unit; ok && u < num_units; u += unit_stride) {
+        int m2, nb;
+        unit_coords(u, m2, nb);
+        const int m0 = (2 * m2 + (int)rank) * BM;
+        const int n0 = nb * P_BN + (int)rank * (P_BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (*abort_flag || !mbar_wait(&empty[s], phase ^ 1)) {
+            report_error(p.status, ERR_WAIT_EMPTY, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          // CTA 0 saw the commit that frees stage s in both CTAs: pass it on (not in the first round, where
+          // nothing had to be freed)
+          if (rank == 0 && round > 0) mbar_arrive_cluster(map_to_cta(smem_u32(&empty[s]), 1));
+          const uint32_t full0 = map_to_cta(smem_u32(&full[s]), 0);
+          mbar_arrive_expect_tx_cluster(full0, P_STAGE_BYTES);
+          uint8_t* a_dst = smemA + s * P_A_BYTES;
+          uint8_t* b_dst = smemB + s * P_B_BYTES;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(a_dst + j * (BK * 128), &tmA, full0, m0 + j * 64, kb * BK);
+          } else {
+            tma_load_2d_pair(a_dst, &tmA, full0, kb * BK, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < P_BN / 2 / 64; ++j)
+              tma_load_2d_pair(b_dst + j * (BK * 128), &tmB, full0, n0 + j * 64, kb * BK);
+          } else {
+            tma_load_2d_pair(b_dst, &tmB, full0, kb * BK, n0);
+          }
+          if (++s == P_STAGES) {
+            s = 0;
+            phase ^= 1;
+            ++round;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (CTA 0 only) --------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc(1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0, 2 * BM, P_BN);
+      int s = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int u = first_unit; ok && u < num_units; u += unit_stride) {
+        if (*abort_flag || !mbar_wait(&tempty[acc], acc_phase ^ 1)) {
+          report_error(p.status, ERR_WAIT_TMEM_EMPTY, u);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * P_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (*abort_flag || !mbar_wait(&full[s], phase)) {
+            report_error(p.status, ERR_WAIT_FULL, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smemA + s * P_A_BYTES);
+          const uint32_t b_addr = smem_u32(smemB + s * P_B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t a_desc = A_MN ? umma_smem_desc(a_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                                         : umma_smem_desc(a_addr + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t b_desc = B_MN ? umma_smem_desc(b_addr + k * (UMMA_K * 128), BK * 128, 1024)
+                                         : umma_smem_desc(b_addr + k * (UMMA_K * 2), 16, 1024);
+            tc_mma_f16_pair(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit_pair(&empty[s]);
+          if (++s == P_STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        tc_commit_pair(&tfull[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ----------------------------------
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int u = first_unit; ok && u < num_units; u += unit_stride) {
+      int m2, nb;
+      unit_coords(u, m2, nb);
+      const int row = (2 * m2 + (int)rank) * BM + row_in_tile;
+      const bool row_ok = row < p.M;
+      if (*abort_flag || !mbar_wait(&tfull[acc], acc_phase)) {
+        report_error(p.status, ERR_WAIT_TMEM_FULL, u);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      if (rank == 0 && warp == 2 && lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tfull[acc]), 1));
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * P_BN;
+#pragma unroll 1
+      for (int c = 0; c < P_BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = nb * P_BN + c * 32;
+        if (row_ok && col0 < p.N) epi_store_chunk(p, row, col0, r);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the other CTA may still read this CTA's shared memory or signal its barriers
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 2 * P_BN);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_gemm_pair(const void* A, const void* B, long long lda, long long ldb, const GemmParams& p,
+                            cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (A_MN) rc = vb_make_tmap_2d(&tmA, A, 2, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)lda * 2, 64, BK);
+  else rc = vb_make_tmap_2d(&tmA, A, 2, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)lda * 2, BK, BM);
+  if (rc) return rc;
+  if (B_MN) rc = vb_make_tmap_2d(&tmB, B, 2, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)ldb * 2, 64, BK);
+  else rc = vb_make_tmap_2d(&tmB, B, 2, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldb * 2, BK, P_BN / 2);
+  if (rc) return rc;
+  auto kern = gemm_pair_kernel<A_MN, B_MN>;
+  static int max_clusters = 0;  // clusters of two that the device can hold at once (per instantiation)
+  if (max_clusters == 0) {
+    VB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_DYN_BYTES));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (vb_num_sms() / 2));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = P_DYN_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = -1;
+    }
+    max_clusters = n;
+  }
+  if (max_clusters < 0) return -7;
+  const int units = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + P_BN - 1) / P_BN);
+  if (units <= 0) return 0;
+  const int clusters = units < max_clusters ? units : max_clusters;
+  kern<<<2 * clusters, NUM_THREADS, P_DYN_BYTES, stream>>>(tmA, tmB, p);
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
 template <int BN, bool A_MN, bool B_MN, int EPI>
 static int launch_gemm(const void* A, const void* B, long long lda, long long ldb, const GemmParams& p,
                        cudaStream_t stream) {
@@ -641,6 +905,20 @@ extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void
 #undef VB_SPLITK
       }
     }
+  }
+  // Large problems: CTA pairs on 256 x 256 tiles (enough tiles to keep every pair busy for several rounds).
+  static const bool pair_enabled = []() {
+    const char* e = getenv("VERL_B200_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  if (pair_enabled && M >= 512 && N >= 512 && K >= 256 &&
+      (long long)((M + 255) / 256) * ((N + 255) / 256) >= vb_num_sms()) {
+    int rc;
+    if (!a_mn && !b_mn) rc = launch_gemm_pair<false, false>(A, B, lda, ldb, p, stream);
+    else if (!a_mn && b_mn) rc = launch_gemm_pair<false, true>(A, B, lda, ldb, p, stream);
+    else if (a_mn && b_mn) rc = launch_gemm_pair<true, true>(A, B, lda, ldb, p, stream);
+    else rc = launch_gemm_pair<true, false>(A, B, lda, ldb, p, stream);
+    if (rc != -7) return rc;  // -7: the device cannot co-schedule the pairs; use the single-CTA kernel
   }
   // Tile width: the widest BN that still yields about one tile per SM. Skinny problems (decode: M <= 128)
   // fall to BN = 64 / 32 so that the weight matrix is streamed by (nearly) all SMs.
