@@ -113,18 +113,19 @@ class PeerComm:
     def is_symmetric(self, t: torch.Tensor) -> bool:
         return any(a.offset_of(t) is not None for a in self.allocs)
 
-    def reserve_grad_buffers(self, numel: int):
-        """Two alternating fp32 buffers for per-unit gradients. While one is being reduced by slower peers the
-        next unit's backward writes the other; a buffer is reused only after a later reduce's entry barrier
-        proved that every peer finished reading it."""
-        if self._grad_bufs and self._grad_bufs[0].numel() >= numel:
+    def reserve_grad_buffers(self, numel: int, count: int = 2):
+        """Rotating fp32 buffers for per-unit gradients. While one is being reduced by slower peers the next
+        unit's backward writes another; the caller reuses a buffer only after a later reduce-scatter proved
+        that every peer finished reading it."""
+        if len(self._grad_bufs) >= count and self._grad_bufs[0].numel() >= numel:
             return
-        self._grad_bufs = [self.alloc(numel, torch.float32), self.alloc(numel, torch.float32)]
+        self._grad_bufs = [self.alloc(numel, torch.float32) for _ in range(count)]
+        self._grad_next = 0
 
     def grad_buffer(self, numel: int) -> torch.Tensor:
         assert self._grad_bufs and self._grad_bufs[0].numel() >= numel, "reserve_grad_buffers() first"
         buf = self._grad_bufs[self._grad_next][:numel]
-        self._grad_next ^= 1
+        self._grad_next = (self._grad_next + 1) % len(self._grad_bufs)
         buf.zero_()
         return buf
 

@@ -44,6 +44,9 @@ class ZeroUnit:
     full: Optional[torch.Tensor] = None  # gathered working-dtype buffer (None when released)
     full_grad: Optional[torch.Tensor] = None  # unit-sized fp32 gradient buffer during backward (W > 1)
     gather_count: int = 0
+    index: int = 0  # position in ZeroShardedParams.units
+    ready: Optional[object] = None  # event of the gather that fills ``full`` on the communication stream
+    grad_seq: int = -1  # sequence number of this backward's gradient buffer / reduce-scatter
 
 
 class ZeroShardedParams:
@@ -79,14 +82,20 @@ class ZeroShardedParams:
             u.shard = u.padded // self.world
             u.offset = off
             off += u.shard
+            u.index = len(self.units)
             self.units.append(u)
         self.total_shard = off
+        # Gathers of the next unit and reduce-scatters of the previous one run on their own stream, under the
+        # compute of the current unit (peer-memory collectives only).
+        self.comm_stream = torch.cuda.Stream(device=self.device) if (comm is not None and self.world > 1) else None
+        self._rs_done: dict = {}
+        self._grad_seq = 0
         dev = self.device
         if comm is not None and self.world > 1:
             # peers read this shard directly over NVLink: it lives in symmetric memory
             self.shard16 = comm.alloc(off, work_dtype)
             if trainable:
-                comm.reserve_grad_buffers(max(u.padded for u in self.units))
+                comm.reserve_grad_buffers(max(u.padded for u in self.units), count=3)
         else:
             self.shard16 = torch.zeros(off, dtype=work_dtype, device=dev)
         if trainable:
@@ -136,21 +145,56 @@ class ZeroShardedParams:
                 del p.main_grad
 
     # ---------------------------------------------------------- gather / release
-    def gather(self, u: ZeroUnit, for_backward: bool = False):
+    def _issue_gather(self, u: ZeroUnit):
+        """Start the all-gather of ``u`` (on the communication stream when there is one)."""
+        full = torch.empty(u.padded, dtype=self.work_dtype, device=self.device)
+        src = self.shard16[u.offset : u.offset + u.shard]
+        if self.comm_stream is not None:
+            main = torch.cuda.current_stream(self.device)
+            self.comm_stream.wait_stream(main)  # the buffer is free and this rank's shard is final
+            with torch.cuda.stream(self.comm_stream):
+                self.comm.all_gather(full, src)
+                u.ready = self.comm_stream.record_event()
+        elif self.comm is not None:
+            self.comm.all_gather(full, src)
+        else:
+            dist.all_gather_into_tensor(full, src, group=self.group)
+        u.full = full
+
+    def _next_grad_buffer(self, u: ZeroUnit) -> torch.Tensor:
+        """Symmetric fp32 buffer for the unit's gradients. Three buffers rotate: peers read buffer n during
+        reduce-scatter n, and this rank knows they are done once its own reduce-scatter n+1 has completed
+        (its entry barrier proves that every peer has started n+1, hence finished n)."""
+        n = self._grad_seq
+        self._grad_seq += 1
+        u.grad_seq = n
+        ev = self._rs_done.pop(n - 2, None)
+        if ev is not None:
+            torch.cuda.current_stream(self.device).wait_event(ev)
+        return self.comm.grad_buffer(u.padded)
+
+    def wait_comm(self):
+        """Make the current stream wait for every collective issued on the communication stream."""
+        if self.comm_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+            self._rs_done.clear()
+
+    def gather(self, u: ZeroUnit, for_backward: bool = False, prefetch: bool = True):
         u.gather_count += 1
         if self.world == 1:
             return
         if u.full is None:
-            full = torch.empty(u.padded, dtype=self.work_dtype, device=self.device)
-            src = self.shard16[u.offset : u.offset + u.shard]
-            if self.comm is not None:
-                self.comm.all_gather(full, src)
-            else:
-                dist.all_gather_into_tensor(full, src, group=self.group)
-            u.full = full
+            self._issue_gather(u)
+        if u.ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(u.ready)
+            u.ready = None
+        if prefetch and self.comm_stream is not None:
+            j = u.index + (-1 if for_backward else 1)
+            if 0 <= j < len(self.units) and self.units[j].full is None:
+                self._issue_gather(self.units[j])
         if for_backward and self.trainable and u.full_grad is None:
             if self.comm is not None:
-                u.full_grad = self.comm.grad_buffer(u.padded)
+                u.full_grad = self._next_grad_buffer(u)
             else:
                 u.full_grad = torch.zeros(u.padded, dtype=torch.float32, device=self.device)
         self._bind(u, u.full, u.full_grad if for_backward else None)
@@ -177,7 +221,12 @@ class ZeroShardedParams:
         if self.world == 1 or not self.trainable or u.full_grad is None:
             return
         dst = self.grad[u.offset : u.offset + u.shard]
-        if self.comm is not None:
+        if self.comm_stream is not None:
+            self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.comm_stream):
+                self.comm.reduce_scatter_add(dst, u.full_grad)
+                self._rs_done[u.grad_seq] = self.comm_stream.record_event()
+        elif self.comm is not None:
             self.comm.reduce_scatter_add(dst, u.full_grad)
         elif dist.get_backend(self.group) == "gloo":
             dist.all_reduce(u.full_grad, group=self.group)
@@ -238,6 +287,7 @@ class ZeroShardedParams:
 
     def zero_grad(self):
         if self.trainable:
+            self.wait_comm()
             self.grad.zero_()
 
     # ------------------------------------------------------------ sharded state io

@@ -251,6 +251,7 @@ class NativeEngine(BaseEngine):
         wd = float(_cfg(oc, "weight_decay", 0.01))
         eps = float(_cfg(oc, "eps", 1e-8))
         self.step_count += 1
+        z.wait_comm()  # the last reduce-scatters run on the communication stream
         if self.device.type == "cuda":
             self._sumsq.zero_()
             ops.sumsq_into(z.grad, self._sumsq)
