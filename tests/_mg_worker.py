@@ -18,9 +18,11 @@ def check_comm(comm, rank, world, dev):
         src = comm.alloc(n, torch.bfloat16)
         src.copy_((torch.arange(n, device=dev) % 251 + rank * 7 + it).to(torch.bfloat16))
         out = torch.empty(n * world, dtype=torch.bfloat16, device=dev)
-        comm.all_gather(out, src)
         exp = torch.cat([(torch.arange(n, device=dev) % 251 + r * 7 + it).to(torch.bfloat16) for r in range(world)])
-        assert torch.equal(out, exp), f"all_gather mismatch (iteration {it})"
+        for ce in (False, True):  # SM-load kernel and copy-engine variant
+            out.zero_()
+            comm.all_gather(out, src, copy_engine=ce)
+            assert torch.equal(out, exp), f"all_gather mismatch (iteration {it}, copy_engine={ce})"
 
         shard = 1024 * 5 + 4 * it
         full = comm.alloc(shard * world, torch.float32)

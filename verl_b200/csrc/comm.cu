@@ -121,17 +121,36 @@ __global__ void peer_reduce_scatter_add_kernel(PeerPtrs fulls, PeerPtrs pads, lo
                                                float4* __restrict__ dst, long long shard4, float scale, int rank,
                                                int world, int channel, uint32_t epoch, uint32_t* gate, int* status) {
   if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
+  constexpr int U = 4;  // independent 16-byte loads in flight per thread and peer
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < shard4; i += stride) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const long long base = full_off4 + (long long)rank * shard4;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < shard4; i0 += stride * U) {
+    float4 acc[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int q = 0; q < world; ++q) {
       const int p = (rank + q) % world;
-      const float4 v = *(reinterpret_cast<const float4*>(fulls.p[p]) + full_off4 + (long long)rank * shard4 + i);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      const float4* src = reinterpret_cast<const float4*>(fulls.p[p]) + base;
+      float4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        v[u] = i < shard4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
+      }
     }
-    float4 d = dst[i];
-    d.x += scale * acc.x; d.y += scale * acc.y; d.z += scale * acc.z; d.w += scale * acc.w;
-    dst[i] = d;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < shard4) {
+        float4 d = dst[i];
+        d.x += scale * acc[u].x; d.y += scale * acc[u].y; d.z += scale * acc[u].z; d.w += scale * acc[u].w;
+        dst[i] = d;
+      }
+    }
   }
 }
 
@@ -142,15 +161,28 @@ __global__ void nvls_reduce_scatter_add_kernel(const float* mc_base, PeerPtrs pa
   if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const float4* src = reinterpret_cast<const float4*>(mc_base) + full_off4 + (long long)rank * shard4;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < shard4; i += stride) {
-    float4 acc;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(acc.x), "=f"(acc.y), "=f"(acc.z), "=f"(acc.w)
-                 : "l"(src + i)
-                 : "memory");
-    float4 d = dst[i];
-    d.x += scale * acc.x; d.y += scale * acc.y; d.z += scale * acc.z; d.w += scale * acc.w;
-    dst[i] = d;
+  constexpr int U = 4;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < shard4; i0 += stride * U) {
+    float4 acc[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < shard4)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(acc[u].x), "=f"(acc[u].y), "=f"(acc[u].z), "=f"(acc[u].w)
+                     : "l"(src + i)
+                     : "memory");
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < shard4) {
+        float4 d = dst[i];
+        d.x += scale * acc[u].x; d.y += scale * acc[u].y; d.z += scale * acc[u].z; d.w += scale * acc[u].w;
+        dst[i] = d;
+      }
+    }
   }
 }
 
@@ -172,7 +204,20 @@ __global__ void peer_segment_copy_kernel(PeerPtrs srcs, PeerPtrs pads, const Seg
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(srcs.p[sg.src_rank]) + sg.src_off);
     uint4* dst = reinterpret_cast<uint4*>(dst_base + sg.dst_off);
     const long long n16 = sg.nbytes >> 4;
-    for (long long i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+    constexpr int U = 4;
+    for (long long i0 = threadIdx.x; i0 < n16; i0 += (long long)blockDim.x * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + (long long)u * blockDim.x;
+        if (i < n16) v[u] = src[i];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + (long long)u * blockDim.x;
+        if (i < n16) dst[i] = v[u];
+      }
+    }
   }
 }
 
@@ -213,13 +258,34 @@ extern "C" int vb_peer_all_gather(const void* const* srcs, const void* const* pa
   return (int)cudaGetLastError();
 }
 
+// The same all-gather with the payload moved by the copy engines: a one-block kernel does the cross-rank
+// handshake (every rank's shard is final), then one asynchronous copy per peer pulls the shards over NVLink
+// without occupying SMs, so a gather issued on a side stream does not slow the GEMMs it overlaps.
+extern "C" int vb_peer_all_gather_ce(const void* const* srcs, const void* const* pads, long long src_off_bytes,
+                                     void* out, long long shard_bytes, int rank, int world, int channel,
+                                     unsigned epoch, int* status, cudaStream_t stream) {
+  if (world > MAX_RANKS) return -3;
+  peer_barrier_kernel<<<1, 32, 0, stream>>>(make_ptrs(pads, world), rank, world, channel, epoch, status);
+  vb_count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  for (int q = 0; q < world; ++q) {
+    const int p = (rank + 1 + q) % world;  // own shard last
+    e = cudaMemcpyAsync(reinterpret_cast<uint8_t*>(out) + (long long)p * shard_bytes,
+                        reinterpret_cast<const uint8_t*>(srcs[p]) + src_off_bytes, (size_t)shard_bytes,
+                        cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
 extern "C" int vb_peer_reduce_scatter_add(const void* const* fulls, const void* const* pads, const void* mc_base,
                                           long long full_off_bytes, float* dst, long long shard_floats, float scale,
                                           int rank, int world, int channel, unsigned epoch, unsigned* gate, int* status,
                                           cudaStream_t stream) {
   if (world > MAX_RANKS || (full_off_bytes & 15) || (shard_floats & 3) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -3;
   const long long shard4 = shard_floats >> 2;
-  long long blocks = (shard4 + 255) / 256;
+  long long blocks = (shard4 + 1023) / 1024;
   const int cap = vb_num_sms();
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;

@@ -34,6 +34,7 @@ def _bind():
     lib.vb_peer_max_ranks.argtypes, lib.vb_peer_max_ranks.restype = [], I
     lib.vb_peer_barrier.argtypes, lib.vb_peer_barrier.restype = [P, I, I, I, U, P, P], I
     lib.vb_peer_all_gather.argtypes, lib.vb_peer_all_gather.restype = [P, P, L, P, L, I, I, I, U, P, P, P], I
+    lib.vb_peer_all_gather_ce.argtypes, lib.vb_peer_all_gather_ce.restype = [P, P, L, P, L, I, I, I, U, P, P], I
     lib.vb_peer_reduce_scatter_add.argtypes = [P, P, P, L, P, L, F, I, I, I, U, P, P, P]
     lib.vb_peer_reduce_scatter_add.restype = I
     lib.vb_peer_segment_copy.argtypes, lib.vb_peer_segment_copy.restype = [P, P, P, I, P, I, I, I, U, P, P, P], I
@@ -145,11 +146,22 @@ class PeerComm:
                                       self._epoch(self.CH_BARRIER), self._status(), _lib.stream())
         _lib.check(rc, "vb_peer_barrier")
 
-    def all_gather(self, out: torch.Tensor, src: torch.Tensor):
-        """out[r * n : (r+1) * n] = rank r's ``src`` (n = src.numel()); ``src`` must be symmetric memory."""
+    def all_gather(self, out: torch.Tensor, src: torch.Tensor, copy_engine: Optional[bool] = None):
+        """out[r * n : (r+1) * n] = rank r's ``src`` (n = src.numel()); ``src`` must be symmetric memory.
+
+        ``copy_engine`` (default: payloads of 1 MiB and more) moves the shards with asynchronous peer copies
+        after a one-block handshake kernel instead of with SM loads."""
         a, off = self._find(src)
         nbytes = src.numel() * src.element_size()
         assert out.numel() * out.element_size() == nbytes * self.world
+        if copy_engine is None:
+            copy_engine = nbytes >= (1 << 20)
+        if copy_engine:
+            rc = self.lib.vb_peer_all_gather_ce(a.ptrs, self.pad_alloc.ptrs, off, out.data_ptr(), nbytes, self.rank,
+                                                self.world, self.CH_GATHER, self._epoch(self.CH_GATHER), self._status(),
+                                                _lib.stream())
+            _lib.check(rc, "vb_peer_all_gather_ce")
+            return
         rc = self.lib.vb_peer_all_gather(a.ptrs, self.pad_alloc.ptrs, off, out.data_ptr(), nbytes, self.rank, self.world,
                                          self.CH_GATHER, self._epoch(self.CH_GATHER), self._gate(self.CH_GATHER),
                                          self._status(), _lib.stream())

@@ -552,6 +552,9 @@ class RayPPOTrainer:
             if cfg.trainer.get("balance_batch", True):
                 self._balance_batch(batch, metrics)
             batch.meta_info["global_token_num"] = torch.sum(batch.batch["attention_mask"], dim=-1).tolist()
+            # under an SPMD launch every rank drives the trainer on its own shard of the batch: the token list is
+            # already per rank and must not be divided by the world size again (MFU)
+            batch.meta_info["token_num_is_local"] = self.spmd
             batch.meta_info["temperature"] = cfg.actor_rollout_ref.rollout.temperature
 
             rc = cfg.algorithm.get("rollout_correction") or {}

@@ -276,7 +276,8 @@ class ActorRolloutRefWorker(_WorkerBase):
             from ..utils.flops_counter import FlopsCounter
 
             est, promised = FlopsCounter(self.model_config).estimate_flops(tokens, dt)
-            metrics["perf/mfu/actor"] = est * self.actor_cfg.ppo_epochs / promised / self.world
+            denom = 1 if data.meta_info.get("token_num_is_local") else self.world
+            metrics["perf/mfu/actor"] = est * self.actor_cfg.ppo_epochs / promised / denom
         return DataProto(meta_info={"metrics": metrics})
 
     @register(dispatch_mode=Dispatch.ONE_TO_ALL, blocking=False)
