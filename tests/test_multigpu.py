@@ -24,3 +24,11 @@ def test_two_ranks(what):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     _run(what, 2)
+
+
+@pytest.mark.parametrize("what", ["comm", "reshard", "zero"])
+def test_all_ranks(what):
+    n = torch.cuda.device_count()
+    if n <= 2:
+        pytest.skip("needs more than 2 GPUs")
+    _run(what, min(n, 8))

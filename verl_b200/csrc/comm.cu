@@ -116,41 +116,63 @@ __global__ void peer_all_gather_kernel(PeerPtrs srcs, PeerPtrs pads, long long s
 }
 
 // dst[i] += scale * sum_p full_p[rank*shard + i], i in [0, shard). fulls.p[r] = base of rank r's symmetric
-// gradient buffer (the unit's full gradient at float offset full_off). float4 granularity.
+// gradient buffer (the unit's full gradient at float offset full_off). float4 granularity. The loads of all
+// W peers (W = world size, compile time) are issued before the first add, so that one NVLink round trip covers
+// W * U * 16 bytes per thread.
+template <int W, int U>
 __global__ void peer_reduce_scatter_add_kernel(PeerPtrs fulls, PeerPtrs pads, long long full_off4,
                                                float4* __restrict__ dst, long long shard4, float scale, int rank,
                                                int world, int channel, uint32_t epoch, uint32_t* gate, int* status) {
   if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
-  constexpr int U = 4;  // independent 16-byte loads in flight per thread and peer
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long base = full_off4 + (long long)rank * shard4;
-  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < shard4; i0 += stride * U) {
-    float4 acc[U];
+  const float4* src[W];
 #pragma unroll
-    for (int u = 0; u < U; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int q = 0; q < world; ++q) {
-      const int p = (rank + q) % world;
-      const float4* src = reinterpret_cast<const float4*>(fulls.p[p]) + base;
-      float4 v[U];
+  for (int q = 0; q < W; ++q) src[q] = reinterpret_cast<const float4*>(fulls.p[(rank + q) % W]) + base;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < shard4; i0 += stride * U) {
+    float4 v[W][U];
+#pragma unroll
+    for (int q = 0; q < W; ++q) {
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long i = i0 + u * stride;
-        v[u] = i < shard4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
+        v[q][u] = i < shard4 ? src[q][i] : make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const long long i = i0 + u * stride;
       if (i < shard4) {
+        float4 acc = v[0][u];
+#pragma unroll
+        for (int q = 1; q < W; ++q) {
+          acc.x += v[q][u].x; acc.y += v[q][u].y; acc.z += v[q][u].z; acc.w += v[q][u].w;
+        }
         float4 d = dst[i];
-        d.x += scale * acc[u].x; d.y += scale * acc[u].y; d.z += scale * acc[u].z; d.w += scale * acc[u].w;
+        d.x += scale * acc.x; d.y += scale * acc.y; d.z += scale * acc.z; d.w += scale * acc.w;
         dst[i] = d;
       }
     }
+  }
+}
+
+// any world size (peers visited one after the other)
+__global__ void peer_reduce_scatter_add_generic_kernel(PeerPtrs fulls, PeerPtrs pads, long long full_off4,
+                                                       float4* __restrict__ dst, long long shard4, float scale,
+                                                       int rank, int world, int channel, uint32_t epoch,
+                                                       uint32_t* gate, int* status) {
+  if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < shard4; i += stride) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = 0; q < world; ++q) {
+      const int p = (rank + q) % world;
+      const float4 v = *(reinterpret_cast<const float4*>(fulls.p[p]) + full_off4 + (long long)rank * shard4 + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float4 d = dst[i];
+    d.x += scale * acc.x; d.y += scale * acc.y; d.z += scale * acc.z; d.w += scale * acc.w;
+    dst[i] = d;
   }
 }
 
@@ -286,7 +308,7 @@ extern "C" int vb_peer_reduce_scatter_add(const void* const* fulls, const void* 
   if (world > MAX_RANKS || (full_off_bytes & 15) || (shard_floats & 3) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -3;
   const long long shard4 = shard_floats >> 2;
   long long blocks = (shard4 + 1023) / 1024;
-  const int cap = vb_num_sms();
+  const int cap = 2 * vb_num_sms();  // all blocks must be co-resident with block 0: two small blocks per SM always fit
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   if (mc_base != nullptr) {
@@ -294,9 +316,13 @@ extern "C" int vb_peer_reduce_scatter_add(const void* const* fulls, const void* 
         reinterpret_cast<const float*>(mc_base), make_ptrs(pads, world), full_off_bytes >> 4,
         reinterpret_cast<float4*>(dst), shard4, scale, rank, world, channel, epoch, gate, status);
   } else {
-    peer_reduce_scatter_add_kernel<<<(int)blocks, 256, 0, stream>>>(
-        make_ptrs(fulls, world), make_ptrs(pads, world), full_off_bytes >> 4, reinterpret_cast<float4*>(dst), shard4,
-        scale, rank, world, channel, epoch, gate, status);
+#define VB_RS_ARGS make_ptrs(fulls, world), make_ptrs(pads, world), full_off_bytes >> 4, reinterpret_cast<float4*>(dst), \
+                   shard4, scale, rank, world, channel, epoch, gate, status
+    if (world == 2) peer_reduce_scatter_add_kernel<2, 4><<<(int)blocks, 256, 0, stream>>>(VB_RS_ARGS);
+    else if (world == 4) peer_reduce_scatter_add_kernel<4, 2><<<(int)blocks, 256, 0, stream>>>(VB_RS_ARGS);
+    else if (world == 8) peer_reduce_scatter_add_kernel<8, 2><<<(int)blocks, 256, 0, stream>>>(VB_RS_ARGS);
+    else peer_reduce_scatter_add_generic_kernel<<<(int)blocks, 256, 0, stream>>>(VB_RS_ARGS);
+#undef VB_RS_ARGS
   }
   vb_count_launch();
   return (int)cudaGetLastError();
