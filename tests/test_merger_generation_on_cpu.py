@@ -1,0 +1,40 @@
+"""Model merger CLI, offline generation and offline evaluation on CPU."""
+
+import json
+
+import torch
+
+
+def test_merge_checkpoint_roundtrip(tmp_path):
+    from verl_b200.model_merger import merge_checkpoint, test_merged
+    from verl_b200.model_merger.merger import main as merger_main
+    from verl_b200.models import preset
+    from verl_b200.models.hf_io import load_hf_checkpoint
+    from verl_b200.workers.engine.native import NativeEngine
+
+    cfg = preset("tiny-qwen2")
+    eng = NativeEngine(cfg, None, {"lr": 1e-3}, device="cpu", seed=5).initialize()
+    ref = {k: v.detach().clone() for k, v in eng.model.named_parameters()}
+    eng.save_checkpoint(str(tmp_path / "actor"), global_step=1)
+    merge_checkpoint(str(tmp_path / "actor"), str(tmp_path / "hf"), dtype=torch.float32)
+    cfg2, sd = load_hf_checkpoint(tmp_path / "hf")
+    assert cfg2.hidden_size == cfg.hidden_size
+    for k, v in ref.items():
+        torch.testing.assert_close(sd[k].float(), v.float())
+    test_merged(str(tmp_path / "actor"), str(tmp_path / "hf"))
+    merger_main(["merge", "--backend", "fsdp", "--local_dir", str(tmp_path / "actor"), "--target_dir", str(tmp_path / "hf2")])
+    merger_main(["test", "--backend", "fsdp", "--local_dir", str(tmp_path / "actor"), "--test_hf_dir", str(tmp_path / "hf2")])
+
+
+def test_generation_and_eval(tmp_path):
+    from verl_b200.trainer.main_eval import main as eval_main
+    from verl_b200.trainer.main_generation import main as gen_main
+
+    rows = [{"prompt": "1 2 3", "data_source": "openai/gsm8k", "reward_model": {"ground_truth": "7"}} for _ in range(3)]
+    (tmp_path / "p.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    gen_main(["model.path=preset:tiny-qwen2", f"data.path={tmp_path}/p.jsonl", f"data.output_path={tmp_path}/o.jsonl",
+              "rollout.n=2", "rollout.response_length=8", "rollout.prompt_length=32", "trainer.device=cpu",
+              "rollout.max_num_seqs=8", "rollout.max_num_batched_tokens=256"])
+    out = [json.loads(line) for line in (tmp_path / "o.jsonl").read_text().splitlines()]
+    assert len(out) == 3 and all(len(r["responses"]) == 2 for r in out)
+    eval_main([f"data.path={tmp_path}/o.jsonl"])

@@ -1,0 +1,67 @@
+"""SFT trainer on CPU: loss goes down on a tiny model, checkpoints resume, datasets build the right loss masks."""
+
+import json
+import os
+
+import torch
+
+from verl_b200.utils.config import compose
+from verl_b200.utils.tokenizer import IntTokenizer
+
+
+def _config(tmp_path, **over):
+    ov = [
+        "model.path=preset:tiny-qwen2", "data.train_files=synthetic:64:24:48:250:1", "data.val_files=synthetic:8:24:48:250:2",
+        "data.train_batch_size=8", "data.micro_batch_size_per_gpu=4", "data.max_token_len_per_gpu=128", "data.max_length=48",
+        "data.multiturn=false", "data.pad_mode=right", "optim.lr=3e-3", "trainer.total_epochs=1", "trainer.total_training_steps=6",
+        "trainer.device=cpu", f"trainer.default_local_dir={tmp_path}/ckpt", "trainer.save_freq=3", "trainer.test_freq=3",
+        "trainer.logger=[console]",
+    ] + [f"{k}={v}" for k, v in over.items()]
+    return compose("sft_trainer", ov)
+
+
+def test_sft_loss_decreases_and_resumes(tmp_path):
+    from verl_b200.trainer.sft_trainer import SFTTrainer
+
+    cfg = _config(tmp_path)
+    tr = SFTTrainer(cfg, tokenizer=IntTokenizer(256))
+    losses = []
+    for step, (_, idx) in enumerate(tr._batches(0)):
+        from verl_b200.utils.dataset.sft_dataset import sft_collate_fn
+
+        m = tr.train_step(sft_collate_fn([tr.train_dataset[i] for i in idx]))
+        losses.append(m["train/loss"])
+        tr.global_step += 1
+        if step == 2:
+            tr.save_checkpoint()
+            v = tr.validate()
+            assert v["val/loss"] > 0
+    assert losses[-1] < losses[0]
+    # a new trainer picks up the step-3 checkpoint and reproduces the weights saved there
+    tr2 = SFTTrainer(cfg, tokenizer=IntTokenizer(256))
+    assert tr2.global_step == 3
+    out = tr2.fit()
+    assert tr2.global_step == 6 and "train/loss" in out
+
+
+def test_sft_dataset_masks(tmp_path):
+    from verl_b200.utils.dataset.sft_dataset import MultiTurnSFTDataset, SFTDataset
+
+    tok = IntTokenizer(512)
+    rows = [{"prompt": "1 2 3", "response": "4 5", "messages": [{"role": "user", "content": "1 2 3"},
+                                                                 {"role": "assistant", "content": "4 5"},
+                                                                 {"role": "user", "content": "6"},
+                                                                 {"role": "assistant", "content": "7 8 9"}]}]
+    f = tmp_path / "d.jsonl"
+    f.write_text("\n".join(json.dumps(r) for r in rows))
+    ds = SFTDataset(str(f), tok, {"max_length": 64, "pad_mode": "right", "truncation": "right"})
+    it = ds[0]
+    n = int(it["attention_mask"].sum())
+    assert it["input_ids"].shape == (64,) and it["loss_mask"][n - 1] == 0
+    # the last prompt position predicts the first response token
+    first = int(torch.nonzero(it["loss_mask"])[0])
+    assert it["loss_mask"][first:n - 1].all() and not it["loss_mask"][:first].any()
+    mt = MultiTurnSFTDataset(str(f), tok, {"max_length": 128, "pad_mode": "no_padding"})
+    it = mt[0]
+    assert it["input_ids"].numel() == it["loss_mask"].numel() < 128
+    assert 0 < int(it["loss_mask"].sum()) < it["loss_mask"].numel()

@@ -51,16 +51,19 @@ def create_rl_sampler(data_config, dataset):
     return SequentialSampler(dataset)
 
 
-def build_tokenizer(config):
-    """HF tokenizer of ``model.path`` when it is a directory with tokenizer files; integer tokenizer for presets."""
+def build_tokenizer(config, model_config=None):
+    """HF tokenizer of ``model.path`` when it is a directory with tokenizer files; integer tokenizer for presets.
+    ``config`` is either the whole trainer config or a model section (``path`` / ``tokenizer_path``)."""
     from ..utils.tokenizer import IntTokenizer, hf_tokenizer
     from ..workers.engine_workers import resolve_model_config
 
-    path = os.path.expanduser(str(config.actor_rollout_ref.model.path))
+    model = config.actor_rollout_ref.model if "actor_rollout_ref" in config else config
+    trust = (config.get("data") or {}).get("trust_remote_code", False) if "actor_rollout_ref" in config else model.get(
+        "trust_remote_code", False)
+    path = os.path.expanduser(str(model.path))
     if os.path.isdir(path) and any(os.path.exists(os.path.join(path, f)) for f in ("tokenizer.json", "tokenizer_config.json")):
-        return hf_tokenizer(config.actor_rollout_ref.model.get("tokenizer_path") or path,
-                            trust_remote_code=config.data.get("trust_remote_code", False))
-    mc, _ = resolve_model_config(config.actor_rollout_ref.model)
+        return hf_tokenizer(model.get("tokenizer_path") or path, trust_remote_code=trust)
+    mc = model_config if model_config is not None else resolve_model_config(model)[0]
     return IntTokenizer(mc.vocab_size, eos_token_id=mc.eos_token_id if mc.eos_token_id is not None else 2)
 
 

@@ -324,6 +324,15 @@ def compose(config_name: str, overrides: Optional[Iterable[str]] = None, config_
     return cfg
 
 
+def compose_from_dict(defaults: dict, overrides: Optional[Iterable[str]] = None, resolve_interpolations: bool = True) -> ConfigDict:
+    """Config for small entry points that ship their defaults as a dict: copy, apply ``a.b=c`` overrides, resolve."""
+    import copy
+
+    cfg = apply_overrides(copy.deepcopy(defaults), list(overrides or []))
+    cfg = to_config(cfg)
+    return resolve(cfg) if resolve_interpolations else cfg
+
+
 def _is_choice(group_dir: Path, val: str) -> bool:
     return any((group_dir / (val + ext)).is_file() for ext in (".yaml", ".yml"))
 
