@@ -374,3 +374,65 @@ def test_paged_decode_attention(B, Hq, Hk, D, bs, maxlen):
             out = ops.paged_decode_attention(q, kc, vc, table, lens.cuda(), num_splits=splits, impl=impl)
             assert _lib.read_status("cuda")[0] == 0
             _bf16_close(out, ref, ulps=4)
+
+
+def _attn_ref(q, k, v, cu, causal, scale):
+    """fp32 reference, one sequence at a time. Returns (out [T,Hq,D], lse [Hq,T])."""
+    T, Hq, D = q.shape
+    G = Hq // k.shape[1]
+    out = torch.empty(T, Hq, D, device=q.device)
+    lse = torch.empty(Hq, T, device=q.device)
+    b = cu.tolist()
+    for s, e in zip(b[:-1], b[1:]):
+        qs = q[s:e].float().transpose(0, 1)
+        ks = k[s:e].float().repeat_interleave(G, dim=1).transpose(0, 1)
+        vs = v[s:e].float().repeat_interleave(G, dim=1).transpose(0, 1)
+        sc = qs @ ks.transpose(1, 2) * scale
+        if causal:
+            n = e - s
+            sc = sc.masked_fill(torch.triu(torch.ones(n, n, device=q.device, dtype=torch.bool), 1), float("-inf"))
+        lse[:, s:e] = torch.logsumexp(sc, -1)
+        out[s:e] = (torch.softmax(sc, -1) @ vs).transpose(0, 1)
+    return out, lse
+
+
+@pytest.mark.parametrize("lens,Hq,Hk,causal", [([300, 77, 512, 129], 28, 4, True), ([1, 128, 640], 8, 8, True),
+                                               ([1000, 333], 16, 2, False), ([2048], 4, 4, True)])
+def test_flash_attention_fwd(lens, Hq, Hk, causal):
+    from verl_b200.ops import _lib
+    from verl_b200.ops.attention import flash_fwd
+
+    torch.manual_seed(11)
+    D, T = 128, sum(lens)
+    # q / k / v as views of one fused buffer (token stride (Hq + 2 Hk) * D), the way the model produces them
+    qkv = torch.randn(T, (Hq + 2 * Hk) * D, device="cuda").bfloat16()
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D : (Hq + Hk) * D].view(T, Hk, D)
+    v = qkv[:, (Hq + Hk) * D :].view(T, Hk, D)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    scale = D ** -0.5
+    out, lse = flash_fwd(q, k, v, cu, max(lens), causal, scale)
+    assert _lib.read_status("cuda")[0] == 0
+    ref, ref_lse = _attn_ref(q, k, v, cu, causal, scale)
+    _bf16_close(out, ref, ulps=4)
+    torch.testing.assert_close(lse, ref_lse, atol=2e-3, rtol=1e-4)
+
+
+def test_flash_attention_autograd_matches_reference():
+    from verl_b200 import ops
+
+    torch.manual_seed(12)
+    lens, Hq, Hk, D = [200, 131, 64], 8, 2, 128
+    T = sum(lens)
+    q = torch.randn(T, Hq, D, device="cuda").bfloat16().requires_grad_(True)
+    k = torch.randn(T, Hk, D, device="cuda").bfloat16().requires_grad_(True)
+    v = torch.randn(T, Hk, D, device="cuda").bfloat16().requires_grad_(True)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    do = torch.randn(T, Hq, D, device="cuda").bfloat16()
+    ops.attention_varlen(q, k, v, cu, max(lens), causal=True, impl="native").backward(do)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref, _ = _attn_ref(qr, kr, vr, cu, True, D ** -0.5)
+    ref.backward(do.float())
+    for got, want in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
+        err = (got.float() - want).abs().max().item()
+        assert err <= 2e-2 * max(1.0, want.abs().max().item()), err

@@ -1,9 +1,11 @@
 """Attention entry points.
 
 * :func:`attention_varlen` — causal GQA attention over packed (remove-padding) sequences for
-  training and prefill. On CUDA this currently calls the ``flash_attn`` varlen kernels (library
-  code, as the reference does through HF ``attn_implementation=flash_attention_2``,
-  verl/workers/fsdp_workers.py:331); on CPU a per-sequence SDPA loop.
+  training and prefill. On CUDA the forward is this package's tcgen05 kernel (head_dim 128; every
+  no-grad pass — prefill, log-prob recomputation, the checkpointed forward — runs on it alone). The
+  backward still calls the ``flash_attn`` varlen backward (library code) with the ``out`` / ``lse`` that our
+  forward produced; other head dims use the library for both (the reference does so for everything through HF
+  ``attn_implementation=flash_attention_2``, verl/workers/fsdp_workers.py:331). CPU: per-sequence SDPA loop.
 * :func:`paged_decode_attention` / :func:`kv_cache_write` — the hand-written paged-KV decode
   path of the native rollout engine.
 """
@@ -27,12 +29,67 @@ def _flash_varlen():
     return _flash
 
 
+def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int,
+              causal: bool, scale: float, need_lse: bool = True):
+    """tcgen05 forward. q [T,Hq,128], k/v [T,Hk,128] bf16 with unit inner strides (views of a fused qkv buffer are
+    fine). Returns (out [T,Hq,128] bf16, lse [Hq,T] fp32 or None)."""
+    T, Hq, D = q.shape
+    Hk = k.shape[1]
+    for t in (q, k, v):
+        if t.stride(2) != 1 or t.stride(1) != D or t.dtype != torch.bfloat16:
+            raise ValueError("flash_fwd expects bf16 [T, H, 128] tensors with contiguous heads")
+    out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((Hq, T), dtype=torch.float32, device=q.device) if need_lse else None
+    rc = _lib.fn("vb_flash_fwd")(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
+                                 cu_seqlens.data_ptr(), cu_seqlens.numel() - 1, T, int(max_seqlen), Hq, Hk, float(scale),
+                                 int(causal), out.data_ptr(), out.stride(0), _lib.ptr(lse),
+                                 _lib.status_word(q.device).data_ptr(), _lib.stream())
+    _lib.check(rc, "vb_flash_fwd")
+    return out, lse
+
+
+class _FlashVarlenFn(torch.autograd.Function):
+    """Own forward; backward through the library's varlen backward kernel (same ``lse`` layout [Hq, T])."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale):
+        out, lse = flash_fwd(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens)
+        ctx.max_seqlen, ctx.causal, ctx.scale = max_seqlen, causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward  # library kernel
+
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+        dq, dk, dv = torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc)
+        _flash_attn_varlen_backward(dout.contiguous(), qc, kc, vc, out, lse, dq, dk, dv, cu, cu, ctx.max_seqlen,
+                                    ctx.max_seqlen, 0.0, ctx.scale, ctx.causal, -1, -1, 0.0, None, False, None)
+        return dq, dk, dv, None, None, None, None
+
+
+def _native_fwd_ok(q, k, v) -> bool:
+    D = q.shape[-1]
+    return (q.dtype == torch.bfloat16 and D == 128 and q.shape[1] % k.shape[1] == 0
+            and all(t.stride(2) == 1 and t.stride(1) == D and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v)))
+
+
 def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int,
-                     causal: bool = True, softmax_scale: float | None = None) -> torch.Tensor:
-    """q [T,Hq,D], k/v [T,Hk,D] packed; cu_seqlens int32 [B+1]. Returns [T,Hq,D]."""
+                     causal: bool = True, softmax_scale: float | None = None, impl: str = "auto") -> torch.Tensor:
+    """q [T,Hq,D], k/v [T,Hk,D] packed; cu_seqlens int32 [B+1]. Returns [T,Hq,D].
+    ``impl``: "native" forces the tcgen05 forward, "library" the flash_attn kernels, "auto" picks native when it applies."""
     D = q.shape[-1]
     scale = softmax_scale if softmax_scale is not None else D ** -0.5
     if q.is_cuda:
+        native = impl != "library" and _native_fwd_ok(q, k, v)
+        if impl == "native" and not native:
+            raise ValueError("native attention forward needs bf16, head_dim 128 and contiguous heads")
+        if native:
+            if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+                return _FlashVarlenFn.apply(q, k, v, cu_seqlens, int(max_seqlen), bool(causal), float(scale))
+            return flash_fwd(q, k, v, cu_seqlens, int(max_seqlen), bool(causal), float(scale), need_lse=False)[0]
         return _flash_varlen()(q, k, v, cu_seqlens, cu_seqlens, max_seqlen, max_seqlen, softmax_scale=scale,
                                causal=causal)
     out = torch.empty_like(q)

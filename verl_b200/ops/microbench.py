@@ -5,6 +5,7 @@
     python -m verl_b200.ops.microbench lmhead --t 8192
     python -m verl_b200.ops.microbench decode --batch 128 --ctx 900
     python -m verl_b200.ops.microbench decode_step --batch 128 --layers 4
+    python -m verl_b200.ops.microbench attn --batch 16 --ctx 1024 --library
 
 Every run prints one JSON line with the time per call, the achieved rate and (``--library``) the same
 measurement for the library kernel (cuBLAS through torch.matmul) as a yardstick. ``--iters 1 --warmup 1``
@@ -107,6 +108,29 @@ def bench_decode(a):
             "kv_bytes": byts, "us": round(us, 1), "gbs": round(byts / us / 1e3, 1)}
 
 
+def bench_attn(a):
+    """Varlen causal GQA attention forward (7B head layout), ours and (``--library``) flash_attn."""
+    from .attention import attention_varlen
+
+    dev = "cuda"
+    B, S, Hq, Hk, D = a.batch, a.ctx, a.hq, a.hk, 128
+    T = B * S
+    qkv = torch.randn(T, (Hq + 2 * Hk) * D, device=dev, dtype=torch.bfloat16)
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D : (Hq + Hk) * D].view(T, Hk, D)
+    v = qkv[:, (Hq + Hk) * D :].view(T, Hk, D)
+    cu = torch.arange(0, T + 1, S, dtype=torch.int32, device=dev)
+    flops = 4.0 * B * Hq * D * S * S / 2
+    out = {"kernel": "flash_fwd", "B": B, "S": S, "Hq": Hq, "Hk": Hk}
+    with torch.no_grad():
+        us = _time(lambda: attention_varlen(q, k, v, cu, S, causal=True, impl="native"), a.iters, a.warmup, graph=False)
+        out.update(us=round(us, 1), tflops=round(flops / us / 1e6, 1))
+        if a.library:
+            us2 = _time(lambda: attention_varlen(q, k, v, cu, S, causal=True, impl="library"), a.iters, a.warmup, graph=False)
+            out.update(library_us=round(us2, 1), library_tflops=round(flops / us2 / 1e6, 1))
+    return out
+
+
 def bench_decode_step(a):
     """One CUDA-graph decode step of the rollout engine on a model with the 7B layer shapes."""
     from ..models import preset
@@ -130,7 +154,7 @@ def bench_decode_step(a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "lmhead", "decode", "decode_step"])
+    ap.add_argument("what", choices=["gemm", "lmhead", "decode", "decode_step", "attn"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -150,7 +174,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--library", action="store_true")
     a = ap.parse_args(argv)
-    fn = {"gemm": bench_gemm, "lmhead": bench_lmhead, "decode": bench_decode, "decode_step": bench_decode_step}[a.what]
+    fn = {"gemm": bench_gemm, "lmhead": bench_lmhead, "decode": bench_decode, "decode_step": bench_decode_step, "attn": bench_attn}[a.what]
     print(json.dumps(fn(a)))
 
 
