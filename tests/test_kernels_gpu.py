@@ -436,3 +436,27 @@ def test_flash_attention_autograd_matches_reference():
     for got, want in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
         err = (got.float() - want).abs().max().item()
         assert err <= 2e-2 * max(1.0, want.abs().max().item()), err
+
+
+def test_flash_attention_fwd_with_cached_prefix():
+    """Queries are the last positions of a longer key stream (chunked prefill on top of cached context)."""
+    from verl_b200.ops.attention import flash_fwd
+
+    torch.manual_seed(13)
+    Hq, Hk, D = 8, 2, 128
+    lq, lk = [100, 1, 260], [100, 300, 700]
+    q = torch.randn(sum(lq), Hq, D, device="cuda").bfloat16()
+    k = torch.randn(sum(lk), Hk, D, device="cuda").bfloat16()
+    v = torch.randn(sum(lk), Hk, D, device="cuda").bfloat16()
+    cu_q = torch.tensor([0] + list(torch.tensor(lq).cumsum(0)), dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor([0] + list(torch.tensor(lk).cumsum(0)), dtype=torch.int32, device="cuda")
+    out, _ = flash_fwd(q, k, v, cu_q, max(lq), True, D ** -0.5, cu_seqlens_k=cu_k)
+    G = Hq // Hk
+    for b in range(len(lq)):
+        qs = q[cu_q[b]:cu_q[b + 1]].float().transpose(0, 1)
+        ks = k[cu_k[b]:cu_k[b + 1]].float().repeat_interleave(G, 1).transpose(0, 1)
+        vs = v[cu_k[b]:cu_k[b + 1]].float().repeat_interleave(G, 1).transpose(0, 1)
+        s = qs @ ks.transpose(1, 2) * D ** -0.5
+        mask = torch.arange(lk[b], device="cuda")[None, :] <= (torch.arange(lq[b], device="cuda")[:, None] + lk[b] - lq[b])
+        ref = (torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ vs).transpose(0, 1)
+        _bf16_close(out[cu_q[b]:cu_q[b + 1]], ref, ulps=4)

@@ -30,7 +30,8 @@ constexpr int FA_BAR_OFF = FA_RING_OFF + FA_SLOTS * FA_TILE;
 constexpr int FA_SMEM = FA_BAR_OFF + 16 * 8 + 16 + 1024;
 
 struct FaParams {
-  const int* cu_seqlens;  // [B + 1]
+  const int* cu_seqlens;  // [B + 1] query side
+  const int* cu_k;        // [B + 1] key side, or null when keys and queries are the same tokens
   __nv_bfloat16* out;
   long long out_stride;   // elements between tokens
   float* lse;             // [Hq, T]
@@ -73,8 +74,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int r0 = qblk * FA_BM;
   if (r0 >= seq_len) return;  // uniform for the CTA, before any barrier or allocation
   const int hk = hq / (p.Hq / p.Hk);
-  const int kv_chunks = (seq_len + FA_BN - 1) / FA_BN;
-  const int n_chunks = p.causal ? min(kv_chunks, qblk + 1) : kv_chunks;
+  // keys may be a longer stream than the queries (prefill on top of a cached prefix): the queries are the last
+  // seq_len positions of the seq_len_k keys, i.e. query i sees keys [0, i + koff]
+  const int k_start = p.cu_k ? p.cu_k[b] : seq_start;
+  const int seq_len_k = p.cu_k ? p.cu_k[b + 1] - k_start : seq_len;
+  const int koff = seq_len_k - seq_len;
+  const int kv_chunks = (seq_len_k + FA_BN - 1) / FA_BN;
+  const int n_chunks = p.causal ? min(kv_chunks, (r0 + FA_BM - 1 + koff) / FA_BN + 1) : kv_chunks;
 
   if (tid == 0) {
     for (int s = 0; s < FA_SLOTS; ++s) {
@@ -118,7 +124,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_arrive_expect_tx(&full[s], FA_TILE);
         uint8_t* dst = ring + s * FA_TILE;
         const CUtensorMap* tm = (t & 1) ? &tmV : &tmK;
-        const int row = seq_start + (t >> 1) * FA_BN;
+        const int row = k_start + (t >> 1) * FA_BN;
         tma_load_2d(dst, tm, &full[s], hk * FA_D, row);
         tma_load_2d(dst + 16384, tm, &full[s], hk * FA_D + 64, row);
       }
@@ -204,8 +210,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       const int c0 = c * FA_BN;
       // keys this row may see in the chunk: [0, lim)
-      int lim = seq_len - c0;
-      if (p.causal) lim = min(lim, qpos - c0 + 1);
+      int lim = seq_len_k - c0;
+      if (p.causal) lim = min(lim, qpos + koff - c0 + 1);
       lim = max(min(lim, FA_BN), 0);
       const uint32_t s_addr = tmem_base + lane_base + i * FA_BN;
       float cmax = -INFINITY;
@@ -313,20 +319,22 @@ using namespace vb;
 
 extern "C" int vb_flash_fwd_supported(int Hq, int Hk, int D) { return (D == FA_D && Hk > 0 && Hq % Hk == 0) ? 1 : 0; }
 
-// q [T, Hq, 128], k / v [T, Hk, 128] bf16 with token strides (elements, multiples of 8); cu_seqlens int32 [B + 1] on
-// the device; out [T, Hq, 128] bf16; lse [Hq, T] fp32 or null.
+// q [T, Hq, 128], k / v [Tk, Hk, 128] bf16 with token strides (elements, multiples of 8); cu_seqlens int32 [B + 1] on
+// the device; cu_k / Tk describe the key stream when it differs from the query stream (null / 0 otherwise; with
+// causal the queries of a sequence are the last positions of its keys); out [T, Hq, 128] bf16; lse [Hq, T] fp32 or null.
 extern "C" int vb_flash_fwd(const void* q, const void* k, const void* v, long long q_stride, long long k_stride,
-                            long long v_stride, const int* cu_seqlens, int B, long long T, int max_seqlen, int Hq, int Hk,
-                            float scale, int causal, void* out, long long out_stride, float* lse, int* status,
-                            cudaStream_t stream) {
+                            long long v_stride, const int* cu_seqlens, const int* cu_k, int B, long long T, long long Tk,
+                            int max_seqlen, int Hq, int Hk, float scale, int causal, void* out, long long out_stride,
+                            float* lse, int* status, cudaStream_t stream) {
   if (B <= 0 || T <= 0 || max_seqlen <= 0) return 0;
+  if (cu_k == nullptr) Tk = T;
   if (Hk <= 0 || Hq % Hk != 0 || (q_stride & 7) || (k_stride & 7) || (v_stride & 7) || (out_stride & 7)) return -3;
   CUtensorMap tmQ, tmK, tmV;
   int rc = vb_make_tmap_2d(&tmQ, q, 2, (uint64_t)Hq * FA_D, (uint64_t)T, (uint64_t)q_stride * 2, 64, FA_BM);
   if (rc) return rc;
-  rc = vb_make_tmap_2d(&tmK, k, 2, (uint64_t)Hk * FA_D, (uint64_t)T, (uint64_t)k_stride * 2, 64, FA_BN);
+  rc = vb_make_tmap_2d(&tmK, k, 2, (uint64_t)Hk * FA_D, (uint64_t)Tk, (uint64_t)k_stride * 2, 64, FA_BN);
   if (rc) return rc;
-  rc = vb_make_tmap_2d(&tmV, v, 2, (uint64_t)Hk * FA_D, (uint64_t)T, (uint64_t)v_stride * 2, 64, FA_BN);
+  rc = vb_make_tmap_2d(&tmV, v, 2, (uint64_t)Hk * FA_D, (uint64_t)Tk, (uint64_t)v_stride * 2, 64, FA_BN);
   if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {
@@ -335,6 +343,7 @@ extern "C" int vb_flash_fwd(const void* q, const void* k, const void* v, long lo
   }
   FaParams p{};
   p.cu_seqlens = cu_seqlens;
+  p.cu_k = cu_k;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.out_stride = out_stride;
   p.lse = lse;

@@ -30,9 +30,11 @@ def _flash_varlen():
 
 
 def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int,
-              causal: bool, scale: float, need_lse: bool = True):
-    """tcgen05 forward. q [T,Hq,128], k/v [T,Hk,128] bf16 with unit inner strides (views of a fused qkv buffer are
-    fine). Returns (out [T,Hq,128] bf16, lse [Hq,T] fp32 or None)."""
+              causal: bool, scale: float, need_lse: bool = True, cu_seqlens_k: torch.Tensor | None = None):
+    """tcgen05 forward. q [T,Hq,128], k/v [Tk,Hk,128] bf16 with unit inner strides (views of a fused qkv buffer are
+    fine). ``cu_seqlens_k``: key-side boundaries when the keys are a longer stream than the queries (prefill on top
+    of cached context; causal then aligns the queries with the end of the keys). ``max_seqlen`` is the longest
+    query sequence. Returns (out [T,Hq,128] bf16, lse [Hq,T] fp32 or None)."""
     T, Hq, D = q.shape
     Hk = k.shape[1]
     for t in (q, k, v):
@@ -41,7 +43,8 @@ def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: tor
     out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
     lse = torch.empty((Hq, T), dtype=torch.float32, device=q.device) if need_lse else None
     rc = _lib.fn("vb_flash_fwd")(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
-                                 cu_seqlens.data_ptr(), cu_seqlens.numel() - 1, T, int(max_seqlen), Hq, Hk, float(scale),
+                                 cu_seqlens.data_ptr(), _lib.ptr(cu_seqlens_k), cu_seqlens.numel() - 1, T, k.shape[0],
+                                 int(max_seqlen), Hq, Hk, float(scale),
                                  int(causal), out.data_ptr(), out.stride(0), _lib.ptr(lse),
                                  _lib.status_word(q.device).data_ptr(), _lib.stream())
     _lib.check(rc, "vb_flash_fwd")

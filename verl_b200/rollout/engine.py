@@ -589,7 +589,12 @@ class NativeRolloutEngine:
 def _varlen_attention_kv(q, k, v, cu_q, cu_k, max_q, max_k):
     """Causal attention where each sequence's queries are the last ``len_q`` positions of its keys."""
     if q.is_cuda:
-        from flash_attn import flash_attn_varlen_func  # library kernel (prefix-cache prefill only)
+        from ..ops.attention import _native_fwd_ok, flash_fwd
+
+        k, v = k.contiguous(), v.contiguous()
+        if _native_fwd_ok(q, k, v):
+            return flash_fwd(q, k, v, cu_q, max_q, True, q.shape[-1] ** -0.5, need_lse=False, cu_seqlens_k=cu_k)[0]
+        from flash_attn import flash_attn_varlen_func  # library kernel (head dims other than 128)
 
         return flash_attn_varlen_func(q, k, v, cu_q, cu_k, max_q, max_k, causal=True)
     out = torch.empty_like(q)
