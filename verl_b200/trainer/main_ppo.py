@@ -67,7 +67,7 @@ def build_tokenizer(config, model_config=None):
     return IntTokenizer(mc.vocab_size, eos_token_id=mc.eos_token_id if mc.eos_token_id is not None else 2)
 
 
-def run_ppo(config, spmd: Optional[bool] = None):
+def run_ppo(config, spmd: Optional[bool] = None, trainer_cls=None, run_fit: bool = True):
     from ..workers.engine_workers import ActorRolloutRefWorker, CriticWorker, RewardModelWorker
     from .ppo.ray_trainer import RayPPOTrainer, ResourcePoolManager
     from .ppo.reward import load_reward_manager
@@ -109,11 +109,13 @@ def run_ppo(config, spmd: Optional[bool] = None):
                                        max_samples=config.data.get("val_max_samples", -1))
         except (FileNotFoundError, OSError):
             val_ds = None
-    trainer = RayPPOTrainer(config=config, tokenizer=tokenizer, role_worker_mapping=mapping, resource_pool_manager=rpm,
+    trainer = (trainer_cls or RayPPOTrainer)(config=config, tokenizer=tokenizer, role_worker_mapping=mapping, resource_pool_manager=rpm,
                             ray_worker_group_cls=wg_cls, reward_fn=reward_fn, val_reward_fn=val_reward_fn,
                             train_dataset=train_ds, val_dataset=val_ds, train_sampler=create_rl_sampler(config.data, train_ds),
                             device_name=device)
     trainer.init_workers()
+    if not run_fit:
+        return trainer  # the caller drives the steps (asynchronous pipelines) and calls trainer.shutdown()
     try:
         trainer.fit()
     finally:

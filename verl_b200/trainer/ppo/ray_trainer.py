@@ -530,6 +530,14 @@ class RayPPOTrainer:
         self.global_steps += 1
         with marked_timer("step", timing_raw):
             batch = self._rollout_and_reward(batch_dict, timing_raw, metrics)
+            self._train_on_batch(batch, timing_raw, metrics)
+        return self._finish_step(timing_raw, metrics)
+
+    def _train_on_batch(self, batch: DataProto, timing_raw: dict, metrics: dict) -> None:
+        """Everything after rollout + reward: filtering, log-probs, advantages, critic / actor update, weight sync.
+        Split out so that asynchronous trainers can feed batches produced elsewhere."""
+        cfg = self.config
+        if True:
             fg = cfg.algorithm.get("filter_groups") or {}
             if fg.get("enable", False):
                 batch.batch["token_level_rewards"] = batch.batch["token_level_scores"]
@@ -613,6 +621,10 @@ class RayPPOTrainer:
             dump_dir = cfg.trainer.get("rollout_data_dir")
             if dump_dir:
                 self._dump_generations(batch, dump_dir)
+        self._last_batch = batch
+
+    def _finish_step(self, timing_raw: dict, metrics: dict) -> dict:
+        batch = self._last_batch
         metrics.update(compute_data_metrics(batch, use_critic=self.use_critic))
         metrics.update(compute_timing_metrics(batch, timing_raw))
         n_gpus = 1 if self.spmd else self.n_gpus
