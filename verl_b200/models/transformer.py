@@ -32,6 +32,7 @@ class PackedBatch:
     position_ids: torch.Tensor  # [T] int64
     cu_seqlens: torch.Tensor  # [B+1] int32
     max_seqlen: int
+    total_tokens: int = -1  # Ulysses: tokens of the whole packed stream when input_ids holds only this rank's slice
 
     @classmethod
     def from_padded(cls, input_ids: torch.Tensor, attention_mask: torch.Tensor, position_ids: torch.Tensor | None = None):
@@ -152,6 +153,30 @@ class Attention(nn.Module):
         if cfg.qk_norm:
             self.q_norm = RMSNormWeight(cfg.head_dim, dtype, device)
             self.k_norm = RMSNormWeight(cfg.head_dim, dtype, device)
+        self.sp_group = None  # Ulysses sequence-parallel group (set by the engine)
+
+    def _attend(self, q, k, v, batch: PackedBatch):
+        """Attention proper. Under Ulysses the inputs are this rank's sequence slice with all heads; an all-to-all
+        makes them the whole sequence with a slice of the heads and another one brings the output back
+        (verl/models/transformers/monkey_patch.py:87-155)."""
+        if self.sp_group is None:
+            return ops.attention_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, causal=True)
+        import torch.distributed as dist
+
+        from ..utils.ulysses import gather_heads_scatter_seq, gather_seq_scatter_heads
+
+        sp = dist.get_world_size(self.sp_group)
+        Hk = k.shape[1]
+        if Hk % sp != 0:  # fewer KV heads than ranks: replicate them so that every rank owns whole heads
+            assert sp % Hk == 0, f"ulysses size {sp} and {Hk} KV heads are incompatible"
+            k = k.repeat_interleave(sp // Hk, dim=1)
+            v = v.repeat_interleave(sp // Hk, dim=1)
+        total = batch.total_tokens if batch.total_tokens > 0 else q.shape[0] * sp
+        q = gather_seq_scatter_heads(q, 0, 1, total, self.sp_group)
+        k = gather_seq_scatter_heads(k, 0, 1, total, self.sp_group)
+        v = gather_seq_scatter_heads(v, 0, 1, total, self.sp_group)
+        o = ops.attention_varlen(q.contiguous(), k.contiguous(), v.contiguous(), batch.cu_seqlens, batch.max_seqlen, causal=True)
+        return gather_heads_scatter_seq(o, 1, 0, self.sp_group)
 
     def forward(self, x, batch: PackedBatch, rope):
         cfg = self.cfg
@@ -167,7 +192,7 @@ class Attention(nn.Module):
         q = qkv[:, : cfg.q_size].view(T, Hq, D)
         k = qkv[:, cfg.q_size : cfg.q_size + cfg.kv_size].view(T, Hk, D)
         v = qkv[:, cfg.q_size + cfg.kv_size :].view(T, Hk, D)
-        o = ops.attention_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, causal=True)
+        o = self._attend(q, k, v, batch)
         return self.o_proj(o.reshape(T, cfg.q_size))
 
 

@@ -44,6 +44,23 @@ def _cfg(obj, key, default=None):
     return default if v is None else v
 
 
+class _SumOverGroup(torch.autograd.Function):
+    """Sum of per-rank partial results whose non-zero rows are disjoint. Every rank goes on to compute the same
+    loss from the sum, so the backward is the identity on this rank's rows: no communication."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        import torch.distributed as dist
+
+        y = x.clone()
+        dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad, None
+
+
 class NativeEngine(BaseEngine):
     def __init__(self, model_config: ModelConfig, engine_config=None, optimizer_config=None, *, value_head: bool = False,
                  device: Optional[str] = None, trainable: bool = True, group=None, seed: int = 0,
@@ -95,6 +112,7 @@ class NativeEngine(BaseEngine):
             units.append(("", head))
         self.zero = ZeroShardedParams(units, group=self.group, work_dtype=self.work_dtype, device=self.device,
                                       trainable=self.trainable, comm=self.comm)
+        self._setup_sequence_parallel()
         self._embed_unit = self.zero.units[0]
         self._layer_units = self.zero.units[1 : 1 + cfg.num_hidden_layers]
         self._head_unit = self.zero.units[0] if tied else self.zero.units[-1]
@@ -112,11 +130,37 @@ class NativeEngine(BaseEngine):
     def world(self) -> int:
         return self.zero.world
 
+    def _setup_sequence_parallel(self):
+        """Ulysses: ``ulysses_sequence_parallel_size`` consecutive ranks form a group that works on the same
+        micro-batch, each on a slice of the packed token stream (mesh (dp, sp) of verl/workers/fsdp_workers.py:146-273).
+        Parameters stay sharded over all ranks; the gradient reduce-scatter over all ranks then sums the partial
+        gradients of the slices as well as those of the data-parallel replicas."""
+        import torch.distributed as dist
+
+        sp = int(_cfg(self.engine_config, "ulysses_sequence_parallel_size", 1) or 1)
+        self.sp_size, self.sp_group, self.sp_rank = 1, None, 0
+        if sp <= 1 or self.zero.world <= 1:
+            return
+        W, r = self.zero.world, self.zero.rank
+        assert W % sp == 0, f"world size {W} is not a multiple of ulysses_sequence_parallel_size {sp}"
+        from ...utils.ulysses import validate_ulysses_config
+
+        validate_ulysses_config(self.model_config.num_attention_heads, sp)
+        ranks_of = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(W))
+        for g in range(W // sp):
+            members = [ranks_of[g * sp + i] for i in range(sp)]
+            grp = dist.new_group(members)  # collective: every rank creates every group
+            if r // sp == g:
+                self.sp_group = grp
+        self.sp_size, self.sp_rank = sp, r % sp
+        for layer in self.model.layers:
+            layer.self_attn.sp_group = self.sp_group
+
     def get_data_parallel_size(self) -> int:
-        return self.zero.world
+        return self.zero.world // self.sp_size
 
     def get_data_parallel_rank(self) -> int:
-        return self.zero.rank
+        return self.zero.rank // self.sp_size
 
     def get_data_parallel_group(self):
         return self.group
@@ -160,6 +204,15 @@ class NativeEngine(BaseEngine):
         """Final-norm input pieces (hidden, residual) restricted to ``rows`` of the packed stream."""
         m, z = self.model, self.zero
         rope = m.rope(self.device)
+        sp_lo = 0
+        if self.sp_size > 1:
+            # this rank's slice of the packed stream; attention re-assembles the sequences per head group
+            from ...utils.ulysses import ulysses_pad_and_slice_inputs
+
+            T = batch.input_ids.shape[0]
+            ids_l, pos_l, _ = ulysses_pad_and_slice_inputs(batch.input_ids, batch.position_ids, self.sp_size, self.sp_group)
+            sp_lo = self.sp_rank * ids_l.shape[0]
+            batch = PackedBatch(ids_l, pos_l, batch.cu_seqlens, batch.max_seqlen, total_tokens=T)
         hidden = unit_call(z, self._embed_unit, lambda: m.embed(batch))
         residual = None
         ckpt = self.gradient_checkpointing or z.world > 1
@@ -168,29 +221,54 @@ class NativeEngine(BaseEngine):
                 hidden, residual = unit_call(z, unit, lambda h, r, layer=layer: layer(h, r, batch, rope), hidden, residual)
             else:
                 hidden, residual = layer(hidden, residual, batch, rope)
+        if self.sp_size > 1:
+            # keep the rows that live in this rank's slice; _sp_merge puts the per-row results back together
+            n_l = hidden.shape[0]
+            all_rows = rows if rows is not None else torch.arange(batch.total_tokens, device=hidden.device)
+            mine = (all_rows >= sp_lo) & (all_rows < sp_lo + n_l)
+            self._sp_sel = (mine, all_rows.numel())
+            local = all_rows[mine] - sp_lo
+            return hidden[local], residual[local]
         if rows is not None:
             hidden, residual = hidden[rows], residual[rows]
         return hidden, residual
+
+    def _sp_merge(self, out):
+        """Scatter this rank's per-row results into the full row order and sum over the sequence-parallel group
+        (every row is owned by exactly one rank). The backward keeps the gradient of the rows this rank owns."""
+        if self.sp_size <= 1:
+            return out
+        mine, n = self._sp_sel
+
+        def one(t):
+            full = torch.zeros((n,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+            full = full.index_put((torch.nonzero(mine, as_tuple=True)[0],), t)
+            return _SumOverGroup.apply(full, self.sp_group)
+
+        return tuple(one(t) if isinstance(t, torch.Tensor) else t for t in out) if isinstance(out, tuple) else one(out)
 
     def forward_logprob(self, batch: PackedBatch, rows: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0):
         """Log-prob of ``labels[i]`` predicted at packed position ``rows[i]`` (+ entropy), both fp32."""
         m, z = self.model, self.zero
         hidden, residual = self._forward_hidden_rows(batch, rows)
 
+        if self.sp_size > 1:
+            labels = labels[self._sp_sel[0]]
+
         def head(h, r):
             return m.logprob_entropy(m.final_norm(h, r), labels, temperature)
 
-        return unit_call(z, self._head_unit, head, hidden, residual)
+        return self._sp_merge(unit_call(z, self._head_unit, head, hidden, residual))
 
     def forward_values(self, batch: PackedBatch, rows: torch.Tensor):
         m, z = self.model, self.zero
         hidden, residual = self._forward_hidden_rows(batch, rows)
-        return unit_call(z, self._head_unit, lambda h, r: m.values(m.final_norm(h, r)), hidden, residual)
+        return self._sp_merge(unit_call(z, self._head_unit, lambda h, r: m.values(m.final_norm(h, r)), hidden, residual))
 
     def forward_logits(self, batch: PackedBatch, rows: Optional[torch.Tensor] = None):
         m, z = self.model, self.zero
         hidden, residual = self._forward_hidden_rows(batch, rows)
-        return unit_call(z, self._head_unit, lambda h, r: m.logits(m.final_norm(h, r)), hidden, residual)
+        return self._sp_merge(unit_call(z, self._head_unit, lambda h, r: m.logits(m.final_norm(h, r)), hidden, residual))
 
     # --------------------------------------------------------- response bookkeeping
     @staticmethod

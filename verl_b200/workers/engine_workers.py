@@ -114,8 +114,15 @@ class ActorRolloutRefWorker(_WorkerBase):
         n = int(_cfg(config.get("rollout", {}), "n", 1))
         if self._is_actor:
             self._norm_batch(self.actor_cfg, n=n)
-        self._register_dispatch_collect_info("actor", dp_rank=self.dp_rank, is_collect=True)
-        self._register_dispatch_collect_info("ref", dp_rank=self.dp_rank, is_collect=True)
+        # Ulysses: the ranks of a sequence-parallel group share one data-parallel rank and the first one reports
+        # (dispatch of verl/single_controller/base/decorator.py:297-328, registration of fsdp_workers.py:146-273)
+        def sp_of(c):
+            return int(_cfg(_cfg(c, "fsdp_config", None), "ulysses_sequence_parallel_size", 1) or 1) if c is not None else 1
+
+        rank = self.dp_rank
+        sp_a, sp_r = sp_of(self.actor_cfg), sp_of(self.ref_cfg if self.ref_cfg is not None else self.actor_cfg)
+        self._register_dispatch_collect_info("actor", dp_rank=rank // sp_a, is_collect=rank % sp_a == 0)
+        self._register_dispatch_collect_info("ref", dp_rank=rank // sp_r, is_collect=rank % sp_r == 0)
         self._register_dispatch_collect_info("rollout", dp_rank=self.dp_rank, is_collect=True)
         self.actor_engine = self.ref_engine = None
         self.actor = self.ref_policy = None
