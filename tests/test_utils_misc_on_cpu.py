@@ -1,0 +1,107 @@
+"""Small utilities: rollout skip / trace, memory buffers, prefix grouper, fs and import helpers."""
+
+import asyncio
+import json
+import os
+
+import numpy as np
+import torch
+
+
+def test_prefix_grouper_roundtrip_and_mask():
+    from verl_b200.trainer.ppo import prefix_grouper_utils as pg
+
+    P, R = 6, 5
+    prompts = torch.tensor([[0, 0, 5, 6, 7, 8]] * 3 + [[0, 9, 9, 9, 9, 9]] * 2)
+    responses = torch.tensor([[1, 2, 3, 0, 0], [4, 5, 0, 0, 0], [6, 7, 8, 9, 1], [2, 2, 0, 0, 0], [3, 0, 0, 0, 0]])
+    mask = torch.cat([(prompts != 0).long(), (responses != 0).long()], 1)
+    groups = pg.build_prefix_groups(prompts, responses, mask)
+    assert [g.rows for g in groups] == [[0, 1, 2], [3, 4]]
+    ids, pos, cu, seg, where = pg.pack_with_shared_prefix(groups)
+    assert cu.tolist() == [0, 4 + 3 + 2 + 5, 14 + 5 + 2 + 1]
+    assert pos[4:7].tolist() == [4, 5, 6] and pos[7:9].tolist() == [4, 5]  # every response continues after the prompt
+    m = pg.prefix_sharing_mask(seg, cu)
+    q = where[1][0]  # first token of response 1 of group 0
+    assert m[q, :4].all() and not m[q, 4:7].any() and m[q, q]
+    vals = torch.arange(ids.numel(), dtype=torch.float32)
+    out = pg.unpack_shared_prefix(vals, where, 5, R)
+    assert out[0, 1] == where[0][0] and out[2, 4] == where[2][0] + 3
+    assert 0.2 < pg.prefix_saving(groups) < 0.6
+
+
+def test_memory_buffer_wrapper():
+    from verl_b200.utils.memory_buffer import MemoryBufferModuleWrapper
+
+    m = torch.nn.Sequential(torch.nn.Linear(8, 4), torch.nn.Linear(4, 2))
+    ref = {k: v.detach().clone() for k, v in m.named_parameters()}
+    w = MemoryBufferModuleWrapper(m)
+    buf = w.get_memory_buffers()[torch.float32]
+    for k, v in m.named_parameters():
+        assert torch.equal(v, ref[k])
+        assert buf.data.data_ptr() <= v.data_ptr() < buf.data.data_ptr() + buf.data.numel() * 4
+    buf.data.zero_()
+    assert all(float(v.abs().sum()) == 0 for v in m.parameters())
+
+
+def test_rollout_trace_file_backend(tmp_path):
+    from verl_b200.utils.rollout_trace import RolloutTraceConfig, rollout_trace_attr, rollout_trace_op
+
+    RolloutTraceConfig.reset()
+    RolloutTraceConfig.init("p", "e", "file", path=str(tmp_path / "t.jsonl"))
+
+    class A:
+        @rollout_trace_op
+        async def step(self, x, y=2):
+            return {"sum": x + y}
+
+    async def go():
+        with rollout_trace_attr(sample_index=3, step=7, rollout_n=1):
+            return await A().step(1, y=5)
+
+    assert asyncio.run(go()) == {"sum": 6}
+    rows = [json.loads(l) for l in open(tmp_path / "t.jsonl")]
+    assert rows[0]["inputs"] == {"x": 1, "y": 5} and rows[0]["attrs"]["step"] == 7 and rows[0]["output"] == {"sum": 6}
+    RolloutTraceConfig.reset()
+
+
+def test_rollout_skip_replays(tmp_path):
+    from verl_b200.protocol import DataProto
+    from verl_b200.utils.config import to_config
+    from verl_b200.utils.rollout_skip import RolloutSkip
+
+    cfg = to_config({"actor_rollout_ref": {"rollout": {"n": 1, "skip_dump_dir": str(tmp_path)}},
+                     "trainer": {"project_name": "p", "experiment_name": "e"},
+                     "data": {"train_batch_size": 2, "max_prompt_length": 4, "max_response_length": 4}})
+    calls = [0]
+
+    class WG:
+        def generate_sequences(self, batch, **kw):
+            calls[0] += 1
+            return DataProto.from_dict(tensors={"responses": torch.full((2, 4), calls[0])})
+
+    batch = DataProto.from_dict(tensors={"input_ids": torch.zeros(2, 4, dtype=torch.long)})
+    wg = WG()
+    RolloutSkip(cfg, wg).wrap_generate_sequences()
+    a = wg.generate_sequences(batch)
+    wg2 = WG()
+    RolloutSkip(cfg, wg2).wrap_generate_sequences()
+    b = wg2.generate_sequences(batch)
+    assert calls[0] == 1 and torch.equal(a.batch["responses"], b.batch["responses"])
+
+
+def test_fs_and_import_helpers(tmp_path):
+    from verl_b200.utils import fs, import_utils, net_utils
+
+    f = tmp_path / "x.txt"
+    f.write_text("hi")
+    assert fs.copy_to_local(str(f)) == str(f)
+    shm = fs.copy_to_local(str(f), use_shm=True)
+    assert shm.startswith("/dev/shm/") and open(shm).read() == "hi"
+    os.remove(shm)
+    assert import_utils.is_package_available("torch") and not import_utils.is_package_available("not_a_package_xyz")
+    assert net_utils.is_ipv4("127.0.0.1") and net_utils.is_ipv6("::1") and net_utils.get_free_port() > 0
+    try:
+        fs.copy_to_local("hdfs://nn/path")
+        raise AssertionError("expected a RuntimeError")
+    except RuntimeError:
+        pass

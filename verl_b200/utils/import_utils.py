@@ -1,0 +1,56 @@
+"""Import helpers (role of verl/utils/import_utils.py)."""
+
+from __future__ import annotations
+
+import importlib
+import importlib.util
+from functools import cache
+
+from .py_functional import load_extern_object  # noqa: F401  (same loader, historical location)
+
+
+@cache
+def is_package_available(name: str) -> bool:
+    return importlib.util.find_spec(name) is not None
+
+
+def is_vllm_available() -> bool:
+    return is_package_available("vllm")
+
+
+def is_sglang_available() -> bool:
+    return is_package_available("sglang")
+
+
+def is_megatron_core_available() -> bool:
+    return is_package_available("megatron.core") if is_package_available("megatron") else False
+
+
+def import_external_libs(external_libs=None) -> None:
+    """Import user modules listed in ``model.external_lib`` (they register models / rewards on import)."""
+    if not external_libs:
+        return
+    if isinstance(external_libs, str):
+        external_libs = [external_libs]
+    for lib in external_libs:
+        importlib.import_module(lib)
+
+
+def load_extern_type(file_path: str, type_name: str):
+    return load_extern_object(file_path, type_name)
+
+
+def deprecated(replacement: str = ""):
+    import functools
+    import warnings
+
+    def deco(fn):
+        @functools.wraps(fn)
+        def wrapper(*a, **k):
+            warnings.warn(f"{fn.__qualname__} is deprecated" + (f"; use {replacement}" if replacement else ""),
+                          DeprecationWarning, stacklevel=2)
+            return fn(*a, **k)
+
+        return wrapper
+
+    return deco
