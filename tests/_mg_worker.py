@@ -110,6 +110,32 @@ def check_zero_step(rank, world, dev, comm):
     torch.testing.assert_close(w_a, w_b, atol=2e-2, rtol=2e-2)
 
 
+def check_ag_gemm(comm, rank, world, dev):
+    """Fused all-gather + GEMM against a GEMM on the explicitly gathered weight."""
+    from verl_b200 import ops
+
+    torch.manual_seed(21)  # same data on every rank
+    M, N, K, w_off = 1000, 1536 + 64, 640, 4096
+    total = w_off + N * K + 777
+    shard_n = (total + world - 1) // world
+    shard_n = (shard_n + 255) // 256 * 256
+    flat = torch.zeros(shard_n * world, dtype=torch.bfloat16, device=dev)
+    flat[:total] = (torch.randn(total, device=dev) * 0.05).bfloat16()
+    shard = comm.alloc(shard_n, torch.bfloat16)
+    shard.copy_(flat[rank * shard_n : (rank + 1) * shard_n])
+    x = torch.randn(M, K, device=dev).bfloat16()
+    bias = torch.randn(N, device=dev).bfloat16()
+    W = flat[w_off : w_off + N * K].view(N, K)
+    for it in range(2):
+        out, w_full = comm.ag_gemm(x, shard, w_off, N, K, bias=bias)
+        torch.cuda.synchronize()
+        comm.check()
+        assert torch.equal(w_full, W), "gathered weight differs"
+        ref = ops.gemm(x, W, bias=bias)
+        assert torch.equal(out, ref), "fused result differs from the plain GEMM on the same weight"
+        comm.barrier()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
@@ -123,6 +149,8 @@ def main():
         check_comm(comm, rank, world, dev)
     if what in ("reshard", "all"):
         check_reshard(comm, rank, world, dev)
+    if what in ("ag_gemm", "all"):
+        check_ag_gemm(comm, rank, world, dev)
     if what in ("zero", "all"):
         check_zero_step(rank, world, dev, comm)
     torch.cuda.synchronize()

@@ -29,7 +29,9 @@ constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int GROUP_M = 8;
 
-enum Epi : int { EPI_STORE = 0, EPI_LSE = 1, EPI_DLOGITS = 2 };
+enum Epi : int { EPI_STORE = 0, EPI_LSE = 1, EPI_DLOGITS = 2, EPI_STORE_AG = 3 };
+constexpr int AG_COPY_THREADS = 128;  // EPI_STORE_AG: four more warps pull the peers' shards of B
+constexpr int AG_MAX_RANKS = 16;
 
 struct GemmParams {
   int M, N, K;
@@ -56,6 +58,15 @@ struct GemmParams {
   int kb_per_split;
   float* ws;        // [k_splits, num_m * BM, num_n * BN] fp32
   int* counters;    // one per tile, zero before the launch and zero again after it
+  // EPI_STORE_AG: B = W [N, K] is assembled in ag_dst from the ranks' flat shards while the GEMM runs. Element e of
+  // the sharded flat vector lives on rank e / ag_shard at offset e % ag_shard; W starts at element ag_w_off.
+  // ag_ready[nb] counts the CTAs that have copied their slice of rows [nb*BN, (nb+1)*BN); a tile may load its B
+  // operand once the count reaches the grid size.
+  const void* ag_src[AG_MAX_RANKS];
+  long long ag_shard;
+  long long ag_w_off;
+  __nv_bfloat16* ag_dst;
+  unsigned* ag_ready;
   int* status;
 };
 
@@ -198,7 +209,7 @@ __device__ __forceinline__ void epi_store4(const GemmParams& p, int row, int col
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(EPI == EPI_STORE_AG ? NUM_THREADS + AG_COPY_THREADS : NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -254,6 +265,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         int ks, kb0, kb1;
         sched.k_range(u, ks, kb0, kb1);
         for (int nb = n_first; ok && nb < n_first + n_count; ++nb) {
+          if (EPI == EPI_STORE_AG) {
+            // rows [nb*BN, (nb+1)*BN) of B must have arrived from all ranks (every CTA copies a slice of them)
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while (true) {
+              unsigned v;
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.ag_ready + nb) : "memory");
+              if (v >= gridDim.x) break;
+              if ((++spins & 0xff) == 0 && (*abort_flag || globaltimer_ns() - t0 > VB_WAIT_LIMIT_NS)) {
+                report_error(p.status, ERR_WAIT_FLAG, nb);
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async.global;" ::: "memory");  // generic-proxy copies -> TMA reads
+          }
           for (int kb = kb0; kb < kb1; ++kb) {
             if (*abort_flag || !mbar_wait(&empty[s], phase ^ 1)) {
               report_error(p.status, ERR_WAIT_EMPTY, kb);
@@ -342,7 +371,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       }
     }
-  } else {
+  } else if (EPI == EPI_STORE_AG && warp >= 6) {
+    // ------------------------------ all-gather of B (copy warps) ----------------------------------
+    // Chunk after chunk, in the order in which the tiles need them, every CTA copies 1/gridDim of the chunk from
+    // the ranks that own it (plain 16-byte loads over NVLink for remote ranks) into the local full matrix.
+    const int ct = threadIdx.x - NUM_THREADS;
+    const int num_n = (p.N + BN - 1) / BN;
+    uint4* dst = reinterpret_cast<uint4*>(p.ag_dst);
+    const long long shard16 = p.ag_shard >> 3, off16 = p.ag_w_off >> 3, row16 = (long long)p.K >> 3;
+    for (int j = 0; j < num_n; ++j) {
+      const long long c_lo = (long long)j * BN * row16;
+      const long long c_hi = min((long long)(j + 1) * BN, (long long)p.N) * row16;
+      const long long per = (c_hi - c_lo + gridDim.x - 1) / gridDim.x;
+      const long long lo = c_lo + (long long)blockIdx.x * per;
+      const long long hi = min(lo + per, c_hi);
+      constexpr int U = 8;
+      for (long long i0 = lo + ct; i0 < hi; i0 += (long long)AG_COPY_THREADS * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + (long long)u * AG_COPY_THREADS;
+          if (i < hi) {
+            const long long e = off16 + i;
+            const int r = (int)(e / shard16);
+            v[u] = reinterpret_cast<const uint4*>(p.ag_src[r])[e - (long long)r * shard16];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + (long long)u * AG_COPY_THREADS;
+          if (i < hi) dst[i] = v[u];
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (ct == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag_ready + j) : "memory");
+    }
+  } else if (warp < 6) {
     // ------------------------------ epilogue ----------------------------------
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     const int row_in_tile = quad * 32 + lane;
@@ -388,7 +453,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           tmem_ld_32x32(t_row + c * 32, r);
           tmem_ld_wait();
           const int col0 = nb * BN + c * 32;
-          if (EPI == EPI_STORE) {
+          if (EPI == EPI_STORE || EPI == EPI_STORE_AG) {
             if (sched.k_splits > 1) {
               // fp32 partial tile, tile-contiguous in the workspace: [tile][k slice][BM][BN]
               float4* dst = reinterpret_cast<float4*>(
@@ -463,7 +528,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           acc_phase ^= 1;
         }
       }
-      if (EPI == EPI_STORE) {
+      if (EPI == EPI_STORE || EPI == EPI_STORE_AG) {
         if (sched.k_splits > 1) {
           // ticket: the unit that arrives last at this tile reduces the slices (fixed order: deterministic)
           __threadfence();
@@ -944,6 +1009,54 @@ extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void
   if (a_mn && b_mn) return VB_DISPATCH(true, true);
   return VB_DISPATCH(true, false);
 #undef VB_DISPATCH
+}
+
+// Fused all-gather + GEMM: C[M,N] = A . W^T where W [N,K] is not there yet. Every rank holds a contiguous slice
+// (`shard_elems` elements) of a flat bf16 vector that contains W at element offset `w_off`; `srcs[r]` is rank r's
+// slice (a peer-mapped pointer for remote ranks). While the tensor-core warps run, four copy warps per CTA pull
+// W chunk by chunk (in tile order) into `W_full`, and a tile's TMA loads wait only for the chunk they need: the
+// NVLink transfer hides under the MMAs of the earlier tiles. `ready` holds ceil(N/256) counters (zeroed here).
+// The caller guarantees that every rank's slice is final (a cross-rank barrier after the last update of the
+// slices) and that no rank rewrites its slice before all ranks have finished this call.
+// w_off, shard_elems and K must be multiples of 8; the kernel is launched cooperatively (its CTAs wait on each
+// other's copies, so all of them must be resident).
+extern "C" int vb_ag_gemm_bf16(const void* A, void* W_full, void* C, const void* bias, int M, int N, int K,
+                               long long lda, long long ldc, const void* const* srcs, int world, long long shard_elems,
+                               long long w_off, unsigned* ready, int out_fp32, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (K & 7) || (w_off & 7) || (shard_elems & 7) || world > AG_MAX_RANKS || world < 1) return -3;
+  if ((w_off + (long long)N * K + shard_elems - 1) / shard_elems > world) return -3;
+  constexpr int BN = 256;
+  using L = SmemLayout<BN>;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.out_fp32 = out_fp32; p.status = status;
+  p.k_splits = 1;
+  for (int r = 0; r < world; ++r) p.ag_src[r] = srcs[r];
+  p.ag_shard = shard_elems; p.ag_w_off = w_off;
+  p.ag_dst = reinterpret_cast<__nv_bfloat16*>(W_full);
+  p.ag_ready = ready;
+  CUtensorMap tmA, tmB;
+  int rc = vb_make_tmap_2d(&tmA, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM);
+  if (rc) return rc;
+  rc = vb_make_tmap_2d(&tmB, W_full, 2, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BN);
+  if (rc) return rc;
+  auto kern = gemm_kernel<BN, false, false, EPI_STORE_AG>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    VB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    attr_set = true;
+  }
+  const int num_n = (N + BN - 1) / BN;
+  const int units = ((M + BM - 1) / BM) * num_n;
+  const int grid = units < vb_num_sms() ? units : vb_num_sms();
+  VB_CUDA_CHECK(cudaMemsetAsync(ready, 0, sizeof(unsigned) * num_n, stream));
+  void* args[] = {(void*)&tmA, (void*)&tmB, (void*)&p};
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(NUM_THREADS + AG_COPY_THREADS), args,
+                                              L::DYN_BYTES, stream);
+  vb_count_launch();
+  return (int)e;
 }
 
 extern "C" int vb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,

@@ -35,6 +35,8 @@ def _bind():
     lib.vb_peer_barrier.argtypes, lib.vb_peer_barrier.restype = [P, I, I, I, U, P, P], I
     lib.vb_peer_all_gather.argtypes, lib.vb_peer_all_gather.restype = [P, P, L, P, L, I, I, I, U, P, P, P], I
     lib.vb_peer_all_gather_ce.argtypes, lib.vb_peer_all_gather_ce.restype = [P, P, L, P, L, I, I, I, U, P, P], I
+    lib.vb_ag_gemm_bf16.argtypes = [P, P, P, P, I, I, I, L, L, P, I, L, L, P, I, P, P]
+    lib.vb_ag_gemm_bf16.restype = I
     lib.vb_peer_reduce_scatter_add.argtypes = [P, P, P, L, P, L, F, I, I, I, U, P, P, P]
     lib.vb_peer_reduce_scatter_add.restype = I
     lib.vb_peer_segment_copy.argtypes, lib.vb_peer_segment_copy.restype = [P, P, P, I, P, I, I, I, U, P, P, P], I
@@ -187,6 +189,31 @@ class PeerComm:
                                            self.rank, self.world, self.CH_COPY, self._epoch(self.CH_COPY),
                                            self._gate(self.CH_COPY), self._status(), _lib.stream())
         _lib.check(rc, "vb_peer_segment_copy")
+
+    def ag_gemm(self, x: torch.Tensor, shard: torch.Tensor, w_off: int, N: int, K: int, bias: Optional[torch.Tensor] = None,
+                w_full: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, barrier: bool = True):
+        """Fused all-gather + GEMM: ``x [M, K] @ W^T`` where ``W [N, K]`` starts at element ``w_off`` of the flat bf16
+        vector whose rank-r slice is ``shard`` (symmetric memory, same size on every rank). The gather runs inside the
+        GEMM kernel (copy warps pull the peers' slices over NVLink chunk by chunk in tile order) and leaves the
+        assembled matrix in ``w_full`` for later use. Returns (out [M, N], w_full [N, K]).
+
+        ``barrier=True`` first runs the cross-rank handshake that makes every rank's slice final; pass False when a
+        previous collective of the same step already did."""
+        a, off = self._find(shard)
+        assert shard.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and x.stride(1) == 1
+        M = x.shape[0]
+        if w_full is None:
+            w_full = torch.empty((N, K), dtype=torch.bfloat16, device=x.device)
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        ready = torch.empty((N + 255) // 256, dtype=torch.int32, device=x.device)
+        if barrier:
+            self.barrier()
+        srcs = (ctypes.c_void_p * self.world)(*[int(p) + off for p in a.ptrs])
+        rc = self.lib.vb_ag_gemm_bf16(x.data_ptr(), w_full.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K, x.stride(0),
+                                      out.stride(0), srcs, self.world, shard.numel(), int(w_off), ready.data_ptr(),
+                                      int(out_dtype == torch.float32), self._status(), _lib.stream())
+        _lib.check(rc, "vb_ag_gemm_bf16")
+        return out, w_full
 
     def check(self):
         """Synchronising read of the status word; raises if a bounded wait ran out."""
