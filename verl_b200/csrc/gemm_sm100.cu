@@ -455,9 +455,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int col0 = nb * BN + c * 32;
           if (EPI == EPI_STORE || EPI == EPI_STORE_AG) {
             if (sched.k_splits > 1) {
-              // fp32 partial tile, tile-contiguous in the workspace: [tile][k slice][BM][BN]
+              // fp32 partial: slice ks of the padded [num_m * BM, num_n * BN] output
               float4* dst = reinterpret_cast<float4*>(
-                  p.ws + (((long long)(m_blk * sched.num_n + nb) * sched.k_splits + ks) * BM + row_in_tile) * BN + c * 32);
+                  p.ws + ((long long)ks * sched.num_m * BM + row) * ((long long)sched.num_n * BN) + col0);
 #pragma unroll
               for (int i = 0; i < 8; ++i)
                 __stcg(dst + i, make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
@@ -530,62 +530,74 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       if (EPI == EPI_STORE || EPI == EPI_STORE_AG) {
         if (sched.k_splits > 1) {
-          // ticket: the unit that arrives last at this tile reduces the slices (fixed order: deterministic)
+          // All units have written their fp32 slice. After a grid-wide barrier (the launch is cooperative and every
+          // CTA owns exactly one unit) EVERY CTA reduces an equal share of the output: its share of each slice comes
+          // back through one bulk async copy into the idle pipeline stages, the slices are summed in slice order
+          // (deterministic) and stored. counters[0] = arrivals, counters[1] = departures; the last CTA to leave
+          // zeroes both for the next launch.
+          const int et = threadIdx.x - 64;
+          const int S = sched.k_splits;
           __threadfence();
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          const int tile = m_blk * sched.num_n + n_first;
-          if (threadIdx.x == 64) *ticket_s = atomicAdd(&p.counters[tile], 1);
+          if (et == 0) {
+            atomicAdd(reinterpret_cast<unsigned*>(p.counters), 1u);
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            int good = ok ? 1 : 0;
+            while (true) {
+              unsigned v;
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.counters) : "memory");
+              if (v >= gridDim.x) break;
+              if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > VB_WAIT_LIMIT_NS) {
+                report_error(p.status, ERR_WAIT_FLAG, 3000);
+                good = 0;
+                break;
+              }
+            }
+            *ticket_s = good;
+          }
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          const bool last = ok && (*ticket_s == sched.k_splits - 1);
-          asm volatile("bar.sync 1, 128;" ::: "memory");  // ticket_s read by all before the next unit writes it
-          if (BN == 128 && last) {
-            // The slices come back through bulk async copies (no registers, full L2 bandwidth) into the pipeline
-            // stages, which are idle: a split-K launch gives every CTA exactly one unit. Four bands of 32 rows,
-            // double-buffered; slices are summed in slice order, so the result does not depend on arrival order.
-            __threadfence();
+          const bool go = *ticket_s != 0;
+          if (go) {
             asm volatile("fence.proxy.async.global;" ::: "memory");
-            const int et = threadIdx.x - 64;
-            const int S = sched.k_splits;
-            constexpr int BAND_ROWS = 32, BAND_BYTES = BAND_ROWS * 128 * 4, BUF_BYTES = 6 * BAND_BYTES;
-            const float* ws_tile = p.ws + (long long)tile * S * (BM * 128);
-            auto issue = [&](int band) {
-              uint64_t* bar = &rbar[band & 1];
-              mbar_arrive_expect_tx(bar, (uint32_t)(S * BAND_BYTES));
-              for (int sp = 0; sp < S; ++sp)
-                bulk_load(smem + (band & 1) * BUF_BYTES + sp * BAND_BYTES,
-                          ws_tile + ((long long)sp * BM + band * BAND_ROWS) * 128, BAND_BYTES, bar);
-            };
-            if (et == 0) {
-              issue(0);
-              issue(1);
-            }
-            bool rok = true;
-#pragma unroll 1
-            for (int band = 0; band < BM / BAND_ROWS; ++band) {
-              if (!mbar_wait(&rbar[band & 1], (band >> 1) & 1)) {
-                report_error(p.status, ERR_WAIT_FULL, 2000 + band);
-                rok = false;
+            const long long ldw4 = (long long)sched.num_n * BN / 4;            // float4 per padded row
+            const long long slice4 = (long long)sched.num_m * BM * ldw4;       // float4 per slice
+            const long long per = (slice4 + gridDim.x - 1) / gridDim.x;
+            const long long lo = (long long)blockIdx.x * per, hi = min(lo + per, slice4);
+            const int cap = (SmemLayout<BN>::BAR_OFFSET / 16) / S;              // float4 of one slice per round
+            const float4* ws4 = reinterpret_cast<const float4*>(p.ws);
+            float4* buf = reinterpret_cast<float4*>(smem);
+            uint32_t rphase = 0;
+            for (long long r0 = lo; r0 < hi; r0 += cap) {
+              const int n = (int)min((long long)cap, hi - r0);
+              if (et == 0) {
+                mbar_arrive_expect_tx(&rbar[0], (uint32_t)(S * n * 16));
+                for (int sp = 0; sp < S; ++sp) bulk_load(buf + (long long)sp * n, ws4 + sp * slice4 + r0, n * 16, &rbar[0]);
               }
-              const uint8_t* buf = smem + (band & 1) * BUF_BYTES;
-              const int g = et & 31, rs = et >> 5;
-              const int col = n_first * 128 + g * 4;
-              if (rok) {
-#pragma unroll
-                for (int j = 0; j < BAND_ROWS / 4; ++j) {
-                  const int rb = rs + 4 * j;
-                  float4 acc = *reinterpret_cast<const float4*>(buf + rb * 512 + g * 16);
-                  for (int sp = 1; sp < S; ++sp) {
-                    const float4 v = *reinterpret_cast<const float4*>(buf + sp * BAND_BYTES + rb * 512 + g * 16);
-                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-                  }
-                  const int orow = m_blk * BM + band * BAND_ROWS + rb;
-                  if (orow < p.M && col < p.N) epi_store4(p, orow, col, acc);
+              if (!mbar_wait(&rbar[0], rphase)) {
+                report_error(p.status, ERR_WAIT_FULL, 2000);
+                break;
+              }
+              rphase ^= 1;
+              for (int i = et; i < n; i += 128) {
+                float4 acc = buf[i];
+                for (int sp = 1; sp < S; ++sp) {
+                  const float4 v = buf[sp * n + i];
+                  acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                 }
+                const long long f = r0 + i;
+                const int orow = (int)(f / ldw4), ocol = (int)(f % ldw4) * 4;
+                if (orow < p.M && ocol < p.N) epi_store4(p, orow, ocol, acc);
               }
-              asm volatile("bar.sync 1, 128;" ::: "memory");  // the buffer is free again
-              if (et == 0 && rok && band + 2 < BM / BAND_ROWS) issue(band + 2);
+              asm volatile("bar.sync 1, 128;" ::: "memory");  // the staging area is free for the next round
             }
-            if (threadIdx.x == 64) p.counters[tile] = 0;
+          }
+          if (et == 0) {
+            const unsigned left = atomicAdd(reinterpret_cast<unsigned*>(p.counters) + 1, 1u);
+            if (left == gridDim.x - 1) {
+              p.counters[0] = 0;
+              p.counters[1] = 0;
+            }
           }
         }
       }
@@ -917,6 +929,21 @@ static int launch_gemm(const void* A, const void* B, long long lda, long long ld
   const int units = (EPI == EPI_LSE) ? num_m * p.num_splits : num_m * num_n * (p.k_splits > 1 ? p.k_splits : 1);
   if (units <= 0) return 0;
   const int grid = units < vb_num_sms() ? units : vb_num_sms();
+  if (EPI == EPI_STORE && p.k_splits > 1) {
+    // the split-K reduction has a grid-wide barrier: every CTA owns one unit and all of them must be resident
+    if (units > vb_num_sms()) return -3;
+    void* args[] = {(void*)&tmA, (void*)&tmB, (void*)&p};
+    cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3(units), dim3(NUM_THREADS), args, L::DYN_BYTES, stream);
+    if (e != cudaSuccess) {
+      // e.g. a capture mode that refuses cooperative nodes: a plain launch of at most one CTA per SM is resident as
+      // a whole on an otherwise idle device, and the barrier's wait is bounded in any case
+      (void)cudaGetLastError();
+      kern<<<units, NUM_THREADS, L::DYN_BYTES, stream>>>(tmA, tmB, p);
+      e = cudaGetLastError();
+    }
+    vb_count_launch();
+    return (int)e;
+  }
   kern<<<grid, NUM_THREADS, L::DYN_BYTES, stream>>>(tmA, tmB, p);
   vb_count_launch();
   return (int)cudaGetLastError();
@@ -946,23 +973,45 @@ extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void
   p.C = C; p.ldc = ldc; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.out_fp32 = out_fp32; p.accumulate = accumulate; p.status = status;
   p.k_splits = 1;
-  if (ws != nullptr && counters != nullptr) {
-    // split-K on 128-wide tiles when even those leave most SMs idle and K is deep enough to cut
-    const int nm = (M + BM - 1) / BM, nn = (N + 127) / 128, nkb = (K + BK - 1) / BK;
-    const int tiles128 = nm * nn;
-    int splits = vb_num_sms() / (tiles128 > 0 ? tiles128 : 1);
-    if (splits > nkb / 4) splits = nkb / 4;
-    if (splits > 6) splits = 6;  // the reducing CTA stages 6 slices x 32 rows per buffer
-    if (N > 128 && splits >= 2 && tiles128 <= num_counters) {
-      const int per = (nkb + splits - 1) / splits;
+  static const int splitk_mode = []() {
+    const char* e = getenv("VERL_B200_SPLITK");  // 0 = never split K, N > 1 = force that many slices (experiments)
+    return e ? atoi(e) : -1;
+  }();
+  if (ws != nullptr && counters != nullptr && splitk_mode != 0) {
+    // Split K when the output tiles alone leave most SMs idle and K is deep enough to cut. 128-wide tiles by
+    // default; VERL_B200_SPLITK_BN=256 selects 256-wide ones (fewer re-reads of A, but more slices to reduce).
+    static const int force_bn = []() {
+      const char* e = getenv("VERL_B200_SPLITK_BN");
+      return e ? atoi(e) : 0;
+    }();
+    const int nm = (M + BM - 1) / BM, nkb = (K + BK - 1) / BK;
+    auto plan = [&](int bn, int& splits, int& per) {
+      const int tiles = nm * ((N + bn - 1) / bn);
+      splits = vb_num_sms() / (tiles > 0 ? tiles : 1);
+      if (splits > nkb / 4) splits = nkb / 4;
+      if (splits > 16) splits = 16;
+      if (splitk_mode > 1) splits = splitk_mode;
+      if (splits < 2) { splits = 1; per = nkb; return; }
+      per = (nkb + splits - 1) / splits;
       splits = (nkb + per - 1) / per;
-      const long long need = (long long)splits * nm * BM * nn * 128 * 4;
-      if (splits >= 2 && need <= ws_bytes) {
+    };
+    int s256, p256, s128, p128;
+    plan(256, s256, p256);
+    plan(128, s128, p128);
+    int bn_sk = 128;
+    if (force_bn == 256 && s256 >= 2) bn_sk = 256;  // measured slower on the 7B decode shapes (more slices to reduce)
+    const int splits = bn_sk == 256 ? s256 : s128, per = bn_sk == 256 ? p256 : p128;
+    const int nn = (N + bn_sk - 1) / bn_sk;
+    if (N > 128 && splits >= 2 && nm * nn * splits <= vb_num_sms() && num_counters >= 2) {
+      const long long need = (long long)splits * nm * BM * nn * bn_sk * 4;
+      if (need <= ws_bytes) {
         p.k_splits = splits;
         p.kb_per_split = per;
         p.ws = ws;
         p.counters = counters;
-#define VB_SPLITK(AMN, BMN) launch_gemm<128, AMN, BMN, EPI_STORE>(A, B, lda, ldb, p, stream)
+#define VB_SPLITK(AMN, BMN)                                                                  \
+  (bn_sk == 256 ? launch_gemm<256, AMN, BMN, EPI_STORE>(A, B, lda, ldb, p, stream)             \
+                : launch_gemm<128, AMN, BMN, EPI_STORE>(A, B, lda, ldb, p, stream))
         if (!a_mn && !b_mn) return VB_SPLITK(false, false);
         if (!a_mn && b_mn) return VB_SPLITK(false, true);
         if (a_mn && b_mn) return VB_SPLITK(true, true);
