@@ -460,3 +460,49 @@ def test_flash_attention_fwd_with_cached_prefix():
         mask = torch.arange(lk[b], device="cuda")[None, :] <= (torch.arange(lq[b], device="cuda")[:, None] + lk[b] - lq[b])
         ref = (torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ vs).transpose(0, 1)
         _bf16_close(out[cu_q[b]:cu_q[b + 1]], ref, ulps=4)
+
+
+def test_moe_grouped_gemm_matches_expert_loop():
+    """Grouped GEMM path of the MoE MLP (one launch per projection, device-side routing layout) against the
+    per-expert fp32 reference: outputs, input gradients, weight gradients (also fused into main_grad)."""
+    from verl_b200 import ops
+    from verl_b200.ops.moe import moe_mlp
+
+    torch.manual_seed(14)
+    T, H, I, E, k = 300, 256, 192, 8, 2
+    x = torch.randn(T, H, device="cuda").bfloat16().requires_grad_(True)
+    gate_up = (torch.randn(E, 2 * I, H, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    down = (torch.randn(E, H, I, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    logits = torch.randn(T, E, device="cuda")
+    logits[:, 5] = -1e9  # an expert without tokens
+    top_w, top_i = torch.topk(torch.softmax(logits, -1), k, -1)
+    top_w = (top_w / top_w.sum(-1, keepdim=True)).detach()
+    dy = torch.randn(T, H, device="cuda").bfloat16()
+    y = moe_mlp(x, top_i, top_w, gate_up, down, ops.swiglu)
+    y.backward(dy)
+    xr, gr, dr = (t.detach().float().requires_grad_(True) for t in (x, gate_up, down))
+    ref = torch.zeros(T, H, device="cuda")
+    for j in range(k):
+        for e in range(E):
+            sel = top_i[:, j] == e
+            if sel.any():
+                gu = xr[sel] @ gr[e].t()
+                h = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+                ref[sel] = ref[sel] + (h @ dr[e].t()) * top_w[sel, j : j + 1].float()
+    ref.backward(dy.float())
+
+    def close(a, b, tol):
+        err = (a.float() - b).abs().max().item()
+        assert err <= tol * max(1.0, b.abs().max().item()), (err, b.abs().max().item())
+
+    close(y, ref.detach(), 2e-2)
+    close(x.grad, xr.grad, 3e-2)
+    close(gate_up.grad, gr.grad, 3e-2)
+    close(down.grad, dr.grad, 3e-2)
+    assert float(gate_up.grad[5].abs().sum()) == 0.0
+    # fused accumulation into fp32 main_grad
+    g2 = gate_up.detach().clone().requires_grad_(True)
+    g2.main_grad = torch.ones(g2.shape, device="cuda")
+    moe_mlp(x.detach(), top_i, top_w, g2, down.detach(), ops.swiglu).backward(dy)
+    assert g2.grad is None
+    close(g2.main_grad - 1.0, gr.grad, 3e-2)

@@ -62,6 +62,14 @@ struct GemmParams {
   // the sharded flat vector lives on rank e / ag_shard at offset e % ag_shard; W starts at element ag_w_off.
   // ag_ready[nb] counts the CTAs that have copied their slice of rows [nb*BN, (nb+1)*BN); a tile may load its B
   // operand once the count reaches the grid size.
+  // Grouped GEMM (mixture-of-experts). grp_mode 1: the rows of A come in 128-row blocks, block b belongs to expert
+  // grp_blk_expert[b] (< 0: unused block) and is multiplied by that expert's matrix, B = [E, N, K] (or [E, K, N]
+  // for an MN-major B). grp_mode 2 (weight gradients): C = [E, M, N], unit (e, tile) contracts over the rows
+  // [grp_off[e], grp_off[e+1]) of A and B (multiples of 64) and adds into C[e] (accumulate must be set).
+  int grp_mode;
+  int grp_E;
+  const int* grp_blk_expert;
+  const int* grp_off;
   const void* ag_src[AG_MAX_RANKS];
   long long ag_shard;
   long long ag_w_off;
@@ -100,6 +108,7 @@ struct Sched {
       nblk_per_split = 1;
       num_splits = num_n;
       num_units = num_m * num_n * k_splits;
+      if (p.grp_mode == 2) num_units *= p.grp_E;
     }
   }
   // k-block range [kb0, kb1) and k slice of unit u (the k slice is the fastest-varying part of u)
@@ -208,6 +217,36 @@ __device__ __forceinline__ void epi_store4(const GemmParams& p, int row, int col
   }
 }
 
+
+// Grouped-GEMM view of unit u: returns false when the unit has no work. On success `u` is the tile index inside the
+// expert (mode 2), b_off the row offset of the expert's matrix in B, c_off the row offset of its output in C.
+struct GroupView {
+  int e, b_off, c_off, kb0, kb1;
+};
+template <bool B_MN>
+__device__ __forceinline__ bool group_view(const GemmParams& p, const Sched& sched, int& u, GroupView& g) {
+  g.e = 0; g.b_off = 0; g.c_off = 0; g.kb0 = -1; g.kb1 = -1;
+  if (p.grp_mode == 2) {
+    const int per_e = sched.num_m * sched.num_n;
+    g.e = u / per_e;
+    u -= g.e * per_e;
+    g.kb0 = p.grp_off[g.e] / BK;
+    g.kb1 = p.grp_off[g.e + 1] / BK;
+    g.c_off = g.e * p.M;
+    return g.kb1 > g.kb0;
+  }
+  return true;
+}
+template <bool B_MN>
+__device__ __forceinline__ bool group_rows(const GemmParams& p, int m_blk, GroupView& g) {
+  if (p.grp_mode == 1) {
+    g.e = p.grp_blk_expert[m_blk];
+    if (g.e < 0) return false;
+    g.b_off = g.e * (B_MN ? p.K : p.N);
+  }
+  return true;
+}
+
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(EPI == EPI_STORE_AG ? NUM_THREADS + AG_COPY_THREADS : NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -259,11 +298,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int u = blockIdx.x; ok && u < sched.num_units; u += gridDim.x) {
+      for (int uu = blockIdx.x; ok && uu < sched.num_units; uu += gridDim.x) {
+        int u = uu;
+        GroupView gv;
+        if (!group_view<B_MN>(p, sched, u, gv)) continue;
         int m_blk, n_first, n_count, split;
         sched.get(u, m_blk, n_first, n_count, split);
+        if (!group_rows<B_MN>(p, m_blk, gv)) continue;
         int ks, kb0, kb1;
         sched.k_range(u, ks, kb0, kb1);
+        if (gv.kb0 >= 0) { kb0 = gv.kb0; kb1 = gv.kb1; }
         for (int nb = n_first; ok && nb < n_first + n_count; ++nb) {
           if (EPI == EPI_STORE_AG) {
             // rows [nb*BN, (nb+1)*BN) of B must have arrived from all ranks (every CTA copies a slice of them)
@@ -303,9 +347,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (B_MN) {
 #pragma unroll
               for (int j = 0; j < BN / 64; ++j)
-                tma_load_2d(b_dst + j * (BK * 128), &tmB, &full[s], nb * BN + j * 64, kb * BK);
+                tma_load_2d(b_dst + j * (BK * 128), &tmB, &full[s], nb * BN + j * 64, gv.b_off + kb * BK);
             } else {
-              tma_load_2d(b_dst, &tmB, &full[s], kb * BK, nb * BN);
+              tma_load_2d(b_dst, &tmB, &full[s], kb * BK, gv.b_off + nb * BN);
             }
             if (++s == L::STAGES) {
               s = 0;
@@ -324,11 +368,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int u = blockIdx.x; ok && u < sched.num_units; u += gridDim.x) {
+      for (int uu = blockIdx.x; ok && uu < sched.num_units; uu += gridDim.x) {
+        int u = uu;
+        GroupView gv;
+        if (!group_view<B_MN>(p, sched, u, gv)) continue;
         int m_blk, n_first, n_count, split;
         sched.get(u, m_blk, n_first, n_count, split);
+        if (!group_rows<B_MN>(p, m_blk, gv)) continue;
         int ks, kb0, kb1;
         sched.k_range(u, ks, kb0, kb1);
+        if (gv.kb0 >= 0) { kb0 = gv.kb0; kb1 = gv.kb1; }
         for (int nb = n_first; ok && nb < n_first + n_count; ++nb) {
           if (*abort_flag || !mbar_wait(&tempty[acc], acc_phase ^ 1)) {
             report_error(p.status, ERR_WAIT_TMEM_EMPTY, nb);
@@ -414,13 +463,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int u = blockIdx.x; ok && u < sched.num_units; u += gridDim.x) {
+    for (int uu = blockIdx.x; ok && uu < sched.num_units; uu += gridDim.x) {
+      int u = uu;
+      GroupView gv;
+      if (!group_view<B_MN>(p, sched, u, gv)) continue;
       int m_blk, n_first, n_count, split;
       sched.get(u, m_blk, n_first, n_count, split);
+      if (!group_rows<B_MN>(p, m_blk, gv)) continue;
       int ks, kb0, kb1;
       sched.k_range(u, ks, kb0, kb1);
-      const int row = m_blk * BM + row_in_tile;
-      const bool row_ok = row < p.M;
+      const bool row_ok = m_blk * BM + row_in_tile < p.M;
+      const int row = gv.c_off + m_blk * BM + row_in_tile;  // grouped weight gradients: row inside C = [E * M, N]
 
       // per-row state for the fused epilogues
       float run_max = -INFINITY, run_sum = 0.f, run_dot = 0.f, label_logit = 0.f;
@@ -1058,6 +1111,71 @@ extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void
   if (a_mn && b_mn) return VB_DISPATCH(true, true);
   return VB_DISPATCH(true, false);
 #undef VB_DISPATCH
+}
+
+// Grouped GEMM for mixture-of-experts layers, one launch for all experts.
+//   mode 1 (forward / input gradients): A [P, K] holds the routed tokens sorted by expert, every expert's rows padded
+//     to a multiple of 128; blk_expert[P / 128] names the expert of each 128-row block (< 0: unused block, skipped).
+//     b_mn = 0: B = [E, N, K], C[rows of e] = A . B[e]^T;  b_mn = 1: B = [E, K, N], C = A . B[e].
+//   mode 2 (weight gradients): A stored [P, M], B stored [P, N] (a_mn = b_mn = 1), C = [E, M, N] fp32,
+//     C[e] += A[rows of e]^T . B[rows of e]; expert_off[E + 1] are the padded row offsets (multiples of 128).
+// N (K for b_mn) must be a multiple of 64 in mode 1 so that a tile never reads the next expert's matrix into the
+// contraction; M, N arbitrary otherwise. Nothing is read back to the host: routing stays on the device.
+extern "C" int vb_grouped_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                    long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32, int accumulate,
+                                    int mode, int E, const int* blk_expert, const int* expert_off, int* status,
+                                    cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || E <= 0) return 0;
+  if ((lda & 7) || (ldb & 7)) return -3;
+  if (mode == 1 && (a_mn || blk_expert == nullptr || (M % BM) != 0 || ((b_mn ? K : N) % 64) != 0)) return -3;
+  if (mode == 2 && (!a_mn || !b_mn || !out_fp32 || !accumulate || expert_off == nullptr)) return -3;
+  if (mode != 1 && mode != 2) return -3;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.out_fp32 = out_fp32; p.accumulate = accumulate; p.status = status;
+  p.k_splits = 1;
+  p.grp_mode = mode; p.grp_E = E; p.grp_blk_expert = blk_expert; p.grp_off = expert_off;
+  // the tensor map of B spans all experts: [E * rows, cols]
+  GemmParams q = p;
+  const bool wide = N >= 512;
+  if (mode == 1) {
+    // B extents for the descriptor: K-major [E * N, K]; MN-major [E * K, N]
+    if (!b_mn) { q.N = E * N; } else { q.K = E * K; }
+  }
+  CUtensorMap tmA, tmB;
+  int rc;
+  const int bn = wide ? 256 : 128;
+  if (a_mn) rc = vb_make_tmap_2d(&tmA, A, 2, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)lda * 2, 64, BK);
+  else rc = vb_make_tmap_2d(&tmA, A, 2, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)lda * 2, BK, BM);
+  if (rc) return rc;
+  if (b_mn) rc = vb_make_tmap_2d(&tmB, B, 2, (uint64_t)q.N, (uint64_t)q.K, (uint64_t)ldb * 2, 64, BK);
+  else rc = vb_make_tmap_2d(&tmB, B, 2, (uint64_t)q.K, (uint64_t)q.N, (uint64_t)ldb * 2, BK, bn);
+  if (rc) return rc;
+  const int num_m = (M + BM - 1) / BM, num_n = (N + bn - 1) / bn;
+  long long units = (long long)num_m * num_n * (mode == 2 ? E : 1);
+  if (units <= 0) return 0;
+  const int grid = units < vb_num_sms() ? (int)units : vb_num_sms();
+#define VB_GRP(BNV, AMN, BMN)                                                                                     \
+  do {                                                                                                            \
+    auto kern = gemm_kernel<BNV, AMN, BMN, EPI_STORE>;                                                            \
+    static bool attr_set = false;                                                                                 \
+    if (!attr_set) {                                                                                              \
+      VB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BNV>::DYN_BYTES)); \
+      attr_set = true;                                                                                            \
+    }                                                                                                             \
+    kern<<<grid, NUM_THREADS, SmemLayout<BNV>::DYN_BYTES, stream>>>(tmA, tmB, p);                                 \
+  } while (0)
+  if (mode == 2) {
+    if (wide) VB_GRP(256, true, true); else VB_GRP(128, true, true);
+  } else if (!b_mn) {
+    if (wide) VB_GRP(256, false, false); else VB_GRP(128, false, false);
+  } else {
+    if (wide) VB_GRP(256, false, true); else VB_GRP(128, false, true);
+  }
+#undef VB_GRP
+  vb_count_launch();
+  return (int)cudaGetLastError();
 }
 
 // Fused all-gather + GEMM: C[M,N] = A . W^T where W [N,K] is not there yet. Every rank holds a contiguous slice

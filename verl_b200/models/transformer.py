@@ -121,27 +121,36 @@ class MoEMLP(nn.Module):
         if self.norm_topk:
             top_w = top_w / top_w.sum(-1, keepdim=True)
         self.last_routing = top_i.detach()
+        if x.is_cuda and I_ok(self.gate_up_proj, self.down_proj):
+            # one grouped GEMM per projection for all experts, routing layout computed on the device
+            from ..ops.moe import moe_mlp
+
+            return moe_mlp(x, top_i, top_w, self.gate_up_proj, self.down_proj, ops.swiglu)
         flat_e = top_i.flatten()
         order = torch.argsort(flat_e, stable=True)
         tok = order // self.k
         counts = torch.bincount(flat_e, minlength=self.E).tolist()
         xs = x[tok]
-        outs = torch.empty(xs.shape[0], H, dtype=x.dtype, device=x.device)
-        start = 0
         pieces = []
+        start = 0
         for e, n in enumerate(counts):
             if n == 0:
                 continue
             seg = xs[start : start + n]
-            # pad the slice to a multiple of 8 rows so the transposed (weight-gradient) operand stays 16-byte aligned
             h = ops.swiglu(ops.linear(seg, self.gate_up_proj[e]))
             pieces.append(ops.linear(h, self.down_proj[e]))
             start += n
-        outs = torch.cat(pieces, dim=0) if pieces else outs
+        outs = torch.cat(pieces, dim=0) if pieces else torch.empty(0, H, dtype=x.dtype, device=x.device)
         w = top_w.flatten()[order].to(x.dtype).unsqueeze(-1)
         y = torch.zeros(T, H, dtype=x.dtype, device=x.device)
         y.index_add_(0, tok, outs * w)
         return y
+
+
+def I_ok(gate_up: torch.Tensor, down: torch.Tensor) -> bool:
+    """Grouped-GEMM constraints: bf16, contraction lengths multiples of 64."""
+    return (gate_up.dtype == torch.bfloat16 and gate_up.shape[1] % 64 == 0 and gate_up.shape[2] % 64 == 0
+            and down.shape[1] % 64 == 0 and down.shape[2] % 64 == 0)
 
 
 class Attention(nn.Module):
