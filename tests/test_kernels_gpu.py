@@ -506,3 +506,32 @@ def test_moe_grouped_gemm_matches_expert_loop():
     moe_mlp(x.detach(), top_i, top_w, g2, down.detach(), ops.swiglu).backward(dy)
     assert g2.grad is None
     close(g2.main_grad - 1.0, gr.grad, 3e-2)
+
+
+def test_bounded_device_wait_reports_status_and_context_survives():
+    """A cross-rank barrier whose peer never arrives: the kernel gives up after its time limit, records the wait in
+    the status word and returns; the host reads the code and the context keeps working."""
+    import ctypes
+    import time
+
+    from verl_b200.ops import _lib, gemm
+
+    lib = _lib.load()
+    lib.vb_peer_barrier.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_uint, ctypes.c_void_p,
+                                    ctypes.c_void_p]
+    lib.vb_peer_barrier.restype = ctypes.c_int
+    _lib.clear_status("cuda")
+    mine = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    absent = torch.zeros(1024, dtype=torch.int32, device="cuda")  # stands for a peer that never writes its slot
+    pads = (ctypes.c_void_p * 2)(mine.data_ptr(), absent.data_ptr())
+    t0 = time.perf_counter()
+    rc = lib.vb_peer_barrier(pads, 0, 2, 3, 1, _lib.status_word("cuda").data_ptr(), _lib.stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    code, _, detail = _lib.read_status("cuda")
+    assert code == 5 and detail == 1, (code, detail)   # ERR_WAIT_FLAG, waiting for rank 1
+    assert 1.0 < dt < 10.0
+    _lib.clear_status("cuda")
+    a = torch.randn(256, 256, device="cuda").bfloat16()
+    _bf16_close(gemm(a, a), a.float() @ a.float().t())
