@@ -418,20 +418,24 @@ def test_flash_attention_fwd(lens, Hq, Hk, causal):
     torch.testing.assert_close(lse, ref_lse, atol=2e-3, rtol=1e-4)
 
 
-def test_flash_attention_autograd_matches_reference():
+@pytest.mark.parametrize("lens,Hq,Hk,causal", [([200, 131, 64], 8, 2, True), ([513, 1], 4, 4, True), ([300, 77], 28, 4, True),
+                                               ([260], 4, 2, False)])
+def test_flash_attention_autograd_matches_reference(lens, Hq, Hk, causal):
     from verl_b200 import ops
+    from verl_b200.ops import _lib
 
     torch.manual_seed(12)
-    lens, Hq, Hk, D = [200, 131, 64], 8, 2, 128
+    D = 128
     T = sum(lens)
     q = torch.randn(T, Hq, D, device="cuda").bfloat16().requires_grad_(True)
     k = torch.randn(T, Hk, D, device="cuda").bfloat16().requires_grad_(True)
     v = torch.randn(T, Hk, D, device="cuda").bfloat16().requires_grad_(True)
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
     do = torch.randn(T, Hq, D, device="cuda").bfloat16()
-    ops.attention_varlen(q, k, v, cu, max(lens), causal=True, impl="native").backward(do)
+    ops.attention_varlen(q, k, v, cu, max(lens), causal=causal, impl="native").backward(do)
+    assert _lib.read_status("cuda")[0] == 0
     qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
-    ref, _ = _attn_ref(qr, kr, vr, cu, True, D ** -0.5)
+    ref, _ = _attn_ref(qr, kr, vr, cu, causal, D ** -0.5)
     ref.backward(do.float())
     for got, want in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
         err = (got.float() - want).abs().max().item()

@@ -1,10 +1,8 @@
 """Attention entry points.
 
 * :func:`attention_varlen` — causal GQA attention over packed (remove-padding) sequences for
-  training and prefill. On CUDA the forward is this package's tcgen05 kernel (head_dim 128; every
-  no-grad pass — prefill, log-prob recomputation, the checkpointed forward — runs on it alone). The
-  backward still calls the ``flash_attn`` varlen backward (library code) with the ``out`` / ``lse`` that our
-  forward produced; other head dims use the library for both (the reference does so for everything through HF
+  training and prefill. On CUDA forward and backward are this package's tcgen05 kernels (head_dim 128);
+  other head dims fall back to the ``flash_attn`` library (the reference uses it for everything through HF
   ``attn_implementation=flash_attention_2``, verl/workers/fsdp_workers.py:331). CPU: per-sequence SDPA loop.
 * :func:`paged_decode_attention` / :func:`kv_cache_write` — the hand-written paged-KV decode
   path of the native rollout engine.
@@ -51,8 +49,30 @@ def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: tor
     return out, lse
 
 
+def flash_bwd(q, k, v, out, lse, dout, cu_seqlens, max_seqlen: int, causal: bool, scale: float):
+    """tcgen05 backward: (dq [T,Hq,128], dk, dv [T,Hk,128]) from the forward's ``out`` and ``lse`` [Hq,T]."""
+    T, Hq, D = q.shape
+    Hk = k.shape[1]
+    dout = dout if (dout.stride(2) == 1 and dout.stride(1) == D) else dout.contiguous()
+    delta = torch.empty((Hq, T), dtype=torch.float32, device=q.device)
+    dq = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
+    dk = torch.empty((T, Hk, D), dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty_like(dk)
+    st, stream = _lib.status_word(q.device).data_ptr(), _lib.stream()
+    B = cu_seqlens.numel() - 1
+    rc = _lib.fn("vb_flash_bwd_delta")(out.data_ptr(), dout.data_ptr(), out.stride(0), dout.stride(0), delta.data_ptr(), T, Hq, stream)
+    _lib.check(rc, "vb_flash_bwd_delta")
+    common = (q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr(), q.stride(0), k.stride(0), v.stride(0), dout.stride(0),
+              cu_seqlens.data_ptr(), B, T, int(max_seqlen), Hq, Hk, float(scale), int(causal), lse.data_ptr(), delta.data_ptr())
+    rc = _lib.fn("vb_flash_bwd_dq")(*common, dq.data_ptr(), dq.stride(0), st, stream)
+    _lib.check(rc, "vb_flash_bwd_dq")
+    rc = _lib.fn("vb_flash_bwd_dkv")(*common, dk.data_ptr(), dv.data_ptr(), dk.stride(0), st, stream)
+    _lib.check(rc, "vb_flash_bwd_dkv")
+    return dq, dk, dv
+
+
 class _FlashVarlenFn(torch.autograd.Function):
-    """Own forward; backward through the library's varlen backward kernel (same ``lse`` layout [Hq, T])."""
+    """Own forward and backward kernels (head_dim 128)."""
 
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale):
@@ -63,14 +83,21 @@ class _FlashVarlenFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward  # library kernel
-
         q, k, v, out, lse, cu = ctx.saved_tensors
-        qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
-        dq, dk, dv = torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc)
-        _flash_attn_varlen_backward(dout.contiguous(), qc, kc, vc, out, lse, dq, dk, dv, cu, cu, ctx.max_seqlen,
-                                    ctx.max_seqlen, 0.0, ctx.scale, ctx.causal, -1, -1, 0.0, None, False, None)
+        if _BWD_IMPL == "library":
+            from flash_attn.flash_attn_interface import _flash_attn_varlen_backward  # library kernel
+
+            qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+            dq, dk, dv = torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc)
+            _flash_attn_varlen_backward(dout.contiguous(), qc, kc, vc, out, lse, dq, dk, dv, cu, cu, ctx.max_seqlen,
+                                        ctx.max_seqlen, 0.0, ctx.scale, ctx.causal, -1, -1, 0.0, None, False, None)
+            return dq, dk, dv, None, None, None, None
+        dq, dk, dv = flash_bwd(q, k, v, out, lse, dout, cu, ctx.max_seqlen, ctx.causal, ctx.scale)
         return dq, dk, dv, None, None, None, None
+
+
+# "native" (default) or "library": which backward the autograd wrapper uses (the library one is kept for comparisons)
+_BWD_IMPL = __import__("os").environ.get("VERL_B200_ATTN_BWD", "native")
 
 
 def _native_fwd_ok(q, k, v) -> bool:

@@ -128,6 +128,24 @@ def bench_attn(a):
         if a.library:
             us2 = _time(lambda: attention_varlen(q, k, v, cu, S, causal=True, impl="library"), a.iters, a.warmup, graph=False)
             out.update(library_us=round(us2, 1), library_tflops=round(flops / us2 / 1e6, 1))
+    # backward (dQ, dK, dV; 2.5x the forward FLOPs), ours and the library's
+    from . import attention as att
+
+    do = torch.randn(T, Hq, D, device=dev, dtype=torch.bfloat16)
+    qg, kg, vg = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    for name in (["native", "library"] if a.library else ["native"]):
+        att._BWD_IMPL = name
+
+        def fb():
+            o = attention_varlen(qg, kg, vg, cu, S, causal=True, impl="native")
+            o.backward(do)
+            qg.grad = kg.grad = vg.grad = None
+
+        us3 = _time(fb, a.iters, a.warmup, graph=False)
+        key = "fwd_bwd" if name == "native" else "fwd_bwd_library_bwd"
+        out[key + "_us"] = round(us3, 1)
+        out[key + "_tflops"] = round(3.5 * flops / us3 / 1e6, 1)
+    att._BWD_IMPL = "native"
     return out
 
 
