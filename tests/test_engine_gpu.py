@@ -100,3 +100,26 @@ def test_rollout_graph_matches_eager_and_training_logprobs(kind):
             # for exactly this); the bulk of the tokens has to agree
             lim = diff.quantile(0.9) if kind == "moe" else diff.max()
             assert lim < 0.1 and diff.mean() < (0.05 if kind == "moe" else 0.02), (float(diff.max()), float(diff.mean()))
+
+
+def test_fp8_rollout_close_to_bf16_rollout():
+    """``quantization="fp8"``: greedy continuations mostly agree with the bf16 engine and the log-probs stay close."""
+    from verl_b200.models.transformer import CausalLM
+    from verl_b200.rollout import NativeRolloutEngine, SamplingParams
+
+    cfg = _cfg("dense")
+    m = CausalLM(cfg, dtype=torch.bfloat16, device="cuda")
+    m.init_weights(2)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 170, 300)]
+    res = {}
+    for q in (None, "fp8"):
+        eng = NativeRolloutEngine(m, max_num_seqs=8, max_model_len=512, max_num_batched_tokens=1024, gpu_memory_utilization=0.1,
+                                  seed=5, quantization=q)
+        assert (len(eng._fp8) > 0) == (q == "fp8")
+        res[q] = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+        del eng
+    first_lp = [abs(a.log_probs[0] - b.log_probs[0]) for a, b in zip(res[None], res["fp8"])]
+    assert max(first_lp) < 0.25, first_lp
+    same_first = sum(a.token_ids[0] == b.token_ids[0] for a, b in zip(res[None], res["fp8"]))
+    assert same_first >= 2

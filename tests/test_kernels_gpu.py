@@ -539,3 +539,37 @@ def test_bounded_device_wait_reports_status_and_context_survives():
     _lib.clear_status("cuda")
     a = torch.randn(256, 256, device="cuda").bfloat16()
     _bf16_close(gemm(a, a), a.float() @ a.float().t())
+
+
+@pytest.mark.parametrize("M,N,K,pow2", [(128, 512, 1024, False), (300, 384 + 64, 640, True), (1000, 256, 3584, False)])
+def test_fp8_blockscale_quant_and_gemm(M, N, K, pow2):
+    from verl_b200.ops import _lib, fp8
+
+    torch.manual_seed(15)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    wq, sw = fp8.quantize_weight(w, pow2)
+    xq, sx = fp8.quantize_activation(x, pow2)
+    # quantisation agrees with the plain PyTorch statement of the scheme
+    wq_ref, sw_ref = fp8.quantize_weight(w.cpu(), pow2)
+    xq_ref, sx_ref = fp8.quantize_activation(x.cpu(), pow2)
+    torch.testing.assert_close(sw.cpu(), sw_ref, rtol=1e-6, atol=0)
+    torch.testing.assert_close(sx.cpu(), sx_ref, rtol=1e-6, atol=0)
+    for got, want in ((wq, wq_ref), (xq, xq_ref)):
+        a, b = got.cpu().float(), want.float()
+        # the kernel multiplies by a fast reciprocal: values next to a rounding boundary may land on the neighbouring
+        # e4m3 code (one step = 1/8 relative), nothing may be further off
+        assert (a != b).float().mean() < 0.02
+        assert ((a - b).abs() <= 0.126 * torch.maximum(a.abs(), b.abs()) + 2 ** -9).all()
+    if pow2:
+        assert torch.equal(torch.log2(sw), torch.log2(sw).round())
+    # GEMM against the dequantised fp32 product, and loosely against the unquantised one
+    out = fp8.fp8_gemm(xq, sx, wq, sw, bias)
+    assert _lib.read_status("cuda")[0] == 0
+    ref = fp8.dequantize(xq, sx, False) @ fp8.dequantize(wq, sw, True).t() + bias.float()
+    _bf16_close(out, ref, ulps=4)
+    full = x.float() @ w.float().t() + bias.float()
+    rel = (out.float() - full).norm() / full.norm()
+    assert rel < 0.06, float(rel)
+    _bf16_close(fp8.fp8_linear(x, wq, sw, bias, pow2), ref, ulps=4)

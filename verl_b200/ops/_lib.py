@@ -51,6 +51,9 @@ _SIGS = {
     # attention
     "vb_decode_num_splits": ([I, I, I], I),
     "vb_grouped_gemm_bf16": ([P, P, P, I, I, I, L, L, L, I, I, I, I, I, I, P, P, P, P], I),
+    "vb_fp8_quant_weight": ([P, L, I, I, P, L, P, I, P], I),
+    "vb_fp8_quant_act": ([P, L, L, I, P, L, P, I, P], I),
+    "vb_fp8_gemm_blockscale": ([P, P, P, P, P, P, I, I, I, L, L, L, P, P], I),
     "vb_flash_bwd_delta": ([P, P, L, L, P, L, I, P], I),
     "vb_flash_bwd_dq": ([P, P, P, P, L, L, L, L, P, I, L, I, I, I, F, I, P, P, P, L, P, P], I),
     "vb_flash_bwd_dkv": ([P, P, P, P, L, L, L, L, P, I, L, I, I, I, F, I, P, P, P, P, L, P, P], I),

@@ -166,8 +166,13 @@ class NativeRolloutEngine:
     def __init__(self, model: CausalLM, *, max_num_seqs: int = 256, max_model_len: int = 2048,
                  max_num_batched_tokens: int = 8192, block_size: int = 16, num_blocks: Optional[int] = None,
                  gpu_memory_utilization: float = 0.5, enable_prefix_caching: bool = True, enforce_eager: bool = False,
-                 seed: int = 0, eos_token_id: Optional[int] = None, cudagraph_capture_sizes: Optional[list] = None):
+                 seed: int = 0, eos_token_id: Optional[int] = None, cudagraph_capture_sizes: Optional[list] = None,
+                 quantization: Optional[str] = None):
         self.model = model
+        if quantization not in (None, "", "fp8"):
+            raise ValueError(f"unsupported rollout quantization {quantization!r} (supported: fp8)")
+        self.quantization = quantization or None
+        self._fp8: dict[int, tuple] = {}
         self.cfg: ModelConfig = model.cfg
         self.device = model.embed_tokens.weight.device
         self.dtype = model.embed_tokens.weight.dtype
@@ -177,7 +182,7 @@ class NativeRolloutEngine:
         self.max_num_batched_tokens = max(max_num_batched_tokens, 16)
         self.block_size = block_size
         self.enable_prefix_caching = enable_prefix_caching
-        self.enforce_eager = enforce_eager or not self.on_gpu or self.cfg.is_moe
+        self.enforce_eager = enforce_eager or not self.on_gpu
         self.seed = seed
         self.eos = self.cfg.eos_token_id if eos_token_id is None else eos_token_id
         self.gpu_memory_utilization = gpu_memory_utilization
@@ -193,6 +198,7 @@ class NativeRolloutEngine:
         self.step_counter = torch.zeros(1, dtype=torch.long, device=self.device)
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0}
         self.wake_up()
+        self.refresh_quantization()
 
     # ----------------------------------------------------------------- memory
     def _page_bytes(self) -> int:
@@ -247,6 +253,7 @@ class NativeRolloutEngine:
         for k, v in native.items():
             if k in own:
                 own[k].data.copy_(v.to(own[k].dtype))
+        self.refresh_quantization()
         self.clear_kv_cache()
 
     # --------------------------------------------------------------- requests
@@ -291,8 +298,7 @@ class NativeRolloutEngine:
     def _layer_attn_in(self, layer, x, positions):
         c = self.cfg
         att = layer.self_attn
-        qkv = ops.gemm(x, att.qkv_proj.weight, bias=att.qkv_proj.bias) if self.on_gpu else torch.nn.functional.linear(
-            x, att.qkv_proj.weight, att.qkv_proj.bias)
+        qkv = self._mm(x, att.qkv_proj.weight, att.qkv_proj.bias)
         T = x.shape[0]
         if c.qk_norm:
             q, k, v = qkv.split([c.q_size, c.kv_size, c.kv_size], dim=-1)
@@ -306,8 +312,30 @@ class NativeRolloutEngine:
         v = qkv[:, c.q_size + c.kv_size :].view(T, c.num_key_value_heads, c.head_dim)
         return q, k, v
 
-    def _mm(self, x, w):
-        return ops.gemm(x, w) if self.on_gpu else x @ w.t()
+    def refresh_quantization(self) -> None:
+        """fp8 rollout (``rollout.quantization = fp8``): block-quantise the projection weights of every layer (e4m3,
+        one scale per 128 x 128 block). Call after every weight sync: the trainer's bf16 weights are the source
+        (quantise-on-resync of verl/utils/vllm/vllm_fp8_utils.py:182-431)."""
+        self._fp8.clear()
+        if self.quantization != "fp8" or not self.on_gpu or self.cfg.is_moe:
+            return
+        from ..ops import fp8
+
+        for layer in self.model.layers:
+            for w in (layer.self_attn.qkv_proj.weight, layer.self_attn.o_proj.weight, layer.mlp.gate_up_proj.weight,
+                      layer.mlp.down_proj.weight):
+                if w.numel():
+                    self._fp8[id(w)] = fp8.quantize_weight(w.data)
+
+    def _mm(self, x, w, bias=None):
+        q = self._fp8.get(id(w))
+        if q is not None:
+            from ..ops import fp8
+
+            return fp8.fp8_linear(x, q[0], q[1], bias)
+        if self.on_gpu:
+            return ops.gemm(x, w, bias=bias)
+        return torch.nn.functional.linear(x, w, bias)
 
     def _layer_rest(self, layer, attn_out, residual):
         c = self.cfg

@@ -189,7 +189,7 @@ class ActorRolloutRefWorker(_WorkerBase):
             max_num_batched_tokens=max(rc.max_num_batched_tokens, rc.prompt_length),
             gpu_memory_utilization=rc.gpu_memory_utilization, enable_prefix_caching=rc.enable_prefix_caching,
             enforce_eager=rc.enforce_eager, seed=seed + 1000 * self.dp_rank, cudagraph_capture_sizes=rc.cudagraph_capture_sizes,
-            **kw)
+            quantization=_cfg(rc, "quantization", None), **kw)
         if rc.free_cache_engine:
             self.rollout_engine.sleep()
 
@@ -294,6 +294,7 @@ class ActorRolloutRefWorker(_WorkerBase):
         if self._is_actor and self._is_rollout and self._rollout_flat is not None:
             self._sync_rollout_weights()
         if self.rollout_engine is not None:
+            self.rollout_engine.refresh_quantization()  # fp8 rollout: re-quantise from the fresh bf16 weights
             self.rollout_engine.clear_kv_cache()
         if self.device.type == "cuda":
             torch.cuda.synchronize()
