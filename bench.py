@@ -53,7 +53,7 @@ def reference_arm(args):
     ref = os.path.join(REPO, "baseline", "_ref")
     why = None
     if not os.path.isdir(os.path.join(ref, "verl")):
-        why = "baseline/_ref is absent: pip install of /root/reference did not run on this box"
+        why = "baseline/_ref is absent: the offline pip install of the reference has not been run in this checkout"
     else:
         probe = subprocess.run([sys.executable, "-c", "import sys; sys.path.insert(0, sys.argv[1]); import verl",
                                 ref], capture_output=True, text=True, cwd=tempfile.gettempdir())

@@ -121,7 +121,7 @@ class MoEMLP(nn.Module):
         if self.norm_topk:
             top_w = top_w / top_w.sum(-1, keepdim=True)
         self.last_routing = top_i.detach()
-        if x.is_cuda and I_ok(self.gate_up_proj, self.down_proj):
+        if x.is_cuda and _grouped_gemm_ok(self.gate_up_proj, self.down_proj):
             # one grouped GEMM per projection for all experts, routing layout computed on the device
             from ..ops.moe import moe_mlp
 
@@ -147,7 +147,7 @@ class MoEMLP(nn.Module):
         return y
 
 
-def I_ok(gate_up: torch.Tensor, down: torch.Tensor) -> bool:
+def _grouped_gemm_ok(gate_up: torch.Tensor, down: torch.Tensor) -> bool:
     """Grouped-GEMM constraints: bf16, contraction lengths multiples of 64."""
     return (gate_up.dtype == torch.bfloat16 and gate_up.shape[1] % 64 == 0 and gate_up.shape[2] % 64 == 0
             and down.shape[1] % 64 == 0 and down.shape[2] % 64 == 0)
