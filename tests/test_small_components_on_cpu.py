@@ -1,0 +1,260 @@
+"""Tools, interactions, scorers, request schema, samplers, tiled MLP, registry and small helpers (CPU)."""
+
+import asyncio
+
+import numpy as np
+import pytest
+import torch
+
+from verl_b200.tools.schemas import OpenAIFunctionToolSchema, ToolResponse
+
+_SCHEMA = OpenAIFunctionToolSchema.model_validate({
+    "type": "function",
+    "function": {"name": "t", "description": "d", "parameters": {"type": "object", "properties": {}, "required": []}}})
+
+
+def test_geo3k_and_zoom_tools():
+    from verl_b200.tools.geo3k_tool import Geo3kTool
+    from verl_b200.tools.image_zoom_in_tool import ImageZoomInTool
+
+    async def run():
+        g = Geo3kTool({}, _SCHEMA)
+        iid, _ = await g.create(ground_truth="12")
+        resp, step, _ = await g.execute(iid, {"answer": "12"})
+        assert "reward=1.0" in resp.text and step == 0.0
+        _, step2, _ = await g.execute(iid, {"answer": "13"})
+        assert step2 == -0.05
+        await g.release(iid)
+
+        z = ImageZoomInTool({}, _SCHEMA)
+        img = np.zeros((100, 200, 3), dtype=np.uint8)
+        iid, _ = await z.create(image=img)
+        r, _, meta = await z.execute(iid, {"bbox_2d": [10, 10, 110, 60], "label": "x"})
+        assert meta["success"] and r.image[0].shape == (50, 100, 3)
+        r, pen, meta = await z.execute(iid, {"bbox_2d": [50, 50, 40, 40]})
+        assert not meta["success"] and pen < 0
+        r, _, meta = await z.execute(iid, {"bbox_2d": [50, 50, 52, 52]})  # tiny box grows to the minimum size
+        assert meta["success"] and min(r.image[0].shape[:2]) >= 28
+
+    asyncio.run(run())
+
+
+def test_mcp_tool_with_injected_client():
+    from verl_b200.tools import mcp_base_tool as m
+
+    async def run():
+        calls = []
+
+        async def fake(name, params, timeout):
+            calls.append((name, params))
+            return {"hits": [1, 2]}
+
+        await m.ClientManager.initialize(rate_limit=100, call_tool=fake)
+        tool = m.MCPBaseTool({"timeout": 1}, _SCHEMA)
+        iid, _ = await tool.create()
+        r, _, meta = await tool.execute(iid, {"q": "x"})
+        assert meta["status"] == "success" and "hits" in r.text and calls == [("t", {"q": "x"})]
+
+        async def boom(name, params, timeout):
+            raise RuntimeError("down")
+
+        await m.ClientManager.initialize(rate_limit=100, call_tool=boom)
+        r, _, meta = await tool.execute(iid, {"q": "x"})
+        assert meta["status"] == "error" and "down" in r.text
+
+    asyncio.run(run())
+
+
+def test_weather_interaction():
+    from verl_b200.interactions.weather_interaction import WeatherInteraction
+
+    async def run():
+        w = WeatherInteraction({})
+        iid = await w.start_interaction()
+        done, _, s, _ = await w.generate_response(iid, [{"role": "assistant", "content": "hello"}])
+        assert not done and s == 0.0
+        done, _, s, _ = await w.generate_response(iid, [{"role": "assistant", "content": "The temperature is 20°C"}])
+        assert done and s == 1.0
+        await w.finalize_interaction(iid)
+
+    asyncio.run(run())
+
+
+def test_prime_and_batch_scorers():
+    from verl_b200.utils.reward_score import default_compute_score, math_batch, math_verify, prime_code, prime_math
+
+    assert prime_math.compute_score("thus \\boxed{\\frac{1}{2}}", "\\frac{1}{2}")[0]
+    assert not prime_math.compute_score("the answer is 7", "8")[0]
+    assert prime_math.compute_score("we get 0.5", "1/2")[0]
+    code = "```python\nn=int(input())\nprint(n*n)\n```"
+    assert prime_code.compute_score(code, {"inputs": ["2", "3"], "outputs": ["4", "9"]})[0] == 1.0
+    s, info = prime_code.compute_score(code, {"inputs": ["2", "3"], "outputs": ["4", "8"]}, continuous=True)
+    assert s == 0.5 and info["passed"] == 1
+    assert prime_code.compute_score("while True: pass", {"inputs": [""], "outputs": [""]}, timeout=0.5)[0] == 0.0
+    assert prime_code.compute_score("def f(x):\n    return x+1", {"functional": "assert f(1) == 2"})[0] == 1.0
+    assert math_batch.compute_score_batched(["a", "a"], ["\\boxed{3}", "\\boxed{4}"], ["3", "3"]) == [1.0, 0.0]
+    assert math_verify.compute_score("so \\boxed{3}", "3") == 1.0
+    assert default_compute_score("prime_math", "\\boxed{5}", "5") == 1.0
+
+
+def test_async_rollout_request_incremental_tokenisation():
+    from verl_b200.utils.tokenizer import IntTokenizer
+    from verl_b200.workers.rollout.schemas import (AsyncRolloutRequest, AsyncRolloutRequestStateEnum,
+                                                   FinishReasonTypeEnum)
+
+    class Tok(IntTokenizer):
+        """<role-marker> content ... per message; generation prompt = assistant marker."""
+
+        MARK = {"system": 900, "user": 901, "assistant": 902, "tool": 903}
+
+        def apply_chat_template(self, messages, add_generation_prompt=True, tokenize=True, **kw):
+            ids = []
+            for m in messages:
+                c = m["content"] if isinstance(m["content"], str) else "7"
+                ids += [self.MARK[m["role"]]] + self.encode(c if c[:1].isdigit() else "5 5")
+            if add_generation_prompt:
+                ids.append(902)
+            return ids
+
+    tok = Tok(1000)
+    req = AsyncRolloutRequest.create(tok, [{"role": "user", "content": "1 2 3"}], request_id="r0", max_prompt_len=8,
+                                     max_response_len=6)
+    assert req.input_ids.tolist() == [901, 1, 2, 3] and req.generation_prompt_ids.tolist() == [902]
+    assert req.get_generation_prompt_ids(tok) == [901, 1, 2, 3, 902]
+    assert req.get_generation_prompt_ids(tok) == [901, 1, 2, 3, 902]  # not appended twice
+    req.add_assistant_message(tok, "10 11", content_ids=[10, 11])
+    req.add_tool_response_messages(tok, [ToolResponse(text="20")])
+    req.get_generation_prompt_ids(tok)
+    req.add_assistant_message(tok, "12")  # tokenised from text
+    req.add_user_message(tok, "30 31")
+    assert req.input_ids.tolist() == [901, 1, 2, 3, 902, 10, 11, 903, 20, 902, 12, 901, 30, 31]
+    assert req.loss_mask.tolist() == [0, 0, 0, 0, 0, 1, 1, 0, 0, 0, 1, 0, 0, 0]
+    assert req.position_ids.tolist() == list(range(14))
+    req.finalize(tok, {"score": 1.0}, FinishReasonTypeEnum.STOP)
+    assert req.state == AsyncRolloutRequestStateEnum.COMPLETED
+    assert req.prompt_ids.tolist() == [901, 1, 2, 3]
+    assert req.response_ids.tolist() == [902, 10, 11, 903, 20, 902] and req.response_loss_mask.tolist() == [0, 1, 1, 0, 0, 0]
+    assert FinishReasonTypeEnum.from_str("tool_call") == FinishReasonTypeEnum.TOOL_CALL
+    with pytest.raises(ValueError):
+        FinishReasonTypeEnum.from_str("nope")
+
+
+def test_curriculum_sampler_prefers_informative_prompts():
+    from verl_b200.experimental.dataset import AbstractCurriculumSampler, DifficultyCurriculumSampler
+    from verl_b200.protocol import DataProto
+
+    s = DifficultyCurriculumSampler(list(range(4)), {"seed": 3, "sampler": {"floor": 0.01, "momentum": 0.0}})
+    assert isinstance(s, AbstractCurriculumSampler) and len(s) == 4
+    scores = torch.zeros(4, 3)
+    scores[0, -1], scores[1, -1] = 1.0, 1.0  # prompts 0,1 always solved; 2,3 never solved
+    batch = DataProto.from_dict({"token_level_scores": scores}, non_tensors={"index": np.arange(4)})
+    s.update(batch)
+    assert np.allclose(s.p, [1, 1, 0, 0])
+    s.p[3] = 0.5
+    draws = [i for _ in range(50) for i in s]
+    assert draws.count(3) > 0.8 * len(draws)
+
+
+def test_tiled_mlp_matches_plain():
+    from verl_b200.models.tiled_mlp import TiledMLP
+
+    torch.manual_seed(0)
+    mlp = torch.nn.Sequential(torch.nn.Linear(8, 32), torch.nn.SiLU(), torch.nn.Linear(32, 8)).double()
+    x = torch.randn(11, 8, dtype=torch.double, requires_grad=True)
+    y = mlp(x)
+    y.square().sum().backward()
+    ref = [x.grad.clone()] + [p.grad.clone() for p in mlp.parameters()]
+    x.grad = None
+    mlp.zero_grad()
+    y2 = TiledMLP(mlp, 3)(x)
+    assert torch.allclose(y, y2)
+    y2.square().sum().backward()
+    got = [x.grad] + [p.grad for p in mlp.parameters()]
+    for a, b in zip(ref, got):
+        assert torch.allclose(a, b)
+
+
+def test_registry_and_model_helpers(tmp_path):
+    from verl_b200.models.registry import ModelRegistry
+    from verl_b200.utils import model as mu
+    from verl_b200.utils.chat_template import extract_system_prompt_and_generation
+
+    assert "Qwen2ForCausalLM" in ModelRegistry.get_supported_archs()
+    assert ModelRegistry.load_model_cls("NopeForCausalLM") is None
+    assert callable(ModelRegistry.load_model_cls("Qwen3MoeForCausalLM", value=True))
+    mask = torch.tensor([[0, 0, 1, 1, 1]])
+    assert mu.compute_position_id_with_mask(mask).tolist() == [[0, 0, 0, 1, 2]]
+    m = mu.create_random_mask(torch.zeros(4, 20, dtype=torch.long), 0.5, 0.2, 0.1)
+    assert m.shape == (4, 20) and (m.sum(-1) >= 2).all() and (m.sum(-1) <= 10).all()
+    t, cu, mx = mu.pad_packed_inputs(torch.arange(10), torch.tensor([0, 4, 10]), 6, 8)
+    assert t.shape[0] == 16 and cu.tolist() == [0, 4, 10, 16] and mx == 6
+    n, scale = mu.get_model_size(torch.nn.Linear(100, 100))
+    assert scale == "K" and abs(n - 10.1) < 1e-6
+    (tmp_path / "adapter_config.json").write_text('{"r": 16}')
+    assert mu.get_lora_rank_from_adapter(tmp_path) == 16
+    assert mu.check_target_modules({"target_modules": ["q_proj"]}, "layers.0.attn.q_proj")
+    assert not mu.check_target_modules({"target_modules": "x.*"}, "layers.0.attn.q_proj")
+
+    class Tok:
+        def apply_chat_template(self, messages, add_generation_prompt=False, tokenize=True, **kw):
+            ids = [1, 1]  # system prompt
+            for _ in messages:
+                ids += [5, 6]
+            return ids + ([9] if add_generation_prompt else [])
+
+    assert extract_system_prompt_and_generation(Tok()) == ([1, 1], [9])
+
+
+def test_run_unvicorn_serves():
+    import urllib.request
+
+    from fastapi import FastAPI
+
+    from verl_b200.workers.rollout.utils import ensure_async_iterator, get_max_position_embeddings, run_unvicorn
+
+    app = FastAPI()
+
+    @app.get("/ping")
+    def ping():
+        return {"ok": True}
+
+    async def run():
+        port, task = await run_unvicorn(app, {"a": 1}, "127.0.0.1")
+        loop = asyncio.get_running_loop()
+        body = await loop.run_in_executor(None, lambda: urllib.request.urlopen(f"http://127.0.0.1:{port}/ping", timeout=5).read())
+        task.server.should_exit = True
+        await task
+        return body, [x async for x in ensure_async_iterator([1, 2])]
+
+    body, items = asyncio.run(run())
+    assert b"true" in body and items == [1, 2]
+
+    class C:
+        max_position_embeddings = None
+
+        class text_config:
+            max_position_embeddings = 77
+
+    assert get_max_position_embeddings(C) == 77
+
+
+def test_model_with_tiled_mlp_matches_plain():
+    from verl_b200.models.config import preset
+    from verl_b200.models.tiled_mlp import apply_tiled_mlp
+    from verl_b200.models.transformer import PackedBatch, build_model
+    from verl_b200.workers.engine.native import NativeEngine
+
+    cfg = preset("tiny-qwen2")
+    ids = torch.randint(3, cfg.vocab_size, (2, 12))
+    pb, _ = PackedBatch.from_padded(ids, torch.ones_like(ids))
+    grads, names = [], []
+    for shards in (0, 3):
+        m = build_model(cfg, dtype=torch.float32, seed=1)
+        if shards:
+            assert apply_tiled_mlp(m, shards) == cfg.num_hidden_layers
+        m.forward_hidden(pb).float().square().mean().backward()
+        grads.append(m.layers[0].mlp.down_proj.weight.grad.clone())
+        names.append(sorted(n for n, _ in m.named_parameters()))
+    assert names[0] == names[1] and torch.allclose(grads[0], grads[1], atol=1e-6)
+    eng = NativeEngine(cfg, None, None, device="cpu", seed=1, trainable=False, tiled_mlp_shards=3).initialize()
+    assert eng.model.layers[0].mlp.tile_shards == 3

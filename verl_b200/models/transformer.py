@@ -80,9 +80,17 @@ class DenseMLP(nn.Module):
         super().__init__()
         self.gate_up_proj = Linear(cfg.hidden_size, 2 * cfg.intermediate_size, False, dtype, device)
         self.down_proj = Linear(cfg.intermediate_size, cfg.hidden_size, False, dtype, device)
+        self.tile_shards = 1  # >1: run over row shards with per-shard recomputation (models/tiled_mlp.py)
+
+    def _plain(self, x):
+        return self.down_proj(ops.swiglu(self.gate_up_proj(x)))
 
     def forward(self, x):
-        return self.down_proj(ops.swiglu(self.gate_up_proj(x)))
+        if self.tile_shards > 1:
+            from .tiled_mlp import tiled_call
+
+            return tiled_call(self._plain, [self.gate_up_proj.weight, self.down_proj.weight], self.tile_shards, x)
+        return self._plain(x)
 
 
 class MoEMLP(nn.Module):

@@ -221,6 +221,7 @@ class RayPPOTrainer:
                 train_sampler = RandomSampler(train_dataset, generator=g)
             else:
                 train_sampler = SequentialSampler(train_dataset)
+        self.train_sampler = train_sampler
         self.train_dataloader = _StatefulLoader(DataLoader(
             train_dataset, batch_size=int(d.get("gen_batch_size", d.train_batch_size)), num_workers=0, drop_last=True,
             collate_fn=collate_fn, sampler=train_sampler))
@@ -636,6 +637,8 @@ class RayPPOTrainer:
         metrics.update(compute_variance_proxy_metrics(batch, metrics.get("actor/grad_norm")))
         metrics["training/global_step"] = self.global_steps
         self._last_batch = batch
+        if hasattr(getattr(self, "train_sampler", None), "update"):  # curriculum samplers learn from the finished batch
+            self.train_sampler.update(batch=batch)
         return self._all_reduce_metrics(metrics)
 
     def _dump_generations(self, batch: DataProto, dump_dir: str):

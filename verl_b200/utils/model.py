@@ -1,0 +1,91 @@
+"""Model helpers (subset of verl/utils/model.py that has a meaning without HF model classes / Megatron)."""
+
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+import torch.nn as nn
+
+
+def update_model_config(module_config, override_config_kwargs: dict) -> None:
+    """verl/utils/model.py:61-71: recursive setattr of overrides."""
+    for k, v in (override_config_kwargs or {}).items():
+        if isinstance(v, dict) and hasattr(module_config, k) and not isinstance(getattr(module_config, k), dict):
+            update_model_config(getattr(module_config, k), v)
+        else:
+            setattr(module_config, k, v)
+
+
+def get_model_size(model: nn.Module, scale: str = "auto"):
+    """verl/utils/model.py:149-173."""
+    n = sum(p.numel() for p in model.parameters())
+    if scale == "auto":
+        scale = "B" if n > 1e9 else "M" if n > 1e6 else "K" if n > 1e3 else ""
+    div = {"B": 1e9, "M": 1e6, "K": 1e3, "": 1}[scale]
+    return n / div, scale
+
+
+def print_model_size(model: nn.Module, name: str | None = None) -> None:
+    n, scale = get_model_size(model)
+    print(f"{name or model.__class__.__name__} contains {n:.2f}{scale} parameters")
+
+
+def compute_position_id_with_mask(mask: torch.Tensor) -> torch.Tensor:
+    """verl/utils/model.py:226-227."""
+    return torch.clip(torch.cumsum(mask, dim=-1) - 1, min=0, max=None)
+
+
+def create_random_mask(input_ids: torch.Tensor, max_ratio_of_valid_token: float, max_ratio_of_left_padding: float,
+                       min_ratio_of_valid_token: float = 0.0) -> torch.Tensor:
+    """Random left/right padded attention mask for tests (verl/utils/model.py:183-223)."""
+    assert 0 < max_ratio_of_valid_token <= 1 and 0 <= max_ratio_of_left_padding < 1
+    b, s = input_ids.shape
+    max_valid = max(1, int(s * max_ratio_of_valid_token))
+    min_valid = max(1, int(s * min_ratio_of_valid_token))
+    max_left = int(s * max_ratio_of_left_padding)
+    assert max_valid + max_left <= s
+    mask = torch.ones_like(input_ids, dtype=torch.int64)
+    for i in range(b):
+        left = int(torch.randint(0, max_left + 1, (1,)))
+        valid = int(torch.randint(min_valid, max_valid + 1, (1,)))
+        mask[i, :left] = 0
+        mask[i, left + valid:] = 0
+    return mask
+
+
+def pad_packed_inputs(unpad_tokens: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen_in_batch: int, size: int):
+    """Pad a packed stream to a multiple of ``size`` with one extra dummy sequence (verl/utils/model.py:503-533)."""
+    total = unpad_tokens.shape[0]
+    pad = (-total) % size
+    if pad:
+        if unpad_tokens.ndim == 1:
+            unpad_tokens = torch.nn.functional.pad(unpad_tokens, (0, pad))
+        else:
+            unpad_tokens = torch.nn.functional.pad(unpad_tokens, (0, 0, 0, pad))
+        cu_seqlens = torch.nn.functional.pad(cu_seqlens, (0, 1), value=int(cu_seqlens[-1]) + pad)
+        max_seqlen_in_batch = max(max_seqlen_in_batch, pad)
+    return unpad_tokens, cu_seqlens, max_seqlen_in_batch
+
+
+def get_lora_rank_from_adapter(adapter_path: str | os.PathLike) -> int:
+    """verl/utils/model.py:741-774: read ``r`` from a PEFT adapter_config.json."""
+    path = os.path.join(adapter_path, "adapter_config.json")
+    if not os.path.exists(path):
+        raise FileNotFoundError(f"adapter_config.json not found in {adapter_path}")
+    with open(path) as f:
+        cfg = json.load(f)
+    if "r" not in cfg:
+        raise ValueError("LoRA rank 'r' not found in adapter_config.json")
+    return int(cfg["r"])
+
+
+def check_target_modules(config, key: str) -> bool:
+    """PEFT-style target-module match (verl/utils/model.py:274-322): str = full regex, list = suffix match."""
+    import re
+
+    target = config.target_modules if hasattr(config, "target_modules") else config["target_modules"]
+    if isinstance(target, str):
+        return re.fullmatch(target, key) is not None
+    return any(key == t or key.endswith("." + t) for t in target)

@@ -35,6 +35,14 @@ def default_compute_score(data_source, solution_str, ground_truth, extra_info=No
                                                ground_truth, continuous=True)
         else:
             raise NotImplementedError("code data sources need reward_model.sandbox_fusion.url")
+    elif data_source in ("prime_math",) or str(data_source).startswith("numina_prime"):
+        from . import prime_math
+
+        res = float(prime_math.compute_score(solution_str, ground_truth)[0])
+    elif data_source in ("prime_code", "livecodebench"):
+        from . import prime_code
+
+        res = prime_code.compute_score(solution_str, ground_truth, continuous=True)[0]
     elif data_source in ("hiyouga/geometry3k",):
         res = geo3k.compute_score(solution_str, ground_truth)
     elif data_source in ("searchR1_nq", "searchR1_triviaqa", "searchR1_popqa", "searchR1_hotpotqa",

@@ -11,7 +11,12 @@ def format_reward(predict_str: str) -> float:
     return 1.0 if _FORMAT.fullmatch(predict_str) else 0.0
 
 
-def acc_reward(predict_str: str, ground_truth: str) -> float:
+def acc_reward(predict_str: str, ground_truth: str, use_boxed: bool = True) -> float:
+    if not use_boxed:  # the tool hands over the bare answer
+        try:
+            return 1.0 if is_equiv(predict_str.strip(), ground_truth) else 0.0
+        except Exception:
+            return 0.0
     boxed = last_boxed_only_string(predict_str)
     if boxed is None:
         return 0.0
@@ -22,4 +27,4 @@ def acc_reward(predict_str: str, ground_truth: str) -> float:
 
 
 def compute_score(predict_str: str, ground_truth: str, use_boxed: bool = True, format_score: float = 0.1) -> float:
-    return (1.0 - format_score) * acc_reward(predict_str, ground_truth) + format_score * format_reward(predict_str)
+    return (1.0 - format_score) * acc_reward(predict_str, ground_truth, use_boxed) + format_score * format_reward(predict_str)

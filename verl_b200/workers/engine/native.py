@@ -64,8 +64,10 @@ class _SumOverGroup(torch.autograd.Function):
 class NativeEngine(BaseEngine):
     def __init__(self, model_config: ModelConfig, engine_config=None, optimizer_config=None, *, value_head: bool = False,
                  device: Optional[str] = None, trainable: bool = True, group=None, seed: int = 0,
-                 state_dict: Optional[dict] = None, comm=None, gradient_checkpointing: bool = True):
+                 state_dict: Optional[dict] = None, comm=None, gradient_checkpointing: bool = True,
+                 tiled_mlp_shards: int = 0):
         self.model_config = model_config
+        self.tiled_mlp_shards = int(tiled_mlp_shards)
         self.engine_config = engine_config
         self.optimizer_config = optimizer_config
         self.value_head = value_head
@@ -94,6 +96,10 @@ class NativeEngine(BaseEngine):
             missing, unexpected = self.model.load_state_dict(
                 {k: v.to(self.work_dtype) for k, v in self._init_state.items()}, strict=False)
             self._init_state = None
+        if self.tiled_mlp_shards > 1:
+            from ...models.tiled_mlp import apply_tiled_mlp
+
+            apply_tiled_mlp(self.model, self.tiled_mlp_shards)
         m = self.model
         tied = m.lm_head is None and not m.value_head
         units = []

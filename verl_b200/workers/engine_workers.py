@@ -140,10 +140,12 @@ class ActorRolloutRefWorker(_WorkerBase):
         seed = int(_cfg(_cfg(self.actor_cfg, "fsdp_config", None), "seed", 42)) if self.actor_cfg else 42
         group = dist.group.WORLD if dist.is_initialized() and self.world > 1 else None
         comm = self._make_comm()
+        tm = _cfg(self.config.model, "tiled_mlp", None) or {}
+        tiled = int(_cfg(tm, "num_shards", 4)) if _cfg(tm, "enabled", False) else 0
         if self._is_actor:
             self.actor_engine = NativeEngine(model_cfg, self.actor_cfg.fsdp_config, self.actor_cfg.optim,
                                              device=str(self.device), group=group, seed=seed, state_dict=state,
-                                             comm=comm, gradient_checkpointing=gc).initialize()
+                                             comm=comm, gradient_checkpointing=gc, tiled_mlp_shards=tiled).initialize()
             self.actor = DataParallelPPOActor(self.actor_cfg, self.actor_engine)
         if self._is_ref:
             ref_eng_cfg = self.ref_cfg.fsdp_config if self.ref_cfg is not None else None
