@@ -147,3 +147,35 @@ def test_hermes_parser():
     text, calls = asyncio.run(HermesToolParser(T()).extract_tool_calls([1]))
     assert len(calls) == 1 and calls[0].name == "f" and json.loads(calls[0].arguments) == {"a": 1}
     assert "<tool_call>" not in text
+
+
+def test_partial_single_turn_loop_resumes_cancelled_sample(server):
+    """A sample cut by abort_all_requests comes back cancelled; running it again continues where it stopped."""
+    from verl_b200.experimental.fully_async_policy.agent_loop import PartialSingleTurnAgentLoop
+
+    cfg = _cfg()
+
+    async def go():
+        loop = PartialSingleTurnAgentLoop(cfg, AsyncLLMServerManager(cfg, [server]), IntTokenizer(2048))
+        sp = {"temperature": 0.0, "max_tokens": 32, "ignore_eos": True}
+        prompt = list(range(30, 50))
+        full = await loop.run(sp, raw_prompt=prompt, param_version=1)
+        assert not full.extra_fields["is_cancel"]
+        task = asyncio.ensure_future(loop.run(sp, raw_prompt=prompt, param_version=1))
+        while not server._pending:
+            await asyncio.sleep(0.001)
+        await asyncio.sleep(0.02)
+        await server.abort_all_requests(reset_prefix_cache=False)
+        part = await task
+        if not part.extra_fields["is_cancel"]:  # the engine finished before the abort landed: nothing to resume
+            assert part.response_ids == full.response_ids
+            return
+        assert len(part.response_ids) < len(full.response_ids)
+        resumed = await loop.run(sp, raw_prompt=prompt, output=part, param_version=2)
+        assert not resumed.extra_fields["is_cancel"]
+        assert resumed.extra_fields["param_version_start"] == 1 and resumed.extra_fields["param_version_end"] == 2
+        assert resumed.prompt_ids == prompt and resumed.response_ids == full.response_ids  # greedy: same continuation
+        assert len(resumed.response_logprobs) == len(resumed.response_ids)
+        assert (await loop.run(sp, raw_prompt=prompt, output=resumed)) is resumed
+
+    asyncio.run(go())

@@ -258,3 +258,116 @@ def test_model_with_tiled_mlp_matches_plain():
     assert names[0] == names[1] and torch.allclose(grads[0], grads[1], atol=1e-6)
     eng = NativeEngine(cfg, None, None, device="cpu", seed=1, trainable=False, tiled_mlp_shards=3).initialize()
     assert eng.model.layers[0].mlp.tile_shards == 3
+
+
+def test_tensordict_utils_roundtrip():
+    from verl_b200.utils import tensordict_utils as tu
+
+    nested = torch.nested.as_nested_tensor([torch.arange(2), torch.arange(3), torch.arange(1), torch.arange(4)], layout=torch.jagged)
+    td = tu.get_tensordict({"x": torch.arange(8).view(4, 2), "ids": nested, "turns": [[], [0.5], [1], [2, 3]]}, {"temp": 0.7})
+    assert td.batch_size[0] == 4 and tu.get(td, "temp") == 0.7 and tu.get(td, "turns")[1] == [0.5]
+    sel = tu.index_select_tensor_dict(td, [3, 0])
+    assert sel["x"].tolist() == [[6, 7], [0, 1]] and [r.tolist() for r in sel["ids"].unbind(0)] == [[0, 1, 2, 3], [0, 1]]
+    assert tu.get(sel, "turns") == [[2, 3], []] and tu.get(sel, "temp") == 0.7
+    chunks = tu.chunk_tensordict(td, 2)
+    tu.assert_tensordict_eq(tu.concat_tensordict(chunks), td)
+    padded, pad = tu.pad_to_divisor(td, 3)
+    assert pad == 2 and padded.batch_size[0] == 6
+    tu.assert_tensordict_eq(tu.unpad(padded, pad), td)
+    tu.assign_non_tensor(td, tags=["a", "b", "c", "d"], step=3)
+    assert tu.get(td, "tags")[2] == "c" and tu.pop(td, "step") == 3 and "step" not in td
+    other = tu.get_tensordict({"x": torch.arange(8).view(4, 2), "y": torch.ones(4)})
+    tu.union_tensor_dict(td, other)
+    assert "y" in td
+    with pytest.raises(AssertionError):
+        tu.union_tensor_dict(td, tu.get_tensordict({"x": torch.zeros(4, 2, dtype=torch.long)}))
+    sub = tu.pop_keys(td, ["x", "y"])
+    assert set(sub.keys()) == {"x", "y"} and "x" not in td
+    batches = list(tu.make_iterator(other, 2, epochs=2, seed=0))
+    assert len(batches) == 4 and batches[0].batch_size[0] == 2
+    pos = torch.nested.as_nested_tensor([torch.zeros(5, 3), torch.zeros(7, 3)], layout=torch.jagged)
+    t3 = tu.get_tensordict({"position_ids": pos})
+    tu.maybe_fix_3d_position_ids(t3)
+    assert [tuple(r.shape) for r in t3["position_ids"].unbind(0)] == [(3, 5), (3, 7)]
+
+
+def test_misc_utils_batch(tmp_path, monkeypatch):
+    from verl_b200.experimental.agent_loop.prometheus_utils import update_prometheus_config
+    from verl_b200.experimental.agent_loop.utils import build_gpt_oss_tool_response_text, resolve_config_path
+    from verl_b200.utils import attention_utils as au
+    from verl_b200.utils import hdfs_io
+    from verl_b200.utils.dataset.dataset_utils import DatasetPadMode, SFTTensorCollator
+    from verl_b200.utils.dataset.vision_utils import process_image, process_video, smart_resize
+    from verl_b200.utils.debug.trajectory_tracker import dump_data, get_trajectory_tracker
+    from verl_b200.utils.logger import LocalLogger
+    from verl_b200.utils.profiler.performance import GPUMemoryLogger, gather_timing, reduce_timing, simple_timer
+    from verl_b200.utils.ray_utils import auto_await, parallel_put
+    from verl_b200.utils.torch_dtypes import PrecisionType
+
+    assert PrecisionType.to_dtype("bf16") is torch.bfloat16 and PrecisionType.to_str(torch.float16) == "fp16"
+    assert PrecisionType.is_fp32(32) and PrecisionType.supported_type("mixed")
+
+    x = torch.arange(24.).view(2, 4, 3)
+    mask = torch.tensor([[1, 1, 0, 0], [1, 1, 1, 0]])
+    flat, idx, cu, mx, used = au.unpad_input(x, mask)
+    assert flat.shape == (5, 3) and cu.tolist() == [0, 2, 5] and mx == 3 and used.tolist() == [2, 3]
+    back = au.pad_input(flat, idx, 2, 4)
+    assert torch.equal(back, x * mask[..., None])
+
+    col = SFTTensorCollator(DatasetPadMode.NO_PADDING)([{"input_ids": torch.arange(3), "n": 1}, {"input_ids": torch.arange(5), "n": 2}])
+    assert col["input_ids"].is_nested and col["n"] == [1, 2]
+    assert SFTTensorCollator("right")([{"a": torch.ones(2)}, {"a": torch.zeros(2)}])["a"].shape == (2, 2)
+
+    assert smart_resize(100, 200, 28) == (112, 196)
+    img = process_image(np.zeros((100, 200, 3), dtype=np.uint8))
+    assert img.size == (196, 112)
+    assert len(process_video({"frames": [np.zeros((56, 56, 3), dtype=np.uint8)] * 10}, nframes=4)) == 4
+
+    monkeypatch.setenv("VERL_ENABLE_TRACKER", "1")
+    monkeypatch.setenv("VERL_TRACKER_HDFS_DIR", str(tmp_path / "trk"))
+    dump_data({"a": torch.ones(2)}, "step0")
+    get_trajectory_tracker().wait_for_hdfs()
+    assert torch.equal(torch.load(tmp_path / "trk" / "step0.pth")["a"], torch.ones(2))
+    assert hdfs_io.exists(str(tmp_path / "trk")) and not hdfs_io.is_non_local(str(tmp_path))
+
+    timing = {}
+    with simple_timer("a", timing):
+        pass
+    assert "a" in timing and reduce_timing(timing) == timing and gather_timing(timing) == {"a": [timing["a"]]}
+    logs = []
+    dec = GPUMemoryLogger("role")
+    dec.logging_function = logs.append
+    assert dec(lambda v: v + 1)(1) == 2 and len(logs) == 2 and logs[0].startswith("Before")
+    LocalLogger().log({"x": 1.0, "s": "skip"}, step=1)
+
+    @auto_await
+    async def co(v):
+        return v * 2
+
+    assert co(2) == 4 and parallel_put([1, 2]) == [1, 2]
+    assert "functions.f to=assistant" in build_gpt_oss_tool_response_text([{"content": "r"}], ["f"])
+    assert resolve_config_path("trainer/config/ppo_trainer.yaml").endswith("ppo_trainer.yaml")
+    with pytest.raises(FileNotFoundError):
+        resolve_config_path("nope/none.yaml")
+    cfg = {"file": str(tmp_path / "prom" / "prometheus.yml"), "port": 1}
+    assert update_prometheus_config(cfg, ["127.0.0.1:8000"], "native")
+    import yaml
+    assert yaml.safe_load(open(cfg["file"]))["scrape_configs"][0]["static_configs"][0]["targets"] == ["127.0.0.1:8000"]
+
+
+def test_dynamic_dataset_grows(tmp_path):
+    import json
+
+    from verl_b200.experimental.dynamic_dataset import DynamicGenDataset
+    from verl_b200.utils.tokenizer import IntTokenizer
+
+    f = tmp_path / "d.jsonl"
+    f.write_text("\n".join(json.dumps({"prompt": "1 2 3", "data_source": "x"}) for _ in range(3)))
+    cfg = {"datagen": {"path": "verl_b200.experimental.dynamic_dataset.dynamicgen_dataset", "name": "MockDataGenerator"},
+           "max_prompt_length": 8}
+    ds = DynamicGenDataset(str(f), IntTokenizer(100), cfg)
+    assert len(ds) == 4
+    ds.on_batch_end(None)
+    assert len(ds) == 5 and ds[4]["raw_prompt_ids"] == [1, 2, 3]
+    with pytest.raises(AssertionError):
+        DynamicGenDataset(str(f), IntTokenizer(100), {"max_prompt_length": 8})

@@ -18,3 +18,18 @@ def test_alias_imports_share_module_objects():
     import verl_b200.utils.config as rc
 
     assert vc.compose is rc.compose and verl.__name__ == "verl"
+
+
+def test_reference_module_paths_with_another_home_here():
+    from verl.experimental.reward_loop.reward_manager.limited import RateLimitedRewardManager
+    from verl.trainer.config.algorithm import AlgoConfig  # noqa: F401
+    from verl.utils.kernel.linear_cross_entropy import lmhead_logprob_entropy  # noqa: F401
+    from verl.workers.fsdp_workers import ActorRolloutRefWorker
+    from verl.workers.reward_manager.naive import NaiveRewardManager
+
+    import verl_b200.experimental.reward_loop.reward_manager as rl
+    import verl_b200.workers.engine_workers as ew
+    import verl_b200.workers.reward_manager as rm
+
+    assert ActorRolloutRefWorker is ew.ActorRolloutRefWorker and NaiveRewardManager is rm.NaiveRewardManager
+    assert RateLimitedRewardManager is rl.RateLimitedRewardManager

@@ -70,6 +70,14 @@ class AsyncLLMServerManager:
         return await server.generate(prompt_ids=prompt_ids, sampling_params=sampling_params,
                                      request_id=uuid4().hex)
 
+    async def generate_for_partial(self, request_id: str, *, prompt_ids: list[int], sampling_params: dict[str, Any],
+                                   image_data=None, video_data=None) -> tuple[list[int], list[float], bool]:
+        """Generation that may be cut short by ``abort_all_requests`` (a weight update in the fully asynchronous
+        pipeline): returns (tokens so far, their log-probs, was_cancelled). The caller resumes a cancelled sample by
+        sending prompt + partial response as the next prompt."""
+        out = await self.generate(request_id, prompt_ids=prompt_ids, sampling_params=sampling_params)
+        return list(out.token_ids), list(out.log_probs or []), out.stop_reason == "aborted"
+
 
 @dataclass
 class AgentLoopMetrics:

@@ -639,6 +639,8 @@ class RayPPOTrainer:
         self._last_batch = batch
         if hasattr(getattr(self, "train_sampler", None), "update"):  # curriculum samplers learn from the finished batch
             self.train_sampler.update(batch=batch)
+        if hasattr(getattr(self, "train_dataset", None), "on_batch_end"):  # datasets that grow during training
+            self.train_dataset.on_batch_end(batch=batch)
         return self._all_reduce_metrics(metrics)
 
     def _dump_generations(self, batch: DataProto, dump_dir: str):

@@ -188,29 +188,21 @@ class NativeAsyncServer:
         async def abort(body: dict):
             return await server.abort_request(body["request_id"])
 
+        @app.get("/metrics")
+        async def metrics():
+            """Prometheus text exposition of the scheduler gauges (scraped by the job that
+            ``update_prometheus_config`` writes)."""
+            from fastapi.responses import PlainTextResponse
+
+            stats = server.engine.sched.stats() if server.engine.sched else {}
+            stats["pending_requests"] = len(server._pending)
+            lines = []
+            for k, v in stats.items():
+                if isinstance(v, (int, float)):
+                    lines += [f"# TYPE verl_rollout_{k} gauge", f"verl_rollout_{k} {v}"]
+            return PlainTextResponse("\n".join(lines) + "\n", media_type="text/plain; version=0.0.4")
+
         return app
 
 
-async def run_unvicorn(app, server_args=None, server_address: str = "127.0.0.1", max_retries: int = 5):
-    """Start uvicorn on a free port, retrying on clashes (verl/workers/rollout/utils.py:38-58). Returns (port, task)."""
-    import socket
-
-    import uvicorn
-
-    last = None
-    for _ in range(max_retries):
-        with socket.socket() as s:
-            s.bind((server_address, 0))
-            port = s.getsockname()[1]
-        try:
-            cfg = uvicorn.Config(app, host=server_address, port=port, log_level="warning")
-            srv = uvicorn.Server(cfg)
-            task = asyncio.create_task(srv.serve())
-            for _ in range(100):
-                if srv.started:
-                    return port, task
-                await asyncio.sleep(0.05)
-            return port, task
-        except OSError as e:
-            last = e
-    raise RuntimeError(f"could not start the HTTP server: {last}")
+from .utils import run_unvicorn  # noqa: E402,F401  (historical import location)
