@@ -273,6 +273,9 @@ def main():
             "rollout_tokens_per_s_per_gpu": last.get("rollout/tokens_per_s"),
             "resync_ms": 1e3 * last.get("timing_s/resync", 0.0),
             "mfu_actor": last.get("perf/mfu/actor"),
+            "kept_activation_layers": getattr(
+                trainer.actor_rollout_wg.worker.worker_dict["actor_rollout"].actor_engine, "last_kept_layers", 0),
+            "keep_info": getattr(trainer.actor_rollout_wg.worker.worker_dict["actor_rollout"].actor_engine, "last_keep_info", None),
         }
         if e2e is not None:
             out["e2e"] = e2e

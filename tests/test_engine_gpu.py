@@ -66,6 +66,33 @@ def test_engine_logprob_and_step_match_cpu_fp32(kind):
     assert _lib.read_status("cuda")[0] == 0
 
 
+def test_kept_activations_match_recomputation_on_gpu():
+    """The custom autograd functions (GEMM with fused weight-gradient accumulation, attention, norms) give the same
+    gradient shard whether a layer's activations are recomputed or kept."""
+    from verl_b200.workers.engine.native import NativeEngine
+
+    class C(dict):
+        __getattr__ = dict.get
+
+    cfg = _cfg("dense")
+    batch, ids = _batch(cfg, [150, 64, 257], "cuda")
+    rows = torch.arange(ids.numel() - 1, device="cuda")
+    labels = ids.cuda()[rows + 1]
+    grads = []
+    for keep in ("0", "1", str(cfg.num_hidden_layers)):
+        eng = NativeEngine(cfg, C(keep_activation_layers=keep), C(lr=1e-3, clip_grad=1.0), device="cuda", seed=9).initialize()
+        with eng.train_mode():
+            eng.optimizer_zero_grad()
+            lp, _ = eng.forward_logprob(batch, rows, labels, 1.0)
+            (-lp.mean()).backward()
+            grads.append(eng.zero.grad.clone())
+    assert float(grads[0].abs().sum()) > 0
+    for g in grads[1:]:
+        torch.testing.assert_close(g, grads[0], atol=1e-5, rtol=1e-3)
+    auto = NativeEngine(cfg, C(), C(lr=1e-3), device="cuda", seed=9).initialize()
+    assert auto._layers_to_keep(4096) == cfg.num_hidden_layers  # a tiny model on an empty GPU keeps everything
+
+
 @pytest.mark.parametrize("kind", ["dense", "moe"])
 def test_rollout_graph_matches_eager_and_training_logprobs(kind):
     """Greedy generation: CUDA-graph decode = eager decode, and the rollout log-probs agree with the training engine's

@@ -368,15 +368,51 @@ class _UnitFn(torch.autograd.Function):
         return (None, None, None, None) + tuple(t.grad if t.requires_grad else None for t in inputs) + (None,)
 
 
+class _UnitFnKeep(torch.autograd.Function):
+    """Like :class:`_UnitFn` but the unit's activations are kept: the forward records the unit's autograd graph and
+    the backward runs it (no recomputation) after gathering the parameters again. The graph refers to the unit's
+    ``Parameter`` objects, whose storage is re-bound by every gather, so it reads the re-gathered weights."""
+
+    @staticmethod
+    def forward(ctx, zero: ZeroShardedParams, unit: ZeroUnit, fn: Callable, mask: tuple, *tensors):
+        ctx.zero, ctx.unit = zero, unit
+        inputs = [t.detach().requires_grad_(t.is_floating_point()) for t in tensors[:-1]]
+        zero.gather(unit)
+        try:
+            with torch.enable_grad():
+                outs = fn(*_expand(mask, inputs))
+        finally:
+            zero.release(unit)
+        ctx.single = not isinstance(outs, tuple)
+        ctx.inputs, ctx.outs = inputs, ((outs,) if ctx.single else outs)
+        det = tuple(o.detach() if isinstance(o, torch.Tensor) else o for o in ctx.outs)
+        return det[0] if ctx.single else det
+
+    @staticmethod
+    def backward(ctx, *grads):
+        zero, unit = ctx.zero, ctx.unit
+        inputs, outs = ctx.inputs, ctx.outs
+        ctx.inputs = ctx.outs = None
+        zero.gather(unit, for_backward=True)
+        try:
+            pairs = [(o, g) for o, g in zip(outs, grads) if g is not None and isinstance(o, torch.Tensor) and o.requires_grad]
+            if pairs:
+                torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+            zero.reduce_grads(unit)
+        finally:
+            zero.release(unit)
+        return (None, None, None, None) + tuple(t.grad if t.requires_grad else None for t in inputs) + (None,)
+
+
 def _expand(mask, tensors):
     it = iter(tensors)
     return [next(it) if m else None for m in mask]
 
 
-def unit_call(zero: ZeroShardedParams, unit: ZeroUnit, fn: Callable, *args):
+def unit_call(zero: ZeroShardedParams, unit: ZeroUnit, fn: Callable, *args, keep_activations: bool = False):
     """Run ``fn(*args)`` (tensor or None arguments) with the unit's parameters gathered. With grad enabled
-    the call is checkpointed: activations are recomputed in backward, and the unit's gradients are
-    reduce-scattered right after its backward."""
+    the call is checkpointed: activations are recomputed in backward (or kept, with ``keep_activations``), and the
+    unit's gradients are reduce-scattered right after its backward."""
     mask = tuple(a is not None for a in args)
     tensors = [a for a in args if a is not None]
     if torch.is_grad_enabled() and zero.trainable:
@@ -384,7 +420,7 @@ def unit_call(zero: ZeroShardedParams, unit: ZeroUnit, fn: Callable, *args):
         # call for its parameters, so every call is anchored on a scalar that requires grad
         if zero._anchor is None:
             zero._anchor = torch.zeros(1, device=zero.device, requires_grad=True)
-        return _UnitFn.apply(zero, unit, fn, mask, *tensors, zero._anchor)
+        return (_UnitFnKeep if keep_activations else _UnitFn).apply(zero, unit, fn, mask, *tensors, zero._anchor)
     zero.gather(unit)
     try:
         with torch.no_grad():

@@ -112,6 +112,9 @@ class FSDPEngineConfig(EngineConfig):
     entropy_from_logits_with_chunking: bool = False
     use_torch_compile: bool = True
     entropy_checkpointing: bool = False
+    # decoder layers whose activations are kept for the backward although gradient checkpointing is on:
+    # an integer, or "auto" = as many as fit in the memory that is free when the micro-batch starts
+    keep_activation_layers: Any = "auto"
     strategy: str = "fsdp"
 
     def __post_init__(self):

@@ -221,12 +221,12 @@ class NativeEngine(BaseEngine):
             batch = PackedBatch(ids_l, pos_l, batch.cu_seqlens, batch.max_seqlen, total_tokens=T)
         hidden = unit_call(z, self._embed_unit, lambda: m.embed(batch))
         residual = None
-        ckpt = self.gradient_checkpointing or z.world > 1
-        for layer, unit in zip(m.layers, self._layer_units):
-            if ckpt or not torch.is_grad_enabled():
-                hidden, residual = unit_call(z, unit, lambda h, r, layer=layer: layer(h, r, batch, rope), hidden, residual)
-            else:
-                hidden, residual = layer(hidden, residual, batch, rope)
+        n_layers = len(m.layers)
+        n_keep = self._layers_to_keep(hidden.shape[0]) if (torch.is_grad_enabled() and self.trainable) else 0
+        for i, (layer, unit) in enumerate(zip(m.layers, self._layer_units)):
+            # the LAST n_keep layers keep their activations: their memory is the first to be freed in the backward
+            hidden, residual = unit_call(z, unit, lambda h, r, layer=layer: layer(h, r, batch, rope), hidden, residual,
+                                         keep_activations=i >= n_layers - n_keep)
         if self.sp_size > 1:
             # keep the rows that live in this rank's slice; _sp_merge puts the per-row results back together
             n_l = hidden.shape[0]
@@ -238,6 +238,36 @@ class NativeEngine(BaseEngine):
         if rows is not None:
             hidden, residual = hidden[rows], residual[rows]
         return hidden, residual
+
+    def _layers_to_keep(self, tokens: int) -> int:
+        """How many decoder layers keep their activations for the backward instead of recomputing them.
+
+        ``gradient_checkpointing=False`` keeps all of them. Otherwise ``keep_activation_layers`` of the engine config
+        decides: an integer, or ``auto`` (default on CUDA): as many layers as fit in the memory that is free right
+        now, after a reserve for the backward's own temporaries. The answer may differ between ranks and between
+        micro-batches; the sequence of collectives does not depend on it."""
+        n_layers = len(self.model.layers)
+        if not self.gradient_checkpointing:
+            return n_layers
+        policy = os.environ.get("VERL_B200_KEEP_ACTIVATION_LAYERS") or _cfg(self.engine_config, "keep_activation_layers", "auto")
+        if str(policy) != "auto":
+            return max(0, min(n_layers, int(policy)))
+        if self.device.type != "cuda":
+            return 0
+        c = self.model_config
+        if c.num_experts:  # routed activations depend on the routing: recompute
+            return 0
+        qkv = (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim
+        per_token = 2 * (5 * c.hidden_size + qkv + c.num_attention_heads * c.head_dim + 3 * c.intermediate_size) + 64
+        per_layer = int(tokens * per_token * 1.1)
+        free, total = torch.cuda.mem_get_info(self.device)
+        free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+        reserve = max(20 << 30, total // 8) + 2 * per_layer
+        n = int(max(0, free - reserve) // max(per_layer, 1))
+        self.last_kept_layers = min(n_layers, n)
+        self.last_keep_info = {"free_gb": round(free / 2**30, 1), "per_layer_gb": round(per_layer / 2**30, 2),
+                               "reserve_gb": round(reserve / 2**30, 1), "tokens": int(tokens)}
+        return self.last_kept_layers
 
     def _sp_merge(self, out):
         """Scatter this rank's per-row results into the full row order and sum over the sequence-parallel group
