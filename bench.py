@@ -275,6 +275,8 @@ def main():
             "mfu_actor": last.get("perf/mfu/actor"),
             "kept_activation_layers": getattr(
                 trainer.actor_rollout_wg.worker.worker_dict["actor_rollout"].actor_engine, "last_kept_layers", 0),
+            "peak_mem_gb": {"allocated": round(torch.cuda.max_memory_allocated() / 2**30, 1),
+                            "reserved": round(torch.cuda.max_memory_reserved() / 2**30, 1)},
             "keep_info": getattr(trainer.actor_rollout_wg.worker.worker_dict["actor_rollout"].actor_engine, "last_keep_info", None),
         }
         if e2e is not None:
