@@ -139,6 +139,45 @@ def check_ag_gemm(comm, rank, world, dev):
         comm.barrier()
 
 
+def check_gemm_rs(comm, rank, world, dev):
+    """Fused GEMM -> reduce-scatter (row-parallel linear) against the fp32 sum of all ranks' products, for a
+    prefill-like and a decode-like (split-K) shape; and a sequence-parallel MLP block built from the TP layers."""
+    from verl_b200.parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear
+
+    for M, N, K in ((1024, 1536, 640), (128, 3584, 2048)):
+        g = torch.Generator(device="cpu").manual_seed(100 + M)
+        xs = [(torch.randn(M, K, generator=g) * 0.5).bfloat16() for _ in range(world)]  # every rank's K-slice
+        ws = [(torch.randn(N, K, generator=g) * 0.05).bfloat16() for _ in range(world)]
+        res = torch.randn(M, N, generator=g).bfloat16()
+        want = sum(x.float() @ w.float().t() for x, w in zip(xs, ws)) + res.float()
+        rows = M // world
+        x, w = xs[rank].to(dev), ws[rank].to(dev)
+        mine = res[rank * rows:(rank + 1) * rows].to(dev).contiguous()
+        for it in range(3):  # repeated calls: the two receive buffers alternate
+            out = comm.gemm_rs(x, w, residual=mine)
+            torch.cuda.synchronize()
+            comm.check()
+            ref = want[rank * rows:(rank + 1) * rows].to(dev)
+            err = (out.float() - ref).abs().max().item()
+            assert err < 0.02 * ref.abs().max().item() + 0.05, (M, N, K, it, err)
+    # column-parallel -> SwiGLU-free elementwise -> row-parallel, against the unsharded computation
+    g = torch.Generator(device="cpu").manual_seed(7)
+    M, H, I = 64 * world, 512, 1024 * world
+    x_full = (torch.randn(M, H, generator=g) * 0.5).bfloat16()
+    w1 = (torch.randn(I, H, generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(H, I, generator=g) * 0.05).bfloat16()
+    want = (torch.relu(x_full.float() @ w1.float().t()).bfloat16().float() @ w2.float().t())
+    ip, rows = I // world, M // world
+    col = ColumnParallelLinear(comm, w1[rank * ip:(rank + 1) * ip].to(dev).contiguous())
+    row = RowParallelLinear(comm, w2[:, rank * ip:(rank + 1) * ip].to(dev).contiguous())
+    y = row(torch.relu(col(x_full[rank * rows:(rank + 1) * rows].to(dev).contiguous())))
+    torch.cuda.synchronize()
+    comm.check()
+    ref = want[rank * rows:(rank + 1) * rows].to(dev)
+    assert (y.float() - ref).abs().max().item() < 0.03 * ref.abs().max().item() + 0.05
+    comm.barrier()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
@@ -154,6 +193,8 @@ def main():
         check_reshard(comm, rank, world, dev)
     if what in ("ag_gemm", "all"):
         check_ag_gemm(comm, rank, world, dev)
+    if what in ("gemm_rs", "all"):
+        check_gemm_rs(comm, rank, world, dev)
     if what in ("zero", "all"):
         check_zero_step(rank, world, dev, comm)
     torch.cuda.synchronize()

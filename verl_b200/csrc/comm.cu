@@ -16,6 +16,8 @@
 //   peer_reduce_scatter_add dst[i] += scale * sum_p peer p's full[rank*shard + i]  (fp32; grad reduce-scatter
 //                           fused with the scale and the accumulation into the optimizer's gradient shard)
 //   nvls_reduce_scatter_add same through multimem.ld_reduce (in-switch add)
+//   peer_sum_slots          second half of GEMM -> reduce-scatter: the GEMM epilogues of all ranks have stored their
+//                           partial rows into this rank's receive slots; barrier, then sum the slots locally
 //   peer_segment_copy       table-driven gather of byte ranges from peers into a local buffer: the
 //                           train -> rollout weight reshard (FSDP shards -> TP/EP layout) in one launch
 #include "common.cuh"
@@ -24,6 +26,12 @@
 namespace vb {
 
 constexpr int MAX_RANKS = 16;
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
 
 struct PeerPtrs {
   void* p[MAX_RANKS];
@@ -176,6 +184,41 @@ __global__ void peer_reduce_scatter_add_generic_kernel(PeerPtrs fulls, PeerPtrs 
   }
 }
 
+// GEMM -> reduce-scatter, second half. slots = this rank's receive buffer [world, n] (bf16 or fp32; slot s was
+// written by rank s's GEMM epilogue over NVLink). After the handshake (every rank's GEMM has finished, so all slots
+// are complete) out[i] = sum_s slots[s][i] (+ residual[i]), fp32 accumulation in rank order. Local reads only.
+template <typename T>
+__global__ void peer_sum_slots_kernel(const T* __restrict__ slots, PeerPtrs pads, T* __restrict__ out,
+                                      const T* __restrict__ residual, long long n, int rank, int world, int channel,
+                                      uint32_t epoch, uint32_t* gate, int* status) {
+  if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
+  constexpr int V = 16 / sizeof(T);
+  const long long n_vec = n / V;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    if (residual != nullptr) {
+      const uint4 rv = reinterpret_cast<const uint4*>(residual)[i];
+      const T* rp = reinterpret_cast<const T*>(&rv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] = to_float(rp[j]);
+    }
+    for (int s = 0; s < world; ++s) {
+      const uint4 v = reinterpret_cast<const uint4*>(slots + (long long)s * n)[i];
+      const T* vp = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += to_float(vp[j]);
+    }
+    uint4 o;
+    T* op = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < V; ++j) op[j] = from_float<T>(acc[j]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
 // Same reduction through the NVSwitch: one multimem.ld_reduce returns the sum over all ranks' copies.
 __global__ void nvls_reduce_scatter_add_kernel(const float* mc_base, PeerPtrs pads, long long full_off4,
                                                float4* __restrict__ dst, long long shard4, float scale, int rank,
@@ -323,6 +366,27 @@ extern "C" int vb_peer_reduce_scatter_add(const void* const* fulls, const void* 
     else if (world == 8) peer_reduce_scatter_add_kernel<8, 2><<<(int)blocks, 256, 0, stream>>>(VB_RS_ARGS);
     else peer_reduce_scatter_add_generic_kernel<<<(int)blocks, 256, 0, stream>>>(VB_RS_ARGS);
 #undef VB_RS_ARGS
+  }
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vb_peer_sum_slots(const void* slots, const void* const* pads, void* out, const void* residual,
+                                 long long n, int fp32, int rank, int world, int channel, unsigned epoch,
+                                 unsigned* gate, int* status, cudaStream_t stream) {
+  if (world > MAX_RANKS || n <= 0 || (n % (fp32 ? 4 : 8)) != 0) return -3;
+  const long long n_vec = n / (fp32 ? 4 : 8);
+  long long blocks = (n_vec + 255) / 256;
+  const long long cap = 4LL * vb_num_sms();
+  if (blocks > cap) blocks = cap;
+  if (fp32) {
+    peer_sum_slots_kernel<float><<<(int)blocks, 256, 0, stream>>>(
+        reinterpret_cast<const float*>(slots), make_ptrs(pads, world), reinterpret_cast<float*>(out),
+        reinterpret_cast<const float*>(residual), n, rank, world, channel, epoch, gate, status);
+  } else {
+    peer_sum_slots_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(slots), make_ptrs(pads, world), reinterpret_cast<__nv_bfloat16*>(out),
+        reinterpret_cast<const __nv_bfloat16*>(residual), n, rank, world, channel, epoch, gate, status);
   }
   vb_count_launch();
   return (int)cudaGetLastError();

@@ -32,6 +32,8 @@ constexpr int GROUP_M = 8;
 enum Epi : int { EPI_STORE = 0, EPI_LSE = 1, EPI_DLOGITS = 2, EPI_STORE_AG = 3 };
 constexpr int AG_COPY_THREADS = 128;  // EPI_STORE_AG: four more warps pull the peers' shards of B
 constexpr int AG_MAX_RANKS = 16;
+constexpr int RS_STAGE_WARP_BYTES = 32 * 256;            // 32 rows x 128 bf16 columns per epilogue warp
+constexpr int RS_STAGE_BYTES = 4 * RS_STAGE_WARP_BYTES + 16;
 
 struct GemmParams {
   int M, N, K;
@@ -70,6 +72,12 @@ struct GemmParams {
   int grp_E;
   const int* grp_blk_expert;
   const int* grp_off;
+  // GEMM -> reduce-scatter (rs_rows > 0): output row r belongs to rank r / rs_rows and is stored at row r % rs_rows
+  // of rs_dst[owner], this rank's slot in the owner's receive buffer (peer memory, plain stores over NVLink).
+  void* rs_dst[AG_MAX_RANKS];
+  int rs_rows;
+  int rs_stage;  // bf16 tiles go through a per-warp shared-memory transpose so that a store instruction covers whole
+                 // 256-byte row segments (uncoalesced 16-byte stores crawl over NVLink); needs RS_STAGE_BYTES more smem
   const void* ag_src[AG_MAX_RANKS];
   long long ag_shard;
   long long ag_w_off;
@@ -131,8 +139,19 @@ struct Sched {
   }
 };
 
+// Base pointer and row index for an output row: the local C, or the owner's receive slot for GEMM -> reduce-scatter.
+__device__ __forceinline__ void* epi_row_base(const GemmParams& p, int& row) {
+  if (p.rs_rows > 0) {
+    const int owner = row / p.rs_rows;
+    row -= owner * p.rs_rows;
+    return p.rs_dst[owner];
+  }
+  return p.C;
+}
+
 // Final store of 32 consecutive columns of one output row (bias, fp32 accumulate or bf16 pack).
 __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, int row, int col0, uint32_t (&r)[32]) {
+                void* const cbase = epi_row_base(p, row);
                 if (p.bias != nullptr) {
   #pragma unroll
                   for (int i = 0; i < 32; ++i) {
@@ -140,7 +159,7 @@ __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, int row, in
                   }
                 }
                 if (p.out_fp32) {
-                  float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+                  float* dst = reinterpret_cast<float*>(cbase) + (long long)row * p.ldc + col0;
                   if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
   #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -163,7 +182,7 @@ __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, int row, in
                     }
                   }
                 } else {
-                  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+                  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cbase) + (long long)row * p.ldc + col0;
                   if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
   #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -186,13 +205,14 @@ __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, int row, in
 __device__ __forceinline__ void epi_store4(const GemmParams& p, int row, int col, float4 v) {
   float x[4] = {v.x, v.y, v.z, v.w};
   const bool full = col + 4 <= p.N;
+  void* const cbase = epi_row_base(p, row);
   if (p.bias != nullptr) {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       if (col + i < p.N) x[i] += __bfloat162float(p.bias[col + i]);
   }
   if (p.out_fp32) {
-    float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+    float* dst = reinterpret_cast<float*>(cbase) + (long long)row * p.ldc + col;
     if (full && (p.ldc & 3) == 0) {
       float4 o = make_float4(x[0], x[1], x[2], x[3]);
       if (p.accumulate) {
@@ -206,7 +226,7 @@ __device__ __forceinline__ void epi_store4(const GemmParams& p, int row, int col
         if (col + i < p.N) dst[i] = p.accumulate ? dst[i] + x[i] : x[i];
     }
   } else {
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cbase) + (long long)row * p.ldc + col;
     if (full && (p.ldc & 3) == 0) {
       *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]));
     } else {
@@ -515,6 +535,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               for (int i = 0; i < 8; ++i)
                 __stcg(dst + i, make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
                                             __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])));
+            } else if (p.rs_stage) {
+              // GEMM -> reduce-scatter over NVLink: transpose 128-column groups through shared memory, then every
+              // store instruction of the warp writes two whole 256-byte row segments of the owner's slot
+              uint8_t* stg = smem + ((L::TOTAL + 15) & ~15) + quad * RS_STAGE_WARP_BYTES;
+              const int cl = c & 3;
+              if (p.bias != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < p.N) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[col0 + i]));
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                const int piece = cl * 4 + j;
+                *reinterpret_cast<uint4*>(stg + lane * 256 + ((piece ^ (lane & 15)) << 4)) = v;
+              }
+              if (cl == 3 || c == BN / 32 - 1) {
+                __syncwarp();
+                const int col_base = nb * BN + (c - cl) * 32;
+                const int pieces = (cl + 1) * 4;
+#pragma unroll 4
+                for (int i = 0; i < 16; ++i) {
+                  const int idx = i * 32 + lane;
+                  const int rr = idx >> 4, piece = idx & 15;
+                  const int grow = m_blk * BM + quad * 32 + rr, gcol = col_base + piece * 8;
+                  if (piece < pieces && grow < p.M && gcol < p.N) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 256 + ((piece ^ (rr & 15)) << 4));
+                    const int owner = grow / p.rs_rows;
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) +
+                                         (long long)(grow - owner * p.rs_rows) * p.ldc + gcol;
+                    *reinterpret_cast<uint4*>(dst) = v;
+                  }
+                }
+                __syncwarp();
+              }
             } else if (row_ok && col0 < p.N) {
               epi_store_chunk(p, row, col0, r);
             }
@@ -972,9 +1031,13 @@ static int launch_gemm(const void* A, const void* B, long long lda, long long ld
   else rc = vb_make_tmap_2d(&tmB, B, 2, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldb * 2, BK, BN);
   if (rc) return rc;
   auto kern = gemm_kernel<BN, A_MN, B_MN, EPI>;
+  constexpr bool can_stage = EPI == EPI_STORE && BN >= 64;  // room for the reduce-scatter staging area
+  if (p.rs_stage && !can_stage) return -3;
+  const int dyn_bytes = L::DYN_BYTES + (p.rs_stage ? RS_STAGE_BYTES : 0);
   static bool attr_set = false;
   if (!attr_set) {
-    VB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    VB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       L::DYN_BYTES + (can_stage ? RS_STAGE_BYTES : 0)));
     attr_set = true;
   }
   const int num_m = (p.M + BM - 1) / BM;
@@ -986,18 +1049,18 @@ static int launch_gemm(const void* A, const void* B, long long lda, long long ld
     // the split-K reduction has a grid-wide barrier: every CTA owns one unit and all of them must be resident
     if (units > vb_num_sms()) return -3;
     void* args[] = {(void*)&tmA, (void*)&tmB, (void*)&p};
-    cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3(units), dim3(NUM_THREADS), args, L::DYN_BYTES, stream);
+    cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3(units), dim3(NUM_THREADS), args, dyn_bytes, stream);
     if (e != cudaSuccess) {
       // e.g. a capture mode that refuses cooperative nodes: a plain launch of at most one CTA per SM is resident as
       // a whole on an otherwise idle device, and the barrier's wait is bounded in any case
       (void)cudaGetLastError();
-      kern<<<units, NUM_THREADS, L::DYN_BYTES, stream>>>(tmA, tmB, p);
+      kern<<<units, NUM_THREADS, dyn_bytes, stream>>>(tmA, tmB, p);
       e = cudaGetLastError();
     }
     vb_count_launch();
     return (int)e;
   }
-  kern<<<grid, NUM_THREADS, L::DYN_BYTES, stream>>>(tmA, tmB, p);
+  kern<<<grid, NUM_THREADS, dyn_bytes, stream>>>(tmA, tmB, p);
   vb_count_launch();
   return (int)cudaGetLastError();
 }
@@ -1015,10 +1078,10 @@ using namespace vb;
 // ws / counters (optional): fp32 workspace of ws_bytes and num_counters zeroed ints that enable split-K for
 // problems with too few output tiles to occupy the GPU (decode-time projections: M <= 128, large K). Calls
 // that share a workspace must be ordered on one stream. The counters are left at zero.
-extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
-                               long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32,
-                               int accumulate, float* ws, long long ws_bytes, int* counters, int num_counters,
-                               int* status, cudaStream_t stream) {
+static int gemm_bf16_run(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                         long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32,
+                         int accumulate, float* ws, long long ws_bytes, int* counters, int num_counters,
+                         int* status, cudaStream_t stream, void* const* rs_dst, int rs_world, int rs_rows) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7)) return -3;
   GemmParams p{};
@@ -1026,6 +1089,14 @@ extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void
   p.C = C; p.ldc = ldc; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.out_fp32 = out_fp32; p.accumulate = accumulate; p.status = status;
   p.k_splits = 1;
+  if (rs_dst != nullptr) {
+    if (rs_world < 1 || rs_world > AG_MAX_RANKS || rs_rows <= 0 || (long long)rs_rows * rs_world < M || accumulate)
+      return -3;
+    for (int r = 0; r < rs_world; ++r) p.rs_dst[r] = rs_dst[r];
+    p.rs_rows = rs_rows;
+    // bf16 tiles of non-skinny problems take the coalescing path (single-CTA kernel, tiles 128 or 256 wide)
+    p.rs_stage = (!out_fp32 && M > 256 && N >= 128 && (N & 7) == 0 && (ldc & 7) == 0) ? 1 : 0;
+  }
   static const int splitk_mode = []() {
     const char* e = getenv("VERL_B200_SPLITK");  // 0 = never split K, N > 1 = force that many slices (experiments)
     return e ? atoi(e) : -1;
@@ -1078,7 +1149,7 @@ extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void
     const char* e = getenv("VERL_B200_GEMM_PAIR");
     return !(e && e[0] == '0');
   }();
-  if (pair_enabled && M >= 512 && N >= 512 && K >= 256 &&
+  if (pair_enabled && !p.rs_stage && M >= 512 && N >= 512 && K >= 256 &&
       (long long)((M + 255) / 256) * ((N + 255) / 256) >= vb_num_sms()) {
     int rc;
     if (!a_mn && !b_mn) rc = launch_gemm_pair<false, false>(A, B, lda, ldb, p, stream);
@@ -1096,9 +1167,10 @@ extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void
   if (N <= 128 || tiles(256) < want) bn = 128;
   const bool kk = !a_mn && !b_mn;
   if (kk && bn == 128 && tiles(128) < want) bn = 64;
-  if (kk && bn == 64 && tiles(64) < want) bn = 32;
+  if (kk && bn == 64 && tiles(64) < want && !p.rs_stage) bn = 32;
   if (N <= 32 && kk) bn = 32;
   else if (N <= 64 && kk) bn = bn < 64 ? bn : 64;
+  if (p.rs_stage && bn < 64) p.rs_stage = 0;  // no room for the staging area next to ten pipeline stages
 #define VB_DISPATCH(AMN, BMN)                                                              \
   (bn == 256 ? launch_gemm<256, AMN, BMN, EPI_STORE>(A, B, lda, ldb, p, stream)             \
              : launch_gemm<128, AMN, BMN, EPI_STORE>(A, B, lda, ldb, p, stream))
@@ -1111,6 +1183,28 @@ extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void
   if (a_mn && b_mn) return VB_DISPATCH(true, true);
   return VB_DISPATCH(true, false);
 #undef VB_DISPATCH
+}
+
+extern "C" int vb_gemm_bf16_ws(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                               long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32,
+                               int accumulate, float* ws, long long ws_bytes, int* counters, int num_counters,
+                               int* status, cudaStream_t stream) {
+  return gemm_bf16_run(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, ws, ws_bytes, counters,
+                       num_counters, status, stream, nullptr, 0, 0);
+}
+
+// GEMM -> reduce-scatter, first half: C = A [M, K] . B [N, K]^T is this rank's partial sum of a row-parallel linear
+// layer. Row r of the result belongs to rank r / rows_per_rank; the epilogue stores every tile straight into
+// dsts[owner] (this rank's slot [rows_per_rank, N] in the owner's receive buffer, peer memory), so the transfer
+// over NVLink overlaps the tiles still being computed. The owner adds the slots up after a cross-rank barrier
+// (vb_peer_sum_slots). Same tiling, split-K and CTA-pair dispatch as the plain GEMM.
+extern "C" int vb_gemm_rs_bf16(const void* A, const void* B, const void* bias, int M, int N, int K, long long lda,
+                               long long ldb, long long ldc, void* const* dsts, int world, int rows_per_rank,
+                               int out_fp32, float* ws, long long ws_bytes, int* counters, int num_counters,
+                               int* status, cudaStream_t stream) {
+  if (dsts == nullptr) return -3;
+  return gemm_bf16_run(A, B, dsts[0], bias, M, N, K, lda, ldb, ldc, 0, 0, out_fp32, 0, ws, ws_bytes, counters,
+                       num_counters, status, stream, dsts, world, rows_per_rank);
 }
 
 // Grouped GEMM for mixture-of-experts layers, one launch for all experts.

@@ -40,6 +40,9 @@ def _bind():
     lib.vb_peer_reduce_scatter_add.argtypes = [P, P, P, L, P, L, F, I, I, I, U, P, P, P]
     lib.vb_peer_reduce_scatter_add.restype = I
     lib.vb_peer_segment_copy.argtypes, lib.vb_peer_segment_copy.restype = [P, P, P, I, P, I, I, I, U, P, P, P], I
+    lib.vb_gemm_rs_bf16.argtypes = [P, P, P, I, I, I, L, L, L, P, I, I, I, P, L, P, I, P, P]
+    lib.vb_gemm_rs_bf16.restype = I
+    lib.vb_peer_sum_slots.argtypes, lib.vb_peer_sum_slots.restype = [P, P, P, P, L, I, I, I, I, U, P, P, P], I
     _SIGS_BOUND = True
     return lib
 
@@ -214,6 +217,52 @@ class PeerComm:
                                       int(out_dtype == torch.float32), self._status(), _lib.stream())
         _lib.check(rc, "vb_ag_gemm_bf16")
         return out, w_full
+
+    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Fused GEMM -> reduce-scatter of a row-parallel linear layer: every rank holds ``x [M, K_local]`` and
+        ``w [N, K_local]`` (its slice of the contraction); returns rows ``[rank * M / world, (rank + 1) * M / world)``
+        of ``sum_ranks x @ w^T`` (+ ``residual`` for those rows; ``bias`` is added by rank 0's partial).
+
+        The GEMM epilogue stores each finished tile into the owning rank's receive slot over NVLink while later tiles
+        are still being computed; a second kernel waits for all ranks (bounded handshake) and adds the slots up from
+        local memory. Collective: every rank calls it with the same shapes. Two receive buffers alternate, so a slot
+        is rewritten only after every peer has passed the handshake of the following call."""
+        from ..ops.gemm import _SPLITK_COUNTERS, _SPLITK_MAX_M, _splitk_workspace
+
+        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+        M, K = x.shape
+        N = w.shape[0]
+        W = self.world
+        assert M % W == 0 and N % 8 == 0 and w.shape[1] == K, (M, N, K, W)
+        rows = M // W
+        n = rows * N
+        key = ("gemm_rs", n)
+        bufs = self.__dict__.setdefault("_rs_slots", {})
+        if key not in bufs:
+            bufs[key] = [self.alloc(W * n, torch.bfloat16, zero=False) for _ in range(2)] + [0]
+            self.barrier()
+        ent = bufs[key]
+        slots = ent[ent[2] & 1]
+        ent[2] += 1
+        a, off = self._find(slots)
+        dsts = (ctypes.c_void_p * W)(*[int(p) + off + self.rank * n * 2 for p in a.ptrs])
+        stream = _lib.stream()
+        ws, counters = _splitk_workspace(x.device, stream) if M <= _SPLITK_MAX_M else (None, None)
+        use_bias = bias if self.rank == 0 else None
+        rc = self.lib.vb_gemm_rs_bf16(x.data_ptr(), w.data_ptr(), _lib.ptr(use_bias), M, N, K, x.stride(0), w.stride(0), N,
+                                      dsts, W, rows, 0, _lib.ptr(ws), ws.numel() * 4 if ws is not None else 0,
+                                      _lib.ptr(counters), _SPLITK_COUNTERS if ws is not None else 0, self._status(),
+                                      stream)
+        _lib.check(rc, "vb_gemm_rs_bf16")
+        out = torch.empty((rows, N), dtype=torch.bfloat16, device=x.device)
+        if residual is not None:
+            assert residual.shape == out.shape and residual.is_contiguous() and residual.dtype == out.dtype
+        rc = self.lib.vb_peer_sum_slots(slots.data_ptr(), self.pad_alloc.ptrs, out.data_ptr(), _lib.ptr(residual), n, 0,
+                                        self.rank, W, self.CH_REDUCE, self._epoch(self.CH_REDUCE),
+                                        self._gate(self.CH_REDUCE), self._status(), stream)
+        _lib.check(rc, "vb_peer_sum_slots")
+        return out
 
     def check(self):
         """Synchronising read of the status word; raises if a bounded wait ran out."""
