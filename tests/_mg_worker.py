@@ -178,6 +178,43 @@ def check_gemm_rs(comm, rank, world, dev):
     comm.barrier()
 
 
+def check_moe_ep(comm, rank, world, dev):
+    """Expert-parallel MoE (dispatch -> grouped GEMMs on the owners -> combine) against every expert evaluated in
+    fp32 on this rank's own tokens. Two rounds with different routings reuse the buffers."""
+    from verl_b200 import ops
+    from verl_b200.parallel.expert_parallel import ExpertParallelMoE
+
+    E, H, I, k, T = 4 * world, 512, 256, 2, 300
+    g = torch.Generator(device="cpu").manual_seed(11)
+    gate_up = (torch.randn(E, 2 * I, H, generator=g) * 0.05).bfloat16()
+    down = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16()
+    El = E // world
+    gu_l, dn_l = gate_up[rank * El:(rank + 1) * El].to(dev).contiguous(), down[rank * El:(rank + 1) * El].to(dev).contiguous()
+    ep = ExpertParallelMoE(comm, E, H, k, max_tokens=T)
+    for rnd in range(2):
+        gr = torch.Generator(device="cpu").manual_seed(100 * rnd + rank)
+        n_tok = T - 37 * rank - 11 * rnd  # ranks hold different numbers of tokens
+        x = (torch.randn(n_tok, H, generator=gr) * 0.5).bfloat16()
+        logits = torch.randn(n_tok, E, generator=gr)
+        if rnd == 1:
+            logits[:, 0] += 4.0  # skewed routing: most tokens on expert 0 (rank 0)
+        top_w, top_i = torch.softmax(logits, -1).topk(k, -1)
+        out = ep.forward(x.to(dev), top_i.to(dev), top_w.to(dev), gu_l, dn_l, ops.swiglu)
+        torch.cuda.synchronize()
+        comm.check()
+        ref = torch.zeros(n_tok, H)
+        for j in range(k):
+            for e in range(E):
+                m = top_i[:, j] == e
+                if m.any():
+                    hgu = (x[m].float() @ gate_up[e].float().t()).bfloat16().float()
+                    act = (torch.nn.functional.silu(hgu[:, :I]) * hgu[:, I:]).bfloat16().float()
+                    ref[m] += top_w[m, j, None] * (act @ down[e].float().t()).bfloat16().float()
+        err = (out.float().cpu() - ref).abs().max().item()
+        assert err < 0.02 * ref.abs().max().item() + 0.02, (rnd, err, ref.abs().max().item())
+    comm.barrier()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
@@ -193,6 +230,8 @@ def main():
         check_reshard(comm, rank, world, dev)
     if what in ("ag_gemm", "all"):
         check_ag_gemm(comm, rank, world, dev)
+    if what in ("moe_ep", "all"):
+        check_moe_ep(comm, rank, world, dev)
     if what in ("gemm_rs", "all"):
         check_gemm_rs(comm, rank, world, dev)
     if what in ("zero", "all"):

@@ -18,6 +18,8 @@
 //   nvls_reduce_scatter_add same through multimem.ld_reduce (in-switch add)
 //   peer_sum_slots          second half of GEMM -> reduce-scatter: the GEMM epilogues of all ranks have stored their
 //                           partial rows into this rank's receive slots; barrier, then sum the slots locally
+//   moe_dispatch / combine  expert-parallel MoE: tokens pushed into the expert owner's grouped-GEMM-ready receive
+//                           buffer; expert outputs pulled back and mixed with the routing weights
 //   peer_segment_copy       table-driven gather of byte ranges from peers into a local buffer: the
 //                           train -> rollout weight reshard (FSDP shards -> TP/EP layout) in one launch
 #include "common.cuh"
@@ -388,6 +390,194 @@ extern "C" int vb_peer_sum_slots(const void* slots, const void* const* pads, voi
         reinterpret_cast<const __nv_bfloat16*>(slots), make_ptrs(pads, world), reinterpret_cast<__nv_bfloat16*>(out),
         reinterpret_cast<const __nv_bfloat16*>(residual), n, rank, world, channel, epoch, gate, status);
   }
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Expert-parallel MoE: dispatch (push) and combine (pull) over peer memory.
+//
+// Rank r owns experts [r * E_local, (r + 1) * E_local). The host side has all-gathered the per-rank expert histograms,
+// so every rank knows where its rows of expert e start in the owner's receive buffer (base[e]); the buffer is laid out
+// exactly as the grouped GEMM wants it (rows sorted by expert, every expert padded to 128 rows), so the owner runs its
+// experts on the received rows without sorting them.
+//   dispatch: one warp per (token, slot) pair claims the next row of its expert's sub-range (local atomic) and stores
+//             the token's hidden vector there with 512-byte warp stores over NVLink; `where` remembers the row.
+//   combine:  after a bounded cross-rank handshake (all owners have finished their experts), one warp per token loads
+//             its k expert outputs from the owners' buffers (all k loads in flight) and writes the weighted sum.
+__global__ void moe_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ top_i, int pairs, int k,
+                                    int h16, int e_local, const int* __restrict__ base, int* __restrict__ cursor,
+                                    PeerPtrs recv, int* __restrict__ where, long long cap_rows, int* status) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int pair = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; pair < pairs; pair += warps) {
+    const int e = top_i[pair];
+    int pos = 0;
+    if (lane == 0) pos = base[e] + atomicAdd(cursor + e, 1);
+    pos = __shfl_sync(0xffffffffu, pos, 0);
+    if (pos < 0 || pos >= cap_rows) {  // the receive buffer is too small for this routing: refuse, do not write
+      if (lane == 0) {
+        report_error(status, ERR_BAD_ARG, pair);
+        where[pair] = -1;
+      }
+      continue;
+    }
+    const uint4* src = x + (long long)(pair / k) * h16;
+    uint4* dst = reinterpret_cast<uint4*>(recv.p[e / e_local]) + (long long)pos * h16;
+    for (int i = lane; i < h16; i += 32) dst[i] = src[i];
+    if (lane == 0) where[pair] = pos;
+  }
+}
+
+// Histogram of this rank's routing (one block): hist[e] = number of (token, slot) pairs routed to expert e.
+__global__ void moe_hist_kernel(const int* __restrict__ top_i, int pairs, int num_experts, int* __restrict__ hist) {
+  extern __shared__ int h_s[];
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) h_s[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = top_i[i];
+    if (e >= 0 && e < num_experts) atomicAdd(h_s + e, 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) hist[e] = h_s[e];
+}
+
+// From the all-gathered histograms hist_all [world, hist_stride] (one block): base[e] = first row, in the owner's
+// receive buffer, of this rank's rows of expert e; expert_off [e_local + 1] and blk_expert [blocks] describe the rows
+// this rank receives (every expert padded to 128 rows; blocks past the end are -1); cursor [E] is zeroed.
+__global__ void moe_layout_kernel(const int* __restrict__ hist_all, int hist_stride, int num_experts, int e_local,
+                                  int rank, int world, int* __restrict__ base, int* __restrict__ expert_off,
+                                  int* __restrict__ blk_expert, int blocks, int* __restrict__ cursor) {
+  extern __shared__ int l_s[];
+  int* padded = l_s;                 // [E]
+  int* off = l_s + num_experts;      // [E] owner-local first row of every expert
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    int tot = 0;
+    for (int s2 = 0; s2 < world; ++s2) tot += hist_all[s2 * hist_stride + e];
+    padded[e] = (tot + 127) / 128 * 128;
+    cursor[e] = 0;
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < world; o += blockDim.x) {  // one thread per owner: serial scan of its experts
+    int run = 0;
+    for (int j = 0; j < e_local; ++j) {
+      off[o * e_local + j] = run;
+      run += padded[o * e_local + j];
+    }
+    if (o == rank) expert_off[e_local] = run;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    int before = 0;
+    for (int s2 = 0; s2 < rank; ++s2) before += hist_all[s2 * hist_stride + e];
+    base[e] = off[e] + before;
+    if (e / e_local == rank) expert_off[e - rank * e_local] = off[e];
+  }
+  const int* my_off = off + rank * e_local;
+  const int* my_pad = padded + rank * e_local;
+  for (int b = threadIdx.x; b < blocks; b += blockDim.x) {
+    const int r0 = b * 128;
+    int found = -1;
+    for (int j = 0; j < e_local; ++j)
+      if (r0 >= my_off[j] && r0 < my_off[j] + my_pad[j]) found = j;
+    blk_expert[b] = found;
+  }
+}
+
+extern "C" int vb_moe_hist(const int* top_i, int pairs, int num_experts, int* hist, cudaStream_t stream) {
+  if (num_experts < 1 || num_experts > 8192) return -3;
+  moe_hist_kernel<<<1, 1024, num_experts * sizeof(int), stream>>>(top_i, pairs, num_experts, hist);
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vb_moe_layout(const int* hist_all, int hist_stride, int num_experts, int e_local, int rank, int world,
+                             int* base, int* expert_off, int* blk_expert, int blocks, int* cursor,
+                             cudaStream_t stream) {
+  if (num_experts < 1 || num_experts > 4096 || e_local * world != num_experts) return -3;
+  moe_layout_kernel<<<1, 256, 2 * num_experts * sizeof(int), stream>>>(hist_all, hist_stride, num_experts, e_local, rank,
+                                                                      world, base, expert_off, blk_expert, blocks, cursor);
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+template <int KMAX>
+__global__ void moe_combine_kernel(PeerPtrs y, PeerPtrs pads, const int* __restrict__ top_i,
+                                   const float* __restrict__ top_w, const int* __restrict__ where, int tokens, int k,
+                                   int h16, int e_local, uint4* __restrict__ out, int rank, int world, int channel,
+                                   uint32_t epoch, uint32_t* gate, int* status) {
+  if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < tokens; t += warps) {
+    const uint4* rowp[KMAX];
+    float w[KMAX];
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) {
+      rowp[j] = nullptr;
+      w[j] = 0.f;
+      if (j < k) {
+        const int row = where[t * k + j];
+        if (row >= 0) {
+          rowp[j] = reinterpret_cast<const uint4*>(y.p[top_i[t * k + j] / e_local]) + (long long)row * h16;
+          w[j] = top_w[t * k + j];
+        }
+      }
+    }
+    for (int i = lane; i < h16; i += 32) {
+      uint4 v[KMAX];
+#pragma unroll
+      for (int j = 0; j < KMAX; ++j) v[j] = rowp[j] != nullptr ? rowp[j][i] : make_uint4(0u, 0u, 0u, 0u);
+      float acc[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+#pragma unroll
+      for (int j = 0; j < KMAX; ++j) {
+        const __nv_bfloat16* hp = reinterpret_cast<const __nv_bfloat16*>(&v[j]);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] += w[j] * __bfloat162float(hp[q]);
+      }
+      uint4 o;
+      __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) op[q] = __float2bfloat16(acc[q]);
+      out[(long long)t * h16 + i] = o;
+    }
+  }
+}
+
+extern "C" int vb_moe_dispatch(const void* x, const int* top_i, int tokens, int k, int hidden, int e_local,
+                               const int* base, int* cursor, const void* const* recv, int world, int* where,
+                               long long cap_rows, int* status, cudaStream_t stream) {
+  if (world > MAX_RANKS || (hidden & 7) || k < 1 || e_local < 1) return -3;
+  const int pairs = tokens * k;
+  if (pairs <= 0) return 0;
+  int blocks = (pairs + 7) / 8;  // 8 warps per block
+  const int cap = 8 * vb_num_sms();
+  if (blocks > cap) blocks = cap;
+  moe_dispatch_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(x), top_i, pairs, k, hidden / 8, e_local,
+                                                  base, cursor, make_ptrs(recv, world), where, cap_rows, status);
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vb_moe_combine(const void* const* y, const void* const* pads, const int* top_i, const float* top_w,
+                              const int* where, int tokens, int k, int hidden, int e_local, void* out, int rank,
+                              int world, int channel, unsigned epoch, unsigned* gate, int* status,
+                              cudaStream_t stream) {
+  if (world > MAX_RANKS || (hidden & 7) || k < 1 || k > 8 || e_local < 1) return -3;
+  int blocks = (tokens + 7) / 8;
+  const int cap = 8 * vb_num_sms();
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;  // the handshake must run even when this rank has no tokens
+#define VB_COMBINE(KM)                                                                                              \
+  moe_combine_kernel<KM><<<blocks, 256, 0, stream>>>(make_ptrs(y, world), make_ptrs(pads, world), top_i, top_w, where, \
+                                                     tokens, k, hidden / 8, e_local, reinterpret_cast<uint4*>(out), rank, \
+                                                     world, channel, epoch, gate, status)
+  if (k <= 2) VB_COMBINE(2);
+  else if (k <= 4) VB_COMBINE(4);
+  else VB_COMBINE(8);
+#undef VB_COMBINE
   vb_count_launch();
   return (int)cudaGetLastError();
 }

@@ -1,7 +1,7 @@
 """Multi-GPU micro-benchmarks of the peer-memory collectives and the fused compute + collective kernels.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        -m verl_b200.parallel.microbench {collectives,ag_gemm,gemm_rs}
+        -m verl_b200.parallel.microbench {collectives,ag_gemm,gemm_rs,moe_ep}
 
 Device time from CUDA events after warm-up, maximum over ranks. Every fused kernel is printed next to its unfused
 form (our GEMM, then the collective) and the NCCL collective, with the roofline figure: the slower of FLOPs over the
@@ -119,6 +119,58 @@ def bench_gemm_rs(comm, rank, world, dev):
     comm.check()
 
 
+def bench_moe_ep(comm, rank, world, dev):
+    """Expert-parallel MoE layer of the Qwen3-30B-A3B architecture (hidden 2048, 128 experts, top-8, expert
+    intermediate 768): whole layer, and its communication (dispatch + combine) next to NCCL all-to-alls of the same
+    payload (uniform random routing)."""
+    from .. import ops
+    from .expert_parallel import ExpertParallelMoE
+
+    E, H, I, k = 128, 2048, 768, 8
+    El = E // world
+    gate_up = (torch.randn(El, 2 * I, H, device=dev) * 0.02).bfloat16()
+    down = (torch.randn(El, H, I, device=dev) * 0.02).bfloat16()
+    for T in (4096, 128):
+        ep = ExpertParallelMoE(comm, E, H, k, max_tokens=T, capacity_rows=2 * T * k + El * 127)
+        x = (torch.randn(T, H, device=dev) * 0.5).bfloat16()
+        top_w, top_i = torch.softmax(torch.randn(T, E, device=dev), -1).topk(k, -1)
+        layer = _timeit(lambda: ep.forward(x, top_i, top_w, gate_up, down, ops.swiglu), dev)
+        comm.check()
+
+        def comm_only():  # layout + dispatch + handshake + combine (the experts' output buffer is read as it is)
+            ti, tw = top_i.to(torch.int32), top_w.float()
+            base, _, _ = ep.layout(ti)
+            where = torch.empty(T * k, dtype=torch.int32, device=dev)
+            ep.lib.vb_moe_dispatch(x.data_ptr(), ti.data_ptr(), T, k, H, El, base.data_ptr(), ep.cursor.data_ptr(),
+                                   ep._recv_ptrs, world, where.data_ptr(), ep.cap, comm._status(), _stream())
+            comm.barrier()
+            out = torch.empty_like(x)
+            ep.lib.vb_moe_combine(ep._y_ptrs, comm.pad_alloc.ptrs, ti.data_ptr(), tw.data_ptr(), where.data_ptr(), T, k, H, El,
+                                  out.data_ptr(), rank, world, comm.CH_COPY, comm._epoch(comm.CH_COPY),
+                                  comm._gate(comm.CH_COPY), comm._status(), _stream())
+
+        t_comm = _timeit(comm_only, dev)
+        rows = T * k
+        send = torch.empty(rows, H, dtype=torch.bfloat16, device=dev)
+        recv = torch.empty_like(send)
+
+        def nccl():
+            dist.all_to_all_single(recv, send)
+            dist.all_to_all_single(send, recv)
+
+        t_nccl = _timeit(nccl, dev)
+        remote = rows * H * 2 * (world - 1) / world  # bytes leaving (dispatch) and entering (combine) this GPU
+        link = 2 * remote / (NVLINK_GBS * 1e6)
+        if rank == 0:
+            print(f"moe_ep T={T}/rank: layer {layer * 1e3:.1f} us, dispatch+combine {t_comm * 1e3:.1f} us "
+                  f"({2 * remote / t_comm / 1e6:.0f} GB/s over NVLink, link-time {link * 1e3:.1f} us = {link / t_comm:.2f}), "
+                  f"two NCCL all-to-alls of the same payload {t_nccl * 1e3:.1f} us")
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
@@ -128,7 +180,7 @@ def main():
 
     comm = PeerComm(dist.group.WORLD)
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm_rs"
-    {"collectives": bench_collectives, "ag_gemm": bench_ag_gemm, "gemm_rs": bench_gemm_rs}[what](comm, rank, world, dev)
+    {"collectives": bench_collectives, "ag_gemm": bench_ag_gemm, "gemm_rs": bench_gemm_rs, "moe_ep": bench_moe_ep}[what](comm, rank, world, dev)
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
