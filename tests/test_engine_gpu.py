@@ -93,6 +93,43 @@ def test_kept_activations_match_recomputation_on_gpu():
     assert auto._layers_to_keep(4096) == cfg.num_hidden_layers  # a tiny model on an empty GPU keeps everything
 
 
+def test_lora_step_on_gpu_matches_cpu_fp32():
+    """LoRA through the tcgen05 GEMMs (rank-8 contraction and rank-8 output): gradients of the adapters against the
+    same model in fp32 on the CPU; the base shard does not change."""
+    from verl_b200.models.lora import lora_named_parameters
+    from verl_b200.workers.engine.native import NativeEngine
+
+    class C(dict):
+        __getattr__ = dict.get
+
+    cfg = _cfg("dense")
+    lora = {"rank": 8, "alpha": 16}
+    lens = [150, 64, 257]
+    grads = {}
+    for dev in ("cuda", "cpu"):
+        eng = NativeEngine(cfg, C(), C(lr=1e-2, clip_grad=1e9, weight_decay=0.0), device=dev, seed=9, lora=lora).initialize()
+        with torch.no_grad():  # B = 0 would make dA vanish: give both adapters the same non-zero values on both devices
+            g = torch.Generator().manual_seed(1)
+            for n, p in lora_named_parameters(eng.model):
+                if n.endswith("lora_B"):
+                    p.copy_((torch.randn(p.shape, generator=g) * 0.02).to(p.device))
+        batch, ids = _batch(cfg, lens, dev)
+        rows = torch.arange(ids.numel() - 1, device=dev)
+        labels = ids.to(dev)[rows + 1]
+        base0 = eng.zero.shard16.clone()
+        with eng.train_mode():
+            eng.optimizer_zero_grad()
+            lp, _ = eng.forward_logprob(batch, rows, labels, 1.0)
+            (-lp.mean()).backward()
+            grads[dev] = {n: p.grad.detach().float().cpu().clone() for n, p in lora_named_parameters(eng.model)}
+            gn = eng.optimizer_step()
+        assert float(gn) > 0 and torch.equal(eng.zero.shard16, base0)
+    for n, g_ref in grads["cpu"].items():
+        g = grads["cuda"][n]
+        denom = g_ref.abs().max().item() + 1e-6
+        assert (g - g_ref).abs().max().item() / denom < 0.08, n
+
+
 @pytest.mark.parametrize("kind", ["dense", "moe"])
 def test_rollout_graph_matches_eager_and_training_logprobs(kind):
     """Greedy generation: CUDA-graph decode = eager decode, and the rollout log-probs agree with the training engine's

@@ -66,7 +66,11 @@ class Linear(nn.Module):
                 self.bias.zero_()
 
     def forward(self, x):
-        return ops.linear(x, self.weight, self.bias)
+        y = ops.linear(x, self.weight, self.bias)
+        a = self.__dict__.get("lora_A")
+        if a is not None and not self.__dict__.get("lora_off", False):  # LoRA branch (models/lora.py): fp32 adapters, cast at use
+            y = y + self.lora_scale * ops.linear(ops.linear(x, a.to(x.dtype)), self.lora_B.to(x.dtype))
+        return y
 
 
 class RMSNormWeight(nn.Module):

@@ -60,6 +60,9 @@ class ZeroShardedParams:
         self.work_dtype = work_dtype
         self.device = torch.device(device)
         self.trainable = trainable
+        # frozen parameters inside a differentiable graph (LoRA base weights): unit calls run under autograd so that
+        # gradients reach the inputs and the tensors captured by the call, but nothing is kept for the parameters
+        self.frozen_grad = False
         self.comm = comm  # optional accelerated collectives (peer-memory kernels); falls back to torch.distributed
         self.units: list[ZeroUnit] = []
         self._anchor = None
@@ -415,7 +418,7 @@ def unit_call(zero: ZeroShardedParams, unit: ZeroUnit, fn: Callable, *args, keep
     unit's gradients are reduce-scattered right after its backward."""
     mask = tuple(a is not None for a in args)
     tensors = [a for a in args if a is not None]
-    if torch.is_grad_enabled() and zero.trainable:
+    if torch.is_grad_enabled() and (zero.trainable or zero.frozen_grad):
         # a unit whose inputs carry no gradient (the embedding: integer ids) must still get a backward
         # call for its parameters, so every call is anchored on a scalar that requires grad
         if zero._anchor is None:

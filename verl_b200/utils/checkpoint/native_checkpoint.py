@@ -80,6 +80,15 @@ def save_engine_checkpoint(engine, local_path: str, global_step: int = 0,
     if "extra" in save_contents:
         torch.save({"lr_scheduler": {"lr_step": engine.lr_step, "step_count": engine.step_count}, "rng": _rng_state(),
                     "global_step": global_step}, path / f"extra_state_world_size_{W}_rank_{r}.pt")
+    if getattr(engine, "_lora_params", None) and r == 0:
+        # LoRA: the base weights above are frozen; the adapter (PEFT layout) and its optimizer state live beside them
+        from ...models.lora import lora_state_dict, save_adapter
+
+        lo = engine.lora
+        save_adapter(engine.model, str(path / "lora_adapter"), int(lo["rank"]), float(lo.get("alpha", 16) or 16),
+                     lo.get("target_modules"))
+        torch.save({"lora": lora_state_dict(engine.model), "optimizer": engine._lora_opt.state_dict(),
+                    "step": engine.step_count}, path / "lora_train_state.pt")
     if r == 0:
         (path / "fsdp_config.json").write_text(json.dumps({"FSDP_version": 2, "world_size": W}, indent=4))
         hf_dir = path / "huggingface"
@@ -87,7 +96,8 @@ def save_engine_checkpoint(engine, local_path: str, global_step: int = 0,
         engine.model_config.save_pretrained(hf_dir)
     if "hf_model" in save_contents:
         sd = {}
-        for k, v in z.named_full_tensors():  # collective: every rank takes part in the gathers
+        named = engine._merged_named_tensors() if hasattr(engine, "_merged_named_tensors") else z.named_full_tensors()
+        for k, v in named:  # collective: every rank takes part in the gathers (LoRA: merged weights)
             if r == 0:
                 sd[k] = v.detach().to(torch.bfloat16).cpu()
         if r == 0:
@@ -131,6 +141,16 @@ def load_engine_checkpoint(engine, local_path: str, load_contents=("model", "opt
         _restore(z, z.exp_avg, st["exp_avg"])
         _restore(z, z.exp_avg_sq, st["exp_avg_sq"])
         engine.step_count = int(st.get("step", 0))
+    lfile = path / "lora_train_state.pt"
+    if getattr(engine, "_lora_params", None) and lfile.exists():
+        from ...models.lora import load_lora_state_dict
+
+        st = torch.load(lfile, map_location="cpu", weights_only=False)
+        if "model" in load_contents:
+            load_lora_state_dict(engine.model, st["lora"])
+        if "optimizer" in load_contents:
+            engine._lora_opt.load_state_dict(st["optimizer"])
+            engine.step_count = int(st.get("step", 0))
     efile = path / f"extra_state_world_size_{W}_rank_{r}.pt"
     if "extra" in load_contents and efile.exists():
         st = torch.load(efile, map_location="cpu", weights_only=False)

@@ -65,9 +65,14 @@ class NativeEngine(BaseEngine):
     def __init__(self, model_config: ModelConfig, engine_config=None, optimizer_config=None, *, value_head: bool = False,
                  device: Optional[str] = None, trainable: bool = True, group=None, seed: int = 0,
                  state_dict: Optional[dict] = None, comm=None, gradient_checkpointing: bool = True,
-                 tiled_mlp_shards: int = 0):
+                 tiled_mlp_shards: int = 0, lora: Optional[dict] = None):
         self.model_config = model_config
         self.tiled_mlp_shards = int(tiled_mlp_shards)
+        # LoRA (``{"rank", "alpha", "target_modules", "exclude_modules"}``): the base weights are frozen and keep no
+        # optimizer state; the adapters are replicated fp32 tensors trained by their own AdamW
+        self.lora = dict(lora) if lora and int(lora.get("rank", 0) or 0) > 0 else None
+        self._lora_params: list = []
+        self._lora_opt = None
         self.engine_config = engine_config
         self.optimizer_config = optimizer_config
         self.value_head = value_head
@@ -100,6 +105,16 @@ class NativeEngine(BaseEngine):
             from ...models.tiled_mlp import apply_tiled_mlp
 
             apply_tiled_mlp(self.model, self.tiled_mlp_shards)
+        if self.lora is not None and self.trainable:
+            from ...models.lora import apply_lora, lora_named_parameters
+
+            if self.device.type == "cuda":
+                assert int(self.lora["rank"]) % 8 == 0, "lora_rank must be a multiple of 8 (GEMM row alignment)"
+            for p in self.model.parameters():
+                p.requires_grad_(False)
+            apply_lora(self.model, int(self.lora["rank"]), float(self.lora.get("alpha", 16) or 16),
+                       self.lora.get("target_modules", "all-linear"), self.lora.get("exclude_modules"), seed=self.seed)
+            self._lora_params = [p for _, p in lora_named_parameters(self.model)]
         m = self.model
         tied = m.lm_head is None and not m.value_head
         units = []
@@ -117,13 +132,19 @@ class NativeEngine(BaseEngine):
                 head.append(("lm_head.weight", m.lm_head.weight))
             units.append(("", head))
         self.zero = ZeroShardedParams(units, group=self.group, work_dtype=self.work_dtype, device=self.device,
-                                      trainable=self.trainable, comm=self.comm)
+                                      trainable=self.trainable and not self._lora_params, comm=self.comm)
+        self.zero.frozen_grad = bool(self._lora_params)
         self._setup_sequence_parallel()
         self._embed_unit = self.zero.units[0]
         self._layer_units = self.zero.units[1 : 1 + cfg.num_hidden_layers]
         self._head_unit = self.zero.units[0] if tied else self.zero.units[-1]
         if self.device.type == "cuda":
             torch.cuda.empty_cache()
+        if self._lora_params:
+            oc = self.optimizer_config
+            self._lora_opt = torch.optim.AdamW(self._lora_params, lr=float(_cfg(oc, "lr", 1e-6)),
+                                               betas=tuple(_cfg(oc, "betas", (0.9, 0.999))), eps=float(_cfg(oc, "eps", 1e-8)),
+                                               weight_decay=float(_cfg(oc, "weight_decay", 0.01)))
         if self.trainable:
             dev = self.device
             self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -329,6 +350,54 @@ class NativeEngine(BaseEngine):
     # ---------------------------------------------------------------- optimizer
     def optimizer_zero_grad(self):
         self.zero.zero_grad()
+        for p in self._lora_params:
+            p.grad = None
+
+    def _lora_optimizer_step(self) -> torch.Tensor:
+        """Sum the adapter gradients over the data-parallel group, clip by their global norm, AdamW. A non-finite
+        norm skips the update."""
+        oc = self.optimizer_config
+        clip = float(_cfg(oc, "clip_grad", 1.0))
+        grads = [p.grad if p.grad is not None else torch.zeros_like(p) for p in self._lora_params]
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        if self.zero.world > 1:
+            dist.all_reduce(flat, group=self.group)
+        norm = flat.double().norm().float()
+        self.step_count += 1
+        if bool(torch.isfinite(norm)):
+            coef = min(1.0, clip / (float(norm) + 1e-6)) if clip > 0 else 1.0
+            off = 0
+            for p in self._lora_params:
+                n = p.numel()
+                p.grad = (flat[off:off + n] * coef).view_as(p)
+                off += n
+            for g in self._lora_opt.param_groups:
+                g["lr"] = self._lr()
+            self._lora_opt.step()
+        else:
+            self.step_count -= 1
+        for p in self._lora_params:
+            p.grad = None
+        return norm.reshape(1)
+
+    @contextmanager
+    def disable_adapter(self):
+        """Run the frozen base model (the reference policy under LoRA: verl's ``ref_in_actor``)."""
+        mods = dict(self.model.named_modules())
+        names = list(getattr(self.model, "lora_modules", []))
+        for n in names:
+            mods[n].__dict__["lora_off"] = True
+        try:
+            yield self
+        finally:
+            for n in names:
+                mods[n].__dict__["lora_off"] = False
+
+    def merge_lora_into(self, model) -> int:
+        """Add the adapters' deltas to the weights of ``model`` (same module names, weights equal to the base)."""
+        from ...models.lora import merge_lora_into
+
+        return merge_lora_into(self.model, model) if self._lora_params else 0
 
     def _lr(self) -> float:
         oc = self.optimizer_config
@@ -358,6 +427,8 @@ class NativeEngine(BaseEngine):
     def optimizer_step(self) -> float:
         """Global grad-norm, clip, fused AdamW on the shards. Returns the (pre-clip) gradient norm; a
         non-finite norm skips the update (verl/workers/actor/dp_actor.py:391-415)."""
+        if self._lora_params:
+            return self._lora_optimizer_step()
         z, oc = self.zero, self.optimizer_config
         clip = float(_cfg(oc, "clip_grad", 1.0))
         lr = self._lr()
@@ -400,14 +471,28 @@ class NativeEngine(BaseEngine):
         """Generator of (HF parameter name, full tensor): one unit is gathered at a time."""
         if self._offloaded:
             self.to(str(self.device))
-        return native_to_hf_items(self.model_config, self.zero.named_full_tensors(dtype))
+        return native_to_hf_items(self.model_config, self._merged_named_tensors(dtype))
+
+    def _merged_named_tensors(self, dtype=None):
+        """(name, full tensor) of every parameter; adapted weights come out merged (W + (alpha / r) B A)."""
+        if not self._lora_params:
+            yield from self.zero.named_full_tensors(dtype)
+            return
+        from ...models.lora import lora_delta
+
+        mods = dict(self.model.named_modules())
+        adapted = {n + ".weight": mods[n] for n in self.model.lora_modules}
+        for k, v in self.zero.named_full_tensors(dtype):
+            if k in adapted:
+                v = (v.float() + lora_delta(adapted[k]).to(v.device)).to(v.dtype)
+            yield k, v
 
     def native_named_tensors(self):
-        return self.zero.named_full_tensors()
+        return self._merged_named_tensors()
 
     def full_state_dict(self, dtype=torch.bfloat16, to_cpu: bool = True) -> dict:
         out = {}
-        for k, v in self.zero.named_full_tensors():
+        for k, v in self._merged_named_tensors():
             t = v.detach().to(dtype)
             out[k] = t.cpu() if to_cpu else t.clone()
         return out

@@ -142,12 +142,18 @@ class ActorRolloutRefWorker(_WorkerBase):
         comm = self._make_comm()
         tm = _cfg(self.config.model, "tiled_mlp", None) or {}
         tiled = int(_cfg(tm, "num_shards", 4)) if _cfg(tm, "enabled", False) else 0
+        lora_rank = int(_cfg(self.config.model, "lora_rank", 0) or 0)
+        lora = {"rank": lora_rank, "alpha": _cfg(self.config.model, "lora_alpha", 16),
+                "target_modules": _cfg(self.config.model, "target_modules", "all-linear"),
+                "exclude_modules": _cfg(self.config.model, "exclude_modules", None)} if lora_rank > 0 else None
+        self._lora = lora is not None
         if self._is_actor:
             self.actor_engine = NativeEngine(model_cfg, self.actor_cfg.fsdp_config, self.actor_cfg.optim,
                                              device=str(self.device), group=group, seed=seed, state_dict=state,
-                                             comm=comm, gradient_checkpointing=gc, tiled_mlp_shards=tiled).initialize()
+                                             comm=comm, gradient_checkpointing=gc, tiled_mlp_shards=tiled,
+                                             lora=lora).initialize()
             self.actor = DataParallelPPOActor(self.actor_cfg, self.actor_engine)
-        if self._is_ref:
+        if self._is_ref and not (self._lora and self._is_actor):  # LoRA: the reference is the actor with adapters off
             ref_eng_cfg = self.ref_cfg.fsdp_config if self.ref_cfg is not None else None
             self.ref_engine = NativeEngine(model_cfg, ref_eng_cfg, None, device=str(self.device), group=group, seed=seed,
                                            state_dict=state, trainable=False, comm=comm).initialize()
@@ -173,7 +179,7 @@ class ActorRolloutRefWorker(_WorkerBase):
         from ..rollout import NativeRolloutEngine
 
         rc = self.rollout_cfg
-        if self._is_actor and self.world == 1:
+        if self._is_actor and self.world == 1 and not getattr(self, "_lora", False):
             self.rollout_model = self.actor_engine.model  # same tensors: weight sync is free
         else:
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
@@ -206,6 +212,9 @@ class ActorRolloutRefWorker(_WorkerBase):
     @torch.no_grad()
     def _sync_rollout_weights(self):
         self._rollout_flat.sync()
+        if getattr(self, "_lora", False):
+            # the rollout copy now holds the frozen base weights: add the adapters' deltas (merged-weight sync)
+            self.actor_engine.merge_lora_into(self.rollout_model)
 
     # ---------------------------------------------------------------- rollout
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("rollout"))
@@ -264,6 +273,10 @@ class ActorRolloutRefWorker(_WorkerBase):
     def compute_ref_log_prob(self, data: DataProto) -> DataProto:
         assert self._is_ref
         self._lp_meta(data, self.ref_cfg or self.config.ref)
+        if self.ref_engine is None:  # LoRA: frozen base weights of the actor engine
+            with self.actor_engine.eval_mode(), self.actor_engine.disable_adapter():
+                lp, _ = self.actor.compute_log_prob(data, calculate_entropy=False)
+            return DataProto.from_dict(tensors={"ref_log_prob": lp.cpu()})
         with self.ref_engine.eval_mode():
             lp, _ = self.ref_policy.compute_log_prob(data, calculate_entropy=False)
         return DataProto.from_dict(tensors={"ref_log_prob": lp.cpu()})
