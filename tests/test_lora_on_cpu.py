@@ -108,3 +108,25 @@ def test_lora_grpo_end_to_end(tmp_path, monkeypatch):
     step_dir = tmp_path / "ckpt" / "global_step_2" / "actor"
     assert (step_dir / "lora_adapter" / "adapter_model.safetensors").exists()
     assert (step_dir / "lora_train_state.pt").exists() and not (step_dir / "optim_world_size_2_rank_0.pt").exists()
+
+
+def test_sft_with_lora(tmp_path):
+    """SFT with model.lora_rank > 0: the loss goes down while only the adapters change."""
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_sft_on_cpu import _config
+
+    from verl_b200.trainer.sft_trainer import SFTTrainer
+    from verl_b200.utils.dataset.sft_dataset import sft_collate_fn
+    from verl_b200.utils.tokenizer import IntTokenizer
+
+    cfg = _config(tmp_path, **{"model.lora_rank": 8, "optim.lr": "2e-2"})
+    tr = SFTTrainer(cfg, tokenizer=IntTokenizer(256))
+    assert tr.engine._lora_params and tr.engine.zero.master is None
+    base0 = tr.engine.zero.shard16.clone()
+    losses = []
+    for step, (_, idx) in enumerate(tr._batches(0)):
+        losses.append(tr.train_step(sft_collate_fn([tr.train_dataset[i] for i in idx]))["train/loss"])
+        tr.global_step += 1
+        if step == 5:
+            break
+    assert losses[-1] < losses[0] and torch.equal(tr.engine.zero.shard16, base0)

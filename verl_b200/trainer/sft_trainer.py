@@ -88,8 +88,12 @@ class SFTTrainer:
                 comm = None
         self.engine = NativeEngine(model_cfg, config.engine, optim, device=str(self.device), group=self.group,
                                    seed=int(_g(config.engine, "seed", 42)), state_dict=state, comm=comm,
-                                   gradient_checkpointing=bool(_g(config.model, "enable_gradient_checkpointing", True))
-                                   ).initialize()
+                                   gradient_checkpointing=bool(_g(config.model, "enable_gradient_checkpointing", True)),
+                                   lora=({"rank": int(_g(config.model, "lora_rank", 0) or 0),
+                                          "alpha": _g(config.model, "lora_alpha", 16),
+                                          "target_modules": _g(config.model, "target_modules", "all-linear"),
+                                          "exclude_modules": _g(config.model, "exclude_modules", None)}
+                                         if int(_g(config.model, "lora_rank", 0) or 0) > 0 else None)).initialize()
         self.global_step = 0
         self.logger = None
         self._resume()
