@@ -13,6 +13,8 @@ Token-in / token-out API: :meth:`add_request`, :meth:`step`, :meth:`generate`, :
 
 from __future__ import annotations
 
+import os
+
 import ctypes
 import time
 from dataclasses import dataclass, field
@@ -435,8 +437,23 @@ class NativeRolloutEngine:
             torch.cuda.current_stream(dev).wait_stream(s)
             torch.cuda.synchronize(dev)
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                run()
+            # thread-local capture mode: CUDA calls made by other threads of the process (a checkpoint writer, a
+            # profiler, another engine's loop) must not invalidate this capture
+            mode = os.environ.get("VERL_B200_GRAPH_CAPTURE_MODE", "thread_local")
+            # Cyclic garbage (an earlier engine with its graphs and pinned buffers) must not be finalised in the
+            # middle of the capture: destroying graphs or freeing memory there invalidates it. Collect now, and
+            # keep the collector off until the capture has ended.
+            import gc
+
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, capture_error_mode=mode):
+                    run()
+            finally:
+                if gc_was_on:
+                    gc.enable()
         self._graphs[B] = (st, graph, run)
         return self._graphs[B]
 
