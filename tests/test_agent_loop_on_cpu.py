@@ -179,3 +179,66 @@ def test_partial_single_turn_loop_resumes_cancelled_sample(server):
         assert (await loop.run(sp, raw_prompt=prompt, output=resumed)) is resumed
 
     asyncio.run(go())
+
+
+def test_partial_tool_agent_loop_resumes_inside_a_turn(tmp_path):
+    """An assistant turn cut by an abort continues in the next run; the tool call spanning both generations is
+    parsed from the whole turn, the tool's tokens are masked, and the loop then finishes normally."""
+    import sys
+    import types
+
+    from verl_b200.experimental.fully_async_policy.agent_loop import PartialToolAgentLoop
+    from verl_b200.tools import BaseTool, ToolResponse
+
+    mod = types.ModuleType("tests_tool_helpers2")
+
+    class EchoTool(BaseTool):
+        async def execute(self, instance_id, parameters, **kw):
+            return ToolResponse(text="7 8 9"), 0.25, {}
+
+    mod.EchoTool = EchoTool
+    sys.modules["tests_tool_helpers2"] = mod
+    tools_yaml = tmp_path / "tools.yaml"
+    tools_yaml.write_text(json.dumps({"tools": [{
+        "class_name": "tests_tool_helpers2.EchoTool", "config": {"type": "native"},
+        "tool_schema": {"type": "function", "function": {"name": "echo", "description": "echo",
+                                                         "parameters": {"type": "object", "properties": {"text": {"type": "string"}}, "required": ["text"]}}}}]}))
+    cfg = _cfg([f"actor_rollout_ref.rollout.multi_turn.tool_config_path={tools_yaml}",
+                "actor_rollout_ref.rollout.multi_turn.max_assistant_turns=4"])
+
+    class Tok(IntTokenizer):
+        def decode(self, ids, skip_special_tokens=True):
+            ids = [int(t) for t in ids]
+            if ids == [101, 102, 103]:  # only the complete turn spells the call
+                return '<tool_call>{"name": "echo", "arguments": {"text": "hi"}}</tool_call>'
+            return super().decode(ids, skip_special_tokens)
+
+    class FakeServers:
+        def __init__(self):
+            self.script = [([101, 102], [-0.1, -0.2], True), ([103], [-0.3], False), ([104], [-0.4], False)]
+            self.prompts = []
+
+        async def generate_for_partial(self, request_id, *, prompt_ids, sampling_params, **kw):
+            self.prompts.append(list(prompt_ids))
+            return self.script.pop(0)
+
+    async def go():
+        servers = FakeServers()
+        loop = PartialToolAgentLoop(cfg, servers, Tok(2048))
+        sp = {"temperature": 0.0}
+        part = await loop.run(sp, raw_prompt=[{"role": "user", "content": "30 31"}], param_version=3)
+        assert part.extra_fields["is_cancel"] and part.response_ids == [101, 102] and part.response_mask == [1, 1]
+        done = await loop.run(sp, raw_prompt=None, output=part, param_version=4)
+        assert not done.extra_fields["is_cancel"]
+        assert done.extra_fields["param_version_start"] == 3 and done.extra_fields["param_version_end"] == 4
+        # second generation continued the cut turn from prompt + partial response
+        assert servers.prompts[1] == servers.prompts[0] + [101, 102]
+        ids, mask = done.response_ids, done.response_mask
+        assert ids[:3] == [101, 102, 103] and ids[-1] == 104 and mask[:3] == [1, 1, 1] and mask[-1] == 1
+        tool = ids[3:-1]
+        assert 7 in tool and 8 in tool and 9 in tool and set(mask[3:-1]) == {0}
+        assert done.extra_fields["tool_rewards"] == [0.25] and len(done.response_logprobs) == len(ids)
+        assert done.num_turns == 4  # user, assistant (in two pieces), tool, assistant
+        assert (await loop.run(sp, raw_prompt=None, output=done)) is done
+
+    asyncio.run(go())

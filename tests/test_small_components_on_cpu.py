@@ -371,3 +371,48 @@ def test_dynamic_dataset_grows(tmp_path):
     assert len(ds) == 5 and ds[4]["raw_prompt_ids"] == [1, 2, 3]
     with pytest.raises(AssertionError):
         DynamicGenDataset(str(f), IntTokenizer(100), {"max_prompt_length": 8})
+
+
+def test_search_utils_retry_and_format(monkeypatch):
+    import requests
+
+    from verl_b200.tools.utils import search_r1_like_utils as su
+
+    calls = {"n": 0}
+
+    class R:
+        def __init__(self, code, body):
+            self.status_code, self._b = code, body
+
+        def raise_for_status(self):
+            if self.status_code >= 400:
+                raise requests.exceptions.HTTPError(str(self.status_code))
+
+        def json(self):
+            return self._b
+
+    def post(url, json=None, timeout=None, headers=None):
+        calls["n"] += 1
+        if calls["n"] < 3:
+            return R(503, {})
+        return R(200, {"result": [[{"document": {"contents": "Title A\nbody a"}}], [{"document": {"contents": "T2\nb2"}}]]})
+
+    monkeypatch.setattr(requests, "post", post)
+    text, meta = su.perform_single_search_batch("http://x", ["q1", "q2"], topk=1, retry_delay=0.0)
+    assert calls["n"] == 3 and meta["status"] == "success" and meta["total_results"] == 2
+    assert "Doc 1 (Title: Title A)" in text and "---" in text
+    monkeypatch.setattr(requests, "post", lambda *a, **k: R(404, {}))
+    resp, err = su.call_search_api("http://x", ["q"], retry_delay=0.0)
+    assert resp is None and "API Request Error" in err
+    monkeypatch.setattr(requests, "post", lambda *a, **k: R(200, {"result": []}))
+    assert su.perform_single_search_batch("http://x", ["q"])[1]["status"] == "no_results"
+
+
+def test_rollout_tokenizer_adapter():
+    from verl_b200.utils.tokenizer import IntTokenizer
+    from verl_b200.workers.rollout.tokenizer import HybridEngineBaseTokenizer, TokenizerAdapter
+
+    t = TokenizerAdapter(IntTokenizer(100, eos_token_id=2, pad_token_id=0))
+    assert isinstance(t, HybridEngineBaseTokenizer) and t.vocab_size == 100 and sorted(t.all_special_ids) == [0, 2]
+    assert t.encode("5 6 7") == [5, 6, 7] and t.decode([5, 2, 6], skip_special_tokens=True) == "5 6"
+    assert t.convert_ids_to_tokens([5, 2], skip_special_tokens=True) == ["5"] and t.convert_tokens_to_string(["a", "b"]) == "a b"

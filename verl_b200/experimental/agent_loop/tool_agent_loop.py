@@ -27,6 +27,7 @@ class AgentState(Enum):
     PROCESSING_TOOLS = "processing_tools"
     INTERACTING = "interacting"
     TERMINATED = "terminated"
+    CANCELLED = "cancelled"  # generation aborted by a weight update: resumable (partial rollout)
 
 
 @dataclass
@@ -47,6 +48,7 @@ class AgentData:
     assistant_turns: int = 0
     metrics: dict = field(default_factory=lambda: {"generate_sequences": 0.0, "tool_calls": 0.0, "num_preempted": 0})
     interaction: Any = None
+    mid_turn: bool = False  # the current assistant turn was cut by an abort and continues in the next generation
 
 
 _TOOLS_CACHE: dict = {}
@@ -92,8 +94,12 @@ class ToolAgentLoop(AgentLoopBase):
                 raise ValueError(f"Interaction '{name}' not found in interaction_map. Available interactions: {list(self.interactions)}")
             data.interaction = self.interactions[name]
             await data.interaction.start_interaction(data.request_id, **data.interaction_kwargs)
-        state = AgentState.PENDING
-        while state != AgentState.TERMINATED:
+        return await self._run_from(data, AgentState.PENDING, sampling_params)
+
+    async def _run_from(self, data: AgentData, state: AgentState, sampling_params: dict[str, Any]) -> AgentLoopOutput:
+        """Drive the state machine from ``state`` until it terminates (or is cancelled: see the partial-rollout
+        subclass in ``fully_async_policy/agent_loop``)."""
+        while state not in (AgentState.TERMINATED, AgentState.CANCELLED):
             if state == AgentState.PENDING:
                 data.prompt_ids = await self.apply_chat_template(data.messages, tools=self.tool_schemas or None)
                 state = AgentState.GENERATING
@@ -103,14 +109,18 @@ class ToolAgentLoop(AgentLoopBase):
                 state = await self._process_tools(data)
             elif state == AgentState.INTERACTING:
                 state = await self._interact(data)
+        return self._output(data, cancelled=state == AgentState.CANCELLED)
+
+    def _output(self, data: AgentData, cancelled: bool = False) -> AgentLoopOutput:
         ids = data.response_ids[: self.response_length]
-        out = AgentLoopOutput(
+        extra = {"turn_scores": data.turn_scores, "tool_rewards": data.tool_rewards}
+        if cancelled:
+            extra.update(is_cancel=True, agent_data=data)
+        return AgentLoopOutput(
             prompt_ids=data.prompt_ids, response_ids=ids, response_mask=data.response_mask[: self.response_length],
             response_logprobs=data.response_logprobs[: self.response_length] if data.response_logprobs else None,
             num_turns=data.user_turns + data.assistant_turns + 1,
-            metrics=AgentLoopMetrics(**data.metrics),
-            extra_fields={"turn_scores": data.turn_scores, "tool_rewards": data.tool_rewards})
-        return out
+            metrics=AgentLoopMetrics(**data.metrics), extra_fields=extra)
 
     # ------------------------------------------------------------------ states
     async def _generate(self, data: AgentData, sampling_params: dict) -> AgentState:
@@ -121,14 +131,24 @@ class ToolAgentLoop(AgentLoopBase):
         out = await self.server_manager.generate(data.request_id, prompt_ids=ctx, sampling_params=sp)
         data.metrics["generate_sequences"] += time.perf_counter() - t0
         data.metrics["num_preempted"] += max(out.num_preempted, 0)
-        data.assistant_turns += 1
-        data.turn_ids = list(out.token_ids)
-        data.response_ids += data.turn_ids
-        data.response_mask += [1] * len(data.turn_ids)
-        if out.log_probs:
-            data.response_logprobs += list(out.log_probs)
+        return await self._after_generation(data, list(out.token_ids), list(out.log_probs or []))
+
+    async def _after_generation(self, data: AgentData, token_ids: list, log_probs: list, turn_complete: bool = True) -> AgentState:
+        """Book the tokens of an assistant turn (``turn_complete=False``: the turn was cut and will be continued)."""
+        if not data.mid_turn:
+            data.assistant_turns += 1
+            data.turn_ids = []
+        data.turn_ids += token_ids
+        data.response_ids += token_ids
+        data.response_mask += [1] * len(token_ids)
+        if log_probs:
+            data.response_logprobs += log_probs
+        data.mid_turn = not turn_complete
         if len(data.response_ids) >= self.response_length:
+            data.mid_turn = False
             return AgentState.TERMINATED
+        if not turn_complete:
+            return AgentState.CANCELLED
         if self.max_assistant_turns and data.assistant_turns >= self.max_assistant_turns:
             return AgentState.TERMINATED
         if self.max_user_turns and data.user_turns >= self.max_user_turns:

@@ -11,30 +11,7 @@ from .base_tool import BaseTool
 from .schemas import OpenAIFunctionToolSchema, ToolResponse
 
 
-def _passages_to_string(result: list[dict]) -> str:
-    out = []
-    for i, doc in enumerate(result):
-        content = doc.get("document", {}).get("contents", "") if isinstance(doc.get("document"), dict) else str(doc)
-        title, _, text = content.partition("\n")
-        out.append(f"Doc {i + 1} (Title: {title})\n{text}\n")
-    return "\n".join(out)
-
-
-def perform_single_search_batch(retrieval_service_url: str, query_list: list[str], topk: int = 3, timeout: int = 30):
-    import requests
-
-    payload = {"queries": query_list, "topk": topk, "return_scores": True}
-    last = None
-    for attempt in range(3):
-        try:
-            r = requests.post(retrieval_service_url, json=payload, timeout=timeout)
-            r.raise_for_status()
-            results = r.json().get("result", [])
-            text = "\n---\n".join(_passages_to_string(x) for x in results)
-            return json.dumps({"result": text}, ensure_ascii=False), {"status": "success", "total_results": sum(len(x) for x in results)}
-        except Exception as e:
-            last = e
-    return json.dumps({"result": f"Search error: {last}"}), {"status": "error"}
+from .utils.search_r1_like_utils import perform_single_search_batch  # noqa: E402
 
 
 class SearchTool(BaseTool):
@@ -58,7 +35,8 @@ class SearchTool(BaseTool):
             return ToolResponse(text=json.dumps({"result": "Error: 'query_list' is missing, empty, or not a list in parameters."})), 0.0, {}
         async with self._sem:
             text, meta = await asyncio.get_event_loop().run_in_executor(
-                None, perform_single_search_batch, self.url, queries, self.topk, self.timeout)
+                None, lambda: perform_single_search_batch(self.url, queries, self.topk, None, self.timeout,
+                                                          max_retries=int(self.config.get("max_retries", 3))))
         return ToolResponse(text=text), 0.0, meta
 
     async def release(self, instance_id: str, **kwargs):
