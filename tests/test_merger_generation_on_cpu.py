@@ -38,3 +38,20 @@ def test_generation_and_eval(tmp_path):
     out = [json.loads(line) for line in (tmp_path / "o.jsonl").read_text().splitlines()]
     assert len(out) == 3 and all(len(r["responses"]) == 2 for r in out)
     eval_main([f"data.path={tmp_path}/o.jsonl"])
+
+
+def test_generation_through_standalone_servers(tmp_path):
+    """Two standalone replicas behind HTTP; greedy decoding gives the same text for identical prompts whichever
+    replica served them."""
+    from verl_b200.trainer.main_generation_server import main as gen_main
+
+    rows = [{"prompt": "1 2 3", "id": i} for i in range(4)]
+    (tmp_path / "p.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    out = gen_main(["model.path=preset:tiny-qwen2", f"data.path={tmp_path}/p.jsonl", f"data.output_path={tmp_path}/o.jsonl",
+                    "rollout.n=2", "rollout.response_length=6", "rollout.prompt_length=32", "trainer.device=cpu",
+                    "rollout.max_num_seqs=8", "rollout.max_num_batched_tokens=256", "rollout.num_replicas=2",
+                    "rollout.do_sample=false"])
+    saved = [json.loads(line) for line in (tmp_path / "o.jsonl").read_text().splitlines()]
+    assert len(out) == len(saved) == 4 and all(len(r["responses"]) == 2 for r in saved)
+    texts = {t for r in saved for t in r["responses"]}
+    assert len(texts) == 1 and len(next(iter(texts)).split()) > 0

@@ -98,7 +98,8 @@ class EngineConfig(BaseConfig):
 @dataclass
 class FSDPEngineConfig(EngineConfig):
     """Sharded data-parallel engine options. ``strategy`` accepts fsdp / fsdp2 (both map to the native
-    ZeRO-3 engine here); ``fsdp_size`` < world gives HSDP-style replicated shard groups."""
+    ZeRO-3 engine here). ``fsdp_size`` is accepted for config compatibility: parameters are always sharded over the
+    whole data-parallel group (one NVSwitch box), there are no replicated shard groups."""
 
     wrap_policy: dict = field(default_factory=dict)
     offload_policy: bool = False
