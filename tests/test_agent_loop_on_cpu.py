@@ -242,3 +242,54 @@ def test_partial_tool_agent_loop_resumes_inside_a_turn(tmp_path):
         assert (await loop.run(sp, raw_prompt=None, output=done)) is done
 
     asyncio.run(go())
+
+
+def test_fully_async_manager_cancels_and_resumes_groups(server):
+    """Prompt groups driven through the fully-async manager: a cancel in mid-generation leaves cancelled outputs,
+    the groups continue after resume, and (greedy) end with the same tokens as an undisturbed run."""
+    from verl_b200.experimental.fully_async_policy.agent_loop import FullyAsyncAgentLoopManager
+
+    cfg = _cfg(["actor_rollout_ref.rollout.agent.num_workers=2"])
+    tok = IntTokenizer(2048)
+    mgr = FullyAsyncAgentLoopManager(cfg, server_handles=[server], tokenizer=tok)
+
+    def group(seed, n=2):
+        p = np.empty(n, dtype=object)
+        p[:] = [list(range(40 + seed, 60 + seed))] * n
+        d = DataProto.from_dict(tensors={"dummy": torch.zeros(n)}, non_tensors={"raw_prompt": p})
+        d.meta_info["validate"] = True  # greedy
+        return d
+
+    groups = [group(s) for s in range(3)]
+
+    async def drive(g, version_box, log):
+        outs, cancelled = await mgr.generate_single_sample_async(g, None, version_box[0])
+        while cancelled:
+            log.append(sum(o.extra_fields["is_cancel"] for o in outs))
+            await mgr.wait_resumed()
+            outs, cancelled = await mgr.generate_single_sample_async(g, outs, version_box[0])
+        return mgr.postprocess(outs), outs
+
+    async def go():
+        ref = [await drive(g, [0], []) for g in groups]  # undisturbed
+        version, log = [0], []
+        tasks = [asyncio.ensure_future(drive(g, version, log)) for g in groups]
+        while not server._pending:
+            await asyncio.sleep(0.001)
+        await asyncio.sleep(0.02)
+        await mgr.cancel()
+        version[0] = 1  # "weights updated"
+        await asyncio.sleep(0.01)
+        assert not any(t.done() for t in tasks) or log == []  # cancelled groups wait for resume
+        await mgr.resume()
+        done = await asyncio.gather(*tasks)
+        return ref, done, log
+
+    ref, done, log = asyncio.run(go())
+    for (rb, _), (db, douts) in zip(ref, done):
+        assert torch.equal(rb.batch["responses"], db.batch["responses"])
+        assert torch.equal(rb.batch["response_mask"], db.batch["response_mask"])
+        assert db.batch["responses"].shape == (2, 32) and "agent_data" not in db.non_tensor_batch
+    if log:  # the cancel landed while requests were in flight: those samples span two parameter versions
+        spans = [(o.extra_fields["param_version_start"], o.extra_fields["param_version_end"]) for _, outs in done for o in outs]
+        assert (0, 1) in spans

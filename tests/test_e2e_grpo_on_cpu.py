@@ -72,3 +72,27 @@ def test_ppo_with_critic_spmd_single_process(tmp_path, monkeypatch):
     cfg2 = compose("ppo_trainer", _overrides(tmp_path, extra + ["trainer.total_training_steps=3"]))
     t2 = run_ppo(cfg2, spmd=True)
     assert t2.global_steps == 3  # resumed at 2, ran one more
+
+
+@pytest.mark.parametrize("spmd", [True, False, "tool"])
+def test_grpo_through_agent_loops(tmp_path, monkeypatch, spmd):
+    """rollout.agent.use_agent_loop: rollouts go through the token-in / token-out server and the agent loops, in
+    process (SPMD launch) and over HTTP to two worker processes."""
+    import json
+
+    from verl_b200.trainer.main_ppo import run_ppo
+
+    monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
+    extra = ["actor_rollout_ref.rollout.agent.use_agent_loop=true", "actor_rollout_ref.rollout.agent.num_workers=2",
+             "trainer.save_freq=-1", "trainer.experiment_name=agent", "data.return_raw_chat=true"]
+    if spmd == "tool":  # multi-turn configuration: the tool-calling state machine drives every sample
+        extra = ["actor_rollout_ref.rollout.multi_turn.enable=true", "actor_rollout_ref.rollout.multi_turn.max_assistant_turns=2",
+                 "actor_rollout_ref.rollout.agent.default_agent_loop=tool_agent"] + extra[1:]
+    if spmd:
+        extra.append("trainer.n_gpus_per_node=1")
+    trainer = run_ppo(compose("ppo_trainer", _overrides(tmp_path, extra)), spmd=bool(spmd))
+    assert trainer.async_rollout_mode and trainer.global_steps == 2
+    m = [json.loads(l) for l in open(tmp_path / "logs" / "cpu_e2e" / "agent.jsonl")][-1]["data"]
+    for key in ("actor/pg_loss", "actor/grad_norm", "response_length/mean", "agent_loop/generate_sequences/mean"):
+        assert key in m and math.isfinite(m[key]), key
+    assert m["response_length/mean"] > 0 and m["actor/grad_norm"] > 0

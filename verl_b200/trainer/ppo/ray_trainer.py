@@ -298,8 +298,57 @@ class RayPPOTrainer:
         if self.ref_in_actor:
             self.ref_policy_wg = self.actor_rollout_wg
         self.async_rollout_mode = False
+        rc = self.config.actor_rollout_ref.rollout
+        agent = rc.get("agent") or {}
+        if (bool((rc.get("multi_turn") or {}).get("enable", False)) or bool(agent.get("use_agent_loop", False))
+                or agent.get("default_agent_loop", "single_turn_agent") not in (None, "single_turn_agent")):
+            self._init_async_rollout_manager()
         self.n_gpus = (self.spmd_world if self.spmd else
                        (self.resource_pool_manager.get_n_gpus() if self.resource_pool_manager else 1))
+
+    def _init_async_rollout_manager(self):
+        """Rollouts through agent loops (multi-turn, tools, interactions) instead of one batched ``generate`` call:
+        role of ``AgentLoopManager`` in the reference's ``rollout.mode=async``. Taken when ``rollout.multi_turn.enable``
+        is set, a non-default agent loop is configured, or ``rollout.agent.use_agent_loop`` is true; plain single-turn
+        RL keeps the batched path (same continuous batching, no per-request hand-off)."""
+        from ...experimental.agent_loop import AgentLoopManager
+
+        if self.spmd:
+            worker = self.actor_rollout_wg.worker.worker_dict["actor_rollout"]
+            handles = [worker.get_async_server()]
+        else:
+            from ...workers.rollout.async_server import HttpServerHandle
+
+            handles = [HttpServerHandle(a) for a in self.actor_rollout_wg.start_rollout_server()]
+        self.async_rollout_manager = AgentLoopManager(self.config, server_handles=handles, tokenizer=self.tokenizer,
+                                                      processor=self.processor)
+        self._rollout_server_handles = handles
+        self.async_rollout_mode = True
+
+    def _generate(self, gen_batch: DataProto) -> DataProto:
+        """One rollout of ``gen_batch`` (already repeated n times): agent loops or the batched engine call."""
+        if self.async_rollout_mode:
+            import asyncio
+
+            free = bool(self.config.actor_rollout_ref.rollout.get("free_cache_engine", True))
+
+            async def run():
+                await asyncio.gather(*[h.wake_up() for h in self._rollout_server_handles])
+                out = await self.async_rollout_manager.generate_sequences_async(gen_batch)
+                if free and not gen_batch.meta_info.get("keep_cache", False):
+                    await asyncio.gather(*[h.sleep() for h in self._rollout_server_handles])
+                for h in self._rollout_server_handles:
+                    if hasattr(h, "close"):
+                        await h.close()
+                return out
+
+            out = asyncio.run(run())
+            timing = out.meta_info.pop("timing", {})
+            out.meta_info["metrics"] = {k: float(v) for k, v in timing.items()}
+            return out
+        div = 1 if self.spmd else self.actor_rollout_wg.world_size
+        padded, pad = pad_dataproto_to_divisor(gen_batch, div)
+        return unpad_dataproto(self.actor_rollout_wg.generate_sequences(padded), pad_size=pad)
 
     def shutdown(self):
         for root in getattr(self, "_wg_roots", []):
@@ -360,9 +409,10 @@ class RayPPOTrainer:
             gen.meta_info.update({"eos_token_id": getattr(self.tokenizer, "eos_token_id", None),
                                   "pad_token_id": getattr(self.tokenizer, "pad_token_id", 0) or 0, "recompute_log_prob": False,
                                   "do_sample": vk.do_sample, "validate": True, "global_steps": self.global_steps})
-            div = 1 if self.spmd else self.actor_rollout_wg.world_size
-            padded, pad = pad_dataproto_to_divisor(gen, div)
-            out = unpad_dataproto(self.actor_rollout_wg.generate_sequences(padded), pad_size=pad)
+            out = self._generate(gen)
+            for k in list(out.non_tensor_batch.keys()):
+                if k in test_batch.non_tensor_batch:
+                    out.non_tensor_batch.pop(k)
             test_batch = test_batch.union(out)
             test_batch.meta_info["validate"] = True
             res = self.val_reward_fn(test_batch, return_dict=True)
@@ -494,17 +544,14 @@ class RayPPOTrainer:
                                     "eos_token_id": getattr(self.tokenizer, "eos_token_id", None)})
         gen_batch = gen_batch.repeat(repeat_times=n, interleave=True)
         with marked_timer("gen", timing_raw, "red"):
-            div = 1 if self.spmd else self.actor_rollout_wg.world_size
-            padded, pad = pad_dataproto_to_divisor(gen_batch, div)
-            gen_out = unpad_dataproto(self.actor_rollout_wg.generate_sequences(padded), pad_size=pad)
+            gen_out = self._generate(gen_batch)
             for k, v in (gen_out.meta_info.pop("metrics", {}) or {}).items():
                 metrics[k] = float(np.mean(v)) if isinstance(v, list) else v
         if cfg.algorithm.adv_estimator == "remax":
             with marked_timer("gen_max", timing_raw, "purple"):
                 base = deepcopy(gen_batch)
                 base.meta_info["do_sample"] = False
-                padded, pad = pad_dataproto_to_divisor(base, div)
-                base_out = unpad_dataproto(self.actor_rollout_wg.generate_sequences(padded), pad_size=pad)
+                base_out = self._generate(base)
                 tmp = batch.repeat(repeat_times=n, interleave=True).union(base_out)
                 rb, _ = compute_reward(tmp, self.reward_fn)
                 batch_baseline = rb.sum(dim=-1)

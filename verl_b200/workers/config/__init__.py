@@ -428,6 +428,8 @@ class CustomAsyncServerConfig(BaseConfig):
 class AgentLoopConfig(BaseConfig):
     num_workers: int = 8
     default_agent_loop: str = "single_turn_agent"
+    # route plain single-turn rollouts through the agent loops too (they are always used for multi-turn / tools)
+    use_agent_loop: bool = False
     agent_loop_config_path: Optional[str] = None
     custom_async_server: CustomAsyncServerConfig = field(default_factory=CustomAsyncServerConfig)
 

@@ -345,6 +345,33 @@ class ActorRolloutRefWorker(_WorkerBase):
             self._profiler.stop()
 
 
+    # ------------------------------------------------------------ rollout server
+    def get_async_server(self):
+        """The token-in / token-out server around this worker's rollout engine (created on first use)."""
+        if getattr(self, "_async_server", None) is None:
+            from .rollout.async_server import NativeAsyncServer
+
+            rc = self.rollout_cfg
+            self.rollout_engine.wake_up()
+            self._async_server = NativeAsyncServer(self.rollout_engine, response_length=int(rc.response_length),
+                                                   prompt_length=int(rc.prompt_length))
+            if rc.free_cache_engine:
+                import asyncio
+
+                asyncio.run(self._async_server.sleep())
+        return self._async_server
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def start_rollout_server(self, address: str = "127.0.0.1") -> str:
+        """Serve the rollout engine over HTTP from this worker process; returns ``host:port`` (the driver's agent
+        loops talk to it through :class:`HttpServerHandle`)."""
+        if getattr(self, "_async_server_address", None) is None:
+            from .rollout.async_server import serve_in_thread
+
+            self._async_server_address = serve_in_thread(self.get_async_server(), address)
+        return self._async_server_address
+
+
 class AsyncActorRolloutRefWorker(ActorRolloutRefWorker):
     """Same worker; kept as a distinct name because the reference selects it for ``rollout.mode=async``."""
 

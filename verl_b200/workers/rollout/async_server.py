@@ -40,6 +40,10 @@ class NativeAsyncServer:
     # ------------------------------------------------------------ engine thread
     def _loop(self):
         eng = self.engine
+        if getattr(eng, "on_gpu", False):
+            import torch
+
+            torch.cuda.set_device(eng.device)  # the engine thread launches on the engine's GPU
         while not self._stop:
             with self._lock:
                 inbox, self._inbox = self._inbox, []
@@ -188,6 +192,30 @@ class NativeAsyncServer:
         async def abort(body: dict):
             return await server.abort_request(body["request_id"])
 
+        @app.post("/wake_up")
+        async def wake_up():
+            await server.wake_up()
+            return {"ok": True}
+
+        @app.post("/sleep")
+        async def sleep():
+            await server.sleep()
+            return {"ok": True}
+
+        @app.post("/abort_all_requests")
+        async def abort_all(body: dict):
+            return await server.abort_all_requests(bool(body.get("reset_prefix_cache", True)))
+
+        @app.post("/resume_all_requests")
+        async def resume_all():
+            await server.resume_all_requests()
+            return {"ok": True}
+
+        @app.post("/clear_kv_cache")
+        async def clear_cache():
+            await server.clear_kv_cache()
+            return {"ok": True}
+
         @app.get("/metrics")
         async def metrics():
             """Prometheus text exposition of the scheduler gauges (scraped by the job that
@@ -206,3 +234,81 @@ class NativeAsyncServer:
 
 
 from .utils import run_unvicorn  # noqa: E402,F401  (historical import location)
+
+
+def serve_in_thread(server: NativeAsyncServer, address: str = "127.0.0.1") -> str:
+    """Serve ``server.build_app()`` from a background thread of this process (its own event loop); returns
+    ``host:port``. Used by worker processes, whose main thread belongs to the worker group's command loop."""
+    box: dict = {}
+    ready = threading.Event()
+
+    def run():
+        async def main():
+            port, task = await run_unvicorn(server.build_app(), None, address)
+            box["port"], box["task"] = port, task
+            ready.set()
+            await task
+
+        try:
+            asyncio.run(main())
+        except BaseException as e:  # surface start-up failures to the caller
+            box["error"] = e
+            ready.set()
+
+    t = threading.Thread(target=run, daemon=True, name="rollout-http")
+    t.start()
+    ready.wait(60)
+    if "error" in box or "port" not in box:
+        raise RuntimeError(f"rollout HTTP server did not start: {box.get('error')}")
+    server._http_thread, server._http_task = t, box["task"]
+    return f"{address}:{box['port']}"
+
+
+class HttpServerHandle:
+    """Client-side handle of a :class:`NativeAsyncServer` in another process: the coroutine interface the agent
+    loops use, carried over the server's HTTP endpoints."""
+
+    def __init__(self, address: str, timeout: float = 3600.0):
+        self.address, self.timeout = address, timeout
+        self._session = None
+
+    async def _post(self, path: str, body: Optional[dict] = None) -> dict:
+        import aiohttp
+
+        # one session per event loop (the agent-loop manager runs a fresh loop per batch)
+        loop = asyncio.get_running_loop()
+        if self._session is None or self._session[0] is not loop or self._session[1].closed:
+            self._session = (loop, aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=self.timeout)))
+        async with self._session[1].post(f"http://{self.address}{path}", json=body or {}) as resp:
+            resp.raise_for_status()
+            return await resp.json()
+
+    async def generate(self, prompt_ids: list[int], sampling_params: Optional[dict] = None, request_id: Optional[str] = None,
+                       image_data=None, video_data=None, priority: int = 0) -> TokenOutput:
+        sp = {k: v for k, v in (sampling_params or {}).items() if isinstance(v, (int, float, bool, str, list, type(None)))}
+        body = await self._post("/generate", {"prompt_ids": [int(t) for t in prompt_ids], "sampling_params": sp,
+                                              "request_id": request_id})
+        return TokenOutput(token_ids=body["token_ids"], log_probs=body.get("log_probs"), stop_reason=body.get("stop_reason"),
+                           num_preempted=int(body.get("num_preempted", 0) or 0), request_id=request_id)
+
+    async def abort_request(self, request_id: str, reset_prefix_cache: bool = False):
+        return await self._post("/abort_request", {"request_id": request_id})
+
+    async def abort_all_requests(self, reset_prefix_cache: bool = True):
+        return await self._post("/abort_all_requests", {"reset_prefix_cache": reset_prefix_cache})
+
+    async def resume_all_requests(self):
+        return await self._post("/resume_all_requests")
+
+    async def wake_up(self, tags=None):
+        return await self._post("/wake_up")
+
+    async def sleep(self):
+        return await self._post("/sleep")
+
+    async def clear_kv_cache(self):
+        return await self._post("/clear_kv_cache")
+
+    async def close(self):
+        if self._session is not None and not self._session[1].closed:
+            await self._session[1].close()
