@@ -197,3 +197,39 @@ def test_fp8_rollout_close_to_bf16_rollout():
     assert max(first_lp) < 0.25, first_lp
     same_first = sum(a.token_ids[0] == b.token_ids[0] for a, b in zip(res[None], res["fp8"]))
     assert same_first >= 2
+
+
+def test_async_server_thread_on_gpu_matches_engine():
+    """The token-in / token-out server steps the engine (CUDA graphs included) from its own thread: concurrent
+    requests give the greedy continuations the engine produces when driven directly, and an abort returns the
+    partial output."""
+    import asyncio
+
+    from verl_b200.models.transformer import CausalLM
+    from verl_b200.rollout import NativeRolloutEngine, SamplingParams
+    from verl_b200.workers.rollout.async_server import NativeAsyncServer
+
+    cfg = _cfg("dense")
+    m = CausalLM(cfg, dtype=torch.bfloat16, device="cuda")
+    m.init_weights(4)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (33, 120, 64, 200)]
+    direct = NativeRolloutEngine(m, max_num_seqs=8, max_model_len=512, max_num_batched_tokens=1024, gpu_memory_utilization=0.1, seed=5)
+    want = [o.token_ids for o in direct.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))]
+    eng = NativeRolloutEngine(m, max_num_seqs=8, max_model_len=512, max_num_batched_tokens=1024, gpu_memory_utilization=0.1, seed=5)
+    srv = NativeAsyncServer(eng, response_length=64, prompt_length=256)
+
+    async def go():
+        sp = {"temperature": 0.0, "max_tokens": 12, "ignore_eos": True}
+        outs = await asyncio.gather(*[srv.generate(p, sp) for p in prompts])
+        long = asyncio.ensure_future(srv.generate(prompts[0], {"temperature": 1.0, "max_tokens": 200, "ignore_eos": True}))
+        await asyncio.sleep(0.05)
+        await srv.abort_all_requests()
+        return outs, await long
+
+    try:
+        outs, cut = asyncio.run(go())
+    finally:
+        srv.shutdown()
+    assert [o.token_ids for o in outs] == want
+    assert cut.stop_reason in ("aborted", "length") and len(cut.token_ids) <= 200
