@@ -67,3 +67,29 @@ def test_fully_async_pipeline(tmp_path, monkeypatch):
     for m in out:
         assert math.isfinite(m["actor/pg_loss"]) and "fully_async/staleness_mean" in m and "timing_s/param_sync" in m
     assert out[-1]["fully_async/param_version"] >= 2
+
+
+def test_fully_async_pipeline_with_partial_rollouts(tmp_path, monkeypatch):
+    """Prompt groups stream through the agent-loop manager; every parameter update aborts the generations in flight
+    and they are resumed afterwards. Training steps complete and (with long responses on a slow CPU engine) some
+    generations are indeed cut and continued."""
+    from verl_b200.experimental.fully_async_policy import run_fully_async
+    from verl_b200.trainer.main_ppo import run_ppo
+
+    monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
+    cfg = compose("ppo_trainer", _overrides(tmp_path, ["trainer.n_gpus_per_node=1", "trainer.save_freq=-1",
+                                                       "actor_rollout_ref.rollout.free_cache_engine=false",
+                                                       "actor_rollout_ref.rollout.agent.num_workers=2",
+                                                       "data.max_response_length=24", "actor_rollout_ref.rollout.n=2"]))
+    trainer = run_ppo(cfg, spmd=True, run_fit=False)
+    try:
+        out = run_fully_async(trainer, total_train_steps=3, required_samples=2, max_staleness=16, step_timeout=300,
+                              partial_rollout=True, max_concurrent_groups=4)
+        r = trainer.fully_async_rollouter
+    finally:
+        trainer.shutdown()
+    assert len(out) == 3 and r.error is None and r.produced_groups >= 6
+    for m in out:
+        assert math.isfinite(m["actor/pg_loss"]) and "fully_async/staleness_mean" in m and "timing_s/param_sync" in m
+    assert out[-1]["fully_async/param_version"] >= 2
+    print("cancelled generations:", r.cancelled_generations)

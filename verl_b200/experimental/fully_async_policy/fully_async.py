@@ -130,6 +130,113 @@ class FullyAsyncRollouter:
             self.mq.close()
 
 
+class StreamingRollouter(FullyAsyncRollouter):
+    """Producer with partial rollouts: every prompt group runs as its own task through the fully-async agent-loop
+    manager. ``pause()`` (a parameter update) aborts the generations in flight; the groups keep their partial
+    outputs and continue after ``resume()`` under the new weights, so a weight sync never waits for the longest
+    sample. A group's queue entry carries the oldest parameter version that produced any of its tokens.
+    (verl/experimental/fully_async_policy/fully_async_rollouter.py: ``partial_rollout=True``.)"""
+
+    def __init__(self, trainer: RayPPOTrainer, message_queue: MessageQueue, manager, max_queue_size: Optional[int] = None,
+                 total_rollout_steps: Optional[int] = None, max_concurrent_groups: int = 64):
+        super().__init__(trainer, message_queue, max_queue_size, total_rollout_steps)
+        self.manager = manager
+        self.max_concurrent_groups = int(max_concurrent_groups)
+        self._loop_obj = None
+        self._ready = threading.Event()
+        self.cancelled_generations = 0
+
+    def pause(self):
+        self._run.clear()
+        if self._thread is None:  # not started yet: nothing in flight
+            return
+        self._ready.wait(60)
+        if self._loop_obj is not None and self._thread is not None and self._thread.is_alive():
+            import asyncio
+
+            asyncio.run_coroutine_threadsafe(self.manager.cancel(), self._loop_obj).result(timeout=600)
+
+    def resume(self):
+        if self._loop_obj is not None and self._thread is not None and self._thread.is_alive():
+            import asyncio
+
+            asyncio.run_coroutine_threadsafe(self.manager.resume(), self._loop_obj).result(timeout=600)
+        self._run.set()
+
+    def _loop(self):
+        import asyncio
+
+        try:
+            asyncio.run(self._main())
+        except BaseException as e:
+            self.error = e
+            self.mq.close()
+        finally:
+            self._ready.set()
+
+    async def _main(self):
+        import asyncio
+        import uuid
+
+        self._loop_obj = asyncio.get_running_loop()
+        self._ready.set()
+        tr, n = self.trainer, self.n
+        sem = asyncio.Semaphore(self.max_concurrent_groups)
+        tasks: set = set()
+        steps = 0
+
+        async def drive(group: DataProto):
+            try:
+                gen = tr._get_gen_batch(group)
+                gen.meta_info.update({"pad_token_id": getattr(tr.tokenizer, "pad_token_id", 0) or 0,
+                                      "eos_token_id": getattr(tr.tokenizer, "eos_token_id", None)})
+                gen = gen.repeat(repeat_times=n, interleave=True)
+                outs, cancelled = await self.manager.generate_single_sample_async(gen, None, self.param_version)
+                while cancelled and not self._stop:
+                    self.cancelled_generations += sum(bool(o.extra_fields.get("is_cancel")) for o in outs)
+                    await self.manager.wait_resumed()
+                    outs, cancelled = await self.manager.generate_single_sample_async(gen, outs, self.param_version)
+                if self._stop:
+                    return
+                version = min(int(o.extra_fields.get("param_version_start", self.param_version)) for o in outs)
+                gen_out = self.manager.postprocess(outs)
+                gen_out.meta_info.pop("metrics", None)
+                batch = tr._attach_rollout_and_reward(group.repeat(repeat_times=n, interleave=True), gen_out, {})
+                await asyncio.get_running_loop().run_in_executor(None, self.mq.put_sample, batch, version)
+                self.produced_groups += 1
+            finally:
+                sem.release()
+
+        await asyncio.gather(*[h.wake_up() for h in self.manager.server_handles])  # the engines stay awake
+        finished = False
+        while not self._stop and not finished:
+            for batch_dict in tr.train_dataloader:
+                if self._stop or (self.total_rollout_steps is not None and steps >= self.total_rollout_steps):
+                    finished = True
+                    break
+                batch = tr._local(DataProto.from_single_dict(batch_dict))
+                batch.non_tensor_batch["uid"] = np.array([str(uuid.uuid4()) for _ in range(len(batch))], dtype=object)
+                for g in range(len(batch)):
+                    while not self._stop:  # back-pressure: room in the queue first, then a free slot
+                        if await asyncio.get_running_loop().run_in_executor(
+                                None, lambda: self.mq.wait_below(self.max_queue_size, timeout=0.5)):
+                            break
+                    if self._stop:
+                        break
+                    await sem.acquire()
+                    t = asyncio.ensure_future(drive(batch[g : g + 1]))
+                    tasks.add(t)
+                    t.add_done_callback(tasks.discard)
+                steps += 1
+            if self.total_rollout_steps is None:
+                finished = True  # one pass over the data
+        if tasks:
+            done, _ = await asyncio.wait(tasks)
+            for t in done:
+                if t.exception() is not None:
+                    raise t.exception()
+
+
 class FullyAsyncTrainer:
     """Consumer: ``required_samples`` prompt groups per training step, parameter sync every k steps."""
 
@@ -179,13 +286,27 @@ def _push_weights(trainer: RayPPOTrainer):
 
 def run_fully_async(trainer: RayPPOTrainer, total_train_steps: int, required_samples: Optional[int] = None,
                     max_queue_size: Optional[int] = None, max_staleness: Optional[int] = 3,
-                    trigger_parameter_sync_step: int = 1, step_timeout: Optional[float] = 600.0) -> list[dict]:
+                    trigger_parameter_sync_step: int = 1, step_timeout: Optional[float] = 600.0,
+                    partial_rollout: bool = False, max_concurrent_groups: int = 64) -> list[dict]:
     """Wire queue, rollouter, synchroniser and trainer around an initialised ``RayPPOTrainer`` and run
-    ``total_train_steps`` trainer steps. Returns the per-step metrics."""
+    ``total_train_steps`` trainer steps. Returns the per-step metrics. ``partial_rollout``: prompt groups stream
+    through the agent-loop manager and generations cut by a parameter update are resumed (:class:`StreamingRollouter`)
+    instead of whole batches being drained before every update."""
     groups_per_batch = int(trainer.config.data.train_batch_size) // max(1, trainer.spmd_world)
     required = int(required_samples or groups_per_batch)
     mq = MessageQueue(max_queue_size or 4 * required, max_staleness)
-    rollouter = FullyAsyncRollouter(trainer, mq, max_queue_size=max_queue_size or 4 * required)
+    if partial_rollout:
+        from .agent_loop import FullyAsyncAgentLoopManager
+
+        if not getattr(trainer, "async_rollout_mode", False):
+            trainer._init_async_rollout_manager()
+        manager = FullyAsyncAgentLoopManager(trainer.config, server_handles=trainer._rollout_server_handles,
+                                             tokenizer=trainer.tokenizer, processor=trainer.processor)
+        rollouter = StreamingRollouter(trainer, mq, manager, max_queue_size=max_queue_size or 4 * required,
+                                       max_concurrent_groups=max_concurrent_groups)
+        trainer.fully_async_rollouter = rollouter
+    else:
+        rollouter = FullyAsyncRollouter(trainer, mq, max_queue_size=max_queue_size or 4 * required)
     sync = ParameterSynchronizer(_push_weights(trainer), mq, rollouter)
     consumer = FullyAsyncTrainer(trainer, mq, sync, required, trigger_parameter_sync_step)
     sync.sync_weights(0)

@@ -556,12 +556,18 @@ class RayPPOTrainer:
                 rb, _ = compute_reward(tmp, self.reward_fn)
                 batch_baseline = rb.sum(dim=-1)
         batch = batch.repeat(repeat_times=n, interleave=True)
+        batch = self._attach_rollout_and_reward(batch, gen_out, timing_raw)
+        if cfg.algorithm.adv_estimator == "remax":
+            batch.batch["reward_baselines"] = batch_baseline
+        return batch
+
+    def _attach_rollout_and_reward(self, batch: DataProto, gen_out: DataProto, timing_raw: dict) -> DataProto:
+        """``batch`` (prompt-side fields, already repeated n times) + rollout output -> batch with
+        ``token_level_scores``. Also used by producers that generate elsewhere (streaming rollouter)."""
         for k in list(gen_out.non_tensor_batch.keys()):
             if k in batch.non_tensor_batch:
                 gen_out.non_tensor_batch.pop(k)
         batch = batch.union(gen_out)
-        if cfg.algorithm.adv_estimator == "remax":
-            batch.batch["reward_baselines"] = batch_baseline
         if "response_mask" not in batch.batch.keys():
             batch.batch["response_mask"] = compute_response_mask(batch)
         with marked_timer("reward", timing_raw, "yellow"):
