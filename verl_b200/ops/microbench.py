@@ -170,9 +170,48 @@ def bench_decode_step(a):
             "us": round(us, 1), "tokens_per_s": round(a.batch / us * 1e6, 0)}
 
 
+def bench_fp8_gemm(a):
+    """Block-scaled fp8 GEMM (1 x 128 activation scales, 128 x 128 weight scales) next to the bf16 GEMM."""
+    from . import fp8, gemm
+
+    M, N, K = a.m, a.n, a.k
+    nrep = max(1, min(8, int(256e6 // (N * K)) + 1))
+    ws = [fp8.quantize_weight(torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05) for _ in range(nrep)]
+    wb = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    xq, sx = fp8.quantize_activation(x)
+    i = [0]
+
+    def ours():
+        wq, sw = ws[i[0] % nrep]
+        fp8.fp8_gemm(xq, sx, wq, sw)
+        i[0] += 1
+
+    us = _time(ours, a.iters, a.warmup)
+    us_q = _time(lambda: fp8.quantize_activation(x), a.iters, a.warmup)
+    us_b = _time(lambda: gemm(x, wb), a.iters, a.warmup)
+    return {"kernel": "fp8_gemm_blockscale", "M": M, "N": N, "K": K, "us": round(us, 2), "tflops": round(2.0 * M * N * K / us / 1e6, 1),
+            "gbs": round((N * K + M * K + 2 * M * N) / us / 1e3, 1), "act_quant_us": round(us_q, 2), "bf16_gemm_us": round(us_b, 2)}
+
+
+def bench_grouped_gemm(a):
+    """Grouped (MoE) GEMM: ``--batch`` experts, ``--m`` routed rows in total (uniform routing), N x K per expert."""
+    from . import moe
+
+    E, T, N, K = a.batch, a.m, a.n, a.k
+    top_i = torch.randint(0, E, (T, 1), device="cuda")
+    dest, blk_expert, expert_off, P = moe.moe_layout(top_i, E)
+    xs = torch.randn(P, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(E, N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    with torch.no_grad():
+        us = _time(lambda: moe.grouped_linear(xs, w, blk_expert, expert_off), a.iters, a.warmup)
+    return {"kernel": "grouped_gemm_bf16", "experts": E, "rows": T, "padded_rows": P, "N": N, "K": K, "us": round(us, 2),
+            "tflops_useful": round(2.0 * T * N * K / us / 1e6, 1), "weight_gbs": round(E * N * K * 2 / us / 1e3, 1)}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "lmhead", "decode", "decode_step", "attn"])
+    ap.add_argument("what", choices=["gemm", "lmhead", "decode", "decode_step", "attn", "fp8_gemm", "grouped_gemm"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -192,7 +231,8 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--library", action="store_true")
     a = ap.parse_args(argv)
-    fn = {"gemm": bench_gemm, "lmhead": bench_lmhead, "decode": bench_decode, "decode_step": bench_decode_step, "attn": bench_attn}[a.what]
+    fn = {"gemm": bench_gemm, "lmhead": bench_lmhead, "decode": bench_decode, "decode_step": bench_decode_step, "attn": bench_attn,
+          "fp8_gemm": bench_fp8_gemm, "grouped_gemm": bench_grouped_gemm}[a.what]
     print(json.dumps(fn(a)))
 
 
