@@ -44,6 +44,9 @@ def parse_args():
     ap.add_argument("--max-token-len", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run as reduced)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--agent-loop", action="store_true",
+                    help="variant: rollouts through the agent loops and the token-in / token-out server (not the headline path)")
+    ap.add_argument("--lora-rank", type=int, default=0, help="variant: LoRA training (not the headline configuration)")
     return ap.parse_args()
 
 
@@ -141,6 +144,11 @@ def build_config(args, world: int):
     ]
     if args.layers:
         ov.append(f"+actor_rollout_ref.model.override_config.num_hidden_layers={args.layers}")
+    if args.agent_loop:
+        ov += ["actor_rollout_ref.rollout.agent.use_agent_loop=true", "actor_rollout_ref.rollout.agent.num_workers=4",
+               "data.return_raw_chat=true"]
+    if args.lora_rank:
+        ov += [f"actor_rollout_ref.model.lora_rank={args.lora_rank}", "actor_rollout_ref.model.lora_alpha=32"]
     return compose("ppo_trainer", ov)
 
 
@@ -260,7 +268,8 @@ def main():
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic prompts (uniform ids), random-init weights", "impl": "ours",
-            "config": {"model": args.model if not args.layers else f"{args.model}-REDUCED-{args.layers}L",
+            "config": {"model": (args.model if not args.layers else f"{args.model}-REDUCED-{args.layers}L")
+                       + ("+agent-loop-rollout" if args.agent_loop else "") + (f"+lora{args.lora_rank}" if args.lora_rank else ""),
                        "layers": c.num_hidden_layers, "hidden": c.hidden_size, "vocab": c.vocab_size,
                        "global_batch": args.prompts_per_gpu * world * args.n, "prompts": args.prompts_per_gpu * world,
                        "n_samples": args.n, "seq_len": args.max_prompt + args.max_response,
