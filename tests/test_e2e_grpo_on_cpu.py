@@ -84,7 +84,8 @@ def test_grpo_through_agent_loops(tmp_path, monkeypatch, spmd):
 
     monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
     extra = ["actor_rollout_ref.rollout.agent.use_agent_loop=true", "actor_rollout_ref.rollout.agent.num_workers=2",
-             "trainer.save_freq=-1", "trainer.experiment_name=agent", "data.return_raw_chat=true"]
+             "trainer.save_freq=-1", "trainer.experiment_name=agent", "data.return_raw_chat=true",
+             "data.max_response_length=24", "actor_rollout_ref.rollout.n=2"]
     if spmd == "tool":  # multi-turn configuration: the tool-calling state machine drives every sample
         extra = ["actor_rollout_ref.rollout.multi_turn.enable=true", "actor_rollout_ref.rollout.multi_turn.max_assistant_turns=2",
                  "actor_rollout_ref.rollout.agent.default_agent_loop=tool_agent"] + extra[1:]

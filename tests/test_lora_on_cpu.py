@@ -97,7 +97,8 @@ def test_lora_grpo_end_to_end(tmp_path, monkeypatch):
 
     monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
     cfg = compose("ppo_trainer", _overrides(tmp_path, ["actor_rollout_ref.model.lora_rank=8", "actor_rollout_ref.model.lora_alpha=16",
-                                                       "actor_rollout_ref.actor.optim.lr=1e-3", "trainer.experiment_name=lora"]))
+                                                       "actor_rollout_ref.actor.optim.lr=1e-3", "trainer.experiment_name=lora",
+                                                       "data.max_response_length=24", "actor_rollout_ref.rollout.n=2"]))
     trainer = run_ppo(cfg, spmd=False)
     assert trainer.global_steps == 2
     rows = [json.loads(l) for l in open(tmp_path / "logs" / "cpu_e2e" / "lora.jsonl")]
