@@ -22,8 +22,10 @@ from ...rollout import NativeRolloutEngine, SamplingParams, TokenOutput
 
 
 class NativeAsyncServer:
-    def __init__(self, engine: NativeRolloutEngine, response_length: int = 512, prompt_length: int = 512):
+    def __init__(self, engine: NativeRolloutEngine, response_length: int = 512, prompt_length: int = 512,
+                 coalesce_ms: float = 20.0):
         self.engine = engine
+        self.coalesce_s = float(coalesce_ms) / 1e3  # longest wait for the rest of a burst of new requests
         self.response_length, self.prompt_length = response_length, prompt_length
         self._lock = threading.Lock()
         self._pending: dict[str, Future] = {}
@@ -48,6 +50,18 @@ class NativeAsyncServer:
             with self._lock:
                 inbox, self._inbox = self._inbox, []
                 aborts, self._aborts = self._aborts, []
+            if inbox:
+                # Requests of one batch arrive within a few milliseconds of each other. Taking them in one go lets the
+                # prefill see them together and the decode batch start at its full size, instead of growing through
+                # every padded size (each of which would need its own CUDA graph after a wake-up).
+                deadline = time.monotonic() + self.coalesce_s
+                quiet = 0
+                while time.monotonic() < deadline and quiet < 3:  # three quiet milliseconds end the burst
+                    time.sleep(0.001)
+                    with self._lock:
+                        more, self._inbox = self._inbox, []
+                    quiet = 0 if more else quiet + 1
+                    inbox.extend(more)
             for rid, prompt, sp in inbox:
                 try:
                     eng.add_request(rid, prompt, sp)
