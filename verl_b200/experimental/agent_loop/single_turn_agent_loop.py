@@ -19,6 +19,9 @@ class SingleTurnAgentLoop(AgentLoopBase):
     async def run(self, sampling_params: dict[str, Any], **kwargs) -> AgentLoopOutput:
         prompt_ids = await self.apply_chat_template(kwargs["raw_prompt"])
         t0 = time.perf_counter()
+        # the output is cut to response_length below: do not let the server spend the unused prompt budget on it
+        sampling_params = dict(sampling_params)
+        sampling_params["max_tokens"] = min(int(sampling_params.get("max_tokens", self.response_length)), self.response_length)
         out = await self.server_manager.generate(uuid4().hex, prompt_ids=prompt_ids, sampling_params=sampling_params)
         dt = time.perf_counter() - t0
         ids = out.token_ids[: self.response_length]
