@@ -87,6 +87,19 @@ def main():
     torch.testing.assert_close(lp2, lp1, atol=1e-4, rtol=1e-4)
     torch.testing.assert_close(ent2, ent1, atol=1e-4, rtol=1e-4)
     assert abs(gn2 - gn1) < 1e-3 * max(1.0, gn1), (gn2, gn1)
+    # sharding-manager interface: the group's shares are gathered before, and split again after, the computation
+    from verl_b200.protocol import DataProto
+    from verl_b200.workers.sharding_manager import FSDPUlyssesShardingManager
+
+    mgr = FSDPUlyssesShardingManager(dist.group.WORLD)
+    mine = DataProto.from_dict({"x": torch.arange(3) + 10 * rank})
+    with mgr:
+        assert U.get_ulysses_sequence_parallel_group() is dist.group.WORLD
+        both = mgr.preprocess_data(mine)
+        assert both.batch["x"].tolist() == [0, 1, 2, 10, 11, 12]
+        back = mgr.postprocess_data(both)
+        assert back.batch["x"].tolist() == [10 * rank, 10 * rank + 1, 10 * rank + 2]
+    assert U.get_ulysses_sequence_parallel_group() is None
     if rank == 0:
         print("ULYSSES_OK")
     dist.destroy_process_group()

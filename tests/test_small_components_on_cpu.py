@@ -416,3 +416,23 @@ def test_rollout_tokenizer_adapter():
     assert isinstance(t, HybridEngineBaseTokenizer) and t.vocab_size == 100 and sorted(t.all_special_ids) == [0, 2]
     assert t.encode("5 6 7") == [5, 6, 7] and t.decode([5, 2, 6], skip_special_tokens=True) == "5 6"
     assert t.convert_ids_to_tokens([5, 2], skip_special_tokens=True) == ["5"] and t.convert_tokens_to_string(["a", "b"]) == "a b"
+
+
+def test_mcp_search_parse_weight_keys_and_sharding_manager():
+    from verl_b200.protocol import DataProto
+    from verl_b200.tools.mcp_base_tool import MCPSearchTool
+    from verl_b200.utils.model import convert_weight_keys, extract_multi_modal_inputs
+    from verl_b200.workers.sharding_manager import FSDPUlyssesShardingManager
+
+    tool = MCPSearchTool({}, _SCHEMA)
+    text, meta = tool._parse_tool_result([{"text": '{"query": "q", "results": ["a", "b"]}'}, {"text": "plain"}, {"image": 1}])
+    assert text == "a\nb\nplain" and meta["query_count"] == 1 and meta["total_results"] == 3
+    assert tool._parse_tool_result([])[0] == "no search result."
+    sd = convert_weight_keys({"module._fsdp_wrapped_module.layers.0.w": 1, "base_model.model.lm_head.weight": 2, "x": 3})
+    assert sd == {"layers.0.w": 1, "lm_head.weight": 2, "x": 3}
+    mm = extract_multi_modal_inputs([{"pixel_values": torch.ones(2, 3)}, {}, {"pixel_values": torch.zeros(1, 3)}], indices=[0, 2])
+    assert mm["pixel_values"].shape == (3, 3)
+    mgr = FSDPUlyssesShardingManager(None)  # no sequence parallelism: a pass-through
+    d = DataProto.from_dict({"x": torch.arange(4)})
+    with mgr:
+        assert mgr.postprocess_data(mgr.preprocess_data(d)) is d

@@ -61,6 +61,7 @@ _MOVED = {
     "verl.experimental.reward_loop.reward_manager.registry": "verl_b200.experimental.reward_loop.reward_manager",
     "verl.experimental.reward_loop.reward_manager.base": "verl_b200.experimental.reward_loop.reward_manager",
     "verl.tools.mcp_search_tool": "verl_b200.tools.mcp_base_tool",
+    "verl.workers.sharding_manager.fsdp_ulysses": "verl_b200.workers.sharding_manager.fsdp_ulysses",
     "verl.tools.utils.mcp_clients.McpClientManager": "verl_b200.tools.mcp_base_tool",
     "verl.utils.dataset.rl_dataset": "verl_b200.utils.dataset.rl_dataset",
 }

@@ -93,3 +93,26 @@ class MCPBaseTool(BaseTool):
 
     async def release(self, instance_id: str, **kwargs) -> None:
         self._instances.pop(instance_id, None)
+
+
+class MCPSearchTool(MCPBaseTool):
+    """MCP search servers answer with a list of content parts; the text parts' JSON payloads carry the hits under
+    ``results`` (verl/tools/mcp_search_tool.py:25-69)."""
+
+    def _parse_tool_result(self, content) -> tuple[str, dict]:
+        parts = content if isinstance(content, list) else [content]
+        hits, queries = [], []
+        for part in parts:
+            text = part.get("text") if isinstance(part, dict) else getattr(part, "text", None)
+            if not text:
+                continue
+            try:
+                body = json.loads(text)
+            except (TypeError, ValueError):
+                hits.append(str(text))
+                continue
+            queries.append(body.get("query", ""))
+            res = body.get("results", body.get("result", []))
+            hits.extend(str(r) for r in (res if isinstance(res, list) else [res]))
+        meta = {"queries": queries, "query_count": len(queries), "total_results": len(hits)}
+        return ("\n".join(hits) if hits else "no search result."), meta

@@ -89,3 +89,31 @@ def check_target_modules(config, key: str) -> bool:
     if isinstance(target, str):
         return re.fullmatch(target, key) is not None
     return any(key == t or key.endswith("." + t) for t in target)
+
+
+def convert_weight_keys(state_dict: dict, model=None) -> dict:
+    """Checkpoints saved by other tool chains prefix or rename keys (``_checkpoint_conversion_mapping`` of HF models,
+    verl/utils/model.py:230-248). The native model takes HF names through ``models.hf_io``; what is left to undo
+    here are wrapper prefixes: ``module.``, ``_orig_mod.``, ``_fsdp_wrapped_module.``, ``base_model.model.``."""
+    out = {}
+    for k, v in state_dict.items():
+        changed = True
+        while changed:
+            changed = False
+            for pre in ("module.", "_orig_mod.", "_fsdp_wrapped_module.", "base_model.model."):
+                if k.startswith(pre):
+                    k, changed = k[len(pre):], True
+        out[k.replace("._fsdp_wrapped_module", "").replace("._orig_mod", "")] = v
+    return out
+
+
+def extract_multi_modal_inputs(batch_data: list[dict], indices=None) -> dict:
+    """Concatenate the per-sample ``multi_modal_inputs`` dicts of a batch key by key (verl/utils/model.py:696-738);
+    ``indices`` selects samples."""
+    picked = batch_data if indices is None else [batch_data[int(i)] for i in indices]
+    keys = sorted({k for d in picked if d for k in d})
+    out = {}
+    for k in keys:
+        vals = [d[k] for d in picked if d and k in d]
+        out[k] = torch.cat(vals, dim=0) if all(isinstance(v, torch.Tensor) for v in vals) else vals
+    return out
