@@ -283,7 +283,7 @@ class NativeEngine(BaseEngine):
         per_layer = int(tokens * per_token * 1.1)
         free, total = torch.cuda.mem_get_info(self.device)
         free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
-        reserve = max(10 << 30, total // 16) + 2 * per_layer
+        reserve = max(12 << 30, total // 12) + 2 * per_layer
         n = int(max(0, free - reserve) // max(per_layer, 1))
         self.last_kept_layers = min(n_layers, n)
         self.last_keep_info = {"free_gb": round(free / 2**30, 1), "per_layer_gb": round(per_layer / 2**30, 2),
