@@ -131,3 +131,28 @@ def test_sft_with_lora(tmp_path):
         if step == 5:
             break
     assert losses[-1] < losses[0] and torch.equal(tr.engine.zero.shard16, base0)
+
+
+def test_lora_single_process_rollout_copy_gets_merged_weights(tmp_path, monkeypatch):
+    """World size 1: the rollout model is a separate copy under LoRA (it would share the actor's tensors otherwise);
+    after a step it holds base + delta."""
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_e2e_grpo_on_cpu import _overrides
+
+    from verl_b200.models.lora import lora_delta
+    from verl_b200.trainer.main_ppo import run_ppo
+    from verl_b200.utils.config import compose
+
+    monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
+    cfg = compose("ppo_trainer", _overrides(tmp_path, ["actor_rollout_ref.model.lora_rank=8", "actor_rollout_ref.actor.optim.lr=1e-2",
+                                                       "trainer.n_gpus_per_node=1", "trainer.save_freq=-1",
+                                                       "data.max_response_length=16", "actor_rollout_ref.rollout.n=2"]))
+    trainer = run_ppo(cfg, spmd=True)
+    w = trainer.actor_rollout_wg.worker.worker_dict["actor_rollout"]
+    assert w.ref_engine is None and w.rollout_model is not w.actor_engine.model
+    name = w.actor_engine.model.lora_modules[0]
+    base_w = dict(w.actor_engine.zero.named_full_tensors())[name + ".weight"].float()
+    roll_w = dict(w.rollout_model.named_parameters())[name + ".weight"].float()
+    delta = lora_delta(dict(w.actor_engine.model.named_modules())[name])
+    assert float(delta.abs().sum()) > 0
+    torch.testing.assert_close(roll_w, base_w + delta, atol=1e-5, rtol=1e-5)

@@ -177,6 +177,17 @@ class RolloutWeights:
         else:
             parts = [z.shard16]
         eb = self.buffer.element_size()
+        if z.world == 1:
+            # one rank: the same source and destination views every time; one batched copy instead of a Python loop
+            if getattr(self, "_views", None) is None or self._views[2] is not z.shard16:
+                dst, src = [], []
+                for s in self.table_host:
+                    so, do, n = int(s["src_off"]) // eb, int(s["dst_off"]) // eb, int(s["nbytes"]) // eb
+                    dst.append(self.buffer[do : do + n])
+                    src.append(z.shard16[so : so + n])
+                self._views = (dst, src, z.shard16)
+            torch._foreach_copy_(self._views[0], self._views[1])
+            return
         for s in self.table_host:
             so, do, n, r = int(s["src_off"]) // eb, int(s["dst_off"]) // eb, int(s["nbytes"]) // eb, int(s["src_rank"])
             self.buffer[do : do + n].copy_(parts[r][so : so + n])
