@@ -73,8 +73,15 @@ def lora_named_parameters(model: nn.Module) -> Iterable[tuple[str, nn.Parameter]
 
 
 def lora_delta(mod) -> torch.Tensor:
-    """``(alpha / r) * B A`` in fp32, the matrix to add to the module's weight."""
-    return mod.lora_scale * (mod.lora_B.detach().float() @ mod.lora_A.detach().float())
+    """``(alpha / r) * B A`` in fp32, the matrix to add to the module's weight. On the GPU the product runs on the
+    framework's own GEMM with the adapters rounded to bf16, exactly what the forward pass multiplies with."""
+    a, b = mod.lora_A.detach(), mod.lora_B.detach()
+    if a.is_cuda:
+        from .. import ops
+
+        prod = ops.gemm(b.to(torch.bfloat16), a.to(torch.bfloat16).contiguous(), b_mn=True, out_dtype=torch.float32)
+        return mod.lora_scale * prod
+    return mod.lora_scale * (b.float() @ a.float())
 
 
 @torch.no_grad()
