@@ -387,6 +387,9 @@ class CriticWorker(_WorkerBase):
     def init_model(self):
         model_cfg, state = resolve_model_config(self.critic_cfg.model)
         model_cfg.num_labels = 1
+        if int(_cfg(self.critic_cfg.model, "lora_rank", 0) or 0) > 0 and self.dp_rank == 0:
+            # adapters on a critic would leave its freshly initialised value head frozen: the critic trains in full
+            print("[verl_b200] critic.model.lora_rank is ignored: LoRA applies to the actor (and SFT); the critic trains all weights")
         if state is not None:
             state = {k: v for k, v in state.items() if not k.startswith("lm_head")}
         group = dist.group.WORLD if dist.is_initialized() and self.world > 1 else None
