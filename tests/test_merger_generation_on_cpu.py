@@ -55,3 +55,17 @@ def test_generation_through_standalone_servers(tmp_path):
     assert len(out) == len(saved) == 4 and all(len(r["responses"]) == 2 for r in saved)
     texts = {t for r in saved for t in r["responses"]}
     assert len(texts) == 1 and len(next(iter(texts)).split()) > 0
+
+
+def test_init_random_model_and_print_cfg(tmp_path, capsys):
+    from verl_b200.models.init_random_model import main as init_main
+    from verl_b200.trainer.print_cfg import main as print_main
+    from verl_b200.workers.engine_workers import resolve_model_config
+
+    out = init_main(["--preset", "tiny-qwen2", "--out", str(tmp_path / "m"), "--seed", "3", "--dtype", "float32",
+                     "--override", "num_hidden_layers=1"])
+    assert (tmp_path / "m" / "config.json").exists()
+    cfg, state = resolve_model_config({"path": out})
+    assert cfg.num_hidden_layers == 1 and state is not None and any(k.startswith("layers.0.") for k in state)
+    text = print_main(["ppo_trainer", "data.train_batch_size=7"])
+    assert "train_batch_size: 7" in text and "actor_rollout_ref" in text

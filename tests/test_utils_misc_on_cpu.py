@@ -105,3 +105,10 @@ def test_fs_and_import_helpers(tmp_path):
         raise AssertionError("expected a RuntimeError")
     except RuntimeError:
         pass
+
+
+def test_diagnose_report():
+    from verl_b200.utils.diagnose import collect
+
+    info = collect()
+    assert info["python"] and "torch" in info and "native_library" in info and isinstance(info["env"], dict)
