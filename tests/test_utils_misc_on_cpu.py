@@ -112,3 +112,17 @@ def test_diagnose_report():
 
     info = collect()
     assert info["python"] and "torch" in info and "native_library" in info and isinstance(info["env"], dict)
+
+
+def test_rollout_viewer(tmp_path):
+    import json
+
+    from verl_b200.utils.rollout_viewer import main
+
+    for step in (1, 2):
+        with open(tmp_path / f"{step}.jsonl", "w") as f:
+            for i in range(3):
+                f.write(json.dumps({"input": f"q{i}", "output": f"answer {i} step {step}", "score": i / 2, "step": step}) + "\n")
+    text = main([str(tmp_path), "--step", "2", "--min-score", "0.5", "--sort", "-score"])
+    assert "2 rollouts" in text and text.index("answer 2 step 2") < text.index("answer 1 step 2") and "step 1" not in text
+    assert "1 rollouts" in main([str(tmp_path / "1.jsonl"), "--grep", "answer 0"])
