@@ -123,6 +123,6 @@ def test_rollout_viewer(tmp_path):
         with open(tmp_path / f"{step}.jsonl", "w") as f:
             for i in range(3):
                 f.write(json.dumps({"input": f"q{i}", "output": f"answer {i} step {step}", "score": i / 2, "step": step}) + "\n")
-    text = main([str(tmp_path), "--step", "2", "--min-score", "0.5", "--sort", "-score"])
+    text = main([str(tmp_path), "--step", "2", "--min-score", "0.5", "--sort", "score_desc"])
     assert "2 rollouts" in text and text.index("answer 2 step 2") < text.index("answer 1 step 2") and "step 1" not in text
     assert "1 rollouts" in main([str(tmp_path / "1.jsonl"), "--grep", "answer 0"])

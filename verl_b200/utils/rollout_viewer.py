@@ -4,7 +4,7 @@ The trainer writes one ``<step>.jsonl`` per step under ``trainer.rollout_data_di
 (fields ``input``, ``output``, ``score``, ``step``).
 
     python -m verl_b200.utils.rollout_viewer DIR_OR_FILE [--step N] [--grep TEXT] [--min-score X] [--max-score X]
-                                            [--sort score|-score|length] [--limit K] [--width 120]
+                                            [--sort score|score_desc|length] [--limit K] [--width 120]
 """
 
 from __future__ import annotations
@@ -39,8 +39,8 @@ def select(rows: Iterable[dict], grep: Optional[str] = None, min_score: Optional
            if (grep is None or grep in str(r.get("input", "")) or grep in str(r.get("output", "")))
            and (min_score is None or float(r.get("score", 0)) >= min_score)
            and (max_score is None or float(r.get("score", 0)) <= max_score)]
-    if sort in ("score", "-score"):
-        out.sort(key=lambda r: float(r.get("score", 0)), reverse=sort.startswith("-"))
+    if sort in ("score", "score_desc"):
+        out.sort(key=lambda r: float(r.get("score", 0)), reverse=sort == "score_desc")
     elif sort == "length":
         out.sort(key=lambda r: len(str(r.get("output", ""))))
     return out[:limit] if limit else out
@@ -66,7 +66,7 @@ def main(argv=None) -> str:
     ap.add_argument("--grep")
     ap.add_argument("--min-score", type=float)
     ap.add_argument("--max-score", type=float)
-    ap.add_argument("--sort", choices=["score", "-score", "length"])
+    ap.add_argument("--sort", choices=["score", "score_desc", "length"])
     ap.add_argument("--limit", type=int)
     ap.add_argument("--width", type=int, default=120)
     a = ap.parse_args(argv)
