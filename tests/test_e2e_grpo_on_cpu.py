@@ -97,3 +97,31 @@ def test_grpo_through_agent_loops(tmp_path, monkeypatch, spmd):
     for key in ("actor/pg_loss", "actor/grad_norm", "response_length/mean", "agent_loop/generate_sequences/mean"):
         assert key in m and math.isfinite(m[key]), key
     assert m["response_length/mean"] > 0 and m["actor/grad_norm"] > 0
+
+
+def test_task_runner_subclass_is_used(tmp_path, monkeypatch):
+    """``run_ppo(config, task_runner_class=...)``: a subclass can swap a worker class."""
+    from verl_b200.trainer.main_ppo import TaskRunner, run_ppo
+    from verl_b200.trainer.ppo.utils import Role
+    from verl_b200.workers.engine_workers import ActorRolloutRefWorker
+
+    seen = []
+
+    from verl_b200.single_controller.base.decorator import Dispatch, register
+
+    class MyWorker(ActorRolloutRefWorker):
+        @register(dispatch_mode=Dispatch.ONE_TO_ALL)  # an override is dispatched only if it is registered again
+        def init_model(self):
+            seen.append("init")
+            return super().init_model()
+
+    class MyRunner(TaskRunner):
+        def add_actor_rollout_worker(self, config):
+            super().add_actor_rollout_worker(config)
+            self.role_worker_mapping[Role.ActorRollout] = MyWorker
+
+    monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
+    cfg = compose("ppo_trainer", _overrides(tmp_path, ["trainer.n_gpus_per_node=1", "trainer.save_freq=-1",
+                                                       "trainer.total_training_steps=1", "data.max_response_length=8"]))
+    t = run_ppo(cfg, spmd=True, task_runner_class=MyRunner)
+    assert t.global_steps == 1 and seen == ["init"]

@@ -67,60 +67,103 @@ def build_tokenizer(config, model_config=None):
     return IntTokenizer(mc.vocab_size, eos_token_id=mc.eos_token_id if mc.eos_token_id is not None else 2)
 
 
-def run_ppo(config, spmd: Optional[bool] = None, trainer_cls=None, run_fit: bool = True):
-    from ..workers.engine_workers import ActorRolloutRefWorker, CriticWorker, RewardModelWorker
-    from .ppo.ray_trainer import RayPPOTrainer, ResourcePoolManager
-    from .ppo.reward import load_reward_manager
+class TaskRunner:
+    """Builds the role -> worker mapping, the resource pools, datasets and reward managers, then runs the trainer
+    (the extension point of verl/trainer/main_ppo.py:108-368: subclass it and override a step to plug in other
+    workers, pools or trainers; ``run_ppo(config, task_runner_class=...)`` uses the subclass)."""
 
-    if spmd is None:
-        spmd = int(os.environ.get("WORLD_SIZE", "1")) > 1 or os.environ.get("VERL_B200_SPMD") == "1"
-    use_ref, use_critic = need_reference_policy(config), need_critic(config)
-    validate_config(config, use_reference_policy=use_ref, use_critic=use_critic)
-    tokenizer = build_tokenizer(config)
-    mapping = {Role.ActorRollout: ActorRolloutRefWorker}
-    pool_id = "global_pool"
-    role_pool = {Role.ActorRollout: pool_id}
-    if use_critic:
-        mapping[Role.Critic] = CriticWorker
-        role_pool[Role.Critic] = pool_id
-    if config.reward_model.get("enable", False):
-        mapping[Role.RewardModel] = RewardModelWorker
-        role_pool[Role.RewardModel] = pool_id
-    device = config.trainer.get("device", "cuda")
-    n_gpus = [config.trainer.n_gpus_per_node] * config.trainer.nnodes
-    if spmd:
-        from ..single_controller.spmd import SPMDResourcePool, SPMDWorkerGroup
+    trainer_cls = None  # default: RayPPOTrainer
 
-        rpm = ResourcePoolManager({pool_id: [1]}, role_pool, pool_cls=SPMDResourcePool, use_gpu=device == "cuda")
-        wg_cls = SPMDWorkerGroup
-    else:
+    def __init__(self):
+        self.role_worker_mapping: dict = {}
+        self.mapping: dict = {}  # role -> resource pool id
+        self.pool_id = "global_pool"
+
+    # ---------------------------------------------------------------- workers
+    def add_actor_rollout_worker(self, config):
+        from ..workers.engine_workers import ActorRolloutRefWorker
+
+        self.role_worker_mapping[Role.ActorRollout] = ActorRolloutRefWorker
+        self.mapping[Role.ActorRollout] = self.pool_id
+        return ActorRolloutRefWorker
+
+    def add_critic_worker(self, config):
+        from ..workers.engine_workers import CriticWorker
+
+        if need_critic(config):
+            self.role_worker_mapping[Role.Critic] = CriticWorker
+            self.mapping[Role.Critic] = self.pool_id
+
+    def add_reward_model_worker(self, config):
+        from ..workers.engine_workers import RewardModelWorker
+
+        if config.reward_model.get("enable", False):
+            self.role_worker_mapping[Role.RewardModel] = RewardModelWorker
+            self.mapping[Role.RewardModel] = self.pool_id
+
+    def add_ref_policy_worker(self, config, ref_policy_cls=None):
+        """The reference policy lives inside the actor worker (``actor_rollout_ref``) unless a class is given."""
+        if ref_policy_cls is not None and need_reference_policy(config):
+            self.role_worker_mapping[Role.RefPolicy] = ref_policy_cls
+            self.mapping[Role.RefPolicy] = self.pool_id
+
+    def init_resource_pool_mgr(self, config, spmd: bool):
+        from .ppo.ray_trainer import ResourcePoolManager
+
+        device = config.trainer.get("device", "cuda")
+        if spmd:
+            from ..single_controller.spmd import SPMDResourcePool, SPMDWorkerGroup
+
+            return (ResourcePoolManager({self.pool_id: [1]}, self.mapping, pool_cls=SPMDResourcePool, use_gpu=device == "cuda"),
+                    SPMDWorkerGroup)
         from ..single_controller.mp import MPWorkerGroup
 
-        rpm = ResourcePoolManager({pool_id: n_gpus}, role_pool, use_gpu=device == "cuda")
-        wg_cls = MPWorkerGroup
-    reward_fn = load_reward_manager(config, tokenizer, num_examine=0)
-    val_reward_fn = load_reward_manager(config, tokenizer, num_examine=1)
-    train_ds = create_rl_dataset(config.data.train_files, config.data, tokenizer, is_train=True,
-                                 max_samples=config.data.get("train_max_samples", -1))
-    val_ds = None
-    if config.data.get("val_files"):
+        n_gpus = [config.trainer.n_gpus_per_node] * config.trainer.nnodes
+        return ResourcePoolManager({self.pool_id: n_gpus}, self.mapping, use_gpu=device == "cuda"), MPWorkerGroup
+
+    # -------------------------------------------------------------------- run
+    def run(self, config, spmd: Optional[bool] = None, trainer_cls=None, run_fit: bool = True):
+        from .ppo.ray_trainer import RayPPOTrainer
+        from .ppo.reward import load_reward_manager
+
+        if spmd is None:
+            spmd = int(os.environ.get("WORLD_SIZE", "1")) > 1 or os.environ.get("VERL_B200_SPMD") == "1"
+        use_ref, use_critic = need_reference_policy(config), need_critic(config)
+        validate_config(config, use_reference_policy=use_ref, use_critic=use_critic)
+        tokenizer = build_tokenizer(config)
+        self.add_actor_rollout_worker(config)
+        self.add_critic_worker(config)
+        self.add_reward_model_worker(config)
+        self.add_ref_policy_worker(config)
+        rpm, wg_cls = self.init_resource_pool_mgr(config, spmd)
+        reward_fn = load_reward_manager(config, tokenizer, num_examine=0)
+        val_reward_fn = load_reward_manager(config, tokenizer, num_examine=1)
+        train_ds = create_rl_dataset(config.data.train_files, config.data, tokenizer, is_train=True,
+                                     max_samples=config.data.get("train_max_samples", -1))
+        val_ds = None
+        if config.data.get("val_files"):
+            try:
+                val_ds = create_rl_dataset(config.data.val_files, config.data, tokenizer, is_train=False,
+                                           max_samples=config.data.get("val_max_samples", -1))
+            except (FileNotFoundError, OSError):
+                val_ds = None
+        cls = trainer_cls or self.trainer_cls or RayPPOTrainer
+        trainer = cls(config=config, tokenizer=tokenizer, role_worker_mapping=self.role_worker_mapping,
+                      resource_pool_manager=rpm, ray_worker_group_cls=wg_cls, reward_fn=reward_fn, val_reward_fn=val_reward_fn,
+                      train_dataset=train_ds, val_dataset=val_ds, train_sampler=create_rl_sampler(config.data, train_ds),
+                      device_name=config.trainer.get("device", "cuda"))
+        trainer.init_workers()
+        if not run_fit:
+            return trainer  # the caller drives the steps (asynchronous pipelines) and calls trainer.shutdown()
         try:
-            val_ds = create_rl_dataset(config.data.val_files, config.data, tokenizer, is_train=False,
-                                       max_samples=config.data.get("val_max_samples", -1))
-        except (FileNotFoundError, OSError):
-            val_ds = None
-    trainer = (trainer_cls or RayPPOTrainer)(config=config, tokenizer=tokenizer, role_worker_mapping=mapping, resource_pool_manager=rpm,
-                            ray_worker_group_cls=wg_cls, reward_fn=reward_fn, val_reward_fn=val_reward_fn,
-                            train_dataset=train_ds, val_dataset=val_ds, train_sampler=create_rl_sampler(config.data, train_ds),
-                            device_name=device)
-    trainer.init_workers()
-    if not run_fit:
-        return trainer  # the caller drives the steps (asynchronous pipelines) and calls trainer.shutdown()
-    try:
-        trainer.fit()
-    finally:
-        trainer.shutdown()
-    return trainer
+            trainer.fit()
+        finally:
+            trainer.shutdown()
+        return trainer
+
+
+def run_ppo(config, spmd: Optional[bool] = None, trainer_cls=None, run_fit: bool = True, task_runner_class=None):
+    return (task_runner_class or TaskRunner)().run(config, spmd=spmd, trainer_cls=trainer_cls, run_fit=run_fit)
 
 
 def main(argv=None):
