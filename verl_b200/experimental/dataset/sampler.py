@@ -36,6 +36,7 @@ class DifficultyCurriculumSampler(AbstractCurriculumSampler):
         sc = (data_config.get("sampler") or {}) if hasattr(data_config, "get") else {}
         self.floor = float(sc.get("floor", 0.05))
         self.momentum = float(sc.get("momentum", 0.5))
+        self.chunk = max(1, int(sc.get("refresh_every", 256)))
         self.rng = np.random.default_rng(int(data_config.get("seed", 1) or 1) if hasattr(data_config, "get") else 1)
         self.p = np.full(self.n, 0.5)
 
@@ -43,9 +44,13 @@ class DifficultyCurriculumSampler(AbstractCurriculumSampler):
         return self.n
 
     def __iter__(self) -> Iterator[int]:
-        for _ in range(self.n):
+        left = self.n
+        while left > 0:  # weights are refreshed every ``chunk`` draws (one O(n) pass per chunk, not per sample)
+            k = min(left, self.chunk)
             w = self.p * (1 - self.p) + self.floor
-            yield int(self.rng.choice(self.n, p=w / w.sum()))
+            for i in self.rng.choice(self.n, size=k, p=w / w.sum()):
+                yield int(i)
+            left -= k
 
     def update(self, batch) -> None:
         idx = batch.non_tensor_batch.get("index")
