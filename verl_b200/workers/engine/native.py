@@ -73,6 +73,7 @@ class NativeEngine(BaseEngine):
         self.lora = dict(lora) if lora and int(lora.get("rank", 0) or 0) > 0 else None
         self._lora_params: list = []
         self._lora_opt = None
+        self._keep_cap: Optional[int] = None  # set to 0 after an out-of-memory error with kept activations
         self.engine_config = engine_config
         self.optimizer_config = optimizer_config
         self.value_head = value_head
@@ -268,6 +269,8 @@ class NativeEngine(BaseEngine):
         now, after a reserve for the backward's own temporaries. The answer may differ between ranks and between
         micro-batches; the sequence of collectives does not depend on it."""
         n_layers = len(self.model.layers)
+        if self._keep_cap is not None:
+            return min(n_layers, self._keep_cap)
         if not self.gradient_checkpointing:
             return n_layers
         policy = os.environ.get("VERL_B200_KEEP_ACTIVATION_LAYERS") or _cfg(self.engine_config, "keep_activation_layers", "auto")
@@ -304,10 +307,25 @@ class NativeEngine(BaseEngine):
 
         return tuple(one(t) if isinstance(t, torch.Tensor) else t for t in out) if isinstance(out, tuple) else one(out)
 
+    def _forward_hidden_rows_safe(self, batch: PackedBatch, rows: Optional[torch.Tensor]):
+        """:meth:`_forward_hidden_rows`; on a single GPU an out-of-memory error in a training forward (nothing of this
+        micro-batch has reached the gradient shard yet) switches the kept-activation policy off for the rest of the
+        run and repeats the forward with every layer recomputed. With several ranks a one-sided repeat would
+        desynchronise the collectives, so the error is raised."""
+        try:
+            return self._forward_hidden_rows(batch, rows)
+        except torch.cuda.OutOfMemoryError:
+            if not (torch.is_grad_enabled() and self.trainable and self.zero.world == 1 and self._keep_cap != 0):
+                raise
+            self._keep_cap = 0
+            print("[verl_b200] out of memory with kept activations: recomputing all layers from now on", flush=True)
+            torch.cuda.empty_cache()
+            return self._forward_hidden_rows(batch, rows)
+
     def forward_logprob(self, batch: PackedBatch, rows: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0):
         """Log-prob of ``labels[i]`` predicted at packed position ``rows[i]`` (+ entropy), both fp32."""
         m, z = self.model, self.zero
-        hidden, residual = self._forward_hidden_rows(batch, rows)
+        hidden, residual = self._forward_hidden_rows_safe(batch, rows)
 
         if self.sp_size > 1:
             labels = labels[self._sp_sel[0]]
@@ -319,7 +337,7 @@ class NativeEngine(BaseEngine):
 
     def forward_values(self, batch: PackedBatch, rows: torch.Tensor):
         m, z = self.model, self.zero
-        hidden, residual = self._forward_hidden_rows(batch, rows)
+        hidden, residual = self._forward_hidden_rows_safe(batch, rows)
         return self._sp_merge(unit_call(z, self._head_unit, lambda h, r: m.values(m.final_norm(h, r)), hidden, residual))
 
     def forward_logits(self, batch: PackedBatch, rows: Optional[torch.Tensor] = None):
