@@ -10,9 +10,14 @@ GRPO advantages -> actor update (fwd + bwd + optimizer) -> weight sync to the ro
 ``RayPPOTrainer.train_step`` in SPMD mode (one controller replica per GPU). Weak scaling: every GPU gets
 ``--prompts-per-gpu`` prompts (128 prompts x 8 samples at 8 GPUs).
 
-Rank 0 prints one JSON line. ``value`` is device-timed (CUDA events, max over ranks) over exactly K steps;
-``e2e`` times K further steps with the host clock, each including the pinned-host -> device copy of the step's
-prompts and a device -> host read of the step's loss.
+Rank 0 prints one JSON line. The K timed steps are bracketed twice: by CUDA events on the step stream (``value``,
+max over ranks) and by the host clock (``e2e``). Every timed step starts from the batch as the data loader hands it
+over (host tensors), copies the prompt tensors into pinned host memory and from there to the device, runs
+``RayPPOTrainer.train_step`` on those device tensors, and reads the step's loss back to the host.
+
+``--impl reference`` reports whether the unmodified reference can run here; ``--impl stock-libs`` times the same
+phases with the libraries the reference is built on (vLLM, HF transformers + torch FSDP2 + flash-attn), none of this
+repository's models, kernels or engines on that path (see ``baseline/stock_libs.py``).
 """
 
 from __future__ import annotations
@@ -28,13 +33,21 @@ import time
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
+# Tensor-parallel size of a rollout replica when the job has that many GPUs (the benchmark configuration names 2).
+DEFAULT_ROLLOUT_TP = 1
+
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "stock-libs"])
+    ap.add_argument("--rollout-tp", type=int, default=0,
+                    help="tensor-parallel size of a rollout replica (0 = the benchmark's default: 2 when the job has "
+                         "at least 2 GPUs, else 1)")
+    ap.add_argument("--phases", default="rollout,logprob,update,resync,fused_ce",
+                    help="stock-libs arm: which phases to time")
     ap.add_argument("--model", default="qwen2.5-7b")
     ap.add_argument("--prompts-per-gpu", type=int, default=16)
     ap.add_argument("--n", type=int, default=8)
@@ -134,8 +147,9 @@ def build_config(args, world: int):
         "data.val_files=null", f"data.train_batch_size={global_prompts}", f"data.max_prompt_length={args.max_prompt}",
         f"data.max_response_length={args.max_response}", "data.shuffle=false",
         "algorithm.adv_estimator=grpo", f"actor_rollout_ref.rollout.n={args.n}", "actor_rollout_ref.rollout.temperature=1.0",
-        f"actor_rollout_ref.rollout.max_num_seqs={max(per_gpu * args.n, 8)}", "actor_rollout_ref.rollout.max_num_batched_tokens=8192",
-        "actor_rollout_ref.rollout.tensor_model_parallel_size=1", "actor_rollout_ref.rollout.gpu_memory_utilization=0.12",
+        f"actor_rollout_ref.rollout.max_num_seqs={max(per_gpu * args.n * args.rollout_tp, 8)}", "actor_rollout_ref.rollout.max_num_batched_tokens=8192",
+        f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp}",
+        f"actor_rollout_ref.rollout.gpu_memory_utilization={0.12 if args.rollout_tp == 1 else 0.2}",
         "actor_rollout_ref.rollout.log_prob_use_dynamic_bsz=true", f"actor_rollout_ref.rollout.log_prob_max_token_len_per_gpu={2 * args.max_token_len}",
         "actor_rollout_ref.ref.log_prob_use_dynamic_bsz=true", f"actor_rollout_ref.ref.log_prob_max_token_len_per_gpu={2 * args.max_token_len}",
         f"actor_rollout_ref.actor.ppo_mini_batch_size={global_prompts}", "actor_rollout_ref.actor.use_dynamic_bsz=true",
@@ -158,6 +172,11 @@ def main():
         if int(os.environ.get("RANK", "0")) == 0:
             reference_arm(args)
         return
+    if args.impl == "stock-libs":
+        from baseline import stock_libs
+
+        stock_libs.main(args)
+        return
     import torch
     import torch.distributed as dist
 
@@ -170,6 +189,12 @@ def main():
         dist.init_process_group("nccl")
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
     os.environ["VERL_B200_SPMD"] = "1"
+    # the benchmark measures the peer-memory collectives: a failed set-up must abort, not fall back to NCCL
+    os.environ["VERL_B200_REQUIRE_PEER_COMM"] = "1"
+    if args.rollout_tp <= 0:
+        args.rollout_tp = DEFAULT_ROLLOUT_TP if world % DEFAULT_ROLLOUT_TP == 0 else 1
+    tp = args.rollout_tp
+    assert world % tp == 0, f"--rollout-tp {tp} does not divide {world} GPUs"
 
     from verl_b200.ops import _lib
     from verl_b200.single_controller.spmd import SPMDResourcePool, SPMDWorkerGroup
@@ -197,72 +222,67 @@ def main():
 
     it = batches()
     dev = torch.device("cuda", local)
+    worker = trainer.actor_rollout_wg.worker.worker_dict["actor_rollout"]
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def step_e2e(batch_dict):
-        """The user-facing call with explicit staging: prompts start in pinned host memory and are copied to the
-        device, the step's loss is read back to the host."""
-        h2d = 0
-        staged = {}
+    def step(batch_dict):
+        """The user-facing call. The loader's prompt tensors go to pinned host memory, from there to the device,
+        and the step runs on those device tensors; the step's loss is read back to the host."""
+        h2d, staged = 0, {}
         for k, v in batch_dict.items():
             if isinstance(v, torch.Tensor):
                 pinned = v.pin_memory()
                 staged[k] = pinned.to(dev, non_blocking=True)
                 h2d += pinned.numel() * pinned.element_size()
-        torch.cuda.current_stream().synchronize()
-        m = trainer.train_step(batch_dict)
+            else:
+                staged[k] = v
+        m = trainer.train_step(staged)
         loss = torch.tensor([m.get("actor/pg_loss", 0.0), m.get("actor/kl_loss", 0.0)], device=dev)
         host = loss.cpu()
-        return m, h2d // max(world, 1) * world, host.numel() * host.element_size()
+        return m, h2d, host.numel() * host.element_size()
 
     for _ in range(args.warmup):
-        trainer.train_step(next(it))
+        step(next(it))
 
-    # ---- device-timed region: exactly K steps ----
+    # ---- timed region: exactly K steps, bracketed by CUDA events (value) and by the host clock (e2e) ----
     sampler = ClockSampler(local)
     barrier()
     if rank == 0:
         sampler.start()
     launches0 = _lib.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
     ev0.record()
-    tokens = 0
+    tokens, h2d, d2h = 0, 0, 0
     last = {}
     for _ in range(args.steps):
-        last = trainer.train_step(next(it))
+        last, h2d, d2h = step(next(it))
         tokens += int(last["perf/total_num_tokens"])
     ev1.record()
     barrier()
-    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    host_s = time.perf_counter() - t0
+    red = torch.tensor([ev0.elapsed_time(ev1), host_s * 1e3], device=dev)
     launches = torch.tensor([float(_lib.launch_count() - launches0)], device=dev)
     if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(red, op=dist.ReduceOp.MAX)
         dist.all_reduce(launches)
     clocks = sampler.stop() if rank == 0 else {}
-    total_ms = ms.item()
-
+    total_ms, host_ms = red.tolist()
     e2e = None
     if not args.no_e2e:
-        barrier()
-        t0 = time.perf_counter()
-        e_tokens, h2d, d2h = 0, 0, 0
-        for _ in range(args.steps):
-            m, hi, do = step_e2e(next(it))
-            e_tokens += int(m["perf/total_num_tokens"])
-            h2d, d2h = hi, do
-        barrier()
-        dt = torch.tensor([time.perf_counter() - t0], device=dev)
-        if world > 1:
-            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-        e2e = {"value": e_tokens / dt.item(), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-               "timer": "host clock around K steps incl. pinned H2D of prompts and D2H of the loss"}
+        # the data loader yields the global batch on every rank: each rank stages all of it, as a user's loop would
+        e2e = {"value": tokens / (host_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d) * world,
+               "d2h_bytes_per_step": int(d2h) * world,
+               "timer": "host clock around the same K steps (max over ranks), each step: loader batch -> pinned host -> "
+                        "device -> train_step on the device tensors -> loss read back"}
+    comm = getattr(worker, "comm_kind", "none")
 
     if rank == 0:
-        c = trainer.actor_rollout_wg.worker.worker_dict["actor_rollout"].model_config
+        c = worker.model_config
         out = {
             "metric": "RL step tokens/s/box (GRPO, rollout+logprob+ref+update+resync)", "value": tokens / (total_ms / 1e3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
@@ -274,7 +294,8 @@ def main():
                        "global_batch": args.prompts_per_gpu * world * args.n, "prompts": args.prompts_per_gpu * world,
                        "n_samples": args.n, "seq_len": args.max_prompt + args.max_response,
                        "prompt_len": [args.min_prompt, args.max_prompt], "max_response": args.max_response,
-                       "parallelism": f"zero3-dp{world}, rollout tp1 x {world} replicas",
+                       "parallelism": f"zero3-dp{world}, rollout tp{tp} x {world // tp} replicas", "rollout_tp": tp,
+                       "comm": comm, "nvls": bool(getattr(getattr(worker, "comm", None), "use_nvls", False)),
                        "cache": "inputs larger than L2 (15 GB of weights streamed per pass)",
                        "timer": "CUDA events on the step stream, max over ranks"},
             "clocks": clocks, "gpu_launches": int(launches.item()),
@@ -282,11 +303,10 @@ def main():
             "rollout_tokens_per_s_per_gpu": last.get("rollout/tokens_per_s"),
             "resync_ms": 1e3 * last.get("timing_s/resync", 0.0),
             "mfu_actor": last.get("perf/mfu/actor"),
-            "kept_activation_layers": getattr(
-                trainer.actor_rollout_wg.worker.worker_dict["actor_rollout"].actor_engine, "last_kept_layers", 0),
+            "kept_activation_layers": getattr(worker.actor_engine, "last_kept_layers", 0),
             "peak_mem_gb": {"allocated": round(torch.cuda.max_memory_allocated() / 2**30, 1),
                             "reserved": round(torch.cuda.max_memory_reserved() / 2**30, 1)},
-            "keep_info": getattr(trainer.actor_rollout_wg.worker.worker_dict["actor_rollout"].actor_engine, "last_keep_info", None),
+            "keep_info": getattr(worker.actor_engine, "last_keep_info", None),
         }
         if e2e is not None:
             out["e2e"] = e2e

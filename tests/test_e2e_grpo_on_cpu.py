@@ -125,3 +125,39 @@ def test_task_runner_subclass_is_used(tmp_path, monkeypatch):
                                                        "trainer.total_training_steps=1", "data.max_response_length=8"]))
     t = run_ppo(cfg, spmd=True, task_runner_class=MyRunner)
     assert t.global_steps == 1 and seen == ["init"]
+
+
+def test_dynamic_sampling_accumulates_over_generation_batches(tmp_path, monkeypatch):
+    """algorithm.filter_groups: when a generation batch keeps only half of its prompt groups, the step trains after a
+    second generation batch; the loader advances by one batch per generation batch (no rewinding) and the limit on
+    generation batches raises."""
+    import json
+
+    from verl_b200.trainer.main_ppo import run_ppo
+    from verl_b200.trainer.ppo.ray_trainer import RayPPOTrainer
+
+    monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
+    seen_prompts = []
+
+    def keep_half(self, batch, metric_name):
+        uids = list(dict.fromkeys(batch.non_tensor_batch["uid"]))
+        seen_prompts.append(batch.batch["prompts"][:: int(self.config.actor_rollout_ref.rollout.n)].clone())
+        keep = set(uids[: len(uids) // 2])
+        return batch[[i for i, u in enumerate(batch.non_tensor_batch["uid"]) if u in keep]]
+
+    monkeypatch.setattr(RayPPOTrainer, "_filter_groups", keep_half)
+    extra = ["trainer.n_gpus_per_node=1", "trainer.save_freq=-1", "trainer.experiment_name=dyn",
+             "+algorithm.filter_groups.enable=true", "+algorithm.filter_groups.metric=seq_reward",
+             "+algorithm.filter_groups.max_num_gen_batches=0", "trainer.balance_batch=false"]
+    t = run_ppo(compose("ppo_trainer", _overrides(tmp_path, extra)), spmd=True)
+    assert t.global_steps == 2
+    assert len(seen_prompts) == 4  # two generation batches per training step
+    for a in range(4):
+        for b in range(a + 1, 4):
+            assert not (seen_prompts[a] == seen_prompts[b]).all(), "a generation batch reused earlier prompts"
+    rows = [json.loads(l)["data"] for l in open(tmp_path / "logs" / "cpu_e2e" / "dyn.jsonl")]
+    assert len(rows) == 2 and all(r["train/num_gen_batches"] == 2 for r in rows)
+    extra[-2] = "+algorithm.filter_groups.max_num_gen_batches=1"
+    extra[2] = "trainer.experiment_name=dyn_limit"
+    with pytest.raises(ValueError, match="dynamic sampling"):
+        run_ppo(compose("ppo_trainer", _overrides(tmp_path, extra)), spmd=True)

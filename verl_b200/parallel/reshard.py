@@ -63,8 +63,6 @@ def tp_slices(cfg: ModelConfig, name: str, shape: tuple, tp_rank: int, tp_size: 
         assert cols % tp_size == 0
         k = cols // tp_size
         return [(0, rows)], (tp_rank * k, (tp_rank + 1) * k)
-    if leaf in ("embed_tokens.weight", "lm_head.weight") and shape[0] % tp_size == 0 and False:
-        return [part(0, shape[0])], None  # vocab-parallel embeddings are not used by the native runner
     return [(0, rows)], None
 
 

@@ -2,8 +2,7 @@
 
 Ray is not a dependency of this framework: the multiprocess backend implements the same
 contract, and these names resolve to it so code written against ``verl.single_controller.ray``
-runs unchanged on one box. When ``ray`` is importable, :mod:`.ray_backend` offers actor-based
-equivalents for multi-node placement.
+runs unchanged on one box (one NVSwitch domain is the whole machine; there is no Ray actor back end).
 """
 
 from ..mp.worker_group import MPClassWithInitArgs as RayClassWithInitArgs

@@ -581,40 +581,59 @@ class RayPPOTrainer:
         return batch
 
     def train_step(self, batch_dict: dict) -> dict:
-        """One RL step on one (global, or per-rank in SPMD mode) batch of prompts. Returns the step's metrics."""
-        cfg = self.config
+        """One RL step on one (global, or per-rank in SPMD mode) batch of prompts. Returns the step's metrics.
+
+        With dynamic sampling (``algorithm.filter_groups``) a batch whose kept groups do not fill the train batch is
+        held back and the call returns ``{"train/accumulating": 1.0, ...}`` without training and without advancing
+        ``global_steps``; the following calls add their kept groups until the batch is full
+        (verl/recipe dapo_ray_trainer: ``continue`` in the batch loop)."""
         metrics: dict = {}
         timing_raw: dict = {}
         self.global_steps += 1
         with marked_timer("step", timing_raw):
             batch = self._rollout_and_reward(batch_dict, timing_raw, metrics)
+            batch = self._dynamic_sampling(batch, metrics)
+            if batch is None:
+                self.global_steps -= 1
+                metrics["train/accumulating"] = 1.0
+                return metrics
             self._train_on_batch(batch, timing_raw, metrics)
         return self._finish_step(timing_raw, metrics)
 
+    def _dynamic_sampling(self, batch: DataProto, metrics: dict) -> Optional[DataProto]:
+        """DAPO dynamic sampling: keep the prompt groups whose metric varies, accumulate them over generation batches
+        until ``train_batch_size`` prompts are there. Returns the batch to train on, or None while accumulating.
+        Raises once ``max_num_gen_batches`` generation batches were not enough."""
+        cfg = self.config
+        fg = cfg.algorithm.get("filter_groups") or {}
+        if not fg.get("enable", False):
+            return batch
+        n = int(cfg.actor_rollout_ref.rollout.n)
+        want = (len(batch) // n) * n
+        batch.batch["token_level_rewards"] = batch.batch["token_level_scores"]
+        kept = self._filter_groups(batch, fg.get("metric") or "seq_reward")
+        pending = getattr(self, "_fg_pending", None)
+        if pending is not None and len(pending):
+            kept = DataProto.concat([pending, kept])
+        self._fg_tries = getattr(self, "_fg_tries", 0) + 1
+        metrics["train/num_gen_batches"] = self._fg_tries
+        if len(kept) < want:
+            max_tries = int(fg.get("max_num_gen_batches", 0) or 0)
+            if max_tries > 0 and self._fg_tries >= max_tries:
+                self._fg_pending, self._fg_tries = None, 0
+                raise ValueError(f"dynamic sampling: {max_tries} generation batches gave {len(kept) // n} of "
+                                 f"{want // n} prompt groups with a varying {fg.get('metric') or 'seq_reward'}; "
+                                 "the data is too easy or too hard, or raise algorithm.filter_groups.max_num_gen_batches")
+            self._fg_pending = kept
+            return None
+        self._fg_pending, self._fg_tries = None, 0
+        return kept[:want]
+
     def _train_on_batch(self, batch: DataProto, timing_raw: dict, metrics: dict) -> None:
-        """Everything after rollout + reward: filtering, log-probs, advantages, critic / actor update, weight sync.
-        Split out so that asynchronous trainers can feed batches produced elsewhere."""
+        """Everything after rollout + reward (+ dynamic sampling): log-probs, advantages, critic / actor update, weight
+        sync. Split out so that asynchronous trainers can feed batches produced elsewhere."""
         cfg = self.config
         if True:
-            fg = cfg.algorithm.get("filter_groups") or {}
-            if fg.get("enable", False):
-                batch.batch["token_level_rewards"] = batch.batch["token_level_scores"]
-                kept = self._filter_groups(batch, fg.get("metric") or "seq_reward")
-                tries, n = 1, int(cfg.actor_rollout_ref.rollout.n)
-                want = (len(batch) // n) * n
-                max_tries = int(fg.get("max_num_gen_batches", 0) or 0)
-                it = iter(self.train_dataloader)
-                while len(kept) < want and (max_tries <= 0 or tries < max_tries):
-                    try:
-                        more = self._rollout_and_reward(next(it), timing_raw, metrics)
-                    except StopIteration:
-                        break
-                    more.batch["token_level_rewards"] = more.batch["token_level_scores"]
-                    kept = DataProto.concat([kept, self._filter_groups(more, fg.get("metric") or "seq_reward")])
-                    tries += 1
-                metrics["train/num_gen_batches"] = tries
-                if len(kept) >= n:
-                    batch = kept[: min(len(kept), want)]
             if cfg.trainer.get("balance_batch", True):
                 self._balance_batch(batch, metrics)
             batch.meta_info["global_token_num"] = torch.sum(batch.batch["attention_mask"], dim=-1).tolist()
@@ -740,6 +759,8 @@ class RayPPOTrainer:
                 metrics = self.train_step(batch_dict)
                 if do_prof:
                     self.actor_rollout_wg.stop_profile()
+                if metrics.get("train/accumulating"):
+                    continue  # dynamic sampling wants another generation batch before this step can train
                 is_last = self.global_steps >= self.total_training_steps
                 if self.val_reward_fn is not None and tr.test_freq > 0 and (is_last or self.global_steps % tr.test_freq == 0):
                     last_val = self._validate()

@@ -6,13 +6,16 @@ docs/advance/checkpoint.rst:20-62):
     <dir>/model_world_size_{W}_rank_{r}.pt        this rank's parameter shard
     <dir>/optim_world_size_{W}_rank_{r}.pt        this rank's optimizer shard (fp32 master + Adam moments)
     <dir>/extra_state_world_size_{W}_rank_{r}.pt  lr-scheduler step + RNG state
-    <dir>/fsdp_config.json                        {"FSDP_version": 2, "world_size": W}
+    <dir>/fsdp_config.json                        {"FSDP_version": 2, "world_size": W, "shard_format": ...}
     <dir>/huggingface/                            config.json (always) + safetensors when "hf_model" is saved
 
 The reference stores ``DTensor`` shards produced by torch FSDP. This engine shards flat per-layer vectors
-instead, so the model file holds, per parameter, the slice of the flattened tensor this rank owns together
-with (global shape, start offset, length); :func:`merge_sharded_checkpoint` re-assembles full tensors from
-the W files (the job of ``python -m verl.model_merger merge --backend fsdp``).
+instead, so by default the model file holds, per parameter, the slice of the flattened tensor this rank owns
+together with (global shape, start offset, length) and ``shard_format`` names that layout;
+:func:`merge_sharded_checkpoint` re-assembles full tensors from the W files (the job of
+``python -m verl.model_merger merge --backend fsdp``). Both directions of interchange with the reference go
+through :mod:`.reference_fsdp`: directories written by torch FSDP load and merge here, and the save content
+``"fsdp_model"`` (instead of ``"model"``) writes torch-FSDP-style DTensor shard files.
 """
 
 from __future__ import annotations
@@ -27,6 +30,8 @@ import torch
 import torch.distributed as dist
 
 from ...models.hf_io import save_hf_checkpoint
+
+FLAT_SHARD_FORMAT = "verl_b200.flat_shard.v1"
 
 
 def _rng_state() -> dict:
@@ -69,12 +74,17 @@ def save_engine_checkpoint(engine, local_path: str, global_step: int = 0,
     if dist.is_initialized():
         dist.barrier()
     W, r = z.world, z.rank
-    if "model" in save_contents:
+    if "fsdp_model" in save_contents:
+        # torch-FSDP shard files (HF names, dim-0 DTensor shards): what the reference's loader and merger read
+        from .reference_fsdp import save_reference_fsdp_shards
+
+        save_reference_fsdp_shards(engine, path)
+    elif "model" in save_contents:
         src = z.master if z.trainable else z.shard16
-        torch.save({"format": "verl_b200.flat_shard.v1", "world_size": W, "rank": r, "params": _param_slices(z, src)},
+        torch.save({"format": FLAT_SHARD_FORMAT, "world_size": W, "rank": r, "params": _param_slices(z, src)},
                    path / f"model_world_size_{W}_rank_{r}.pt")
     if "optimizer" in save_contents and z.trainable:
-        torch.save({"format": "verl_b200.flat_shard.v1", "world_size": W, "rank": r, "step": engine.step_count,
+        torch.save({"format": FLAT_SHARD_FORMAT, "world_size": W, "rank": r, "step": engine.step_count,
                     "exp_avg": _param_slices(z, z.exp_avg), "exp_avg_sq": _param_slices(z, z.exp_avg_sq)},
                    path / f"optim_world_size_{W}_rank_{r}.pt")
     if "extra" in save_contents:
@@ -90,7 +100,8 @@ def save_engine_checkpoint(engine, local_path: str, global_step: int = 0,
         torch.save({"lora": lora_state_dict(engine.model), "optimizer": engine._lora_opt.state_dict(),
                     "step": engine.step_count}, path / "lora_train_state.pt")
     if r == 0:
-        (path / "fsdp_config.json").write_text(json.dumps({"FSDP_version": 2, "world_size": W}, indent=4))
+        fmt = "torch.fsdp.dtensor" if "fsdp_model" in save_contents else FLAT_SHARD_FORMAT
+        (path / "fsdp_config.json").write_text(json.dumps({"FSDP_version": 2, "world_size": W, "shard_format": fmt}, indent=4))
         hf_dir = path / "huggingface"
         hf_dir.mkdir(exist_ok=True)
         engine.model_config.save_pretrained(hf_dir)
@@ -124,23 +135,29 @@ def load_engine_checkpoint(engine, local_path: str, load_contents=("model", "opt
     W, r = z.world, z.rank
     mfile = path / f"model_world_size_{W}_rank_{r}.pt"
     if "model" in load_contents:
-        if mfile.exists():
-            st = torch.load(mfile, map_location="cpu", weights_only=False)
-            assert st["world_size"] == W
+        st = torch.load(mfile, map_location="cpu", weights_only=False) if mfile.exists() else None
+        if isinstance(st, dict) and st.get("format") == FLAT_SHARD_FORMAT and st["world_size"] == W:
             if z.trainable:
                 _restore(z, z.master, st["params"])
                 z.shard16.copy_(z.master.to(z.shard16.dtype))
             else:
                 _restore(z, z.shard16, st["params"])
-        else:  # a different world size (or an HF export): rebuild from full tensors
-            full = merge_sharded_checkpoint(path)
-            z.load_full_state(full)
+        else:
+            # another world size, or shard files written by torch FSDP (the reference's DTensor / ShardedTensor state
+            # dicts): rebuild full tensors from all files of the directory and re-shard them
+            z.load_full_state(merge_sharded_checkpoint(path, engine.model_config))
     ofile = path / f"optim_world_size_{W}_rank_{r}.pt"
-    if "optimizer" in load_contents and z.trainable and ofile.exists():
-        st = torch.load(ofile, map_location="cpu", weights_only=False)
-        _restore(z, z.exp_avg, st["exp_avg"])
-        _restore(z, z.exp_avg_sq, st["exp_avg_sq"])
-        engine.step_count = int(st.get("step", 0))
+    if "optimizer" in load_contents and z.trainable:
+        st = torch.load(ofile, map_location="cpu", weights_only=False) if ofile.exists() else None
+        if isinstance(st, dict) and st.get("format") == FLAT_SHARD_FORMAT:
+            _restore(z, z.exp_avg, st["exp_avg"])
+            _restore(z, z.exp_avg_sq, st["exp_avg_sq"])
+            engine.step_count = int(st.get("step", 0))
+        elif r == 0:
+            why = ("was written by another engine" if st is not None else
+                   f"is absent (the checkpoint has another world size than {W}, or was saved without the optimizer)")
+            print(f"[verl_b200] WARNING: {ofile.name} {why}: Adam moments restart from zero, "
+                  "the parameters and the learning-rate schedule are restored")
     lfile = path / "lora_train_state.pt"
     if getattr(engine, "_lora_params", None) and lfile.exists():
         from ...models.lora import load_lora_state_dict
@@ -159,14 +176,22 @@ def load_engine_checkpoint(engine, local_path: str, load_contents=("model", "opt
         _load_rng_state(st["rng"])
 
 
-def merge_sharded_checkpoint(local_path: str | Path) -> dict:
-    """Re-assemble full (native-named) tensors from all ``model_world_size_*_rank_*.pt`` files of a directory."""
+def merge_sharded_checkpoint(local_path: str | Path, model_config=None) -> dict:
+    """Re-assemble full (native-named) tensors from all ``model_world_size_*_rank_*.pt`` files of a directory: this
+    engine's flat shards, or the per-parameter DTensor / ShardedTensor shards torch FSDP writes in the reference
+    (those need ``model_config``, or the ``huggingface/config.json`` of the directory, for the name mapping)."""
     path = Path(local_path)
     cfg = json.loads((path / "fsdp_config.json").read_text())
     W = int(cfg["world_size"])
+    first = torch.load(path / f"model_world_size_{W}_rank_0.pt", map_location="cpu", weights_only=False)
+    if not (isinstance(first, dict) and first.get("format") == FLAT_SHARD_FORMAT):
+        from .reference_fsdp import load_reference_fsdp_shards
+
+        return load_reference_fsdp_shards(path, model_config)
     full: dict = {}
     for r in range(W):
-        st = torch.load(path / f"model_world_size_{W}_rank_{r}.pt", map_location="cpu", weights_only=False)
+        st = first if r == 0 else torch.load(path / f"model_world_size_{W}_rank_{r}.pt", map_location="cpu",
+                                             weights_only=False)
         for name, ent in st["params"].items():
             n = int(np.prod(ent["shape"])) if len(ent["shape"]) else 1
             if name not in full:

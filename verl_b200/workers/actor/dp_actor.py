@@ -92,6 +92,8 @@ class DataParallelPPOActor:
         t = torch.tensor([float(mask.sum()), float((mask.sum(-1) > 0).sum())], dtype=torch.float64, device=self.device)
         if self.engine.world > 1:
             dist.all_reduce(t, group=self.engine.group)
+            # the ranks of a sequence-parallel group hold the same samples: count each sample once
+            t = t / max(int(getattr(self.engine, "sp_size", 1) or 1), 1)
         return max(t[0].item(), 1.0), max(t[1].item(), 1.0)
 
     def update_policy(self, data: DataProto) -> dict:
@@ -127,13 +129,17 @@ class DataParallelPPOActor:
                     old = log_prob.detach() if on_policy else b["old_log_probs"].to(self.device)
                     ref = b["ref_log_prob"].to(self.device) if use_kl else None
                     isw = b["rollout_is_weights"].to(self.device) if "rollout_is_weights" in b else None
-                    fused_ok = (self.use_fused_loss and loss_mode == "vanilla" and cfg.loss_agg_mode == "token-mean")
+                    # the fused kernel differentiates every KL estimator itself; the "+" variants (estimator's value,
+                    # gradient of k2: core_algos.kl_penalty) take the composed path
+                    kl_plus = use_kl and str(cfg.kl_loss_type).endswith("+")
+                    fused_ok = (self.use_fused_loss and loss_mode == "vanilla" and cfg.loss_agg_mode == "token-mean"
+                                and not kl_plus)
                     if fused_ok:
                         loss, sums = ops.ppo_loss_fused(
                             log_prob, old, adv, mask, entropy=entropy, ref_logp=ref, is_weight=isw,
                             clip_low=_cfg(cfg, "clip_ratio_low", cfg.clip_ratio), clip_high=_cfg(cfg, "clip_ratio_high", cfg.clip_ratio),
                             clip_c=_cfg(cfg, "clip_ratio_c", 3.0), kl_coef=float(cfg.kl_loss_coef) if use_kl else 0.0,
-                            kl_type=cfg.kl_loss_type.rstrip("+"), entropy_coeff=entropy_coeff, denom=n_tok)
+                            kl_type=cfg.kl_loss_type, entropy_coeff=entropy_coeff, denom=n_tok)
                         loss.backward()
                         s = sums.tolist()
                         n_local = max(s[6], 1.0)

@@ -84,14 +84,19 @@ class _WorkerBase(Worker):
             self.device = torch.device("cpu")
 
     def _norm_batch(self, cfg, mini_key="ppo_mini_batch_size", micro_key="ppo_micro_batch_size", n: int = 1):
-        """YAML batch sizes are global prompt counts; workers use per-rank sample counts
+        """YAML batch sizes are global prompt counts; workers use per-rank sample counts. The ranks of a
+        sequence-parallel group share their samples, so the divisor is the data-parallel size ``world // sp``
         (verl/workers/fsdp_workers.py:239-273)."""
-        mini = int(getattr(cfg, mini_key)) * n // self.world
-        assert mini > 0, f"{mini_key} {getattr(cfg, mini_key)} * n {n} must be >= world size {self.world}"
+        eng_cfg = _cfg(cfg, "fsdp_config", None) or _cfg(_cfg(cfg, "model", None), "fsdp_config", None)
+        sp = int(_cfg(eng_cfg, "ulysses_sequence_parallel_size", 1) or 1) if eng_cfg is not None else 1
+        sp = int(_cfg(cfg, "ulysses_sequence_parallel_size", sp) or sp)
+        dp = max(self.world // max(sp, 1), 1)
+        mini = int(getattr(cfg, mini_key)) * n // dp
+        assert mini > 0, f"{mini_key} {getattr(cfg, mini_key)} * n {n} must be >= data-parallel size {dp}"
         object.__setattr__(cfg, mini_key, mini)
         micro = getattr(cfg, micro_key, None)
         if micro is not None:
-            per = max(int(micro) // self.world, 1)
+            per = max(int(micro) // dp, 1)
             object.__setattr__(cfg, micro_key + "_per_gpu", per)
         per_gpu = getattr(cfg, micro_key + "_per_gpu", None)
         if per_gpu is not None and not getattr(cfg, "use_dynamic_bsz", False):
@@ -164,16 +169,25 @@ class ActorRolloutRefWorker(_WorkerBase):
             torch.cuda.empty_cache()
 
     def _make_comm(self):
-        if self.device.type != "cuda" or self.world <= 1 or os.environ.get("VERL_B200_DISABLE_PEER_COMM"):
+        """Peer-memory communicator of the whole job (``comm_kind`` records which collective path runs: "peer", "nccl"
+        or "none"). With ``VERL_B200_REQUIRE_PEER_COMM=1`` a failed set-up raises instead of falling back to NCCL."""
+        self.comm, self.comm_kind = None, "none"
+        if self.world <= 1:
+            return None
+        self.comm_kind = "nccl" if self.device.type == "cuda" else "gloo"
+        if self.device.type != "cuda" or os.environ.get("VERL_B200_DISABLE_PEER_COMM"):
             return None
         try:
             from ..parallel.peer_comm import PeerComm
 
-            return PeerComm(dist.group.WORLD)
+            self.comm = PeerComm(dist.group.WORLD)
+            self.comm_kind = "peer"
         except Exception as e:  # peer memory not available: plain NCCL collectives
+            if os.environ.get("VERL_B200_REQUIRE_PEER_COMM") == "1":
+                raise RuntimeError(f"peer-memory collectives are required but could not be set up: {e}") from e
             if self.dp_rank == 0:
                 print(f"[verl_b200] peer-memory collectives unavailable ({type(e).__name__}: {e}); using NCCL")
-            return None
+        return self.comm
 
     def _build_rollout(self, model_cfg: ModelConfig, state, seed: int):
         from ..rollout import NativeRolloutEngine
