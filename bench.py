@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--rollout-tp", type=int, default=0,
                     help="tensor-parallel size of a rollout replica (0 = the benchmark's default: 2 when the job has "
                          "at least 2 GPUs, else 1)")
+    ap.add_argument("--breakdown", default="",
+                    help="after the timed steps, run update_actor and compute_log_prob once more under the torch "
+                         "profiler and write the per-kernel device-time shares to this JSON file (rank 0)")
     ap.add_argument("--phases", default="rollout,logprob,update,resync,fused_ce",
                     help="stock-libs arm: which phases to time")
     ap.add_argument("--model", default="qwen2.5-7b")
@@ -311,6 +314,16 @@ def main():
         if e2e is not None:
             out["e2e"] = e2e
         print(json.dumps(out))
+    if args.breakdown:
+        from verl_b200.utils.profiler.kernel_breakdown import kernel_breakdown
+
+        b = trainer._last_batch
+        res = {"n_gpus": world, "note": "device times under the torch profiler: shares only"}
+        res["update_actor"] = kernel_breakdown(lambda: trainer.actor_rollout_wg.update_actor(b))
+        res["compute_log_prob"] = kernel_breakdown(lambda: trainer.actor_rollout_wg.compute_log_prob(b))
+        if rank == 0:
+            with open(args.breakdown, "w") as f:
+                json.dump(res, f, indent=1)
     if world > 1:
         dist.destroy_process_group()
 

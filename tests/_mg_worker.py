@@ -87,7 +87,7 @@ def check_zero_step(rank, world, dev, comm):
         __getattr__ = dict.get
 
     cfg = preset("tiny-qwen2")
-    optim = C(lr=1e-2, weight_decay=0.01, betas=(0.9, 0.95), clip_grad=1.0, lr_warmup_steps=0, total_training_steps=10)
+    optim = C(lr=1e-3, weight_decay=0.01, betas=(0.9, 0.95), clip_grad=1.0, lr_warmup_steps=0, total_training_steps=10)
     outs = []
     # third variant: every layer keeps its activations (no recomputation), over the peer-memory collectives
     for use_comm, keep in ((True, "0"), (False, "0"), (True, str(cfg.num_hidden_layers))):
@@ -104,13 +104,17 @@ def check_zero_step(rank, world, dev, comm):
             lp, ent = eng.forward_logprob(batch, rows, labels, 1.0)
             (-lp.mean()).backward()
             gn = eng.optimizer_step()
-        outs.append((float(gn), eng.zero.shard16.clone().float(), float(lp.mean())))
+        outs.append((float(gn), eng.zero.master.clone().float(), float(lp.mean())))
     (gn_a, w_a, l_a), (gn_b, w_b, l_b), (gn_c, w_c, l_c) = outs
     assert abs(l_a - l_c) < 1e-5 and abs(gn_a - gn_c) <= 1e-4 * max(1.0, abs(gn_a)), (l_a, l_c, gn_a, gn_c)
     torch.testing.assert_close(w_a, w_c, atol=1e-3, rtol=1e-3)
     assert abs(l_a - l_b) < 1e-3, (l_a, l_b)
     assert abs(gn_a - gn_b) <= 2e-3 * max(1.0, abs(gn_b)), (gn_a, gn_b)
-    torch.testing.assert_close(w_a, w_b, atol=2e-2, rtol=2e-2)
+    # one AdamW step moves every weight by about lr = 1e-3: the two collective paths must agree to a small fraction of
+    # that on nearly all elements (a gradient next to zero may flip the sign of its normalised update)
+    diff = (w_a - w_b).abs()
+    assert float((diff > 1e-4).float().mean()) < 1e-3 and float(diff.max()) <= 2.5e-3, (float(diff.max()),
+                                                                                          float((diff > 1e-4).float().mean()))
 
 
 def check_ag_gemm(comm, rank, world, dev):

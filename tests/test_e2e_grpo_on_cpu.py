@@ -161,3 +161,31 @@ def test_dynamic_sampling_accumulates_over_generation_batches(tmp_path, monkeypa
     extra[2] = "trainer.experiment_name=dyn_limit"
     with pytest.raises(ValueError, match="dynamic sampling"):
         run_ppo(compose("ppo_trainer", _overrides(tmp_path, extra)), spmd=True)
+
+
+def test_grpo_with_tensor_parallel_rollout_replica(tmp_path, monkeypatch):
+    """rollout.tensor_model_parallel_size=2 on two gloo workers: one replica sliced over both ranks (weights synced from
+    the ZeRO shards into the TP layout), both ranks receive the same prompts, rank 0 reports."""
+    import json
+
+    from verl_b200.trainer.main_ppo import run_ppo
+
+    monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
+    extra = ["actor_rollout_ref.rollout.tensor_model_parallel_size=2", "trainer.save_freq=-1", "trainer.experiment_name=tp2",
+             "actor_rollout_ref.rollout.max_num_seqs=32"]
+    trainer = run_ppo(compose("ppo_trainer", _overrides(tmp_path, extra)), spmd=False)
+    assert trainer.global_steps == 2
+    m = [json.loads(l) for l in open(tmp_path / "logs" / "cpu_e2e" / "tp2.jsonl")][-1]["data"]
+    for key in ("actor/pg_loss", "actor/grad_norm", "response_length/mean", "timing_s/gen"):
+        assert key in m and math.isfinite(m[key]), key
+    # rollout and training log-probs of the same tokens agree: the TP replica holds the trainer's weights
+    assert abs(m.get("training/rollout_probs_diff_mean", 0.0)) < 1e-3
+
+
+def test_unservable_rollout_parallelism_is_an_error(tmp_path):
+    from verl_b200.trainer.main_ppo import run_ppo
+
+    with pytest.raises(Exception, match="tensor_model_parallel_size"):
+        run_ppo(compose("ppo_trainer", _overrides(tmp_path, ["trainer.n_gpus_per_node=1", "trainer.save_freq=-1",
+                                                             "actor_rollout_ref.rollout.tensor_model_parallel_size=2"])),
+                spmd=True)

@@ -32,3 +32,15 @@ def test_all_ranks(what):
     if n <= 2:
         pytest.skip("needs more than 2 GPUs")
     _run(what, min(n, 8))
+
+
+def test_tensor_parallel_rollout_replica_two_ranks():
+    """A rollout replica sliced over 2 GPUs (fused all-reduce + RMSNorm over peer memory, CUDA graphs) generates what
+    the whole model generates on one GPU: dense, replicated KV heads, expert-parallel MoE."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    port = 29500 + (os.getpid() % 400)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "_tp_rollout_worker.py"), "cuda"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "TP_ROLLOUT_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-6000:])

@@ -126,3 +126,16 @@ def test_rollout_viewer(tmp_path):
     text = main([str(tmp_path), "--step", "2", "--min-score", "0.5", "--sort", "score_desc"])
     assert "2 rollouts" in text and text.index("answer 2 step 2") < text.index("answer 1 step 2") and "step 1" not in text
     assert "1 rollouts" in main([str(tmp_path / "1.jsonl"), "--grep", "answer 0"])
+
+
+def test_kernel_breakdown_interval_arithmetic_and_classes():
+    from verl_b200.utils.profiler.kernel_breakdown import _subtract, _union, classify
+
+    assert _union([(0, 2), (1, 3), (5, 6)]) == [[0, 3], [5, 6]]
+    # communication [0,4] and [10,12]; compute covers [1,2] and [3,11]: exposed = [0,1] + [2,3] + [11,12]
+    assert _subtract(_union([(0, 4), (10, 12)]), _union([(1, 2), (3, 11)])) == 3
+    assert classify("void vb::gemm_kernel<256, false, false, 0>(vb::GemmParams)") == "gemm"
+    assert classify("vb::flash_bwd_dq_kernel") == "attention_bwd"
+    assert classify("void vb::peer_reduce_scatter_add_kernel<8, 2>") == "comm"
+    assert classify("vb::adamw_kernel") == "optimizer"
+    assert classify("at::native::vectorized_elementwise_kernel") == "other_torch"

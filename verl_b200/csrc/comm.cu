@@ -20,6 +20,8 @@
 //                           partial rows into this rank's receive slots; barrier, then sum the slots locally
 //   moe_dispatch / combine  expert-parallel MoE: tokens pushed into the expert owner's grouped-GEMM-ready receive
 //                           buffer; expert outputs pulled back and mixed with the routing weights
+//   tp_allreduce_rmsnorm    tensor-parallel row-parallel epilogue: all-reduce of the ranks' partial products fused with
+//                           the residual add and the RMSNorm of the next block; device-side epoch (graph-replayable)
 //   peer_segment_copy       table-driven gather of byte ranges from peers into a local buffer: the
 //                           train -> rollout weight reshard (FSDP shards -> TP/EP layout) in one launch
 #include "common.cuh"
@@ -249,6 +251,107 @@ __global__ void nvls_reduce_scatter_add_kernel(const float* mc_base, PeerPtrs pa
         d.x += scale * acc[u].x; d.y += scale * acc[u].y; d.z += scale * acc[u].z; d.w += scale * acc[u].w;
         dst[i] = d;
       }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-parallel row-parallel epilogue in one launch: all-reduce + residual add + RMSNorm.
+//
+// Every rank's GEMM has written its partial product [rows, H] (bf16) at the same offset of its symmetric buffer. After
+// the cross-rank handshake each rank pulls all partials over NVLink (all ranks' loads in flight), adds them in rank
+// order in fp32 (+ the residual stream), so that every rank gets bit-identical sums, writes the new residual stream and,
+// when w != nullptr, the RMS-normalised row for the next column-parallel GEMM.
+//
+// The epoch of this channel lives on the device (*epoch_ctr) and is advanced by the last block to leave, so the same
+// launch can be replayed from a CUDA graph; the channel must not be shared with launchers that pass epochs from the host.
+// The partial buffer may be rewritten once a LATER handshake of this channel has passed on this rank (callers alternate
+// two buffers).
+template <int W>
+__global__ void tp_allreduce_rmsnorm_kernel(PeerPtrs partials, PeerPtrs pads, long long off16,
+                                            const __nv_bfloat16* __restrict__ residual_in,
+                                            const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ normed,
+                                            __nv_bfloat16* __restrict__ residual_out, int rows, int H, float eps, int rank,
+                                            int world, int channel, uint32_t* epoch_ctr, uint32_t* done_ctr,
+                                            uint32_t* gate, int* status) {
+  extern __shared__ uint4 row_s[];  // H / 8 vectors: the summed row as bf16
+  __shared__ float red_s[32];
+  __shared__ uint32_t epoch_s;
+  if (threadIdx.x == 0) epoch_s = *reinterpret_cast<volatile uint32_t*>(epoch_ctr) + 1u;
+  __syncthreads();
+  const uint32_t epoch = epoch_s;
+  const bool ok = grid_enter(pads, rank, world, channel, epoch, gate, status);
+  if (ok) {
+    const int nvec = H >> 3;
+    const uint4* src[W];
+#pragma unroll
+    for (int q = 0; q < W; ++q) src[q] = reinterpret_cast<const uint4*>(partials.p[q]) + off16;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+      const long long base = (long long)row * nvec;
+      float ss = 0.f;
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        uint4 pv[W];
+#pragma unroll
+        for (int q = 0; q < W; ++q) pv[q] = src[q][base + v];
+        float acc[8];
+        if (residual_in != nullptr) {
+          const uint4 rv = reinterpret_cast<const uint4*>(residual_in)[base + v];
+          const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(&rv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = __bfloat162float(rp[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        }
+#pragma unroll
+        for (int q = 0; q < W; ++q) {
+          const __nv_bfloat16* pp = reinterpret_cast<const __nv_bfloat16*>(&pv[q]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(pp[j]);
+        }
+        uint4 o;
+        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          op[j] = __float2bfloat16(acc[j]);
+          const float r = __bfloat162float(op[j]);  // the norm sees exactly what later layers will read
+          ss += r * r;
+        }
+        row_s[v] = o;
+        reinterpret_cast<uint4*>(residual_out)[base + v] = o;
+      }
+      if (w != nullptr) {
+        ss = warp_reduce_sum(ss);
+        if ((threadIdx.x & 31) == 0) red_s[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red_s[i];
+        const float rstd = rsqrtf(tot / H + eps);
+        for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+          const uint4 hv = row_s[v];
+          const uint4 wv = reinterpret_cast<const uint4*>(w)[v];
+          const __nv_bfloat16* hp = reinterpret_cast<const __nv_bfloat16*>(&hv);
+          const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(&wv);
+          uint4 o;
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) op[j] = __float2bfloat16(__bfloat162float(hp[j]) * rstd * __bfloat162float(wp[j]));
+          reinterpret_cast<uint4*>(normed)[base + v] = o;
+        }
+        __syncthreads();  // red_s and row_s are reused by the next row
+      }
+    }
+  }
+  // leave: the last block advances the epoch for the next launch (also after a failed handshake, so that the counters
+  // of a later attempt start from a consistent state)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(done_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      *done_ctr = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(epoch_ctr) = epoch;
     }
   }
 }
@@ -578,6 +681,35 @@ extern "C" int vb_moe_combine(const void* const* y, const void* const* pads, con
   else if (k <= 4) VB_COMBINE(4);
   else VB_COMBINE(8);
 #undef VB_COMBINE
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+// partials[r] = base of rank r's symmetric buffer, the partial product sits at byte offset `off_bytes` in each of them.
+// ctrs: three device words owned by the caller for this channel (epoch, done counter, gate), zero before first use.
+extern "C" int vb_tp_allreduce_rmsnorm(const void* const* partials, const void* const* pads, long long off_bytes,
+                                       const void* residual_in, const void* w, void* normed, void* residual_out, int rows,
+                                       int H, float eps, int rank, int world, int channel, unsigned* ctrs, int* status,
+                                       cudaStream_t stream) {
+  if (world > MAX_RANKS || (H & 7) || (off_bytes & 15) || rows <= 0 || residual_out == nullptr) return -3;
+  if (w != nullptr && normed == nullptr) return -3;
+  int blocks = rows;
+  const int cap = 4 * vb_num_sms();  // every block must be resident while block 0 runs the handshake
+  if (blocks > cap) blocks = cap;
+  const int threads = H >= 4096 ? 512 : 256;
+  const size_t smem = (size_t)H * 2;
+  if (smem > 48 * 1024) return -3;
+#define VB_TPAR(WV)                                                                                                  \
+  tp_allreduce_rmsnorm_kernel<WV><<<blocks, threads, smem, stream>>>(                                                \
+      make_ptrs(partials, world), make_ptrs(pads, world), off_bytes >> 4,                                            \
+      reinterpret_cast<const __nv_bfloat16*>(residual_in), reinterpret_cast<const __nv_bfloat16*>(w),                \
+      reinterpret_cast<__nv_bfloat16*>(normed), reinterpret_cast<__nv_bfloat16*>(residual_out), rows, H, eps, rank,  \
+      world, channel, ctrs, ctrs + 1, ctrs + 2, status)
+  if (world == 2) VB_TPAR(2);
+  else if (world == 4) VB_TPAR(4);
+  else if (world == 8) VB_TPAR(8);
+  else return -3;
+#undef VB_TPAR
   vb_count_launch();
   return (int)cudaGetLastError();
 }

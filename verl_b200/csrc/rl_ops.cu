@@ -386,3 +386,66 @@ extern "C" int vb_sample(const void* logits, int dtype, long long row_stride, in
   vb_count_launch();
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Decode-step chaining: the last kernel of a decode step turns the sampled tokens into the inputs of the next step,
+// so that several steps (replays of one CUDA graph) run back to back without the host in between.
+//   ring:   out_tok / out_lp [kmax, B] row *bpos receives this step's tokens / log-probs (-1 / 0 for rows that ended)
+//   rows that are alive: a row ends when it samples `eos` (unless flags bit 0 = ignore eos) or reaches its length limit
+//           (position + 2 >= limit: the sequence then holds `limit` tokens); it stops advancing and its cache slot
+//           becomes -1, which the KV write skips
+//   others: ids <- token, pos += 1, lens += 1, slot <- block_table[pos / block_size] * block_size + pos % block_size
+//           (the host has reserved the pages of the whole burst before it started)
+// One block; also advances the sampler's step counter and *bpos.
+namespace vb {
+__global__ void decode_advance_kernel(const long long* __restrict__ tok, const float* __restrict__ lp,
+                                      long long* __restrict__ ids, long long* __restrict__ pos,
+                                      long long* __restrict__ slots, int* __restrict__ lens,
+                                      const int* __restrict__ bt, int mb, int block_size, const int* __restrict__ limit,
+                                      int* __restrict__ alive, const int* __restrict__ flags, long long eos,
+                                      long long* __restrict__ out_tok, float* __restrict__ out_lp, int* bpos,
+                                      long long* sampler_step, int B, int kmax) {
+  const int s = *bpos;
+  __syncthreads();
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    const int a = alive[b];
+    const long long t = tok[b];
+    if (s >= 0 && s < kmax) {
+      out_tok[(long long)s * B + b] = a ? t : -1;
+      out_lp[(long long)s * B + b] = a ? lp[b] : 0.f;
+    }
+    if (a) {
+      long long p = pos[b];
+      const bool done = (((flags[b] & 1) == 0) && t == eos) || (p + 2 >= (long long)limit[b]);
+      if (done) {
+        alive[b] = 0;
+        slots[b] = -1;
+      } else {
+        p += 1;
+        const int blk = (int)(p / block_size);
+        ids[b] = t;
+        pos[b] = p;
+        lens[b] += 1;
+        slots[b] = blk < mb ? (long long)bt[(long long)b * mb + blk] * block_size + (p % block_size) : -1;
+        if (blk >= mb) alive[b] = 0;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *bpos = s + 1;
+    if (sampler_step != nullptr) *sampler_step += 1;
+  }
+}
+}  // namespace vb
+
+extern "C" int vb_decode_advance(const long long* tok, const float* lp, long long* ids, long long* pos, long long* slots,
+                                 int* lens, const int* bt, int mb, int block_size, const int* limit, int* alive,
+                                 const int* flags, long long eos, long long* out_tok, float* out_lp, int* bpos,
+                                 long long* sampler_step, int B, int kmax, cudaStream_t stream) {
+  if (B <= 0 || kmax <= 0 || block_size <= 0) return -3;
+  vb::decode_advance_kernel<<<1, 256, 0, stream>>>(tok, lp, ids, pos, slots, lens, bt, mb, block_size, limit, alive, flags,
+                                                   eos, out_tok, out_lp, bpos, sampler_step, B, kmax);
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}

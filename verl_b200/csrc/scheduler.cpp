@@ -369,6 +369,74 @@ void vb_sched_commit(void* h, const int64_t* new_tokens, const int32_t* finished
   }
 }
 
+// Burst decode: after vb_sched_step planned a pure decode step, reserve pages so that up to `k` consecutive decode
+// steps of the planned sequences can run on the device without the host (the device advances positions and slots from
+// the block tables by itself; a sequence that ends inside the burst just stops advancing). Returns the number of steps
+// (1..k) that the reservation covers. 1 when the step contains prefill work, or when a waiting request could be
+// admitted at the next step (a burst would delay it).
+int vb_sched_reserve_burst(void* h, int k) {
+  auto* s = static_cast<Scheduler*>(h);
+  if (k <= 1 || s->step_seq_ids.empty()) return 1;
+  if (!s->waiting.empty() && (int)s->running.size() < s->max_num_seqs) return 1;
+  for (size_t i = 0; i < s->step_seq_ids.size(); ++i)
+    if (s->step_is_prefill[i] || s->step_num_tokens[i] != 1) return 1;
+  auto need_pages = [&](int kk) {
+    long long need = 0;
+    for (int64_t id : s->step_seq_ids) {
+      const Seq& q = s->seqs[id];
+      const int upto = std::min(q.computed + kk, q.max_total);
+      const int pages = (upto + s->block_size - 1) / s->block_size;
+      need += std::max(0, pages - (int)q.blocks.size());
+    }
+    return need;
+  };
+  while (k > 1 && need_pages(k) > free_pages(s)) k /= 2;
+  if (k <= 1) return 1;
+  for (int64_t id : s->step_seq_ids) {
+    Seq& q = s->seqs[id];
+    if (!ensure_pages(s, q, std::min(q.computed + k, q.max_total))) return 1;  // cannot happen after the count above
+  }
+  return k;
+}
+
+// Commit a burst of `k` decode steps of the last planned step. toks is [k][n] (n = planned sequences; entries of a
+// sequence after its end are ignored), finished_at[i] = 1-based step at which the caller's stop criteria ended
+// sequence i (0 = none). Length limits are enforced here. accepted_out[i] = number of tokens taken for sequence i,
+// done_out[i] = 1 when it ended.
+void vb_sched_commit_burst(void* h, const int64_t* toks, int k, const int32_t* finished_at, int32_t* accepted_out,
+                           int32_t* done_out) {
+  auto* s = static_cast<Scheduler*>(h);
+  const size_t n = s->step_seq_ids.size();
+  for (size_t i = 0; i < n; ++i) {
+    const int64_t id = s->step_seq_ids[i];
+    auto it = s->seqs.find(id);
+    if (it == s->seqs.end()) { done_out[i] = 1; accepted_out[i] = 0; continue; }
+    Seq& q = it->second;
+    int done = 0, acc = 0;
+    for (int j = 0; j < k && !done; ++j) {
+      q.computed += 1;
+      const int64_t t = toks[(size_t)j * n + i];
+      if (t >= 0) { q.tokens.push_back((int32_t)t); ++acc; }
+      if ((finished_at && finished_at[i] == j + 1) || (int)q.tokens.size() >= q.max_total || t < 0) done = 1;
+    }
+    publish_pages(s, q);
+    if (done) {
+      q.finished = true;
+      release_seq_pages(s, q);
+      auto r = std::find(s->running.begin(), s->running.end(), id);
+      if (r != s->running.end()) s->running.erase(r);
+    }
+    accepted_out[i] = acc;
+    done_out[i] = done;
+  }
+}
+
+// max_total (prompt + allowed new tokens) of the sequences of the last planned step
+void vb_sched_step_limits(void* h, int32_t* limits) {
+  auto* s = static_cast<Scheduler*>(h);
+  for (size_t i = 0; i < s->step_seq_ids.size(); ++i) limits[i] = s->seqs[s->step_seq_ids[i]].max_total;
+}
+
 // Number of generated tokens (tokens beyond the prompt) and copy of them.
 int vb_sched_output(void* h, int64_t id, int32_t* out, int cap) {
   auto* s = static_cast<Scheduler*>(h);

@@ -109,9 +109,14 @@ class MoEMLP(nn.Module):
         self.E, self.k = cfg.num_experts, cfg.num_experts_per_tok
         self.norm_topk = cfg.norm_topk_prob
         I, H = cfg.moe_intermediate_size, cfg.hidden_size
+        # expert parallelism over replicated tokens (a tensor-parallel rollout replica): this module holds the experts
+        # [e_off, e_off + E_local) and returns its partial sum; the caller adds the ranks' results up
+        ep, ep_rank = int(cfg.extra.get("ep_size", 1) or 1), int(cfg.extra.get("ep_rank", 0) or 0)
+        assert self.E % ep == 0, f"{self.E} experts are not divisible by expert-parallel size {ep}"
+        self.E_local, self.e_off = self.E // ep, ep_rank * (self.E // ep)
         self.gate = Linear(H, self.E, False, dtype, device)
-        self.gate_up_proj = nn.Parameter(torch.empty(self.E, 2 * I, H, dtype=dtype, device=device))
-        self.down_proj = nn.Parameter(torch.empty(self.E, H, I, dtype=dtype, device=device))
+        self.gate_up_proj = nn.Parameter(torch.empty(self.E_local, 2 * I, H, dtype=dtype, device=device))
+        self.down_proj = nn.Parameter(torch.empty(self.E_local, H, I, dtype=dtype, device=device))
         self.last_routing = None
         self.replay_routing = None
 
@@ -137,7 +142,8 @@ class MoEMLP(nn.Module):
             # one grouped GEMM per projection for all experts, routing layout computed on the device
             from ..ops.moe import moe_mlp
 
-            return moe_mlp(x, top_i, top_w, self.gate_up_proj, self.down_proj, ops.swiglu)
+            return moe_mlp(x, top_i, top_w, self.gate_up_proj, self.down_proj, ops.swiglu, expert_offset=self.e_off,
+                           num_experts=self.E)
         flat_e = top_i.flatten()
         order = torch.argsort(flat_e, stable=True)
         tok = order // self.k
@@ -149,8 +155,11 @@ class MoEMLP(nn.Module):
             if n == 0:
                 continue
             seg = xs[start : start + n]
-            h = ops.swiglu(ops.linear(seg, self.gate_up_proj[e]))
-            pieces.append(ops.linear(h, self.down_proj[e]))
+            if self.e_off <= e < self.e_off + self.E_local:
+                h = ops.swiglu(ops.linear(seg, self.gate_up_proj[e - self.e_off]))
+                pieces.append(ops.linear(h, self.down_proj[e - self.e_off]))
+            else:  # another rank's expert: no contribution to this rank's partial sum
+                pieces.append(torch.zeros(n, H, dtype=x.dtype, device=x.device))
             start += n
         outs = torch.cat(pieces, dim=0) if pieces else torch.empty(0, H, dtype=x.dtype, device=x.device)
         w = top_w.flatten()[order].to(x.dtype).unsqueeze(-1)

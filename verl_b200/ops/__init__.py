@@ -7,10 +7,11 @@ from .attention import attention_varlen, decode_workspace, kv_cache_write, paged
 from .gemm import gemm, linear
 from .lmhead import lmhead_logprob_entropy
 from .nn import embedding, rmsnorm, rope_qkv, rope_tables, swiglu
-from .rl import (PPO_METRIC_NAMES, adamw_step, clip_coef, gae, grpo_advantage, ppo_loss_fused, sample, sumsq_into)
+from .rl import (PPO_METRIC_NAMES, adamw_step, clip_coef, decode_advance, gae, grpo_advantage, ppo_loss_fused, sample,
+                 sumsq_into)
 
 __all__ = [
     "_lib", "gemm", "linear", "lmhead_logprob_entropy", "embedding", "rmsnorm", "rope_qkv", "rope_tables", "swiglu",
     "attention_varlen", "paged_decode_attention", "kv_cache_write", "decode_workspace", "ppo_loss_fused", "gae",
-    "grpo_advantage", "sample", "adamw_step", "sumsq_into", "clip_coef", "PPO_METRIC_NAMES",
+    "grpo_advantage", "sample", "decode_advance", "adamw_step", "sumsq_into", "clip_coef", "PPO_METRIC_NAMES",
 ]

@@ -48,6 +48,7 @@ _SIGS = {
     "vb_gae": ([P, P, P, P, P, I, I, F, F, P], I),
     "vb_grpo_adv": ([P, P, P, P, P, I, I, I, F, I, P], I),
     "vb_sample": ([P, I, L, I, I, P, P, P, U, P, P, P, P], I),
+    "vb_decode_advance": ([P, P, P, P, P, P, P, I, I, P, P, P, L, P, P, P, P, I, I, P], I),
     # attention
     "vb_decode_num_splits": ([I, I, I], I),
     "vb_grouped_gemm_bf16": ([P, P, P, I, I, I, L, L, L, I, I, I, I, I, I, P, P, P, P], I),

@@ -92,12 +92,25 @@ def grouped_linear(xs: torch.Tensor, weight: torch.Tensor, blk_expert: torch.Ten
     return _GroupedLinearFn.apply(xs, weight, blk_expert, expert_off)
 
 
-def moe_mlp(x: torch.Tensor, top_i: torch.Tensor, top_w: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, swiglu):
-    """Routed expert MLP. x [T, H], top_i / top_w [T, k], gate_up [E, 2I, H], down [E, H, I]."""
+def moe_mlp(x: torch.Tensor, top_i: torch.Tensor, top_w: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, swiglu,
+            expert_offset: int = 0, num_experts: int | None = None):
+    """Routed expert MLP. x [T, H], top_i / top_w [T, k], gate_up [E, 2I, H], down [E, H, I].
+
+    Expert parallelism over replicated tokens: with ``num_experts`` larger than ``E`` the matrices are the experts
+    ``[expert_offset, expert_offset + E)`` of the layer; pairs routed elsewhere fall into a spare bucket whose blocks
+    the grouped GEMM skips, and the result is this rank's partial sum (the ranks' results add up to the layer's)."""
     T, H = x.shape
     k = top_i.shape[1]
     E = gate_up.shape[0]
-    dest, blk_expert, expert_off, P = moe_layout(top_i, E)
+    if num_experts is not None and num_experts != E:
+        local = top_i - expert_offset
+        local = torch.where((local >= 0) & (local < E), local, torch.full_like(local, E))
+        dest, blk_expert, expert_off, P = moe_layout(local, E + 1)
+        blk_expert = torch.where(blk_expert == E, torch.full_like(blk_expert, -1), blk_expert)
+        top_w = torch.where(local < E, top_w, torch.zeros_like(top_w))
+        expert_off = expert_off[: E + 1].contiguous()
+    else:
+        dest, blk_expert, expert_off, P = moe_layout(top_i, E)
     tok = torch.arange(T * k, device=x.device) // k
     xs = torch.zeros((P, H), dtype=x.dtype, device=x.device).index_copy(0, dest, x.index_select(0, tok))
     h = swiglu(grouped_linear(xs, gate_up, blk_expert, expert_off))

@@ -122,6 +122,40 @@ def sample(logits: torch.Tensor, *, temperature: torch.Tensor | None = None, top
     return out_tokens, out_logprobs
 
 
+def decode_advance(tok, lp, ids, pos, slots, lens, bt, block_size: int, limit, alive, flags, eos: int, ring_tok, ring_lp,
+                   bpos, sampler_step=None) -> None:
+    """Last op of a decode step: store the sampled tokens / log-probs in row ``bpos`` of the burst ring and turn them into
+    the next step's inputs in place (``ids, pos, slots, lens``); rows that sample ``eos`` (unless ``flags`` bit 0) or
+    reach ``limit`` tokens stop advancing (``alive`` 0, slot -1). Also advances ``bpos`` and the sampler's step counter."""
+    B = tok.numel()
+    kmax = ring_tok.shape[0]
+    if tok.is_cuda:
+        rc = _lib.fn("vb_decode_advance")(tok.data_ptr(), lp.data_ptr(), ids.data_ptr(), pos.data_ptr(), slots.data_ptr(),
+                                          lens.data_ptr(), bt.data_ptr(), bt.shape[1], int(block_size), limit.data_ptr(),
+                                          alive.data_ptr(), flags.data_ptr(), int(eos), ring_tok.data_ptr(),
+                                          ring_lp.data_ptr(), bpos.data_ptr(), _lib.ptr(sampler_step), B, kmax, _lib.stream())
+        _lib.check(rc, "vb_decode_advance")
+        return
+    s = int(bpos.item())
+    a = alive.bool()
+    if 0 <= s < kmax:
+        ring_tok[s] = torch.where(a, tok, torch.full_like(tok, -1))
+        ring_lp[s] = torch.where(a, lp, torch.zeros_like(lp))
+    done = a & ((((flags & 1) == 0) & (tok == eos)) | (pos + 2 >= limit.long()))
+    go = a & ~done
+    p = pos + 1
+    blk = torch.div(p, block_size, rounding_mode="floor").clamp(max=bt.shape[1] - 1)
+    new_slot = bt.long().gather(1, blk[:, None])[:, 0] * block_size + p % block_size
+    ids.copy_(torch.where(go, tok, ids))
+    pos.copy_(torch.where(go, p, pos))
+    lens.copy_(torch.where(go, lens + 1, lens))
+    slots.copy_(torch.where(go, new_slot, torch.where(done, torch.full_like(slots, -1), slots)))
+    alive.copy_(torch.where(done, torch.zeros_like(alive), alive))
+    bpos.add_(1)
+    if sampler_step is not None:
+        sampler_step.add_(1)
+
+
 # ------------------------------------------------------------------------- optimizer
 def adamw_step(p32, grad, m, v, p16, *, lr, betas, eps, weight_decay, step, scale=None, skip=None):
     """Fused AdamW on a flat fp32 master shard; also refreshes the bf16 working copy ``p16``.

@@ -43,6 +43,8 @@ def _bind():
     lib.vb_gemm_rs_bf16.argtypes = [P, P, P, I, I, I, L, L, L, P, I, I, I, P, L, P, I, P, P]
     lib.vb_gemm_rs_bf16.restype = I
     lib.vb_peer_sum_slots.argtypes, lib.vb_peer_sum_slots.restype = [P, P, P, P, L, I, I, I, I, U, P, P, P], I
+    lib.vb_tp_allreduce_rmsnorm.argtypes = [P, P, L, P, P, P, P, I, I, F, I, I, I, P, P, P]
+    lib.vb_tp_allreduce_rmsnorm.restype = I
     _SIGS_BOUND = True
     return lib
 
@@ -66,6 +68,7 @@ class _Alloc:
 
 class PeerComm:
     CH_GATHER, CH_REDUCE, CH_COPY, CH_BARRIER = 0, 1, 2, 3
+    CH_TP = 4  # epoch kept on the device (tp_allreduce_rmsnorm): never used with host-side epochs
 
     def __init__(self, group=None, use_nvls: Optional[bool] = None):
         import torch.distributed._symmetric_memory as symm_mem
@@ -83,6 +86,7 @@ class PeerComm:
         self.allocs: list[_Alloc] = []
         self.epochs = [0, 0, 0, 0]
         self.gates = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.tp_ctrs = torch.zeros(4, dtype=torch.int32, device=self.device)  # epoch, done counter, gate of CH_TP
         self.pads = self.alloc(1024, torch.int32, zero=True)
         self.pad_alloc = self.allocs[-1]
         self._grad_bufs: list[torch.Tensor] = []
@@ -263,6 +267,27 @@ class PeerComm:
                                         self._gate(self.CH_REDUCE), self._status(), stream)
         _lib.check(rc, "vb_peer_sum_slots")
         return out
+
+    def tp_allreduce_rmsnorm(self, partial: torch.Tensor, residual: Optional[torch.Tensor],
+                             weight: Optional[torch.Tensor], eps: float = 1e-6):
+        """Row-parallel epilogue of a tensor-parallel block in one launch: ``h = sum_ranks partial (+ residual)``,
+        returns ``(rmsnorm(h) * weight, h)`` (``(None, h)`` without ``weight``). ``partial [rows, H]`` (bf16) is this
+        rank's partial product at the same offset of a symmetric buffer on every rank; the sums are bit-identical on
+        all ranks. The kernel keeps its epoch on the device, so it can be captured in and replayed from a CUDA graph.
+        The caller must not rewrite ``partial``'s buffer before a later call of this method has run on this rank
+        (alternate two buffers)."""
+        a, off = self._find(partial)
+        rows, H = partial.shape
+        assert partial.dtype == torch.bfloat16 and partial.is_contiguous()
+        h = torch.empty((rows, H), dtype=torch.bfloat16, device=partial.device)
+        y = torch.empty_like(h) if weight is not None else None
+        if residual is not None:
+            assert residual.shape == h.shape and residual.is_contiguous() and residual.dtype == torch.bfloat16
+        rc = self.lib.vb_tp_allreduce_rmsnorm(a.ptrs, self.pad_alloc.ptrs, off, _lib.ptr(residual), _lib.ptr(weight),
+                                              _lib.ptr(y), h.data_ptr(), rows, H, float(eps), self.rank, self.world,
+                                              self.CH_TP, self.tp_ctrs.data_ptr(), self._status(), _lib.stream())
+        _lib.check(rc, "vb_tp_allreduce_rmsnorm")
+        return y, h
 
     def check(self):
         """Synchronising read of the status word; raises if a bounded wait ran out."""

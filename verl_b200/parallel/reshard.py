@@ -40,8 +40,32 @@ class DestTensor:
     col_range: Optional[tuple] = None  # (c0, c1) columns kept from each row (None = all)
 
 
+def tp_model_config(cfg: ModelConfig, tp_rank: int, tp_size: int) -> ModelConfig:
+    """Architecture of one tensor-parallel rank's slice of the model: 1 / tp of the query heads, of the KV heads (one
+    replicated KV head per rank when there are fewer KV heads than ranks), of the MLP columns and of the experts."""
+    import dataclasses
+
+    if tp_size == 1:
+        return cfg
+    Hq, Hk = cfg.num_attention_heads, cfg.num_key_value_heads
+    if Hq % tp_size != 0:
+        raise ValueError(f"tensor_model_parallel_size {tp_size} does not divide {Hq} attention heads")
+    if Hk % tp_size != 0 and tp_size % Hk != 0:
+        raise ValueError(f"tensor_model_parallel_size {tp_size} and {Hk} KV heads are incompatible")
+    if not cfg.is_moe and cfg.intermediate_size % (8 * tp_size) != 0:
+        raise ValueError(f"intermediate size {cfg.intermediate_size} cannot be split over {tp_size} ranks in multiples of 8")
+    if cfg.is_moe and cfg.num_experts % tp_size != 0:
+        raise ValueError(f"{cfg.num_experts} experts cannot be split over {tp_size} ranks")
+    extra = dict(cfg.extra)
+    extra.update({"tp_size": tp_size, "tp_rank": tp_rank})
+    if cfg.is_moe:
+        extra.update({"ep_size": tp_size, "ep_rank": tp_rank})
+    return dataclasses.replace(cfg, num_attention_heads=Hq // tp_size, num_key_value_heads=max(Hk // tp_size, 1),
+                               head_dim=cfg.head_dim, intermediate_size=cfg.intermediate_size // tp_size, extra=extra)
+
+
 def tp_slices(cfg: ModelConfig, name: str, shape: tuple, tp_rank: int, tp_size: int):
-    """(row_ranges, col_range) of native parameter ``name`` owned by ``tp_rank``."""
+    """(row_ranges, col_range) of native parameter ``name`` owned by ``tp_rank`` (``cfg``: the whole model)."""
     rows = shape[0] if len(shape) >= 1 else 1
     if tp_size == 1 or len(shape) == 0:
         return [(0, rows)], None
@@ -51,10 +75,17 @@ def tp_slices(cfg: ModelConfig, name: str, shape: tuple, tp_rank: int, tp_size: 
         k = n // tp_size
         return (r0 + tp_rank * k, r0 + (tp_rank + 1) * k)
 
+    def kv_part(r0):
+        Hk, D = cfg.num_key_value_heads, cfg.head_dim
+        if Hk % tp_size == 0:
+            return part(r0, Hk * D)
+        head = tp_rank // (tp_size // Hk)  # fewer KV heads than ranks: neighbouring ranks share (replicate) a head
+        return (r0 + head * D, r0 + (head + 1) * D)
+
     leaf = name.split(".")[-2] + "." + name.split(".")[-1] if "." in name else name
     if leaf in ("qkv_proj.weight", "qkv_proj.bias"):
         q, kv = cfg.q_size, cfg.kv_size
-        return [part(0, q), part(q, kv), part(q + kv, kv)], None
+        return [part(0, q), kv_part(q), kv_part(q + kv)], None
     if leaf == "gate_up_proj.weight":
         i = shape[0] // 2
         return [part(0, i), part(i, i)], None
@@ -63,7 +94,24 @@ def tp_slices(cfg: ModelConfig, name: str, shape: tuple, tp_rank: int, tp_size: 
         assert cols % tp_size == 0
         k = cols // tp_size
         return [(0, rows)], (tp_rank * k, (tp_rank + 1) * k)
+    if leaf in ("mlp.gate_up_proj", "mlp.down_proj") and len(shape) == 3:  # stacked expert matrices: whole experts
+        return [part(0, shape[0])], None
     return [(0, rows)], None
+
+
+def shard_state_dict(cfg: ModelConfig, full: dict, tp_rank: int, tp_size: int) -> dict:
+    """This rank's slices of a whole-model state dict (native names), in the layout of :func:`tp_model_config`."""
+    out = {}
+    for name, t in full.items():
+        row_ranges, col_range = tp_slices(cfg, name, tuple(t.shape), tp_rank, tp_size)
+        if t.dim() == 0:
+            out[name] = t
+            continue
+        piece = torch.cat([t[a:b] for a, b in row_ranges], dim=0) if len(row_ranges) > 1 or row_ranges[0] != (0, t.shape[0]) else t
+        if col_range is not None:
+            piece = piece[:, col_range[0] : col_range[1]]
+        out[name] = piece.contiguous()
+    return out
 
 
 def build_dest_layout(cfg: ModelConfig, zero_units, tp_rank: int = 0, tp_size: int = 1, align: int = 8):

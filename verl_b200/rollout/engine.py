@@ -92,6 +92,9 @@ def _sched_lib():
         lib.vb_sched_remove.argtypes, lib.vb_sched_remove.restype = [P, L], I
         lib.vb_sched_reset_prefix_cache.argtypes, lib.vb_sched_reset_prefix_cache.restype = [P], None
         lib.vb_sched_stats.argtypes, lib.vb_sched_stats.restype = [P, P], None
+        lib.vb_sched_reserve_burst.argtypes, lib.vb_sched_reserve_burst.restype = [P, I], I
+        lib.vb_sched_commit_burst.argtypes, lib.vb_sched_commit_burst.restype = [P, P, I, P, P, P], None
+        lib.vb_sched_step_limits.argtypes, lib.vb_sched_step_limits.restype = [P, P], None
         lib._sched_bound = True
     return lib
 
@@ -116,6 +119,8 @@ class Scheduler:
         self.slots = np.zeros(cap_t, np.int64)
         self.block_tables = np.zeros((cap_s, self.max_blocks), np.int32)
         self.done = np.zeros(cap_s, np.int32)
+        self.accepted = np.zeros(cap_s, np.int32)
+        self.limits = np.zeros(cap_s, np.int32)
 
     def __del__(self):
         try:
@@ -138,6 +143,33 @@ class Scheduler:
                                        p(self.seq_total), p(self.tokens), p(self.positions), p(self.slots),
                                        p(self.block_tables), self.max_blocks)
         return n, t
+
+    def _fetch(self) -> int:
+        p = lambda a: a.ctypes.data  # noqa: E731
+        return self.lib.vb_sched_get_step(self.h, p(self.seq_ids), p(self.seq_ntok), p(self.seq_start), p(self.seq_prefill),
+                                          p(self.seq_total), p(self.tokens), p(self.positions), p(self.slots),
+                                          p(self.block_tables), self.max_blocks)
+
+    def reserve_burst(self, k: int) -> int:
+        """Pages for up to ``k`` consecutive decode steps of the planned (pure decode) step; returns the number of
+        steps covered (1 = no burst) and refreshes the block tables."""
+        got = self.lib.vb_sched_reserve_burst(self.h, int(k))
+        if got > 1:
+            self._fetch()
+        return got
+
+    def step_limits(self, n: int) -> np.ndarray:
+        self.lib.vb_sched_step_limits(self.h, self.limits.ctypes.data)
+        return self.limits[:n]
+
+    def commit_burst(self, toks: np.ndarray, finished_at: np.ndarray):
+        """toks [k, n] int64, finished_at [n] int32 (1-based step of the caller's stop, 0 = none) -> (accepted, done)."""
+        k, n = toks.shape
+        toks = np.ascontiguousarray(toks, dtype=np.int64)
+        finished_at = np.ascontiguousarray(finished_at, dtype=np.int32)
+        self.lib.vb_sched_commit_burst(self.h, toks.ctypes.data, int(k), finished_at.ctypes.data, self.accepted.ctypes.data,
+                                       self.done.ctypes.data)
+        return self.accepted[:n], self.done[:n]
 
     def commit(self, new_tokens: np.ndarray, finished: np.ndarray) -> np.ndarray:
         n = len(new_tokens)
@@ -169,8 +201,26 @@ class NativeRolloutEngine:
                  max_num_batched_tokens: int = 8192, block_size: int = 16, num_blocks: Optional[int] = None,
                  gpu_memory_utilization: float = 0.5, enable_prefix_caching: bool = True, enforce_eager: bool = False,
                  seed: int = 0, eos_token_id: Optional[int] = None, cudagraph_capture_sizes: Optional[list] = None,
-                 quantization: Optional[str] = None):
+                 quantization: Optional[str] = None, tp_group=None, tp_comm=None, full_config: Optional[ModelConfig] = None,
+                 decode_burst: int = 8):
+        """``model``: the whole model, or (tensor parallelism) this rank's slice of it as laid out by
+        :func:`verl_b200.parallel.reshard.tp_model_config`, with ``tp_group`` the replica's process group, ``tp_comm``
+        its peer-memory communicator (CUDA) and ``full_config`` the architecture of the whole model. Every rank of a
+        replica runs the same scheduler on the same requests and samples the same tokens (the all-reduced activations
+        are bit-identical on all ranks), so the ranks need no control traffic besides the activation all-reduces."""
         self.model = model
+        # up to this many decode steps run back to back on the device (each step's last kernel prepares the next
+        # step's inputs); the host reads their tokens in one go. 1 = the host takes part in every step.
+        self.decode_burst = max(1, min(int(decode_burst), 64))
+        self.tp_group, self.tp_comm = tp_group, tp_comm
+        self.tp = 1
+        if tp_group is not None:
+            import torch.distributed as dist
+
+            self.tp = dist.get_world_size(tp_group)
+            self.tp_rank = dist.get_rank(tp_group)
+        self.full_cfg: ModelConfig = full_config if full_config is not None else model.cfg
+        self._tp_bufs: list = []
         if quantization not in (None, "", "fp8"):
             raise ValueError(f"unsupported rollout quantization {quantization!r} (supported: fp8)")
         self.quantization = quantization or None
@@ -199,6 +249,16 @@ class NativeRolloutEngine:
         self._capture_sizes = cudagraph_capture_sizes
         self.step_counter = torch.zeros(1, dtype=torch.long, device=self.device)
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0}
+        if self.tp > 1 and self.on_gpu:
+            if tp_comm is None:
+                raise ValueError("a tensor-parallel rollout replica on CUDA needs its peer-memory communicator (tp_comm)")
+            # Partial products of the row-parallel GEMMs, read by the peers' all-reduce kernels: two alternating buffers
+            # for the decode path and two for the prefill path (a buffer is rewritten only after a later all-reduce of
+            # the replica has passed its handshake; both paths run an even number of all-reduces)
+            rows = max(self.max_num_batched_tokens + self.max_num_seqs, self.max_num_seqs) + 8
+            self._tp_rows = rows
+            self._tp_bufs = [tp_comm.alloc(rows * self.cfg.hidden_size, torch.bfloat16, zero=False) for _ in range(4)]
+            tp_comm.barrier()
         self.wake_up()
         self.refresh_quantization()
 
@@ -223,6 +283,12 @@ class NativeRolloutEngine:
             nb = min(nb, self.max_num_seqs * ((self.max_model_len + self.block_size - 1) // self.block_size) + 64)
         else:
             nb = self.max_num_seqs * ((self.max_model_len + self.block_size - 1) // self.block_size) + 8
+        if self.tp > 1:  # the ranks of a replica must run identical schedulers: agree on the smallest cache
+            import torch.distributed as dist
+
+            t = torch.tensor([int(nb)], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.tp_group)
+            nb = int(t.item())
         self.num_blocks = int(nb)
         c = self.cfg
         shape = (self.num_blocks, c.num_key_value_heads, self.block_size, c.head_dim)
@@ -250,7 +316,11 @@ class NativeRolloutEngine:
         """Load HF-named tensors into the engine's (fused-layout) parameters. When the engine shares its
         module with the trainer on the same device this is unnecessary; it serves separate replicas."""
         hf = {k: v for k, v in weights}
-        native = hf_to_native_state_dict(self.cfg, hf)
+        native = hf_to_native_state_dict(self.full_cfg, hf)
+        if self.tp > 1:
+            from ..parallel.reshard import shard_state_dict
+
+            native = shard_state_dict(self.full_cfg, native, self.tp_rank, self.tp)
         own = dict(self.model.named_parameters())
         for k, v in native.items():
             if k in own:
@@ -339,19 +409,65 @@ class NativeRolloutEngine:
             return ops.gemm(x, w, bias=bias)
         return torch.nn.functional.linear(x, w, bias)
 
-    def _layer_rest(self, layer, attn_out, residual):
-        c = self.cfg
-        o = self._mm(attn_out.reshape(attn_out.shape[0], c.q_size), layer.self_attn.o_proj.weight)
-        x, residual = ops.rmsnorm(o, layer.post_attention_layernorm.weight, c.rms_norm_eps, residual)
-        if c.is_moe:
-            h = layer.mlp(x)
-        else:
-            h = self._mm(ops.swiglu(self._mm(x, layer.mlp.gate_up_proj.weight)), layer.mlp.down_proj.weight)
-        return h, residual
+    def _mm_partial(self, x, w, slot: int, path: int):
+        """Row-parallel GEMM. Tensor parallelism on CUDA: the partial product goes straight into the symmetric buffer
+        ``2 * path + slot`` (path 0 = decode, 1 = prefill) that the peers' all-reduce kernels read."""
+        if self.tp == 1 or not self.on_gpu:
+            return self._mm(x, w)
+        buf = self._tp_bufs[2 * path + slot][: x.shape[0] * w.shape[0]].view(x.shape[0], w.shape[0])
+        q = self._fp8.get(id(w))
+        if q is not None:
+            from ..ops import fp8
 
-    def _final_logits(self, hidden, residual):
+            buf.copy_(fp8.fp8_linear(x, q[0], q[1], None))
+        else:
+            ops.gemm(x, w, out=buf)
+        return buf
+
+    def _to_partial(self, y, slot: int, path: int):
+        if self.tp == 1 or not self.on_gpu:
+            return y
+        buf = self._tp_bufs[2 * path + slot][: y.numel()].view(y.shape)
+        buf.copy_(y)
+        return buf
+
+    def _reduce_norm(self, partial, norm_w, residual):
+        """(rmsnorm(h) * norm_w, h) with h = sum over the replica's ranks of ``partial`` + ``residual``: one fused
+        all-reduce + residual + RMSNorm kernel over peer memory; plain RMSNorm without tensor parallelism."""
+        eps = self.cfg.rms_norm_eps
+        if self.tp == 1:
+            return ops.rmsnorm(partial, norm_w, eps, residual)
+        if self.on_gpu:
+            return self.tp_comm.tp_allreduce_rmsnorm(partial, residual, norm_w, eps)
+        import torch.distributed as dist
+
+        partial = partial.contiguous()
+        dist.all_reduce(partial, group=self.tp_group)
+        return ops.rmsnorm(partial, norm_w, eps, residual)
+
+    def _forward_layers(self, h, attend, path: int):
+        """Decoder stack on embedded tokens ``h [T, H]``; ``attend(li, layer, x)`` returns the attention output of the
+        layer's (local) heads for the normalised input ``x``. Returns the final-norm hidden states. Every RMSNorm after
+        the first one is fused with the residual add (and, under tensor parallelism, with the all-reduce of the
+        preceding row-parallel GEMM)."""
         c = self.cfg
-        x, _ = ops.rmsnorm(hidden, self.model.norm.weight, c.rms_norm_eps, residual)
+        layers = self.model.layers
+        T = h.shape[0]
+        x, residual = ops.rmsnorm(h, layers[0].input_layernorm.weight, c.rms_norm_eps, None)
+        for li, layer in enumerate(layers):
+            attn = attend(li, layer, x)
+            o = self._mm_partial(attn.reshape(T, c.q_size), layer.self_attn.o_proj.weight, 0, path)
+            x, residual = self._reduce_norm(o, layer.post_attention_layernorm.weight, residual)
+            if c.is_moe:
+                d = self._to_partial(layer.mlp(x), 1, path)
+            else:
+                d = self._mm_partial(ops.swiglu(self._mm(x, layer.mlp.gate_up_proj.weight)), layer.mlp.down_proj.weight,
+                                     1, path)
+            nw = layers[li + 1].input_layernorm.weight if li + 1 < len(layers) else self.model.norm.weight
+            x, residual = self._reduce_norm(d, nw, residual)
+        return x
+
+    def _final_logits(self, x):
         w = self.model.lm_head_weight
         if self.on_gpu:
             return ops.gemm(x, w, out_dtype=torch.float32)
@@ -360,17 +476,15 @@ class NativeRolloutEngine:
     # ------------------------------------------------------------------ decode
     @torch.no_grad()
     def _decode_forward(self, ids, positions, slots, block_table, seq_lens, splits, work):
-        c = self.cfg
         h = ops.embedding(ids, self.model.embed_tokens.weight)
-        residual = None
-        for li, layer in enumerate(self.model.layers):
-            x, residual = ops.rmsnorm(h, layer.input_layernorm.weight, c.rms_norm_eps, residual)
+
+        def attend(li, layer, x):
             q, k, v = self._layer_attn_in(layer, x, positions)
             ops.kv_cache_write(k, v, slots, self.k_cache[li], self.v_cache[li])
-            attn = ops.paged_decode_attention(q, self.k_cache[li], self.v_cache[li], block_table, seq_lens,
+            return ops.paged_decode_attention(q, self.k_cache[li], self.v_cache[li], block_table, seq_lens,
                                               num_splits=splits, work=work)
-            h, residual = self._layer_rest(layer, attn, residual)
-        return self._final_logits(h, residual)
+
+        return self._final_logits(self._forward_layers(h, attend, 0))
 
     def _graph_sizes(self):
         if self._capture_sizes:
@@ -392,17 +506,20 @@ class NativeRolloutEngine:
         # two outputs in one more buffer that comes back in one copy: a decode step costs two small transfers.
         fields = [("ids", np.int64, (B,), 0), ("pos", np.int64, (B,), 0), ("slots", np.int64, (B,), -1),
                   ("lens", np.int32, (B,), 1), ("temp", np.float32, (B,), 1.0), ("topk", np.int32, (B,), -1),
-                  ("topp", np.float32, (B,), 1.0), ("bt", np.int32, (B, mb), 0)]
+                  ("topp", np.float32, (B,), 1.0), ("limit", np.int32, (B,), 0), ("alive", np.int32, (B,), 0),
+                  ("flags", np.int32, (B,), 0), ("bpos", np.int32, (1,), 0), ("bt", np.int32, (B, mb), 0)]
         off, layout = 0, {}
         for name, dt, shape, _ in fields:
             nb = int(np.prod(shape)) * np.dtype(dt).itemsize
             layout[name] = (off, nb)
             off = (off + nb + 255) // 256 * 256
         pin = dev.type == "cuda"
+        K = self.decode_burst
         host = torch.zeros(off, dtype=torch.uint8, pin_memory=pin)
         devbuf = torch.zeros(off, dtype=torch.uint8, device=dev)
-        out_dev = torch.zeros(B * 12, dtype=torch.uint8, device=dev)
-        out_host = torch.zeros(B * 12, dtype=torch.uint8, pin_memory=pin)
+        # ring of the burst's results: K rows of B tokens (int64) followed by K rows of B log-probs (fp32)
+        out_dev = torch.zeros(K * B * 12, dtype=torch.uint8, device=dev)
+        out_host = torch.zeros(K * B * 12, dtype=torch.uint8, pin_memory=pin)
         tdt = {np.int64: torch.int64, np.int32: torch.int32, np.float32: torch.float32}
         st = {"host": {}, "pad": {}, "host_buf": host, "dev_buf": devbuf, "out_dev": out_dev, "out_host": out_host,
               "sig": None}
@@ -414,19 +531,24 @@ class NativeRolloutEngine:
             st["host"][name][...] = pad
             st["pad"][name] = pad
         devbuf.copy_(host)
-        st["tok"] = out_dev[: B * 8].view(torch.int64)
-        st["lp"] = out_dev[B * 8 :].view(torch.float32)
-        st["host_tok"] = out_host.numpy()[: B * 8].view(np.int64)
-        st["host_lp"] = out_host.numpy()[B * 8 :].view(np.float32)
+        st["ring_tok"] = out_dev[: K * B * 8].view(torch.int64).view(K, B)
+        st["ring_lp"] = out_dev[K * B * 8 :].view(torch.float32).view(K, B)
+        st["host_tok"] = out_host.numpy()[: K * B * 8].view(np.int64).reshape(K, B)
+        st["host_lp"] = out_host.numpy()[K * B * 8 :].view(np.float32).reshape(K, B)
+        st["tok"] = torch.zeros(B, dtype=torch.int64, device=dev)
+        st["lp"] = torch.zeros(B, dtype=torch.float32, device=dev)
         splits, work = ops.decode_workspace(B, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
                                             self.max_model_len, dev)
         st["splits"], st["work"] = splits, work
+        eos = -1 if self.eos is None else int(self.eos)
 
         def run():
             logits = self._decode_forward(st["ids"], st["pos"], st["slots"], st["bt"], st["lens"], splits, work)
             ops.sample(logits, temperature=st["temp"], top_k=st["topk"], top_p=st["topp"], seed=self.seed,
                        step=self.step_counter, out_tokens=st["tok"], out_logprobs=st["lp"])
-            self.step_counter.add_(1)
+            ops.decode_advance(st["tok"], st["lp"], st["ids"], st["pos"], st["slots"], st["lens"], st["bt"],
+                               self.block_size, st["limit"], st["alive"], st["flags"], eos, st["ring_tok"], st["ring_lp"],
+                               st["bpos"], self.step_counter)
 
         graph = None
         if not self.enforce_eager:
@@ -504,20 +626,19 @@ class NativeRolloutEngine:
             cu_k_t = torch.tensor(cu_k, dtype=torch.int32, device=dev)
             max_k = max(b - a for a, b in zip(cu_k[:-1], cu_k[1:]))
         h = ops.embedding(ids, self.model.embed_tokens.weight)
-        residual = None
-        for li, layer in enumerate(self.model.layers):
-            x, residual = ops.rmsnorm(h, layer.input_layernorm.weight, c.rms_norm_eps, residual)
+
+        def attend(li, layer, x):
             q, k, v = self._layer_attn_in(layer, x, pos)
             ops.kv_cache_write(k, v, slots, self.k_cache[li], self.v_cache[li])
             if not has_ctx:
-                attn = ops.attention_varlen(q, k, v, cu_q, max_q, causal=True)
-            else:
-                k_all = torch.cat([self.k_cache[li][blk, :, off], k], dim=0)[order_t]
-                v_all = torch.cat([self.v_cache[li][blk, :, off], v], dim=0)[order_t]
-                attn = _varlen_attention_kv(q, k_all, v_all, cu_q, cu_k_t, max_q, max_k)
-            h, residual = self._layer_rest(layer, attn, residual)
+                return ops.attention_varlen(q, k, v, cu_q, max_q, causal=True)
+            k_all = torch.cat([self.k_cache[li][blk, :, off], k], dim=0)[order_t]
+            v_all = torch.cat([self.v_cache[li][blk, :, off], v], dim=0)[order_t]
+            return _varlen_attention_kv(q, k_all, v_all, cu_q, cu_k_t, max_q, max_k)
+
+        x = self._forward_layers(h, attend, 1)
         last = torch.tensor([b - 1 for b in cu[1:]], dtype=torch.long, device=dev)
-        return self._final_logits(h[last], residual[last])
+        return self._final_logits(x[last])
 
     # -------------------------------------------------------------------- step
     @torch.no_grad()
@@ -537,38 +658,50 @@ class NativeRolloutEngine:
         new_tokens = np.full(n, -1, np.int64)
         new_lps = np.zeros(n, np.float32)
         dev = self.device
+        burst = None
         if dec:
             nd = len(dec)
             B = self._pad_batch(nd)
             st, graph, run = self._get_graph(B)
             di = np.asarray(dec)
+            sids_d = sc.seq_ids[di]
+            sps = [self.requests[int(sid)].params for sid in sids_d]
+            k = 1
+            if not pre and self.decode_burst > 1 and not any(p.stop_token_ids for p in sps):
+                k = sc.reserve_burst(self.decode_burst)
             t_idx = np.asarray([tok_lo[i] for i in dec])
             hp, pad = st["host"], st["pad"]
-            sig = (nd, sc.seq_ids[di].tobytes())
-            fresh = st["sig"] != sig  # batch membership changed: rewrite the padding and the sampling parameters
+            sig = (nd, sids_d.tobytes())
+            fresh = st["sig"] != sig  # batch membership changed: rewrite the padding and the per-request constants
             for name, arr in (("ids", sc.tokens[t_idx]), ("pos", sc.positions[t_idx]), ("slots", sc.slots[t_idx]),
                               ("bt", sc.block_tables[di]), ("lens", sc.seq_total[di])):
                 hp[name][:nd] = arr
                 if fresh:
                     hp[name][nd:] = pad[name]
             if fresh:
-                sps = [self.requests[int(sid)].params for sid in sc.seq_ids[di]]
                 for name, vals in (("temp", [p.temperature for p in sps]), ("topk", [p.top_k for p in sps]),
-                                   ("topp", [p.top_p for p in sps])):
+                                   ("topp", [p.top_p for p in sps]), ("flags", [int(p.ignore_eos) for p in sps]),
+                                   ("limit", sc.step_limits(n)[di]), ("alive", 1)):
                     hp[name][:nd] = vals
                     hp[name][nd:] = pad[name]
                 st["sig"] = sig
             st["dev_buf"].copy_(st["host_buf"], non_blocking=True)
-            if graph is not None:
-                graph.replay()
-            else:
-                run()
+            for _ in range(k):
+                if graph is not None:
+                    graph.replay()
+                else:
+                    run()
             st["out_host"].copy_(st["out_dev"], non_blocking=True)
             if dev.type == "cuda":
                 torch.cuda.current_stream(dev).synchronize()
-            new_tokens[di] = st["host_tok"][:nd]
-            new_lps[di] = st["host_lp"][:nd]
-            self.stats["decode_tokens"] += nd
+            if k > 1:
+                burst = (k, st["host_tok"][:k, :nd].copy(), st["host_lp"][:k, :nd].copy(), sps)
+            else:
+                new_tokens[di] = st["host_tok"][0, :nd]
+                new_lps[di] = st["host_lp"][0, :nd]
+            self.stats["decode_tokens"] += nd * k
+        if burst is not None:
+            return self._commit_burst(n, *burst)
         if pre:
             logits = self._prefill_forward(pre, [tok_lo[i] for i in pre])
             # only chunks that complete their sequence sample a token
@@ -602,6 +735,30 @@ class NativeRolloutEngine:
                 req.logprobs.append(lps[i])
             if done[i]:
                 outs.append(self._finish(sids[i], reasons.get(sids[i], "length")))
+        return outs
+
+    def _commit_burst(self, n: int, k: int, toks: np.ndarray, lps: np.ndarray, sps: list) -> list[TokenOutput]:
+        """Book-keeping of a burst of ``k`` decode steps over the ``n`` planned sequences (toks / lps are [k, n])."""
+        sc = self.sched
+        eos = self.eos
+        finished_at = np.zeros(n, np.int32)
+        if eos is not None:
+            hit = toks == eos
+            ign = np.asarray([p.ignore_eos for p in sps])
+            hit[:, ign] = False
+            any_hit = hit.any(0)
+            finished_at[any_hit] = hit.argmax(0)[any_hit] + 1
+        sids = sc.seq_ids[:n].tolist()
+        accepted, done = sc.commit_burst(toks, finished_at)
+        accepted, done = accepted.tolist(), done.tolist()
+        outs = []
+        for i, sid in enumerate(sids):
+            req = self.requests[sid]
+            a = accepted[i]
+            if a:
+                req.logprobs.extend(lps[:a, i].tolist())
+            if done[i]:
+                outs.append(self._finish(sid, "completed" if 0 < finished_at[i] <= a else "length"))
         return outs
 
     def _was_sampled(self, i: int) -> bool:

@@ -128,7 +128,14 @@ class ActorRolloutRefWorker(_WorkerBase):
         sp_a, sp_r = sp_of(self.actor_cfg), sp_of(self.ref_cfg if self.ref_cfg is not None else self.actor_cfg)
         self._register_dispatch_collect_info("actor", dp_rank=rank // sp_a, is_collect=rank % sp_a == 0)
         self._register_dispatch_collect_info("ref", dp_rank=rank // sp_r, is_collect=rank % sp_r == 0)
-        self._register_dispatch_collect_info("rollout", dp_rank=self.dp_rank, is_collect=True)
+        # a rollout replica spans `tensor_model_parallel_size` consecutive ranks: they receive the same prompts and
+        # the first one reports (verl/workers/rollout/replica.py:96-143)
+        self.rollout_tp = int(_cfg(self.rollout_cfg, "tensor_model_parallel_size", 1) or 1) if self._is_rollout else 1
+        if self._is_rollout:
+            self._check_rollout_parallelism()
+        self._register_dispatch_collect_info("rollout", dp_rank=self.dp_rank // self.rollout_tp,
+                                             is_collect=self.dp_rank % self.rollout_tp == 0)
+        self.tp_group = self.tp_comm = None
         self.actor_engine = self.ref_engine = None
         self.actor = self.ref_policy = None
         self.rollout_engine = None
@@ -152,6 +159,9 @@ class ActorRolloutRefWorker(_WorkerBase):
                 "target_modules": _cfg(self.config.model, "target_modules", "all-linear"),
                 "exclude_modules": _cfg(self.config.model, "exclude_modules", None)} if lora_rank > 0 else None
         self._lora = lora is not None
+        if self._lora and self._is_rollout and self.rollout_tp > 1:
+            raise ValueError("LoRA training syncs merged weights into a whole-model rollout copy: set "
+                             "rollout.tensor_model_parallel_size=1 with model.lora_rank > 0")
         if self._is_actor:
             self.actor_engine = NativeEngine(model_cfg, self.actor_cfg.fsdp_config, self.actor_cfg.optim,
                                              device=str(self.device), group=group, seed=seed, state_dict=state,
@@ -189,14 +199,61 @@ class ActorRolloutRefWorker(_WorkerBase):
                 print(f"[verl_b200] peer-memory collectives unavailable ({type(e).__name__}: {e}); using NCCL")
         return self.comm
 
+    def _check_rollout_parallelism(self):
+        """Parallel sizes of a rollout replica that this engine cannot serve are errors, not silently ignored."""
+        rc, tp = self.rollout_cfg, self.rollout_tp
+        pp = int(_cfg(rc, "pipeline_model_parallel_size", 1) or 1)
+        dpr = int(_cfg(rc, "data_parallel_size", 1) or 1)
+        ep = int(_cfg(rc, "expert_parallel_size", 1) or 1)
+        if pp != 1 or dpr != 1:
+            raise ValueError("rollout.pipeline_model_parallel_size and rollout.data_parallel_size must be 1: one NVSwitch "
+                             "box is served by tensor-parallel replicas (replicas = GPUs / tensor_model_parallel_size)")
+        if tp < 1 or self.world % tp != 0:
+            raise ValueError(f"rollout.tensor_model_parallel_size={tp} does not divide the {self.world} rank(s) of this "
+                             "job; set it to a divisor (1 runs one replica per GPU)")
+        if ep not in (1, tp):
+            raise ValueError(f"rollout.expert_parallel_size={ep}: experts are sharded over the ranks of a replica, so it "
+                             f"must be 1 or equal to tensor_model_parallel_size ({tp})")
+
+    def _setup_rollout_tp(self):
+        """Process group (and, on CUDA, peer-memory communicator) of this rank's rollout replica."""
+        tp = self.rollout_tp
+        mine = None
+        for g in range(self.world // tp):  # collective: every rank creates every group
+            ranks = list(range(g * tp, (g + 1) * tp))
+            grp = dist.new_group(ranks)
+            if self.dp_rank in ranks:
+                mine = grp
+        self.tp_group = mine
+        if self.device.type == "cuda":
+            from ..parallel.peer_comm import PeerComm
+
+            self.tp_comm = self.comm if tp == self.world and self.comm is not None else PeerComm(mine)
+
     def _build_rollout(self, model_cfg: ModelConfig, state, seed: int):
         from ..rollout import NativeRolloutEngine
 
         rc = self.rollout_cfg
-        if self._is_actor and self.world == 1 and not getattr(self, "_lora", False):
+        tp = self.rollout_tp
+        dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        if tp > 1:
+            from ..parallel.reshard import shard_state_dict, tp_model_config
+
+            self._setup_rollout_tp()
+            tp_rank = self.dp_rank % tp
+            self.rollout_model = CausalLM(tp_model_config(model_cfg, tp_rank, tp), dtype=dtype, device=self.device)
+            if self._is_actor:
+                self._bind_rollout_to_flat(tp_rank, tp)
+            else:
+                if state is None:  # random init of the whole model, then this rank's slices (same seed on all ranks)
+                    full = CausalLM(model_cfg, dtype=dtype, device=self.device).init_weights(seed)
+                    state = dict(full.state_dict())
+                    del full
+                sl = shard_state_dict(model_cfg, {k: v.to(dtype) for k, v in state.items()}, tp_rank, tp)
+                self.rollout_model.load_state_dict(sl, strict=False)
+        elif self._is_actor and self.world == 1 and not getattr(self, "_lora", False):
             self.rollout_model = self.actor_engine.model  # same tensors: weight sync is free
         else:
-            dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
             self.rollout_model = CausalLM(model_cfg, dtype=dtype, device=self.device)
             if self._is_actor:
                 self._bind_rollout_to_flat()
@@ -210,17 +267,19 @@ class ActorRolloutRefWorker(_WorkerBase):
             self.rollout_model, max_num_seqs=rc.max_num_seqs, max_model_len=max_len,
             max_num_batched_tokens=max(rc.max_num_batched_tokens, rc.prompt_length),
             gpu_memory_utilization=rc.gpu_memory_utilization, enable_prefix_caching=rc.enable_prefix_caching,
-            enforce_eager=rc.enforce_eager, seed=seed + 1000 * self.dp_rank, cudagraph_capture_sizes=rc.cudagraph_capture_sizes,
-            quantization=_cfg(rc, "quantization", None), **kw)
+            enforce_eager=rc.enforce_eager, seed=seed + 1000 * (self.dp_rank // tp),
+            cudagraph_capture_sizes=rc.cudagraph_capture_sizes, quantization=_cfg(rc, "quantization", None),
+            tp_group=self.tp_group, tp_comm=self.tp_comm, full_config=model_cfg, **kw)
         if rc.free_cache_engine:
             self.rollout_engine.sleep()
 
-    def _bind_rollout_to_flat(self):
+    def _bind_rollout_to_flat(self, tp_rank: int = 0, tp_size: int = 1):
         """Rollout parameters become views into one destination buffer; a weight sync executes a precomputed
-        copy table (trainer shards on all ranks -> this rank's rollout layout) in a single kernel launch."""
+        copy table (trainer shards on all ranks -> this rank's rollout layout, tensor-parallel slices included) in a
+        single kernel launch."""
         from ..parallel.reshard import RolloutWeights
 
-        self._rollout_flat = RolloutWeights(self.model_config, self.actor_engine.zero, self.rollout_model)
+        self._rollout_flat = RolloutWeights(self.model_config, self.actor_engine.zero, self.rollout_model, tp_rank, tp_size)
         self._sync_rollout_weights()
 
     @torch.no_grad()
@@ -253,7 +312,15 @@ class ActorRolloutRefWorker(_WorkerBase):
                             max_tokens=int(meta.get("response_length", rc.response_length)), ignore_eos=rc.ignore_eos)
         ids, mask = prompts.batch["input_ids"], prompts.batch["attention_mask"]
         prompt_lists = [row[m.bool()].tolist() for row, m in zip(ids.cpu(), mask.cpu())]
-        outs = eng.generate(prompt_lists, sp)
+        if self.rollout_tp > 1 and os.environ.get("VERL_B200_SPMD") == "1":
+            # SPMD launch: every rank drives its own share of the batch, but the ranks of a replica must serve the
+            # same requests: pool the replica's prompts, generate once, keep this rank's rows
+            pooled = [None] * self.rollout_tp
+            dist.all_gather_object(pooled, prompt_lists, group=self.tp_group)
+            lo = sum(len(p) for p in pooled[: self.dp_rank % self.rollout_tp])
+            outs = eng.generate([p for part in pooled for p in part], sp)[lo : lo + len(prompt_lists)]
+        else:
+            outs = eng.generate(prompt_lists, sp)
         out = assemble_rollout_batch(ids.cpu(), mask.cpu(), outs, rc.response_length, pad_token_id=meta.get("pad_token_id", 0),
                                      with_logprobs=True)
         gen_time = time.perf_counter() - t0
