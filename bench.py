@@ -304,6 +304,7 @@ def main():
             "clocks": clocks, "gpu_launches": int(launches.item()),
             "breakdown_s": {k.split("/", 1)[1]: round(v, 3) for k, v in last.items() if k.startswith("timing_s/")},
             "rollout_tokens_per_s_per_gpu": last.get("rollout/tokens_per_s"),
+            "rollout_engine": {k.split("engine_", 1)[1]: round(v, 3) for k, v in last.items() if k.startswith("rollout/engine_")},
             "resync_ms": 1e3 * last.get("timing_s/resync", 0.0),
             "mfu_actor": last.get("perf/mfu/actor"),
             "kept_activation_layers": getattr(worker.actor_engine, "last_kept_layers", 0),

@@ -60,10 +60,13 @@ def test_gemm_fp32_accumulate_and_bias():
 
 
 @pytest.mark.parametrize("M,N,K,mode", [(128, 3584, 18944, "tn"), (64, 4608, 3584, "tn"), (7, 520, 2048, "tn"),
-                                        (128, 1024, 4096, "nn"), (200, 640, 8192, "tn")])
+                                        (128, 1024, 4096, "nn"), (200, 640, 8192, "tn"), (128, 3584, 3584, "tn"),
+                                        (256, 2304, 3584, "tn"), (128, 4608, 3584, "tn"), (100, 1796, 1800, "tn")])
 def test_gemm_split_k(M, N, K, mode):
-    """Skinny problems take the split-K path (fp32 slices + last-arriver reduction): same numbers as the
-    fp32 reference, bit-identical between calls, bias / accumulate handled by the reducing CTA."""
+    """Skinny problems split K: over the CTAs of a cluster with the reduction through distributed shared memory
+    (uneven row shares when the slice count does not divide 128, ragged N and K), or, with fp32 accumulation into C,
+    over fp32 slices in a workspace. Same numbers as the fp32 reference, bit-identical between calls, bias handled by
+    the reducing CTA."""
     from verl_b200.ops import gemm, _lib
 
     torch.manual_seed(3)

@@ -60,6 +60,10 @@ struct GemmParams {
   int kb_per_split;
   float* ws;        // [k_splits, num_m * BM, num_n * BN] fp32
   int* counters;    // one per tile, zero before the launch and zero again after it
+  // k_cluster != 0: the k_splits slices of a tile are the CTAs of one thread-block cluster (cluster size = k_splits,
+  // one unit per CTA); the partial tiles stay in shared memory and are added up through distributed shared memory,
+  // every CTA reducing and storing its share of the tile's rows. No workspace, no grid-wide barrier.
+  int k_cluster;
   // EPI_STORE_AG: B = W [N, K] is assembled in ag_dst from the ranks' flat shards while the GEMM runs. Element e of
   // the sharded flat vector lives on rank e / ag_shard at offset e % ag_shard; W starts at element ag_w_off.
   // ag_ready[nb] counts the CTAs that have copied their slice of rows [nb*BN, (nb+1)*BN); a tile may load its B
@@ -527,7 +531,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           tmem_ld_wait();
           const int col0 = nb * BN + c * 32;
           if (EPI == EPI_STORE || EPI == EPI_STORE_AG) {
-            if (sched.k_splits > 1) {
+            if (sched.k_splits > 1 && p.k_cluster) {
+              // fp32 partial tile into the (now idle) pipeline stages: [BM rows][BN / 4 float4], the float4 index
+              // XOR-swizzled by the row so that the 32 rows of a warp do not hit the same banks
+              float4* stg = reinterpret_cast<float4*>(smem);
+              constexpr int SWZ = (BN / 4 >= 32) ? 31 : (BN / 4 - 1);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int j = c * 8 + i;
+                stg[row_in_tile * (BN / 4) + (j ^ (row_in_tile & SWZ))] =
+                    make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
+                                __uint_as_float(r[4 * i + 3]));
+              }
+            } else if (sched.k_splits > 1) {
               // fp32 partial: slice ks of the padded [num_m * BM, num_n * BN] output
               float4* dst = reinterpret_cast<float4*>(
                   p.ws + ((long long)ks * sched.num_m * BM + row) * ((long long)sched.num_n * BN) + col0);
@@ -641,7 +657,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       }
       if (EPI == EPI_STORE || EPI == EPI_STORE_AG) {
-        if (sched.k_splits > 1) {
+        if (sched.k_splits > 1 && !p.k_cluster) {
           // All units have written their fp32 slice. After a grid-wide barrier (the launch is cooperative and every
           // CTA owns exactly one unit) EVERY CTA reduces an equal share of the output: its share of each slice comes
           // back through one bulk async copy into the idle pipeline stages, the slices are summed in slice order
@@ -722,6 +738,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   }
 
+  if (EPI == EPI_STORE && p.k_cluster && sched.k_splits > 1) {
+    // Split-K inside a cluster: every CTA has left its fp32 partial tile in its own shared memory. After a cluster
+    // barrier CTA r adds up rows [r * rows_per, (r + 1) * rows_per) of all CTAs' tiles (slice order: deterministic)
+    // through distributed shared memory and stores them; a second barrier keeps every CTA's shared memory alive
+    // until its peers have read it. All threads of the CTA take part in both barriers.
+    cluster_sync_all();
+    if (warp >= 2 && warp < 6) {
+      const int et = threadIdx.x - 64;
+      const int S = sched.k_splits;
+      const int cr = (int)cluster_ctarank();
+      int m_blk, n_first, n_count, split;
+      sched.get((int)blockIdx.x, m_blk, n_first, n_count, split);
+      const int rows_per = (BM + S - 1) / S;
+      const int r0 = cr * rows_per, r1 = min(BM, r0 + rows_per);
+      constexpr int Q4 = BN / 4;
+      constexpr int SWZ = (Q4 >= 32) ? 31 : (Q4 - 1);
+      const float4* stg = reinterpret_cast<const float4*>(smem);
+      for (int idx = et; idx < (r1 - r0) * Q4; idx += 128) {
+        const int rr = r0 + idx / Q4, j = idx % Q4;
+        const uint32_t local = smem_u32(stg + rr * Q4 + (j ^ (rr & SWZ)));
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp = 0; sp < S; ++sp) {
+          const uint32_t remote = map_to_cta(local, (uint32_t)sp);
+          float4 v;
+          asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                       : "r"(remote)
+                       : "memory");
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const int grow = m_blk * BM + rr, gcol = n_first * BN + j * 4;
+        if (grow < p.M && gcol < p.N) epi_store4(p, grow, gcol, acc);
+      }
+    }
+    cluster_sync_all();
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -1045,6 +1097,24 @@ static int launch_gemm(const void* A, const void* B, long long lda, long long ld
   const int units = (EPI == EPI_LSE) ? num_m * p.num_splits : num_m * num_n * (p.k_splits > 1 ? p.k_splits : 1);
   if (units <= 0) return 0;
   const int grid = units < vb_num_sms() ? units : vb_num_sms();
+  if (EPI == EPI_STORE && p.k_splits > 1 && p.k_cluster) {
+    // one cluster per output tile, one CTA per k slice; clusters are scheduled as SMs free up (no grid-wide barrier)
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(units);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = dyn_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.k_splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+    vb_count_launch();
+    return (int)e;
+  }
   if (EPI == EPI_STORE && p.k_splits > 1) {
     // the split-K reduction has a grid-wide barrier: every CTA owns one unit and all of them must be resident
     if (units > vb_num_sms()) return -3;
@@ -1101,6 +1171,33 @@ static int gemm_bf16_run(const void* A, const void* B, void* C, const void* bias
     const char* e = getenv("VERL_B200_SPLITK");  // 0 = never split K, N > 1 = force that many slices (experiments)
     return e ? atoi(e) : -1;
   }();
+  static const bool cluster_sk = []() {
+    const char* e = getenv("VERL_B200_SPLITK_CLUSTER");  // 0 = workspace + grid-barrier reduction (the older path)
+    return !(e && e[0] == '0');
+  }();
+  if (cluster_sk && splitk_mode != 0 && !accumulate && N > 128) {
+    // Skinny problems (decode projections): split K over the CTAs of a cluster and reduce through distributed shared
+    // memory. As many slices as fill the SMs once, at most 8 (portable cluster size), at least 4 k-blocks per slice.
+    const int nm = (M + BM - 1) / BM, nkb = (K + BK - 1) / BK;
+    const int tiles = nm * ((N + 127) / 128);
+    int splits = vb_num_sms() / (tiles > 0 ? tiles : 1);
+    if (splits > 8) splits = 8;
+    if (splits > nkb / 4) splits = nkb / 4;
+    if (splitk_mode > 1) splits = splitk_mode > 8 ? 8 : splitk_mode;
+    if (splits >= 2) {
+      const int per = (nkb + splits - 1) / splits;
+      splits = (nkb + per - 1) / per;
+      if (splits >= 2) {
+        p.k_splits = splits;
+        p.kb_per_split = per;
+        p.k_cluster = 1;
+        if (!a_mn && !b_mn) return launch_gemm<128, false, false, EPI_STORE>(A, B, lda, ldb, p, stream);
+        if (!a_mn && b_mn) return launch_gemm<128, false, true, EPI_STORE>(A, B, lda, ldb, p, stream);
+        if (a_mn && b_mn) return launch_gemm<128, true, true, EPI_STORE>(A, B, lda, ldb, p, stream);
+        return launch_gemm<128, true, false, EPI_STORE>(A, B, lda, ldb, p, stream);
+      }
+    }
+  }
   if (ws != nullptr && counters != nullptr && splitk_mode != 0) {
     // Split K when the output tiles alone leave most SMs idle and K is deep enough to cut. 128-wide tiles by
     // default; VERL_B200_SPLITK_BN=256 selects 256-wide ones (fewer re-reads of A, but more slices to reduce).

@@ -83,8 +83,18 @@ def bench_lmhead(a):
     w = torch.randn(V, H, device=dev, dtype=torch.bfloat16) * 0.02
     labels = torch.randint(0, V, (T,), device=dev)
     us = _time(lambda: lmhead_logprob_entropy(h, w, labels, 1.0), a.iters, a.warmup, graph=False)
+    hg, wg = h.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    g_lp = torch.rand(T, device=dev)
+
+    def fwd_bwd():
+        hg.grad = wg.grad = None
+        lp, ent = lmhead_logprob_entropy(hg, wg, labels, 1.0)
+        lp.backward(g_lp)
+
+    us_fb = _time(fwd_bwd, max(a.iters // 4, 3), a.warmup, graph=False)
     return {"kernel": "lmhead_logprob_fwd", "T": T, "H": H, "V": V, "us": round(us, 1),
-            "tflops": round(2.0 * T * H * V / us / 1e6, 1)}
+            "tflops": round(2.0 * T * H * V / us / 1e6, 1), "fwd_bwd_us": round(us_fb, 1),
+            "fwd_bwd_tflops": round(6.0 * T * H * V / us_fb / 1e6, 1)}
 
 
 def bench_decode(a):

@@ -248,7 +248,8 @@ class NativeRolloutEngine:
         self._graphs: dict[int, tuple] = {}
         self._capture_sizes = cudagraph_capture_sizes
         self.step_counter = torch.zeros(1, dtype=torch.long, device=self.device)
-        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0}
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "step_s": 0.0,
+                      "decode_wait_s": 0.0, "prefill_s": 0.0}
         if self.tp > 1 and self.on_gpu:
             if tp_comm is None:
                 raise ValueError("a tensor-parallel rollout replica on CUDA needs its peer-memory communicator (tp_comm)")
@@ -645,6 +646,7 @@ class NativeRolloutEngine:
     def step(self) -> list[TokenOutput]:
         """One scheduler iteration. Returns the requests that finished in it."""
         sc = self.sched
+        t_step = time.perf_counter()
         n, _ = sc.step()
         if n == 0:
             return []
@@ -692,8 +694,11 @@ class NativeRolloutEngine:
                 else:
                     run()
             st["out_host"].copy_(st["out_dev"], non_blocking=True)
+            t_wait = time.perf_counter()
             if dev.type == "cuda":
                 torch.cuda.current_stream(dev).synchronize()
+            self.stats["decode_wait_s"] += time.perf_counter() - t_wait
+            self.stats["decode_steps"] += k
             if k > 1:
                 burst = (k, st["host_tok"][:k, :nd].copy(), st["host_lp"][:k, :nd].copy(), sps)
             else:
@@ -701,8 +706,11 @@ class NativeRolloutEngine:
                 new_lps[di] = st["host_lp"][0, :nd]
             self.stats["decode_tokens"] += nd * k
         if burst is not None:
-            return self._commit_burst(n, *burst)
+            outs = self._commit_burst(n, *burst)
+            self.stats["step_s"] += time.perf_counter() - t_step
+            return outs
         if pre:
+            t_pre = time.perf_counter()
             logits = self._prefill_forward(pre, [tok_lo[i] for i in pre])
             # only chunks that complete their sequence sample a token
             sps = [self.requests[int(sc.seq_ids[i])].params for i in pre]
@@ -714,6 +722,7 @@ class NativeRolloutEngine:
             new_tokens[np.asarray(pre)] = tok.cpu().numpy()
             new_lps[np.asarray(pre)] = lp.cpu().numpy()
             self.stats["prefill_tokens"] += int(sum(sc.seq_ntok[i] for i in pre))
+            self.stats["prefill_s"] += time.perf_counter() - t_pre
         # stop criteria
         finished = np.zeros(n, np.int32)
         reasons = {}
@@ -735,6 +744,7 @@ class NativeRolloutEngine:
                 req.logprobs.append(lps[i])
             if done[i]:
                 outs.append(self._finish(sids[i], reasons.get(sids[i], "length")))
+        self.stats["step_s"] += time.perf_counter() - t_step
         return outs
 
     def _commit_burst(self, n: int, k: int, toks: np.ndarray, lps: np.ndarray, sps: list) -> list[TokenOutput]:

@@ -178,10 +178,6 @@ class RayPPOTrainer:
             from ...single_controller.mp import MPWorkerGroup as ray_worker_group_cls
         self.ray_worker_group_cls = ray_worker_group_cls
         self.spmd = bool(getattr(ray_worker_group_cls, "is_spmd", False))
-        sp = int((config.actor_rollout_ref.actor.get("fsdp_config") or {}).get("ulysses_sequence_parallel_size", 1) or 1)
-        if self.spmd and sp > 1 and int(os.environ.get("WORLD_SIZE", "1")) > 1:
-            raise NotImplementedError("ulysses_sequence_parallel_size > 1 needs the dispatching worker group (every rank of a "
-                                      "sequence-parallel group must see the same samples); launch without torchrun")
         self.device_name = device_name or config.trainer.get("device", "cuda")
         self.hybrid_engine = config.actor_rollout_ref.hybrid_engine
         assert self.hybrid_engine, "Currently, only support hybrid engine"

@@ -89,7 +89,7 @@ class _WorkerBase(Worker):
         (verl/workers/fsdp_workers.py:239-273)."""
         eng_cfg = _cfg(cfg, "fsdp_config", None) or _cfg(_cfg(cfg, "model", None), "fsdp_config", None)
         sp = int(_cfg(eng_cfg, "ulysses_sequence_parallel_size", 1) or 1) if eng_cfg is not None else 1
-        sp = int(_cfg(cfg, "ulysses_sequence_parallel_size", sp) or sp)
+        sp = max(sp, int(_cfg(cfg, "ulysses_sequence_parallel_size", 1) or 1))
         dp = max(self.world // max(sp, 1), 1)
         mini = int(getattr(cfg, mini_key)) * n // dp
         assert mini > 0, f"{mini_key} {getattr(cfg, mini_key)} * n {n} must be >= data-parallel size {dp}"
@@ -101,6 +101,36 @@ class _WorkerBase(Worker):
         per_gpu = getattr(cfg, micro_key + "_per_gpu", None)
         if per_gpu is not None and not getattr(cfg, "use_dynamic_bsz", False):
             assert mini % per_gpu == 0, f"normalized {mini_key} {mini} should be divisible by {micro_key}_per_gpu {per_gpu}"
+
+
+def _spmd() -> bool:
+    return os.environ.get("VERL_B200_SPMD") == "1"
+
+
+def sp_pool(data: DataProto, engine) -> tuple[DataProto, Optional[tuple]]:
+    """SPMD launch with Ulysses: every rank drives its own share of the batch, but the ranks of a sequence-parallel
+    group must work on the same samples. Pool the group's shares (rank order); :func:`sp_unpool` hands every rank the
+    rows of its own share back. A no-op under the dispatching worker group (the dispatch already sends a group the
+    same samples) and without sequence parallelism."""
+    sp = int(getattr(engine, "sp_size", 1) or 1)
+    if sp <= 1 or not _spmd():
+        return data, None
+    parts = [None] * sp
+    dist.all_gather_object(parts, data, group=engine.sp_group)
+    pooled = DataProto.concat(parts)
+    pooled.meta_info = dict(data.meta_info)
+    tok = pooled.meta_info.get("global_token_num")
+    if tok is not None and data.meta_info.get("token_num_is_local"):
+        pooled.meta_info["global_token_num"] = [t for p in parts for t in (p.meta_info.get("global_token_num") or [])]
+    lo = sum(len(p) for p in parts[: engine.sp_rank])
+    return pooled, (lo, len(data))
+
+
+def sp_unpool(out: DataProto, info: Optional[tuple]) -> DataProto:
+    if info is None or out.batch is None:
+        return out
+    lo, n = info
+    return out[lo : lo + n]
 
 
 class ActorRolloutRefWorker(_WorkerBase):
@@ -302,6 +332,7 @@ class ActorRolloutRefWorker(_WorkerBase):
         eng = self.rollout_engine
         t0 = time.perf_counter()
         eng.wake_up()
+        stats0 = dict(eng.stats)
         meta = prompts.meta_info
         validate = meta.get("validate", False)
         do_sample = meta.get("do_sample", rc.do_sample if not validate else rc.val_kwargs.do_sample)
@@ -329,6 +360,8 @@ class ActorRolloutRefWorker(_WorkerBase):
         out.meta_info["metrics"] = {"rollout/generate_sequences_s": gen_time,
                                     "rollout/num_preempted": float(sum(o.num_preempted for o in outs)),
                                     "rollout/tokens_per_s": n_tok / max(gen_time, 1e-9)}
+        for k_ in ("step_s", "decode_wait_s", "prefill_s", "decode_steps", "steps"):  # where the engine's time went
+            out.meta_info["metrics"][f"rollout/engine_{k_}"] = float(eng.stats[k_] - stats0[k_])
         if rc.free_cache_engine and not meta.get("keep_cache", False):
             eng.sleep()
         return out
@@ -344,29 +377,32 @@ class ActorRolloutRefWorker(_WorkerBase):
     def compute_log_prob(self, data: DataProto) -> DataProto:
         assert self._is_actor
         self._lp_meta(data, self.rollout_cfg if self.rollout_cfg is not None else self.config.rollout)
+        data, pooled = sp_pool(data, self.actor_engine)
         with self.actor_engine.eval_mode():
             lp, ent = self.actor.compute_log_prob(data, calculate_entropy=True)
         out = DataProto.from_dict(tensors={"old_log_probs": lp.cpu(), "entropys": ent.cpu()},
                                   meta_info={"temperature": data.meta_info["temperature"]})
-        return out
+        return sp_unpool(out, pooled)
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("ref"))
     def compute_ref_log_prob(self, data: DataProto) -> DataProto:
         assert self._is_ref
         self._lp_meta(data, self.ref_cfg or self.config.ref)
+        data, pooled = sp_pool(data, self.ref_engine if self.ref_engine is not None else self.actor_engine)
         if self.ref_engine is None:  # LoRA: frozen base weights of the actor engine
             with self.actor_engine.eval_mode(), self.actor_engine.disable_adapter():
                 lp, _ = self.actor.compute_log_prob(data, calculate_entropy=False)
-            return DataProto.from_dict(tensors={"ref_log_prob": lp.cpu()})
+            return sp_unpool(DataProto.from_dict(tensors={"ref_log_prob": lp.cpu()}), pooled)
         with self.ref_engine.eval_mode():
             lp, _ = self.ref_policy.compute_log_prob(data, calculate_entropy=False)
-        return DataProto.from_dict(tensors={"ref_log_prob": lp.cpu()})
+        return sp_unpool(DataProto.from_dict(tensors={"ref_log_prob": lp.cpu()}), pooled)
 
     # ------------------------------------------------------------------ update
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("actor"))
     def update_actor(self, data: DataProto) -> DataProto:
         assert self._is_actor
         data.meta_info.setdefault("temperature", _cfg(self.config.get("rollout", {}), "temperature", 1.0))
+        data, _ = sp_pool(data, self.actor_engine)
         t0 = time.perf_counter()
         with self.actor_engine.train_mode():
             metrics = self.actor.update_policy(data)
@@ -379,7 +415,9 @@ class ActorRolloutRefWorker(_WorkerBase):
             from ..utils.flops_counter import FlopsCounter
 
             est, promised = FlopsCounter(self.model_config).estimate_flops(tokens, dt)
-            denom = 1 if data.meta_info.get("token_num_is_local") else self.world
+            # tokens of this call's batch are processed by `sp` ranks (local counts) or by the whole job (global counts)
+            denom = max(int(getattr(self.actor_engine, "sp_size", 1) or 1), 1) if data.meta_info.get("token_num_is_local") \
+                else self.world
             metrics["perf/mfu/actor"] = est * self.actor_cfg.ppo_epochs / promised / denom
         return DataProto(meta_info={"metrics": metrics})
 
@@ -488,12 +526,14 @@ class CriticWorker(_WorkerBase):
         data.meta_info.setdefault("micro_batch_size", c.forward_micro_batch_size_per_gpu or c.ppo_micro_batch_size_per_gpu)
         data.meta_info.setdefault("max_token_len", c.forward_max_token_len_per_gpu)
         data.meta_info.setdefault("use_dynamic_bsz", c.use_dynamic_bsz)
+        data, pooled = sp_pool(data, self.engine)
         with self.engine.eval_mode():
             values = self.critic.compute_values(data)
-        return DataProto.from_dict(tensors={"values": values.cpu()})
+        return sp_unpool(DataProto.from_dict(tensors={"values": values.cpu()}), pooled)
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("critic"))
     def update_critic(self, data: DataProto) -> DataProto:
+        data, _ = sp_pool(data, self.engine)
         with self.engine.train_mode():
             metrics = self.critic.update_critic(data)
         metrics["critic/lr"] = self.engine._lr()
