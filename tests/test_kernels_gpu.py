@@ -344,7 +344,10 @@ def test_sampler_distribution_and_modes():
 
 @pytest.mark.parametrize("B,Hq,Hk,D,bs,maxlen", [(5, 28, 4, 128, 16, 700), (3, 4, 2, 64, 16, 300), (2, 32, 4, 128, 32, 3000),
                                                  (4, 40, 8, 128, 16, 150), (3, 32, 2, 128, 128, 1000),
-                                                 (2, 8, 8, 128, 8, 260)])
+                                                 (2, 8, 8, 128, 8, 260),
+                                                 # more (sequence, head, split) items than resident CTAs: the
+                                                 # persistent kernel (CTAs walk several items, some of them empty)
+                                                 (100, 28, 4, 128, 16, 700), (80, 32, 8, 128, 16, 300)])
 def test_paged_decode_attention(B, Hq, Hk, D, bs, maxlen):
     from verl_b200 import ops
 

@@ -346,6 +346,112 @@ class NativeEngine(BaseEngine):
         return self._sp_merge(unit_call(z, self._head_unit, lambda h, r: m.logits(m.final_norm(h, r)), hidden, residual))
 
     # --------------------------------------------------------- response bookkeeping
+    # ----------------------------------------------------------- TensorDict batch interface
+    def forward_backward_batch(self, data, loss_function=None, forward_only: bool = False) -> dict:
+        """One pass over a batch in the no-padding layout (verl/workers/engine/fsdp/transformer_impl.py:
+        forward_backward_batch + prepare_model_inputs / prepare_model_outputs).
+
+        ``data``: TensorDict with ``input_ids`` as a jagged nested tensor ``[bsz, j]`` (optionally ``position_ids``),
+        the loss inputs (``loss_mask`` nested for SFT; ``prompts / responses / response_mask / attention_mask / ...``
+        for RL losses), and the non-tensor knobs ``use_dynamic_bsz``, ``max_token_len_per_gpu``,
+        ``micro_batch_size_per_gpu``, ``temperature``, ``calculate_entropy``.
+
+        The model outputs handed to ``loss_function(model_output=..., data=micro_batch, dp_group=...)`` are nested
+        tensors aligned with ``input_ids``: ``log_probs[i][t]`` is the log-probability of token ``t + 1`` of sample
+        ``i`` (``entropy`` likewise), ``values[i][t]`` for a value head. Returns ``{"loss": [per micro-batch],
+        "model_output": {...concatenated nested tensors...}, "metrics": {name: [per micro-batch]}}``."""
+        import torch.distributed as dist
+
+        from ...utils import tensordict_utils as tu
+
+        ids = data["input_ids"]
+        assert ids.is_nested, "the engine's batch interface takes input_ids as a jagged nested tensor (no padding)"
+        temperature = float(tu.get(data, "temperature", 1.0) or 1.0)
+        calc_ent = bool(tu.get(data, "calculate_entropy", False))
+        lens = ids.offsets().diff()
+        # global normalisers of the loss (sum over the data-parallel group): tokens that count, samples
+        if "loss_mask" in data.keys():
+            counted = float(data["loss_mask"].values().sum())
+        elif "response_mask" in data.keys():
+            counted = float(data["response_mask"].sum())
+        else:
+            counted = float(lens.sum())
+        norm = torch.tensor([counted, float(len(lens))], dtype=torch.float64, device=self.device)
+        dp_group = self.get_data_parallel_group()
+        dp = self.get_data_parallel_size()
+        if self.zero.world > 1:
+            dist.all_reduce(norm, group=self.group)
+            norm = norm / max(self.sp_size, 1)
+        # micro-batches: fixed sample count, or packed up to a token budget
+        n = len(lens)
+        if tu.get(data, "use_dynamic_bsz", False):
+            budget = int(tu.get(data, "max_token_len_per_gpu", 16384) or 16384)
+            groups, cur, tok = [], [], 0
+            for i, L in enumerate(lens.tolist()):
+                if cur and tok + L > budget:
+                    groups.append(cur)
+                    cur, tok = [], 0
+                cur.append(i)
+                tok += L
+            if cur:
+                groups.append(cur)
+        else:
+            mb = int(tu.get(data, "micro_batch_size_per_gpu", None) or n)
+            groups = [list(range(i, min(i + mb, n))) for i in range(0, n, mb)]
+        out = {"loss": [], "metrics": {}, "model_output": {}}
+        pieces: dict = {}
+        for g in groups:
+            micro = data[torch.tensor(g)]
+            mids = micro["input_ids"]
+            vals, offs = mids.values().to(self.device), mids.offsets().to(self.device)
+            if "position_ids" in micro.keys() and micro["position_ids"].is_nested:
+                pos = micro["position_ids"].values().to(self.device)
+            else:
+                mlens = offs.diff()
+                pos = torch.arange(vals.numel(), device=self.device) - torch.repeat_interleave(offs[:-1], mlens)
+            packed = PackedBatch(vals, pos, offs.int(), int(offs.diff().max().item()))
+            rows = torch.arange(vals.numel(), device=self.device)
+
+            def nest(t):
+                return torch.nested.nested_tensor_from_jagged(t, offsets=offs)
+
+            if self.model.value_head:
+                model_output = {"values": nest(self.forward_values(packed, rows))}
+            else:
+                labels = torch.roll(vals, -1)
+                lp, ent = self.forward_logprob(packed, rows, labels, temperature)
+                model_output = {"log_probs": nest(lp)}
+                if calc_ent and ent is not None:
+                    model_output["entropy"] = nest(ent)
+            for k, v in model_output.items():
+                pieces.setdefault(k, []).append(v.detach())
+            if loss_function is not None:
+                tu.assign_non_tensor(micro, dp_size=dp, batch_num_tokens=float(norm[0]), global_batch_size=float(norm[1]))
+                loss, metrics = loss_function(model_output=model_output, data=micro, dp_group=dp_group)
+                if not forward_only:
+                    loss.backward()
+                out["loss"].append(float(loss.detach()))
+                for k, v in (metrics or {}).items():
+                    out["metrics"].setdefault(k, []).append(float(v) if not isinstance(v, (list, dict)) else v)
+        for k, v in pieces.items():
+            out["model_output"][k] = tu.concat_nested_tensors(v) if len(v) > 1 else v[0]
+        return out
+
+    def train_batch(self, data, loss_function) -> dict:
+        """zero-grad -> forward / backward over the micro-batches -> optimizer step (BaseEngine.train_batch of the
+        reference); ``metrics["grad_norm"]`` is added."""
+        self.optimizer_zero_grad()
+        out = self.forward_backward_batch(data, loss_function, forward_only=False)
+        out["metrics"]["grad_norm"] = float(self.optimizer_step())
+        return out
+
+    def infer_batch(self, data, loss_function=None) -> dict:
+        with torch.no_grad():
+            return self.forward_backward_batch(data, loss_function, forward_only=True)
+
+    def is_mp_src_rank_with_outputs(self) -> bool:
+        return self.sp_rank == 0
+
     @staticmethod
     def response_rows(input_ids: torch.Tensor, attention_mask: torch.Tensor, response_length: int,
                       position_ids: Optional[torch.Tensor] = None):
