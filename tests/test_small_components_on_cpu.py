@@ -436,3 +436,41 @@ def test_mcp_search_parse_weight_keys_and_sharding_manager():
     d = DataProto.from_dict({"x": torch.arange(4)})
     with mgr:
         assert mgr.postprocess_data(mgr.preprocess_data(d)) is d
+
+
+def test_hf_rollout_greedy_matches_paged_engine_and_honours_sampling_modes():
+    import torch
+
+    from verl_b200 import DataProto
+    from verl_b200.models import CausalLM, preset
+    from verl_b200.rollout import NativeRolloutEngine, SamplingParams
+    from verl_b200.workers.rollout.base import get_rollout_class
+
+    cfg = preset("tiny-qwen2")
+    model = CausalLM(cfg, dtype=torch.float32).init_weights(2)
+    HF = get_rollout_class("hf", "sync")
+    ro = HF(model, {"response_length": 6, "micro_batch_size": 2, "do_sample": True, "temperature": 1.0, "top_k": 0, "top_p": 0.9,
+                    "val_kwargs": {"temperature": 0.0001, "top_k": 1, "top_p": 1.0}}, model_config=cfg)
+    g = torch.Generator().manual_seed(0)
+    lens = [5, 8, 3, 8]
+    ids = torch.zeros(4, 8, dtype=torch.long)
+    mask = torch.zeros(4, 8, dtype=torch.long)
+    for i, n in enumerate(lens):  # left padding
+        ids[i, 8 - n:] = torch.randint(3, 2000, (n,), generator=g)
+        mask[i, 8 - n:] = 1
+    batch = DataProto.from_dict({"input_ids": ids, "attention_mask": mask, "position_ids": (mask.cumsum(-1) - 1).clamp(min=0)},
+                                meta_info={"eos_token_id": 2, "pad_token_id": 0, "do_sample": False})
+    out = ro.generate_sequences(batch)
+    assert out.batch["responses"].shape == (4, 6) and out.batch["input_ids"].shape == (4, 14)
+    eng = NativeRolloutEngine(model, max_num_seqs=4, max_model_len=32, max_num_batched_tokens=64, num_blocks=32)
+    ref = eng.generate([ids[i][mask[i].bool()].tolist() for i in range(4)], SamplingParams(temperature=0.0, max_tokens=6))
+    for i, o in enumerate(ref):
+        n = len(o.token_ids)
+        assert out.batch["responses"][i, :n].tolist() == o.token_ids
+        assert int(out.batch["response_mask"][i].sum()) == n
+    # validation sampling with top_k = 1 is greedy as well; plain sampling stays inside the top-p nucleus (finite lps)
+    batch.meta_info.update({"do_sample": True, "validate": True})
+    assert torch.equal(ro.generate_sequences(batch).batch["responses"], out.batch["responses"])
+    batch.meta_info.update({"validate": False, "num_return_sequences": 2})
+    s = ro.generate_sequences(batch)
+    assert len(s) == 8 and torch.isfinite(s.batch["rollout_log_probs"]).all()

@@ -74,6 +74,11 @@ def save_engine_checkpoint(engine, local_path: str, global_step: int = 0,
     if dist.is_initialized():
         dist.barrier()
     W, r = z.world, z.rank
+    if getattr(engine, "hsdp", False) and getattr(engine, "replica_index", 0) != 0:
+        # hybrid sharding: the replicas hold identical shards; the first replica group writes the files
+        if dist.is_initialized():
+            dist.barrier()
+        return
     if "fsdp_model" in save_contents:
         # torch-FSDP shard files (HF names, dim-0 DTensor shards): what the reference's loader and merger read
         from .reference_fsdp import save_reference_fsdp_shards

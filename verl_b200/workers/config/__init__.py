@@ -98,8 +98,9 @@ class EngineConfig(BaseConfig):
 @dataclass
 class FSDPEngineConfig(EngineConfig):
     """Sharded data-parallel engine options. ``strategy`` accepts fsdp / fsdp2 (both map to the native
-    ZeRO-3 engine here). ``fsdp_size`` is accepted for config compatibility: parameters are always sharded over the
-    whole data-parallel group (one NVSwitch box), there are no replicated shard groups."""
+    ZeRO-3 engine here). ``fsdp_size`` in ``[1, world)`` selects hybrid sharding: parameters, gradients and optimizer
+    state are sharded over ``fsdp_size`` consecutive ranks and replicated over the ``world / fsdp_size`` groups;
+    -1 (default) shards over the whole data-parallel group."""
 
     wrap_policy: dict = field(default_factory=dict)
     offload_policy: bool = False

@@ -132,7 +132,8 @@ class NativeEngine(BaseEngine):
             else:
                 head.append(("lm_head.weight", m.lm_head.weight))
             units.append(("", head))
-        self.zero = ZeroShardedParams(units, group=self.group, work_dtype=self.work_dtype, device=self.device,
+        self._setup_hybrid_sharding()
+        self.zero = ZeroShardedParams(units, group=self.shard_group, work_dtype=self.work_dtype, device=self.device,
                                       trainable=self.trainable and not self._lora_params, comm=self.comm)
         self.zero.frozen_grad = bool(self._lora_params)
         self._setup_sequence_parallel()
@@ -156,7 +157,43 @@ class NativeEngine(BaseEngine):
 
     @property
     def world(self) -> int:
-        return self.zero.world
+        """Ranks of the engine's group (data parallel x sequence parallel); under hybrid sharding this is larger than
+        ``zero.world``, the number of ranks over which the parameters are sharded."""
+        return self.dp_world
+
+    def _setup_hybrid_sharding(self):
+        """``fsdp_size`` < world (HSDP, verl/workers/fsdp_workers.py:98-108 ``create_device_mesh``): parameters,
+        gradients and optimizer state are sharded over ``fsdp_size`` consecutive ranks and replicated across the
+        ``world / fsdp_size`` groups; the replicas' gradient shards are summed before the optimizer step."""
+        import torch.distributed as dist
+
+        self.dp_world = dist.get_world_size(self.group) if self.group is not None else 1
+        self.dp_rank_all = dist.get_rank(self.group) if self.group is not None else 0
+        self.shard_group, self.replica_group, self.hsdp = self.group, None, False
+        fs = int(_cfg(self.engine_config, "fsdp_size", -1) or -1)
+        W = self.dp_world
+        if fs <= 0 or fs >= W:
+            return
+        if W % fs != 0:
+            raise ValueError(f"fsdp_size {fs} does not divide the {W} ranks of the engine's group")
+        ranks_of = dist.get_process_group_ranks(self.group)
+        r = self.dp_rank_all
+        for g in range(W // fs):  # collective: every rank creates every group
+            grp = dist.new_group([ranks_of[g * fs + i] for i in range(fs)])
+            if r // fs == g:
+                self.shard_group = grp
+        for i in range(fs):
+            grp = dist.new_group([ranks_of[g * fs + i] for g in range(W // fs)])
+            if r % fs == i:
+                self.replica_group = grp
+        self.hsdp = True
+        self.replica_index = r // fs
+        if self.comm is not None and self.device.type == "cuda":
+            from ...parallel.peer_comm import PeerComm
+
+            self.comm = PeerComm(self.shard_group) if fs > 1 else None  # the sharder's collectives stay in the group
+        if fs == 1:
+            self.comm = None
 
     def _setup_sequence_parallel(self):
         """Ulysses: ``ulysses_sequence_parallel_size`` consecutive ranks form a group that works on the same
@@ -167,9 +204,9 @@ class NativeEngine(BaseEngine):
 
         sp = int(_cfg(self.engine_config, "ulysses_sequence_parallel_size", 1) or 1)
         self.sp_size, self.sp_group, self.sp_rank = 1, None, 0
-        if sp <= 1 or self.zero.world <= 1:
+        if sp <= 1 or self.dp_world <= 1:
             return
-        W, r = self.zero.world, self.zero.rank
+        W, r = self.dp_world, self.dp_rank_all
         assert W % sp == 0, f"world size {W} is not a multiple of ulysses_sequence_parallel_size {sp}"
         from ...utils.ulysses import validate_ulysses_config
 
@@ -185,10 +222,10 @@ class NativeEngine(BaseEngine):
             layer.self_attn.sp_group = self.sp_group
 
     def get_data_parallel_size(self) -> int:
-        return self.zero.world // self.sp_size
+        return self.dp_world // self.sp_size
 
     def get_data_parallel_rank(self) -> int:
-        return self.zero.rank // self.sp_size
+        return self.dp_rank_all // self.sp_size
 
     def get_data_parallel_group(self):
         return self.group
@@ -379,7 +416,7 @@ class NativeEngine(BaseEngine):
         norm = torch.tensor([counted, float(len(lens))], dtype=torch.float64, device=self.device)
         dp_group = self.get_data_parallel_group()
         dp = self.get_data_parallel_size()
-        if self.zero.world > 1:
+        if self.dp_world > 1:
             dist.all_reduce(norm, group=self.group)
             norm = norm / max(self.sp_size, 1)
         # micro-batches: fixed sample count, or packed up to a token budget
@@ -484,7 +521,7 @@ class NativeEngine(BaseEngine):
         clip = float(_cfg(oc, "clip_grad", 1.0))
         grads = [p.grad if p.grad is not None else torch.zeros_like(p) for p in self._lora_params]
         flat = torch.cat([g.reshape(-1) for g in grads])
-        if self.zero.world > 1:
+        if self.dp_world > 1:
             dist.all_reduce(flat, group=self.group)
         norm = flat.double().norm().float()
         self.step_count += 1
@@ -561,19 +598,23 @@ class NativeEngine(BaseEngine):
         eps = float(_cfg(oc, "eps", 1e-8))
         self.step_count += 1
         z.wait_comm()  # the last reduce-scatters run on the communication stream
+        if self.hsdp:  # hybrid sharding: add up the replicas' gradient shards (the loss is normalised globally)
+            dist.all_reduce(z.grad, group=self.replica_group)
         if self.device.type == "cuda":
             self._sumsq.zero_()
             ops.sumsq_into(z.grad, self._sumsq)
             if z.world > 1:
-                dist.all_reduce(self._sumsq, group=self.group)
+                dist.all_reduce(self._sumsq, group=self.shard_group)
             ops.clip_coef(self._sumsq, clip, 1.0, self._scale, self._skip, self._norm)
             ops.adamw_step(z.master, z.grad, z.exp_avg, z.exp_avg_sq, z.shard16, lr=lr, betas=betas, eps=eps,
                            weight_decay=wd, step=self.step_count, scale=self._scale, skip=self._skip)
             norm = self._norm
+            if int(self._skip.item()):  # a non-finite norm skipped the update: the step does not count
+                self.step_count -= 1
         else:
             sq = z.grad.double().pow(2).sum().reshape(1)
             if z.world > 1:
-                dist.all_reduce(sq, group=self.group)
+                dist.all_reduce(sq, group=self.shard_group)
             norm = sq.sqrt().float()
             if torch.isfinite(norm).all():
                 coef = min(1.0, clip / (norm.item() + 1e-6)) if clip > 0 else 1.0
