@@ -1135,6 +1135,51 @@ static int launch_gemm(const void* A, const void* B, long long lda, long long ld
   return (int)cudaGetLastError();
 }
 
+
+// Number of clusters of `cluster` CTAs of the plain-store GEMM kernel with BN-wide tiles that the device can hold at
+// once (one CTA per SM because of its shared memory; a cluster must fit inside one GPC). Cached; 0 if the query fails.
+static int max_active_clusters(int bn, int cluster) {
+  static int cache[2][9];
+  static bool init = false;
+  if (!init) {
+    for (auto& row : cache)
+      for (int& v : row) v = -1;
+    init = true;
+  }
+  if (cluster < 1 || cluster > 8 || (bn != 128 && bn != 64)) return 0;
+  int& slot = cache[bn == 128 ? 0 : 1][cluster];
+  if (slot >= 0) return slot;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(cluster * 64);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  cudaError_t e;
+  if (bn == 128) {
+    auto kern = gemm_kernel<128, false, false, EPI_STORE>;
+    cfg.dynamicSmemBytes = SmemLayout<128>::DYN_BYTES;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<128>::DYN_BYTES + RS_STAGE_BYTES);
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+  } else {
+    auto kern = gemm_kernel<64, false, false, EPI_STORE>;
+    cfg.dynamicSmemBytes = SmemLayout<64>::DYN_BYTES;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<64>::DYN_BYTES + RS_STAGE_BYTES);
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+  }
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    n = 0;
+  }
+  slot = n;
+  return n;
+}
+
 }  // namespace vb
 
 using namespace vb;
@@ -1177,25 +1222,43 @@ static int gemm_bf16_run(const void* A, const void* B, void* C, const void* bias
   }();
   if (cluster_sk && splitk_mode != 0 && !accumulate && N > 128) {
     // Skinny problems (decode projections): split K over the CTAs of a cluster and reduce through distributed shared
-    // memory. As many slices as fill the SMs once, at most 8 (portable cluster size), at least 4 k-blocks per slice.
+    // memory. Among tile widths {128, 64} and cluster sizes 2..8 take the pair that puts the most CTAs to work in ONE
+    // wave: a cluster needs all its SMs free inside one GPC at once, so the number of co-resident clusters (asked
+    // from the occupancy calculator, cached) bounds the tile count; a second wave would cost more than it gains.
     const int nm = (M + BM - 1) / BM, nkb = (K + BK - 1) / BK;
-    const int tiles = nm * ((N + 127) / 128);
-    int splits = vb_num_sms() / (tiles > 0 ? tiles : 1);
-    if (splits > 8) splits = 8;
-    if (splits > nkb / 4) splits = nkb / 4;
-    if (splitk_mode > 1) splits = splitk_mode > 8 ? 8 : splitk_mode;
-    if (splits >= 2) {
-      const int per = (nkb + splits - 1) / splits;
-      splits = (nkb + per - 1) / per;
-      if (splits >= 2) {
-        p.k_splits = splits;
-        p.kb_per_split = per;
-        p.k_cluster = 1;
-        if (!a_mn && !b_mn) return launch_gemm<128, false, false, EPI_STORE>(A, B, lda, ldb, p, stream);
+    int best_bn = 0, best_s = 0, best_ctas = 0;
+    for (int bi = 0; bi < 2; ++bi) {
+      const int bn = bi == 0 ? 128 : 64;
+      const int tiles = nm * ((N + bn - 1) / bn);
+      for (int sp = 2; sp <= 8; ++sp) {
+        if (sp > nkb / 4) break;
+        if (splitk_mode > 1 && sp != (splitk_mode > 8 ? 8 : splitk_mode)) continue;
+        const int per = (nkb + sp - 1) / sp;
+        if ((nkb + per - 1) / per != sp) continue;  // this slice count leaves an empty slice
+        const int ctas = tiles * sp;
+        if (ctas > vb_num_sms() || ctas <= best_ctas) continue;
+        if (tiles > max_active_clusters(bn, sp)) continue;
+        best_bn = bn; best_s = sp; best_ctas = ctas;
+      }
+    }
+    // worth it only when it beats what plain tiling puts to work
+    const int plain_ctas = nm * ((N + 31) / 32) < vb_num_sms() ? nm * ((N + 31) / 32) : vb_num_sms();
+    if (best_s >= 2 && (best_ctas * 5 >= vb_num_sms() * 3 || best_ctas > plain_ctas)) {
+      p.k_splits = best_s;
+      p.kb_per_split = (nkb + best_s - 1) / best_s;
+      p.k_cluster = 1;
+#define VB_CLUSTER(AMN, BMN)                                                                \
+  (best_bn == 128 ? launch_gemm<128, AMN, BMN, EPI_STORE>(A, B, lda, ldb, p, stream)         \
+                  : launch_gemm<64, AMN, BMN, EPI_STORE>(A, B, lda, ldb, p, stream))
+      if (!a_mn && !b_mn) return VB_CLUSTER(false, false);
+      if (best_bn == 128) {
         if (!a_mn && b_mn) return launch_gemm<128, false, true, EPI_STORE>(A, B, lda, ldb, p, stream);
         if (a_mn && b_mn) return launch_gemm<128, true, true, EPI_STORE>(A, B, lda, ldb, p, stream);
         return launch_gemm<128, true, false, EPI_STORE>(A, B, lda, ldb, p, stream);
       }
+#undef VB_CLUSTER
+      p.k_splits = 1;  // 64-wide tiles exist for the K-major layout only: other layouts take the paths below
+      p.k_cluster = 0;
     }
   }
   if (ws != nullptr && counters != nullptr && splitk_mode != 0) {

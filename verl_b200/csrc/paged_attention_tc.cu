@@ -362,7 +362,12 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 // producer warp runs ahead into the next item (its Q rows, block-table entries and first K / V tiles) while the
 // softmax warps still finish the current one, so the pipeline does not drain between items. Ring stages, S / P / O
 // buffers and Q buffers alternate by running counters that continue across items.
-constexpr int TCP_BAR_OFF = TC_STAGES * STAGE_BYTES_TC + 2 * Q_BYTES + 2 * P_BYTES;
+// One Q^T operand (a second one would push the CTA over half an SM's shared memory and halve the occupancy): the
+// producer refills it as soon as the last QK MMA of the previous item has completed, which the look-ahead issue makes
+// early (before that item's last softmax and P.V).
+constexpr int TCP_BAR_OFF = TC_STAGES * STAGE_BYTES_TC + Q_BYTES + 2 * P_BYTES;
+static_assert(2 * (TCP_BAR_OFF + 20 * 8 + 64 + TC_BT_MAX * 4 + 2 * TC_NH * 4 * 4 + 1024) <= 227 * 1024,
+              "two CTAs of the persistent decode kernel must fit in one SM");
 constexpr int TCP_BT_OFF = TCP_BAR_OFF + 20 * 8 + 64;
 constexpr int TCP_RED_OFF = TCP_BT_OFF + TC_BT_MAX * 4;
 constexpr int TCP_SMEM = TCP_RED_OFF + 2 * TC_NH * 4 * 4 + 1024;
@@ -390,8 +395,8 @@ paged_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tmK, const __
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage0 = smem;
-  uint8_t* q_s = smem + TC_STAGES * STAGE_BYTES_TC;  // two Q^T operands of Q_BYTES
-  uint8_t* p_s = q_s + 2 * Q_BYTES;
+  uint8_t* q_s = smem + TC_STAGES * STAGE_BYTES_TC;
+  uint8_t* p_s = q_s + Q_BYTES;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + TCP_BAR_OFF);
   uint64_t* empty = full + TC_STAGES;
   uint64_t* s_full = empty + TC_STAGES;
@@ -424,8 +429,8 @@ paged_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tmK, const __
     *abort_flag = 0;
     mbar_fence_init();
   }
-  // rows >= G of both Q^T operands and of both P buffers stay zero for the whole kernel
-  for (int i = tid; i < (2 * Q_BYTES + 2 * P_BYTES) / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
+  // rows >= G of the Q^T operand and of both P buffers stay zero for the whole kernel
+  for (int i = tid; i < (Q_BYTES + 2 * P_BYTES) / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
   fence_proxy_async_smem();
   if (warp == 5) {
     tmem_alloc(tmem_slot, 64);
@@ -447,11 +452,11 @@ paged_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tmK, const __
     for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
       const TcItem it = tc_item(p, item);
       if (it.n_chunks <= 0) continue;
-      const int qb = ig & 1;
-      // the Q buffer is free once the QK MMAs of the item that used it two items ago have completed
+      const int qb = 0;
+      // the Q operand is free once the QK MMAs of the previous item have completed
       int good = 1;  // lane 0 decides for the warp: the lanes must leave the loop together
       if (lane == 0) {
-        good = (!*abort_flag && mbar_wait(&q_empty[qb], ((ig >> 1) & 1) ^ 1)) ? 1 : 0;
+        good = (!*abort_flag && mbar_wait(&q_empty[qb], (ig & 1) ^ 1)) ? 1 : 0;
         if (!good) {
           report_error(p.status, ERR_WAIT_EMPTY, 5000 + item);
           *abort_flag = 1;
@@ -517,8 +522,8 @@ paged_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tmK, const __
       for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
         const TcItem it = tc_item(p, item);
         if (it.n_chunks <= 0) continue;
-        const int qb = ig & 1;
-        if (*abort_flag || !mbar_wait(&q_full[qb], (ig >> 1) & 1)) {
+        const int qb = 0;
+        if (*abort_flag || !mbar_wait(&q_full[qb], ig & 1)) {
           report_error(p.status, ERR_WAIT_FULL, 5000 + item);
           *abort_flag = 1;
           break;

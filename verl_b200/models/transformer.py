@@ -85,8 +85,14 @@ class DenseMLP(nn.Module):
         self.gate_up_proj = Linear(cfg.hidden_size, 2 * cfg.intermediate_size, False, dtype, device)
         self.down_proj = Linear(cfg.intermediate_size, cfg.hidden_size, False, dtype, device)
         self.tile_shards = 1  # >1: run over row shards with per-shard recomputation (models/tiled_mlp.py)
+        self.tp_group = None  # training-side tensor parallelism: this module holds a column / row slice of the MLP
 
     def _plain(self, x):
+        if self.tp_group is not None:
+            from ..parallel.tensor_parallel import copy_to_tp_region, reduce_from_tp_region
+
+            x = copy_to_tp_region(x, self.tp_group)
+            return reduce_from_tp_region(self.down_proj(ops.swiglu(self.gate_up_proj(x))), self.tp_group)
         return self.down_proj(ops.swiglu(self.gate_up_proj(x)))
 
     def forward(self, x):
@@ -119,6 +125,7 @@ class MoEMLP(nn.Module):
         self.down_proj = nn.Parameter(torch.empty(self.E_local, H, I, dtype=dtype, device=device))
         self.last_routing = None
         self.replay_routing = None
+        self.tp_group = None  # training with the experts sharded over a tensor-parallel group (tokens replicated)
 
     def reset_parameters(self, generator=None):
         self.gate.reset_parameters(generator)
@@ -127,8 +134,18 @@ class MoEMLP(nn.Module):
                 p.copy_(torch.empty(p.shape, dtype=torch.float32, device=p.device).normal_(0.0, 0.02, generator=generator))
 
     def forward(self, x):
+        if self.tp_group is not None:
+            from ..parallel.tensor_parallel import copy_to_tp_region, reduce_from_tp_region
+
+            # every rank routes the same tokens and runs its own experts; the partial sums add up to the layer's
+            # output. Through the experts every rank sees only its share of d x and of d (routing weights): those are
+            # summed over the group; the router itself runs replicated on x, so its own d x is already complete.
+            return reduce_from_tp_region(self._forward(copy_to_tp_region(x, self.tp_group), x), self.tp_group)
+        return self._forward(x, x)
+
+    def _forward(self, x, x_router):
         T, H = x.shape
-        logits = self.gate(x).float()
+        logits = self.gate(x_router).float()
         probs = torch.softmax(logits, dim=-1)
         if self.replay_routing is not None:
             top_i = self.replay_routing
@@ -137,6 +154,10 @@ class MoEMLP(nn.Module):
             top_w, top_i = torch.topk(probs, self.k, dim=-1)
         if self.norm_topk:
             top_w = top_w / top_w.sum(-1, keepdim=True)
+        if self.tp_group is not None:
+            from ..parallel.tensor_parallel import copy_to_tp_region
+
+            top_w = copy_to_tp_region(top_w, self.tp_group)  # each rank sees only its experts' share of d top_w
         self.last_routing = top_i.detach()
         if x.is_cuda and _grouped_gemm_ok(self.gate_up_proj, self.down_proj):
             # one grouped GEMM per projection for all experts, routing layout computed on the device
@@ -184,6 +205,7 @@ class Attention(nn.Module):
             self.q_norm = RMSNormWeight(cfg.head_dim, dtype, device)
             self.k_norm = RMSNormWeight(cfg.head_dim, dtype, device)
         self.sp_group = None  # Ulysses sequence-parallel group (set by the engine)
+        self.tp_group = None  # training-side tensor parallelism: this module holds 1 / tp of the heads
 
     def _attend(self, q, k, v, batch: PackedBatch):
         """Attention proper. Under Ulysses the inputs are this rank's sequence slice with all heads; an all-to-all
@@ -212,18 +234,30 @@ class Attention(nn.Module):
         cfg = self.cfg
         Hq, Hk, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         T = x.shape[0]
+        if self.tp_group is not None:
+            from ..parallel.tensor_parallel import copy_to_tp_region
+
+            x = copy_to_tp_region(x, self.tp_group)
         qkv = self.qkv_proj(x)
         if cfg.qk_norm:
             q, k, v = qkv.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=-1)
-            q, _ = ops.rmsnorm(q.reshape(T * Hq, D), self.q_norm.weight, cfg.rms_norm_eps)
-            k, _ = ops.rmsnorm(k.reshape(T * Hk, D), self.k_norm.weight, cfg.rms_norm_eps)
+            qw, kw = self.q_norm.weight, self.k_norm.weight
+            if self.tp_group is not None:  # shared by all heads: every rank sees its own heads' share of the gradient
+                qw, kw = copy_to_tp_region(qw, self.tp_group), copy_to_tp_region(kw, self.tp_group)
+            q, _ = ops.rmsnorm(q.reshape(T * Hq, D), qw, cfg.rms_norm_eps)
+            k, _ = ops.rmsnorm(k.reshape(T * Hk, D), kw, cfg.rms_norm_eps)
             qkv = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v], dim=-1)
         qkv = ops.rope_qkv(qkv, batch.position_ids, rope[0], rope[1], Hq, Hk, D)
         q = qkv[:, : cfg.q_size].view(T, Hq, D)
         k = qkv[:, cfg.q_size : cfg.q_size + cfg.kv_size].view(T, Hk, D)
         v = qkv[:, cfg.q_size + cfg.kv_size :].view(T, Hk, D)
         o = self._attend(q, k, v, batch)
-        return self.o_proj(o.reshape(T, cfg.q_size))
+        out = self.o_proj(o.reshape(T, cfg.q_size))
+        if self.tp_group is not None:
+            from ..parallel.tensor_parallel import reduce_from_tp_region
+
+            out = reduce_from_tp_region(out, self.tp_group)
+        return out
 
 
 class DecoderLayer(nn.Module):
@@ -260,8 +294,12 @@ class CausalLM(nn.Module):
         elif cfg.tie_word_embeddings:
             self.lm_head = None
         else:
-            self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, False, dtype, device)
+            # training-side tensor parallelism may give this rank a slice of the vocabulary rows
+            self.lm_head = Linear(cfg.hidden_size, int(cfg.extra.get("lm_head_rows", cfg.vocab_size)), False, dtype, device)
         self.gradient_checkpointing = False
+        # training-side tensor parallelism: an untied lm_head holds a slice of the vocabulary rows
+        self.tp_group = None
+        self.vocab_offset = 0
 
     # ------------------------------------------------------------------ init
     def init_weights(self, seed: int = 0):
@@ -306,6 +344,12 @@ class CausalLM(nn.Module):
 
     def logprob_entropy(self, hidden: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0):
         """Per-token log-prob of ``labels`` and entropy from final hidden states (fused, no logits)."""
+        if self.tp_group is not None and self.lm_head is not None and self.lm_head.weight.shape[0] != self.cfg.vocab_size:
+            from ..ops.lmhead import lmhead_logprob_entropy_tp
+            from ..parallel.tensor_parallel import copy_to_tp_region
+
+            return lmhead_logprob_entropy_tp(copy_to_tp_region(hidden, self.tp_group), self.lm_head.weight, labels,
+                                             temperature, self.vocab_offset, self.tp_group)
         return ops.lmhead_logprob_entropy(hidden, self.lm_head_weight, labels, temperature)
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:

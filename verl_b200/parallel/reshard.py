@@ -64,11 +64,15 @@ def tp_model_config(cfg: ModelConfig, tp_rank: int, tp_size: int) -> ModelConfig
                                head_dim=cfg.head_dim, intermediate_size=cfg.intermediate_size // tp_size, extra=extra)
 
 
-def tp_slices(cfg: ModelConfig, name: str, shape: tuple, tp_rank: int, tp_size: int):
-    """(row_ranges, col_range) of native parameter ``name`` owned by ``tp_rank`` (``cfg``: the whole model)."""
+def tp_slices(cfg: ModelConfig, name: str, shape: tuple, tp_rank: int, tp_size: int, vocab_parallel_head: bool = False):
+    """(row_ranges, col_range) of native parameter ``name`` owned by ``tp_rank`` (``cfg``: the whole model).
+    ``vocab_parallel_head``: an untied ``lm_head.weight`` is split by vocabulary rows (training engine)."""
     rows = shape[0] if len(shape) >= 1 else 1
     if tp_size == 1 or len(shape) == 0:
         return [(0, rows)], None
+    if vocab_parallel_head and name.endswith("lm_head.weight") and shape[0] % tp_size == 0:
+        k = shape[0] // tp_size
+        return [(tp_rank * k, (tp_rank + 1) * k)], None
 
     def part(r0, n):
         assert n % tp_size == 0, f"{name}: {n} rows not divisible by tp {tp_size}"
@@ -99,11 +103,11 @@ def tp_slices(cfg: ModelConfig, name: str, shape: tuple, tp_rank: int, tp_size: 
     return [(0, rows)], None
 
 
-def shard_state_dict(cfg: ModelConfig, full: dict, tp_rank: int, tp_size: int) -> dict:
+def shard_state_dict(cfg: ModelConfig, full: dict, tp_rank: int, tp_size: int, vocab_parallel_head: bool = False) -> dict:
     """This rank's slices of a whole-model state dict (native names), in the layout of :func:`tp_model_config`."""
     out = {}
     for name, t in full.items():
-        row_ranges, col_range = tp_slices(cfg, name, tuple(t.shape), tp_rank, tp_size)
+        row_ranges, col_range = tp_slices(cfg, name, tuple(t.shape), tp_rank, tp_size, vocab_parallel_head)
         if t.dim() == 0:
             out[name] = t
             continue
@@ -111,6 +115,39 @@ def shard_state_dict(cfg: ModelConfig, full: dict, tp_rank: int, tp_size: int) -
         if col_range is not None:
             piece = piece[:, col_range[0] : col_range[1]]
         out[name] = piece.contiguous()
+    return out
+
+
+def unshard_state_dict(cfg: ModelConfig, parts: list, vocab_parallel_head: bool = False) -> dict:
+    """Inverse of :func:`shard_state_dict`: the ranks' slices (rank order) -> whole tensors. Replicated tensors are
+    taken from rank 0; replicated KV heads are de-duplicated."""
+    tp = len(parts)
+    if tp == 1:
+        return dict(parts[0])
+    out = {}
+    for name, t0 in parts[0].items():
+        leaf = name.split(".")[-2] + "." + name.split(".")[-1] if "." in name else name
+        ts = [p[name] for p in parts]
+        if leaf in ("qkv_proj.weight", "qkv_proj.bias"):
+            Hq, Hk, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+            ql = Hq // tp * D
+            kl = max(Hk // tp, 1) * D
+            q = torch.cat([t[:ql] for t in ts], 0)
+            step = 1 if Hk % tp == 0 else tp // Hk  # replicated heads: every `step`-th rank holds a new one
+            k = torch.cat([t[ql : ql + kl] for t in ts[::step]], 0)
+            v = torch.cat([t[ql + kl : ql + 2 * kl] for t in ts[::step]], 0)
+            out[name] = torch.cat([q, k, v], 0)
+        elif leaf == "gate_up_proj.weight":
+            i = t0.shape[0] // 2
+            out[name] = torch.cat([torch.cat([t[:i] for t in ts], 0), torch.cat([t[i:] for t in ts], 0)], 0)
+        elif leaf in ("o_proj.weight", "down_proj.weight"):
+            out[name] = torch.cat(ts, 1)
+        elif leaf in ("mlp.gate_up_proj", "mlp.down_proj") and t0.dim() == 3:
+            out[name] = torch.cat(ts, 0)
+        elif vocab_parallel_head and name.endswith("lm_head.weight") and t0.shape[0] != cfg.vocab_size:
+            out[name] = torch.cat(ts, 0)
+        else:
+            out[name] = t0
     return out
 
 

@@ -55,3 +55,52 @@ class RowParallelLinear:
             y = ops.linear(h, self.weight, self.bias)
             return y if residual_rows is None else y + residual_rows
         return self.comm.gemm_rs(h, self.weight, residual=residual_rows, bias=self.bias)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Training-side tensor parallelism: the two conjugate operators of a column-parallel -> row-parallel block
+# (Megatron's f / g; the reference gets them from megatron.core.tensor_parallel through its Megatron engine,
+# verl/workers/engine/megatron/transformer_impl.py:57-526).
+import torch.distributed as dist  # noqa: E402
+
+
+class _CopyToTP(torch.autograd.Function):
+    """Forward: identity on activations that are replicated over the tensor-parallel group. Backward: all-reduce, since
+    every rank back-propagates only through its own slice of the following column-parallel weights."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _ReduceFromTP(torch.autograd.Function):
+    """Forward: all-reduce of the partial products of a row-parallel layer. Backward: identity."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def copy_to_tp_region(x: torch.Tensor, group) -> torch.Tensor:
+    if group is None or dist.get_world_size(group) == 1:
+        return x
+    return _CopyToTP.apply(x, group)
+
+
+def reduce_from_tp_region(x: torch.Tensor, group) -> torch.Tensor:
+    if group is None or dist.get_world_size(group) == 1:
+        return x
+    return _ReduceFromTP.apply(x, group)

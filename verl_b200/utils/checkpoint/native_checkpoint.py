@@ -73,7 +73,7 @@ def save_engine_checkpoint(engine, local_path: str, global_step: int = 0,
         path.mkdir(parents=True, exist_ok=True)
     if dist.is_initialized():
         dist.barrier()
-    W, r = z.world, z.rank
+    W, r = _file_world_rank(engine)
     if getattr(engine, "hsdp", False) and getattr(engine, "replica_index", 0) != 0:
         # hybrid sharding: the replicas hold identical shards; the first replica group writes the files
         if dist.is_initialized():
@@ -86,7 +86,8 @@ def save_engine_checkpoint(engine, local_path: str, global_step: int = 0,
         save_reference_fsdp_shards(engine, path)
     elif "model" in save_contents:
         src = z.master if z.trainable else z.shard16
-        torch.save({"format": FLAT_SHARD_FORMAT, "world_size": W, "rank": r, "params": _param_slices(z, src)},
+        torch.save({"format": FLAT_SHARD_FORMAT, "world_size": W, "rank": r, "tp": int(getattr(engine, "tp_size", 1)),
+                    "params": _param_slices(z, src)},
                    path / f"model_world_size_{W}_rank_{r}.pt")
     if "optimizer" in save_contents and z.trainable:
         torch.save({"format": FLAT_SHARD_FORMAT, "world_size": W, "rank": r, "step": engine.step_count,
@@ -134,19 +135,31 @@ def _restore(zero, dst: torch.Tensor, slices: dict) -> None:
             dst[u.offset + s - lo : u.offset + s - lo + data.numel()].copy_(data.to(dst.device, dst.dtype))
 
 
+def _file_world_rank(engine) -> tuple[int, int]:
+    """(W, r) in the shard file names: the sharding group's, or (tensor parallelism: one set of slices per
+    tensor-parallel rank) the engine group's."""
+    if getattr(engine, "tp_size", 1) > 1:
+        return engine.dp_world, engine.dp_rank_all
+    return engine.zero.world, engine.zero.rank
+
+
 def load_engine_checkpoint(engine, local_path: str, load_contents=("model", "optimizer", "extra")) -> None:
     z = engine.zero
     path = Path(local_path)
-    W, r = z.world, z.rank
+    W, r = _file_world_rank(engine)
     mfile = path / f"model_world_size_{W}_rank_{r}.pt"
     if "model" in load_contents:
         st = torch.load(mfile, map_location="cpu", weights_only=False) if mfile.exists() else None
-        if isinstance(st, dict) and st.get("format") == FLAT_SHARD_FORMAT and st["world_size"] == W:
+        tp = int(getattr(engine, "tp_size", 1))
+        if isinstance(st, dict) and st.get("format") == FLAT_SHARD_FORMAT and st["world_size"] == W and st.get("tp", 1) == tp:
             if z.trainable:
                 _restore(z, z.master, st["params"])
                 z.shard16.copy_(z.master.to(z.shard16.dtype))
             else:
                 _restore(z, z.shard16, st["params"])
+        elif tp > 1:
+            raise ValueError(f"{path}: a tensor-parallel engine resumes from shard files of the same layout "
+                             f"(world {W}, tp {tp}) or from the HF weights under huggingface/ (model.path)")
         else:
             # another world size, or shard files written by torch FSDP (the reference's DTensor / ShardedTensor state
             # dicts): rebuild full tensors from all files of the directory and re-shard them

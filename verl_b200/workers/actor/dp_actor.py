@@ -92,8 +92,8 @@ class DataParallelPPOActor:
         t = torch.tensor([float(mask.sum()), float((mask.sum(-1) > 0).sum())], dtype=torch.float64, device=self.device)
         if self.engine.world > 1:
             dist.all_reduce(t, group=self.engine.group)
-            # the ranks of a sequence-parallel group hold the same samples: count each sample once
-            t = t / max(int(getattr(self.engine, "sp_size", 1) or 1), 1)
+            # the ranks of a sequence- / tensor-parallel group hold the same samples: count each sample once
+            t = t / max(int(getattr(self.engine, "mp_size", 1) or 1), 1)
         return max(t[0].item(), 1.0), max(t[1].item(), 1.0)
 
     def update_policy(self, data: DataProto) -> dict:

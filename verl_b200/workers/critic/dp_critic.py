@@ -70,7 +70,7 @@ class DataParallelPPOCritic:
                 n_tok = torch.tensor([float(mini.batch["response_mask"].sum())], dtype=torch.float64, device=self.device)
                 if eng.world > 1:
                     dist.all_reduce(n_tok, group=eng.group)
-                    n_tok = n_tok / max(int(getattr(eng, "sp_size", 1) or 1), 1)  # an SP group shares its samples
+                    n_tok = n_tok / max(int(getattr(eng, "mp_size", 1) or 1), 1)  # an SP group shares its samples
                 n_tok = max(n_tok.item(), 1.0)
                 micros, _ = self._micro_batches(mini, int(cfg.ppo_max_token_len_per_gpu), cfg.ppo_micro_batch_size_per_gpu,
                                                 bool(cfg.use_dynamic_bsz))

@@ -96,12 +96,16 @@ class NativeEngine(BaseEngine):
     # ------------------------------------------------------------------- build
     def initialize(self):
         cfg = self.model_config
-        self.model = CausalLM(cfg, dtype=self.work_dtype, device=self.device, value_head=self.value_head)
-        self.model.init_weights(self.seed)
-        if self._init_state is not None:
-            missing, unexpected = self.model.load_state_dict(
-                {k: v.to(self.work_dtype) for k, v in self._init_state.items()}, strict=False)
-            self._init_state = None
+        self._setup_tensor_parallel()
+        if self.tp_size > 1:
+            self._build_tp_model()
+        else:
+            self.model = CausalLM(cfg, dtype=self.work_dtype, device=self.device, value_head=self.value_head)
+            self.model.init_weights(self.seed)
+            if self._init_state is not None:
+                missing, unexpected = self.model.load_state_dict(
+                    {k: v.to(self.work_dtype) for k, v in self._init_state.items()}, strict=False)
+        self._init_state = None
         if self.tiled_mlp_shards > 1:
             from ...models.tiled_mlp import apply_tiled_mlp
 
@@ -161,6 +165,66 @@ class NativeEngine(BaseEngine):
         ``zero.world``, the number of ranks over which the parameters are sharded."""
         return self.dp_world
 
+    def _setup_tensor_parallel(self):
+        """``tensor_model_parallel_size`` > 1 (the Megatron-style training layout, verl/workers/config/engine.py
+        McoreEngineConfig): ``tp`` consecutive ranks hold column / row slices of every block, 1 / tp of the experts and of
+        an untied lm_head's vocabulary rows; activations between blocks are replicated over the group. Parameters,
+        gradients and optimizer state of a slice are ZeRO-sharded over the ranks with the same slice."""
+        import torch.distributed as dist
+
+        self.tp_size, self.tp_rank, self.tp_group = 1, 0, None
+        tp = int(_cfg(self.engine_config, "tensor_model_parallel_size", 1) or 1)
+        W = dist.get_world_size(self.group) if self.group is not None else 1
+        if tp <= 1:
+            return
+        if W % tp != 0:
+            raise ValueError(f"tensor_model_parallel_size {tp} does not divide the {W} ranks of the engine's group")
+        cfg = self.model_config
+        if cfg.num_key_value_heads % tp != 0:
+            raise ValueError(f"training with tensor_model_parallel_size {tp} needs it to divide the {cfg.num_key_value_heads} "
+                             "KV heads (replicated KV heads would need their gradients summed between the replicas)")
+        if int(_cfg(self.engine_config, "ulysses_sequence_parallel_size", 1) or 1) > 1:
+            raise ValueError("tensor_model_parallel_size > 1 and ulysses_sequence_parallel_size > 1 cannot be combined")
+        if self.lora is not None:
+            raise ValueError("LoRA adapters are not sliced: use tensor_model_parallel_size = 1 with model.lora_rank > 0")
+        ranks_of = dist.get_process_group_ranks(self.group)
+        r = dist.get_rank(self.group)
+        for g in range(W // tp):  # collective: every rank creates every group
+            grp = dist.new_group([ranks_of[g * tp + i] for i in range(tp)])
+            if r // tp == g:
+                self.tp_group = grp
+        self._tp_dp_group = None
+        for i in range(tp):
+            grp = dist.new_group([ranks_of[g * tp + i] for g in range(W // tp)])
+            if r % tp == i:
+                self._tp_dp_group = grp
+        self.tp_size, self.tp_rank = tp, r % tp
+
+    def _build_tp_model(self):
+        """This rank's slice of the model: the whole model is initialised (or given), then sliced."""
+        from ...parallel.reshard import shard_state_dict, tp_model_config
+
+        cfg, tp, r = self.model_config, self.tp_size, self.tp_rank
+        state = self._init_state
+        if state is None:
+            full = CausalLM(cfg, dtype=self.work_dtype, device=self.device, value_head=self.value_head).init_weights(self.seed)
+            state = dict(full.state_dict())
+            del full
+        vp = (not self.value_head) and (not cfg.tie_word_embeddings) and cfg.vocab_size % tp == 0
+        self._vocab_parallel_head = vp
+        tcfg = tp_model_config(cfg, r, tp)
+        if vp:
+            tcfg.extra["lm_head_rows"] = cfg.vocab_size // tp
+        self.model = CausalLM(tcfg, dtype=self.work_dtype, device=self.device, value_head=self.value_head)
+        sl = shard_state_dict(cfg, {k: v.to(self.work_dtype) for k, v in state.items()}, r, tp, vocab_parallel_head=vp)
+        self.model.load_state_dict(sl, strict=False)
+        for layer in self.model.layers:
+            layer.self_attn.tp_group = self.tp_group
+            layer.mlp.tp_group = self.tp_group
+        if vp:
+            self.model.tp_group = self.tp_group
+            self.model.vocab_offset = r * (cfg.vocab_size // tp)
+
     def _setup_hybrid_sharding(self):
         """``fsdp_size`` < world (HSDP, verl/workers/fsdp_workers.py:98-108 ``create_device_mesh``): parameters,
         gradients and optimizer state are sharded over ``fsdp_size`` consecutive ranks and replicated across the
@@ -172,6 +236,16 @@ class NativeEngine(BaseEngine):
         self.shard_group, self.replica_group, self.hsdp = self.group, None, False
         fs = int(_cfg(self.engine_config, "fsdp_size", -1) or -1)
         W = self.dp_world
+        if self.tp_size > 1:
+            # the slices are sharded over the ranks that hold the same slice
+            if 0 < fs < W // self.tp_size:
+                raise ValueError("fsdp_size (hybrid sharding) cannot be combined with tensor_model_parallel_size > 1")
+            self.shard_group = self._tp_dp_group if W // self.tp_size > 1 else None
+            if self.comm is not None and self.device.type == "cuda":
+                from ...parallel.peer_comm import PeerComm
+
+                self.comm = PeerComm(self.shard_group) if self.shard_group is not None else None
+            return
         if fs <= 0 or fs >= W:
             return
         if W % fs != 0:
@@ -221,11 +295,24 @@ class NativeEngine(BaseEngine):
         for layer in self.model.layers:
             layer.self_attn.sp_group = self.sp_group
 
+    @property
+    def mp_size(self) -> int:
+        """Ranks that work on the same samples: a sequence-parallel or a tensor-parallel group."""
+        return max(self.sp_size, 1) * max(self.tp_size, 1)
+
+    @property
+    def mp_group(self):
+        return self.tp_group if self.tp_size > 1 else self.sp_group
+
+    @property
+    def mp_rank(self) -> int:
+        return self.tp_rank if self.tp_size > 1 else self.sp_rank
+
     def get_data_parallel_size(self) -> int:
-        return self.dp_world // self.sp_size
+        return self.dp_world // self.mp_size
 
     def get_data_parallel_rank(self) -> int:
-        return self.dp_rank_all // self.sp_size
+        return self.dp_rank_all // self.mp_size
 
     def get_data_parallel_group(self):
         return self.group
@@ -418,7 +505,7 @@ class NativeEngine(BaseEngine):
         dp = self.get_data_parallel_size()
         if self.dp_world > 1:
             dist.all_reduce(norm, group=self.group)
-            norm = norm / max(self.sp_size, 1)
+            norm = norm / self.mp_size
         # micro-batches: fixed sample count, or packed up to a token budget
         n = len(lens)
         if tu.get(data, "use_dynamic_bsz", False):
@@ -487,7 +574,7 @@ class NativeEngine(BaseEngine):
             return self.forward_backward_batch(data, loss_function, forward_only=True)
 
     def is_mp_src_rank_with_outputs(self) -> bool:
-        return self.sp_rank == 0
+        return self.mp_rank == 0
 
     @staticmethod
     def response_rows(input_ids: torch.Tensor, attention_mask: torch.Tensor, response_length: int,
@@ -602,9 +689,11 @@ class NativeEngine(BaseEngine):
             dist.all_reduce(z.grad, group=self.replica_group)
         if self.device.type == "cuda":
             self._sumsq.zero_()
-            ops.sumsq_into(z.grad, self._sumsq)
+            ops.sumsq_into(z.grad if self.tp_size == 1 else z.grad * self._tp_norm_weight(), self._sumsq)
             if z.world > 1:
                 dist.all_reduce(self._sumsq, group=self.shard_group)
+            if self.tp_size > 1:
+                dist.all_reduce(self._sumsq, group=self.tp_group)
             ops.clip_coef(self._sumsq, clip, 1.0, self._scale, self._skip, self._norm)
             ops.adamw_step(z.master, z.grad, z.exp_avg, z.exp_avg_sq, z.shard16, lr=lr, betas=betas, eps=eps,
                            weight_decay=wd, step=self.step_count, scale=self._scale, skip=self._skip)
@@ -612,9 +701,12 @@ class NativeEngine(BaseEngine):
             if int(self._skip.item()):  # a non-finite norm skipped the update: the step does not count
                 self.step_count -= 1
         else:
-            sq = z.grad.double().pow(2).sum().reshape(1)
+            g_n = z.grad if self.tp_size == 1 else z.grad * self._tp_norm_weight()
+            sq = g_n.double().pow(2).sum().reshape(1)
             if z.world > 1:
                 dist.all_reduce(sq, group=self.shard_group)
+            if self.tp_size > 1:
+                dist.all_reduce(sq, group=self.tp_group)
             norm = sq.sqrt().float()
             if torch.isfinite(norm).all():
                 coef = min(1.0, clip / (norm.item() + 1e-6)) if clip > 0 else 1.0
@@ -631,6 +723,32 @@ class NativeEngine(BaseEngine):
         z.zero_grad()
         return norm
 
+    _TP_SLICED = ("qkv_proj.weight", "qkv_proj.bias", "gate_up_proj.weight", "o_proj.weight", "down_proj.weight",
+                  "mlp.gate_up_proj", "mlp.down_proj")
+
+    def _tp_is_sliced(self, name: str) -> bool:
+        leaf = name.split(".")[-2] + "." + name.split(".")[-1] if "." in name else name
+        return leaf in self._TP_SLICED or (getattr(self, "_vocab_parallel_head", False) and name.endswith("lm_head.weight"))
+
+    def _tp_norm_weight(self) -> torch.Tensor:
+        """Per-element factor of the gradient-norm sum over (shard group x tensor-parallel group): replicated
+        parameters (norms, embeddings, routers) appear once per tensor-parallel rank, so their squares count 1 / tp."""
+        w = getattr(self, "_tp_w", None)
+        if w is None:
+            z = self.zero
+            w = torch.ones_like(z.grad)
+            dup = (1.0 / self.tp_size) ** 0.5
+            for u in z.units:
+                lo, hi = z.rank * u.shard, (z.rank + 1) * u.shard
+                for name, n, o in zip(u.names, u.numels, u.offsets):
+                    if self._tp_is_sliced(name):
+                        continue
+                    s_, e_ = max(o, lo), min(o + n, hi)
+                    if s_ < e_:
+                        w[u.offset + s_ - lo : u.offset + e_ - lo] = dup
+            self._tp_w = w
+        return w
+
     # --------------------------------------------------------------- weights out
     def get_per_tensor_param(self, dtype: Optional[torch.dtype] = None):
         """Generator of (HF parameter name, full tensor): one unit is gathered at a time."""
@@ -639,7 +757,22 @@ class NativeEngine(BaseEngine):
         return native_to_hf_items(self.model_config, self._merged_named_tensors(dtype))
 
     def _merged_named_tensors(self, dtype=None):
-        """(name, full tensor) of every parameter; adapted weights come out merged (W + (alpha / r) B A)."""
+        """(name, full tensor) of every parameter; adapted weights come out merged (W + (alpha / r) B A); tensor-parallel
+        slices are gathered over the group and put back together."""
+        if self.tp_size > 1:
+            import torch.distributed as dist
+
+            from ...parallel.reshard import unshard_state_dict
+
+            for k, v in self.zero.named_full_tensors(dtype):
+                if not self._tp_is_sliced(k):
+                    yield k, v
+                    continue
+                parts = [torch.empty_like(v) for _ in range(self.tp_size)]
+                dist.all_gather(parts, v.contiguous(), group=self.tp_group)
+                yield k, unshard_state_dict(self.model_config, [{k: p} for p in parts],
+                                            getattr(self, "_vocab_parallel_head", False))[k]
+            return
         if not self._lora_params:
             yield from self.zero.named_full_tensors(dtype)
             return
@@ -678,12 +811,12 @@ class NativeEngine(BaseEngine):
         load_engine_checkpoint(self, local_path, load_contents=load_contents)
 
 
-@EngineRegistry.register(model_type="language_model", backend=["fsdp", "fsdp2", "native"], device=["cuda", "cpu"])
+@EngineRegistry.register(model_type="language_model", backend=["fsdp", "fsdp2", "native", "megatron"], device=["cuda", "cpu"])
 class NativeEngineWithLMHead(NativeEngine):
     pass
 
 
-@EngineRegistry.register(model_type="value_model", backend=["fsdp", "fsdp2", "native"], device=["cuda", "cpu"])
+@EngineRegistry.register(model_type="value_model", backend=["fsdp", "fsdp2", "native", "megatron"], device=["cuda", "cpu"])
 class NativeEngineWithValueHead(NativeEngine):
     def __init__(self, *args, **kwargs):
         kwargs["value_head"] = True

@@ -90,6 +90,7 @@ class _WorkerBase(Worker):
         eng_cfg = _cfg(cfg, "fsdp_config", None) or _cfg(_cfg(cfg, "model", None), "fsdp_config", None)
         sp = int(_cfg(eng_cfg, "ulysses_sequence_parallel_size", 1) or 1) if eng_cfg is not None else 1
         sp = max(sp, int(_cfg(cfg, "ulysses_sequence_parallel_size", 1) or 1))
+        sp *= int(_cfg(eng_cfg, "tensor_model_parallel_size", 1) or 1) if eng_cfg is not None else 1
         dp = max(self.world // max(sp, 1), 1)
         mini = int(getattr(cfg, mini_key)) * n // dp
         assert mini > 0, f"{mini_key} {getattr(cfg, mini_key)} * n {n} must be >= data-parallel size {dp}"
@@ -108,21 +109,21 @@ def _spmd() -> bool:
 
 
 def sp_pool(data: DataProto, engine) -> tuple[DataProto, Optional[tuple]]:
-    """SPMD launch with Ulysses: every rank drives its own share of the batch, but the ranks of a sequence-parallel
-    group must work on the same samples. Pool the group's shares (rank order); :func:`sp_unpool` hands every rank the
+    """SPMD launch with Ulysses or tensor parallelism: every rank drives its own share of the batch, but the ranks of
+    a sequence-parallel / tensor-parallel group must work on the same samples. Pool the group's shares (rank order); :func:`sp_unpool` hands every rank the
     rows of its own share back. A no-op under the dispatching worker group (the dispatch already sends a group the
     same samples) and without sequence parallelism."""
-    sp = int(getattr(engine, "sp_size", 1) or 1)
+    sp = int(getattr(engine, "mp_size", getattr(engine, "sp_size", 1)) or 1)
     if sp <= 1 or not _spmd():
         return data, None
     parts = [None] * sp
-    dist.all_gather_object(parts, data, group=engine.sp_group)
+    dist.all_gather_object(parts, data, group=engine.mp_group)
     pooled = DataProto.concat(parts)
     pooled.meta_info = dict(data.meta_info)
     tok = pooled.meta_info.get("global_token_num")
     if tok is not None and data.meta_info.get("token_num_is_local"):
         pooled.meta_info["global_token_num"] = [t for p in parts for t in (p.meta_info.get("global_token_num") or [])]
-    lo = sum(len(p) for p in parts[: engine.sp_rank])
+    lo = sum(len(p) for p in parts[: engine.mp_rank])
     return pooled, (lo, len(data))
 
 
@@ -151,8 +152,11 @@ class ActorRolloutRefWorker(_WorkerBase):
             self._norm_batch(self.actor_cfg, n=n)
         # Ulysses: the ranks of a sequence-parallel group share one data-parallel rank and the first one reports
         # (dispatch of verl/single_controller/base/decorator.py:297-328, registration of fsdp_workers.py:146-273)
-        def sp_of(c):
-            return int(_cfg(_cfg(c, "fsdp_config", None), "ulysses_sequence_parallel_size", 1) or 1) if c is not None else 1
+        def sp_of(c):  # ranks that share their samples: sequence-parallel x tensor-parallel
+            if c is None:
+                return 1
+            ec = _cfg(c, "fsdp_config", None)
+            return (int(_cfg(ec, "ulysses_sequence_parallel_size", 1) or 1) * int(_cfg(ec, "tensor_model_parallel_size", 1) or 1))
 
         rank = self.dp_rank
         sp_a, sp_r = sp_of(self.actor_cfg), sp_of(self.ref_cfg if self.ref_cfg is not None else self.actor_cfg)
@@ -272,8 +276,10 @@ class ActorRolloutRefWorker(_WorkerBase):
             self._setup_rollout_tp()
             tp_rank = self.dp_rank % tp
             self.rollout_model = CausalLM(tp_model_config(model_cfg, tp_rank, tp), dtype=dtype, device=self.device)
-            if self._is_actor:
+            if self._is_actor and self.actor_engine.tp_size == 1:
                 self._bind_rollout_to_flat(tp_rank, tp)
+            elif self._is_actor:
+                self._generic_sync = True
             else:
                 if state is None:  # random init of the whole model, then this rank's slices (same seed on all ranks)
                     full = CausalLM(model_cfg, dtype=dtype, device=self.device).init_weights(seed)
@@ -281,12 +287,14 @@ class ActorRolloutRefWorker(_WorkerBase):
                     del full
                 sl = shard_state_dict(model_cfg, {k: v.to(dtype) for k, v in state.items()}, tp_rank, tp)
                 self.rollout_model.load_state_dict(sl, strict=False)
-        elif self._is_actor and self.world == 1 and not getattr(self, "_lora", False):
+        elif self._is_actor and self.world == 1 and not getattr(self, "_lora", False) and self.actor_engine.tp_size == 1:
             self.rollout_model = self.actor_engine.model  # same tensors: weight sync is free
         else:
             self.rollout_model = CausalLM(model_cfg, dtype=dtype, device=self.device)
-            if self._is_actor:
+            if self._is_actor and self.actor_engine.tp_size == 1:
                 self._bind_rollout_to_flat()
+            elif self._is_actor:
+                self._generic_sync = True  # a tensor-parallel trainer: weights travel as whole (HF-named) tensors
             elif state is not None:
                 self.rollout_model.load_state_dict({k: v.to(dtype) for k, v in state.items()}, strict=False)
             else:
@@ -300,6 +308,8 @@ class ActorRolloutRefWorker(_WorkerBase):
             enforce_eager=rc.enforce_eager, seed=seed + 1000 * (self.dp_rank // tp),
             cudagraph_capture_sizes=rc.cudagraph_capture_sizes, quantization=_cfg(rc, "quantization", None),
             tp_group=self.tp_group, tp_comm=self.tp_comm, full_config=model_cfg, **kw)
+        if getattr(self, "_generic_sync", False):
+            self.rollout_engine.update_weights(self.actor_engine.get_per_tensor_param())
         if rc.free_cache_engine:
             self.rollout_engine.sleep()
 
@@ -416,7 +426,7 @@ class ActorRolloutRefWorker(_WorkerBase):
 
             est, promised = FlopsCounter(self.model_config).estimate_flops(tokens, dt)
             # tokens of this call's batch are processed by `sp` ranks (local counts) or by the whole job (global counts)
-            denom = max(int(getattr(self.actor_engine, "sp_size", 1) or 1), 1) if data.meta_info.get("token_num_is_local") \
+            denom = max(int(getattr(self.actor_engine, "mp_size", 1) or 1), 1) if data.meta_info.get("token_num_is_local") \
                 else self.world
             metrics["perf/mfu/actor"] = est * self.actor_cfg.ppo_epochs / promised / denom
         return DataProto(meta_info={"metrics": metrics})
@@ -427,6 +437,8 @@ class ActorRolloutRefWorker(_WorkerBase):
         t0 = time.perf_counter()
         if self._is_actor and self._is_rollout and self._rollout_flat is not None:
             self._sync_rollout_weights()
+        elif self._is_actor and self._is_rollout and getattr(self, "_generic_sync", False):
+            self.rollout_engine.update_weights(self.actor_engine.get_per_tensor_param())
         if self.rollout_engine is not None:
             self.rollout_engine.refresh_quantization()  # fp8 rollout: re-quantise from the fresh bf16 weights
             self.rollout_engine.clear_kv_cache()
