@@ -281,17 +281,26 @@ class DecoderLayer(nn.Module):
 class CausalLM(nn.Module):
     """Packed-sequence causal LM with an lm_head (policy / reference) or a value head (critic)."""
 
-    def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", value_head: bool = False):
+    def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", value_head: bool = False,
+                 layer_range: Optional[tuple] = None, has_embed: bool = True, has_head: bool = True):
+        """``layer_range = (lo, hi)``, ``has_embed``, ``has_head``: one pipeline stage of the model (decoder layers
+        ``lo .. hi - 1``; the embedding lives on the first stage, final norm and head on the last). ``layers[i]`` is then
+        decoder layer ``lo + i`` (``layer_offset``)."""
         super().__init__()
         self.cfg = cfg
         self.value_head = value_head or cfg.num_labels == 1
-        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
-        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device) for _ in range(cfg.num_hidden_layers)])
-        self.norm = RMSNormWeight(cfg.hidden_size, dtype, device)
-        if self.value_head:
+        lo, hi = layer_range if layer_range is not None else (0, cfg.num_hidden_layers)
+        self.layer_offset = lo
+        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device) if has_embed else None
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device) for _ in range(lo, hi)])
+        self.norm = RMSNormWeight(cfg.hidden_size, dtype, device) if has_head else None
+        if not has_head:
+            self.lm_head = None
+        elif self.value_head:
             self.score = Linear(cfg.hidden_size, 1, False, dtype, device)
             self.lm_head = None
         elif cfg.tie_word_embeddings:
+            assert has_embed, "tied embeddings need the embedding and the head on the same pipeline stage"
             self.lm_head = None
         else:
             # training-side tensor parallelism may give this rank a slice of the vocabulary rows
@@ -303,11 +312,13 @@ class CausalLM(nn.Module):
 
     # ------------------------------------------------------------------ init
     def init_weights(self, seed: int = 0):
-        gen = torch.Generator(device=self.embed_tokens.weight.device)
+        dev = next(self.parameters()).device
+        gen = torch.Generator(device=dev)
         gen.manual_seed(seed)
-        with torch.no_grad():
-            w = self.embed_tokens.weight
-            w.copy_(torch.empty(w.shape, dtype=torch.float32, device=w.device).normal_(0.0, 0.02, generator=gen))
+        if self.embed_tokens is not None:
+            with torch.no_grad():
+                w = self.embed_tokens.weight
+                w.copy_(torch.empty(w.shape, dtype=torch.float32, device=w.device).normal_(0.0, 0.02, generator=gen))
         for m in self.modules():
             if isinstance(m, (Linear, MoEMLP)):
                 m.reset_parameters(gen)

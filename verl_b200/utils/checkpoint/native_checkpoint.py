@@ -86,7 +86,8 @@ def save_engine_checkpoint(engine, local_path: str, global_step: int = 0,
         save_reference_fsdp_shards(engine, path)
     elif "model" in save_contents:
         src = z.master if z.trainable else z.shard16
-        torch.save({"format": FLAT_SHARD_FORMAT, "world_size": W, "rank": r, "tp": int(getattr(engine, "tp_size", 1)),
+        layout = int(getattr(engine, "tp_size", 1)) * 1000 + int(getattr(engine, "pp_size", 1))
+        torch.save({"format": FLAT_SHARD_FORMAT, "world_size": W, "rank": r, "tp": layout if layout != 1001 else 1,
                     "params": _param_slices(z, src)},
                    path / f"model_world_size_{W}_rank_{r}.pt")
     if "optimizer" in save_contents and z.trainable:
@@ -138,8 +139,8 @@ def _restore(zero, dst: torch.Tensor, slices: dict) -> None:
 def _file_world_rank(engine) -> tuple[int, int]:
     """(W, r) in the shard file names: the sharding group's, or (tensor parallelism: one set of slices per
     tensor-parallel rank) the engine group's."""
-    if getattr(engine, "tp_size", 1) > 1:
-        return engine.dp_world, engine.dp_rank_all
+    if getattr(engine, "tp_size", 1) > 1 or getattr(engine, "pp_size", 1) > 1:
+        return engine.full_world, engine.full_rank
     return engine.zero.world, engine.zero.rank
 
 
@@ -150,7 +151,8 @@ def load_engine_checkpoint(engine, local_path: str, load_contents=("model", "opt
     mfile = path / f"model_world_size_{W}_rank_{r}.pt"
     if "model" in load_contents:
         st = torch.load(mfile, map_location="cpu", weights_only=False) if mfile.exists() else None
-        tp = int(getattr(engine, "tp_size", 1))
+        tp = int(getattr(engine, "tp_size", 1)) * 1000 + int(getattr(engine, "pp_size", 1))  # (tp, pp) of the layout
+        tp = tp if tp != 1001 else 1
         if isinstance(st, dict) and st.get("format") == FLAT_SHARD_FORMAT and st["world_size"] == W and st.get("tp", 1) == tp:
             if z.trainable:
                 _restore(z, z.master, st["params"])
@@ -158,8 +160,8 @@ def load_engine_checkpoint(engine, local_path: str, load_contents=("model", "opt
             else:
                 _restore(z, z.shard16, st["params"])
         elif tp > 1:
-            raise ValueError(f"{path}: a tensor-parallel engine resumes from shard files of the same layout "
-                             f"(world {W}, tp {tp}) or from the HF weights under huggingface/ (model.path)")
+            raise ValueError(f"{path}: a tensor- / pipeline-parallel engine resumes from shard files of the same layout "
+                             f"(world {W}) or from the HF weights under huggingface/ (model.path)")
         else:
             # another world size, or shard files written by torch FSDP (the reference's DTensor / ShardedTensor state
             # dicts): rebuild full tensors from all files of the directory and re-shard them

@@ -96,9 +96,10 @@ class NativeEngine(BaseEngine):
     # ------------------------------------------------------------------- build
     def initialize(self):
         cfg = self.model_config
+        self._setup_pipeline()
         self._setup_tensor_parallel()
-        if self.tp_size > 1:
-            self._build_tp_model()
+        if self.tp_size > 1 or self.pp_size > 1:
+            self._build_parallel_model()
         else:
             self.model = CausalLM(cfg, dtype=self.work_dtype, device=self.device, value_head=self.value_head)
             self.model.init_weights(self.seed)
@@ -121,15 +122,16 @@ class NativeEngine(BaseEngine):
                        self.lora.get("target_modules", "all-linear"), self.lora.get("exclude_modules"), seed=self.seed)
             self._lora_params = [p for _, p in lora_named_parameters(self.model)]
         m = self.model
-        tied = m.lm_head is None and not m.value_head
+        first, last = self.pp_rank == 0, self.pp_rank == self.pp_size - 1
+        tied = last and m.lm_head is None and not m.value_head
         units = []
         if tied:
             units.append(("", [("embed_tokens.weight", m.embed_tokens.weight), ("norm.weight", m.norm.weight)]))
-        else:
+        elif first:
             units.append(("", [("embed_tokens.weight", m.embed_tokens.weight)]))
         for i, layer in enumerate(m.layers):
-            units.append((f"layers.{i}", layer))
-        if not tied:
+            units.append((f"layers.{i + m.layer_offset}", layer))
+        if last and not tied:
             head = [("norm.weight", m.norm.weight)]
             if m.value_head:
                 head.append(("score.weight", m.score.weight))
@@ -141,9 +143,10 @@ class NativeEngine(BaseEngine):
                                       trainable=self.trainable and not self._lora_params, comm=self.comm)
         self.zero.frozen_grad = bool(self._lora_params)
         self._setup_sequence_parallel()
-        self._embed_unit = self.zero.units[0]
-        self._layer_units = self.zero.units[1 : 1 + cfg.num_hidden_layers]
-        self._head_unit = self.zero.units[0] if tied else self.zero.units[-1]
+        n0 = 1 if (first or tied) else 0
+        self._embed_unit = self.zero.units[0] if (first or tied) else None
+        self._layer_units = self.zero.units[n0 : n0 + len(m.layers)]
+        self._head_unit = (self.zero.units[0] if tied else self.zero.units[-1]) if last else None
         if self.device.type == "cuda":
             torch.cuda.empty_cache()
         if self._lora_params:
@@ -164,6 +167,31 @@ class NativeEngine(BaseEngine):
         """Ranks of the engine's group (data parallel x sequence parallel); under hybrid sharding this is larger than
         ``zero.world``, the number of ranks over which the parameters are sharded."""
         return self.dp_world
+
+    def _block_groups(self, k: int, strided: bool):
+        """This rank's group among the groups of ``k`` ranks inside its block of ranks (the engine's group, or this
+        pipeline stage's part of it): consecutive ranks ``[g k, (g + 1) k)``, or (``strided``) the ranks with the same
+        index inside those. Process-group creation is collective over the whole job, so the groups of EVERY pipeline
+        stage's block are created here, in the same order on every rank."""
+        import torch.distributed as dist
+
+        if self.pp_size > 1:
+            full = dist.get_process_group_ranks(self.full_group)
+            S = len(full) // self.pp_size
+            blocks = [full[st * S : (st + 1) * S] for st in range(self.pp_size)]
+        else:
+            blocks = [dist.get_process_group_ranks(self.group)]
+        me = dist.get_rank()
+        mine = None
+        for block in blocks:
+            W = len(block)
+            lists = ([[block[g * k + i] for g in range(W // k)] for i in range(k)] if strided
+                     else [[block[g * k + i] for i in range(k)] for g in range(W // k)])
+            for members in lists:
+                grp = dist.new_group(members)
+                if me in members:
+                    mine = grp
+        return mine
 
     def _setup_tensor_parallel(self):
         """``tensor_model_parallel_size`` > 1 (the Megatron-style training layout, verl/workers/config/engine.py
@@ -187,21 +215,57 @@ class NativeEngine(BaseEngine):
             raise ValueError("tensor_model_parallel_size > 1 and ulysses_sequence_parallel_size > 1 cannot be combined")
         if self.lora is not None:
             raise ValueError("LoRA adapters are not sliced: use tensor_model_parallel_size = 1 with model.lora_rank > 0")
-        ranks_of = dist.get_process_group_ranks(self.group)
         r = dist.get_rank(self.group)
-        for g in range(W // tp):  # collective: every rank creates every group
-            grp = dist.new_group([ranks_of[g * tp + i] for i in range(tp)])
-            if r // tp == g:
-                self.tp_group = grp
-        self._tp_dp_group = None
-        for i in range(tp):
-            grp = dist.new_group([ranks_of[g * tp + i] for g in range(W // tp)])
-            if r % tp == i:
-                self._tp_dp_group = grp
+        self.tp_group = self._block_groups(tp, strided=False)
+        self._tp_dp_group = self._block_groups(tp, strided=True)
         self.tp_size, self.tp_rank = tp, r % tp
 
-    def _build_tp_model(self):
-        """This rank's slice of the model: the whole model is initialised (or given), then sliced."""
+    def _setup_pipeline(self):
+        """``pipeline_model_parallel_size`` > 1: the engine's group is cut into ``pp`` consecutive blocks of ranks, block
+        ``s`` holds stage ``s`` (a contiguous run of decoder layers; embedding on the first, final norm and head on the
+        last stage). Everything else (tensor parallelism, sharding, data parallelism) is set up inside a stage's block;
+        rank ``i`` of a block exchanges the residual stream with rank ``i`` of the neighbouring blocks."""
+        import torch.distributed as dist
+
+        self.full_group = self.group
+        self.full_world = dist.get_world_size(self.group) if self.group is not None else 1
+        self.full_rank = dist.get_rank(self.group) if self.group is not None else 0
+        self.pp_size, self.pp_rank, self.pp_group = 1, 0, None
+        pp = int(_cfg(self.engine_config, "pipeline_model_parallel_size", 1) or 1)
+        if pp <= 1:
+            return
+        W, r = self.full_world, self.full_rank
+        cfg = self.model_config
+        if W % pp != 0:
+            raise ValueError(f"pipeline_model_parallel_size {pp} does not divide the {W} ranks of the engine's group")
+        if pp > cfg.num_hidden_layers:
+            raise ValueError(f"pipeline_model_parallel_size {pp} exceeds the {cfg.num_hidden_layers} decoder layers")
+        if cfg.tie_word_embeddings and not self.value_head:
+            raise ValueError("tied input / output embeddings cannot be split over pipeline stages")
+        if self.lora is not None or int(_cfg(self.engine_config, "ulysses_sequence_parallel_size", 1) or 1) > 1:
+            raise ValueError("pipeline_model_parallel_size > 1 cannot be combined with LoRA or Ulysses")
+        S = W // pp
+        ranks_of = dist.get_process_group_ranks(self.group)
+        stage_group = None
+        for st in range(pp):  # collective: every rank creates every group
+            grp = dist.new_group(ranks_of[st * S : (st + 1) * S])
+            if r // S == st:
+                stage_group = grp
+        for i in range(S):
+            grp = dist.new_group([ranks_of[st * S + i] for st in range(pp)])
+            if r % S == i:
+                self.pp_group = grp
+        self.pp_size, self.pp_rank = pp, r // S
+        self.pp_prev = ranks_of[r - S] if self.pp_rank > 0 else None           # global ranks of the neighbours
+        self.pp_next = ranks_of[r + S] if self.pp_rank < pp - 1 else None
+        self.pp_last = ranks_of[(pp - 1) * S + r % S]
+        self.pp_stage_ranks = [ranks_of[st * S + r % S] for st in range(pp)]
+        self.group = stage_group  # may hold this rank alone
+
+    def _build_parallel_model(self):
+        """This rank's part of the model: the whole model is initialised (or given), cut to the stage's layers and
+        sliced for the tensor-parallel rank."""
+        from ...parallel.pipeline import stage_layers
         from ...parallel.reshard import shard_state_dict, tp_model_config
 
         cfg, tp, r = self.model_config, self.tp_size, self.tp_rank
@@ -210,17 +274,35 @@ class NativeEngine(BaseEngine):
             full = CausalLM(cfg, dtype=self.work_dtype, device=self.device, value_head=self.value_head).init_weights(self.seed)
             state = dict(full.state_dict())
             del full
-        vp = (not self.value_head) and (not cfg.tie_word_embeddings) and cfg.vocab_size % tp == 0
+        lo, hi = stage_layers(cfg.num_hidden_layers, self.pp_size, self.pp_rank)
+        first, last = self.pp_rank == 0, self.pp_rank == self.pp_size - 1
+        if self.pp_size > 1:  # keep this stage's tensors; layers are renumbered from 0 inside the stage's module
+            kept = {}
+            for k, v in state.items():
+                if k.startswith("layers."):
+                    i = int(k.split(".")[1])
+                    if lo <= i < hi:
+                        kept[f"layers.{i - lo}." + k.split(".", 2)[2]] = v
+                elif k.startswith("embed_tokens."):
+                    if first:
+                        kept[k] = v
+                elif last:
+                    kept[k] = v
+            state = kept
+        vp = last and (not self.value_head) and (not cfg.tie_word_embeddings) and tp > 1 and cfg.vocab_size % tp == 0
         self._vocab_parallel_head = vp
         tcfg = tp_model_config(cfg, r, tp)
         if vp:
             tcfg.extra["lm_head_rows"] = cfg.vocab_size // tp
-        self.model = CausalLM(tcfg, dtype=self.work_dtype, device=self.device, value_head=self.value_head)
+        self.model = CausalLM(tcfg, dtype=self.work_dtype, device=self.device, value_head=self.value_head,
+                              layer_range=(lo, hi), has_embed=first or (last and cfg.tie_word_embeddings and not self.value_head),
+                              has_head=last)
         sl = shard_state_dict(cfg, {k: v.to(self.work_dtype) for k, v in state.items()}, r, tp, vocab_parallel_head=vp)
         self.model.load_state_dict(sl, strict=False)
-        for layer in self.model.layers:
-            layer.self_attn.tp_group = self.tp_group
-            layer.mlp.tp_group = self.tp_group
+        if tp > 1:
+            for layer in self.model.layers:
+                layer.self_attn.tp_group = self.tp_group
+                layer.mlp.tp_group = self.tp_group
         if vp:
             self.model.tp_group = self.tp_group
             self.model.vocab_offset = r * (cfg.vocab_size // tp)
@@ -240,26 +322,19 @@ class NativeEngine(BaseEngine):
             # the slices are sharded over the ranks that hold the same slice
             if 0 < fs < W // self.tp_size:
                 raise ValueError("fsdp_size (hybrid sharding) cannot be combined with tensor_model_parallel_size > 1")
-            self.shard_group = self._tp_dp_group if W // self.tp_size > 1 else None
+            self.shard_group = self._tp_dp_group  # may hold this rank alone
             if self.comm is not None and self.device.type == "cuda":
                 from ...parallel.peer_comm import PeerComm
 
-                self.comm = PeerComm(self.shard_group) if self.shard_group is not None else None
+                self.comm = PeerComm(self.shard_group) if W // self.tp_size > 1 else None
             return
         if fs <= 0 or fs >= W:
             return
         if W % fs != 0:
             raise ValueError(f"fsdp_size {fs} does not divide the {W} ranks of the engine's group")
-        ranks_of = dist.get_process_group_ranks(self.group)
         r = self.dp_rank_all
-        for g in range(W // fs):  # collective: every rank creates every group
-            grp = dist.new_group([ranks_of[g * fs + i] for i in range(fs)])
-            if r // fs == g:
-                self.shard_group = grp
-        for i in range(fs):
-            grp = dist.new_group([ranks_of[g * fs + i] for g in range(W // fs)])
-            if r % fs == i:
-                self.replica_group = grp
+        self.shard_group = self._block_groups(fs, strided=False)
+        self.replica_group = self._block_groups(fs, strided=True)
         self.hsdp = True
         self.replica_index = r // fs
         if self.comm is not None and self.device.type == "cuda":
@@ -285,34 +360,54 @@ class NativeEngine(BaseEngine):
         from ...utils.ulysses import validate_ulysses_config
 
         validate_ulysses_config(self.model_config.num_attention_heads, sp)
-        ranks_of = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(W))
-        for g in range(W // sp):
-            members = [ranks_of[g * sp + i] for i in range(sp)]
-            grp = dist.new_group(members)  # collective: every rank creates every group
-            if r // sp == g:
-                self.sp_group = grp
+        self.sp_group = self._block_groups(sp, strided=False)
         self.sp_size, self.sp_rank = sp, r % sp
         for layer in self.model.layers:
             layer.self_attn.sp_group = self.sp_group
 
     @property
+    def model_parallel(self) -> bool:
+        """The model itself is split over ranks (tensor or pipeline parallelism), not only its storage."""
+        return self.tp_size > 1 or self.pp_size > 1
+
+    @property
     def mp_size(self) -> int:
         """Ranks that work on the same samples: a sequence-parallel or a tensor-parallel group."""
+        return self._mp_inner * max(self.pp_size, 1)
+
+    @property
+    def _mp_inner(self) -> int:
         return max(self.sp_size, 1) * max(self.tp_size, 1)
 
     @property
     def mp_group(self):
-        return self.tp_group if self.tp_size > 1 else self.sp_group
+        """Group of the ranks that work on the same samples (created on first use: a collective)."""
+        if self.pp_size <= 1:
+            return self.tp_group if self.tp_size > 1 else self.sp_group
+        if getattr(self, "_pool_group", None) is None:
+            import torch.distributed as dist
+
+            ranks_of = dist.get_process_group_ranks(self.full_group)
+            S, inner = self.full_world // self.pp_size, self._mp_inner
+            for d in range(S // inner):
+                members = [ranks_of[st * S + d * inner + i] for st in range(self.pp_size) for i in range(inner)]
+                grp = dist.new_group(members)
+                if (self.full_rank % S) // inner == d:
+                    self._pool_group, self._pool_rank = grp, members.index(ranks_of[self.full_rank])
+        return self._pool_group
 
     @property
     def mp_rank(self) -> int:
+        if self.pp_size > 1:
+            _ = self.mp_group
+            return self._pool_rank
         return self.tp_rank if self.tp_size > 1 else self.sp_rank
 
     def get_data_parallel_size(self) -> int:
-        return self.dp_world // self.mp_size
+        return self.dp_world // self._mp_inner
 
     def get_data_parallel_rank(self) -> int:
-        return self.dp_rank_all // self.mp_size
+        return self.dp_rank_all // self._mp_inner
 
     def get_data_parallel_group(self):
         return self.group
@@ -365,7 +460,13 @@ class NativeEngine(BaseEngine):
             ids_l, pos_l, _ = ulysses_pad_and_slice_inputs(batch.input_ids, batch.position_ids, self.sp_size, self.sp_group)
             sp_lo = self.sp_rank * ids_l.shape[0]
             batch = PackedBatch(ids_l, pos_l, batch.cu_seqlens, batch.max_seqlen, total_tokens=T)
-        hidden = unit_call(z, self._embed_unit, lambda: m.embed(batch))
+        if self.pp_rank > 0:
+            from ...parallel.pipeline import pipe_recv
+
+            hidden = pipe_recv(self.pp_prev, (batch.input_ids.shape[0], self.model_config.hidden_size), self.work_dtype,
+                               self.device, need_grad=self.trainable)
+        else:
+            hidden = unit_call(z, self._embed_unit, lambda: m.embed(batch))
         residual = None
         n_layers = len(m.layers)
         n_keep = self._layers_to_keep(hidden.shape[0]) if (torch.is_grad_enabled() and self.trainable) else 0
@@ -381,9 +482,28 @@ class NativeEngine(BaseEngine):
             self._sp_sel = (mine, all_rows.numel())
             local = all_rows[mine] - sp_lo
             return hidden[local], residual[local]
+        if self.pp_rank < self.pp_size - 1:
+            from ...parallel.pipeline import pipe_send
+
+            # one tensor travels: the next stage's first RMSNorm re-creates (normed, residual) from hidden + residual
+            return "sent", pipe_send(hidden if residual is None else hidden + residual, self.pp_next)
         if rows is not None:
-            hidden, residual = hidden[rows], residual[rows]
+            hidden, residual = hidden[rows], (residual[rows] if residual is not None else None)
         return hidden, residual
+
+    def _pp_share(self, outs: tuple, token, n: int):
+        """Pipeline stages other than the last one return placeholders that carry the last stage's VALUES (broadcast
+        over the stages) and, through ``token``, this stage's part of the graph: calling backward on a loss built from
+        them runs the stage's backward (receive the gradient from the next stage, back-propagate, send it on)."""
+        import torch.distributed as dist
+
+        last = self.pp_rank == self.pp_size - 1
+        shared = []
+        for t in outs:
+            vals = t.detach().float().clone() if last else torch.zeros(n, dtype=torch.float32, device=self.device)
+            dist.broadcast(vals, src=self.pp_last, group=self.pp_group)
+            shared.append(t if last else vals + 0.0 * token)
+        return tuple(shared)
 
     def _layers_to_keep(self, tokens: int) -> int:
         """How many decoder layers keep their activations for the backward instead of recomputing them.
@@ -450,6 +570,8 @@ class NativeEngine(BaseEngine):
         """Log-prob of ``labels[i]`` predicted at packed position ``rows[i]`` (+ entropy), both fp32."""
         m, z = self.model, self.zero
         hidden, residual = self._forward_hidden_rows_safe(batch, rows)
+        if isinstance(hidden, str):  # an earlier pipeline stage: the residual stream went to the next stage
+            return self._pp_share((0, 0), residual, rows.numel())
 
         if self.sp_size > 1:
             labels = labels[self._sp_sel[0]]
@@ -457,12 +579,16 @@ class NativeEngine(BaseEngine):
         def head(h, r):
             return m.logprob_entropy(m.final_norm(h, r), labels, temperature)
 
-        return self._sp_merge(unit_call(z, self._head_unit, head, hidden, residual))
+        out = self._sp_merge(unit_call(z, self._head_unit, head, hidden, residual))
+        return self._pp_share(out, None, rows.numel()) if self.pp_size > 1 else out
 
     def forward_values(self, batch: PackedBatch, rows: torch.Tensor):
         m, z = self.model, self.zero
         hidden, residual = self._forward_hidden_rows_safe(batch, rows)
-        return self._sp_merge(unit_call(z, self._head_unit, lambda h, r: m.values(m.final_norm(h, r)), hidden, residual))
+        if isinstance(hidden, str):
+            return self._pp_share((0,), residual, rows.numel())[0]
+        out = self._sp_merge(unit_call(z, self._head_unit, lambda h, r: m.values(m.final_norm(h, r)), hidden, residual))
+        return self._pp_share((out,), None, rows.numel())[0] if self.pp_size > 1 else out
 
     def forward_logits(self, batch: PackedBatch, rows: Optional[torch.Tensor] = None):
         m, z = self.model, self.zero
@@ -502,10 +628,9 @@ class NativeEngine(BaseEngine):
             counted = float(lens.sum())
         norm = torch.tensor([counted, float(len(lens))], dtype=torch.float64, device=self.device)
         dp_group = self.get_data_parallel_group()
-        dp = self.get_data_parallel_size()
         if self.dp_world > 1:
             dist.all_reduce(norm, group=self.group)
-            norm = norm / self.mp_size
+            norm = norm / self._mp_inner
         # micro-batches: fixed sample count, or packed up to a token budget
         n = len(lens)
         if tu.get(data, "use_dynamic_bsz", False):
@@ -524,6 +649,7 @@ class NativeEngine(BaseEngine):
             groups = [list(range(i, min(i + mb, n))) for i in range(0, n, mb)]
         out = {"loss": [], "metrics": {}, "model_output": {}}
         pieces: dict = {}
+        pending: list = []
         for g in groups:
             micro = data[torch.tensor(g)]
             mids = micro["input_ids"]
@@ -550,13 +676,20 @@ class NativeEngine(BaseEngine):
             for k, v in model_output.items():
                 pieces.setdefault(k, []).append(v.detach())
             if loss_function is not None:
-                tu.assign_non_tensor(micro, dp_size=dp, batch_num_tokens=float(norm[0]), global_batch_size=float(norm[1]))
+                # this engine SUMS the ranks' gradients (reduce-scatter without averaging), so the factor with which the
+                # reference undoes its gradient averaging is 1: a rank's loss is its part of the global mean
+                tu.assign_non_tensor(micro, dp_size=1, batch_num_tokens=float(norm[0]), global_batch_size=float(norm[1]))
                 loss, metrics = loss_function(model_output=model_output, data=micro, dp_group=dp_group)
                 if not forward_only:
-                    loss.backward()
+                    if self.pp_size > 1:
+                        pending.append(loss)  # pipelined: all forwards first, then the backwards in the same order
+                    else:
+                        loss.backward()
                 out["loss"].append(float(loss.detach()))
                 for k, v in (metrics or {}).items():
                     out["metrics"].setdefault(k, []).append(float(v) if not isinstance(v, (list, dict)) else v)
+        for loss in pending:
+            loss.backward()
         for k, v in pieces.items():
             out["model_output"][k] = tu.concat_nested_tensors(v) if len(v) > 1 else v[0]
         return out
@@ -574,7 +707,8 @@ class NativeEngine(BaseEngine):
             return self.forward_backward_batch(data, loss_function, forward_only=True)
 
     def is_mp_src_rank_with_outputs(self) -> bool:
-        return self.mp_rank == 0
+        inner = self.tp_rank if self.tp_size > 1 else self.sp_rank
+        return inner == 0 and self.pp_rank == self.pp_size - 1
 
     @staticmethod
     def response_rows(input_ids: torch.Tensor, attention_mask: torch.Tensor, response_length: int,
@@ -694,6 +828,8 @@ class NativeEngine(BaseEngine):
                 dist.all_reduce(self._sumsq, group=self.shard_group)
             if self.tp_size > 1:
                 dist.all_reduce(self._sumsq, group=self.tp_group)
+            if self.pp_size > 1:  # every stage holds its own layers: the norm is over all of them
+                dist.all_reduce(self._sumsq, group=self.pp_group)
             ops.clip_coef(self._sumsq, clip, 1.0, self._scale, self._skip, self._norm)
             ops.adamw_step(z.master, z.grad, z.exp_avg, z.exp_avg_sq, z.shard16, lr=lr, betas=betas, eps=eps,
                            weight_decay=wd, step=self.step_count, scale=self._scale, skip=self._skip)
@@ -707,6 +843,8 @@ class NativeEngine(BaseEngine):
                 dist.all_reduce(sq, group=self.shard_group)
             if self.tp_size > 1:
                 dist.all_reduce(sq, group=self.tp_group)
+            if self.pp_size > 1:
+                dist.all_reduce(sq, group=self.pp_group)
             norm = sq.sqrt().float()
             if torch.isfinite(norm).all():
                 coef = min(1.0, clip / (norm.item() + 1e-6)) if clip > 0 else 1.0
@@ -757,8 +895,33 @@ class NativeEngine(BaseEngine):
         return native_to_hf_items(self.model_config, self._merged_named_tensors(dtype))
 
     def _merged_named_tensors(self, dtype=None):
-        """(name, full tensor) of every parameter; adapted weights come out merged (W + (alpha / r) B A); tensor-parallel
-        slices are gathered over the group and put back together."""
+        """(name, full tensor) of every parameter of the WHOLE model, in the same order on every rank: pipeline stages
+        take turns broadcasting their tensors to the ranks at the same position of the other stages."""
+        if self.pp_size <= 1:
+            yield from self._stage_named_tensors(dtype)
+            return
+        import torch.distributed as dist
+
+        for st in range(self.pp_size):
+            src = self.pp_stage_ranks[st]
+            mine = st == self.pp_rank
+            it = self._stage_named_tensors(dtype) if mine else None
+            while True:
+                head = [None]
+                if mine:
+                    nxt = next(it, None)
+                    head = [None if nxt is None else (nxt[0], tuple(nxt[1].shape), nxt[1].dtype)]
+                dist.broadcast_object_list(head, src=src, group=self.pp_group)
+                if head[0] is None:
+                    break
+                name, shape, dt = head[0]
+                t = nxt[1].contiguous() if mine else torch.empty(shape, dtype=dt, device=self.device)
+                dist.broadcast(t, src=src, group=self.pp_group)
+                yield name, t
+
+    def _stage_named_tensors(self, dtype=None):
+        """(name, full tensor) of every parameter of this pipeline stage; adapted weights come out merged
+        (W + (alpha / r) B A); tensor-parallel slices are gathered over the group and put back together."""
         if self.tp_size > 1:
             import torch.distributed as dist
 

@@ -90,7 +90,8 @@ class _WorkerBase(Worker):
         eng_cfg = _cfg(cfg, "fsdp_config", None) or _cfg(_cfg(cfg, "model", None), "fsdp_config", None)
         sp = int(_cfg(eng_cfg, "ulysses_sequence_parallel_size", 1) or 1) if eng_cfg is not None else 1
         sp = max(sp, int(_cfg(cfg, "ulysses_sequence_parallel_size", 1) or 1))
-        sp *= int(_cfg(eng_cfg, "tensor_model_parallel_size", 1) or 1) if eng_cfg is not None else 1
+        if eng_cfg is not None:
+            sp *= int(_cfg(eng_cfg, "tensor_model_parallel_size", 1) or 1) * int(_cfg(eng_cfg, "pipeline_model_parallel_size", 1) or 1)
         dp = max(self.world // max(sp, 1), 1)
         mini = int(getattr(cfg, mini_key)) * n // dp
         assert mini > 0, f"{mini_key} {getattr(cfg, mini_key)} * n {n} must be >= data-parallel size {dp}"
@@ -152,16 +153,22 @@ class ActorRolloutRefWorker(_WorkerBase):
             self._norm_batch(self.actor_cfg, n=n)
         # Ulysses: the ranks of a sequence-parallel group share one data-parallel rank and the first one reports
         # (dispatch of verl/single_controller/base/decorator.py:297-328, registration of fsdp_workers.py:146-273)
-        def sp_of(c):  # ranks that share their samples: sequence-parallel x tensor-parallel
+        def mesh_of(c):
+            """(data-parallel rank, reports results) of this rank under the engine's layout: pipeline stages are
+            consecutive blocks of ranks; inside a block ``tp x sp`` consecutive ranks share their samples; the last
+            stage's first rank of such a group reports."""
             if c is None:
-                return 1
+                return self.dp_rank, True
             ec = _cfg(c, "fsdp_config", None)
-            return (int(_cfg(ec, "ulysses_sequence_parallel_size", 1) or 1) * int(_cfg(ec, "tensor_model_parallel_size", 1) or 1))
+            inner = (int(_cfg(ec, "ulysses_sequence_parallel_size", 1) or 1) * int(_cfg(ec, "tensor_model_parallel_size", 1) or 1))
+            pp = int(_cfg(ec, "pipeline_model_parallel_size", 1) or 1)
+            S = max(self.world // pp, 1)
+            local = self.dp_rank % S
+            return local // inner, (local % inner == 0 and self.dp_rank // S == pp - 1)
 
-        rank = self.dp_rank
-        sp_a, sp_r = sp_of(self.actor_cfg), sp_of(self.ref_cfg if self.ref_cfg is not None else self.actor_cfg)
-        self._register_dispatch_collect_info("actor", dp_rank=rank // sp_a, is_collect=rank % sp_a == 0)
-        self._register_dispatch_collect_info("ref", dp_rank=rank // sp_r, is_collect=rank % sp_r == 0)
+        (dp_a, col_a), (dp_r, col_r) = mesh_of(self.actor_cfg), mesh_of(self.ref_cfg if self.ref_cfg is not None else self.actor_cfg)
+        self._register_dispatch_collect_info("actor", dp_rank=dp_a, is_collect=col_a)
+        self._register_dispatch_collect_info("ref", dp_rank=dp_r, is_collect=col_r)
         # a rollout replica spans `tensor_model_parallel_size` consecutive ranks: they receive the same prompts and
         # the first one reports (verl/workers/rollout/replica.py:96-143)
         self.rollout_tp = int(_cfg(self.rollout_cfg, "tensor_model_parallel_size", 1) or 1) if self._is_rollout else 1
@@ -276,7 +283,7 @@ class ActorRolloutRefWorker(_WorkerBase):
             self._setup_rollout_tp()
             tp_rank = self.dp_rank % tp
             self.rollout_model = CausalLM(tp_model_config(model_cfg, tp_rank, tp), dtype=dtype, device=self.device)
-            if self._is_actor and self.actor_engine.tp_size == 1:
+            if self._is_actor and not self.actor_engine.model_parallel:
                 self._bind_rollout_to_flat(tp_rank, tp)
             elif self._is_actor:
                 self._generic_sync = True
@@ -287,11 +294,11 @@ class ActorRolloutRefWorker(_WorkerBase):
                     del full
                 sl = shard_state_dict(model_cfg, {k: v.to(dtype) for k, v in state.items()}, tp_rank, tp)
                 self.rollout_model.load_state_dict(sl, strict=False)
-        elif self._is_actor and self.world == 1 and not getattr(self, "_lora", False) and self.actor_engine.tp_size == 1:
+        elif self._is_actor and self.world == 1 and not getattr(self, "_lora", False) and not self.actor_engine.model_parallel:
             self.rollout_model = self.actor_engine.model  # same tensors: weight sync is free
         else:
             self.rollout_model = CausalLM(model_cfg, dtype=dtype, device=self.device)
-            if self._is_actor and self.actor_engine.tp_size == 1:
+            if self._is_actor and not self.actor_engine.model_parallel:
                 self._bind_rollout_to_flat()
             elif self._is_actor:
                 self._generic_sync = True  # a tensor-parallel trainer: weights travel as whole (HF-named) tensors

@@ -89,8 +89,10 @@ class TrainingWorker(Worker):
         if dist.is_initialized() and dist.get_world_size() > 1:
             dev = torch.device(self.engine.device)
             loss = loss.to(dev)
+            # a rank's loss is its samples' part of the global mean: add the parts up (ranks of a tensor- / sequence-
+            # parallel group report the same part)
             dist.all_reduce(loss, group=grp)
-            loss = loss / dist.get_world_size(grp)
+            loss = loss / max(int(getattr(self.engine, "_mp_inner", 1)), 1)
         grad_norm, lr = metrics.pop("grad_norm", None), metrics.pop("lr", None)
         final = {}
         if dist.is_initialized() and dist.get_world_size() > 1:
