@@ -126,6 +126,7 @@ class MoEMLP(nn.Module):
         self.last_routing = None
         self.replay_routing = None
         self.tp_group = None  # training with the experts sharded over a tensor-parallel group (tokens replicated)
+        self.ep_group = None  # training with expert parallelism: tokens travel to the rank that owns the expert
 
     def reset_parameters(self, generator=None):
         self.gate.reset_parameters(generator)
@@ -159,6 +160,10 @@ class MoEMLP(nn.Module):
 
             top_w = copy_to_tp_region(top_w, self.tp_group)  # each rank sees only its experts' share of d top_w
         self.last_routing = top_i.detach()
+        if self.ep_group is not None:
+            from ..parallel.expert_parallel import ep_moe_mlp
+
+            return ep_moe_mlp(x, top_i, top_w, self.gate_up_proj, self.down_proj, ops.swiglu, self.ep_group, self.E)
         if x.is_cuda and _grouped_gemm_ok(self.gate_up_proj, self.down_proj):
             # one grouped GEMM per projection for all experts, routing layout computed on the device
             from ..ops.moe import moe_mlp

@@ -116,3 +116,85 @@ class ExpertParallelMoE:
                                      c._epoch(c.CH_COPY), c._gate(c.CH_COPY), status, stream)
         _lib.check(rc, "vb_moe_combine")
         return out
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Training-side expert parallelism: every rank routes its OWN tokens, sends each (token, slot) pair to the rank that
+# owns the expert, runs its experts on what arrives and sends the results back (role of Megatron's token dispatcher
+# under the reference's ``expert_model_parallel_size``, verl/workers/config/engine.py:80). Differentiable: the
+# backward of an all-to-all is the all-to-all with the split sizes swapped.
+import torch.distributed as dist  # noqa: E402
+
+
+def _all_to_all_rows(x: torch.Tensor, send: list, recv: list, group) -> torch.Tensor:
+    """Rows ``x[sum(send[:r]) : sum(send[:r + 1])]`` go to rank r; returns the rows received, in rank order."""
+    out = x.new_empty((sum(recv),) + tuple(x.shape[1:]))
+    if dist.get_backend(group) == "gloo":
+        # gloo has no all-to-all: every rank gathers all buffers and keeps the rows addressed to it (CPU tests)
+        W, me = dist.get_world_size(group), dist.get_rank(group)
+        cap = torch.tensor([x.shape[0]], dtype=torch.long)
+        caps = [torch.zeros(1, dtype=torch.long) for _ in range(W)]
+        dist.all_gather(caps, cap, group=group)
+        m = int(max(c.item() for c in caps))
+        pad = x.new_zeros((m,) + tuple(x.shape[1:]))
+        pad[: x.shape[0]] = x
+        bufs = [torch.empty_like(pad) for _ in range(W)]
+        dist.all_gather(bufs, pad, group=group)
+        splits = [None] * W
+        dist.all_gather_object(splits, list(send), group=group)
+        o = 0
+        for r in range(W):
+            lo = sum(splits[r][:me])
+            n = splits[r][me]
+            out[o : o + n] = bufs[r][lo : lo + n]
+            o += n
+        return out
+    dist.all_to_all_single(out, x.contiguous(), output_split_sizes=list(recv), input_split_sizes=list(send), group=group)
+    return out
+
+
+class _AllToAllRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, send, recv, group):
+        ctx.send, ctx.recv, ctx.group = send, recv, group
+        return _all_to_all_rows(x, send, recv, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_to_all_rows(g.contiguous(), ctx.recv, ctx.send, ctx.group), None, None, None
+
+
+def ep_moe_mlp(x: torch.Tensor, top_i: torch.Tensor, top_w: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, act,
+               group, num_experts: int) -> torch.Tensor:
+    """Expert-parallel routed MLP for training. ``x [T, H]``: this rank's tokens; ``top_i / top_w [T, k]``: global expert
+    ids and weights; ``gate_up [E / W, 2I, H]``, ``down [E / W, H, I]``: this rank's experts (rank r owns experts
+    ``[r E / W, (r + 1) E / W)``). Returns ``[T, H]``."""
+    from ..ops.moe import moe_mlp
+
+    W = dist.get_world_size(group)
+    T, k = top_i.shape
+    E_local = num_experts // W
+    flat_e = top_i.reshape(-1)
+    dest = torch.div(flat_e, E_local, rounding_mode="floor")
+    order = torch.argsort(dest, stable=True)
+    send = torch.bincount(dest, minlength=W).tolist()          # pairs this rank sends to every rank
+    counts = torch.tensor(send, dtype=torch.long, device=x.device)
+    got = torch.empty_like(counts)
+    if dist.get_backend(group) == "gloo":
+        allc = [torch.empty_like(counts) for _ in range(W)]
+        dist.all_gather(allc, counts, group=group)
+        got = torch.stack(allc)[:, dist.get_rank(group)].contiguous()
+    else:
+        dist.all_to_all_single(got, counts, group=group)
+    recv = got.tolist()
+    tok = torch.div(order, k, rounding_mode="floor")
+    xs = x.index_select(0, tok)                                 # rows in destination order
+    x_in = _AllToAllRows.apply(xs, send, recv, group)
+    e_in = _all_to_all_rows((flat_e[order] % E_local).contiguous(), send, recv, group)
+    if x_in.shape[0] > 0:
+        y_in = moe_mlp(x_in, e_in[:, None], torch.ones(x_in.shape[0], 1, dtype=torch.float32, device=x.device), gate_up, down, act)
+    else:  # no token for this rank's experts: keep the graph (and the collectives) alive
+        y_in = x_in * 0.0 + 0.0 * (gate_up.sum() + down.sum()).to(x_in.dtype)
+    ys = _AllToAllRows.apply(y_in, recv, send, group)           # back in this rank's destination order
+    w = top_w.reshape(-1)[order].to(ys.dtype).unsqueeze(-1)
+    return torch.zeros_like(x).index_add(0, tok, ys * w)

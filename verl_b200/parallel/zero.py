@@ -47,6 +47,12 @@ class ZeroUnit:
     index: int = 0  # position in ZeroShardedParams.units
     ready: Optional[object] = None  # event of the gather that fills ``full`` on the communication stream
     grad_seq: int = -1  # sequence number of this backward's gradient buffer / reduce-scatter
+    # Expert parallelism: a unit of stacked expert matrices [E, ...] whose rank-r shard is exactly experts
+    # [r E / W, (r + 1) E / W). It is never gathered for compute: the parameters are permanent views of this rank's
+    # shard (shape [E / W, ...]) and their gradients accumulate straight into this rank's gradient shard, because the
+    # tokens routed to these experts are sent here. Storage, optimizer, checkpoints and the train -> rollout reshard
+    # see an ordinary sharded unit.
+    local: bool = False
 
 
 class ZeroShardedParams:
@@ -68,7 +74,9 @@ class ZeroShardedParams:
         self._anchor = None
         seen: set[int] = set()
         off = 0
-        for name, mod in units:
+        for spec in units:
+            name, mod = spec[0], spec[1]
+            opts = spec[2] if len(spec) > 2 else {}
             named = list(mod.named_parameters()) if isinstance(mod, nn.Module) else list(mod)
             named = [(n, p) for n, p in named if id(p) not in seen]
             seen.update(id(p) for _, p in named)
@@ -82,6 +90,15 @@ class ZeroShardedParams:
             u.numel = cur
             quantum = align * self.world
             u.padded = (cur + quantum - 1) // quantum * quantum
+            if opts.get("local") and self.world > 1:
+                p0 = u.params[0]
+                ok = (len(u.params) == 1 and p0.dim() >= 2 and p0.shape[0] % self.world == 0
+                      and (p0.numel() // self.world) % 8 == 0)
+                if not ok:
+                    raise ValueError(f"expert-parallel unit {name}: one stacked tensor [E, ...] with E divisible by the "
+                                     f"{self.world} ranks and 16-byte aligned expert slices is required")
+                u.local = True
+                u.padded = p0.numel()
             u.shard = u.padded // self.world
             u.offset = off
             off += u.shard
@@ -116,7 +133,10 @@ class ZeroShardedParams:
                 u.full = self.shard16[u.offset : u.offset + u.shard]
         else:
             for u in self.units:
-                self._unbind(u)
+                if u.local:
+                    self._bind_local(u)
+                else:
+                    self._unbind(u)
 
     # ------------------------------------------------------------- initial load
     @torch.no_grad()
@@ -139,6 +159,14 @@ class ZeroShardedParams:
             p.data = full[o : o + n].view(shape)
             if full_grad is not None and p.requires_grad:
                 p.main_grad = full_grad[o : o + n].view(shape)
+
+    def _bind_local(self, u: ZeroUnit):
+        """Expert-parallel unit: the parameter becomes this rank's experts, a view of the shard."""
+        p, shape = u.params[0], u.shapes[0]
+        local_shape = (shape[0] // self.world,) + tuple(shape[1:])
+        p.data = self.shard16[u.offset : u.offset + u.shard].view(local_shape)
+        if self.trainable and p.requires_grad:
+            p.main_grad = self.grad[u.offset : u.offset + u.shard].view(local_shape)
 
     def _unbind(self, u: ZeroUnit):
         empty = torch.empty(0, dtype=self.work_dtype, device=self.device)
@@ -184,7 +212,7 @@ class ZeroShardedParams:
 
     def gather(self, u: ZeroUnit, for_backward: bool = False, prefetch: bool = True):
         u.gather_count += 1
-        if self.world == 1:
+        if self.world == 1 or u.local:
             return
         if u.full is None:
             self._issue_gather(u)
@@ -193,7 +221,7 @@ class ZeroShardedParams:
             u.ready = None
         if prefetch and self.comm_stream is not None:
             j = u.index + (-1 if for_backward else 1)
-            if 0 <= j < len(self.units) and self.units[j].full is None:
+            if 0 <= j < len(self.units) and self.units[j].full is None and not self.units[j].local:
                 self._issue_gather(self.units[j])
         if for_backward and self.trainable and u.full_grad is None:
             if self.comm is not None:
@@ -204,7 +232,7 @@ class ZeroShardedParams:
 
     def release(self, u: ZeroUnit):
         u.gather_count -= 1
-        if self.world == 1 or u.gather_count > 0:
+        if self.world == 1 or u.gather_count > 0 or u.local:
             return
         self._unbind(u)
         u.full = None
@@ -221,7 +249,7 @@ class ZeroShardedParams:
     def reduce_grads(self, u: ZeroUnit):
         """Sum the unit's gradient over ranks and add this rank's slice into the fp32 gradient shard."""
         self.fold_param_grads(u)
-        if self.world == 1 or not self.trainable or u.full_grad is None:
+        if self.world == 1 or not self.trainable or u.full_grad is None or u.local:
             return
         dst = self.grad[u.offset : u.offset + u.shard]
         if self.comm_stream is not None:
@@ -259,6 +287,12 @@ class ZeroShardedParams:
         """Generator of (name, full tensor), gathering one unit at a time (weight export / sync).
         Role of ``get_per_tensor_param`` (verl/workers/engine/fsdp/transformer_impl.py:635-671)."""
         for u in self.units:
+            if u.local and self.world > 1:  # expert-parallel unit: gathered for export only
+                full = torch.empty(u.padded, dtype=self.work_dtype, device=self.device)
+                dist.all_gather_into_tensor(full, self.shard16[u.offset : u.offset + u.shard].contiguous(), group=self.group)
+                t = full.view(u.shapes[0])
+                yield u.names[0], (t if dtype is None else t.to(dtype))
+                continue
             self.gather(u)
             try:
                 for i, name in enumerate(u.names):
@@ -324,6 +358,9 @@ class ZeroShardedParams:
             return h
 
         if params and self.world > 1 and self.comm is None:
+            for u in self.units:
+                if u.local:
+                    self._unbind(u)
             self.shard16 = to_host(self.shard16)
         if optimizer and self.trainable:
             self.master, self.exp_avg, self.exp_avg_sq = map(to_host, (self.master, self.exp_avg, self.exp_avg_sq))
@@ -336,6 +373,16 @@ class ZeroShardedParams:
             t = getattr(self, name)
             if t is not None and t.device != dev:
                 setattr(self, name, t.to(dev, non_blocking=True))
+        for u in self.units:
+            if u.local and self.world > 1:
+                self._bind_local(u)
+
+    def fold_local_units(self):
+        """Expert-parallel units are outside the per-layer gather / reduce cycle: gradients that autograd left in
+        ``p.grad`` (ops without a fused accumulate) are added to the gradient shard here, before the optimizer step."""
+        for u in self.units:
+            if u.local:
+                self.fold_param_grads(u)
 
 
 class _UnitFn(torch.autograd.Function):

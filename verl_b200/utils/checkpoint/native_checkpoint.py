@@ -88,10 +88,11 @@ def save_engine_checkpoint(engine, local_path: str, global_step: int = 0,
         src = z.master if z.trainable else z.shard16
         layout = int(getattr(engine, "tp_size", 1)) * 1000 + int(getattr(engine, "pp_size", 1))
         torch.save({"format": FLAT_SHARD_FORMAT, "world_size": W, "rank": r, "tp": layout if layout != 1001 else 1,
+                    "layout": _layout_sig(z),
                     "params": _param_slices(z, src)},
                    path / f"model_world_size_{W}_rank_{r}.pt")
     if "optimizer" in save_contents and z.trainable:
-        torch.save({"format": FLAT_SHARD_FORMAT, "world_size": W, "rank": r, "step": engine.step_count,
+        torch.save({"format": FLAT_SHARD_FORMAT, "world_size": W, "rank": r, "step": engine.step_count, "layout": _layout_sig(z),
                     "exp_avg": _param_slices(z, z.exp_avg), "exp_avg_sq": _param_slices(z, z.exp_avg_sq)},
                    path / f"optim_world_size_{W}_rank_{r}.pt")
     if "extra" in save_contents:
@@ -136,6 +137,17 @@ def _restore(zero, dst: torch.Tensor, slices: dict) -> None:
             dst[u.offset + s - lo : u.offset + s - lo + data.numel()].copy_(data.to(dst.device, dst.dtype))
 
 
+def _layout_sig(zero) -> str:
+    """Fingerprint of how the parameters are cut into shards: per-rank slices can be restored directly only into the
+    same cut (another unit composition, e.g. expert-parallel units, goes through the full tensors)."""
+    import hashlib
+
+    h = hashlib.sha1()
+    for u in zero.units:
+        h.update(f"{u.name}|{','.join(u.names)}|{u.shard}|{u.padded};".encode())
+    return h.hexdigest()[:16]
+
+
 def _file_world_rank(engine) -> tuple[int, int]:
     """(W, r) in the shard file names: the sharding group's, or (tensor parallelism: one set of slices per
     tensor-parallel rank) the engine group's."""
@@ -153,7 +165,8 @@ def load_engine_checkpoint(engine, local_path: str, load_contents=("model", "opt
         st = torch.load(mfile, map_location="cpu", weights_only=False) if mfile.exists() else None
         tp = int(getattr(engine, "tp_size", 1)) * 1000 + int(getattr(engine, "pp_size", 1))  # (tp, pp) of the layout
         tp = tp if tp != 1001 else 1
-        if isinstance(st, dict) and st.get("format") == FLAT_SHARD_FORMAT and st["world_size"] == W and st.get("tp", 1) == tp:
+        if (isinstance(st, dict) and st.get("format") == FLAT_SHARD_FORMAT and st["world_size"] == W and st.get("tp", 1) == tp
+                and st.get("layout", _layout_sig(z)) == _layout_sig(z)):
             if z.trainable:
                 _restore(z, z.master, st["params"])
                 z.shard16.copy_(z.master.to(z.shard16.dtype))
@@ -169,7 +182,7 @@ def load_engine_checkpoint(engine, local_path: str, load_contents=("model", "opt
     ofile = path / f"optim_world_size_{W}_rank_{r}.pt"
     if "optimizer" in load_contents and z.trainable:
         st = torch.load(ofile, map_location="cpu", weights_only=False) if ofile.exists() else None
-        if isinstance(st, dict) and st.get("format") == FLAT_SHARD_FORMAT:
+        if isinstance(st, dict) and st.get("format") == FLAT_SHARD_FORMAT and st.get("layout", _layout_sig(z)) == _layout_sig(z):
             _restore(z, z.exp_avg, st["exp_avg"])
             _restore(z, z.exp_avg_sq, st["exp_avg_sq"])
             engine.step_count = int(st.get("step", 0))

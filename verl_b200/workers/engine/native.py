@@ -129,8 +129,21 @@ class NativeEngine(BaseEngine):
             units.append(("", [("embed_tokens.weight", m.embed_tokens.weight), ("norm.weight", m.norm.weight)]))
         elif first:
             units.append(("", [("embed_tokens.weight", m.embed_tokens.weight)]))
+        # expert parallelism: the stacked expert matrices form units of their own that are never gathered (rank r's
+        # shard IS experts [r E / W, (r + 1) E / W)); they go to the end of the list so that the layer units stay
+        # neighbours for the gather prefetch
+        ep = int(_cfg(self.engine_config, "expert_model_parallel_size", 1) or 1)
+        self.ep_size = ep if (cfg.is_moe and ep > 1) else 1
+        expert_units = []
         for i, layer in enumerate(m.layers):
-            units.append((f"layers.{i + m.layer_offset}", layer))
+            name = f"layers.{i + m.layer_offset}"
+            if self.ep_size > 1:
+                skip = {id(layer.mlp.gate_up_proj), id(layer.mlp.down_proj)}
+                units.append((name, [(n, p) for n, p in layer.named_parameters() if id(p) not in skip]))
+                expert_units.append((name, [("mlp.gate_up_proj", layer.mlp.gate_up_proj)], {"local": True}))
+                expert_units.append((name, [("mlp.down_proj", layer.mlp.down_proj)], {"local": True}))
+            else:
+                units.append((name, layer))
         if last and not tied:
             head = [("norm.weight", m.norm.weight)]
             if m.value_head:
@@ -138,15 +151,27 @@ class NativeEngine(BaseEngine):
             else:
                 head.append(("lm_head.weight", m.lm_head.weight))
             units.append(("", head))
+        n_plain = len(units)
+        units += expert_units
         self._setup_hybrid_sharding()
         self.zero = ZeroShardedParams(units, group=self.shard_group, work_dtype=self.work_dtype, device=self.device,
                                       trainable=self.trainable and not self._lora_params, comm=self.comm)
+        if self.ep_size > 1:
+            if self.tp_size > 1 or self.lora is not None:
+                raise ValueError("expert_model_parallel_size > 1 cannot be combined with tensor parallelism (which already "
+                                 "splits the experts over its group) or LoRA")
+            if self.zero.world > 1 and self.ep_size != self.zero.world:
+                raise ValueError(f"expert_model_parallel_size {self.ep_size} must equal the size of the sharding group "
+                                 f"({self.zero.world}): every rank of the group owns E / {self.zero.world} experts")
+            if self.zero.world > 1:
+                for layer in m.layers:
+                    layer.mlp.ep_group = self.shard_group
         self.zero.frozen_grad = bool(self._lora_params)
         self._setup_sequence_parallel()
         n0 = 1 if (first or tied) else 0
         self._embed_unit = self.zero.units[0] if (first or tied) else None
         self._layer_units = self.zero.units[n0 : n0 + len(m.layers)]
-        self._head_unit = (self.zero.units[0] if tied else self.zero.units[-1]) if last else None
+        self._head_unit = (self.zero.units[0] if tied else self.zero.units[n_plain - 1]) if last else None
         if self.device.type == "cuda":
             torch.cuda.empty_cache()
         if self._lora_params:
@@ -819,6 +844,7 @@ class NativeEngine(BaseEngine):
         eps = float(_cfg(oc, "eps", 1e-8))
         self.step_count += 1
         z.wait_comm()  # the last reduce-scatters run on the communication stream
+        z.fold_local_units()
         if self.hsdp:  # hybrid sharding: add up the replicas' gradient shards (the loss is normalised globally)
             dist.all_reduce(z.grad, group=self.replica_group)
         if self.device.type == "cuda":
