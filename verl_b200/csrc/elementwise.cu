@@ -152,7 +152,11 @@ __global__ void colsum_kernel(const float* __restrict__ partial, int nparts, int
 // sign = +1 forward, -1 backward (transpose of the rotation).
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k, long long q_stride,
                             long long k_stride, const long long* __restrict__ pos, const float* __restrict__ cos_t,
-                            const float* __restrict__ sin_t, int T, int Hq, int Hk, int D, float sign) {
+                            const float* __restrict__ sin_t, int T, int Hq, int Hk, int D, float sign, int mrope_s0,
+                            int mrope_s1) {
+  // multimodal rotary embedding (mrope_s0 > 0): pos is [3, T] (temporal, height, width); rotary frequency j takes the
+  // position of axis 0 for j < s0, of axis 1 for j < s0 + s1, of axis 2 above (sections are multiples of 8, so the 8
+  // frequencies of one thread share an axis)
   const int half = D >> 1;
   const int vec_per_head = half >> 3;
   const long long total = (long long)T * (Hq + Hk) * vec_per_head;
@@ -163,7 +167,14 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16* __rest
     const int h = th % (Hq + Hk);
     const long long t = th / (Hq + Hk);
     __nv_bfloat16* base = (h < Hq) ? (q + t * q_stride + (long long)h * D) : (k + t * k_stride + (long long)(h - Hq) * D);
-    const long long p = pos[t];
+    long long p;
+    if (mrope_s0 > 0) {
+      const int j = v * 8;
+      const int axis = j < mrope_s0 ? 0 : (j < mrope_s0 + mrope_s1 ? 1 : 2);
+      p = pos[(long long)axis * T + t];
+    } else {
+      p = pos[t];
+    }
     const float* c = cos_t + p * half + v * 8;
     const float* s = sin_t + p * half + v * 8;
     float a[8], b[8];
@@ -359,15 +370,32 @@ extern "C" int vb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   return (int)cudaGetLastError();
 }
 
+static int rope_launch(void* q, void* k, long long q_stride, long long k_stride, const long long* pos, const float* cos_t,
+                       const float* sin_t, int T, int Hq, int Hk, int D, int backward, int s0, int s1, cudaStream_t stream);
+
 extern "C" int vb_rope(void* q, void* k, long long q_stride, long long k_stride, const long long* pos,
                        const float* cos_t, const float* sin_t, int T, int Hq, int Hk, int D, int backward,
                        cudaStream_t stream) {
+  return rope_launch(q, k, q_stride, k_stride, pos, cos_t, sin_t, T, Hq, Hk, D, backward, 0, 0, stream);
+}
+
+// Multimodal RoPE: pos is [3, T]; s0 / s1 = number of rotary frequencies (of D / 2) that follow the temporal / height
+// positions (the rest follow the width positions); both multiples of 8.
+extern "C" int vb_mrope(void* q, void* k, long long q_stride, long long k_stride, const long long* pos3,
+                        const float* cos_t, const float* sin_t, int T, int Hq, int Hk, int D, int s0, int s1, int backward,
+                        cudaStream_t stream) {
+  if (s0 <= 0 || s1 < 0 || (s0 & 7) || (s1 & 7) || s0 + s1 > D / 2) return -3;
+  return rope_launch(q, k, q_stride, k_stride, pos3, cos_t, sin_t, T, Hq, Hk, D, backward, s0, s1, stream);
+}
+
+static int rope_launch(void* q, void* k, long long q_stride, long long k_stride, const long long* pos, const float* cos_t,
+                       const float* sin_t, int T, int Hq, int Hk, int D, int backward, int s0, int s1, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (D & 15) return -3;
   const long long total = (long long)T * (Hq + Hk) * (D / 16);
   rope_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, stream>>>((__nv_bfloat16*)q, (__nv_bfloat16*)k, q_stride,
                                                                   k_stride, pos, cos_t, sin_t, T, Hq, Hk, D,
-                                                                  backward ? -1.f : 1.f);
+                                                                  backward ? -1.f : 1.f, s0, s1);
   vb_count_launch();
   return (int)cudaGetLastError();
 }

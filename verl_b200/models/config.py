@@ -16,12 +16,16 @@ _ARCH_TO_TYPE = {
     "Qwen2ForCausalLM": "qwen2",
     "Qwen3ForCausalLM": "qwen3",
     "Qwen3MoeForCausalLM": "qwen3_moe",
+    "Qwen2VLForConditionalGeneration": "qwen2_vl",
+    "Qwen2_5_VLForConditionalGeneration": "qwen2_5_vl",
     "LlamaForTokenClassification": "llama",
     "Qwen2ForTokenClassification": "qwen2",
     "Qwen3ForTokenClassification": "qwen3",
 }
 _TYPE_TO_ARCH = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
-                 "qwen3_moe": "Qwen3MoeForCausalLM"}
+                 "qwen3_moe": "Qwen3MoeForCausalLM", "qwen2_vl": "Qwen2VLForConditionalGeneration",
+                 "qwen2_5_vl": "Qwen2_5_VLForConditionalGeneration"}
+_VL_TYPES = ("qwen2_vl", "qwen2_5_vl")
 
 
 @dataclass
@@ -57,7 +61,7 @@ class ModelConfig:
         if self.head_dim is None:
             self.head_dim = self.hidden_size // self.num_attention_heads
         if self.attention_bias is None:
-            self.attention_bias = self.model_type == "qwen2"
+            self.attention_bias = self.model_type in ("qwen2",) + _VL_TYPES
         if self.qk_norm is None:
             self.qk_norm = self.model_type in ("qwen3", "qwen3_moe")
 
@@ -65,6 +69,20 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    # vision-language models (Qwen2-VL family): the decoder fields above describe the language model; the vision tower,
+    # the placeholder token ids and the multimodal RoPE sections live in ``extra``
+    @property
+    def is_vl(self) -> bool:
+        return bool(self.extra.get("vision_config"))
+
+    @property
+    def mrope_section(self):
+        return self.extra.get("mrope_section")
+
+    @property
+    def image_token_id(self) -> int:
+        return int(self.extra.get("image_token_id", 151655))
 
     @property
     def q_size(self) -> int:
@@ -97,6 +115,22 @@ class ModelConfig:
         if mt is None:
             archs = d.get("architectures") or ["Qwen2ForCausalLM"]
             mt = _ARCH_TO_TYPE.get(archs[0], "qwen2")
+        if mt in _VL_TYPES:  # language-model fields are nested under text_config in recent HF versions
+            top = {k: v for k, v in d.items() if k not in ("text_config", "vision_config")}
+            flat = dict(top)
+            flat.update(d.get("text_config") or {})
+            rope = flat.get("rope_scaling") or flat.get("rope_parameters") or {}
+            flat["model_type"] = mt
+            extra_vl = {"vision_config": dict(d.get("vision_config") or {}),
+                        "mrope_section": list(rope.get("mrope_section") or []) or None}
+            if "rope_theta" not in flat and rope.get("rope_theta"):
+                flat["rope_theta"] = rope["rope_theta"]
+            for k in ("image_token_id", "video_token_id", "vision_start_token_id", "vision_end_token_id"):
+                if k in top:
+                    extra_vl[k] = top[k]
+            d = {k: v for k, v in flat.items() if k not in ("rope_scaling", "rope_parameters", "image_token_id",
+                                                            "video_token_id", "vision_start_token_id", "vision_end_token_id")}
+            d["_vl_extra"] = extra_vl
         known = {f for f in cls.__dataclass_fields__}
         kw = {k: v for k, v in d.items() if k in known and k != "extra"}
         kw["model_type"] = mt
@@ -106,7 +140,8 @@ class ModelConfig:
         if isinstance(eos, list):
             kw["eos_token_id"] = eos[0]
         cfg = cls(**kw)
-        cfg.extra = {k: v for k, v in d.items() if k not in known}
+        cfg.extra = {k: v for k, v in d.items() if k not in known and k != "_vl_extra"}
+        cfg.extra.update(d.get("_vl_extra") or {})
         return cfg
 
     @classmethod
@@ -119,6 +154,18 @@ class ModelConfig:
     def to_hf_dict(self) -> dict[str, Any]:
         d = asdict(self)
         extra = d.pop("extra")
+        if self.model_type in _VL_TYPES:
+            text = {k: v for k, v in d.items() if k not in ("num_experts", "num_experts_per_tok", "moe_intermediate_size",
+                                                            "norm_topk_prob", "router_aux_loss_coef", "num_labels")}
+            text["model_type"] = self.model_type + "_text"
+            text["rope_scaling"] = {"type": "mrope", "mrope_section": list(extra.get("mrope_section") or [])}
+            out = {"architectures": [_TYPE_TO_ARCH[self.model_type]], "model_type": self.model_type, "torch_dtype": "bfloat16",
+                   "text_config": text, "vision_config": dict(extra.get("vision_config") or {}),
+                   "tie_word_embeddings": self.tie_word_embeddings}
+            for k in ("image_token_id", "video_token_id", "vision_start_token_id", "vision_end_token_id"):
+                if k in extra:
+                    out[k] = extra[k]
+            return out
         arch = _TYPE_TO_ARCH.get(self.model_type, "Qwen2ForCausalLM")
         if self.num_labels:
             arch = arch.replace("ForCausalLM", "ForTokenClassification")
@@ -160,6 +207,21 @@ PRESETS: dict[str, dict] = {
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", vocab_size=2048, hidden_size=256, intermediate_size=512,
                            num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                            num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, eos_token_id=2),
+    "tiny-qwen2-vl": dict(model_type="qwen2_vl", vocab_size=2048, hidden_size=256, intermediate_size=512,
+                          num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, rope_theta=1e6, eos_token_id=2,
+                          extra={"vision_config": dict(depth=2, embed_dim=64, hidden_size=256, num_heads=2, mlp_ratio=2,
+                                                       in_channels=3, patch_size=4, spatial_merge_size=2,
+                                                       temporal_patch_size=2),
+                                 "mrope_section": [8, 12, 12], "image_token_id": 2000, "video_token_id": 2001,
+                                 "vision_start_token_id": 2002}),
+    "qwen2-vl-7b": dict(model_type="qwen2_vl", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+                        num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6,
+                        eos_token_id=151645,
+                        extra={"vision_config": dict(depth=32, embed_dim=1280, hidden_size=3584, num_heads=16, mlp_ratio=4,
+                                                     in_channels=3, patch_size=14, spatial_merge_size=2,
+                                                     temporal_patch_size=2),
+                               "mrope_section": [16, 24, 24], "image_token_id": 151655, "video_token_id": 151656,
+                               "vision_start_token_id": 151652}),
     "llama-3-8b": dict(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
                        num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, rope_theta=5e5,
                        rms_norm_eps=1e-5, eos_token_id=128001),

@@ -18,9 +18,36 @@ import torch
 from .config import ModelConfig
 
 
+_VIS_HF_TO_NATIVE = (("attn.qkv.", "qkv."), ("attn.proj.", "proj."), ("mlp.fc1.", "fc1."), ("mlp.fc2.", "fc2."),
+                     ("merger.ln_q.", "ln_q."), ("merger.mlp.0.", "merge_fc1."), ("merger.mlp.2.", "merge_fc2."),
+                     ("patch_embed.proj.", "patch_embed."))
+
+
+def _normalise_vl_keys(hf_sd: dict) -> dict:
+    """Vision-language checkpoints: ``model.language_model.*`` (recent HF) or ``model.*`` (original release) for the
+    decoder, ``model.visual.*`` or ``visual.*`` for the tower -> ``model.*`` and ``visual.*``."""
+    out = {}
+    for k, v in hf_sd.items():
+        if k.startswith("model.language_model."):
+            k = "model." + k[len("model.language_model."):]
+        elif k.startswith("model.visual."):
+            k = k[len("model."):]
+        out[k] = v
+    return out
+
+
 def hf_to_native_state_dict(cfg: ModelConfig, hf_sd: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
     """Fuse an HF state dict into native parameter names/shapes."""
     out: dict[str, torch.Tensor] = {}
+    if cfg.is_vl or any(k.startswith(("model.language_model.", "model.visual.", "visual.")) for k in hf_sd):
+        hf_sd = _normalise_vl_keys(hf_sd)
+        for k, v in hf_sd.items():
+            if not k.startswith("visual."):
+                continue
+            n = k
+            for a, b in _VIS_HF_TO_NATIVE:
+                n = n.replace(a, b)
+            out[n] = v.reshape(v.shape[0], -1) if n == "visual.patch_embed.weight" else v
     g = lambda k: hf_sd[k]  # noqa: E731
     out["embed_tokens.weight"] = g("model.embed_tokens.weight")
     out["norm.weight"] = g("model.norm.weight")
@@ -57,7 +84,24 @@ def hf_to_native_state_dict(cfg: ModelConfig, hf_sd: dict[str, torch.Tensor]) ->
 def native_to_hf_items(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tensor]]) -> Iterator[tuple[str, torch.Tensor]]:
     """Stream (hf_name, tensor) pairs from native (name, tensor) pairs, splitting fused tensors.
     Works one parameter at a time so it can drive a weight-sync generator."""
+    vl = cfg.is_vl
+    lm = "model.language_model." if vl else "model."
     for name, t in named:
+        if name.startswith("visual."):
+            n = _vis_native_to_hf(name)
+            if name == "visual.patch_embed.weight":
+                vc = cfg.extra["vision_config"]
+                t = t.reshape(t.shape[0], vc.get("in_channels", 3), vc.get("temporal_patch_size", 2), vc.get("patch_size", 14),
+                              vc.get("patch_size", 14))
+            yield "model." + n, t
+            continue
+        if vl and name in ("embed_tokens.weight", "norm.weight"):
+            yield lm + name, t
+            continue
+        if vl and name.startswith("layers."):
+            for hn, ht in native_to_hf_items(_text_only(cfg), [(name, t)]):
+                yield lm + hn[len("model."):], ht
+            continue
         if name == "embed_tokens.weight":
             yield "model.embed_tokens.weight", t
         elif name == "norm.weight":
@@ -89,6 +133,23 @@ def native_to_hf_items(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tensor
                 yield p + rest, t
         else:
             yield name, t
+
+
+def _vis_native_to_hf(name: str) -> str:
+    body = name[len("visual."):]
+    parts = body.split(".")
+    # blocks.N.<x>.<w|b> or top-level <x>.<w|b>
+    leaf = parts[-2] + "."
+    for hf, nat in _VIS_HF_TO_NATIVE:
+        if leaf == nat:
+            return "visual." + ".".join(parts[:-2] + [hf[:-1], parts[-1]])
+    return name
+
+
+def _text_only(cfg: ModelConfig) -> ModelConfig:
+    import dataclasses
+
+    return dataclasses.replace(cfg, extra={})
 
 
 def native_to_hf_state_dict(cfg: ModelConfig, sd: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:

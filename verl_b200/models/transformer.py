@@ -33,6 +33,10 @@ class PackedBatch:
     cu_seqlens: torch.Tensor  # [B+1] int32
     max_seqlen: int
     total_tokens: int = -1  # Ulysses: tokens of the whole packed stream when input_ids holds only this rank's slice
+    # vision-language models: patches of all images of the batch (in order) and their (t, h, w) grids; position_ids is
+    # then [3, T] (multimodal RoPE)
+    pixel_values: Optional[torch.Tensor] = None
+    image_grid_thw: Optional[torch.Tensor] = None
 
     @classmethod
     def from_padded(cls, input_ids: torch.Tensor, attention_mask: torch.Tensor, position_ids: torch.Tensor | None = None):
@@ -252,7 +256,7 @@ class Attention(nn.Module):
             q, _ = ops.rmsnorm(q.reshape(T * Hq, D), qw, cfg.rms_norm_eps)
             k, _ = ops.rmsnorm(k.reshape(T * Hk, D), kw, cfg.rms_norm_eps)
             qkv = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v], dim=-1)
-        qkv = ops.rope_qkv(qkv, batch.position_ids, rope[0], rope[1], Hq, Hk, D)
+        qkv = ops.rope_qkv(qkv, batch.position_ids, rope[0], rope[1], Hq, Hk, D, mrope_section=cfg.mrope_section)
         q = qkv[:, : cfg.q_size].view(T, Hq, D)
         k = qkv[:, cfg.q_size : cfg.q_size + cfg.kv_size].view(T, Hk, D)
         v = qkv[:, cfg.q_size + cfg.kv_size :].view(T, Hk, D)
@@ -310,6 +314,11 @@ class CausalLM(nn.Module):
         else:
             # training-side tensor parallelism may give this rank a slice of the vocabulary rows
             self.lm_head = Linear(cfg.hidden_size, int(cfg.extra.get("lm_head_rows", cfg.vocab_size)), False, dtype, device)
+        self.visual = None
+        if cfg.is_vl and has_embed:
+            from .vision import VisionConfig, VisionTower
+
+            self.visual = VisionTower(VisionConfig.from_dict(cfg.extra["vision_config"]), dtype=dtype, device=device)
         self.gradient_checkpointing = False
         # training-side tensor parallelism: an untied lm_head holds a slice of the vocabulary rows
         self.tp_group = None
@@ -327,6 +336,8 @@ class CausalLM(nn.Module):
         for m in self.modules():
             if isinstance(m, (Linear, MoEMLP)):
                 m.reset_parameters(gen)
+        if self.visual is not None:
+            self.visual.init_weights(seed + 1)
         return self
 
     @property
@@ -339,7 +350,14 @@ class CausalLM(nn.Module):
 
     # --------------------------------------------------------------- forward
     def embed(self, batch: PackedBatch) -> torch.Tensor:
-        return ops.embedding(batch.input_ids, self.embed_tokens.weight)
+        h = ops.embedding(batch.input_ids, self.embed_tokens.weight)
+        if self.visual is not None and batch.pixel_values is not None and batch.pixel_values.numel():
+            # the vision tower's outputs replace the embeddings of the image placeholder tokens, in order
+            img = self.visual(batch.pixel_values, batch.image_grid_thw).to(h.dtype)
+            where = torch.nonzero(batch.input_ids == self.cfg.image_token_id, as_tuple=True)[0]
+            assert where.numel() == img.shape[0], f"{where.numel()} image tokens but {img.shape[0]} image embeddings"
+            h = h.index_put((where,), img)
+        return h
 
     def final_norm(self, hidden, residual) -> torch.Tensor:
         out, _ = ops.rmsnorm(hidden, self.norm.weight, self.cfg.rms_norm_eps, residual)

@@ -1,0 +1,207 @@
+"""Vision side of the Qwen2-VL family: ViT tower with 2-D rotary attention and the 2 x 2 patch merger, multimodal RoPE
+position ids, and the merge of image embeddings into the token stream.
+
+The reference takes these models from ``transformers`` and patches their forward for packed inputs and mrope
+(verl/models/transformers/qwen2_vl.py:1-548; position ids: ``get_rope_index`` there and
+verl/utils/tensordict_utils.py:847). Here the tower runs on the same native linear / attention ops as the decoder
+(packed patches, one attention segment per frame).
+"""
+
+from __future__ import annotations
+
+from dataclasses import asdict, dataclass
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+
+
+@dataclass
+class VisionConfig:
+    depth: int = 32
+    embed_dim: int = 1280
+    hidden_size: int = 3584          # width of the language model the merger projects to
+    num_heads: int = 16
+    mlp_ratio: float = 4.0
+    in_channels: int = 3
+    patch_size: int = 14
+    spatial_merge_size: int = 2
+    temporal_patch_size: int = 2
+    hidden_act: str = "quick_gelu"
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "VisionConfig":
+        known = {f for f in cls.__dataclass_fields__}
+        return cls(**{k: v for k, v in d.items() if k in known})
+
+    def to_dict(self) -> dict:
+        return asdict(self)
+
+    @property
+    def patch_dim(self) -> int:
+        return self.in_channels * self.temporal_patch_size * self.patch_size * self.patch_size
+
+
+class _Lin(nn.Module):
+    """Linear with bias on the native GEMM (CPU: torch)."""
+
+    def __init__(self, i: int, o: int, bias: bool, dtype, device):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(o, i, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(o, dtype=dtype, device=device)) if bias else None
+
+    def forward(self, x):
+        if x.is_cuda and x.shape[-1] % 8 == 0 and self.weight.shape[0] % 8 == 0:
+            return ops.linear(x, self.weight, self.bias)
+        return F.linear(x, self.weight, self.bias)
+
+
+class _LayerNormW(nn.Module):
+    def __init__(self, dim: int, dtype, device, eps: float = 1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(dim, dtype=dtype, device=device))
+        self.eps = eps
+
+    def forward(self, x):
+        return F.layer_norm(x.float(), (x.shape[-1],), self.weight.float(), self.bias.float(), self.eps).to(x.dtype)
+
+
+def _rotate_half(x):
+    a, b = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2 :]
+    return torch.cat([-b, a], -1)
+
+
+class VisionBlock(nn.Module):
+    def __init__(self, c: VisionConfig, dtype, device):
+        super().__init__()
+        self.c = c
+        self.norm1 = _LayerNormW(c.embed_dim, dtype, device)
+        self.norm2 = _LayerNormW(c.embed_dim, dtype, device)
+        self.qkv = _Lin(c.embed_dim, 3 * c.embed_dim, True, dtype, device)
+        self.proj = _Lin(c.embed_dim, c.embed_dim, True, dtype, device)
+        hid = int(c.embed_dim * c.mlp_ratio)
+        self.fc1 = _Lin(c.embed_dim, hid, True, dtype, device)
+        self.fc2 = _Lin(hid, c.embed_dim, True, dtype, device)
+
+    def forward(self, x, cu_seqlens, max_seqlen, cos, sin):
+        c = self.c
+        N = x.shape[0]
+        hd = c.embed_dim // c.num_heads
+        qkv = self.qkv(self.norm1(x)).view(N, 3, c.num_heads, hd)
+        q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
+        q = (q.float() * cos + _rotate_half(q.float()) * sin).to(x.dtype)
+        k = (k.float() * cos + _rotate_half(k.float()) * sin).to(x.dtype)
+        a = ops.attention_varlen(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens, max_seqlen, causal=False)
+        x = x + self.proj(a.reshape(N, c.embed_dim))
+        h = self.fc1(self.norm2(x))
+        h = h * torch.sigmoid(1.702 * h) if c.hidden_act == "quick_gelu" else F.gelu(h)
+        return x + self.fc2(h)
+
+
+class VisionTower(nn.Module):
+    """``pixel_values [N, C * T * P * P]`` (patches already in 2 x 2 merge order) + ``grid_thw [n_images, 3]`` ->
+    ``[N / merge^2, hidden_size]`` embeddings, one per image placeholder token."""
+
+    def __init__(self, c: VisionConfig, dtype=torch.bfloat16, device="cpu"):
+        super().__init__()
+        self.c = c
+        self.patch_embed = _Lin(c.patch_dim, c.embed_dim, False, dtype, device)  # the Conv3d of the reference, as a GEMM
+        self.blocks = nn.ModuleList([VisionBlock(c, dtype, device) for _ in range(c.depth)])
+        self.ln_q = _LayerNormW(c.embed_dim, dtype, device)
+        m2 = c.spatial_merge_size ** 2
+        self.merge_fc1 = _Lin(c.embed_dim * m2, c.embed_dim * m2, True, dtype, device)
+        self.merge_fc2 = _Lin(c.embed_dim * m2, c.hidden_size, True, dtype, device)
+
+    def init_weights(self, seed: int = 0):
+        g = torch.Generator(device=self.patch_embed.weight.device)
+        g.manual_seed(seed)
+        with torch.no_grad():
+            for n, p in self.named_parameters():
+                if n.endswith("weight") and p.dim() == 2:
+                    p.copy_(torch.empty(p.shape, dtype=torch.float32, device=p.device).normal_(0.0, 0.02, generator=g))
+        return self
+
+    def rot_pos(self, grid_thw: torch.Tensor):
+        """(cos, sin) [N, 1, head_dim] of the 2-D rotary embedding: half of the frequencies follow the patch's row,
+        half its column, in the merge-block order of the patches."""
+        c = self.c
+        m = c.spatial_merge_size
+        hd = c.embed_dim // c.num_heads
+        dim = hd // 2
+        dev = grid_thw.device
+        ids = []
+        for t, h, w in grid_thw.tolist():
+            hp = torch.arange(h, device=dev).unsqueeze(1).expand(-1, w)
+            wp = torch.arange(w, device=dev).unsqueeze(0).expand(h, -1)
+            hp = hp.reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).flatten()
+            wp = wp.reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).flatten()
+            ids.append(torch.stack([hp, wp], -1).repeat(t, 1))
+        ids = torch.cat(ids, 0)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, dim, 2, dtype=torch.float32, device=dev) / dim))
+        freqs = torch.arange(int(grid_thw[:, 1:].max()), dtype=torch.float32, device=dev)[:, None] * inv[None]
+        emb = freqs[ids].flatten(1)                    # [N, dim]: row frequencies, then column frequencies
+        emb = torch.cat([emb, emb], -1)                # [N, head_dim]
+        return emb.cos()[:, None, :], emb.sin()[:, None, :]
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+        c = self.c
+        x = self.patch_embed(pixel_values.to(self.patch_embed.weight.dtype))
+        cos, sin = self.rot_pos(grid_thw)
+        per_frame = (grid_thw[:, 1] * grid_thw[:, 2]).repeat_interleave(grid_thw[:, 0])
+        cu = F.pad(per_frame.cumsum(0), (1, 0)).to(torch.int32)
+        max_len = int(per_frame.max())
+        for blk in self.blocks:
+            x = blk(x, cu, max_len, cos, sin)
+        m2 = c.spatial_merge_size ** 2
+        x = self.ln_q(x).view(-1, c.embed_dim * m2)
+        return self.merge_fc2(F.gelu(self.merge_fc1(x)))
+
+
+def get_rope_index(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tensor], image_token_id: int,
+                   spatial_merge_size: int = 2, video_grid_thw: Optional[torch.Tensor] = None,
+                   video_token_id: Optional[int] = None) -> tuple[torch.Tensor, int]:
+    """Multimodal RoPE positions of ONE sequence of token ids (no padding): ``[3, L]`` (temporal, height, width) and
+    the delta to add to a text position after the sequence (``max position + 1 - L``). Text tokens advance all three
+    axes together; the placeholder tokens of an image take (frame, row, column) of their merged patch, offset by the
+    position at which the image starts; the text after it continues from the largest position so far + 1."""
+    L = input_ids.numel()
+    dev = input_ids.device
+    ids = input_ids.tolist()
+    grids = []
+    if image_grid_thw is not None:
+        grids += [(image_token_id, g) for g in image_grid_thw.tolist()]
+    vids = [(video_token_id, g) for g in video_grid_thw.tolist()] if video_grid_thw is not None else []
+    if not grids and not vids:
+        p = torch.arange(L, device=dev)
+        return torch.stack([p, p, p]), 0
+    out = []
+    st, nxt = 0, 0
+    img_it, vid_it = iter(grids), iter(vids)
+    while st < L:
+        ends = [ids.index(tok, st) if tok is not None and tok in ids[st:] else L + 1 for tok in (image_token_id, video_token_id)]
+        if min(ends) > L:
+            break
+        use_img = ends[0] <= ends[1]
+        ed = ends[0] if use_img else ends[1]
+        _, (t, h, w) = next(img_it if use_img else vid_it)
+        gh, gw = h // spatial_merge_size, w // spatial_merge_size
+        n_text = ed - st
+        if n_text:
+            p = torch.arange(n_text, device=dev) + nxt
+            out.append(torch.stack([p, p, p]))
+            nxt += n_text
+        ti = torch.arange(t, device=dev).view(-1, 1).expand(-1, gh * gw).flatten()
+        hi = torch.arange(gh, device=dev).view(1, -1, 1).expand(t, -1, gw).flatten()
+        wi = torch.arange(gw, device=dev).view(1, 1, -1).expand(t, gh, -1).flatten()
+        out.append(torch.stack([ti, hi, wi]) + nxt)
+        nxt = int(out[-1].max()) + 1
+        st = ed + t * gh * gw
+    if st < L:
+        p = torch.arange(L - st, device=dev) + nxt
+        out.append(torch.stack([p, p, p]))
+    pos = torch.cat(out, 1)
+    return pos, int(pos.max()) + 1 - L

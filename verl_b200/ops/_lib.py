@@ -35,6 +35,7 @@ _SIGS = {
     "vb_rmsnorm_bwd_parts": ([L], I),
     "vb_rmsnorm_bwd": ([P, P, P, P, P, P, P, P, I, L, I, P], I),
     "vb_rope": ([P, P, L, L, P, P, P, I, I, I, I, I, P], I),
+    "vb_mrope": ([P, P, L, L, P, P, P, I, I, I, I, I, I, I, P], I),
     "vb_swiglu_fwd": ([P, P, L, I, P], I),
     "vb_swiglu_bwd": ([P, P, P, L, I, P], I),
     "vb_embedding_fwd": ([P, P, P, L, I, P], I),

@@ -102,43 +102,81 @@ def _rope_ref(t, pos, cos_t, sin_t, n_heads, D, sign=1.0):
     return torch.cat([a * c - b * s, b * c + a * s], -1).reshape(T, n_heads * D).to(t.dtype)
 
 
+def _mrope_cos_sin(pos3, cos_t, sin_t, sections):
+    """Per-token cos / sin [T, D/2] of multimodal RoPE: frequency j follows the temporal / height / width position
+    according to ``sections`` (numbers of frequencies per axis)."""
+    half = cos_t.shape[1]
+    axis = torch.repeat_interleave(torch.arange(3, device=pos3.device), torch.tensor(list(sections), device=pos3.device))
+    axis = axis[:half]
+    j = torch.arange(half, device=pos3.device)
+    p = pos3[axis]                      # [half, T]: the position each frequency uses
+    return cos_t[p, j[:, None]].t().contiguous(), sin_t[p, j[:, None]].t().contiguous()
+
+
 class _RopeFn(torch.autograd.Function):
-    """In-place rotary embedding on the q and k slices of a packed qkv activation [T, (Hq+2Hk)*D]."""
+    """In-place rotary embedding on the q and k slices of a packed qkv activation [T, (Hq+2Hk)*D]. ``sections``
+    (multimodal RoPE) makes ``pos`` a [3, T] tensor of temporal / height / width positions."""
 
     @staticmethod
-    def forward(ctx, qkv, pos, cos_t, sin_t, Hq, Hk, D):
+    def _run(qkv, pos, cos_t, sin_t, Hq, Hk, D, sections, backward):
         T = qkv.shape[0]
         q = qkv[:, : Hq * D]
         k = qkv[:, Hq * D : (Hq + Hk) * D]
-        rc = _lib.fn("vb_rope")(q.data_ptr(), k.data_ptr(), qkv.stride(0), qkv.stride(0), pos.data_ptr(),
-                                cos_t.data_ptr(), sin_t.data_ptr(), T, Hq, Hk, D, 0, _lib.stream())
+        if sections is None:
+            rc = _lib.fn("vb_rope")(q.data_ptr(), k.data_ptr(), qkv.stride(0), qkv.stride(0), pos.data_ptr(),
+                                    cos_t.data_ptr(), sin_t.data_ptr(), T, Hq, Hk, D, backward, _lib.stream())
+        else:
+            rc = _lib.fn("vb_mrope")(q.data_ptr(), k.data_ptr(), qkv.stride(0), qkv.stride(0), pos.data_ptr(),
+                                     cos_t.data_ptr(), sin_t.data_ptr(), T, Hq, Hk, D, int(sections[0]), int(sections[1]),
+                                     backward, _lib.stream())
         _lib.check(rc, "vb_rope")
+
+    @staticmethod
+    def forward(ctx, qkv, pos, cos_t, sin_t, Hq, Hk, D, sections):
+        _RopeFn._run(qkv, pos, cos_t, sin_t, Hq, Hk, D, sections, 0)
         ctx.save_for_backward(pos, cos_t, sin_t)
-        ctx.dims = (Hq, Hk, D)
+        ctx.dims = (Hq, Hk, D, sections)
         ctx.mark_dirty(qkv)
         return qkv
 
     @staticmethod
     def backward(ctx, dqkv):
         pos, cos_t, sin_t = ctx.saved_tensors
-        Hq, Hk, D = ctx.dims
+        Hq, Hk, D, sections = ctx.dims
         dqkv = dqkv.contiguous().clone() if not dqkv.is_contiguous() else dqkv.clone()
-        T = dqkv.shape[0]
-        q = dqkv[:, : Hq * D]
-        k = dqkv[:, Hq * D : (Hq + Hk) * D]
-        rc = _lib.fn("vb_rope")(q.data_ptr(), k.data_ptr(), dqkv.stride(0), dqkv.stride(0), pos.data_ptr(),
-                                cos_t.data_ptr(), sin_t.data_ptr(), T, Hq, Hk, D, 1, _lib.stream())
-        _lib.check(rc, "vb_rope")
-        return dqkv, None, None, None, None, None, None
+        _RopeFn._run(dqkv, pos, cos_t, sin_t, Hq, Hk, D, sections, 1)
+        return dqkv, None, None, None, None, None, None, None
 
 
-def rope_qkv(qkv: torch.Tensor, pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor, Hq: int, Hk: int, D: int):
-    """Apply rotate-half RoPE to the q and k parts of packed ``qkv`` ([T, (Hq+2Hk)*D]); v is untouched."""
-    if qkv.is_cuda:
-        return _RopeFn.apply(qkv, pos, cos_t, sin_t, Hq, Hk, D)
+def rope_qkv(qkv: torch.Tensor, pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor, Hq: int, Hk: int, D: int,
+             mrope_section=None):
+    """Apply rotate-half RoPE to the q and k parts of packed ``qkv`` ([T, (Hq+2Hk)*D]); v is untouched. With
+    ``mrope_section = (t, h, w)`` (frequencies per axis, sum D / 2) ``pos`` is ``[3, T]`` (multimodal RoPE of the
+    Qwen2-VL family, verl/models/transformers/qwen2_vl.py)."""
+    if pos.dim() == 2 and mrope_section is None:
+        pos = pos[0]
+    if pos.dim() == 1:
+        mrope_section = None
+    if qkv.is_cuda and (mrope_section is None or all(int(x) % 8 == 0 for x in mrope_section[:2])):
+        return _RopeFn.apply(qkv, pos.contiguous(), cos_t, sin_t, Hq, Hk, D,
+                             None if mrope_section is None else tuple(int(x) for x in mrope_section))
+    if mrope_section is not None:
+        c, s_ = _mrope_cos_sin(pos, cos_t, sin_t, mrope_section)
+        q = _rope_apply(qkv[:, : Hq * D], c, s_, Hq, D)
+        k = _rope_apply(qkv[:, Hq * D : (Hq + Hk) * D], c, s_, Hk, D)
+        return torch.cat([q, k, qkv[:, (Hq + Hk) * D :]], dim=-1)
     q = _rope_ref(qkv[:, : Hq * D], pos, cos_t, sin_t, Hq, D)
     k = _rope_ref(qkv[:, Hq * D : (Hq + Hk) * D], pos, cos_t, sin_t, Hk, D)
     return torch.cat([q, k, qkv[:, (Hq + Hk) * D :]], dim=-1)
+
+
+def _rope_apply(t, c, s_, n_heads, D):
+    """Rotate-half with per-token cos / sin [T, D/2]."""
+    T = t.shape[0]
+    tf = t.float().reshape(T, n_heads, D)
+    a, b = tf[..., : D // 2], tf[..., D // 2 :]
+    c, s_ = c[:, None, :], s_[:, None, :]
+    return torch.cat([a * c - b * s_, b * c + a * s_], -1).reshape(T, n_heads * D).to(t.dtype)
 
 
 # ---------------------------------------------------------------------------- SwiGLU
