@@ -48,7 +48,10 @@ class PackedBatch:
         ids = input_ids.flatten()[idx]
         if position_ids is None:
             position_ids = (torch.cumsum(mask.long(), -1) - 1).clamp(min=0)
-        pos = position_ids.flatten()[idx]
+        if position_ids.dim() == 3:  # [B, 3, S] multimodal RoPE positions -> [3, T]
+            pos = torch.stack([position_ids[:, a].flatten()[idx] for a in range(position_ids.shape[1])])
+        else:
+            pos = position_ids.flatten()[idx]
         cu = torch.zeros(seqlens.numel() + 1, dtype=torch.int32, device=input_ids.device)
         cu[1:] = torch.cumsum(seqlens, 0)
         return cls(ids, pos, cu, int(seqlens.max().item()) if seqlens.numel() else 0), idx

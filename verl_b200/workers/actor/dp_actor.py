@@ -42,10 +42,20 @@ class DataParallelPPOActor:
         input_ids = b["input_ids"].to(self.device)
         mask = b["attention_mask"].to(self.device)
         pos = b["position_ids"].to(self.device) if "position_ids" in b else None
-        if pos is not None and pos.dim() == 3:  # mrope layouts carry [b, 3|4, S]; text positions are row 0
-            pos = pos[:, 0]
+        vl = bool(getattr(self.engine.model_config, "is_vl", False))
+        if pos is not None and pos.dim() == 3:
+            # mrope layouts carry [b, 3, S] or [b, 4, S] (row 0 = text positions, rows 1..3 = temporal / height / width)
+            pos = pos[:, -3:] if vl else pos[:, 0]
         R = b["responses"].shape[-1]
         packed, rows, labels, bj = NativeEngine.response_rows(input_ids, mask, R, pos)
+        mm = micro.non_tensor_batch.get("multi_modal_inputs") if vl else None
+        if mm is not None:
+            from ...utils.model import extract_multi_modal_inputs
+
+            inputs = extract_multi_modal_inputs(list(mm))
+            if inputs.get("pixel_values") is not None:
+                packed.pixel_values = inputs["pixel_values"].to(self.device)
+                packed.image_grid_thw = inputs["image_grid_thw"].to(self.device)
         lp, ent = self.engine.forward_logprob(packed, rows, labels, temperature)
         B = input_ids.shape[0]
         log_probs = torch.zeros(B, R, dtype=torch.float32, device=self.device)

@@ -125,10 +125,12 @@ class NativeEngine(BaseEngine):
         first, last = self.pp_rank == 0, self.pp_rank == self.pp_size - 1
         tied = last and m.lm_head is None and not m.value_head
         units = []
+        # a vision tower lives (and is gathered) with the embedding: its outputs replace placeholder-token embeddings
+        vis = [("visual." + n, p) for n, p in m.visual.named_parameters()] if getattr(m, "visual", None) is not None else []
         if tied:
-            units.append(("", [("embed_tokens.weight", m.embed_tokens.weight), ("norm.weight", m.norm.weight)]))
+            units.append(("", [("embed_tokens.weight", m.embed_tokens.weight), ("norm.weight", m.norm.weight)] + vis))
         elif first:
-            units.append(("", [("embed_tokens.weight", m.embed_tokens.weight)]))
+            units.append(("", [("embed_tokens.weight", m.embed_tokens.weight)] + vis))
         # expert parallelism: the stacked expert matrices form units of their own that are never gathered (rank r's
         # shard IS experts [r E / W, (r + 1) E / W)); they go to the end of the list so that the layer units stay
         # neighbours for the gather prefetch
