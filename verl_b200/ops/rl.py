@@ -141,13 +141,14 @@ def decode_advance(tok, lp, ids, pos, slots, lens, bt, block_size: int, limit, a
     if 0 <= s < kmax:
         ring_tok[s] = torch.where(a, tok, torch.full_like(tok, -1))
         ring_lp[s] = torch.where(a, lp, torch.zeros_like(lp))
-    done = a & ((((flags & 1) == 0) & (tok == eos)) | (pos + 2 >= limit.long()))
+    ti = lens.long() - 1  # index of the token just processed (the RoPE position may be offset from it)
+    done = a & ((((flags & 1) == 0) & (tok == eos)) | (ti + 2 >= limit.long()))
     go = a & ~done
-    p = pos + 1
+    p = ti + 1
     blk = torch.div(p, block_size, rounding_mode="floor").clamp(max=bt.shape[1] - 1)
     new_slot = bt.long().gather(1, blk[:, None])[:, 0] * block_size + p % block_size
     ids.copy_(torch.where(go, tok, ids))
-    pos.copy_(torch.where(go, p, pos))
+    pos.copy_(torch.where(go, pos + 1, pos))
     lens.copy_(torch.where(go, lens + 1, lens))
     slots.copy_(torch.where(go, new_slot, torch.where(done, torch.full_like(slots, -1), slots)))
     alive.copy_(torch.where(done, torch.zeros_like(alive), alive))

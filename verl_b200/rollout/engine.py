@@ -243,6 +243,7 @@ class NativeRolloutEngine:
         self.v_cache: list = []
         self.sched: Optional[Scheduler] = None
         self.requests: dict[int, _Request] = {}
+        self._mmreq: dict[int, dict] = {}  # per-request multimodal state of vision-language models
         self.by_rid: dict[str, int] = {}
         self._next_sid = 0
         self._graphs: dict[int, tuple] = {}
@@ -330,21 +331,59 @@ class NativeRolloutEngine:
         self.clear_kv_cache()
 
     # --------------------------------------------------------------- requests
-    def add_request(self, request_id: str, prompt_ids: list[int], sampling_params=None) -> None:
+    def add_request(self, request_id: str, prompt_ids: list[int], sampling_params=None,
+                    multi_modal_inputs: Optional[dict] = None) -> None:
+        """``multi_modal_inputs`` (vision-language models): ``{"pixel_values": [patches, C * T * P * P],
+        "image_grid_thw": [n_images, 3]}`` for the image placeholder tokens of ``prompt_ids``, as an HF image processor
+        returns them (role of the multimodal inputs of verl/workers/rollout/vllm_rollout/vllm_async_server.py:445-547)."""
         if self.sched is None:
             self.wake_up()
         sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
         max_new = min(sp.max_tokens, self.max_model_len - len(prompt_ids))
         sid = self._next_sid
         self._next_sid += 1
-        rc = self.sched.add(sid, list(prompt_ids), max_new)
+        sched_ids = list(prompt_ids)
+        mm = None
+        if multi_modal_inputs and multi_modal_inputs.get("pixel_values") is not None:
+            mm, sched_ids = self._prepare_multimodal(prompt_ids, multi_modal_inputs)
+        rc = self.sched.add(sid, sched_ids, max_new)
         if rc != 0:
             raise ValueError(f"request {request_id}: prompt of {len(prompt_ids)} tokens does not fit (code {rc})")
         self.requests[sid] = _Request(request_id, sid, sp, len(prompt_ids))
         self.by_rid[request_id] = sid
+        if mm is not None:
+            self._mmreq[sid] = mm
+
+    @torch.no_grad()
+    def _prepare_multimodal(self, prompt_ids: list[int], inputs: dict):
+        """Run the vision tower once for the request and keep what prefill and decode need: the image embeddings, the
+        prompt indices of the placeholder tokens, the [3, L] multimodal RoPE positions and the offset of later text
+        positions. The scheduler sees salted ids (>= vocabulary size, derived from the pixels) in place of the
+        placeholder tokens, so that prompts with the same text but other images never share prefix-cache pages."""
+        from ..models.vision import get_rope_index
+
+        cfg = self.full_cfg
+        if getattr(self.model, "visual", None) is None:
+            raise ValueError("multi_modal_inputs were given but the model has no vision tower")
+        pv = inputs["pixel_values"].to(self.device)
+        grid = inputs["image_grid_thw"].to(self.device)
+        emb = self.model.visual(pv, grid).to(self.dtype)
+        ids = torch.tensor(prompt_ids, dtype=torch.long)
+        where = torch.nonzero(ids == cfg.image_token_id, as_tuple=True)[0]
+        if where.numel() != emb.shape[0]:
+            raise ValueError(f"{where.numel()} image placeholder tokens but {emb.shape[0]} image embeddings")
+        merge = int(cfg.extra["vision_config"].get("spatial_merge_size", 2))
+        pos3, delta = get_rope_index(ids, grid.cpu(), cfg.image_token_id, merge)
+        salt = int(pv.float().sum().item() * 1000003) & 0x3FFFFFFF
+        room = (1 << 31) - 1 - cfg.vocab_size
+        sched = list(prompt_ids)
+        for j, w in enumerate(where.tolist()):
+            sched[w] = cfg.vocab_size + (salt + 7919 * j) % room
+        return {"emb": emb, "where": where.numpy(), "pos3": pos3.numpy(), "delta": int(delta)}, sched
 
     def _finish(self, sid: int, reason: str) -> TokenOutput:
         req = self.requests.pop(sid)
+        self._mmreq.pop(sid, None)
         self.by_rid.pop(req.rid, None)
         toks = self.sched.output(sid, self.max_model_len)
         pre = self.sched.preempt_count(sid)
@@ -379,7 +418,8 @@ class NativeRolloutEngine:
             k, _ = ops.rmsnorm(k.reshape(T * c.num_key_value_heads, c.head_dim).contiguous(), att.k_norm.weight, c.rms_norm_eps)
             qkv = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v], dim=-1)
         rope = self.model.rope(self.device)
-        qkv = ops.rope_qkv(qkv, positions, rope[0], rope[1], c.num_attention_heads, c.num_key_value_heads, c.head_dim)
+        qkv = ops.rope_qkv(qkv, positions, rope[0], rope[1], c.num_attention_heads, c.num_key_value_heads, c.head_dim,
+                           mrope_section=c.mrope_section if positions.dim() == 2 else None)
         q = qkv[:, : c.q_size].view(T, c.num_attention_heads, c.head_dim)
         k = qkv[:, c.q_size : c.q_size + c.kv_size].view(T, c.num_key_value_heads, c.head_dim)
         v = qkv[:, c.q_size + c.kv_size :].view(T, c.num_key_value_heads, c.head_dim)
@@ -626,7 +666,30 @@ class NativeRolloutEngine:
             order_t = torch.from_numpy(np.concatenate(order)).to(dev)
             cu_k_t = torch.tensor(cu_k, dtype=torch.int32, device=dev)
             max_k = max(b - a for a, b in zip(cu_k[:-1], cu_k[1:]))
+        vl = bool(self.full_cfg.is_vl)
+        if vl:
+            # salted placeholder ids (>= vocabulary) look up row 0; their embeddings are replaced below
+            ids = torch.where(ids < self.full_cfg.vocab_size, ids, torch.zeros_like(ids))
         h = ops.embedding(ids, self.model.embed_tokens.weight)
+        if vl:
+            # multimodal RoPE: [3, T] positions; a request with images takes them from its table (its text after the
+            # images is offset by the request's delta), the others advance all three axes together
+            pos3 = pos.unsqueeze(0).repeat(3, 1)
+            for j, i in enumerate(seq_idx):
+                mm = self._mmreq.get(int(sc.seq_ids[i]))
+                if mm is None:
+                    continue
+                st, n = int(sc.seq_start[i]), cu[j + 1] - cu[j]
+                L = mm["pos3"].shape[1]
+                tok = np.arange(st, st + n)
+                p3 = np.where(tok[None, :] < L, mm["pos3"][:, np.minimum(tok, L - 1)], tok[None, :] + mm["delta"])
+                pos3[:, cu[j] : cu[j + 1]] = torch.from_numpy(p3).to(dev)
+                hit = (mm["where"] >= st) & (mm["where"] < st + n)
+                if hit.any():
+                    k0 = int(np.searchsorted(mm["where"], st))
+                    rows_ = torch.from_numpy(mm["where"][hit] - st + cu[j]).to(dev)
+                    h = h.index_put((rows_,), mm["emb"][k0 : k0 + int(hit.sum())])
+            pos = pos3
 
         def attend(li, layer, x):
             q, k, v = self._layer_attn_in(layer, x, pos)
@@ -675,7 +738,10 @@ class NativeRolloutEngine:
             hp, pad = st["host"], st["pad"]
             sig = (nd, sids_d.tobytes())
             fresh = st["sig"] != sig  # batch membership changed: rewrite the padding and the per-request constants
-            for name, arr in (("ids", sc.tokens[t_idx]), ("pos", sc.positions[t_idx]), ("slots", sc.slots[t_idx]),
+            dec_pos = sc.positions[t_idx]
+            if self._mmreq:  # after its images a request's text positions are offset (all three RoPE axes are equal then)
+                dec_pos = dec_pos + np.asarray([self._mmreq.get(int(sid), {}).get("delta", 0) for sid in sids_d])
+            for name, arr in (("ids", sc.tokens[t_idx]), ("pos", dec_pos), ("slots", sc.slots[t_idx]),
                               ("bt", sc.block_tables[di]), ("lens", sc.seq_total[di])):
                 hp[name][:nd] = arr
                 if fresh:
