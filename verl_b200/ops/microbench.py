@@ -219,9 +219,100 @@ def bench_grouped_gemm(a):
             "tflops_useful": round(2.0 * T * N * K / us / 1e6, 1), "weight_gbs": round(E * N * K * 2 / us / 1e3, 1)}
 
 
+def bench_small(a):
+    """Every small (bandwidth-bound) kernel once or twice on inputs larger than L2: RMSNorm forward / backward, RoPE,
+    SwiGLU forward / backward, embedding forward / backward, AdamW, sum of squares, fused PPO loss, GAE, GRPO advantage,
+    sampler, KV-cache write, decode advance, fp8 quantisation. Prints CUDA-event times and effective bandwidths; meant
+    to be run under a profiler for per-kernel summaries as well."""
+    from . import (adamw_step, decode_advance, embedding, gae, grpo_advantage, kv_cache_write, ppo_loss_fused, rmsnorm,
+                   rope_qkv, rope_tables, sample, sumsq_into, swiglu)
+    from . import fp8
+
+    dev = "cuda"
+    T, H, I = a.t, a.hidden, 18944
+    bf = torch.bfloat16
+    out = {"kernel": "small_kernels", "T": T, "H": H}
+
+    def timed(name, fn, nbytes):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3
+        out[name] = {"us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1)}
+
+    x = torch.randn(T, H, device=dev, dtype=bf, requires_grad=True)
+    res = torch.randn(T, H, device=dev, dtype=bf)
+    w = torch.ones(H, device=dev, dtype=bf, requires_grad=True)
+    timed("rmsnorm_fwd", lambda: rmsnorm(x.detach(), w.detach(), 1e-6, res), 4 * T * H * 2)
+    y, hsum = rmsnorm(x, w, 1e-6, res)
+    gy = torch.randn_like(y)
+    timed("rmsnorm_bwd", lambda: torch.autograd.grad(y, x, gy, retain_graph=True), 3 * T * H * 2)
+    Hq, Hk, D = 28, 4, 128
+    qkv = torch.randn(T, (Hq + 2 * Hk) * D, device=dev, dtype=bf)
+    cos, sin = rope_tables(D, 32768, 1e6, dev)
+    pos = torch.arange(T, device=dev) % 4096
+    timed("rope", lambda: rope_qkv(qkv, pos, cos, sin, Hq, Hk, D), 2 * T * (Hq + Hk) * D * 2)
+    gu = torch.randn(T // 2, 2 * I, device=dev, dtype=bf, requires_grad=True)
+    timed("swiglu_fwd", lambda: swiglu(gu.detach()), 3 * (T // 2) * I * 2)
+    so = swiglu(gu)
+    gso = torch.randn_like(so)
+    timed("swiglu_bwd", lambda: torch.autograd.grad(so, gu, gso, retain_graph=True), 5 * (T // 2) * I * 2)
+    V = 152064
+    emb = torch.randn(V, H, device=dev, dtype=bf, requires_grad=True)
+    ids = torch.randint(0, V, (T,), device=dev)
+    timed("embedding_fwd", lambda: embedding(ids, emb.detach()), 2 * T * H * 2)
+    eo = embedding(ids, emb)
+    geo = torch.randn_like(eo)
+    timed("embedding_bwd", lambda: torch.autograd.grad(eo, emb, geo, retain_graph=True), T * H * 2 + T * H * 4)
+    n = 64 << 20
+    p32, g32, m32, v32 = (torch.randn(n, device=dev) for _ in range(4))
+    v32.abs_()
+    p16 = torch.empty(n, device=dev, dtype=bf)
+    timed("adamw", lambda: adamw_step(p32, g32, m32, v32, p16, lr=1e-6, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
+                                      step=3), n * (4 * 4 + 3 * 4 + 2))
+    acc = torch.zeros(1, device=dev)
+    timed("sumsq", lambda: sumsq_into(g32, acc), n * 4)
+    B, R = 4096, 8192
+    lp = -torch.rand(B, R, device=dev)
+    lp.requires_grad_(True)
+    old, adv, ref = lp.detach() + 0.01, torch.randn(B, R, device=dev), lp.detach() - 0.01
+    mask = torch.ones(B, R, device=dev)
+    timed("ppo_loss", lambda: ppo_loss_fused(lp, old, adv, mask, ref_logp=ref, kl_coef=0.001), 6 * B * R * 4)
+    timed("gae", lambda: gae(adv, old, mask, 1.0, 0.95), 5 * B * R * 4)
+    gids = (torch.arange(B, device=dev) // 8).int()
+    timed("grpo_adv", lambda: grpo_advantage(adv[:, 0].contiguous(), gids, mask, B // 8), 2 * B * R * 4)
+    logits = torch.randn(256, V, device=dev)
+    step = torch.zeros(1, dtype=torch.long, device=dev)
+    timed("sample", lambda: sample(logits, temperature=torch.ones(256, device=dev), seed=1, step=step), 256 * V * 4)
+    NB, bs = 16384, 16
+    kc = torch.zeros(NB, Hk, bs, D, device=dev, dtype=bf)
+    vc = torch.zeros_like(kc)
+    kn, vn = torch.randn(T, Hk, D, device=dev, dtype=bf), torch.randn(T, Hk, D, device=dev, dtype=bf)
+    slots = torch.randperm(NB * bs, device=dev)[:T]
+    timed("kv_cache_write", lambda: kv_cache_write(kn, vn, slots, kc, vc), 4 * T * Hk * D * 2)
+    Bd, mb = 256, 96
+    z64 = lambda: torch.zeros(Bd, dtype=torch.long, device=dev)  # noqa: E731
+    z32 = lambda v=0: torch.full((Bd,), v, dtype=torch.int32, device=dev)  # noqa: E731
+    bt = torch.arange(Bd * mb, device=dev, dtype=torch.int32).view(Bd, mb)
+    ring_t, ring_l = torch.zeros(8, Bd, dtype=torch.long, device=dev), torch.zeros(8, Bd, device=dev)
+    bpos = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = (z64(), torch.zeros(Bd, device=dev), z64(), z64(), z64(), z32(5), bt, 16, z32(1000), z32(1), z32(0), 2, ring_t, ring_l,
+          bpos, step)
+    timed("decode_advance", lambda: (bpos.zero_(), decode_advance(*st)), Bd * 64)
+    wq = torch.randn(18944, 3584, device=dev, dtype=bf)
+    timed("fp8_quant_weight", lambda: fp8.quantize_weight(wq), wq.numel() * 3)
+    xa = torch.randn(T, H, device=dev, dtype=bf)
+    timed("fp8_quant_act", lambda: fp8.quantize_activation(xa), xa.numel() * 3)
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "lmhead", "decode", "decode_step", "attn", "fp8_gemm", "grouped_gemm"])
+    ap.add_argument("what", choices=["gemm", "lmhead", "decode", "decode_step", "attn", "fp8_gemm", "grouped_gemm", "small"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -242,7 +333,7 @@ def main(argv=None):
     ap.add_argument("--library", action="store_true")
     a = ap.parse_args(argv)
     fn = {"gemm": bench_gemm, "lmhead": bench_lmhead, "decode": bench_decode, "decode_step": bench_decode_step, "attn": bench_attn,
-          "fp8_gemm": bench_fp8_gemm, "grouped_gemm": bench_grouped_gemm}[a.what]
+          "fp8_gemm": bench_fp8_gemm, "grouped_gemm": bench_grouped_gemm, "small": bench_small}[a.what]
     print(json.dumps(fn(a)))
 
 
