@@ -43,6 +43,84 @@ def check_comm(comm, rank, world, dev):
     assert _lib.read_status(dev)[0] == 0
 
 
+def check_ulysses_a2a(comm, rank, world, dev):
+    """The peer-memory all-to-all of the Ulysses exchanges equals the torch.distributed one, in both directions, for
+    several rounds (alternating staging buffers), and a decoder layer under sequence parallelism uses it."""
+    from verl_b200.utils import ulysses
+
+    Tl, H, D = 96, 4 * world, 128
+    for it in range(4):
+        g = torch.Generator().manual_seed(10 * it + rank)
+        x = torch.randn(Tl, H, D, generator=g).to(dev, torch.bfloat16)
+        want = ulysses._all_to_all(x, 1, 0, dist.group.WORLD)           # NCCL: [W Tl, H / W, D]
+        got = comm.all_to_all_heads(x, gather_seq=True)
+        assert torch.equal(got, want), f"gather-seq exchange differs (round {it})"
+        back_want = ulysses._all_to_all(want, 0, 1, dist.group.WORLD)   # [Tl, H, D]
+        back = comm.all_to_all_heads(got, gather_seq=False)
+        assert torch.equal(back, back_want) and torch.equal(back, x), f"gather-heads exchange differs (round {it})"
+    ulysses.register_peer_comm(dist.group.WORLD, comm)
+    x = torch.randn(Tl, H, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    y = ulysses.gather_seq_scatter_heads(x, 0, 1, group=dist.group.WORLD)
+    z = ulysses.gather_heads_scatter_seq(y * 2.0, 1, 0, group=dist.group.WORLD)
+    z.sum().backward()
+    assert torch.equal(z.detach(), (x * 2.0).detach()) and torch.equal(x.grad, torch.full_like(x, 2.0))
+    ulysses._PEER_COMMS.clear()
+    comm.check()
+
+
+def check_tp_allreduce(comm, rank, world, dev):
+    """Fused all-reduce + residual + RMSNorm over peer memory: bit-identical on all ranks, equal to the fp32 reference,
+    also when replayed from a CUDA graph (device-side epoch)."""
+    if world not in (2, 4, 8):
+        return
+    rows, H = 200, 3584
+    bufs = [comm.alloc(rows * H, torch.bfloat16, zero=False) for _ in range(2)]
+    comm.barrier()
+    w = (torch.rand(H, generator=torch.Generator().manual_seed(1)) + 0.5).to(dev, torch.bfloat16)
+    res = torch.randn(rows, H, generator=torch.Generator().manual_seed(2)).to(dev, torch.bfloat16)
+    parts = [torch.randn(rows, H, generator=torch.Generator().manual_seed(100 + r)).to(torch.bfloat16) for r in range(world)]
+    ref_h = (sum(p.float() for p in parts) + res.float().cpu()).to(torch.bfloat16)
+    ref_y = (ref_h.float() * torch.rsqrt(ref_h.float().pow(2).mean(-1, keepdim=True) + 1e-6) * w.float().cpu()).to(torch.bfloat16)
+
+    def one(i):
+        b = bufs[i & 1][: rows * H].view(rows, H)
+        b.copy_(parts[rank].to(dev))
+        return comm.tp_allreduce_rmsnorm(b, res, w, 1e-6)
+
+    for i in range(4):
+        y, h = one(i)
+        torch.testing.assert_close(h.float().cpu(), ref_h.float(), atol=6e-2, rtol=2e-2)
+        torch.testing.assert_close(y.float().cpu(), ref_y.float(), atol=6e-2, rtol=2e-2)
+        both = [torch.empty_like(h) for _ in range(world)]
+        dist.all_gather(both, h)
+        assert all(torch.equal(b_, both[0]) for b_ in both), "the ranks' sums differ"
+    # replay from a CUDA graph: the kernel advances its own epoch
+    stage = [parts[rank].to(dev)]
+    g = torch.cuda.CUDAGraph()
+    s_ = torch.cuda.Stream()
+    s_.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s_):
+        outs = []
+        for i in range(2):
+            b = bufs[i & 1][: rows * H].view(rows, H)
+            b.copy_(stage[0])
+            outs.append(comm.tp_allreduce_rmsnorm(b, res, w, 1e-6))
+    torch.cuda.current_stream().wait_stream(s_)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(g):
+        outs = []
+        for i in range(2):
+            b = bufs[i & 1][: rows * H].view(rows, H)
+            b.copy_(stage[0])
+            outs.append(comm.tp_allreduce_rmsnorm(b, res, w, 1e-6))
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    for y, h in outs:
+        torch.testing.assert_close(h.float().cpu(), ref_h.float(), atol=6e-2, rtol=2e-2)
+    comm.check()
+
+
 def _packed(ids, lens, dev):
     from verl_b200.models.transformer import PackedBatch
 
@@ -240,6 +318,10 @@ def main():
         check_gemm_rs(comm, rank, world, dev)
     if what in ("zero", "all"):
         check_zero_step(rank, world, dev, comm)
+    if what in ("ulysses_a2a", "all"):
+        check_ulysses_a2a(comm, rank, world, dev)
+    if what in ("tp_allreduce", "all"):
+        check_tp_allreduce(comm, rank, world, dev)
     torch.cuda.synchronize()
     dist.barrier()
     if rank == 0:

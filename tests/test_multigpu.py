@@ -19,14 +19,14 @@ def _run(what: str, nproc: int = 2, timeout: int = 600):
     assert r.returncode == 0 and f"MG_WORKER_OK {what}" in r.stdout, (r.stdout[-3000:], r.stderr[-6000:])
 
 
-@pytest.mark.parametrize("what", ["comm", "reshard", "zero", "ag_gemm", "gemm_rs", "moe_ep"])
+@pytest.mark.parametrize("what", ["comm", "reshard", "zero", "ag_gemm", "gemm_rs", "moe_ep", "ulysses_a2a", "tp_allreduce"])
 def test_two_ranks(what):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     _run(what, 2)
 
 
-@pytest.mark.parametrize("what", ["comm", "reshard", "zero", "ag_gemm", "gemm_rs", "moe_ep"])
+@pytest.mark.parametrize("what", ["comm", "reshard", "zero", "ag_gemm", "gemm_rs", "moe_ep", "ulysses_a2a", "tp_allreduce"])
 def test_all_ranks(what):
     n = torch.cuda.device_count()
     if n <= 2:

@@ -22,6 +22,8 @@
 //                           buffer; expert outputs pulled back and mixed with the routing weights
 //   tp_allreduce_rmsnorm    tensor-parallel row-parallel epilogue: all-reduce of the ranks' partial products fused with
 //                           the residual add and the RMSNorm of the next block; device-side epoch (graph-replayable)
+//   peer_a2a_chunks         all-to-all of row chunks (Ulysses: gather the sequence / scatter the heads and back), pulled
+//                           straight into the destination layout
 //   peer_segment_copy       table-driven gather of byte ranges from peers into a local buffer: the
 //                           train -> rollout weight reshard (FSDP shards -> TP/EP layout) in one launch
 #include "common.cuh"
@@ -353,6 +355,49 @@ __global__ void tp_allreduce_rmsnorm_kernel(PeerPtrs partials, PeerPtrs pads, lo
       __threadfence();
       *reinterpret_cast<volatile uint32_t*>(epoch_ctr) = epoch;
     }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// All-to-all of row chunks over peer memory (the Ulysses exchanges around attention: gather the sequence and scatter
+// the heads, and back). Every rank has staged its tensor in symmetric memory; after the handshake each rank PULLS, from
+// every rank r, `rows` chunks of `chunk16` 16-byte units: chunk t of rank r starts at src_base16[r] + t * src_stride16
+// in r's buffer and lands at dst_base16[r] + t * dst_stride16 locally, i.e. directly in the layout the attention (or the
+// projection after it) wants: no intermediate buffers, no concatenation pass.
+struct A2AParams {
+  long long src_base16[MAX_RANKS];
+  long long dst_base16[MAX_RANKS];
+  long long src_stride16, dst_stride16;
+  int rows, chunk16;
+};
+
+__global__ void peer_a2a_chunks_kernel(PeerPtrs srcs, PeerPtrs pads, long long src_off16, uint4* __restrict__ dst,
+                                       A2AParams q, int rank, int world, int channel, uint32_t epoch, uint32_t* gate,
+                                       int* status) {
+  if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
+  const long long per_rank = (long long)q.rows * q.chunk16;
+  const long long total = per_rank * world;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  constexpr int U = 4;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
+    uint4 v[U];
+    long long d[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      d[u] = -1;
+      if (i < total) {
+        const int rr = (int)(i / per_rank);
+        const int r = (rr + rank) % world;  // start every rank on a different peer
+        const long long w = i - (long long)rr * per_rank;
+        const long long t = w / q.chunk16, c = w - t * q.chunk16;
+        v[u] = (reinterpret_cast<const uint4*>(srcs.p[r]) + src_off16)[q.src_base16[r] + t * q.src_stride16 + c];
+        d[u] = q.dst_base16[r] + t * q.dst_stride16 + c;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (d[u] >= 0) dst[d[u]] = v[u];
   }
 }
 
@@ -710,6 +755,33 @@ extern "C" int vb_tp_allreduce_rmsnorm(const void* const* partials, const void* 
   else if (world == 8) VB_TPAR(8);
   else return -3;
 #undef VB_TPAR
+  vb_count_launch();
+  return (int)cudaGetLastError();
+}
+
+// src_base / dst_base: `world` offsets each, strides and chunk in units of 16 bytes (see peer_a2a_chunks_kernel).
+extern "C" int vb_peer_a2a_chunks(const void* const* srcs, const void* const* pads, long long src_off_bytes, void* dst,
+                                  const long long* src_base16, const long long* dst_base16, long long src_stride16,
+                                  long long dst_stride16, int rows, int chunk16, int rank, int world, int channel,
+                                  unsigned epoch, unsigned* gate, int* status, cudaStream_t stream) {
+  if (world > MAX_RANKS || (src_off_bytes & 15) || rows < 0 || chunk16 <= 0 || (reinterpret_cast<uintptr_t>(dst) & 15)) return -3;
+  A2AParams q{};
+  for (int r = 0; r < world; ++r) {
+    q.src_base16[r] = src_base16[r];
+    q.dst_base16[r] = dst_base16[r];
+  }
+  q.src_stride16 = src_stride16;
+  q.dst_stride16 = dst_stride16;
+  q.rows = rows;
+  q.chunk16 = chunk16;
+  const long long total = (long long)rows * chunk16 * world;
+  long long blocks = (total + 1023) / 1024;
+  const int cap = 2 * vb_num_sms();  // every block must be resident while block 0 runs the handshake
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  peer_a2a_chunks_kernel<<<(int)blocks, 256, 0, stream>>>(make_ptrs(srcs, world), make_ptrs(pads, world), src_off_bytes >> 4,
+                                                          reinterpret_cast<uint4*>(dst), q, rank, world, channel, epoch,
+                                                          gate, status);
   vb_count_launch();
   return (int)cudaGetLastError();
 }

@@ -43,6 +43,8 @@ def _bind():
     lib.vb_gemm_rs_bf16.argtypes = [P, P, P, I, I, I, L, L, L, P, I, I, I, P, L, P, I, P, P]
     lib.vb_gemm_rs_bf16.restype = I
     lib.vb_peer_sum_slots.argtypes, lib.vb_peer_sum_slots.restype = [P, P, P, P, L, I, I, I, I, U, P, P, P], I
+    lib.vb_peer_a2a_chunks.argtypes = [P, P, L, P, P, P, L, L, I, I, I, I, I, U, P, P, P]
+    lib.vb_peer_a2a_chunks.restype = I
     lib.vb_tp_allreduce_rmsnorm.argtypes = [P, P, L, P, P, P, P, I, I, F, I, I, I, P, P, P]
     lib.vb_tp_allreduce_rmsnorm.restype = I
     _SIGS_BOUND = True
@@ -288,6 +290,59 @@ class PeerComm:
                                               self.CH_TP, self.tp_ctrs.data_ptr(), self._status(), _lib.stream())
         _lib.check(rc, "vb_tp_allreduce_rmsnorm")
         return y, h
+
+    def all_to_all_heads(self, x: torch.Tensor, gather_seq: bool) -> torch.Tensor:
+        """The two exchanges of Ulysses sequence parallelism on ``x [rows, heads, D]`` (16-bit elements), one kernel each,
+        pulled over peer memory straight into the output layout:
+
+        * ``gather_seq=True``:  ``[T / W, H, D]`` (this rank's tokens, all heads) -> ``[T, H / W, D]`` (all tokens, this
+          rank's heads), rank r's tokens at rows ``[r T / W, (r + 1) T / W)``;
+        * ``gather_seq=False``: ``[T, H / W, D]`` -> ``[T / W, H, D]``, rank r's heads at ``[r H / W, (r + 1) H / W)``.
+
+        The input is staged in one of two alternating symmetric buffers (rewritten only after a later exchange of this
+        communicator has passed its handshake). Collective: same shapes on every rank."""
+        W, me = self.world, self.rank
+        assert x.dim() == 3 and x.element_size() == 2
+        x = x.contiguous()
+        n = x.numel()
+        key = ("a2a", n, x.dtype)
+        bufs = self.__dict__.setdefault("_a2a_bufs", {})
+        if key not in bufs:
+            bufs[key] = [self.alloc(n, x.dtype, zero=False) for _ in range(2)] + [0]
+            self.barrier()
+        ent = bufs[key]
+        stage = ent[ent[2] & 1]
+        ent[2] += 1
+        stage.copy_(x.view(-1))
+        D = x.shape[2]
+        if gather_seq:
+            Tl, H = x.shape[0], x.shape[1]
+            assert H % W == 0
+            Hl = H // W
+            chunk = Hl * D
+            out = torch.empty((W * Tl, Hl, D), dtype=x.dtype, device=x.device)
+            src_base = [me * chunk] * W
+            dst_base = [r * Tl * chunk for r in range(W)]
+            src_stride, dst_stride, rows = H * D, chunk, Tl
+        else:
+            T, Hl = x.shape[0], x.shape[1]
+            assert T % W == 0
+            Tl = T // W
+            chunk = Hl * D
+            out = torch.empty((Tl, W * Hl, D), dtype=x.dtype, device=x.device)
+            src_base = [me * Tl * chunk] * W
+            dst_base = [r * chunk for r in range(W)]
+            src_stride, dst_stride, rows = chunk, W * chunk, Tl
+        assert (chunk * 2) % 16 == 0, "heads-per-rank x head_dim must be a multiple of 8 elements"
+        to16 = lambda v: [int(e) * 2 // 16 for e in v]  # noqa: E731
+        a, off = self._find(stage)
+        LL = ctypes.c_longlong * W
+        rc = self.lib.vb_peer_a2a_chunks(a.ptrs, self.pad_alloc.ptrs, off, out.data_ptr(), LL(*to16(src_base)),
+                                         LL(*to16(dst_base)), src_stride * 2 // 16, dst_stride * 2 // 16, rows, chunk * 2 // 16,
+                                         me, W, self.CH_COPY, self._epoch(self.CH_COPY), self._gate(self.CH_COPY),
+                                         self._status(), _lib.stream())
+        _lib.check(rc, "vb_peer_a2a_chunks")
+        return out
 
     def check(self):
         """Synchronising read of the status word; raises if a bounded wait ran out."""

@@ -14,6 +14,13 @@ import torch
 import torch.distributed as dist
 
 _SP_GROUP = None
+_PEER_COMMS: dict = {}  # process group -> peer-memory communicator that carries the exchanges of that group
+
+
+def register_peer_comm(group, comm) -> None:
+    """Route the all-to-alls of ``group`` through ``comm`` (:meth:`PeerComm.all_to_all_heads`: one kernel that pulls
+    straight into the output layout over NVLink) instead of ``torch.distributed``."""
+    _PEER_COMMS[group] = comm
 
 
 def set_ulysses_sequence_parallel_group(group) -> None:
@@ -45,6 +52,10 @@ def _all_to_all(x: torch.Tensor, scatter_dim: int, gather_dim: int, group) -> to
     sp = dist.get_world_size(group)
     if sp == 1:
         return x
+    comm = _PEER_COMMS.get(group)
+    if (comm is not None and x.is_cuda and x.dim() == 3 and x.element_size() == 2 and {scatter_dim, gather_dim} == {0, 1}
+            and x.shape[scatter_dim] % sp == 0 and (x.shape[1] // (sp if scatter_dim == 1 else 1)) * x.shape[2] % 8 == 0):
+        return comm.all_to_all_heads(x, gather_seq=(gather_dim == 0))
     parts = [t.contiguous() for t in torch.tensor_split(x, sp, dim=scatter_dim)]
     if dist.get_backend(group) == "gloo":
         # gloo has no all-to-all: gather every rank's parts and keep the ones addressed to this rank (CPU tests)

@@ -389,6 +389,12 @@ class NativeEngine(BaseEngine):
         validate_ulysses_config(self.model_config.num_attention_heads, sp)
         self.sp_group = self._block_groups(sp, strided=False)
         self.sp_size, self.sp_rank = sp, r % sp
+        if self.device.type == "cuda" and self.comm is not None:
+            # the exchanges around attention run as peer-memory kernels of the sequence-parallel group
+            from ...parallel.peer_comm import PeerComm
+            from ...utils.ulysses import register_peer_comm
+
+            register_peer_comm(self.sp_group, self.comm if sp == self.dp_world else PeerComm(self.sp_group))
         for layer in self.model.layers:
             layer.self_attn.sp_group = self.sp_group
 
