@@ -579,3 +579,71 @@ def test_fp8_blockscale_quant_and_gemm(M, N, K, pow2):
     rel = (out.float() - full).norm() / full.norm()
     assert rel < 0.06, float(rel)
     _bf16_close(fp8.fp8_linear(x, wq, sw, bias, pow2), ref, ulps=4)
+
+
+@pytest.mark.parametrize("T", [8, 128, 1000])
+def test_programmatic_dependent_launch_chain_is_bit_identical(T):
+    """A decode-layer-shaped chain (norm -> GEMM -> rope -> cache write -> paged attention -> GEMM -> norm -> GEMM ->
+    swiglu -> GEMM) gives the same bits whether each kernel waits for the one before it at launch (the ordinary
+    stream order) or only before its first global access (programmatic dependent launch), eagerly and in a graph."""
+    from verl_b200 import ops
+    from verl_b200.ops import _lib
+
+    torch.manual_seed(3)
+    H, Hq, Hk, D, I, bs = 1024, 8, 2, 128, 2048, 16
+    dev = "cuda"
+    x0 = torch.randn(T, H, device=dev).bfloat16()
+    wn = torch.randn(H, device=dev).bfloat16()
+    wqkv = (torch.randn((Hq + 2 * Hk) * D, H, device=dev) * 0.03).bfloat16()
+    wo = (torch.randn(H, Hq * D, device=dev) * 0.03).bfloat16()
+    wgu = (torch.randn(2 * I, H, device=dev) * 0.03).bfloat16()
+    wd = (torch.randn(H, I, device=dev) * 0.03).bfloat16()
+    ctx = 200
+    nblk = (ctx + bs) // bs + 1
+    kc = torch.randn(T * nblk, Hk, bs, D, device=dev).bfloat16()
+    vc = torch.randn_like(kc)
+    table = torch.arange(T * nblk, device=dev, dtype=torch.int32).reshape(T, nblk)
+    lens = torch.full((T,), ctx + 1, device=dev, dtype=torch.int32)
+    pos = torch.full((T,), ctx, device=dev, dtype=torch.long)
+    slots = table[:, ctx // bs].long() * bs + ctx % bs
+    cos, sin = ops.rope_tables(D, 4096, 10000.0, dev)
+
+    def chain(x):
+        for _ in range(3):
+            h, res = ops.rmsnorm(x, wn, 1e-6, None)
+            qkv = ops.gemm(h, wqkv)
+            qkv = ops.rope_qkv(qkv, pos, cos, sin, Hq, Hk, D)
+            q = qkv[:, : Hq * D].view(T, Hq, D)
+            k = qkv[:, Hq * D : (Hq + Hk) * D].view(T, Hk, D)
+            v = qkv[:, (Hq + Hk) * D :].view(T, Hk, D)
+            ops.kv_cache_write(k, v, slots, kc, vc)
+            a = ops.paged_decode_attention(q, kc, vc, table, lens)
+            o = ops.gemm(a.reshape(T, Hq * D), wo)
+            h, res = ops.rmsnorm(o, wn, 1e-6, res)
+            x = ops.gemm(ops.swiglu(ops.gemm(h, wgu)), wd)
+        return x
+
+    outs = {}
+    try:
+        for on in (False, True):
+            _lib.set_pdl(on)
+            outs[on, "eager"] = chain(x0).clone()
+            g = torch.cuda.CUDAGraph()
+            static_in = x0.clone()
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                chain(static_in)
+            torch.cuda.current_stream().wait_stream(s)
+            with torch.cuda.graph(g):
+                static_out = chain(static_in)
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            outs[on, "graph"] = static_out.clone()
+    finally:
+        _lib.set_pdl(True)
+    ref = outs[False, "eager"]
+    assert torch.isfinite(ref.float()).all()
+    for key, val in outs.items():
+        assert torch.equal(val, ref), f"{key} differs from the ordinary stream order"

@@ -53,6 +53,18 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
 // ---------------------------------------------------------------------------
+// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute may start while
+// its predecessor in the stream still runs: what it does before pdl_wait() (barrier init, TMEM allocation,
+// descriptor prefetch) overlaps the predecessor's tail. pdl_wait() returns once every prerequisite grid has
+// finished and its writes are visible; no global memory that another kernel produces or reads may be touched
+// before it. pdl_trigger() lets the NEXT kernel be scheduled; call it only after this CTA holds every resource it
+// will ever allocate (TMEM above all: a dependent that took the columns first would wait on this kernel while
+// this kernel waits on the columns). Both are no-ops in a kernel launched the ordinary way.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

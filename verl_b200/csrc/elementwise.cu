@@ -49,6 +49,8 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
                                    __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int H,
                                    float eps) {
   __shared__ float sh[32];
+  pdl_trigger();
+  pdl_wait();
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * H;
   const int nvec = H >> 3;
@@ -157,6 +159,8 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16* __rest
   // multimodal rotary embedding (mrope_s0 > 0): pos is [3, T] (temporal, height, width); rotary frequency j takes the
   // position of axis 0 for j < s0, of axis 1 for j < s0 + s1, of axis 2 above (sections are multiples of 8, so the 8
   // frequencies of one thread share an axis)
+  pdl_trigger();
+  pdl_wait();
   const int half = D >> 1;
   const int vec_per_head = half >> 3;
   const long long total = (long long)T * (Hq + Hk) * vec_per_head;
@@ -196,6 +200,8 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16* __rest
 // gu: [T, 2I] (gate | up), out: [T, I]
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long T,
                                   int I) {
+  pdl_trigger();
+  pdl_wait();
   const int nvec = I >> 3;
   const long long total = T * nvec;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -339,11 +345,11 @@ extern "C" int vb_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
   if (rows <= 0) return 0;
   if (H & 7) return -3;
   const int threads = H >= 4096 ? 512 : 256;
-  rmsnorm_fwd_kernel<<<(unsigned)rows, threads, 0, stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
-      (__nv_bfloat16*)res_out, rstd, H, eps);
+  cudaError_t e = vb_launch_pdl(rmsnorm_fwd_kernel, dim3((unsigned)rows), dim3(threads), 0, stream, 1,
+                                (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+                                (__nv_bfloat16*)y, (__nv_bfloat16*)res_out, rstd, H, eps);
   vb_count_launch();
-  return (int)cudaGetLastError();
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 // Number of partial rows the backward uses; dw_partial must hold that many rows of H floats.
@@ -393,20 +399,20 @@ static int rope_launch(void* q, void* k, long long q_stride, long long k_stride,
   if (T <= 0) return 0;
   if (D & 15) return -3;
   const long long total = (long long)T * (Hq + Hk) * (D / 16);
-  rope_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, stream>>>((__nv_bfloat16*)q, (__nv_bfloat16*)k, q_stride,
-                                                                  k_stride, pos, cos_t, sin_t, T, Hq, Hk, D,
-                                                                  backward ? -1.f : 1.f, s0, s1);
+  cudaError_t e = vb_launch_pdl(rope_kernel, dim3(grid_for(total, 256, 148 * 16)), dim3(256), 0, stream, 1,
+                                (__nv_bfloat16*)q, (__nv_bfloat16*)k, q_stride, k_stride, pos, cos_t, sin_t, T, Hq, Hk,
+                                D, backward ? -1.f : 1.f, s0, s1);
   vb_count_launch();
-  return (int)cudaGetLastError();
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 extern "C" int vb_swiglu_fwd(const void* gu, void* out, long long T, int I, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (I & 7) return -3;
-  swiglu_fwd_kernel<<<grid_for(T * (I / 8), 256, 148 * 16), 256, 0, stream>>>((const __nv_bfloat16*)gu,
-                                                                              (__nv_bfloat16*)out, T, I);
+  cudaError_t e = vb_launch_pdl(swiglu_fwd_kernel, dim3(grid_for(T * (I / 8), 256, 148 * 16)), dim3(256), 0, stream, 1,
+                                (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
   vb_count_launch();
-  return (int)cudaGetLastError();
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 extern "C" int vb_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long T, int I, cudaStream_t stream) {

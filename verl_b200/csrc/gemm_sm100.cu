@@ -313,6 +313,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();  // TMEM is held: a dependent kernel may take what is left
+  pdl_wait();     // nothing above reads or writes global memory
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -881,6 +883,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   cluster_sync_all();  // both CTAs' barriers are initialised and both allocations are done
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();  // TMEM is held: a dependent kernel may take what is left
+  pdl_wait();     // nothing above reads or writes global memory
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
@@ -1065,9 +1069,9 @@ static int launch_gemm_pair(const void* A, const void* B, long long lda, long lo
   const int units = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + P_BN - 1) / P_BN);
   if (units <= 0) return 0;
   const int clusters = units < max_clusters ? units : max_clusters;
-  kern<<<2 * clusters, NUM_THREADS, P_DYN_BYTES, stream>>>(tmA, tmB, p);
+  cudaError_t e = vb_launch_pdl(kern, dim3(2 * clusters), dim3(NUM_THREADS), P_DYN_BYTES, stream, 1, tmA, tmB, p);
   vb_count_launch();
-  return (int)cudaGetLastError();
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
@@ -1097,21 +1101,12 @@ static int launch_gemm(const void* A, const void* B, long long lda, long long ld
   const int units = (EPI == EPI_LSE) ? num_m * p.num_splits : num_m * num_n * (p.k_splits > 1 ? p.k_splits : 1);
   if (units <= 0) return 0;
   const int grid = units < vb_num_sms() ? units : vb_num_sms();
+  // kernels that wait on other ranks (all-gather prologue, reduce-scatter epilogue) start the ordinary way
+  const bool pdl = EPI != EPI_STORE_AG && p.rs_rows == 0;
   if (EPI == EPI_STORE && p.k_splits > 1 && p.k_cluster) {
     // one cluster per output tile, one CTA per k slice; clusters are scheduled as SMs free up (no grid-wide barrier)
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(units);
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = dyn_bytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = p.k_splits;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+    cudaError_t e = vb_launch_ex(kern, dim3(units), dim3(NUM_THREADS), dyn_bytes, stream, (unsigned)p.k_splits, pdl,
+                                 tmA, tmB, p);
     vb_count_launch();
     return (int)e;
   }
@@ -1130,9 +1125,9 @@ static int launch_gemm(const void* A, const void* B, long long lda, long long ld
     vb_count_launch();
     return (int)e;
   }
-  kern<<<grid, NUM_THREADS, dyn_bytes, stream>>>(tmA, tmB, p);
+  cudaError_t e = vb_launch_ex(kern, dim3(grid), dim3(NUM_THREADS), dyn_bytes, stream, 1, pdl, tmA, tmB, p);
   vb_count_launch();
-  return (int)cudaGetLastError();
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 

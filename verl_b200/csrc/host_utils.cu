@@ -3,6 +3,7 @@
 // loads on a machine without a GPU), the launch counter, device properties.
 #include "common.cuh"
 #include "host_utils.h"
+#include <cstdlib>
 
 #include <atomic>
 #include <mutex>
@@ -92,5 +93,16 @@ int vb_num_sms() {
   }
   return sms[dev];
 }
+
+static int g_pdl = -1;
+int vb_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("VERL_B200_PDL");
+    g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl;
+}
+// Switch programmatic dependent launch on or off for launches (and graph captures) made after the call.
+extern "C" void vb_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
 extern "C" int vb_abi_version() { return 1; }

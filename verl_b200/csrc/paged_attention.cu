@@ -212,6 +212,8 @@ __global__ void kv_write_kernel(const __nv_bfloat16* __restrict__ k, const __nv_
                                 long long k_stride, long long v_stride, const long long* __restrict__ slots,
                                 __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc, long long T, int Hk,
                                 int D, int block_size) {
+  pdl_trigger();
+  pdl_wait();
   const int vec_per_tok = Hk * D / 8;
   const long long total = T * vec_per_tok;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -291,8 +293,9 @@ extern "C" int vb_kv_cache_write(const void* k, const void* v, long long k_strid
   if (D & 7) return -3;
   long long g = (T * (Hk * D / 8) + 255) / 256;
   if (g > 148 * 8) g = 148 * 8;
-  kv_write_kernel<<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v, k_stride, v_stride,
-                                              slots, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, T, Hk, D, block_size);
+  cudaError_t e = vb_launch_pdl(kv_write_kernel, dim3((unsigned)g), dim3(256), 0, stream, 1, (const __nv_bfloat16*)k,
+                                (const __nv_bfloat16*)v, k_stride, v_stride, slots, (__nv_bfloat16*)kc,
+                                (__nv_bfloat16*)vc, T, Hk, D, block_size);
   vb_count_launch();
-  return (int)cudaGetLastError();
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }

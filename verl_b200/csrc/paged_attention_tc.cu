@@ -97,12 +97,6 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
   const int G = p.Hq / p.Hk;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int seq_len = p.seq_lens[b];
-  const int chunks_total = (seq_len + TC_CHUNK - 1) / TC_CHUNK;
-  const int per_split = (chunks_total + p.num_splits - 1) / p.num_splits;
-  const int c_begin = split * per_split;
-  const int c_end = min(chunks_total, c_begin + per_split);
-  const int n_chunks = max(c_end - c_begin, 0);
 
   if (tid == 0) {
     for (int s = 0; s < TC_STAGES; ++s) {
@@ -117,6 +111,25 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     *abort_flag = 0;
     mbar_fence_init();
   }
+  // Q^T operand: [16 heads x 128 dims], rows >= G are zero. P buffers start zeroed (rows >= G stay zero).
+  for (int i = tid; i < (Q_BYTES + 2 * P_BYTES) / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 64);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();  // TMEM is held: a dependent kernel may take what is left
+  pdl_wait();     // nothing above reads or writes global memory
+
+  const int seq_len = p.seq_lens[b];
+  const int chunks_total = (seq_len + TC_CHUNK - 1) / TC_CHUNK;
+  const int per_split = (chunks_total + p.num_splits - 1) / p.num_splits;
+  const int c_begin = split * per_split;
+  const int c_end = min(chunks_total, c_begin + per_split);
+  const int n_chunks = max(c_end - c_begin, 0);
   // block-table entries of this CTA's pages: the producer must not chase global loads between its copies
   const int pages_per_chunk = TC_CHUNK / p.block_size;
   const int n_pages = (seq_len + p.block_size - 1) / p.block_size;
@@ -126,23 +139,13 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const int cnt = min(min(n_chunks * pages_per_chunk, n_pages - page_base), TC_BT_MAX);
     for (int i = tid; i < cnt; i += TC_THREADS) bt_s[i] = bt[page_base + i];
   }
-  // Q^T operand: [16 heads x 128 dims], rows >= G are zero. P buffers start zeroed (rows >= G stay zero).
-  for (int i = tid; i < (Q_BYTES + 2 * P_BYTES) / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
-  __syncthreads();
   for (int i = tid; i < G * TC_D; i += TC_THREADS) {
     const int g = i / TC_D, d = i % TC_D;
     const __nv_bfloat16 v = p.q[(long long)b * p.q_stride + (long long)(h * G + g) * TC_D + d];
     *reinterpret_cast<__nv_bfloat16*>(q_s + sw128_off(g, d, TC_NH)) = v;
   }
   fence_proxy_async_smem();
-  if (warp == 5) {
-    tmem_alloc(tmem_slot, 64);
-    tmem_relinquish();
-  }
-  tc_fence_before();
   __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 4) {
     // ------------------------------- TMA producer -------------------------------
@@ -440,6 +443,8 @@ paged_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tmK, const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();  // TMEM is held: a dependent kernel may take what is left
+  pdl_wait();     // nothing above reads or writes global memory
 
   if (warp == 4) {
     // ------------------- producer: Q rows, block table, K / V tiles of item after item -------------------
@@ -776,13 +781,14 @@ extern "C" int vb_paged_decode_tc(const void* q, long long q_stride, const void*
                                          TCP_SMEM));
       attr2_set = true;
     }
-    paged_decode_tc_persist_kernel<<<2 * vb_num_sms(), TC_THREADS, TCP_SMEM, stream>>>(tmK, tmV, p, items);
+    rc = (int)vb_launch_pdl(paged_decode_tc_persist_kernel, dim3(2 * vb_num_sms()), dim3(TC_THREADS), TCP_SMEM, stream,
+                            1, tmK, tmV, p, items);
   } else {
     dim3 grid(B, Hk, num_splits);
-    paged_decode_tc_kernel<<<grid, TC_THREADS, TC_SMEM, stream>>>(tmK, tmV, p);
+    rc = (int)vb_launch_pdl(paged_decode_tc_kernel, grid, dim3(TC_THREADS), TC_SMEM, stream, 1, tmK, tmV, p);
   }
   vb_count_launch(num_splits > 1 ? 2 : 1);
-  rc = (int)cudaGetLastError();
+  if (rc == 0) rc = (int)cudaGetLastError();
   if (rc || num_splits == 1) return rc;
   return vb_decode_merge_128(p.o_part, p.ml_part, B, Hq, num_splits, out, out_stride, stream);
 }

@@ -184,6 +184,114 @@ __device__ __forceinline__ uint4 philox(uint4 c, uint2 k) {
 }
 __device__ __forceinline__ float u01(uint32_t x) { return ((float)(x >> 8) + 0.5f) * (1.f / 16777216.f); }
 
+// Four consecutive logits starting at v0 (a multiple of 4) as floats; elements past V read as -inf. `vec` says that the
+// row base is aligned for one 16-byte (fp32) / 8-byte (bf16) load.
+__device__ __forceinline__ void load4_logits(const float* lg, bool vec, int v0, int V, float (&x)[4]) {
+  if (vec && v0 + 3 < V) {
+    const float4 t = *reinterpret_cast<const float4*>(lg + v0);
+    x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = v0 + j < V ? lg[v0 + j] : -INFINITY;
+  }
+}
+__device__ __forceinline__ void load4_logits(const __nv_bfloat16* lg, bool vec, int v0, int V, float (&x)[4]) {
+  if (vec && v0 + 3 < V) {
+    const uint2 t = *reinterpret_cast<const uint2*>(lg + v0);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = v0 + j < V ? __bfloat162float(lg[v0 + j]) : -INFINITY;
+  }
+}
+
+// Unrestricted support (no top-k / top-p, or greedy): ONE pass over the row. Each thread keeps an online
+// (max, sum of exp) pair and the Gumbel-max candidate of its elements; the argmax of logit / T + Gumbel noise needs no
+// normaliser, and the log-prob of the winner is x - max - log(sum).
+template <typename T>
+__device__ __forceinline__ void sample_row_one_pass(const T* __restrict__ lg, int V, int row, float inv_t, bool greedy,
+                                                    unsigned long long seed, unsigned long long st,
+                                                    long long* __restrict__ token_out,
+                                                    float* __restrict__ logprob_out) {
+  __shared__ float sm_m[32], sm_z[32], sm_b[32];
+  __shared__ int sm_i[32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const bool vec = (reinterpret_cast<uintptr_t>(lg) & (4 * sizeof(T) - 1)) == 0;
+  float m = -INFINITY, zs = 0.f, best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int v0 = threadIdx.x * 4; v0 < V; v0 += blockDim.x * 4) {
+    float x[4];
+    load4_logits(lg, vec, v0, V, x);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] *= inv_t;
+    const float gm = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+    if (gm > m) {
+      zs *= __expf(m - gm);  // m = -inf: zs is still 0
+      m = gm;
+    }
+    if (m > -INFINITY) zs += __expf(x[0] - m) + __expf(x[1] - m) + __expf(x[2] - m) + __expf(x[3] - m);
+    uint32_t rr[4] = {0u, 0u, 0u, 0u};
+    if (!greedy) {
+      const uint4 rnd = philox(make_uint4((uint32_t)v0, (uint32_t)row, (uint32_t)st, (uint32_t)(st >> 32)),
+                               make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
+      rr[0] = rnd.x; rr[1] = rnd.y; rr[2] = rnd.z; rr[3] = rnd.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (v0 + j < V) {
+        const float sc = greedy ? x[j] : x[j] - __logf(-__logf(u01(rr[j])));
+        if (sc > best) {  // indices only grow inside a thread: ties keep the lowest
+          best = sc;
+          best_i = v0 + j;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o), oz = __shfl_xor_sync(0xffffffffu, zs, o);
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    const float nm = fmaxf(m, om);
+    zs = nm > -INFINITY ? zs * __expf(m - nm) + oz * __expf(om - nm) : 0.f;
+    m = nm;
+    if (ob > best || (ob == best && oi < best_i)) {
+      best = ob;
+      best_i = oi;
+    }
+  }
+  if (lane == 0) {
+    sm_m[warp] = m; sm_z[warp] = zs; sm_b[warp] = best; sm_i[warp] = best_i;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    m = lane < nw ? sm_m[lane] : -INFINITY;
+    zs = lane < nw ? sm_z[lane] : 0.f;
+    best = lane < nw ? sm_b[lane] : -INFINITY;
+    best_i = lane < nw ? sm_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o), oz = __shfl_xor_sync(0xffffffffu, zs, o);
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      const float nm = fmaxf(m, om);
+      zs = nm > -INFINITY ? zs * __expf(m - nm) + oz * __expf(om - nm) : 0.f;
+      m = nm;
+      if (ob > best || (ob == best && oi < best_i)) {
+        best = ob;
+        best_i = oi;
+      }
+    }
+    if (lane == 0) {
+      const int tok = best_i < V ? best_i : 0;
+      token_out[row] = tok;
+      if (logprob_out) logprob_out[row] = ((float)lg[tok] * inv_t - m) - __logf(zs);
+    }
+  }
+}
+
 // One block per row. Gumbel-max sampling from softmax(logits / T) restricted by top-k / top-p
 // (threshold found by bisection on the probability value), greedy when temperature == 0.
 // Outputs the token and the log-prob of the sampled token under the *processed* distribution
@@ -206,6 +314,11 @@ __global__ void sample_kernel(const T* __restrict__ logits, long long row_stride
   const int k = top_k ? top_k[row] : -1;
   const float tp = top_p ? top_p[row] : 1.f;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (greedy || !((k > 0 && k < V) || tp < 1.f)) {  // the same for every thread of the block
+    sample_row_one_pass<T>(lg, V, row, inv_t, greedy, seed, step ? (unsigned long long)(*step) : 0ull, token_out,
+                           logprob_out);
+    return;
+  }
 
   // pass 1: max
   float mx = -INFINITY;

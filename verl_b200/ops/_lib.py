@@ -24,6 +24,7 @@ _SIGS = {
     "vb_abi_version": ([], I),
     "vb_launch_count": ([], L),
     "vb_launch_count_reset": ([], None),
+    "vb_set_pdl": ([I], None),
     # gemm
     "vb_gemm_bf16": ([P, P, P, P, I, I, I, L, L, L, I, I, I, I, P, P], I),
     "vb_gemm_bf16_ws": ([P, P, P, P, I, I, I, L, L, L, I, I, I, I, P, L, P, I, P, P], I),
@@ -112,6 +113,13 @@ def fn(name: str):
         return getattr(lib, name)
     except AttributeError as e:
         raise NativeLibraryError(f"symbol {name} not in {_LIB_PATH}; rebuild the native library") from e
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for the kernels that support it (default on; VERL_B200_PDL=0 turns it off):
+    each such kernel may start while the kernel before it in the stream still runs, and waits for it only before
+    its first access to global memory. Applies to launches and graph captures made after the call."""
+    fn("vb_set_pdl")(1 if on else 0)
 
 
 def ptr(t) -> int | None:

@@ -175,6 +175,15 @@ def bench_decode_step(a):
     prompts = [torch.randint(100, cfg.vocab_size - 100, (a.ctx - 8,), generator=g).tolist() for _ in range(a.batch)]
     eng.generate(prompts, SamplingParams(temperature=1.0, max_tokens=4, ignore_eos=True))
     st, graph, run = eng._get_graph(a.batch)
+    # the sequences above have finished and their rows are padding again: give every row a context of `ctx` tokens
+    # (pages spread over the whole cache) and leave it not alive, so that replays do not advance or write the cache
+    per = (a.ctx + eng.block_size - 1) // eng.block_size
+    nblk = eng.k_cache[0].shape[0]
+    st["bt"][:, :per] = (torch.randperm(a.batch * per, device=dev) % nblk).view(a.batch, per).int()
+    st["lens"].fill_(a.ctx)
+    st["pos"].fill_(a.ctx - 1)
+    st["alive"].zero_()
+    st["slots"].fill_(-1)
     us = _time(graph.replay, a.iters, a.warmup, graph=False)
     return {"kernel": "decode_step_graph", "model": a.model, "layers": a.layers, "B": a.batch, "ctx": a.ctx,
             "us": round(us, 1), "tokens_per_s": round(a.batch / us * 1e6, 0)}
