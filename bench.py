@@ -51,6 +51,9 @@ def parse_args():
                          "profiler and write the per-kernel device-time shares to this JSON file (rank 0)")
     ap.add_argument("--phases", default="rollout,logprob,update,resync,fused_ce",
                     help="stock-libs arm: which phases to time")
+    ap.add_argument("--config", type=int, default=1, choices=[1, 2],
+                    help="1 = GRPO (the headline); 2 = PPO with a critic of the same architecture, GAE, 32 prompts x 1 "
+                         "sample per GPU, even-id reward")
     ap.add_argument("--model", default="qwen2.5-7b")
     ap.add_argument("--prompts-per-gpu", type=int, default=16)
     ap.add_argument("--n", type=int, default=8)
@@ -159,6 +162,18 @@ def build_config(args, world: int):
         f"actor_rollout_ref.actor.ppo_max_token_len_per_gpu={args.max_token_len}", "actor_rollout_ref.actor.use_kl_loss=true",
         "actor_rollout_ref.actor.kl_loss_coef=0.001", "actor_rollout_ref.actor.optim.lr=1e-6",
     ]
+    if args.config == 2:
+        # PPO with a critic: GAE (gamma = lambda = 1), value clip 0.5, KL against the reference policy in the reward,
+        # reward = fraction of even ids at the last token
+        ov = [o for o in ov if not o.startswith(("algorithm.adv_estimator", "data.train_files", "actor_rollout_ref.actor.use_kl_loss"))]
+        ov += ["algorithm.adv_estimator=gae", "algorithm.gamma=1.0", "algorithm.lam=1.0",
+               "actor_rollout_ref.actor.use_kl_loss=false", "algorithm.use_kl_in_reward=true",
+               f"data.train_files=synthetic:{global_prompts * 4}:{args.min_prompt}:{args.max_prompt}:100:151000:0:synthetic/even_fraction",
+               f"critic.model.path=preset:{args.model}", "critic.optim.lr=1e-5", "critic.cliprange_value=0.5",
+               f"critic.ppo_mini_batch_size={global_prompts}", "critic.use_dynamic_bsz=true",
+               f"critic.ppo_max_token_len_per_gpu={args.max_token_len}"]
+        if args.layers:
+            ov.append(f"+critic.model.override_config.num_hidden_layers={args.layers}")
     if args.layers:
         ov.append(f"+actor_rollout_ref.model.override_config.num_hidden_layers={args.layers}")
     if args.agent_loop:
@@ -211,8 +226,13 @@ def main():
     cfg = build_config(args, world)
     tok = build_tokenizer(cfg)
     ds = create_rl_dataset(cfg.data.train_files, cfg.data, tok)
-    rpm = ResourcePoolManager({"global_pool": [1]}, {Role.ActorRollout: "global_pool"}, pool_cls=SPMDResourcePool)
-    trainer = RayPPOTrainer(config=cfg, tokenizer=tok, role_worker_mapping={Role.ActorRollout: ActorRolloutRefWorker},
+    roles, mapping = {Role.ActorRollout: ActorRolloutRefWorker}, {Role.ActorRollout: "global_pool"}
+    if args.config == 2:
+        from verl_b200.workers.engine_workers import CriticWorker
+
+        roles[Role.Critic], mapping[Role.Critic] = CriticWorker, "global_pool"
+    rpm = ResourcePoolManager({"global_pool": [1]}, mapping, pool_cls=SPMDResourcePool)
+    trainer = RayPPOTrainer(config=cfg, tokenizer=tok, role_worker_mapping=roles,
                             resource_pool_manager=rpm, ray_worker_group_cls=SPMDWorkerGroup,
                             reward_fn=load_reward_manager(cfg, tok), val_reward_fn=None, train_dataset=ds,
                             train_sampler=create_rl_sampler(cfg.data, ds), device_name="cuda")
@@ -287,13 +307,15 @@ def main():
     if rank == 0:
         c = worker.model_config
         out = {
-            "metric": "RL step tokens/s/box (GRPO, rollout+logprob+ref+update+resync)", "value": tokens / (total_ms / 1e3),
+            "metric": ("RL step tokens/s/box (GRPO, rollout+logprob+ref+update+resync)" if args.config == 1 else
+                       "RL step tokens/s/box (PPO + critic, rollout+logprob+values+update_critic+update_actor+resync)"),
+            "value": tokens / (total_ms / 1e3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic prompts (uniform ids), random-init weights", "impl": "ours",
             "config": {"model": (args.model if not args.layers else f"{args.model}-REDUCED-{args.layers}L")
                        + ("+agent-loop-rollout" if args.agent_loop else "") + (f"+lora{args.lora_rank}" if args.lora_rank else ""),
-                       "layers": c.num_hidden_layers, "hidden": c.hidden_size, "vocab": c.vocab_size,
+                       "benchmark_config": args.config, "layers": c.num_hidden_layers, "hidden": c.hidden_size, "vocab": c.vocab_size,
                        "global_batch": args.prompts_per_gpu * world * args.n, "prompts": args.prompts_per_gpu * world,
                        "n_samples": args.n, "seq_len": args.max_prompt + args.max_response,
                        "prompt_len": [args.min_prompt, args.max_prompt], "max_response": args.max_response,

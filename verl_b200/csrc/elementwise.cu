@@ -354,7 +354,7 @@ extern "C" int vb_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
 
 // Number of partial rows the backward uses; dw_partial must hold that many rows of H floats.
 extern "C" int vb_rmsnorm_bwd_parts(long long rows) {
-  const int g = 2 * vb_num_sms();
+  const int g = 6 * vb_num_sms();  // six resident blocks per SM: 75 % of the warp slots (two left the loads starved)
   return rows < g ? (int)rows : g;
 }
 
