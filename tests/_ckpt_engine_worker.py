@@ -42,6 +42,33 @@ def main():
             assert torch.equal(model.state_dict()[k], v), k
     eng.finalize()
     dist.barrier()
+
+    # pinned-host bucket engine with its overlap thread: ranks 0 and 1 are trainer ranks that own alternate buckets,
+    # every rank consumes every bucket; a second version overwrites the first
+    pe = CheckpointEngineRegistry.new("pinned_async", bucket_size=1 << 20, rank=rank, trainer_ranks=[0, 1],
+                                      group=dist.group.WORLD, device="cpu")
+    info = [(k, tuple(v.shape), v.dtype) for k, v in ref.state_dict().items()]
+    buckets = pe.register(info)
+    assert len(buckets) >= 2 and {b.owner for b in buckets} == {0, 1}
+    assert set(pe.host) == ({i for i, b in enumerate(buckets) if b.owner == rank} if rank < 2 else set())
+    for version in (1, 2):
+        src = {k: v + float(version) for k, v in ref.state_dict().items()}
+        if rank < 2:
+            pe.stage(src, version=version)
+        got = {}
+        order = []
+
+        def consume(pairs):
+            order.append(len(pairs))
+            for n, t in pairs:
+                got[n] = t.clone()
+
+        nbytes = pe.publish(consume)
+        assert nbytes == sum(b.nbytes for b in buckets) and len(order) == len(buckets)
+        for k, v in src.items():
+            assert torch.equal(got[k], v), (version, k)
+    pe.finalize()
+    dist.barrier()
     if rank == 0:
         print("CKPT_ENGINE_OK")
     dist.destroy_process_group()

@@ -52,3 +52,40 @@ def test_manager_aborts_and_resumes_replicas_around_the_sync():
     assert log == [("sleep", 0)]
     mgr.add_replicas([Replica(2)])
     assert len(mgr.replicas) == 2
+
+
+def test_pinned_bucket_engine_single_process_and_param_sync():
+    """Bucket planning (alignment, oversize tensors, owners), staging, publishing through the overlap thread, and the
+    engine behind the fully asynchronous pipeline's parameter synchroniser."""
+    import torch
+
+    from verl_b200.checkpoint_engine import PinnedBucketEngine, plan_buckets
+    from verl_b200.experimental.fully_async_policy.param_sync import bucket_sync_fn
+
+    info = [("a", (100, 3), torch.float32), ("big", (5000,), torch.float32), ("b", (7,), torch.bfloat16), ("c", (64,), torch.int64)]
+    buckets = plan_buckets(info, bucket_bytes=4096, num_owners=2)
+    assert [len(b.metas) for b in buckets] == [1, 1, 2] and [b.owner for b in buckets] == [0, 1, 0]
+    assert all(m.offset % 256 == 0 for b in buckets for m in b.metas) and buckets[1].nbytes >= 20000
+    weights = {"a": torch.randn(100, 3), "big": torch.randn(5000), "b": torch.randn(7).bfloat16(), "c": torch.arange(64)}
+    eng = PinnedBucketEngine(bucket_size=4096, device="cpu")
+    eng.register(info)
+    eng.stage(weights, version=5)
+    staged_a = weights["a"].clone()
+    weights["a"].add_(1.0)  # after staging: the published version is the staged one
+    got = {}
+    eng.publish(lambda pairs: got.update({n: t.clone() for n, t in pairs}))
+    assert torch.equal(got["a"], staged_a) and torch.equal(got["big"], weights["big"]) and eng.version == 5
+    assert got["b"].dtype == torch.bfloat16 and torch.equal(got["c"], weights["c"])
+
+    # a consumer that fails surfaces in the caller, and the engine stays usable
+    import pytest
+
+    with pytest.raises(RuntimeError, match="boom"):
+        eng.publish(lambda pairs: (_ for _ in ()).throw(RuntimeError("boom")))
+    eng.publish(lambda pairs: None)
+
+    # as the sync function of the parameter synchroniser
+    loaded = {}
+    fn = bucket_sync_fn(eng, lambda: weights, lambda pairs: loaded.update({n: t.clone() for n, t in pairs}))
+    out = fn(7)
+    assert out["buckets"] == 3 and out["bytes"] > 0 and eng.version == 7 and torch.equal(loaded["a"], weights["a"])

@@ -1,0 +1,45 @@
+
+
+def test_flops_counter_architectures():
+    """Analytical FLOPs per architecture family (reference: verl/utils/flops_counter.py; tests/utils/test_flops_counter.py
+    checks the same families against hand-computed values)."""
+    from types import SimpleNamespace as NS
+
+    from verl_b200.models import preset
+    from verl_b200.utils.flops_counter import FlopsCounter
+
+    # dense: 6 * params * tokens + 12 * sum(s^2) * q_size * layers, computed by hand for a small config
+    c = NS(model_type="llama", hidden_size=64, num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=3,
+           intermediate_size=128, vocab_size=1000)
+    per_layer = 64 * 128 * 3 + 64 * (64 + 2 * 32 + 64)
+    want = 6 * (per_layer * 3 + 1000 * 64 * 2) * 30 + 12 * (10 * 10 + 20 * 20) * 64 * 3
+    got, peak = FlopsCounter(c).estimate_flops([10, 20], 2.0)
+    assert abs(got * 1e12 * 2.0 - want) < 1e-3 * want and peak > 0
+    # Apertus: two MLP matrices instead of three
+    a = NS(**{**vars(c), "model_type": "apertus"})
+    assert FlopsCounter(a).estimate_flops([10, 20], 1.0)[0] < FlopsCounter(c).estimate_flops([10, 20], 1.0)[0]
+    # sliding-window layers cost less than full attention once sequences are longer than the window
+    g = NS(**{**vars(c), "model_type": "gemma3_text", "head_dim": 16, "sliding_window": 8, "sliding_window_pattern": 3})
+    full = NS(**{**vars(g), "sliding_window": None})
+    assert FlopsCounter(g).estimate_flops([64], 1.0)[0] < FlopsCounter(full).estimate_flops([64], 1.0)[0]
+    assert FlopsCounter(g).estimate_flops([4], 1.0)[0] == FlopsCounter(full).estimate_flops([4], 1.0)[0]
+    # DeepSeek-V3: ~37 B active parameters per token
+    ds = NS(model_type="deepseek_v3", hidden_size=7168, num_attention_heads=128, num_hidden_layers=61, q_lora_rank=1536,
+            kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, first_k_dense_replace=3,
+            moe_layer_freq=1, num_experts_per_tok=8, n_shared_experts=1, n_routed_experts=256, moe_intermediate_size=2048,
+            intermediate_size=18432, vocab_size=129280)
+    f1 = FlopsCounter(ds).estimate_flops([1], 1.0)[0] * 1e12 / 6
+    assert 36e9 < f1 < 39e9
+    # GPT-OSS: experts counted by the number a token is routed to
+    o = NS(model_type="gpt_oss", hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+           num_hidden_layers=2, intermediate_size=64, num_local_experts=8, num_experts_per_tok=2, vocab_size=1000,
+           sliding_window=4, layer_types=["sliding_attention", "full_attention"])
+    o4 = NS(**{**vars(o), "num_experts_per_tok": 4})
+    assert FlopsCounter(o4).estimate_flops([16], 1.0)[0] > FlopsCounter(o).estimate_flops([16], 1.0)[0]
+    # VL: the vision tower adds work in proportion to the image patches
+    v = preset("tiny-qwen2-vl")
+    base = FlopsCounter(v).estimate_flops([64], 1.0)[0]
+    assert FlopsCounter(v).estimate_flops([64], 1.0, images_seqlens=[16, 64])[0] > base > 0
+    # MoE preset and an unknown type
+    assert FlopsCounter(preset("tiny-qwen3-moe")).estimate_flops([32], 1.0)[0] > 0
+    assert FlopsCounter(NS(model_type="not-a-model")).estimate_flops([32], 1.0)[0] == 0.0
