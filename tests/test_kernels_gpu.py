@@ -647,3 +647,53 @@ def test_programmatic_dependent_launch_chain_is_bit_identical(T):
     assert torch.isfinite(ref.float()).all()
     for key, val in outs.items():
         assert torch.equal(val, ref), f"{key} differs from the ordinary stream order"
+
+
+def test_kernels_write_inside_their_buffers():
+    """Every output and workspace that the ops allocate sits between canary bands while a battery of kernels runs on
+    tile-edge shapes; no band may change (the sanitizer-free memory-safety check of this code base)."""
+    from verl_b200 import ops
+    from verl_b200.utils.debug.guard_bands import guard_allocations
+
+    torch.manual_seed(5)
+    dev = "cuda"
+    with guard_allocations() as g:
+        for M, N, K in [(1, 72, 64), (127, 136, 200), (129, 264, 72), (300, 4608, 512), (8, 3584, 1024)]:
+            a = torch.randn(M, K, device=dev).bfloat16()
+            w = torch.randn(N, K, device=dev).bfloat16()
+            ops.gemm(a, w)
+            ops.gemm(a, w, out_dtype=torch.float32)
+        for T, H in [(1, 64), (37, 1000), (130, 3584)]:
+            x = torch.randn(T, H, device=dev).bfloat16()
+            wn = torch.randn(H, device=dev).bfloat16()
+            y, r = ops.rmsnorm(x, wn, 1e-6, x)
+            ops.swiglu(torch.randn(T, 2 * 256, device=dev).bfloat16())
+        Hq, Hk, D, bs = 8, 2, 128, 16
+        for T in (1, 33, 200):
+            qkv = torch.randn(T, (Hq + 2 * Hk) * D, device=dev).bfloat16()
+            cos, sin = ops.rope_tables(D, 2048, 10000.0, dev)
+            qkv = ops.rope_qkv(qkv, torch.arange(T, device=dev), cos, sin, Hq, Hk, D)
+            q = qkv[:, : Hq * D].view(T, Hq, D)
+            k = qkv[:, Hq * D : (Hq + Hk) * D].view(T, Hk, D)
+            v = qkv[:, (Hq + Hk) * D :].view(T, Hk, D)
+            cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+            ops.attention_varlen(q.contiguous(), k.contiguous(), v.contiguous(), cu, T, causal=True)
+        B, ctx = 5, 77
+        nblk = (ctx + bs - 1) // bs
+        kc = torch.zeros(B * nblk + 2, Hk, bs, D, device=dev, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        table = torch.arange(B * nblk, device=dev, dtype=torch.int32).reshape(B, nblk)
+        lens = torch.tensor([ctx, 1, 16, 17, 64], device=dev, dtype=torch.int32)
+        knew = torch.randn(B, Hk, D, device=dev).bfloat16()
+        slots = table[torch.arange(B, device=dev), ((lens - 1) // bs).long()].long() * bs + ((lens - 1) % bs).long()
+        ops.kv_cache_write(knew, knew, slots, kc, vc)
+        q1 = torch.randn(B, Hq, D, device=dev).bfloat16()
+        for splits in (1, 3):
+            ops.paged_decode_attention(q1, kc, vc, table, lens, num_splits=splits)
+        logits = torch.randn(7, 1001, device=dev)
+        ops.sample(logits, temperature=torch.ones(7, device=dev), seed=3)
+        h = torch.randn(100, 256, device=dev).bfloat16()
+        wl = (torch.randn(1000, 256, device=dev) * 0.05).bfloat16()
+        ops.lmhead_logprob_entropy(h, wl, torch.randint(0, 1000, (100,), device=dev), 1.0)
+        n_checked = g.check()
+    assert n_checked >= 40

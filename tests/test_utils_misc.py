@@ -43,3 +43,35 @@ def test_flops_counter_architectures():
     # MoE preset and an unknown type
     assert FlopsCounter(preset("tiny-qwen3-moe")).estimate_flops([32], 1.0)[0] > 0
     assert FlopsCounter(NS(model_type="not-a-model")).estimate_flops([32], 1.0)[0] == 0.0
+
+
+def test_guard_bands_catch_writes_outside_an_allocation():
+    """Canary bands around allocations: a write past either edge is reported, writes inside are not."""
+    import pytest
+    import torch
+
+    from verl_b200.utils.debug.guard_bands import GuardError, guard_allocations
+
+    with guard_allocations("cpu") as g:
+        a = torch.empty(10, 3, dtype=torch.float32, device="cpu")
+        b = torch.zeros_like(a)
+        c = torch.zeros((4,), dtype=torch.int64, device="cpu")
+        a.fill_(1.0)
+        b.copy_(a)
+        c += 7
+        assert g.check() == 3 and float(b.sum()) == 30.0 and a.shape == (10, 3) and int(c.sum()) == 28
+    assert torch.empty(2).shape == (2,)  # the torch functions are restored
+    with pytest.raises(GuardError, match="past the end"):
+        with guard_allocations("cpu"):
+            a = torch.empty(8, dtype=torch.float32, device="cpu")
+            torch.as_strided(a, (9,), (1,)).fill_(0.0)  # a "kernel" that writes one element too many
+    with pytest.raises(GuardError, match="before the start"):
+        with guard_allocations("cpu") as g:
+            a = torch.empty(8, dtype=torch.float32, device="cpu")
+            base = g.allocs[0][0]
+            base[g.band - 1] = 0
+    # requests the guard does not handle fall through to torch
+    with guard_allocations("cpu") as g:
+        torch.empty(4, device="meta")
+        torch.empty(4, device="cpu", pin_memory=False)
+        assert g.count == 1
