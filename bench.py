@@ -55,8 +55,8 @@ def parse_args():
                     help="1 = GRPO (the headline); 2 = PPO with a critic of the same architecture, GAE, 32 prompts x 1 "
                          "sample per GPU, even-id reward")
     ap.add_argument("--model", default="qwen2.5-7b")
-    ap.add_argument("--prompts-per-gpu", type=int, default=16)
-    ap.add_argument("--n", type=int, default=8)
+    ap.add_argument("--prompts-per-gpu", type=int, default=None, help="default: 16 (config 1), 32 (config 2)")
+    ap.add_argument("--n", type=int, default=None, help="samples per prompt; default: 8 (config 1), 1 (config 2)")
     ap.add_argument("--min-prompt", type=int, default=256)
     ap.add_argument("--max-prompt", type=int, default=512)
     ap.add_argument("--max-response", type=int, default=1024)
@@ -66,7 +66,12 @@ def parse_args():
     ap.add_argument("--agent-loop", action="store_true",
                     help="variant: rollouts through the agent loops and the token-in / token-out server (not the headline path)")
     ap.add_argument("--lora-rank", type=int, default=0, help="variant: LoRA training (not the headline configuration)")
-    return ap.parse_args()
+    args = ap.parse_args()
+    if args.prompts_per_gpu is None:
+        args.prompts_per_gpu = 16 if args.config == 1 else 32
+    if args.n is None:
+        args.n = 8 if args.config == 1 else 1
+    return args
 
 
 def reference_arm(args):
@@ -303,6 +308,15 @@ def main():
                "timer": "host clock around the same K steps (max over ranks), each step: loader batch -> pinned host -> "
                         "device -> train_step on the device tensors -> loss read back"}
     comm = getattr(worker, "comm_kind", "none")
+    # the last step's rollout times of every rank (a straggler shows here, not in rank 0's breakdown)
+    rt = getattr(worker, "last_rollout_times", {})
+    mine = torch.tensor([rt.get("generate_s", 0.0), rt.get("sleep_s", 0.0), rt.get("engine_step_s", 0.0)], device=dev)
+    per_rank = [torch.zeros_like(mine) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(per_rank, mine)
+    else:
+        per_rank = [mine]
+    per_rank = [[round(float(x), 3) for x in t.tolist()] for t in per_rank]
 
     if rank == 0:
         c = worker.model_config
@@ -327,6 +341,7 @@ def main():
             "breakdown_s": {k.split("/", 1)[1]: round(v, 3) for k, v in last.items() if k.startswith("timing_s/")},
             "rollout_tokens_per_s_per_gpu": last.get("rollout/tokens_per_s"),
             "rollout_engine": {k.split("engine_", 1)[1]: round(v, 3) for k, v in last.items() if k.startswith("rollout/engine_")},
+            "rollout_per_rank": {"columns": ["generate_s", "sleep_s", "engine_step_s"], "rows": per_rank},
             "resync_ms": 1e3 * last.get("timing_s/resync", 0.0),
             "mfu_actor": last.get("perf/mfu/actor"),
             "kept_activation_layers": getattr(worker.actor_engine, "last_kept_layers", 0),

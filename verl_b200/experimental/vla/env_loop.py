@@ -7,9 +7,11 @@ that the trajectory is a token sequence the PPO machinery can train on: per step
 tokens), ``old_log_probs`` and the environment reward; ``to_dataproto`` lays the finished trajectories out as
 [prompt | response] rows with a response mask.
 
-The OpenVLA-OFT vision-language model of the reference is not part of this package (its simulators need a graphics
-stack that this box does not have); any callable ``policy(obs) -> (action_tokens, log_probs)`` drives the loop, and
-``NaiveRolloutRob`` wraps a token-level language model that reads a tokenised state.
+Any callable ``policy(obs) -> (action_tokens, log_probs)`` drives the loop:
+``verl_b200.models.openvla_oft.OpenVLAPolicy`` wraps the OpenVLA-OFT vision-language-action model (images + task
+string in, one parallel-decoded action chunk out), ``NaiveRolloutRob`` wraps a token-level language model that reads a
+tokenised state. The reference's simulators (LIBERO, Isaac) need a graphics stack; ``envs/synthetic_env.py`` has the
+same interface without one.
 """
 
 from __future__ import annotations

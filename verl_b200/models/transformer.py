@@ -37,6 +37,9 @@ class PackedBatch:
     # then [3, T] (multimodal RoPE)
     pixel_values: Optional[torch.Tensor] = None
     image_grid_thw: Optional[torch.Tensor] = None
+    # embeddings computed by the caller ([T, H]; vision-language-action models splice projected image patches and
+    # action placeholders into the token stream themselves): used instead of the embedding lookup
+    inputs_embeds: Optional[torch.Tensor] = None
 
     @classmethod
     def from_padded(cls, input_ids: torch.Tensor, attention_mask: torch.Tensor, position_ids: torch.Tensor | None = None):
@@ -353,6 +356,8 @@ class CausalLM(nn.Module):
 
     # --------------------------------------------------------------- forward
     def embed(self, batch: PackedBatch) -> torch.Tensor:
+        if batch.inputs_embeds is not None:
+            return batch.inputs_embeds.to(self.embed_tokens.weight.dtype)
         h = ops.embedding(batch.input_ids, self.embed_tokens.weight)
         if self.visual is not None and batch.pixel_values is not None and batch.pixel_values.numel():
             # the vision tower's outputs replace the embeddings of the image placeholder tokens, in order

@@ -240,6 +240,7 @@ class NativeRolloutEngine:
         self.gpu_memory_utilization = gpu_memory_utilization
         self._num_blocks_arg = num_blocks
         self.k_cache: list = []
+        self._kv_store = None  # one allocation behind the per-layer K / V views
         self.v_cache: list = []
         self.sched: Optional[Scheduler] = None
         self.requests: dict[int, _Request] = {}
@@ -294,8 +295,12 @@ class NativeRolloutEngine:
         self.num_blocks = int(nb)
         c = self.cfg
         shape = (self.num_blocks, c.num_key_value_heads, self.block_size, c.head_dim)
-        self.k_cache = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in range(c.num_hidden_layers)]
-        self.v_cache = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in range(c.num_hidden_layers)]
+        # ONE allocation for the K and V pages of all layers: freeing it on sleep() is one driver call instead of one
+        # per layer and side (with peer access enabled every cudaFree of a large block is expensive)
+        L = c.num_hidden_layers
+        self._kv_store = torch.zeros((2 * L,) + shape, dtype=self.dtype, device=self.device)
+        self.k_cache = [self._kv_store[i] for i in range(L)]
+        self.v_cache = [self._kv_store[L + i] for i in range(L)]
         self.sched = Scheduler(self.num_blocks, self.block_size, self.max_num_seqs, self.max_num_batched_tokens,
                                self.max_model_len, self.enable_prefix_caching)
         self._graphs = {}
@@ -304,6 +309,7 @@ class NativeRolloutEngine:
         """Free the KV cache (and captured graphs). Running requests must have been drained or aborted."""
         self.abort_all_requests()
         self.k_cache, self.v_cache, self._graphs = [], [], {}
+        self._kv_store = None
         self.sched = None
         if self.on_gpu:
             torch.cuda.empty_cache()

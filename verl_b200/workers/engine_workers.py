@@ -379,8 +379,12 @@ class ActorRolloutRefWorker(_WorkerBase):
                                     "rollout/tokens_per_s": n_tok / max(gen_time, 1e-9)}
         for k_ in ("step_s", "decode_wait_s", "prefill_s", "decode_steps", "steps"):  # where the engine's time went
             out.meta_info["metrics"][f"rollout/engine_{k_}"] = float(eng.stats[k_] - stats0[k_])
+        t_sleep = time.perf_counter()
         if rc.free_cache_engine and not meta.get("keep_cache", False):
             eng.sleep()
+        # this rank's own times (the metrics above travel with the batch and get merged over ranks)
+        self.last_rollout_times = {"generate_s": gen_time, "sleep_s": time.perf_counter() - t_sleep,
+                                   "engine_step_s": float(eng.stats["step_s"] - stats0["step_s"])}
         return out
 
     # ---------------------------------------------------------------- log-probs
