@@ -220,12 +220,19 @@ class Attention(nn.Module):
             self.q_norm = RMSNormWeight(cfg.head_dim, dtype, device)
             self.k_norm = RMSNormWeight(cfg.head_dim, dtype, device)
         self.sp_group = None  # Ulysses sequence-parallel group (set by the engine)
+        self.cp_group = None  # context-parallel group: the batch then holds this rank's two zig-zag chunks
         self.tp_group = None  # training-side tensor parallelism: this module holds 1 / tp of the heads
 
     def _attend(self, q, k, v, batch: PackedBatch):
         """Attention proper. Under Ulysses the inputs are this rank's sequence slice with all heads; an all-to-all
         makes them the whole sequence with a slice of the heads and another one brings the output back
         (verl/models/transformers/monkey_patch.py:87-155)."""
+        if self.cp_group is not None:
+            from ..parallel.context_parallel import cp_attention
+
+            # batch.cu_seqlens / max_seqlen describe ONE chunk of every sequence; q, k, v hold two of them
+            return cp_attention(q.contiguous(), k.contiguous(), v.contiguous(), batch.cu_seqlens, batch.max_seqlen,
+                                self.cp_group)
         if self.sp_group is None:
             return ops.attention_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, causal=True)
         import torch.distributed as dist

@@ -111,6 +111,9 @@ class FSDPEngineConfig(EngineConfig):
     use_orig_params: bool = False
     mixed_precision: Optional[dict] = None
     ulysses_sequence_parallel_size: int = 1
+    # context parallelism: this many consecutive ranks share a micro-batch, each holding two zig-zag chunks of every
+    # sequence (not combinable with Ulysses / tensor / pipeline parallelism)
+    context_parallel_size: int = 1
     entropy_from_logits_with_chunking: bool = False
     use_torch_compile: bool = True
     entropy_checkpointing: bool = False

@@ -170,6 +170,7 @@ class NativeEngine(BaseEngine):
                     layer.mlp.ep_group = self.shard_group
         self.zero.frozen_grad = bool(self._lora_params)
         self._setup_sequence_parallel()
+        self._setup_context_parallel()
         n0 = 1 if (first or tied) else 0
         self._embed_unit = self.zero.units[0] if (first or tied) else None
         self._layer_units = self.zero.units[n0 : n0 + len(m.layers)]
@@ -398,6 +399,26 @@ class NativeEngine(BaseEngine):
         for layer in self.model.layers:
             layer.self_attn.sp_group = self.sp_group
 
+    def _setup_context_parallel(self):
+        """``context_parallel_size`` consecutive ranks share a micro-batch; each holds two zig-zag chunks of every
+        sequence (``parallel/context_parallel.py``; the reference reaches this through Megatron's
+        ``context_parallel_size``, verl/workers/config/engine.py + verl/models/mcore/util.py:25-116). Parameters stay
+        sharded over all ranks, as under Ulysses."""
+        cp = int(_cfg(self.engine_config, "context_parallel_size", 1) or 1)
+        self.cp_size, self.cp_group, self.cp_rank = 1, None, 0
+        if cp <= 1 or self.dp_world <= 1:
+            return
+        if self.sp_size > 1 or self.tp_size > 1 or self.pp_size > 1:
+            raise ValueError("context_parallel_size > 1 cannot be combined with Ulysses, tensor or pipeline parallelism")
+        if getattr(self.model_config, "is_vl", False):
+            raise ValueError("context_parallel_size > 1 is not supported for vision-language models")
+        W, r = self.dp_world, self.dp_rank_all
+        assert W % cp == 0, f"world size {W} is not a multiple of context_parallel_size {cp}"
+        self.cp_group = self._block_groups(cp, strided=False)
+        self.cp_size, self.cp_rank = cp, r % cp
+        for layer in self.model.layers:
+            layer.self_attn.cp_group = self.cp_group
+
     @property
     def model_parallel(self) -> bool:
         """The model itself is split over ranks (tensor or pipeline parallelism), not only its storage."""
@@ -410,12 +431,14 @@ class NativeEngine(BaseEngine):
 
     @property
     def _mp_inner(self) -> int:
-        return max(self.sp_size, 1) * max(self.tp_size, 1)
+        return max(self.sp_size, 1) * max(self.tp_size, 1) * max(getattr(self, "cp_size", 1), 1)
 
     @property
     def mp_group(self):
         """Group of the ranks that work on the same samples (created on first use: a collective)."""
         if self.pp_size <= 1:
+            if getattr(self, "cp_size", 1) > 1:
+                return self.cp_group
             return self.tp_group if self.tp_size > 1 else self.sp_group
         if getattr(self, "_pool_group", None) is None:
             import torch.distributed as dist
@@ -493,6 +516,21 @@ class NativeEngine(BaseEngine):
             ids_l, pos_l, _ = ulysses_pad_and_slice_inputs(batch.input_ids, batch.position_ids, self.sp_size, self.sp_group)
             sp_lo = self.sp_rank * ids_l.shape[0]
             batch = PackedBatch(ids_l, pos_l, batch.cu_seqlens, batch.max_seqlen, total_tokens=T)
+        cp_inv = None
+        if self.cp_size > 1:
+            # this rank's two zig-zag chunks of every sequence, chunk-major; padding rows (index -1) sit past the end
+            # of their sequence, so no real query ever attends to them
+            from ...parallel.context_parallel import cp_local_index
+
+            T = batch.input_ids.shape[0]
+            idx, cu_chunk, offs = cp_local_index(batch.cu_seqlens, self.cp_rank, self.cp_size)
+            held = idx >= 0
+            safe = idx.clamp(min=0)
+            ids_l = torch.where(held, batch.input_ids[safe], torch.zeros_like(safe))
+            pos_l = torch.where(held, batch.position_ids[safe], offs)
+            cp_inv = torch.full((T,), -1, dtype=torch.long, device=idx.device)
+            cp_inv[idx[held]] = torch.nonzero(held, as_tuple=True)[0]
+            batch = PackedBatch(ids_l, pos_l, cu_chunk, int((cu_chunk[1:] - cu_chunk[:-1]).max()), total_tokens=T)
         if self.pp_rank > 0:
             from ...parallel.pipeline import pipe_recv
 
@@ -507,6 +545,12 @@ class NativeEngine(BaseEngine):
             # the LAST n_keep layers keep their activations: their memory is the first to be freed in the backward
             hidden, residual = unit_call(z, unit, lambda h, r, layer=layer: layer(h, r, batch, rope), hidden, residual,
                                          keep_activations=i >= n_layers - n_keep)
+        if cp_inv is not None:
+            all_rows = rows if rows is not None else torch.arange(batch.total_tokens, device=hidden.device)
+            loc = cp_inv[all_rows]
+            mine = loc >= 0
+            self._sp_sel = (mine, all_rows.numel())
+            return hidden[loc[mine]], residual[loc[mine]]
         if self.sp_size > 1:
             # keep the rows that live in this rank's slice; _sp_merge puts the per-row results back together
             n_l = hidden.shape[0]
@@ -573,14 +617,15 @@ class NativeEngine(BaseEngine):
     def _sp_merge(self, out):
         """Scatter this rank's per-row results into the full row order and sum over the sequence-parallel group
         (every row is owned by exactly one rank). The backward keeps the gradient of the rows this rank owns."""
-        if self.sp_size <= 1:
+        if self.sp_size <= 1 and self.cp_size <= 1:
             return out
         mine, n = self._sp_sel
+        group = self.cp_group if self.cp_size > 1 else self.sp_group
 
         def one(t):
             full = torch.zeros((n,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
             full = full.index_put((torch.nonzero(mine, as_tuple=True)[0],), t)
-            return _SumOverGroup.apply(full, self.sp_group)
+            return _SumOverGroup.apply(full, group)
 
         return tuple(one(t) if isinstance(t, torch.Tensor) else t for t in out) if isinstance(out, tuple) else one(out)
 
@@ -606,7 +651,7 @@ class NativeEngine(BaseEngine):
         if isinstance(hidden, str):  # an earlier pipeline stage: the residual stream went to the next stage
             return self._pp_share((0, 0), residual, rows.numel())
 
-        if self.sp_size > 1:
+        if self.sp_size > 1 or self.cp_size > 1:
             labels = labels[self._sp_sel[0]]
 
         def head(h, r):

@@ -92,6 +92,7 @@ class _WorkerBase(Worker):
         sp = max(sp, int(_cfg(cfg, "ulysses_sequence_parallel_size", 1) or 1))
         if eng_cfg is not None:
             sp *= int(_cfg(eng_cfg, "tensor_model_parallel_size", 1) or 1) * int(_cfg(eng_cfg, "pipeline_model_parallel_size", 1) or 1)
+            sp *= int(_cfg(eng_cfg, "context_parallel_size", 1) or 1)
         dp = max(self.world // max(sp, 1), 1)
         mini = int(getattr(cfg, mini_key)) * n // dp
         assert mini > 0, f"{mini_key} {getattr(cfg, mini_key)} * n {n} must be >= data-parallel size {dp}"
@@ -155,12 +156,13 @@ class ActorRolloutRefWorker(_WorkerBase):
         # (dispatch of verl/single_controller/base/decorator.py:297-328, registration of fsdp_workers.py:146-273)
         def mesh_of(c):
             """(data-parallel rank, reports results) of this rank under the engine's layout: pipeline stages are
-            consecutive blocks of ranks; inside a block ``tp x sp`` consecutive ranks share their samples; the last
+            consecutive blocks of ranks; inside a block ``tp x sp x cp`` consecutive ranks share their samples; the last
             stage's first rank of such a group reports."""
             if c is None:
                 return self.dp_rank, True
             ec = _cfg(c, "fsdp_config", None)
-            inner = (int(_cfg(ec, "ulysses_sequence_parallel_size", 1) or 1) * int(_cfg(ec, "tensor_model_parallel_size", 1) or 1))
+            inner = (int(_cfg(ec, "ulysses_sequence_parallel_size", 1) or 1) * int(_cfg(ec, "tensor_model_parallel_size", 1) or 1)
+                     * int(_cfg(ec, "context_parallel_size", 1) or 1))
             pp = int(_cfg(ec, "pipeline_model_parallel_size", 1) or 1)
             S = max(self.world // pp, 1)
             local = self.dp_rank % S
