@@ -62,11 +62,21 @@ def _digest(path: Path, extra: str) -> str:
     return h.hexdigest()
 
 
-def _compile_one(src: Path, verbose: bool, ptxas_verbose: bool) -> Path:
+# Build flavours: "" = the library every run uses; "jitter" = the same sources with -DVB_JITTER=1 (blocks of the
+# communication kernels and of the GEMM sleep a pseudo-random time before they start), for race hunting in tests.
+FLAVOUR_FLAGS = {"": [], "jitter": ["-DVB_JITTER=1"]}
+
+
+def lib_path(flavour: str = "") -> Path:
+    return LIB_DIR / (f"libverl_b200_{flavour}.so" if flavour else "libverl_b200.so")
+
+
+def _compile_one(src: Path, verbose: bool, ptxas_verbose: bool, flavour: str = "") -> Path:
     is_cu = src.suffix == ".cu"
-    flags = NVCC_FLAGS if is_cu else CXX_FLAGS
-    obj = OBJ_DIR / (src.name + ".o")
-    stamp = OBJ_DIR / (src.name + ".sha1")
+    flags = (NVCC_FLAGS if is_cu else CXX_FLAGS) + FLAVOUR_FLAGS[flavour]
+    obj_dir = OBJ_DIR if not flavour else OBJ_DIR.parent / f"build_{flavour}"
+    obj = obj_dir / (src.name + ".o")
+    stamp = obj_dir / (src.name + ".sha1")
     dig = _digest(src, " ".join(flags))
     if obj.exists() and stamp.exists() and stamp.read_text() == dig and not ptxas_verbose:
         return obj
@@ -88,27 +98,30 @@ def _compile_one(src: Path, verbose: bool, ptxas_verbose: bool) -> Path:
     return obj
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_verbose: bool = False) -> Path:
-    """Compile all native sources and link the shared library. Returns its path."""
-    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, ptxas_verbose: bool = False, flavour: str = "") -> Path:
+    """Compile all native sources and link the shared library (of the given flavour). Returns its path."""
+    obj_dir = OBJ_DIR if not flavour else OBJ_DIR.parent / f"build_{flavour}"
+    out = lib_path(flavour)
+    obj_dir.mkdir(parents=True, exist_ok=True)
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     if force:
-        for f in OBJ_DIR.glob("*.sha1"):
+        for f in obj_dir.glob("*.sha1"):
             f.unlink()
     cu, cpp = _sources()
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
-        objs = list(ex.map(lambda s: _compile_one(s, verbose, ptxas_verbose), cu + cpp))
+        objs = list(ex.map(lambda s: _compile_one(s, verbose, ptxas_verbose, flavour), cu + cpp))
     newest = max(o.stat().st_mtime for o in objs)
-    if force or not LIB_PATH.exists() or LIB_PATH.stat().st_mtime < newest:
-        cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lcudart", "-lpthread"]
+    if force or not out.exists() or out.stat().st_mtime < newest:
+        cmd = [_nvcc(), "-shared", "-o", str(out), *map(str, objs), "-lcudart", "-lpthread"]
         if verbose:
             print(" ".join(cmd), flush=True)
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed\n{res.stdout}\n{res.stderr}")
-    return LIB_PATH
+    return out
 
 
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv, ptxas_verbose="--ptxas" in sys.argv)
+    p = build(force="--force" in sys.argv, verbose="-v" in sys.argv, ptxas_verbose="--ptxas" in sys.argv,
+              flavour="jitter" if "--jitter" in sys.argv else "")
     print(p)

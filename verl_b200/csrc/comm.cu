@@ -81,6 +81,7 @@ __device__ bool barrier_all_ranks(const PeerPtrs& pads, int rank, int world, int
 }
 
 __global__ void peer_barrier_kernel(PeerPtrs pads, int rank, int world, int channel, uint32_t epoch, int* status) {
+  vb_jitter(1u);
   barrier_all_ranks(pads, rank, world, channel, epoch, status);
 }
 
@@ -116,6 +117,7 @@ __device__ bool grid_enter(const PeerPtrs& pads, int rank, int world, int channe
 __global__ void peer_all_gather_kernel(PeerPtrs srcs, PeerPtrs pads, long long src_off16, uint4* __restrict__ out,
                                        long long shard16, int rank, int world, int channel, uint32_t epoch,
                                        uint32_t* gate, int* status) {
+  vb_jitter(2u);
   if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
   const long long total = shard16 * world;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -137,6 +139,7 @@ template <int W, int U>
 __global__ void peer_reduce_scatter_add_kernel(PeerPtrs fulls, PeerPtrs pads, long long full_off4,
                                                float4* __restrict__ dst, long long shard4, float scale, int rank,
                                                int world, int channel, uint32_t epoch, uint32_t* gate, int* status) {
+  vb_jitter(3u);
   if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long base = full_off4 + (long long)rank * shard4;
@@ -175,6 +178,7 @@ __global__ void peer_reduce_scatter_add_generic_kernel(PeerPtrs fulls, PeerPtrs 
                                                        float4* __restrict__ dst, long long shard4, float scale,
                                                        int rank, int world, int channel, uint32_t epoch,
                                                        uint32_t* gate, int* status) {
+  vb_jitter(4u);
   if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < shard4; i += stride) {
@@ -197,6 +201,7 @@ template <typename T>
 __global__ void peer_sum_slots_kernel(const T* __restrict__ slots, PeerPtrs pads, T* __restrict__ out,
                                       const T* __restrict__ residual, long long n, int rank, int world, int channel,
                                       uint32_t epoch, uint32_t* gate, int* status) {
+  vb_jitter(5u);
   if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
   constexpr int V = 16 / sizeof(T);
   const long long n_vec = n / V;
@@ -229,6 +234,7 @@ __global__ void peer_sum_slots_kernel(const T* __restrict__ slots, PeerPtrs pads
 __global__ void nvls_reduce_scatter_add_kernel(const float* mc_base, PeerPtrs pads, long long full_off4,
                                                float4* __restrict__ dst, long long shard4, float scale, int rank,
                                                int world, int channel, uint32_t epoch, uint32_t* gate, int* status) {
+  vb_jitter(6u);
   if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const float4* src = reinterpret_cast<const float4*>(mc_base) + full_off4 + (long long)rank * shard4;
@@ -276,6 +282,7 @@ __global__ void tp_allreduce_rmsnorm_kernel(PeerPtrs partials, PeerPtrs pads, lo
                                             __nv_bfloat16* __restrict__ residual_out, int rows, int H, float eps, int rank,
                                             int world, int channel, uint32_t* epoch_ctr, uint32_t* done_ctr,
                                             uint32_t* gate, int* status) {
+  vb_jitter(7u);
   extern __shared__ uint4 row_s[];  // H / 8 vectors: the summed row as bf16
   __shared__ float red_s[32];
   __shared__ uint32_t epoch_s;
@@ -374,6 +381,7 @@ struct A2AParams {
 __global__ void peer_a2a_chunks_kernel(PeerPtrs srcs, PeerPtrs pads, long long src_off16, uint4* __restrict__ dst,
                                        A2AParams q, int rank, int world, int channel, uint32_t epoch, uint32_t* gate,
                                        int* status) {
+  vb_jitter(8u);
   if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
   const long long per_rank = (long long)q.rows * q.chunk16;
   const long long total = per_rank * world;
@@ -413,6 +421,7 @@ struct Segment {
 __global__ void peer_segment_copy_kernel(PeerPtrs srcs, PeerPtrs pads, const Segment* __restrict__ segs, int nseg,
                                          uint8_t* __restrict__ dst_base, int rank, int world, int channel,
                                          uint32_t epoch, uint32_t* gate, int* status) {
+  vb_jitter(9u);
   if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
   for (int s = blockIdx.x; s < nseg; s += gridDim.x) {
     const Segment sg = segs[s];
@@ -556,6 +565,7 @@ extern "C" int vb_peer_sum_slots(const void* slots, const void* const* pads, voi
 __global__ void moe_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ top_i, int pairs, int k,
                                     int h16, int e_local, const int* __restrict__ base, int* __restrict__ cursor,
                                     PeerPtrs recv, int* __restrict__ where, long long cap_rows, int* status) {
+  vb_jitter(10u);
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   for (int pair = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; pair < pairs; pair += warps) {
@@ -579,6 +589,7 @@ __global__ void moe_dispatch_kernel(const uint4* __restrict__ x, const int* __re
 
 // Histogram of this rank's routing (one block): hist[e] = number of (token, slot) pairs routed to expert e.
 __global__ void moe_hist_kernel(const int* __restrict__ top_i, int pairs, int num_experts, int* __restrict__ hist) {
+  vb_jitter(11u);
   extern __shared__ int h_s[];
   for (int e = threadIdx.x; e < num_experts; e += blockDim.x) h_s[e] = 0;
   __syncthreads();
@@ -596,6 +607,7 @@ __global__ void moe_hist_kernel(const int* __restrict__ top_i, int pairs, int nu
 __global__ void moe_layout_kernel(const int* __restrict__ hist_all, int hist_stride, int num_experts, int e_local,
                                   int rank, int world, int* __restrict__ base, int* __restrict__ expert_off,
                                   int* __restrict__ blk_expert, int blocks, int* __restrict__ cursor) {
+  vb_jitter(12u);
   extern __shared__ int l_s[];
   int* padded = l_s;                 // [E]
   int* off = l_s + num_experts;      // [E] owner-local first row of every expert
@@ -654,6 +666,7 @@ __global__ void moe_combine_kernel(PeerPtrs y, PeerPtrs pads, const int* __restr
                                    const float* __restrict__ top_w, const int* __restrict__ where, int tokens, int k,
                                    int h16, int e_local, uint4* __restrict__ out, int rank, int world, int channel,
                                    uint32_t epoch, uint32_t* gate, int* status) {
+  vb_jitter(13u);
   if (!grid_enter(pads, rank, world, channel, epoch, gate, status)) return;
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;

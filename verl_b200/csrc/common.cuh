@@ -52,6 +52,24 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
+// Launch-order jitter for race hunting (build flavour -DVB_JITTER=1, never the default library): every block sleeps a
+// pseudo-random time of up to ~16 us before it starts, so that blocks and ranks reach their flags, barriers and
+// peer loads in orders that a quiet machine never produces. Results must not change.
+#ifdef VB_JITTER
+__device__ __forceinline__ void vb_jitter(uint32_t salt) {
+  if (threadIdx.x == 0) {
+    uint32_t h = (blockIdx.x * 2654435761u) ^ (uint32_t)globaltimer_ns() ^ (salt * 0x9E3779B9u);
+    h ^= h >> 15;
+    h *= 0x2c1b3c6du;
+    h ^= h >> 12;
+    __nanosleep(h & 0x3fffu);
+  }
+  __syncthreads();
+}
+#else
+__device__ __forceinline__ void vb_jitter(uint32_t) {}
+#endif
+
 // ---------------------------------------------------------------------------
 // Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute may start while
 // its predecessor in the stream still runs: what it does before pdl_wait() (barrier init, TMEM allocation,

@@ -291,6 +291,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const Sched sched(p, BN, EPI == EPI_LSE);
+  vb_jitter(100u);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; ++s) {

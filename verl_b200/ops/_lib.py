@@ -78,15 +78,19 @@ def lib_path() -> Path:
 
 def load(build_if_missing: bool = True):
     """Load (building first if necessary) and return the ctypes handle."""
-    global _LIB
+    global _LIB, _LIB_PATH
     if _LIB is not None:
         return _LIB
+    flavour = "jitter" if os.environ.get("VERL_B200_JITTER") == "1" else ""
+    if flavour:  # the race-hunting build: blocks of the communication kernels start after pseudo-random sleeps
+        _LIB_PATH = _LIB_PATH.with_name(f"libverl_b200_{flavour}.so")
     if not _LIB_PATH.exists():
         if not build_if_missing:
-            raise NativeLibraryError(f"native library missing: {_LIB_PATH}; run `python -m verl_b200._build`")
+            raise NativeLibraryError(f"native library missing: {_LIB_PATH}; run `python -m verl_b200._build`"
+                                     + (" --jitter" if flavour else ""))
         from verl_b200 import _build
 
-        _build.build()
+        _build.build(flavour=flavour)
     lib = ctypes.CDLL(str(_LIB_PATH), mode=os.RTLD_NOW | os.RTLD_GLOBAL)
     for name, (argtypes, restype) in _SIGS.items():
         try:
