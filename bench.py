@@ -356,7 +356,10 @@ def main():
         from verl_b200.utils.profiler.kernel_breakdown import kernel_breakdown
 
         b = trainer._last_batch
-        res = {"n_gpus": world, "note": "device times under the torch profiler: shares only"}
+        # with programmatic dependent launch a kernel's recorded duration includes its wait for the kernel before it;
+        # the breakdown pass runs in plain stream order so that per-kernel times add up
+        _lib.set_pdl(False)
+        res = {"n_gpus": world, "note": "device times under the torch profiler: shares only; plain stream order"}
         res["update_actor"] = kernel_breakdown(lambda: trainer.actor_rollout_wg.update_actor(b))
         res["compute_log_prob"] = kernel_breakdown(lambda: trainer.actor_rollout_wg.compute_log_prob(b))
         if rank == 0:

@@ -6,8 +6,10 @@
 Role of verl/model_merger/ (``merge|test --backend fsdp|megatron --local_dir --target_dir``): the FSDP merger
 there concatenates DTensor shards by placement; here every rank file stores, per parameter, the slice of the flat
 unit shard that belongs to it (``model_world_size_{W}_rank_{r}.pt``), so merging is a scatter by (start, length).
-``--backend megatron`` is accepted for CLI compatibility and handled the same way: this framework has one
-checkpoint format.
+Directories written by the reference itself (torch FSDP: per-parameter DTensor / ShardedTensor shards in the same
+file names) are recognised by their content and merged by placement, so the CLI serves both. ``--backend megatron``
+is accepted for CLI compatibility and handled the same way: the engine writes one format whatever its parallel layout
+(tensor-, pipeline- and expert-parallel runs export merged tensors).
 """
 
 from __future__ import annotations
