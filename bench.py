@@ -66,6 +66,8 @@ def parse_args():
     ap.add_argument("--agent-loop", action="store_true",
                     help="variant: rollouts through the agent loops and the token-in / token-out server (not the headline path)")
     ap.add_argument("--lora-rank", type=int, default=0, help="variant: LoRA training (not the headline configuration)")
+    ap.add_argument("--prefix-sharing", action="store_true",
+                    help="variant: the log-prob passes evaluate each prompt once for its n samples (use_prefix_grouper)")
     args = ap.parse_args()
     if args.prompts_per_gpu is None:
         args.prompts_per_gpu = 16 if args.config == 1 else 32
@@ -184,6 +186,8 @@ def build_config(args, world: int):
     if args.agent_loop:
         ov += ["actor_rollout_ref.rollout.agent.use_agent_loop=true", "actor_rollout_ref.rollout.agent.num_workers=4",
                "data.return_raw_chat=true"]
+    if args.prefix_sharing:
+        ov.append("actor_rollout_ref.actor.use_prefix_grouper=true")
     if args.lora_rank:
         ov += [f"actor_rollout_ref.model.lora_rank={args.lora_rank}", "actor_rollout_ref.model.lora_alpha=32"]
     return compose("ppo_trainer", ov)
@@ -328,7 +332,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic prompts (uniform ids), random-init weights", "impl": "ours",
             "config": {"model": (args.model if not args.layers else f"{args.model}-REDUCED-{args.layers}L")
-                       + ("+agent-loop-rollout" if args.agent_loop else "") + (f"+lora{args.lora_rank}" if args.lora_rank else ""),
+                       + ("+agent-loop-rollout" if args.agent_loop else "") + (f"+lora{args.lora_rank}" if args.lora_rank else "") + ("+prefix-sharing-logprob" if args.prefix_sharing else ""),
                        "benchmark_config": args.config, "layers": c.num_hidden_layers, "hidden": c.hidden_size, "vocab": c.vocab_size,
                        "global_batch": args.prompts_per_gpu * world * args.n, "prompts": args.prompts_per_gpu * world,
                        "n_samples": args.n, "seq_len": args.max_prompt + args.max_response,

@@ -1,0 +1,70 @@
+"""Shared-prefix evaluation (``use_prefix_grouper``): every distinct prompt of a micro-batch is evaluated once and its
+n responses attend to its keys; log-probs and entropies equal those of the plain layout that repeats the prompt."""
+
+import torch
+
+
+def _batch(n_prompts=3, n=4, P=12, R=9, vocab=1500, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    B = n_prompts * n
+    ids = torch.zeros(B, P + R, dtype=torch.long)
+    mask = torch.zeros(B, P + R, dtype=torch.long)
+    for p in range(n_prompts):
+        plen = int(torch.randint(3, P + 1, (1,), generator=g))
+        prompt = torch.randint(5, vocab, (plen,), generator=g)
+        for s in range(n):
+            i = p * n + s
+            rlen = int(torch.randint(1, R + 1, (1,), generator=g))
+            ids[i, P - plen : P] = prompt
+            mask[i, P - plen : P] = 1
+            ids[i, P : P + rlen] = torch.randint(5, vocab, (rlen,), generator=g)
+            mask[i, P : P + rlen] = 1
+    pos = (mask.cumsum(-1) - 1).clamp(min=0)
+    return ids, mask, pos, R
+
+
+def test_shared_prefix_layout():
+    from verl_b200.trainer.ppo.prefix_grouper_utils import shared_prefix_batch
+
+    ids, mask, pos, R = _batch()
+    packed, rows, labels, bj, saving = shared_prefix_batch(ids, mask, R)
+    ps = packed.prefix_share
+    P = ids.shape[1] - R
+    n_prompt = sum(int(mask[i, :P].sum()) for i in range(0, 12, 4))
+    assert ps["n_prompt_tokens"] == n_prompt and packed.input_ids.numel() == n_prompt + int(mask[:, P:].sum())
+    assert 0.3 < saving < 0.8 and rows.numel() == labels.numel() == bj.shape[0] == int(mask[:, P:].sum())
+    # the row that predicts a response's first token is the last token of its prompt (stored once per group)
+    first = rows[bj[:, 1] == 0]
+    assert first.numel() == 12 and len(set(first.tolist())) == 3 and int(first.max()) < n_prompt
+    # keys of a response = its prompt's positions, then its own
+    lens_k = (ps["cu_k"][1:] - ps["cu_k"][:-1]).tolist()
+    assert lens_k == [int(mask[i].sum()) for i in range(12)]
+    assert torch.equal(packed.input_ids[rows[bj[:, 1] > 0] + 1], labels[bj[:, 1] > 0])
+
+
+def test_actor_log_probs_with_shared_prefix_equal_the_plain_layout():
+    from verl_b200 import DataProto
+    from verl_b200.models import preset
+    from verl_b200.workers.actor.dp_actor import DataParallelPPOActor
+    from verl_b200.workers.config import FSDPActorConfig
+    from verl_b200.workers.engine.native import NativeEngine
+
+    class C(dict):
+        __getattr__ = dict.get
+
+    for name in ("tiny-qwen2", "tiny-qwen3-moe"):
+        eng = NativeEngine(preset(name), C(), C(lr=1e-3, clip_grad=1.0), device="cpu", seed=3).initialize()
+        ids, mask, pos, R = _batch(seed=4)
+        data = DataProto.from_dict({"input_ids": ids, "attention_mask": mask, "position_ids": pos, "responses": ids[:, -R:],
+                                    "response_mask": mask[:, -R:]}, meta_info={"temperature": 0.8, "micro_batch_size": 8})
+        res = {}
+        for flag in (False, True):
+            actor = DataParallelPPOActor(FSDPActorConfig(ppo_mini_batch_size=12, ppo_micro_batch_size_per_gpu=8,
+                                                         use_prefix_grouper=flag), eng)
+            res[flag] = actor.compute_log_prob(data, calculate_entropy=True)
+            if flag:  # micro-batches of 8 and 4 samples: two whole groups, then one
+                assert 0.2 < actor.last_prefix_saving < 0.8
+        m = mask[:, -R:].bool()
+        torch.testing.assert_close(res[True][0][m], res[False][0][m], atol=2e-5, rtol=1e-4)
+        torch.testing.assert_close(res[True][1][m], res[False][1][m], atol=2e-5, rtol=1e-4)
+        assert float(res[True][0][~m].abs().sum()) == 0.0

@@ -40,6 +40,10 @@ class PackedBatch:
     # embeddings computed by the caller ([T, H]; vision-language-action models splice projected image patches and
     # action placeholders into the token stream themselves): used instead of the embedding lookup
     inputs_embeds: Optional[torch.Tensor] = None
+    # shared-prefix evaluation (forward only): the stream holds every distinct prompt ONCE, then all responses; a
+    # response attends to its prompt's keys and to itself. dict(n_prompt_tokens, cu_prompt, max_prompt, cu_resp,
+    # max_resp, k_gather [sum(prompt + response lengths)], cu_k, max_k): see trainer/ppo/prefix_grouper_utils.py
+    prefix_share: Optional[dict] = None
 
     @classmethod
     def from_padded(cls, input_ids: torch.Tensor, attention_mask: torch.Tensor, position_ids: torch.Tensor | None = None):
@@ -227,6 +231,8 @@ class Attention(nn.Module):
         """Attention proper. Under Ulysses the inputs are this rank's sequence slice with all heads; an all-to-all
         makes them the whole sequence with a slice of the heads and another one brings the output back
         (verl/models/transformers/monkey_patch.py:87-155)."""
+        if batch.prefix_share is not None:
+            return self._attend_shared_prefix(q, k, v, batch.prefix_share)
         if self.cp_group is not None:
             from ..parallel.context_parallel import cp_attention
 
@@ -251,6 +257,20 @@ class Attention(nn.Module):
         v = gather_seq_scatter_heads(v, 0, 1, total, self.sp_group)
         o = ops.attention_varlen(q.contiguous(), k.contiguous(), v.contiguous(), batch.cu_seqlens, batch.max_seqlen, causal=True)
         return gather_heads_scatter_seq(o, 1, 0, self.sp_group)
+
+    def _attend_shared_prefix(self, q, k, v, ps: dict):
+        """Prompts (each stored once) attend to themselves causally; every response attends to the keys of ITS prompt
+        followed by its own keys, causally aligned at the end (the prefix-sharing attention of the reference's
+        ``use_prefix_grouper`` path, verl/trainer/ppo/prefix_grouper_utils.py). Forward only."""
+        assert not (torch.is_grad_enabled() and q.requires_grad), "shared-prefix attention is a forward-only path"
+        assert self.sp_group is None and self.cp_group is None, "shared-prefix attention does not combine with SP / CP"
+        from ..rollout.engine import _varlen_attention_kv
+
+        Tp = ps["n_prompt_tokens"]
+        out_p = ops.attention_varlen(q[:Tp], k[:Tp], v[:Tp], ps["cu_prompt"], ps["max_prompt"], causal=True)
+        k_cat, v_cat = k.index_select(0, ps["k_gather"]), v.index_select(0, ps["k_gather"])
+        out_r = _varlen_attention_kv(q[Tp:], k_cat, v_cat, ps["cu_resp"], ps["cu_k"], ps["max_resp"], ps["max_k"])
+        return torch.cat([out_p, out_r.to(out_p.dtype)], dim=0)
 
     def forward(self, x, batch: PackedBatch, rope):
         cfg = self.cfg

@@ -7,9 +7,12 @@ prompt tokens) and ``pack_with_shared_prefix`` lays a group out as ONE packed se
 prompt) and a segment table for a prefix-sharing attention mask: response i attends to the prompt and to itself.
 ``unpack_shared_prefix`` scatters per-token results of the packed stream back to ``[B, R]``.
 
-The native varlen attention kernel does not take a prefix-sharing mask; the engine falls back to repeating the
-prompt unless ``use_prefix_grouper`` finds an attention backend for it, so these helpers are currently the data
-layout half of the feature (and are exact for models evaluated with :func:`prefix_shared_attention_reference`).
+Attention backend: :func:`shared_prefix_batch` lays a micro-batch out as ``[distinct prompts..., responses...]`` and
+``models/transformer.py::Attention._attend_shared_prefix`` evaluates it with the ordinary varlen kernels (prompts
+causally; every response against its prompt's keys followed by its own, through the key-stream form of the forward
+kernel). That path is FORWARD ONLY (``compute_log_prob`` of the actor and of the reference policy with
+``use_prefix_grouper``): the backward kernels take one boundary table for queries and keys, so ``update_policy``
+keeps repeating the prompt.
 """
 
 from __future__ import annotations
@@ -99,3 +102,59 @@ def prefix_saving(groups: list[PrefixGroup]) -> float:
     repeated = sum(len(g.rows) * g.prompt.numel() + sum(r.numel() for r in g.responses) for g in groups)
     packed = sum(g.prompt.numel() + sum(r.numel() for r in g.responses) for g in groups)
     return 1.0 - packed / max(repeated, 1)
+
+
+def shared_prefix_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, response_length: int):
+    """Left-padded prompts / right-padded responses ``[b, P + R]`` -> the shared-prefix packed stream.
+
+    Returns ``(packed, rows, labels, bj, saving)`` with the meaning of ``NativeEngine.response_rows``: ``rows[i]`` is
+    the packed position whose hidden state predicts response token ``bj[i] = (sample, j)`` (the LAST prompt token of
+    the sample's group for j = 0), ``labels[i]`` that token. ``saving`` = fraction of tokens not evaluated. Samples with
+    identical prompt tokens form a group; the positions of a response continue after its prompt."""
+    from ...models.transformer import PackedBatch
+
+    dev = input_ids.device
+    b, S = input_ids.shape
+    P = S - response_length
+    ids_c, mask_c = input_ids.cpu(), attention_mask.cpu().bool()
+    groups: dict = {}
+    prompts = []
+    for i in range(b):
+        pt = ids_c[i, :P][mask_c[i, :P]]
+        key = pt.numpy().tobytes()
+        if key not in groups:
+            groups[key] = len(prompts)
+            prompts.append(pt)
+    gid = [groups[ids_c[i, :P][mask_c[i, :P]].numpy().tobytes()] for i in range(b)]
+    plen = [int(p.numel()) for p in prompts]
+    p_off = [0]
+    for n in plen:
+        p_off.append(p_off[-1] + n)
+    Tp = p_off[-1]
+    resp = [ids_c[i, P:][mask_c[i, P:]] for i in range(b)]
+    rlen = [int(r.numel()) for r in resp]
+    r_off = [0]
+    for n in rlen:
+        r_off.append(r_off[-1] + n)
+    ids = torch.cat(prompts + resp)
+    pos = torch.cat([torch.arange(n) for n in plen] + [torch.arange(rlen[i]) + plen[gid[i]] for i in range(b)])
+    k_gather = torch.cat([torch.cat([torch.arange(plen[gid[i]]) + p_off[gid[i]], torch.arange(rlen[i]) + Tp + r_off[i]])
+                          for i in range(b)]) if b else torch.zeros(0, dtype=torch.long)
+    klen = [plen[gid[i]] + rlen[i] for i in range(b)]
+    cu = lambda lens: torch.tensor([0] + list(torch.tensor(lens, dtype=torch.long).cumsum(0).tolist()) if lens else [0], dtype=torch.int32)  # noqa: E731
+    share = {"n_prompt_tokens": Tp, "cu_prompt": cu(plen).to(dev), "max_prompt": max(plen) if plen else 0,
+             "cu_resp": cu(rlen).to(dev), "max_resp": max(rlen) if rlen else 0, "k_gather": k_gather.to(dev),
+             "cu_k": cu(klen).to(dev), "max_k": max(klen) if klen else 0}
+    packed = PackedBatch(ids.to(dev), pos.to(dev), torch.cat([cu(plen), cu(rlen)[1:] + Tp]).to(dev),
+                         max(max(plen, default=0), max(rlen, default=0)), prefix_share=share)
+    rows, labels, bj = [], [], []
+    for i in range(b):
+        for j in range(rlen[i]):
+            rows.append(p_off[gid[i]] + plen[gid[i]] - 1 if j == 0 else Tp + r_off[i] + j - 1)
+            bj.append((i, j))
+        labels.append(resp[i])
+    rows_t = torch.tensor(rows, dtype=torch.long, device=dev)
+    bj_t = torch.tensor(bj, dtype=torch.long, device=dev).view(-1, 2)
+    total_plain = sum(plen[gid[i]] + rlen[i] for i in range(b))
+    saving = 1.0 - (Tp + r_off[-1]) / max(total_plain, 1)
+    return packed, rows_t, (torch.cat(labels).to(dev) if labels else torch.zeros(0, dtype=torch.long, device=dev)), bj_t, saving

@@ -34,6 +34,9 @@ class DataParallelPPOActor:
         self.engine = engine
         self.device = engine.device
         self.use_fused_loss = self.device.type == "cuda"
+        # forward-only passes evaluate every distinct prompt of a micro-batch once (trainer/ppo/prefix_grouper_utils.py)
+        self.use_prefix_grouper = bool(_cfg(config, "use_prefix_grouper", False))
+        self.last_prefix_saving = 0.0
 
     # ------------------------------------------------------------------ forward
     def _forward_micro_batch(self, micro: DataProto, temperature: float, calculate_entropy: bool):
@@ -47,7 +50,17 @@ class DataParallelPPOActor:
             # mrope layouts carry [b, 3, S] or [b, 4, S] (row 0 = text positions, rows 1..3 = temporal / height / width)
             pos = pos[:, -3:] if vl else pos[:, 0]
         R = b["responses"].shape[-1]
-        packed, rows, labels, bj = NativeEngine.response_rows(input_ids, mask, R, pos)
+        e = self.engine
+        if (self.use_prefix_grouper and not torch.is_grad_enabled() and not vl
+                and getattr(e, "sp_size", 1) <= 1 and getattr(e, "cp_size", 1) <= 1 and getattr(e, "pp_size", 1) <= 1):
+            # forward-only evaluation: every distinct prompt of the micro-batch is evaluated once, its n responses
+            # attend to its keys (update_policy keeps the plain layout: the backward kernels have no such form)
+            from ...trainer.ppo.prefix_grouper_utils import shared_prefix_batch
+
+            packed, rows, labels, bj, saving = shared_prefix_batch(input_ids, mask, R)
+            self.last_prefix_saving = saving
+        else:
+            packed, rows, labels, bj = NativeEngine.response_rows(input_ids, mask, R, pos)
         mm = micro.non_tensor_batch.get("multi_modal_inputs") if vl else None
         if mm is not None:
             from ...utils.model import extract_multi_modal_inputs

@@ -216,6 +216,8 @@ class ActorRolloutRefWorker(_WorkerBase):
             self.ref_engine = NativeEngine(model_cfg, ref_eng_cfg, None, device=str(self.device), group=group, seed=seed,
                                            state_dict=state, trainable=False, comm=comm).initialize()
             self.ref_policy = DataParallelPPOActor(self.ref_cfg or self.actor_cfg, self.ref_engine)
+            if self.actor_cfg is not None:  # the reference policy evaluates the same batches: same layout choice
+                self.ref_policy.use_prefix_grouper = bool(_cfg(self.actor_cfg, "use_prefix_grouper", False))
         if self._is_rollout:
             self._build_rollout(model_cfg, state, seed)
         if self.device.type == "cuda":
