@@ -68,3 +68,34 @@ def test_actor_log_probs_with_shared_prefix_equal_the_plain_layout():
         torch.testing.assert_close(res[True][0][m], res[False][0][m], atol=2e-5, rtol=1e-4)
         torch.testing.assert_close(res[True][1][m], res[False][1][m], atol=2e-5, rtol=1e-4)
         assert float(res[True][0][~m].abs().sum()) == 0.0
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.gpu
+def test_shared_prefix_on_the_kernels():
+    """Same comparison on a GPU: the response part runs the key-stream form of the tcgen05 forward kernel."""
+    from verl_b200 import DataProto
+    from verl_b200.models import preset
+    from verl_b200.workers.actor.dp_actor import DataParallelPPOActor
+    from verl_b200.workers.config import FSDPActorConfig
+    from verl_b200.workers.engine.native import NativeEngine
+
+    class C(dict):
+        __getattr__ = dict.get
+
+    cfg = preset("qwen2.5-0.5b", num_hidden_layers=3, vocab_size=32768, num_attention_heads=4, num_key_value_heads=2,
+                 head_dim=128, hidden_size=512, intermediate_size=1024)
+    eng = NativeEngine(cfg, C(), C(lr=1e-5), device="cuda:0", seed=3).initialize()
+    ids, mask, pos, R = _batch(n_prompts=4, n=8, P=200, R=150, vocab=30000, seed=7)
+    data = DataProto.from_dict({"input_ids": ids, "attention_mask": mask, "position_ids": pos, "responses": ids[:, -R:],
+                                "response_mask": mask[:, -R:]}, meta_info={"temperature": 1.0, "micro_batch_size": 16})
+    res = {}
+    for flag in (False, True):
+        actor = DataParallelPPOActor(FSDPActorConfig(ppo_mini_batch_size=32, ppo_micro_batch_size_per_gpu=16,
+                                                     use_prefix_grouper=flag), eng)
+        res[flag] = actor.compute_log_prob(data, calculate_entropy=True)
+    m = mask[:, -R:].bool()
+    d = (res[True][0].cpu()[m] - res[False][0].cpu()[m]).abs()
+    assert float(d.max()) < 0.08 and float(d.mean()) < 0.01, (float(d.max()), float(d.mean()))
