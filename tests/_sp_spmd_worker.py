@@ -1,5 +1,6 @@
-"""Child of tests/test_ulysses_on_cpu.py::test_update_policy_with_sp_matches_dp: 2 gloo ranks under an SPMD launch.
-``update_actor`` with ulysses_sequence_parallel_size=2 (the two ranks pool their shares and work on the same samples)
+"""Child of tests/test_ulysses_on_cpu.py::test_update_policy_with_sp_matches_dp (and, with the argument ``cp``, of
+tests/test_context_parallel.py): 2 gloo ranks under an SPMD launch.
+``update_actor`` with ulysses_sequence_parallel_size=2 (or context_parallel_size=2) (the two ranks pool their shares and work on the same samples)
 must give the loss, gradient norm, number of optimizer steps and weights of a run without sequence parallelism in which
 the ranks train on their own shares (data parallel)."""
 import os
@@ -19,13 +20,15 @@ def main():
     from verl_b200.utils.config import compose
     from verl_b200.workers.engine_workers import ActorRolloutRefWorker
 
+    key = {"sp": "ulysses_sequence_parallel_size", "cp": "context_parallel_size"}[sys.argv[1] if len(sys.argv) > 1 else "sp"]
+
     def build(sp):
         cfg = compose("ppo_trainer", [
             "actor_rollout_ref.model.path=preset:tiny-qwen2", "trainer.device=cpu", "actor_rollout_ref.rollout.n=1",
             "actor_rollout_ref.rollout.tensor_model_parallel_size=1",
             "actor_rollout_ref.actor.ppo_mini_batch_size=8", "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=2",
             "actor_rollout_ref.actor.use_kl_loss=false", "actor_rollout_ref.actor.optim.lr=1e-3",
-            f"actor_rollout_ref.actor.fsdp_config.ulysses_sequence_parallel_size={sp}",
+            f"actor_rollout_ref.actor.fsdp_config.{key}={sp}",
             "actor_rollout_ref.rollout.max_num_seqs=8", "actor_rollout_ref.rollout.max_num_batched_tokens=64",
             "data.max_prompt_length=8", "data.max_response_length=8"])
         w = ActorRolloutRefWorker(cfg.actor_rollout_ref, role="actor", device_name="cpu")

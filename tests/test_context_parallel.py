@@ -81,3 +81,14 @@ def test_chunk_pair_attention_on_the_kernels(lens, cp):
     for a, b in zip(gcp, gref):
         s = float(b.float().abs().max())
         assert float((a.float() - b.float()).abs().max()) <= 0.04 * s + 1e-3
+
+
+@pytest.mark.timeout(600)
+def test_update_actor_with_context_parallelism_under_spmd_launch():
+    """The worker path (batch pooling inside the group, mini-batch normalisation, dispatch registration): update_actor
+    with context_parallel_size=2 equals the data-parallel update over the same samples."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(29800 + os.getpid() % 90), os.path.join(here, "_sp_spmd_worker.py"), "cp"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=560)
+    assert r.returncode == 0 and "SP_SPMD_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-3000:])

@@ -114,6 +114,11 @@ class FSDPEngineConfig(EngineConfig):
     # context parallelism: this many consecutive ranks share a micro-batch, each holding two zig-zag chunks of every
     # sequence (not combinable with Ulysses / tensor / pipeline parallelism)
     context_parallel_size: int = 1
+    # model parallelism of the one native engine (the reference reaches these through its Megatron back end):
+    # tensor-parallel ranks per model copy, pipeline stages, ranks that share the experts of an MoE model
+    tensor_model_parallel_size: int = 1
+    pipeline_model_parallel_size: int = 1
+    expert_model_parallel_size: int = 1
     entropy_from_logits_with_chunking: bool = False
     use_torch_compile: bool = True
     entropy_checkpointing: bool = False
