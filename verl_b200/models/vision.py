@@ -187,7 +187,12 @@ def get_rope_index(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tenso
             break
         use_img = ends[0] <= ends[1]
         ed = ends[0] if use_img else ends[1]
-        _, (t, h, w) = next(img_it if use_img else vid_it)
+        nxt_grid = next(img_it if use_img else vid_it, None)
+        if nxt_grid is None:
+            # more placeholder ids than grids: a policy sampled the placeholder id as an ordinary token (a generated
+            # response); everything from here on is text
+            break
+        _, (t, h, w) = nxt_grid
         gh, gw = h // spatial_merge_size, w // spatial_merge_size
         n_text = ed - st
         if n_text:

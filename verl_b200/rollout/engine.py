@@ -516,9 +516,17 @@ class NativeRolloutEngine:
 
     def _final_logits(self, x):
         w = self.model.lm_head_weight
-        if self.on_gpu:
-            return ops.gemm(x, w, out_dtype=torch.float32)
-        return x.float() @ w.float().t()
+        logits = ops.gemm(x, w, out_dtype=torch.float32) if self.on_gpu else x.float() @ w.float().t()
+        ban = getattr(self, "_banned_ids", None)
+        if ban is None:
+            # vision-language models: the image placeholder id stands for pixels and is never a token to generate (a
+            # sampled one would be taken for an image by every later consumer of the sequence)
+            c = self.full_cfg
+            ids = [c.image_token_id] if getattr(c, "is_vl", False) and c.image_token_id is not None else []
+            ban = self._banned_ids = torch.tensor(ids, dtype=torch.long, device=self.device)
+        if ban.numel():
+            logits.index_fill_(1, ban, float("-inf"))
+        return logits
 
     # ------------------------------------------------------------------ decode
     @torch.no_grad()
@@ -848,13 +856,16 @@ class NativeRolloutEngine:
         return int(self.sched.seq_prefill[i]) != 2
 
     # ---------------------------------------------------------------- generate
-    def generate(self, prompts: list[list[int]], sampling_params=None, request_ids: Optional[list[str]] = None):
-        """Blocking batch generation. ``sampling_params``: one for all or a list. Returns TokenOutputs in order."""
+    def generate(self, prompts: list[list[int]], sampling_params=None, request_ids: Optional[list[str]] = None,
+                 multi_modal_inputs: Optional[list] = None):
+        """Blocking batch generation. ``sampling_params``: one for all or a list; ``multi_modal_inputs``: per prompt a
+        dict (``pixel_values`` / ``image_grid_thw``) or None. Returns TokenOutputs in order."""
         n = len(prompts)
         sps = sampling_params if isinstance(sampling_params, list) else [sampling_params] * n
         rids = request_ids or [f"gen-{self._next_sid + i}-{time.monotonic_ns()}" for i in range(n)]
-        for rid, p, sp in zip(rids, prompts, sps):
-            self.add_request(rid, p, sp)
+        mms = multi_modal_inputs if multi_modal_inputs is not None else [None] * n
+        for rid, p, sp, mm in zip(rids, prompts, sps, mms):
+            self.add_request(rid, p, sp, multi_modal_inputs=mm)
         results: dict[str, TokenOutput] = {}
         want = set(rids)
         idle = 0

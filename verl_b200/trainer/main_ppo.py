@@ -26,12 +26,14 @@ def create_rl_dataset(data_paths, data_config, tokenizer, processor=None, is_tra
         return cls(data_files=data_paths, tokenizer=tokenizer, processor=processor, config=data_config)
     if isinstance(data_paths, str) and data_paths.startswith("synthetic:"):
         # synthetic:<num>:<min_len>:<max_len>:<id_lo>:<id_hi>:<seed>[:<data_source>[:<ground_truth>]]
+        # with a vision-language processor and data.synthetic_image_size > 0 every prompt carries one random image
         parts = data_paths.split(":")
         num, lo, hi, id_lo, id_hi, seed = (int(x) for x in parts[1:7])
         source = parts[7] if len(parts) > 7 else "synthetic/even_fraction"
         gt = int(parts[8]) if len(parts) > 8 else None
         return SyntheticPromptDataset(num, lo, hi, id_lo, id_hi, data_config.max_prompt_length, seed, source,
-                                      getattr(tokenizer, "pad_token_id", 0) or 0, gt)
+                                      getattr(tokenizer, "pad_token_id", 0) or 0, gt, processor=processor,
+                                      image_size=int(data_config.get("synthetic_image_size", 0) or 0))
     return RLHFDataset(data_paths, tokenizer, data_config, processor, max_samples)
 
 
@@ -65,6 +67,16 @@ def build_tokenizer(config, model_config=None):
         return hf_tokenizer(model.get("tokenizer_path") or path, trust_remote_code=trust)
     mc = model_config if model_config is not None else resolve_model_config(model)[0]
     return IntTokenizer(mc.vocab_size, eos_token_id=mc.eos_token_id if mc.eos_token_id is not None else 2)
+
+
+def build_processor(config, model_config=None):
+    """Multimodal processor of the policy model (None for text-only models)."""
+    from ..utils.dataset.vision_utils import VLProcessor
+    from ..workers.engine_workers import resolve_model_config
+
+    model = config.actor_rollout_ref.model if "actor_rollout_ref" in config else config
+    mc = model_config if model_config is not None else resolve_model_config(model)[0]
+    return VLProcessor.from_model_config(mc)
 
 
 class TaskRunner:
@@ -131,6 +143,7 @@ class TaskRunner:
         use_ref, use_critic = need_reference_policy(config), need_critic(config)
         validate_config(config, use_reference_policy=use_ref, use_critic=use_critic)
         tokenizer = build_tokenizer(config)
+        processor = build_processor(config)
         self.add_actor_rollout_worker(config)
         self.add_critic_worker(config)
         self.add_reward_model_worker(config)
@@ -138,12 +151,12 @@ class TaskRunner:
         rpm, wg_cls = self.init_resource_pool_mgr(config, spmd)
         reward_fn = load_reward_manager(config, tokenizer, num_examine=0)
         val_reward_fn = load_reward_manager(config, tokenizer, num_examine=1)
-        train_ds = create_rl_dataset(config.data.train_files, config.data, tokenizer, is_train=True,
+        train_ds = create_rl_dataset(config.data.train_files, config.data, tokenizer, processor, is_train=True,
                                      max_samples=config.data.get("train_max_samples", -1))
         val_ds = None
         if config.data.get("val_files"):
             try:
-                val_ds = create_rl_dataset(config.data.val_files, config.data, tokenizer, is_train=False,
+                val_ds = create_rl_dataset(config.data.val_files, config.data, tokenizer, processor, is_train=False,
                                            max_samples=config.data.get("val_max_samples", -1))
             except (FileNotFoundError, OSError):
                 val_ds = None

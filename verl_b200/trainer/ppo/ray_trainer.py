@@ -383,6 +383,8 @@ class RayPPOTrainer:
         nt = [k for k in ("raw_prompt_ids", "raw_prompt", "tools_kwargs", "interaction_kwargs", "agent_name")
               if k in batch.non_tensor_batch]
         gen = batch.pop(batch_keys=keys, non_tensor_batch_keys=nt)
+        if "multi_modal_inputs" in batch.non_tensor_batch:  # images: the rollout needs them, the actor too (kept)
+            gen.non_tensor_batch["multi_modal_inputs"] = batch.non_tensor_batch["multi_modal_inputs"]
         if batch.batch is not None and len(list(batch.batch.keys())) == 0:
             batch.batch = None
         return gen

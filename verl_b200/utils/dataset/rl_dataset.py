@@ -94,12 +94,22 @@ class RLHFDataset(Dataset):
     def __getitem__(self, item):
         row = dict(self.rows[item])
         messages = row.pop(self.prompt_key)
-        ids = torch.tensor([self._tokenize(messages)], dtype=torch.long)
+        toks = self._tokenize(messages)
+        images = row.pop(self.config.get("image_key", "images"), None)
+        pos3 = None
+        if images is not None and len(images) and self.processor is not None:
+            # vision-language prompt: placeholders expanded to one token per merged patch, pixels and grids travel
+            # with the row, rows 1..3 of position_ids carry the multimodal RoPE positions
+            toks, mm, pos3 = self.processor(toks, list(images))
+            row["multi_modal_inputs"] = mm
+        ids = torch.tensor([toks], dtype=torch.long)
         mask = torch.ones_like(ids)
         pad = getattr(self.tokenizer, "pad_token_id", 0) or 0
         ids, mask = F_.postprocess_data(ids, mask, self.max_prompt_length, pad, left_pad=True, truncation=self.truncation)
         row["input_ids"], row["attention_mask"] = ids[0], mask[0]
         row["position_ids"] = F_.compute_position_id_with_mask(mask)[0]
+        if pos3 is not None:
+            row["position_ids"] = _with_mrope_rows(row["position_ids"], mask[0], pos3)
         row["raw_prompt_ids"] = ids[0][mask[0].bool()].tolist()
         if self.return_raw_chat:
             row["raw_prompt"] = messages
@@ -117,24 +127,46 @@ class RLHFDataset(Dataset):
         return self.__dict__.copy()
 
 
+def _with_mrope_rows(text_pos: torch.Tensor, mask: torch.Tensor, pos3: torch.Tensor) -> torch.Tensor:
+    """[S] text positions + [3, L] multimodal positions of the L unpadded tokens -> [4, S]."""
+    out = torch.zeros(4, text_pos.numel(), dtype=torch.long)
+    out[0] = text_pos
+    out[1:, mask.bool()] = pos3[:, -int(mask.sum()):]  # left truncation keeps the tail
+    return out
+
+
 class SyntheticPromptDataset(Dataset):
     """Uniform-random token prompts: lengths in [min_len, max_len], ids in [id_lo, id_hi), fixed seed.
     Rows look like RLHFDataset rows so the same trainer, reward manager and collate function apply."""
 
     def __init__(self, num_prompts: int, min_len: int, max_len: int, id_lo: int, id_hi: int, max_prompt_length: int,
-                 seed: int = 0, data_source: str = "synthetic/even_fraction", pad_token_id: int = 0, ground_truth=None):
+                 seed: int = 0, data_source: str = "synthetic/even_fraction", pad_token_id: int = 0, ground_truth=None,
+                 processor=None, image_size: int = 0):
+        """``processor`` + ``image_size`` > 0: every prompt starts with one random RGB image of that size (vision-
+        language models); the text length is then in addition to the image placeholders."""
         g = torch.Generator().manual_seed(seed)
         self.items = []
         for i in range(num_prompts):
             n = int(torch.randint(min_len, max_len + 1, (1,), generator=g))
             toks = torch.randint(id_lo, id_hi, (n,), generator=g)
+            extra_row, pos3 = {}, None
+            if processor is not None and image_size > 0:
+                img = torch.randint(0, 256, (image_size, image_size, 3), generator=g, dtype=torch.uint8).numpy()
+                tl, mm, pos3 = processor(toks.tolist(), [img])
+                toks = torch.tensor(tl, dtype=torch.long)
+                n = toks.numel()
+                assert n <= max_prompt_length, f"prompt of {n} tokens (with image placeholders) exceeds max_prompt_length"
+                extra_row["multi_modal_inputs"] = mm
             ids = torch.full((max_prompt_length,), pad_token_id, dtype=torch.long)
             mask = torch.zeros(max_prompt_length, dtype=torch.long)
             ids[-n:], mask[-n:] = toks, 1
+            pos = F_.compute_position_id_with_mask(mask)
+            if pos3 is not None:
+                pos = _with_mrope_rows(pos, mask, pos3)
             self.items.append({"input_ids": ids, "attention_mask": mask,
-                               "position_ids": F_.compute_position_id_with_mask(mask), "data_source": data_source,
+                               "position_ids": pos, "data_source": data_source,
                                "reward_model": {"ground_truth": ground_truth, "style": "rule"}, "extra_info": {"index": i},
-                               "index": i, "raw_prompt_ids": toks.tolist()})
+                               "index": i, "raw_prompt_ids": toks.tolist(), **extra_row})
 
     def __len__(self):
         return len(self.items)

@@ -372,9 +372,18 @@ class ActorRolloutRefWorker(_WorkerBase):
             lo = sum(len(p) for p in pooled[: self.dp_rank % self.rollout_tp])
             outs = eng.generate([p for part in pooled for p in part], sp)[lo : lo + len(prompt_lists)]
         else:
-            outs = eng.generate(prompt_lists, sp)
+            mm = prompts.non_tensor_batch.get("multi_modal_inputs")
+            outs = eng.generate(prompt_lists, sp, multi_modal_inputs=list(mm) if mm is not None else None)
         out = assemble_rollout_batch(ids.cpu(), mask.cpu(), outs, rc.response_length, pad_token_id=meta.get("pad_token_id", 0),
                                      with_logprobs=True)
+        if getattr(self.model_config, "is_vl", False):
+            # [B, 4, S]: text positions + multimodal RoPE positions of prompt and response (the actor's input layout)
+            from ..utils.dataset.vision_utils import vl_position_ids
+
+            v = self.model_config.extra.get("vision_config") or {}
+            out.batch["position_ids"] = vl_position_ids(out.batch["input_ids"], out.batch["attention_mask"],
+                                                        prompts.non_tensor_batch.get("multi_modal_inputs"),
+                                                        self.model_config.image_token_id, int(v.get("spatial_merge_size", 2)))
         gen_time = time.perf_counter() - t0
         out.non_tensor_batch.update(prompts.non_tensor_batch)
         n_tok = int(out.batch["response_mask"].sum())
