@@ -99,3 +99,37 @@ def test_shared_prefix_on_the_kernels():
     m = mask[:, -R:].bool()
     d = (res[True][0].cpu()[m] - res[False][0].cpu()[m]).abs()
     assert float(d.max()) < 0.08 and float(d.mean()) < 0.01, (float(d.max()), float(d.mean()))
+
+
+def test_token_budget_micro_batches_keep_groups_together():
+    from verl_b200 import DataProto
+    from verl_b200.models import preset
+    from verl_b200.workers.actor.dp_actor import DataParallelPPOActor
+    from verl_b200.workers.config import FSDPActorConfig
+    from verl_b200.workers.engine.native import NativeEngine
+
+    class C(dict):
+        __getattr__ = dict.get
+
+    eng = NativeEngine(preset("tiny-qwen2"), C(), C(lr=1e-3), device="cpu", seed=3).initialize()
+    ids, mask, pos, R = _batch(n_prompts=5, n=4, seed=9)
+    perm = torch.randperm(20, generator=torch.Generator().manual_seed(1))  # the samples of a prompt arrive scattered
+    ids, mask, pos = ids[perm], mask[perm], pos[perm]
+    data = DataProto.from_dict({"input_ids": ids, "attention_mask": mask, "position_ids": pos, "responses": ids[:, -R:],
+                                "response_mask": mask[:, -R:]},
+                               meta_info={"temperature": 1.0, "use_dynamic_bsz": True, "max_token_len": 90})
+    res = {}
+    for flag in (False, True):
+        actor = DataParallelPPOActor(FSDPActorConfig(ppo_mini_batch_size=20, use_dynamic_bsz=True, use_prefix_grouper=flag), eng)
+        res[flag] = actor.compute_log_prob(data, calculate_entropy=False)[0]
+        if flag:
+            with torch.no_grad():
+                micros, bins = actor._micro_batches(data, 90, None, True)
+            P = ids.shape[1] - R
+            for mb in micros:  # whole groups only: 4 samples per distinct prompt
+                keys = [mb.batch["input_ids"][i, :P][mb.batch["attention_mask"][i, :P].bool()].numpy().tobytes() for i in range(len(mb))]
+                assert all(keys.count(k) == 4 for k in set(keys))
+            assert sorted(i for b in bins for i in b) == list(range(20)) and len(micros) >= 2
+            assert actor.last_prefix_saving > 0.2
+    m = mask[:, -R:].bool()
+    torch.testing.assert_close(res[True][m], res[False][m], atol=2e-5, rtol=1e-4)

@@ -78,7 +78,46 @@ class DataParallelPPOActor:
             entropy = entropy.index_put((bj[:, 0], bj[:, 1]), ent)
         return log_probs, (entropy if calculate_entropy else None)
 
+    def _micro_batches_by_group(self, data: DataProto, max_token_len: int):
+        """Token-budget micro-batches for the shared-prefix layout: the samples of one prompt stay together (a group
+        counts its prompt once), groups are spread over the micro-batches largest first onto the least loaded one, and
+        every rank makes the same number of micro-batches. Returns None when there are fewer groups than micro-batches."""
+        b = data.batch
+        R = b["responses"].shape[-1]
+        ids, mask = b["input_ids"], b["attention_mask"]
+        P = ids.shape[1] - R
+        groups: dict = {}
+        for i in range(ids.shape[0]):
+            groups.setdefault(ids[i, :P][mask[i, :P].bool()].cpu().numpy().tobytes(), []).append(i)
+        rows = list(groups.values())
+        cost = [int(mask[r[0], :P].sum()) + int(mask[r, P:].sum()) for r in rows]
+        k = max(1, -(-sum(cost) // max(int(max_token_len), 1)))
+        if self.engine.world > 1:
+            t = torch.tensor([k, -len(rows)], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.engine.group)
+            k, min_groups = int(t[0]), -int(t[1])
+        else:
+            min_groups = len(rows)
+        if min_groups < k:
+            return None
+        bins: list[list[int]] = [[] for _ in range(k)]
+        load = [0] * k
+        for g in sorted(range(len(rows)), key=lambda g: -cost[g]):
+            j = min(range(k), key=lambda j: load[j])
+            bins[j] += rows[g]
+            load[j] += cost[g]
+        out = []
+        for idx in bins:
+            sel = torch.tensor(idx, dtype=torch.long)
+            nt = {key: v[idx] for key, v in data.non_tensor_batch.items()}
+            out.append(DataProto(batch=b[sel], non_tensor_batch=nt, meta_info=data.meta_info))
+        return out, bins
+
     def _micro_batches(self, data: DataProto, max_token_len: Optional[int], micro_bsz: Optional[int], use_dyn: bool):
+        if use_dyn and self.use_prefix_grouper and not torch.is_grad_enabled() and max_token_len:
+            grouped = self._micro_batches_by_group(data, int(max_token_len))
+            if grouped is not None:
+                return grouped
         if use_dyn:
             return prepare_dynamic_batch(data, max_token_len=max_token_len, dp_group=self.engine.group
                                          if self.engine.world > 1 else None)
