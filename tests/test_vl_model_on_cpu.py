@@ -193,3 +193,55 @@ def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch):
     assert m["actor/grad_norm"] > 0
     # the rollout engine (vision tower at admission, mrope in prefill / decode) and the trainer agree on the policy
     assert m["training/rollout_probs_diff_mean"] < 5e-3, m["training/rollout_probs_diff_mean"]
+
+
+def test_qwen2_5_vl_tower_matches_hf():
+    """Qwen2.5-VL: RMSNorm blocks with a gated SiLU MLP, attention inside windows except in the full-attention blocks,
+    window-ordered patches restored after the merger. Logits of a sequence with two images (one of them with ragged
+    edge windows) against ``transformers``; HF names round-trip."""
+    pytest.importorskip("transformers")
+    from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
+
+    hf_cfg = Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]},
+                         max_position_embeddings=512, tie_word_embeddings=False, rope_theta=10000.0),
+        vision_config=dict(depth=3, hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, in_channels=3,
+                           patch_size=4, spatial_merge_size=2, temporal_patch_size=2, window_size=16,
+                           fullatt_block_indexes=[1], hidden_act="silu"),
+        image_token_id=500, video_token_id=501, vision_start_token_id=502, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = Qwen2_5_VLForConditionalGeneration(hf_cfg).float().eval()
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict())
+    assert cfg.is_vl and cfg.model_type == "qwen2_5_vl"
+    native = hf_to_native_state_dict(cfg, dict(hf.state_dict()))
+    model = CausalLM(cfg, dtype=torch.float32)
+    assert model.visual.c.variant == "qwen2_5_vl" and model.visual.c.embed_dim == 32 and model.visual.c.hidden_size == 64
+    missing, unexpected = model.load_state_dict(native, strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    # image 1: 8 x 8 patches = 4 x 4 merged units = four 2 x 2 windows; image 2: 4 x 12 patches = 2 x 6 units: windows of
+    # 2 x 2 units, three of them
+    grid = torch.tensor([[1, 8, 8], [1, 4, 12]])
+    g = torch.Generator().manual_seed(1)
+    pixels = torch.randn(64 + 48, 3 * 2 * 4 * 4, generator=g)
+    ids = torch.tensor([5, 502] + [500] * 16 + [7, 9, 502] + [500] * 12 + [11, 13])
+    pos3, delta = get_rope_index(ids, grid, image_token_id=500, spatial_merge_size=2)
+    with torch.no_grad():
+        vis_ref = hf.model.visual(pixels, grid_thw=grid)
+        vis_ref = vis_ref.pooler_output if hasattr(vis_ref, "pooler_output") else vis_ref
+        torch.testing.assert_close(model.visual(pixels, grid), vis_ref, atol=2e-4, rtol=2e-4)
+        mm = (ids == 500).int()[None]
+        am = torch.ones(1, ids.numel(), dtype=torch.long)
+        # the positions are passed explicitly: still images keep ONE temporal position (that of the image's start), the
+        # rule of the model's release; the per-second scaling of video frames is not modelled here
+        ref = hf(input_ids=ids[None], pixel_values=pixels, image_grid_thw=grid, attention_mask=am, mm_token_type_ids=mm,
+                 position_ids=pos3[:, None])
+        batch = PackedBatch(ids, pos3, torch.tensor([0, ids.numel()], dtype=torch.int32), ids.numel(), pixel_values=pixels,
+                            image_grid_thw=grid)
+        logits = model(batch)
+    torch.testing.assert_close(logits, ref.logits[0], atol=3e-4, rtol=3e-4)
+    back = native_to_hf_state_dict(cfg, native)
+    ref_sd = dict(hf.state_dict())
+    assert set(back) == set(ref_sd)
+    for k in ref_sd:
+        assert torch.equal(back[k], ref_sd[k]), k

@@ -214,6 +214,23 @@ PRESETS: dict[str, dict] = {
                                                        temporal_patch_size=2),
                                  "mrope_section": [8, 12, 12], "image_token_id": 2000, "video_token_id": 2001,
                                  "vision_start_token_id": 2002}),
+    "tiny-qwen2.5-vl": dict(model_type="qwen2_5_vl", vocab_size=2048, hidden_size=256, intermediate_size=512,
+                            num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, rope_theta=1e6, eos_token_id=2,
+                            extra={"vision_config": dict(depth=3, hidden_size=64, out_hidden_size=256, intermediate_size=96,
+                                                         num_heads=2, in_channels=3, patch_size=4, spatial_merge_size=2,
+                                                         temporal_patch_size=2, window_size=16, fullatt_block_indexes=[1],
+                                                         hidden_act="silu"),
+                                   "mrope_section": [8, 12, 12], "image_token_id": 2000, "video_token_id": 2001,
+                                   "vision_start_token_id": 2002}),
+    "qwen2.5-vl-7b": dict(model_type="qwen2_5_vl", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+                          num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6,
+                          eos_token_id=151645,
+                          extra={"vision_config": dict(depth=32, hidden_size=1280, out_hidden_size=3584, intermediate_size=3420,
+                                                       num_heads=16, in_channels=3, patch_size=14, spatial_merge_size=2,
+                                                       temporal_patch_size=2, window_size=112,
+                                                       fullatt_block_indexes=[7, 15, 23, 31], hidden_act="silu"),
+                                 "mrope_section": [16, 24, 24], "image_token_id": 151655, "video_token_id": 151656,
+                                 "vision_start_token_id": 151652}),
     "qwen2-vl-7b": dict(model_type="qwen2_vl", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
                         num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6,
                         eos_token_id=151645,

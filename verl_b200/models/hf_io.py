@@ -19,6 +19,7 @@ from .config import ModelConfig
 
 
 _VIS_HF_TO_NATIVE = (("attn.qkv.", "qkv."), ("attn.proj.", "proj."), ("mlp.fc1.", "fc1."), ("mlp.fc2.", "fc2."),
+                     ("mlp.gate_proj.", "fc_gate."), ("mlp.up_proj.", "fc_up."), ("mlp.down_proj.", "fc2."),
                      ("merger.ln_q.", "ln_q."), ("merger.mlp.0.", "merge_fc1."), ("merger.mlp.2.", "merge_fc2."),
                      ("patch_embed.proj.", "patch_embed."))
 
@@ -88,7 +89,8 @@ def native_to_hf_items(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tensor
     lm = "model.language_model." if vl else "model."
     for name, t in named:
         if name.startswith("visual."):
-            n = _vis_native_to_hf(name)
+            n = _vis_native_to_hf(name, gated=(cfg.extra.get("vision_config") or {}).get("intermediate_size") is not None
+                                  or cfg.model_type == "qwen2_5_vl")
             if name == "visual.patch_embed.weight":
                 vc = cfg.extra["vision_config"]
                 t = t.reshape(t.shape[0], vc.get("in_channels", 3), vc.get("temporal_patch_size", 2), vc.get("patch_size", 14),
@@ -135,13 +137,16 @@ def native_to_hf_items(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tensor
             yield name, t
 
 
-def _vis_native_to_hf(name: str) -> str:
+def _vis_native_to_hf(name: str, gated: bool = False) -> str:
+    """``gated``: the Qwen2.5-VL tower (gate / up / down projections) rather than the Qwen2-VL one (fc1 / fc2)."""
     body = name[len("visual."):]
     parts = body.split(".")
     # blocks.N.<x>.<w|b> or top-level <x>.<w|b>
     leaf = parts[-2] + "."
     for hf, nat in _VIS_HF_TO_NATIVE:
         if leaf == nat:
+            if nat == "fc2." and gated != (hf == "mlp.down_proj."):
+                continue
             return "visual." + ".".join(parts[:-2] + [hf[:-1], parts[-1]])
     return name
 

@@ -31,9 +31,28 @@ class VisionConfig:
     spatial_merge_size: int = 2
     temporal_patch_size: int = 2
     hidden_act: str = "quick_gelu"
+    # Qwen2.5-VL: RMSNorm instead of LayerNorm, gated SiLU MLP of ``intermediate_size``, attention inside windows of
+    # ``window_size`` pixels except in the blocks ``fullatt_block_indexes`` (verl/models/transformers/qwen2_vl.py serves
+    # both generations through transformers; here ``variant`` selects the block layout)
+    variant: str = "qwen2_vl"
+    intermediate_size: int = 0
+    window_size: int = 112
+    fullatt_block_indexes: tuple = (7, 15, 23, 31)
 
     @classmethod
     def from_dict(cls, d: dict) -> "VisionConfig":
+        d = dict(d)
+        if "out_hidden_size" in d or d.get("variant") == "qwen2_5_vl":
+            # the HF Qwen2.5-VL vision config calls the tower's width ``hidden_size`` and the language model's width
+            # ``out_hidden_size``
+            if "out_hidden_size" in d:
+                d["embed_dim"], d["hidden_size"] = d["hidden_size"], d["out_hidden_size"]
+            d["variant"] = "qwen2_5_vl"
+            d.setdefault("hidden_act", "silu")
+        if "in_chans" in d and "in_channels" not in d:
+            d["in_channels"] = d["in_chans"]
+        if "fullatt_block_indexes" in d:
+            d["fullatt_block_indexes"] = tuple(d["fullatt_block_indexes"])
         known = {f for f in cls.__dataclass_fields__}
         return cls(**{k: v for k, v in d.items() if k in known})
 
@@ -70,6 +89,17 @@ class _LayerNormW(nn.Module):
         return F.layer_norm(x.float(), (x.shape[-1],), self.weight.float(), self.bias.float(), self.eps).to(x.dtype)
 
 
+class _RMSNormW(nn.Module):
+    def __init__(self, dim: int, dtype, device, eps: float = 1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
+        self.eps = eps
+
+    def forward(self, x):
+        h = x.float()
+        return (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight.float()).to(x.dtype)
+
+
 def _rotate_half(x):
     a, b = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2 :]
     return torch.cat([-b, a], -1)
@@ -79,12 +109,19 @@ class VisionBlock(nn.Module):
     def __init__(self, c: VisionConfig, dtype, device):
         super().__init__()
         self.c = c
-        self.norm1 = _LayerNormW(c.embed_dim, dtype, device)
-        self.norm2 = _LayerNormW(c.embed_dim, dtype, device)
+        Norm = _RMSNormW if c.variant == "qwen2_5_vl" else _LayerNormW
+        self.norm1 = Norm(c.embed_dim, dtype, device)
+        self.norm2 = Norm(c.embed_dim, dtype, device)
         self.qkv = _Lin(c.embed_dim, 3 * c.embed_dim, True, dtype, device)
         self.proj = _Lin(c.embed_dim, c.embed_dim, True, dtype, device)
-        hid = int(c.embed_dim * c.mlp_ratio)
-        self.fc1 = _Lin(c.embed_dim, hid, True, dtype, device)
+        if c.variant == "qwen2_5_vl":
+            hid = int(c.intermediate_size)
+            self.fc_gate = _Lin(c.embed_dim, hid, True, dtype, device)
+            self.fc_up = _Lin(c.embed_dim, hid, True, dtype, device)
+            self.fc1 = None
+        else:
+            hid = int(c.embed_dim * c.mlp_ratio)
+            self.fc1 = _Lin(c.embed_dim, hid, True, dtype, device)
         self.fc2 = _Lin(hid, c.embed_dim, True, dtype, device)
 
     def forward(self, x, cu_seqlens, max_seqlen, cos, sin):
@@ -97,8 +134,12 @@ class VisionBlock(nn.Module):
         k = (k.float() * cos + _rotate_half(k.float()) * sin).to(x.dtype)
         a = ops.attention_varlen(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens, max_seqlen, causal=False)
         x = x + self.proj(a.reshape(N, c.embed_dim))
-        h = self.fc1(self.norm2(x))
-        h = h * torch.sigmoid(1.702 * h) if c.hidden_act == "quick_gelu" else F.gelu(h)
+        y = self.norm2(x)
+        if self.fc1 is None:  # gated SiLU
+            h = F.silu(self.fc_gate(y)) * self.fc_up(y)
+        else:
+            h = self.fc1(y)
+            h = h * torch.sigmoid(1.702 * h) if c.hidden_act == "quick_gelu" else F.gelu(h)
         return x + self.fc2(h)
 
 
@@ -111,7 +152,7 @@ class VisionTower(nn.Module):
         self.c = c
         self.patch_embed = _Lin(c.patch_dim, c.embed_dim, False, dtype, device)  # the Conv3d of the reference, as a GEMM
         self.blocks = nn.ModuleList([VisionBlock(c, dtype, device) for _ in range(c.depth)])
-        self.ln_q = _LayerNormW(c.embed_dim, dtype, device)
+        self.ln_q = (_RMSNormW if c.variant == "qwen2_5_vl" else _LayerNormW)(c.embed_dim, dtype, device)
         m2 = c.spatial_merge_size ** 2
         self.merge_fc1 = _Lin(c.embed_dim * m2, c.embed_dim * m2, True, dtype, device)
         self.merge_fc2 = _Lin(c.embed_dim * m2, c.hidden_size, True, dtype, device)
@@ -147,6 +188,26 @@ class VisionTower(nn.Module):
         emb = torch.cat([emb, emb], -1)                # [N, head_dim]
         return emb.cos()[:, None, :], emb.sin()[:, None, :]
 
+    def window_order(self, grid_thw: torch.Tensor):
+        """Qwen2.5-VL: (order of the merged-patch units window by window, window boundaries in patches). The merged grid
+        of every frame is cut into squares of ``window_size / patch_size / merge`` units; a unit list per window, frame by
+        frame, image by image; windows at the right / bottom edge are smaller."""
+        c = self.c
+        ws = c.window_size // c.spatial_merge_size // c.patch_size
+        m2 = c.spatial_merge_size ** 2
+        order, bounds, base = [], [0], 0
+        for t, h, w in grid_thw.tolist():
+            gh, gw = h // c.spatial_merge_size, w // c.spatial_merge_size
+            unit = torch.arange(t * gh * gw).view(t, gh, gw)
+            for f in range(t):
+                for r0 in range(0, gh, ws):
+                    for c0 in range(0, gw, ws):
+                        win = unit[f, r0 : r0 + ws, c0 : c0 + ws].reshape(-1)
+                        order.append(win + base)
+                        bounds.append(bounds[-1] + win.numel() * m2)
+            base += t * gh * gw
+        return torch.cat(order), torch.tensor(bounds, dtype=torch.int32)
+
     def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
         c = self.c
         x = self.patch_embed(pixel_values.to(self.patch_embed.weight.dtype))
@@ -154,9 +215,23 @@ class VisionTower(nn.Module):
         per_frame = (grid_thw[:, 1] * grid_thw[:, 2]).repeat_interleave(grid_thw[:, 0])
         cu = F.pad(per_frame.cumsum(0), (1, 0)).to(torch.int32)
         max_len = int(per_frame.max())
+        m2 = c.spatial_merge_size ** 2
+        if c.variant == "qwen2_5_vl":
+            # patches travel window by window (whole merge units stay together); the merged outputs go back to the
+            # original order at the end
+            order, cu_win = self.window_order(grid_thw.cpu())
+            order, cu_win = order.to(x.device), cu_win.to(x.device)
+            max_win = int((cu_win[1:] - cu_win[:-1]).max())
+            regroup = lambda t: t.reshape(t.shape[0] // m2, m2, *t.shape[1:])[order].reshape(t.shape)  # noqa: E731
+            x, cos, sin = regroup(x), regroup(cos), regroup(sin)
+            for i, blk in enumerate(self.blocks):
+                full = i in c.fullatt_block_indexes
+                x = blk(x, cu if full else cu_win, max_len if full else max_win, cos, sin)
+            x = self.ln_q(x).view(-1, c.embed_dim * m2)
+            out = self.merge_fc2(F.gelu(self.merge_fc1(x)))
+            return out[torch.argsort(order)]
         for blk in self.blocks:
             x = blk(x, cu, max_len, cos, sin)
-        m2 = c.spatial_merge_size ** 2
         x = self.ln_q(x).view(-1, c.embed_dim * m2)
         return self.merge_fc2(F.gelu(self.merge_fc1(x)))
 
