@@ -16,6 +16,7 @@ _ARCH_TO_TYPE = {
     "Qwen2ForCausalLM": "qwen2",
     "Qwen3ForCausalLM": "qwen3",
     "Qwen3MoeForCausalLM": "qwen3_moe",
+    "ApertusForCausalLM": "apertus",
     "Qwen2VLForConditionalGeneration": "qwen2_vl",
     "Qwen2_5_VLForConditionalGeneration": "qwen2_5_vl",
     "LlamaForTokenClassification": "llama",
@@ -24,7 +25,7 @@ _ARCH_TO_TYPE = {
 }
 _TYPE_TO_ARCH = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                  "qwen3_moe": "Qwen3MoeForCausalLM", "qwen2_vl": "Qwen2VLForConditionalGeneration",
-                 "qwen2_5_vl": "Qwen2_5_VLForConditionalGeneration"}
+                 "qwen2_5_vl": "Qwen2_5_VLForConditionalGeneration", "apertus": "ApertusForCausalLM"}
 _VL_TYPES = ("qwen2_vl", "qwen2_5_vl")
 
 
@@ -43,7 +44,9 @@ class ModelConfig:
     max_position_embeddings: int = 32768
     tie_word_embeddings: bool = False
     attention_bias: bool | None = None  # None -> family default (qwen2: True)
-    qk_norm: bool | None = None  # None -> family default (qwen3*: True)
+    qk_norm: bool | None = None  # None -> family default (qwen3*, apertus: True)
+    # "silu": gated SwiGLU MLP (gate / up / down); "xielu": Apertus' two-matrix MLP with the learnable xIELU activation
+    hidden_act: str | None = None
     # MoE (qwen3_moe)
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -63,12 +66,18 @@ class ModelConfig:
         if self.attention_bias is None:
             self.attention_bias = self.model_type in ("qwen2",) + _VL_TYPES
         if self.qk_norm is None:
-            self.qk_norm = self.model_type in ("qwen3", "qwen3_moe")
+            self.qk_norm = self.model_type in ("qwen3", "qwen3_moe", "apertus")
+        if self.hidden_act is None:
+            self.hidden_act = "xielu" if self.model_type == "apertus" else "silu"
 
     # ------------------------------------------------------------------ derived
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    @property
+    def mlp_gated(self) -> bool:
+        return self.hidden_act != "xielu"
 
     # vision-language models (Qwen2-VL family): the decoder fields above describe the language model; the vision tower,
     # the placeholder token ids and the multimodal RoPE sections live in ``extra``
@@ -102,7 +111,7 @@ class ModelConfig:
         if self.is_moe:
             mlp = self.num_experts * 3 * H * self.moe_intermediate_size + H * self.num_experts
         else:
-            mlp = 3 * H * self.intermediate_size
+            mlp = (3 if self.mlp_gated else 2) * H * self.intermediate_size + (0 if self.mlp_gated else 2)
         total = L * (attn + mlp + 2 * H) + H
         if include_embedding:
             total += self.vocab_size * H * (1 if self.tie_word_embeddings else 2)
@@ -131,8 +140,21 @@ class ModelConfig:
             d = {k: v for k, v in flat.items() if k not in ("rope_scaling", "rope_parameters", "image_token_id",
                                                             "video_token_id", "vision_start_token_id", "vision_end_token_id")}
             d["_vl_extra"] = extra_vl
+        else:
+            # text models: recent HF versions nest theta and the scaling rule under rope_parameters
+            rope = d.get("rope_parameters") or d.get("rope_scaling") or None
+            if isinstance(rope, dict):
+                d = dict(d)
+                if d.get("rope_theta") is None and rope.get("rope_theta") is not None:
+                    d["rope_theta"] = rope["rope_theta"]
+                kind = rope.get("rope_type") or rope.get("type") or "default"
+                d.pop("rope_parameters", None)
+                d.pop("rope_scaling", None)
+                if kind != "default":
+                    d["rope_scaling"] = {k: v for k, v in rope.items() if k != "rope_theta"}
         known = {f for f in cls.__dataclass_fields__}
-        kw = {k: v for k, v in d.items() if k in known and k != "extra"}
+        may_be_none = ("eos_token_id", "pad_token_id", "bos_token_id", "head_dim", "attention_bias", "qk_norm", "hidden_act")
+        kw = {k: v for k, v in d.items() if k in known and k != "extra" and (v is not None or k in may_be_none)}
         kw["model_type"] = mt
         if "num_local_experts" in d and "num_experts" not in d:
             kw["num_experts"] = d["num_local_experts"]
@@ -239,6 +261,13 @@ PRESETS: dict[str, dict] = {
                                                      temporal_patch_size=2),
                                "mrope_section": [16, 24, 24], "image_token_id": 151655, "video_token_id": 151656,
                                "vision_start_token_id": 151652}),
+    "tiny-apertus": dict(model_type="apertus", vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, rope_theta=1e6, rms_norm_eps=1e-5, eos_token_id=2),
+    "apertus-8b": dict(model_type="apertus", vocab_size=131072, hidden_size=4096, intermediate_size=21504,
+                       num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, rope_theta=1.2e7,
+                       rms_norm_eps=1e-5, eos_token_id=2, max_position_embeddings=65536,
+                       extra={"rope_scaling": {"rope_type": "llama3", "factor": 8.0, "original_max_position_embeddings": 8192,
+                                               "low_freq_factor": 1.0, "high_freq_factor": 4.0}}),
     "llama-3-8b": dict(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
                        num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, rope_theta=5e5,
                        rms_norm_eps=1e-5, eos_token_id=128001),

@@ -56,10 +56,12 @@ def hf_to_native_state_dict(cfg: ModelConfig, hf_sd: dict[str, torch.Tensor]) ->
         out["lm_head.weight"] = g("lm_head.weight")
     if "score.weight" in hf_sd:
         out["score.weight"] = g("score.weight")
+    apertus = cfg.model_type == "apertus"  # other names for the two norms, a two-matrix MLP with activation parameters
     for i in range(cfg.num_hidden_layers):
         p, n = f"model.layers.{i}.", f"layers.{i}."
-        out[n + "input_layernorm.weight"] = g(p + "input_layernorm.weight")
-        out[n + "post_attention_layernorm.weight"] = g(p + "post_attention_layernorm.weight")
+        out[n + "input_layernorm.weight"] = g(p + ("attention_layernorm.weight" if apertus else "input_layernorm.weight"))
+        out[n + "post_attention_layernorm.weight"] = g(p + ("feedforward_layernorm.weight" if apertus else
+                                                           "post_attention_layernorm.weight"))
         out[n + "self_attn.qkv_proj.weight"] = torch.cat(
             [g(p + f"self_attn.{x}_proj.weight") for x in "qkv"], dim=0)
         if cfg.attention_bias:
@@ -75,6 +77,11 @@ def hf_to_native_state_dict(cfg: ModelConfig, hf_sd: dict[str, torch.Tensor]) ->
                 for e in range(cfg.num_experts)])
             out[n + "mlp.down_proj"] = torch.stack(
                 [g(p + f"mlp.experts.{e}.down_proj.weight") for e in range(cfg.num_experts)])
+        elif not cfg.mlp_gated:
+            out[n + "mlp.up_proj.weight"] = g(p + "mlp.up_proj.weight")
+            out[n + "mlp.down_proj.weight"] = g(p + "mlp.down_proj.weight")
+            out[n + "mlp.act_alpha_p"] = g(p + "mlp.act_fn.alpha_p").reshape(1)
+            out[n + "mlp.act_alpha_n"] = g(p + "mlp.act_fn.alpha_n").reshape(1)
         else:
             out[n + "mlp.gate_up_proj.weight"] = torch.cat(
                 [g(p + "mlp.gate_proj.weight"), g(p + "mlp.up_proj.weight")], dim=0)
@@ -119,6 +126,13 @@ def native_to_hf_items(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tensor
                 yield p + f"self_attn.q_proj.{kind}", q
                 yield p + f"self_attn.k_proj.{kind}", k
                 yield p + f"self_attn.v_proj.{kind}", v
+            elif cfg.model_type == "apertus" and rest in ("input_layernorm.weight", "post_attention_layernorm.weight"):
+                yield p + ("attention_layernorm.weight" if rest.startswith("input") else "feedforward_layernorm.weight"), t
+            elif rest in ("mlp.act_alpha_p", "mlp.act_alpha_n"):
+                yield p + "mlp.act_fn." + rest[len("mlp.act_"):], t
+                if rest.endswith("_n"):  # the two constants of the activation are buffers of the HF module
+                    yield p + "mlp.act_fn.beta", torch.tensor(0.5, dtype=t.dtype)
+                    yield p + "mlp.act_fn.eps", torch.tensor(-1e-6, dtype=t.dtype)
             elif rest == "mlp.gate_up_proj.weight":
                 gte, up = t.chunk(2, dim=0)
                 yield p + "mlp.gate_proj.weight", gte

@@ -17,8 +17,11 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional
 
+import math
+
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from .. import ops
 from .config import ModelConfig
@@ -115,6 +118,32 @@ class DenseMLP(nn.Module):
 
             return tiled_call(self._plain, [self.gate_up_proj.weight, self.down_proj.weight], self.tile_shards, x)
         return self._plain(x)
+
+
+class XieluMLP(nn.Module):
+    """Apertus: ``down(xielu(up(x)))`` with xielu(v) = alpha_p v^2 + beta v for v > 0 and
+    alpha_n (expm1(min(v, eps)) - v) + beta v otherwise; alpha_p = softplus(a_p), alpha_n = beta + softplus(a_n) with one
+    learnable (a_p, a_n) pair per layer (transformers' ``ApertusMLP`` / ``XIELUActivation``; the reference serves the
+    family through verl/models/transformers/apertus.py)."""
+
+    BETA, EPS = 0.5, -1e-6
+
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.up_proj = Linear(cfg.hidden_size, cfg.intermediate_size, False, dtype, device)
+        self.down_proj = Linear(cfg.intermediate_size, cfg.hidden_size, False, dtype, device)
+        init = math.log(math.expm1(0.8))
+        self.act_alpha_p = nn.Parameter(torch.full((1,), init, dtype=dtype, device=device))
+        self.act_alpha_n = nn.Parameter(torch.full((1,), math.log(math.expm1(0.8 - self.BETA)), dtype=dtype, device=device))
+        self.tp_group = None
+
+    def forward(self, x):
+        v = self.up_proj(x).float()
+        ap = F.softplus(self.act_alpha_p.float())
+        an = self.BETA + F.softplus(self.act_alpha_n.float())
+        neg = (torch.expm1(torch.clamp(v, max=self.EPS)) - v) * an + self.BETA * v
+        h = torch.where(v > 0, ap * v * v + self.BETA * v, neg)
+        return self.down_proj(h.to(x.dtype))
 
 
 class MoEMLP(nn.Module):
@@ -309,7 +338,8 @@ class DecoderLayer(nn.Module):
         self.input_layernorm = RMSNormWeight(cfg.hidden_size, dtype, device)
         self.self_attn = Attention(cfg, dtype, device)
         self.post_attention_layernorm = RMSNormWeight(cfg.hidden_size, dtype, device)
-        self.mlp = MoEMLP(cfg, dtype, device) if cfg.is_moe else DenseMLP(cfg, dtype, device)
+        self.mlp = (MoEMLP(cfg, dtype, device) if cfg.is_moe else
+                    DenseMLP(cfg, dtype, device) if cfg.mlp_gated else XieluMLP(cfg, dtype, device))
 
     def forward(self, hidden, residual, batch: PackedBatch, rope):
         """(hidden, residual) -> (hidden, residual); the residual add is fused into the next norm."""
@@ -379,7 +409,7 @@ class CausalLM(nn.Module):
 
     def rope(self, device) -> tuple[torch.Tensor, torch.Tensor]:
         c = self.cfg
-        return ops.rope_tables(c.head_dim, c.max_position_embeddings, c.rope_theta, device)
+        return ops.rope_tables(c.head_dim, c.max_position_embeddings, c.rope_theta, device, c.extra.get("rope_scaling"))
 
     # --------------------------------------------------------------- forward
     def embed(self, batch: PackedBatch) -> torch.Tensor:

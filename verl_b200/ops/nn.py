@@ -84,10 +84,28 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: 
 _rope_cache: dict = {}
 
 
-def rope_tables(head_dim: int, max_pos: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
-    key = (head_dim, max_pos, float(theta), str(device))
+def rope_tables(head_dim: int, max_pos: int, theta: float, device, scaling: dict | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos / sin tables [max_pos, head_dim / 2]. ``scaling``: the HF ``rope_scaling`` / ``rope_parameters`` dict;
+    ``llama3`` (frequencies below the low-frequency cut divided by ``factor``, a smooth blend up to the high-frequency
+    cut: Llama 3.1+, Apertus) and ``linear`` (all frequencies divided by ``factor``) are implemented."""
+    kind = (scaling or {}).get("rope_type") or (scaling or {}).get("type") or "default"
+    key = (head_dim, max_pos, float(theta), str(device), kind, tuple(sorted((k, str(v)) for k, v in (scaling or {}).items())))
     if key not in _rope_cache:
         inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+        if kind == "llama3":
+            import math
+
+            factor = float(scaling.get("factor", 8.0))
+            lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+            orig = float(scaling.get("original_max_position_embeddings", 8192))
+            wavelen = 2 * math.pi / inv
+            smooth = ((orig / wavelen - lo) / (hi - lo)).clamp(0.0, 1.0)
+            blended = (1 - smooth) * inv / factor + smooth * inv
+            inv = torch.where(wavelen > orig / lo, inv / factor, torch.where(wavelen < orig / hi, inv, blended))
+        elif kind == "linear":
+            inv = inv / float(scaling.get("factor", 1.0))
+        elif kind not in ("default", "mrope"):
+            raise NotImplementedError(f"rope scaling type {kind!r} is not implemented")
         ang = torch.arange(max_pos, dtype=torch.float32, device=device)[:, None] * inv[None]
         _rope_cache[key] = (ang.cos().contiguous(), ang.sin().contiguous())
     return _rope_cache[key]

@@ -47,6 +47,8 @@ def tp_model_config(cfg: ModelConfig, tp_rank: int, tp_size: int) -> ModelConfig
 
     if tp_size == 1:
         return cfg
+    if not cfg.mlp_gated:
+        raise ValueError(f"tensor parallelism is not implemented for the {cfg.model_type} MLP layout")
     Hq, Hk = cfg.num_attention_heads, cfg.num_key_value_heads
     if Hq % tp_size != 0:
         raise ValueError(f"tensor_model_parallel_size {tp_size} does not divide {Hq} attention heads")

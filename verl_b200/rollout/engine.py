@@ -436,7 +436,7 @@ class NativeRolloutEngine:
         one scale per 128 x 128 block). Call after every weight sync: the trainer's bf16 weights are the source
         (quantise-on-resync of verl/utils/vllm/vllm_fp8_utils.py:182-431)."""
         self._fp8.clear()
-        if self.quantization != "fp8" or not self.on_gpu or self.cfg.is_moe:
+        if self.quantization != "fp8" or not self.on_gpu or self.cfg.is_moe or not self.cfg.mlp_gated:
             return
         from ..ops import fp8
 
@@ -505,7 +505,7 @@ class NativeRolloutEngine:
             attn = attend(li, layer, x)
             o = self._mm_partial(attn.reshape(T, c.q_size), layer.self_attn.o_proj.weight, 0, path)
             x, residual = self._reduce_norm(o, layer.post_attention_layernorm.weight, residual)
-            if c.is_moe:
+            if c.is_moe or not c.mlp_gated:  # routed experts / the two-matrix xIELU MLP: the module's own forward
                 d = self._to_partial(layer.mlp(x), 1, path)
             else:
                 d = self._mm_partial(ops.swiglu(self._mm(x, layer.mlp.gate_up_proj.weight)), layer.mlp.down_proj.weight,
