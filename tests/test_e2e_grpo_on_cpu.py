@@ -182,6 +182,27 @@ def test_grpo_with_tensor_parallel_rollout_replica(tmp_path, monkeypatch):
     assert abs(m.get("training/rollout_probs_diff_mean", 0.0)) < 1e-3
 
 
+def test_agent_loops_over_a_tensor_parallel_replica(tmp_path, monkeypatch):
+    """Server mode with rollout.tensor_model_parallel_size=2: the replica has ONE endpoint on its first rank; that
+    rank's engine thread announces every request, abort, cache operation and step to the other rank's engine thread,
+    which does the same to its slice of the model."""
+    import json
+
+    from verl_b200.trainer.main_ppo import run_ppo
+
+    monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
+    extra = ["actor_rollout_ref.rollout.tensor_model_parallel_size=2", "trainer.save_freq=-1", "trainer.experiment_name=tp2_agent",
+             "actor_rollout_ref.rollout.max_num_seqs=32", "actor_rollout_ref.rollout.agent.use_agent_loop=true",
+             "actor_rollout_ref.rollout.agent.num_workers=2", "data.return_raw_chat=true", "data.max_response_length=24",
+             "actor_rollout_ref.rollout.n=2"]
+    trainer = run_ppo(compose("ppo_trainer", _overrides(tmp_path, extra)), spmd=False)
+    assert trainer.async_rollout_mode and trainer.global_steps == 2 and len(trainer._rollout_server_handles) == 1
+    m = [json.loads(l) for l in open(tmp_path / "logs" / "cpu_e2e" / "tp2_agent.jsonl")][-1]["data"]
+    for key in ("actor/pg_loss", "actor/grad_norm", "response_length/mean", "agent_loop/generate_sequences/mean"):
+        assert key in m and math.isfinite(m[key]), key
+    assert m["response_length/mean"] > 0 and abs(m.get("training/rollout_probs_diff_mean", 0.0)) < 1e-3
+
+
 def test_unservable_rollout_parallelism_is_an_error(tmp_path):
     from verl_b200.trainer.main_ppo import run_ppo
 

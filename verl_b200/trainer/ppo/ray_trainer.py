@@ -310,12 +310,17 @@ class RayPPOTrainer:
         from ...experimental.agent_loop import AgentLoopManager
 
         if self.spmd:
+            if int(self.config.actor_rollout_ref.rollout.get("tensor_model_parallel_size", 1) or 1) > 1:
+                raise ValueError("rollouts through the agent loops with rollout.tensor_model_parallel_size > 1 need the "
+                                 "dispatching worker group (one driver that owns the replicas' endpoints); under an SPMD "
+                                 "launch every rank drives its own requests. Use the batched rollout or TP = 1.")
             worker = self.actor_rollout_wg.worker.worker_dict["actor_rollout"]
             handles = [worker.get_async_server()]
         else:
             from ...workers.rollout.async_server import HttpServerHandle
 
-            handles = [HttpServerHandle(a) for a in self.actor_rollout_wg.start_rollout_server()]
+            # one endpoint per replica: the followers of a tensor-parallel replica answer with an empty address
+            handles = [HttpServerHandle(a) for a in self.actor_rollout_wg.start_rollout_server() if a]
         self.async_rollout_manager = AgentLoopManager(self.config, server_handles=handles, tokenizer=self.tokenizer,
                                                       processor=self.processor)
         self._rollout_server_handles = handles

@@ -270,6 +270,15 @@ class ActorRolloutRefWorker(_WorkerBase):
             if self.dp_rank in ranks:
                 mine = grp
         self.tp_group = mine
+        # control group of the replica for the server mode (object broadcasts between the engine threads; gloo so
+        # that a waiting follower does not occupy the GPU)
+        ctrl = None
+        for g in range(self.world // tp):
+            ranks = list(range(g * tp, (g + 1) * tp))
+            grp = dist.new_group(ranks, backend="gloo")
+            if self.dp_rank in ranks:
+                ctrl = grp
+        self.tp_ctrl_group = ctrl
         if self.device.type == "cuda":
             from ..parallel.peer_comm import PeerComm
 
@@ -508,12 +517,13 @@ class ActorRolloutRefWorker(_WorkerBase):
 
             rc = self.rollout_cfg
             self.rollout_engine.wake_up()
+            tp_group = getattr(self, "tp_ctrl_group", None) if self.rollout_tp > 1 else None
             self._async_server = NativeAsyncServer(self.rollout_engine, response_length=int(rc.response_length),
-                                                   prompt_length=int(rc.prompt_length))
-            if rc.free_cache_engine:
+                                                   prompt_length=int(rc.prompt_length), tp_group=tp_group)
+            if rc.free_cache_engine and self._async_server.tp_leader:
                 import asyncio
 
-                asyncio.run(self._async_server.sleep())
+                asyncio.run(self._async_server.sleep())  # under tensor parallelism the followers mirror it
         return self._async_server
 
     @register(dispatch_mode=Dispatch.ONE_TO_ALL)
@@ -523,7 +533,9 @@ class ActorRolloutRefWorker(_WorkerBase):
         if getattr(self, "_async_server_address", None) is None:
             from .rollout.async_server import serve_in_thread
 
-            self._async_server_address = serve_in_thread(self.get_async_server(), address)
+            srv = self.get_async_server()
+            # a tensor-parallel replica has ONE endpoint, on its first rank; the other ranks follow it ("" here)
+            self._async_server_address = serve_in_thread(srv, address) if srv.tp_leader else ""
         return self._async_server_address
 
 

@@ -23,8 +23,24 @@ from ...rollout import NativeRolloutEngine, SamplingParams, TokenOutput
 
 class NativeAsyncServer:
     def __init__(self, engine: NativeRolloutEngine, response_length: int = 512, prompt_length: int = 512,
-                 coalesce_ms: float = 20.0):
+                 coalesce_ms: float = 20.0, tp_group=None):
+        """``tp_group``: control group (gloo) of the ranks of a tensor-parallel replica. The first rank of the group is
+        the leader: it takes the requests; every iteration of its engine thread broadcasts what it is about to do (new
+        requests, aborts, wake-up / sleep / cache operations, whether to step) and the other ranks' engine threads do
+        the same to their slice of the model, so that all schedulers stay identical and every ``step()`` is one
+        collective forward of the replica (role of the rank-0 driver with tensor-parallel workers behind
+        verl/workers/rollout/vllm_rollout/vllm_async_server.py)."""
         self.engine = engine
+        self.tp_group = tp_group
+        self.tp_leader = True
+        self._tp_src = 0
+        if tp_group is not None:
+            import torch.distributed as dist
+
+            ranks = dist.get_process_group_ranks(tp_group)
+            self._tp_src = ranks[0]
+            self.tp_leader = dist.get_rank() == ranks[0]
+        self._ctrl: list = []  # engine operations queued for the engine thread (replica-wide under tensor parallelism)
         self.coalesce_s = float(coalesce_ms) / 1e3  # longest wait for the rest of a burst of new requests
         self.response_length, self.prompt_length = response_length, prompt_length
         self._lock = threading.Lock()
@@ -46,10 +62,20 @@ class NativeAsyncServer:
             import torch
 
             torch.cuda.set_device(eng.device)  # the engine thread launches on the engine's GPU
-        while not self._stop:
+        while True:
+            if not self.tp_leader:
+                # follower of a tensor-parallel replica: do what the leader announces
+                cmd = self._bcast(None)
+                if self._apply(cmd) == "stop":
+                    return
+                continue
+            if self._stop:
+                self._bcast({"stop": True})
+                return
             with self._lock:
                 inbox, self._inbox = self._inbox, []
                 aborts, self._aborts = self._aborts, []
+                ctrl, self._ctrl = self._ctrl, []
             if inbox:
                 # Requests of one batch arrive within a few milliseconds of each other. Taking them in one go lets the
                 # prefill see them together and the decode batch start at its full size, instead of growing through
@@ -62,6 +88,16 @@ class NativeAsyncServer:
                         more, self._inbox = self._inbox, []
                     quiet = 0 if more else quiet + 1
                     inbox.extend(more)
+            for name, args, done in ctrl:
+                try:
+                    if self.tp_group is not None:
+                        self._bcast({"ctrl": [(name, args)]})
+                    getattr(eng, name)(*args)
+                    done.set_result(None)
+                except Exception as e:
+                    done.set_exception(e)
+            if self.tp_group is not None and (inbox or aborts):
+                self._bcast({"add": inbox, "abort": aborts})
             for rid, prompt, sp in inbox:
                 try:
                     eng.add_request(rid, prompt, sp)
@@ -81,6 +117,8 @@ class NativeAsyncServer:
                 continue
             self._idle.clear()
             try:
+                if self.tp_group is not None:
+                    self._bcast({"step": True})
                 outs = eng.step()
             except Exception as e:  # fail every waiter rather than hang them
                 with self._lock:
@@ -94,6 +132,47 @@ class NativeAsyncServer:
                 fut = self._pending.pop(o.request_id, None)
                 if fut is not None and not fut.done():
                     fut.set_result(o)
+
+    # ------------------------------------------------- tensor-parallel lockstep
+    def _bcast(self, cmd):
+        import torch.distributed as dist
+
+        box = [cmd]
+        dist.broadcast_object_list(box, src=self._tp_src, group=self.tp_group)
+        return box[0]
+
+    def _apply(self, cmd: dict):
+        """A follower's side of one announcement."""
+        eng = self.engine
+        if cmd.get("stop"):
+            return "stop"
+        for name, args in cmd.get("ctrl", ()):
+            getattr(eng, name)(*args)
+        for rid, prompt, sp in cmd.get("add", ()):
+            try:
+                eng.add_request(rid, prompt, sp)
+            except Exception:
+                pass  # the leader saw the same error and failed the request
+        for rid in cmd.get("abort", ()):
+            eng.abort_request(rid)
+        if cmd.get("step"):
+            try:
+                eng.step()
+            except Exception:
+                eng.abort_all_requests()  # as the leader does
+        return None
+
+    def _engine_op(self, name: str, *args):
+        """Run an engine operation: directly without tensor parallelism, through the engine thread (and with it on
+        every rank of the replica) otherwise."""
+        if self.tp_group is None:
+            getattr(self.engine, name)(*args)
+            return None
+        done: Future = Future()
+        with self._lock:
+            self._ctrl.append((name, args, done))
+        self._wake.set()
+        return done
 
     # ------------------------------------------------------------------ public
     def submit(self, prompt_ids: list[int], sampling_params: Optional[dict] = None, request_id: Optional[str] = None) -> Future:
@@ -146,15 +225,21 @@ class NativeAsyncServer:
         self._paused = True
 
     async def wake_up(self, tags: Optional[list[str]] = None):
-        self.engine.wake_up(tags)
+        fut = self._engine_op("wake_up", tags)
+        if fut is not None:
+            await asyncio.wrap_future(fut)
 
     async def sleep(self):
         await self.wait_for_requests_to_drain()
         self._idle.wait(5.0)
-        self.engine.sleep()
+        fut = self._engine_op("sleep")
+        if fut is not None:
+            await asyncio.wrap_future(fut)
 
     async def clear_kv_cache(self):
-        self.engine.clear_kv_cache()
+        fut = self._engine_op("clear_kv_cache")
+        if fut is not None:
+            await asyncio.wrap_future(fut)
 
     async def start_profile(self, **kwargs):
         import torch
