@@ -75,3 +75,31 @@ def test_guard_bands_catch_writes_outside_an_allocation():
         torch.empty(4, device="meta")
         torch.empty(4, device="cpu", pin_memory=False)
         assert g.count == 1
+
+
+def test_server_adapter_generates_batches_on_the_attached_engine():
+    """The rollout backend object (registry names of the reference's engines resolve to it) runs batch generation
+    itself: greedy outputs equal the argmax continuation of the same model."""
+    import torch
+
+    from verl_b200 import DataProto
+    from verl_b200.models import CausalLM, PackedBatch, preset
+    from verl_b200.rollout import NativeRolloutEngine
+    from verl_b200.workers.rollout.base import get_rollout_class
+
+    cfg = preset("tiny-qwen2")
+    model = CausalLM(cfg, dtype=torch.float32).init_weights(0)
+    eng = NativeRolloutEngine(model, max_num_seqs=4, max_model_len=48, max_num_batched_tokens=64, num_blocks=32)
+    adapter = get_rollout_class("vllm", "async")({"response_length": 5, "ignore_eos": True}, cfg)
+    adapter.attach(eng)
+    ids = torch.randint(5, 2000, (3, 10), generator=torch.Generator().manual_seed(0))
+    mask = torch.ones(3, 10, dtype=torch.long)
+    mask[0, :4] = 0
+    out = adapter.generate_sequences(DataProto.from_dict({"input_ids": ids, "attention_mask": mask}, meta_info={"do_sample": False}))
+    assert out.batch["responses"].shape == (3, 5) and out.batch["input_ids"].shape == (3, 15)
+    for b in range(3):
+        seq = out.batch["input_ids"][b][out.batch["attention_mask"][b].bool()]
+        n = seq.numel()
+        with torch.no_grad():
+            logits = model(PackedBatch(seq, torch.arange(n), torch.tensor([0, n], dtype=torch.int32), n))
+        assert logits[n - 6 : n - 1].argmax(-1).tolist() == out.batch["responses"][b].tolist()
