@@ -436,13 +436,18 @@ class NativeRolloutEngine:
         one scale per 128 x 128 block). Call after every weight sync: the trainer's bf16 weights are the source
         (quantise-on-resync of verl/utils/vllm/vllm_fp8_utils.py:182-431)."""
         self._fp8.clear()
-        if self.quantization != "fp8" or not self.on_gpu or self.cfg.is_moe or not self.cfg.mlp_gated:
+        if self.quantization != "fp8" or not self.on_gpu:
             return
         from ..ops import fp8
 
+        # routed experts (no grouped fp8 GEMM) and the two-matrix xIELU MLP stay in bf16: for those models the
+        # attention projections alone are quantised
+        dense_mlp = not self.cfg.is_moe and self.cfg.mlp_gated
         for layer in self.model.layers:
-            for w in (layer.self_attn.qkv_proj.weight, layer.self_attn.o_proj.weight, layer.mlp.gate_up_proj.weight,
-                      layer.mlp.down_proj.weight):
+            ws = [layer.self_attn.qkv_proj.weight, layer.self_attn.o_proj.weight]
+            if dense_mlp:
+                ws += [layer.mlp.gate_up_proj.weight, layer.mlp.down_proj.weight]
+            for w in ws:
                 if w.numel():
                     self._fp8[id(w)] = fp8.quantize_weight(w.data)
 
