@@ -168,6 +168,8 @@ def build_config(args, world: int):
         f"actor_rollout_ref.actor.ppo_mini_batch_size={global_prompts}", "actor_rollout_ref.actor.use_dynamic_bsz=true",
         f"actor_rollout_ref.actor.ppo_max_token_len_per_gpu={args.max_token_len}", "actor_rollout_ref.actor.use_kl_loss=true",
         "actor_rollout_ref.actor.kl_loss_coef=0.001", "actor_rollout_ref.actor.optim.lr=1e-6",
+        # the rule-based reward runs on a host thread while the GPUs compute the log-probs (an option of the reference)
+        "reward_model.launch_reward_fn_async=true",
     ]
     if args.config == 2:
         # PPO with a critic: GAE (gamma = lambda = 1), value clip 0.5, KL against the reference policy in the reward,

@@ -203,6 +203,25 @@ def test_agent_loops_over_a_tensor_parallel_replica(tmp_path, monkeypatch):
     assert m["response_length/mean"] > 0 and abs(m.get("training/rollout_probs_diff_mean", 0.0)) < 1e-3
 
 
+def test_async_reward_gives_the_same_step_as_the_synchronous_one(tmp_path, monkeypatch):
+    """reward_model.launch_reward_fn_async: the rule-based reward runs on a host thread during the log-prob passes and is
+    joined before the advantages (with batch balancing on, so rows are permuted before the reward starts)."""
+    import json
+
+    from verl_b200.trainer.main_ppo import run_ppo
+
+    monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
+    res = {}
+    for flag in ("false", "true"):
+        extra = ["trainer.n_gpus_per_node=1", "trainer.save_freq=-1", f"trainer.experiment_name=rw_{flag}",
+                 f"reward_model.launch_reward_fn_async={flag}", "trainer.balance_batch=true", "trainer.total_training_steps=1"]
+        run_ppo(compose("ppo_trainer", _overrides(tmp_path, extra)), spmd=True)
+        res[flag] = [json.loads(l) for l in open(tmp_path / "logs" / "cpu_e2e" / f"rw_{flag}.jsonl")][-1]["data"]
+    for key in ("critic/score/mean", "actor/pg_loss", "actor/grad_norm", "critic/advantages/mean"):
+        assert abs(res["true"][key] - res["false"][key]) < 1e-6 * max(1.0, abs(res["false"][key])), key
+    assert "timing_s/reward_wait" in res["true"]
+
+
 def test_unservable_rollout_parallelism_is_an_error(tmp_path):
     from verl_b200.trainer.main_ppo import run_ppo
 

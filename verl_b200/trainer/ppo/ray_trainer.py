@@ -576,12 +576,37 @@ class RayPPOTrainer:
         with marked_timer("reward", timing_raw, "yellow"):
             if self.use_rm and "rm_scores" not in batch.batch.keys() and self.rm_wg is not None:
                 batch = batch.union(self.rm_wg.compute_rm_score(batch))
-            reward_tensor, extra = compute_reward(batch, self.reward_fn)
-            batch.batch["token_level_scores"] = reward_tensor
-            if extra:
-                batch.non_tensor_batch.update({k: np.array(v, dtype=object) for k, v in extra.items()
-                                               if len(v) == len(batch)})
+            fg = self.config.algorithm.get("filter_groups") or {}
+            rm_cfg = self.config.get("reward_model") or {}
+            if bool(rm_cfg.get("launch_reward_fn_async", False)) and not fg.get("enable", False):
+                # the rule-based reward runs on a host thread while the GPUs compute the log-probs; joined before the
+                # advantages (reward_model.launch_reward_fn_async of the reference, verl/trainer/ppo/ray_trainer.py).
+                # Dynamic sampling needs the scores at once and keeps the synchronous path.
+                # Rows must not be permuted after this point, so the sequence-length
+                # balancing of the batch happens now instead of at the start of the training part.
+                if self.config.trainer.get("balance_batch", True):
+                    self._balance_batch(batch, {})
+                    batch.meta_info["batch_balanced"] = True
+                if not hasattr(self, "_reward_futures"):
+                    self._reward_futures = {}
+                # kept on the trainer (a future cannot travel to worker processes), keyed by the batch's first sample
+                self._reward_futures[str(batch.non_tensor_batch["uid"][0])] = compute_reward_async(batch, reward_fn=self.reward_fn)
+                return batch
+            self._attach_reward(batch, *compute_reward(batch, self.reward_fn))
         return batch
+
+    @staticmethod
+    def _attach_reward(batch: DataProto, reward_tensor, extra) -> None:
+        batch.batch["token_level_scores"] = reward_tensor
+        if extra:
+            batch.non_tensor_batch.update({k: np.array(v, dtype=object) for k, v in extra.items() if len(v) == len(batch)})
+
+    def _join_reward(self, batch: DataProto, timing_raw: dict) -> None:
+        fut = getattr(self, "_reward_futures", {}).pop(str(batch.non_tensor_batch["uid"][0]), None) \
+            if "uid" in batch.non_tensor_batch else None
+        if fut is not None:
+            with marked_timer("reward_wait", timing_raw, "yellow"):
+                self._attach_reward(batch, *fut.result())
 
     def train_step(self, batch_dict: dict) -> dict:
         """One RL step on one (global, or per-rank in SPMD mode) batch of prompts. Returns the step's metrics.
@@ -637,7 +662,7 @@ class RayPPOTrainer:
         sync. Split out so that asynchronous trainers can feed batches produced elsewhere."""
         cfg = self.config
         if True:
-            if cfg.trainer.get("balance_batch", True):
+            if cfg.trainer.get("balance_batch", True) and not batch.meta_info.pop("batch_balanced", False):
                 self._balance_batch(batch, metrics)
             batch.meta_info["global_token_num"] = torch.sum(batch.batch["attention_mask"], dim=-1).tolist()
             # under an SPMD launch every rank drives the trainer on its own shard of the batch: the token list is
@@ -669,6 +694,7 @@ class RayPPOTrainer:
             if self.use_critic:
                 with marked_timer("values", timing_raw, "cyan"):
                     batch = batch.union(self.critic_wg.compute_values(batch))
+            self._join_reward(batch, timing_raw)
             with marked_timer("adv", timing_raw, "brown"):
                 if cfg.algorithm.get("use_kl_in_reward", False):
                     batch, kl_m = apply_kl_penalty(batch, self.kl_ctrl_in_reward, cfg.algorithm.kl_penalty)
