@@ -147,11 +147,6 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* d
 }
 
 // Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes).
-// Hint: bring a tile into L2 ahead of the load that will move it into shared memory (no shared memory, no barrier).
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* desc, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(desc), "r"(x), "r"(y) : "memory");
-}
-
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(smem_dst)),

@@ -53,7 +53,6 @@ struct DecodeTcParams {
   float* o_part;
   float* ml_part;
   int* status;
-  int l2_prefetch;  // tiles of lookahead that the producer requests into L2 beyond the shared-memory ring (0 = off)
 };
 
 // byte offset of element (row r, col k) inside a K-major, 128-byte-swizzled operand of `rows` rows whose
@@ -154,29 +153,9 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       const int* bt = p.block_table + (long long)b * p.max_blocks;
-      // The ring holds three tiles; under load a tile takes several microseconds from DRAM, more than the ring can
-      // cover. Tiles further ahead are requested into L2 (a hint: no shared memory, no barrier), so that the ring's
-      // own loads find them there.
-      auto prefetch_tile = [&](int tp) {
-        const CUtensorMap* tmp = (tp & 1) ? &tmV : &tmK;
-        const int pg0 = (c_begin + (tp >> 1)) * pages_per_chunk;
-        for (int pg = 0; pg < pages_per_chunk; ++pg) {
-          const int pi = pg0 + pg;
-          if (pi >= n_pages) break;
-          const int rel = pi - page_base;
-          const int blk = rel < TC_BT_MAX ? bt_s[rel] : bt[pi];
-          const int row = (blk * p.Hk + h) * p.block_size;
-          tma_prefetch_l2_2d(tmp, 0, row);
-          tma_prefetch_l2_2d(tmp, 64, row);
-        }
-      };
-      const int PF = p.l2_prefetch;
-      if (PF > 0)
-        for (int tp = TC_STAGES; tp < min(TC_STAGES + PF, 2 * n_chunks); ++tp) prefetch_tile(tp);
       for (int t = 0; t < 2 * n_chunks; ++t) {
         const int s = t % TC_STAGES;
         const uint32_t par = ((t / TC_STAGES) & 1) ^ 1;
-        if (PF > 0 && t + TC_STAGES + PF < 2 * n_chunks) prefetch_tile(t + TC_STAGES + PF);
         if (*abort_flag || !mbar_wait(&empty[s], par)) {
           report_error(p.status, ERR_WAIT_EMPTY, t);
           *abort_flag = 1;
@@ -510,26 +489,9 @@ paged_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tmK, const __
       for (int i = lane; i < cnt; i += 32) bt_s[i] = bt[page_base + i];
       __syncwarp();
       if (lane == 0) {
-        auto prefetch_tile = [&](int tp) {  // see the non-persistent kernel
-          const CUtensorMap* tmp = (tp & 1) ? &tmV : &tmK;
-          const int pg0 = (it.c_begin + (tp >> 1)) * pages_per_chunk;
-          for (int pg = 0; pg < pages_per_chunk; ++pg) {
-            const int pi = pg0 + pg;
-            if (pi >= n_pages) break;
-            const int rel = pi - page_base;
-            const int blk = rel < TC_BT_MAX ? bt_s[rel] : bt[pi];
-            const int row = (blk * p.Hk + it.h) * p.block_size;
-            tma_prefetch_l2_2d(tmp, 0, row);
-            tma_prefetch_l2_2d(tmp, 64, row);
-          }
-        };
-        const int PF = p.l2_prefetch;
-        if (PF > 0)
-          for (int tp = TC_STAGES; tp < min(TC_STAGES + PF, 2 * it.n_chunks); ++tp) prefetch_tile(tp);
         for (int t = 0; t < 2 * it.n_chunks; ++t, ++tg) {
           const int s = tg % TC_STAGES;
           const uint32_t par = ((tg / TC_STAGES) & 1) ^ 1;
-          if (PF > 0 && t + TC_STAGES + PF < 2 * it.n_chunks) prefetch_tile(t + TC_STAGES + PF);
           if (*abort_flag || !mbar_wait(&empty[s], par)) {
             report_error(p.status, ERR_WAIT_EMPTY, t);
             *abort_flag = 1;
@@ -806,11 +768,6 @@ extern "C" int vb_paged_decode_tc(const void* q, long long q_stride, const void*
   p.o_part = work;
   p.ml_part = work ? work + (long long)B * Hq * num_splits * TC_D : nullptr;
   p.status = status;
-  static const int l2_prefetch = []() {
-    const char* e = getenv("VERL_B200_DECODE_L2_PREFETCH");  // tiles of L2 lookahead beyond the ring; 0 = off
-    return e ? atoi(e) : 0;
-  }();
-  p.l2_prefetch = l2_prefetch < 0 ? 0 : (l2_prefetch > 16 ? 16 : l2_prefetch);
   static const bool persist = []() {
     const char* e = getenv("VERL_B200_DECODE_PERSIST");  // 0 = one CTA per (sequence, head, split)
     return !(e && e[0] == '0');

@@ -202,7 +202,7 @@ class NativeRolloutEngine:
                  gpu_memory_utilization: float = 0.5, enable_prefix_caching: bool = True, enforce_eager: bool = False,
                  seed: int = 0, eos_token_id: Optional[int] = None, cudagraph_capture_sizes: Optional[list] = None,
                  quantization: Optional[str] = None, tp_group=None, tp_comm=None, full_config: Optional[ModelConfig] = None,
-                 decode_burst: int = 8):
+                 decode_burst: int = 16):
         """``model``: the whole model, or (tensor parallelism) this rank's slice of it as laid out by
         :func:`verl_b200.parallel.reshard.tp_model_config`, with ``tp_group`` the replica's process group, ``tp_comm``
         its peer-memory communicator (CUDA) and ``full_config`` the architecture of the whole model. Every rank of a
