@@ -18,5 +18,6 @@ $LAUNCH -m verl_b200.trainer.main_ppo \
   actor_rollout_ref.rollout.log_prob_use_dynamic_bsz=true actor_rollout_ref.rollout.log_prob_max_token_len_per_gpu=32768 \
   actor_rollout_ref.ref.log_prob_use_dynamic_bsz=true actor_rollout_ref.ref.log_prob_max_token_len_per_gpu=32768 \
   actor_rollout_ref.actor.use_kl_loss=true actor_rollout_ref.actor.kl_loss_coef=0.001 actor_rollout_ref.actor.optim.lr=1e-6 \
+  actor_rollout_ref.rollout.tensor_model_parallel_size=${ROLLOUT_TP:-1} \
   trainer.n_gpus_per_node="$NGPU" trainer.nnodes=1 trainer.logger='[console]' trainer.val_before_train=false \
   trainer.total_epochs=1 trainer.save_freq=-1 trainer.test_freq=-1 "$@"

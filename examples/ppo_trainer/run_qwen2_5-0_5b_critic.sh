@@ -13,5 +13,6 @@ $LAUNCH -m verl_b200.trainer.main_ppo \
   actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=16 actor_rollout_ref.rollout.log_prob_micro_batch_size_per_gpu=32 \
   actor_rollout_ref.ref.log_prob_micro_batch_size_per_gpu=32 critic.ppo_micro_batch_size_per_gpu=16 \
   actor_rollout_ref.actor.use_kl_loss=false critic.optim.lr=1e-5 actor_rollout_ref.actor.optim.lr=1e-6 \
+  actor_rollout_ref.rollout.tensor_model_parallel_size=${ROLLOUT_TP:-1} \
   trainer.n_gpus_per_node="$NGPU" trainer.nnodes=1 trainer.logger='[console]' trainer.val_before_train=false \
   trainer.total_epochs=1 trainer.save_freq=-1 trainer.test_freq=-1 "$@"

@@ -178,7 +178,7 @@ def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch):
         "trainer.logger=[file]", "trainer.total_epochs=1", "trainer.total_training_steps=2", "trainer.val_before_train=false",
         f"trainer.default_local_dir={tmp_path}/ckpt", "trainer.save_freq=-1", "trainer.test_freq=-1",
         "trainer.project_name=cpu_e2e", "trainer.experiment_name=vl",
-        "data.train_files=synthetic:16:6:10:16:1900:0", "+data.synthetic_image_size=16", "data.val_files=null",
+        "data.train_files=synthetic:16:6:10:16:1900:0", "data.synthetic_image_size=16", "data.val_files=null",
         "data.train_batch_size=4", "data.max_prompt_length=32", "data.max_response_length=12", "data.shuffle=false",
         "algorithm.adv_estimator=grpo", "actor_rollout_ref.rollout.n=2", "actor_rollout_ref.rollout.max_num_seqs=8",
         "actor_rollout_ref.rollout.max_num_batched_tokens=128", "actor_rollout_ref.rollout.tensor_model_parallel_size=1",

@@ -156,6 +156,30 @@ def bench_attn(a):
         out[key + "_us"] = round(us3, 1)
         out[key + "_tflops"] = round(3.5 * flops / us3 / 1e6, 1)
     att._BWD_IMPL = "native"
+    if a.library:
+        # a newer yardstick than flash_attn 2: cuDNN's fused attention through torch SDPA (same shapes, dense batch)
+        try:
+            from torch.nn.attention import SDPBackend, sdpa_kernel
+
+            qd = q.view(B, S, Hq, D).transpose(1, 2).contiguous().requires_grad_(True)
+            kd = k.view(B, S, Hk, D).transpose(1, 2).contiguous().requires_grad_(True)
+            vd = v.view(B, S, Hk, D).transpose(1, 2).contiguous().requires_grad_(True)
+            dod = do.view(B, S, Hq, D).transpose(1, 2).contiguous()
+            sdpa = torch.nn.functional.scaled_dot_product_attention
+            with sdpa_kernel(SDPBackend.CUDNN_ATTENTION):
+                with torch.no_grad():
+                    us4 = _time(lambda: sdpa(qd, kd, vd, is_causal=True, enable_gqa=True), a.iters, a.warmup, graph=False)
+
+                def fb2():
+                    o = sdpa(qd, kd, vd, is_causal=True, enable_gqa=True)
+                    o.backward(dod)
+                    qd.grad = kd.grad = vd.grad = None
+
+                us5 = _time(fb2, a.iters, a.warmup, graph=False)
+            out.update(cudnn_sdpa_us=round(us4, 1), cudnn_sdpa_tflops=round(flops / us4 / 1e6, 1),
+                       cudnn_sdpa_fwd_bwd_us=round(us5, 1), cudnn_sdpa_fwd_bwd_tflops=round(3.5 * flops / us5 / 1e6, 1))
+        except Exception as e:  # backend not available for this shape / build
+            out["cudnn_sdpa_error"] = f"{type(e).__name__}: {str(e)[:160]}"
     return out
 
 
