@@ -103,3 +103,19 @@ def test_server_adapter_generates_batches_on_the_attached_engine():
         with torch.no_grad():
             logits = model(PackedBatch(seq, torch.arange(n), torch.tensor([0, n], dtype=torch.int32), n))
         assert logits[n - 6 : n - 1].argmax(-1).tolist() == out.batch["responses"][b].tolist()
+
+
+def test_jitter_flavour_of_the_native_library_builds_and_loads():
+    """``VERL_B200_JITTER=1`` selects the race-hunting build (``-DVB_JITTER=1``): it is a separate shared object with the
+    same C ABI; host-side entry points (the scheduler) work through it."""
+    import os
+    import subprocess
+    import sys
+
+    code = ("from verl_b200.ops import _lib; lib = _lib.load(); assert str(_lib._LIB_PATH).endswith('libverl_b200_jitter.so');"
+            "assert lib.vb_abi_version() == 1;"
+            "from verl_b200.rollout.engine import Scheduler; s = Scheduler(16, 16, 4, 64, 64); assert s.add(0, [1, 2, 3], 4) == 0;"
+            "print('JITTER_OK')")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600,
+                       env={**os.environ, "VERL_B200_JITTER": "1"}, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0 and "JITTER_OK" in r.stdout, (r.stdout[-500:], r.stderr[-2000:])
