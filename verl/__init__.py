@@ -64,6 +64,108 @@ _MOVED = {
     "verl.workers.sharding_manager.fsdp_ulysses": "verl_b200.workers.sharding_manager.fsdp_ulysses",
     "verl.tools.utils.mcp_clients.McpClientManager": "verl_b200.tools.mcp_base_tool",
     "verl.utils.dataset.rl_dataset": "verl_b200.utils.dataset.rl_dataset",
+    # backends of the reference whose role the one native engine / rollout engine plays here
+    "verl.workers.megatron_workers": "verl_b200.workers.engine_workers",
+    "verl.workers.actor.megatron_actor": "verl_b200.workers.actor.dp_actor",
+    "verl.workers.critic.megatron_critic": "verl_b200.workers.critic.dp_critic",
+    "verl.workers.engine.fsdp.utils": "verl_b200.workers.engine.utils",
+    "verl.workers.engine.megatron": "verl_b200.workers.engine.native",
+    "verl.workers.engine.megatron.transformer_impl": "verl_b200.workers.engine.native",
+    "verl.workers.engine.megatron.utils": "verl_b200.workers.engine.utils",
+    "verl.workers.engine.veomni": "verl_b200.workers.engine.native",
+    "verl.workers.engine.veomni.transformer_impl": "verl_b200.workers.engine.native",
+    "verl.workers.engine.veomni.utils": "verl_b200.workers.engine.utils",
+    "verl.workers.reward_model.megatron": "verl_b200.workers.reward_model",
+    "verl.workers.reward_model.megatron.reward_model": "verl_b200.workers.reward_model.base",
+    "verl.workers.rollout.naive": "verl_b200.workers.rollout.naive_rollout",
+    "verl.workers.rollout.naive.naive_rollout": "verl_b200.workers.rollout.naive_rollout",
+    "verl.workers.rollout.vllm_rollout": "verl_b200.workers.rollout.native_rollout",
+    "verl.workers.rollout.vllm_rollout.vllm_rollout": "verl_b200.workers.rollout.native_rollout",
+    "verl.workers.rollout.vllm_rollout.vllm_async_server": "verl_b200.workers.rollout.async_server",
+    "verl.workers.rollout.vllm_rollout.utils": "verl_b200.workers.rollout.utils",
+    "verl.workers.rollout.sglang_rollout": "verl_b200.workers.rollout.native_rollout",
+    "verl.workers.rollout.sglang_rollout.sglang_rollout": "verl_b200.workers.rollout.native_rollout",
+    "verl.workers.rollout.sglang_rollout.async_sglang_server": "verl_b200.workers.rollout.async_server",
+    "verl.workers.rollout.sglang_rollout.http_server_engine": "verl_b200.workers.rollout.async_server",
+    "verl.workers.rollout.sglang_rollout.utils": "verl_b200.workers.rollout.utils",
+    "verl.workers.rollout.trtllm_rollout.trtllm_rollout": "verl_b200.workers.rollout.native_rollout",
+    "verl.workers.rollout.trtllm_rollout.trtllm_async_server": "verl_b200.workers.rollout.async_server",
+    "verl.utils.checkpoint.megatron_checkpoint_manager": "verl_b200.utils.checkpoint.native_checkpoint",
+    "verl.utils.megatron.tensor_parallel": "verl_b200.parallel.vocab_parallel",
+    "verl.utils.megatron.sequence_parallel": "verl_b200.parallel.vocab_parallel",
+    "verl.utils.megatron.pipeline_parallel": "verl_b200.parallel.pipeline",
+    "verl.utils.megatron.memory": "verl_b200.utils.memory_buffer",
+    "verl.utils.metric.utils": "verl_b200.utils.metric",
+    "verl.utils.transformers_compat": "verl_b200.utils.import_utils",
+    "verl.utils.vllm.utils": "verl_b200.utils.import_utils",
+    "verl.utils.vllm.vllm_fp8_utils": "verl_b200.ops.fp8",
+    "verl.utils.sglang.sglang_fp8_utils": "verl_b200.ops.fp8",
+    "verl.utils.experimental.torch_functional": "verl_b200.ops.lmhead",
+    "verl.utils.profiler.empty_annotations": "verl_b200.utils.profiler.profile",
+    "verl.utils.fsdp_utils": "verl_b200.parallel.zero",
+    "verl.model_merger.megatron_model_merger": "verl_b200.model_merger.merger",
+    "verl.models.weight_loader_registry": "verl_b200.models.registry",
+    "verl.models.mcore.registry": "verl_b200.models.registry",
+    "verl.models.mcore.weight_converter": "verl_b200.models.hf_io",
+    "verl.models.mcore.loader": "verl_b200.models.hf_io",
+    "verl.models.mcore.saver": "verl_b200.models.hf_io",
+    "verl.models.mcore.config_converter": "verl_b200.models.config",
+    "verl.models.mcore.model_initializer": "verl_b200.models.registry",
+    "verl.models.mcore.model_forward": "verl_b200.models.transformer",
+    "verl.models.mcore.model_forward_fused": "verl_b200.ops.lmhead",
+    "verl.models.mcore.qwen2_5_vl": "verl_b200.models.vision",
+    "verl.models.mcore.qwen2_5_vl.model": "verl_b200.models.vision",
+    "verl.models.mcore.qwen2_5_vl.vision_model": "verl_b200.models.vision",
+    "verl.models.mcore.qwen2_5_vl.rope_utils": "verl_b200.models.vision",
+    "verl.models.transformers.tiled_mlp": "verl_b200.models.tiled_mlp",
+    "verl.models.transformers.qwen2_vl": "verl_b200.models.vision",
+    "verl.models.transformers.qwen2": "verl_b200.models.transformer",
+    "verl.models.transformers.llama": "verl_b200.models.transformer",
+    "verl.models.transformers.apertus": "verl_b200.models.transformer",
+    "verl.models.transformers.dense_common": "verl_b200.ops.lmhead",
+    "verl.models.transformers.monkey_patch": "verl_b200.trainer.ppo.prefix_grouper_utils",
+    "verl.models.llama.megatron.modeling_llama_megatron": "verl_b200.models.transformer",
+    "verl.models.llama.megatron.layers": "verl_b200.parallel.tensor_parallel",
+    "verl.models.llama.megatron.checkpoint_utils": "verl_b200.models.hf_io",
+    "verl.models.qwen2.megatron.modeling_qwen2_megatron": "verl_b200.models.transformer",
+    "verl.models.qwen2.megatron.layers": "verl_b200.parallel.tensor_parallel",
+    "verl.models.qwen2.megatron.checkpoint_utils": "verl_b200.models.hf_io",
+    "verl.single_controller.ray.base": "verl_b200.single_controller.ray",
+    "verl.checkpoint_engine.nixl_checkpoint_engine": "verl_b200.checkpoint_engine.base",
+    "verl.experimental.fully_async_policy.checkpoint_engine": "verl_b200.checkpoint_engine.pinned_bucket",
+    "verl.experimental.fully_async_policy.base_detach_sync": "verl_b200.experimental.fully_async_policy.param_sync",
+    "verl.experimental.fully_async_policy.fsdp_workers": "verl_b200.experimental.fully_async_policy.param_sync",
+    "verl.experimental.fully_async_policy.megatron_worker": "verl_b200.experimental.fully_async_policy.param_sync",
+    "verl.experimental.fully_async_policy.ray_trainer": "verl_b200.experimental.fully_async_policy.fully_async",
+    "verl.experimental.fully_async_policy.vllm_rollout": "verl_b200.workers.rollout.async_server",
+    "verl.experimental.fully_async_policy.vllm_rollout.vllm_async_server": "verl_b200.workers.rollout.async_server",
+    "verl.experimental.fully_async_policy.sglang_rollout": "verl_b200.workers.rollout.async_server",
+    "verl.experimental.fully_async_policy.sglang_rollout.sglang_async_server": "verl_b200.workers.rollout.async_server",
+    "verl.experimental.one_step_off_policy.main_ppo": "verl_b200.experimental.one_step_off_policy.ray_trainer",
+    "verl.experimental.one_step_off_policy.fsdp_workers": "verl_b200.experimental.fully_async_policy.param_sync",
+    "verl.experimental.one_step_off_policy.megatron_workers": "verl_b200.experimental.fully_async_policy.param_sync",
+    "verl.experimental.one_step_off_policy.distributed_utils": "verl_b200.utils.distributed",
+    "verl.experimental.one_step_off_policy.agent_loop": "verl_b200.experimental.agent_loop",
+    "verl.experimental.one_step_off_policy.agent_loop.agent_loop": "verl_b200.experimental.agent_loop.agent_loop",
+    "verl.experimental.transfer_queue.agent_loop": "verl_b200.experimental.agent_loop.agent_loop",
+    "verl.experimental.transfer_queue.main_ppo": "verl_b200.trainer.main_ppo",
+    "verl.experimental.transfer_queue.ray_trainer": "verl_b200.trainer.ppo.ray_trainer",
+    "verl.experimental.vla.models.openvla_oft": "verl_b200.models.openvla_oft",
+    "verl.experimental.vla.models.openvla_oft.modeling_prismatic": "verl_b200.models.openvla_oft",
+    "verl.experimental.vla.models.openvla_oft.configuration_prismatic": "verl_b200.models.openvla_oft",
+    "verl.experimental.vla.naive_rollout_rob": "verl_b200.experimental.vla.env_loop",
+    "verl.experimental.vla.rob_ray_trainer": "verl_b200.experimental.vla.env_loop",
+    "verl.experimental.vla.workers.env.env_worker": "verl_b200.experimental.vla.env_loop",
+    "verl.experimental.vla.workers.env.env_manager": "verl_b200.experimental.vla.env_loop",
+    "verl.utils.reward_score.prime_code.utils": "verl_b200.utils.reward_score.prime_code",
+    "verl.utils.reward_score.prime_code.testing_util": "verl_b200.utils.reward_score.prime_code",
+    "verl.utils.reward_score.prime_math.grader": "verl_b200.utils.reward_score.prime_math",
+    "verl.utils.reward_score.prime_math.math_normalize": "verl_b200.utils.reward_score.prime_math",
+    "verl.utils.reward_score.sandbox_fusion.utils": "verl_b200.utils.reward_score.sandbox_fusion",
+    "verl.experimental.one_step_off_policy.utils": "verl_b200.trainer.ppo.utils",
+    "verl.experimental.vla.dp_rob": "verl_b200.workers.actor.dp_actor",
+    "verl.experimental.vla.fsdp_workers": "verl_b200.workers.engine_workers",
+    "verl.utils.checkpoint.checkpoint_handler": "verl_b200.utils.checkpoint.checkpoint_handler",
 }
 
 

@@ -244,6 +244,9 @@ class CheckpointEngineManager:
             asyncio.run(pre())
         res = self.trainer.update_weights(global_steps)
         res = res.result() if hasattr(res, "result") else res
+        if isinstance(res, (list, tuple)):  # one future per worker: wait for every one before the replicas resume
+            res = [r.result() if hasattr(r, "result") else r for r in res]
+            res = res[0] if res else None
         if self.replicas and self.backend not in ("naive", "nvlink"):
             asyncio.run(post())
         return res

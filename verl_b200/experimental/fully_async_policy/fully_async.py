@@ -19,7 +19,7 @@ from typing import Optional
 import numpy as np
 
 from ...protocol import DataProto
-from ...trainer.ppo.ray_trainer import RayPPOTrainer
+from ...trainer.ppo.ray_trainer import RayPPOTrainer, _wait_all
 from .message_queue import MessageQueue
 from .param_sync import ParameterSynchronizer
 
@@ -275,10 +275,7 @@ class FullyAsyncTrainer:
 
 def _push_weights(trainer: RayPPOTrainer):
     def sync(version: int):
-        res = trainer.actor_rollout_wg.update_weights(version)
-        res = res.result() if hasattr(res, "result") else res
-        if isinstance(res, list):
-            res = res[0]
+        res = _wait_all(trainer.actor_rollout_wg.update_weights(version))
         return res if isinstance(res, dict) else {}
 
     return sync

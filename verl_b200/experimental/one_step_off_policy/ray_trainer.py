@@ -18,7 +18,7 @@ from typing import Optional
 
 import torch
 
-from ...trainer.ppo.ray_trainer import RayPPOTrainer, marked_timer
+from ...trainer.ppo.ray_trainer import RayPPOTrainer, _wait_all, marked_timer
 from ...utils.tracking import Tracking
 
 
@@ -49,9 +49,7 @@ class OneStepOffRayTrainer(RayPPOTrainer):
                           config=None) if self.rank == 0 else None
         self.global_steps = 0
         self._load_checkpoint()
-        res = self.actor_rollout_wg.update_weights(self.global_steps)
-        if hasattr(res, "result"):
-            res.result()
+        _wait_all(self.actor_rollout_wg.update_weights(self.global_steps))
         last: dict = {}
         it = iter(self._epoch_iterator())
         try:

@@ -211,3 +211,37 @@ def lmhead_logprob_entropy_tp(hidden: torch.Tensor, weight_shard: torch.Tensor, 
     rank. The gradient with respect to ``hidden`` is this rank's partial sum."""
     return _LMHeadTPFn.apply(hidden.contiguous(), weight_shard, labels.contiguous().long(), float(temperature),
                              int(vocab_offset), group)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The reference's call shapes over the same fused op.
+def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0,
+                         reduction: str = "none", dist_process_group=None) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(log_probs, entropy)`` of ``labels`` under ``softmax(hidden @ weight.T / temperature)`` with the argument list of
+    verl/utils/kernel/linear_cross_entropy.py:38-139. ``hidden`` may be ``[B, T, H]`` with ``labels [B, T]``; with a
+    ``dist_process_group`` ``weight`` is this rank's slice of the vocabulary (slices in rank order)."""
+    shape = labels.shape
+    h2, l1 = hidden.reshape(-1, hidden.shape[-1]), labels.reshape(-1)
+    if dist_process_group is not None and torch.distributed.get_world_size(dist_process_group) > 1:
+        off = torch.distributed.get_rank(dist_process_group) * weight.shape[0]
+        lp, ent = lmhead_logprob_entropy_tp(h2, weight, l1, temperature, off, dist_process_group)
+    else:
+        lp, ent = lmhead_logprob_entropy(h2, weight, l1, temperature)
+    if reduction == "mean":
+        return lp.mean(), ent.mean()
+    if reduction == "sum":
+        return lp.sum(), ent.sum()
+    return lp.view(shape), ent.view(shape)
+
+
+class FusedLinearForPPO(torch.nn.Module):
+    """Module form with the call shape of verl/utils/experimental/torch_functional.py:190-216. ``chunk_size`` is accepted
+    and unused: the kernel tiles the vocabulary itself and never holds a ``[T, V]`` tensor."""
+
+    def __init__(self, chunk_size: int = 512):
+        super().__init__()
+        self.chunk_size = chunk_size
+
+    def forward(self, hidden_states: torch.Tensor, vocab_weights: torch.Tensor, input_ids: torch.Tensor,
+                temperature: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+        return linear_cross_entropy(hidden_states, vocab_weights, input_ids.to(torch.int64), temperature)

@@ -165,6 +165,18 @@ class _StatefulLoader:
         self.epoch, self._skip = int(st.get("epoch", 0)), int(st.get("consumed", 0))
 
 
+def _wait_all(res):
+    """Result of a non-blocking worker-group call: a future, or one future per worker. Waits for EVERY worker (the
+    rollout servers take requests over HTTP, outside the workers' command queues, so a weight push still running on
+    one worker must not overlap the next generation) and returns the first worker's value."""
+    if hasattr(res, "result"):
+        res = res.result()
+    if isinstance(res, (list, tuple)):
+        res = [r.result() if hasattr(r, "result") else r for r in res]
+        res = res[0] if res else None
+    return res
+
+
 class RayPPOTrainer:
     def __init__(self, config, tokenizer, role_worker_mapping: dict, resource_pool_manager=None,
                  ray_worker_group_cls=None, processor=None, reward_fn=None, val_reward_fn=None, train_dataset=None,
@@ -718,10 +730,7 @@ class RayPPOTrainer:
                     out = self.actor_rollout_wg.update_actor(batch)
                 metrics.update(reduce_metrics(out.meta_info["metrics"]))
                 with marked_timer("update_weights", timing_raw, "red"):
-                    res = self.actor_rollout_wg.update_weights(self.global_steps)
-                    res = res.result() if hasattr(res, "result") else res
-                    if isinstance(res, list):
-                        res = res[0]
+                    res = _wait_all(self.actor_rollout_wg.update_weights(self.global_steps))
                     if isinstance(res, dict) and "resync_s" in res:
                         metrics["timing_s/resync"] = res["resync_s"]
             dump_dir = cfg.trainer.get("rollout_data_dir")
@@ -767,9 +776,7 @@ class RayPPOTrainer:
             logger = Tracking(tr.project_name, tr.experiment_name, list(tr.logger), config=to_container(cfg))
         self.global_steps = 0
         self._load_checkpoint()
-        res = self.actor_rollout_wg.update_weights(self.global_steps)
-        if hasattr(res, "result"):
-            res.result()
+        _wait_all(self.actor_rollout_wg.update_weights(self.global_steps))
         if self.val_reward_fn is not None and tr.get("val_before_train", True):
             val_metrics = self._validate()
             if val_metrics and logger is not None:

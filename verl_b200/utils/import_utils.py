@@ -5,6 +5,7 @@ from __future__ import annotations
 import importlib
 import importlib.util
 from functools import cache
+from typing import Optional
 
 from .py_functional import load_extern_object  # noqa: F401  (same loader, historical location)
 
@@ -54,3 +55,25 @@ def deprecated(replacement: str = ""):
         return wrapper
 
     return deco
+
+
+def is_version_in_range(package: str, min_version: Optional[str] = None, max_version: Optional[str] = None) -> bool:
+    """Installed version of ``package`` within ``[min_version, max_version]`` (either bound may be None)."""
+    import importlib.metadata
+
+    from packaging import version
+
+    try:
+        v = version.parse(importlib.metadata.version(package))
+    except importlib.metadata.PackageNotFoundError as e:
+        raise ModuleNotFoundError(f"The `{package}` package is not installed.") from e
+    return (min_version is None or version.parse(min_version) <= v) and (max_version is None or v <= version.parse(max_version))
+
+
+def is_transformers_version_in_range(min_version: Optional[str] = None, max_version: Optional[str] = None) -> bool:
+    """verl/utils/transformers_compat.py:41-60."""
+    return is_version_in_range("transformers", min_version, max_version)
+
+
+def is_version_ge(pkg: str = "transformers", minver: str = "0") -> bool:
+    return is_version_in_range(pkg, min_version=minver)

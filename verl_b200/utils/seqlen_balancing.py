@@ -120,10 +120,15 @@ def rearrange_micro_batches(batch, max_token_len: int, dp_group=None, num_batche
                             use_dynamic_bsz_balance: bool = True):
     """Split a TensorDict-like ``batch`` (needs ``attention_mask``) into micro-batches whose total
     token count is at most ``max_token_len``. Returns (micro_batches, index lists)."""
-    mask = batch["attention_mask"]
-    max_seq_len = mask.shape[-1]
+    ids = batch["input_ids"] if "input_ids" in batch.keys() else None
+    if ids is not None and ids.is_nested:  # the no-padding layout: one jagged row per sample, no mask
+        seq_lens = ids.offsets().diff()
+        max_seq_len, mask = int(seq_lens.max()), seq_lens
+    else:
+        mask = batch["attention_mask"]
+        max_seq_len = mask.shape[-1]
+        seq_lens = mask.sum(dim=1)
     assert max_token_len >= max_seq_len, f"max_token_len must be greater than the sequence length. Got {max_token_len=} and {max_seq_len=}"
-    seq_lens = mask.sum(dim=1)
     total = int(seq_lens.sum())
     num = min(len(seq_lens), ceildiv(total, max_token_len))
     if min_num_micro_batch is not None:

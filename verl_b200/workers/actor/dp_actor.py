@@ -24,11 +24,12 @@ from ...trainer.ppo.core_algos import agg_loss, get_policy_loss_fn, kl_penalty
 from ...utils.py_functional import append_to_dict
 from ...utils.seqlen_balancing import prepare_dynamic_batch, restore_dynamic_batch
 from ..engine.native import NativeEngine, _cfg
+from .base import BasePPOActor
 
 __all__ = ["DataParallelPPOActor"]
 
 
-class DataParallelPPOActor:
+class DataParallelPPOActor(BasePPOActor):
     def __init__(self, config, engine: NativeEngine):
         self.config = config
         self.engine = engine

@@ -18,11 +18,12 @@ from ...utils.py_functional import append_to_dict
 from ...utils.seqlen_balancing import prepare_dynamic_batch, restore_dynamic_batch
 from ...utils.torch_functional import masked_mean
 from ..engine.native import NativeEngine, _cfg
+from .base import BasePPOCritic
 
 __all__ = ["DataParallelPPOCritic"]
 
 
-class DataParallelPPOCritic:
+class DataParallelPPOCritic(BasePPOCritic):
     def __init__(self, config, engine: NativeEngine):
         self.config, self.engine, self.device = config, engine, engine.device
 
