@@ -1,9 +1,10 @@
 #!/usr/bin/env bash
-# GRPO on a Qwen2-VL architecture: images travel as multi_modal_inputs, the vision tower runs at admission in the
+# GRPO on a Qwen2-VL / Qwen2.5-VL / Qwen3-VL architecture: images travel as multi_modal_inputs, the vision tower runs at admission in the
 # rollout engine and trains with the embedding unit. Synthetic image prompts; a random-init preset by default.
 set -euo pipefail
 NGPU=${NGPU:-1}
-MODEL=${MODEL:-preset:tiny-qwen2-vl}         # preset:qwen2-vl-7b or a HF checkpoint directory for the real size
+MODEL=${MODEL:-preset:tiny-qwen2-vl}         # preset:tiny-qwen2.5-vl, preset:tiny-qwen3-vl; preset:qwen2-vl-7b,
+                                             # qwen2.5-vl-7b, qwen3-vl-8b or a HF checkpoint directory for the real size
 LAUNCH="python"
 [ "$NGPU" -gt 1 ] && LAUNCH="python -m torch.distributed.run --nnodes=1 --nproc-per-node $NGPU --master-addr 127.0.0.1 --master-port ${PORT:-29500}"
 $LAUNCH -m verl_b200.trainer.main_ppo \

@@ -60,7 +60,8 @@ def test_vl_logits_match_hf_and_names_round_trip():
         assert torch.equal(back[k], ref_sd[k]), k
 
 
-def test_vl_batch_through_engine_and_actor():
+@pytest.mark.parametrize("name", ["tiny-qwen2-vl", "tiny-qwen3-vl"])
+def test_vl_batch_through_engine_and_actor(name):
     """A padded batch with one image per sample: the actor's log-probs (multi_modal_inputs + [b, 4, S] position ids through
     the ZeRO engine) equal a direct forward of the same model, and an update step trains the vision tower too."""
     from verl_b200 import DataProto
@@ -74,7 +75,7 @@ def test_vl_batch_through_engine_and_actor():
 
     import numpy as np
 
-    cfg = preset("tiny-qwen2-vl")
+    cfg = preset(name)
     eng = NativeEngine(cfg, C(), C(lr=1e-3, clip_grad=1.0), device="cpu", seed=3).initialize()
     actor = DataParallelPPOActor(FSDPActorConfig(ppo_mini_batch_size=2, ppo_micro_batch_size_per_gpu=1, use_kl_loss=False), eng)
     g = torch.Generator().manual_seed(2)
@@ -117,22 +118,24 @@ def test_vl_batch_through_engine_and_actor():
         torch.testing.assert_close(lp[i, :n_resp], full_lp[-n_resp:], atol=1e-4, rtol=1e-4)
     data.batch["old_log_probs"] = lp
     data.batch["advantages"] = torch.randn(B, R, generator=g)
-    before = {k: v.clone() for k, v in eng.zero.named_full_tensors() if k.startswith("visual.blocks.0.qkv")}
+    watch = ("visual.blocks.0.qkv", "visual.deepstack.0.fc1", "visual.pos_embed")
+    before = {k: v.clone() for k, v in eng.zero.named_full_tensors() if k.startswith(watch)}
     with eng.train_mode():
         m = actor.update_policy(data)
     assert m["actor/grad_norm"][0] > 0
     after = {k: v for k, v in eng.zero.named_full_tensors() if k in before}
-    assert any(not torch.equal(before[k], after[k]) for k in before), "the vision tower did not train"
+    assert all(not torch.equal(before[k], after[k]) for k in before), "a part of the vision tower did not train"
 
 
-def test_vl_rollout_with_images_matches_full_recompute():
+@pytest.mark.parametrize("name", ["tiny-qwen2-vl", "tiny-qwen3-vl"])
+def test_vl_rollout_with_images_matches_full_recompute(name):
     """The paged engine with multimodal requests (vision tower at admission, placeholder embeddings and [3, T] positions
     in prefill, offset positions in burst decode) generates greedily what a full forward over the growing sequence
     predicts; two requests with the same text but other pixels do not share cached pages."""
     from verl_b200.models import CausalLM, PackedBatch, preset
     from verl_b200.rollout import NativeRolloutEngine, SamplingParams
 
-    cfg = preset("tiny-qwen2-vl")
+    cfg = preset(name)
     model = CausalLM(cfg, dtype=torch.float32).init_weights(5)
     g = torch.Generator().manual_seed(3)
     grid = torch.tensor([[1, 4, 4]])
@@ -162,7 +165,8 @@ def test_vl_rollout_with_images_matches_full_recompute():
     assert len(done["text"]) == 7
 
 
-def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch):
+@pytest.mark.parametrize("name", ["tiny-qwen2-vl", "tiny-qwen3-vl"])
+def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch, name):
     """The trainer path for images: dataset rows with pixels and grids (native image -> patch processing, placeholder
     expansion, [4, S] position ids), rollout with images, multimodal RoPE positions of the generated sequences, actor
     and reference log-probs, one update. Two steps of GRPO on the tiny Qwen2-VL preset with synthetic images."""
@@ -174,7 +178,7 @@ def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch):
 
     monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
     cfg = compose("ppo_trainer", [
-        "actor_rollout_ref.model.path=preset:tiny-qwen2-vl", "trainer.device=cpu", "trainer.n_gpus_per_node=1", "trainer.nnodes=1",
+        f"actor_rollout_ref.model.path=preset:{name}", "trainer.device=cpu", "trainer.n_gpus_per_node=1", "trainer.nnodes=1",
         "trainer.logger=[file]", "trainer.total_epochs=1", "trainer.total_training_steps=2", "trainer.val_before_train=false",
         f"trainer.default_local_dir={tmp_path}/ckpt", "trainer.save_freq=-1", "trainer.test_freq=-1",
         "trainer.project_name=cpu_e2e", "trainer.experiment_name=vl",
@@ -245,3 +249,69 @@ def test_qwen2_5_vl_tower_matches_hf():
     assert set(back) == set(ref_sd)
     for k in ref_sd:
         assert torch.equal(back[k], ref_sd[k]), k
+
+
+def test_qwen3_vl_matches_hf():
+    """Qwen3-VL: LayerNorm tower with an interpolated learned position table and full attention, deepstack features
+    added to the hidden states of the image tokens after the first decoder layers, a Qwen3 decoder (QK-norm) with
+    interleaved multimodal RoPE. Tower outputs, deepstack features and logits of a sequence with two images against
+    ``transformers``; HF names round-trip."""
+    pytest.importorskip("transformers")
+    try:
+        from transformers import Qwen3VLConfig, Qwen3VLForConditionalGeneration
+    except ImportError:
+        pytest.skip("this transformers version has no Qwen3-VL")
+
+    hf_cfg = Qwen3VLConfig(
+        text_config=dict(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=16, max_position_embeddings=512,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [3, 3, 2],
+                                          "mrope_interleaved": True}),
+        vision_config=dict(depth=3, hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, in_channels=3,
+                           patch_size=4, spatial_merge_size=2, temporal_patch_size=2, num_position_embeddings=36,
+                           deepstack_visual_indexes=[0, 2], hidden_act="gelu_pytorch_tanh"),
+        image_token_id=500, video_token_id=501, vision_start_token_id=502, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = Qwen3VLForConditionalGeneration(hf_cfg).float().eval()
+    with torch.no_grad():  # the defaults (zero biases, unit norms) would hide a swapped or dropped tensor
+        for n, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn_like(p))
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict())
+    assert cfg.is_vl and cfg.model_type == "qwen3_vl" and cfg.qk_norm and not cfg.attention_bias and cfg.mrope_interleaved
+    assert cfg.mrope_section == [3, 3, 2] and cfg.rope_theta == 10000.0 and cfg.head_dim == 16
+    native = hf_to_native_state_dict(cfg, dict(hf.state_dict()))
+    model = CausalLM(cfg, dtype=torch.float32)
+    assert model.visual.c.variant == "qwen3_vl" and model.num_deepstack == 2
+    missing, unexpected = model.load_state_dict(native, strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    grid = torch.tensor([[1, 8, 8], [1, 4, 12]])
+    g = torch.Generator().manual_seed(1)
+    pixels = torch.randn(64 + 48, 3 * 2 * 4 * 4, generator=g)
+    ids = torch.tensor([5, 502] + [500] * 16 + [7, 9, 502] + [500] * 12 + [11, 13])
+    pos3, delta = get_rope_index(ids, grid, image_token_id=500, spatial_merge_size=2)
+    with torch.no_grad():
+        vis_ref = hf.model.visual(pixels, grid_thw=grid)
+        out, taps = model.visual(pixels, grid, return_deepstack=True)
+        torch.testing.assert_close(out, vis_ref.pooler_output, atol=2e-4, rtol=2e-4)
+        assert len(taps) == 2
+        for a, b in zip(taps, vis_ref.deepstack_features):
+            torch.testing.assert_close(a, b, atol=2e-4, rtol=2e-4)
+        mm = (ids == 500).int()[None]
+        am = torch.ones(1, ids.numel(), dtype=torch.long)
+        # positions computed by the model itself: the rule for still images is the one of get_rope_index
+        ref = hf(input_ids=ids[None], pixel_values=pixels, image_grid_thw=grid, attention_mask=am, mm_token_type_ids=mm)
+        ref_pos, ref_delta = hf.model.get_rope_index(ids[None], mm, image_grid_thw=grid, attention_mask=am)
+        assert torch.equal(ref_pos[:, 0], pos3) and int(ref_delta) == delta
+        batch = PackedBatch(ids, pos3, torch.tensor([0, ids.numel()], dtype=torch.int32), ids.numel(), pixel_values=pixels,
+                            image_grid_thw=grid)
+        logits = model(batch)
+    torch.testing.assert_close(logits, ref.logits[0], atol=3e-4, rtol=3e-4)
+    back = native_to_hf_state_dict(cfg, native)
+    ref_sd = dict(hf.state_dict())
+    assert set(back) == set(ref_sd), (set(back) ^ set(ref_sd))
+    for k in ref_sd:
+        assert torch.equal(back[k], ref_sd[k]), k
+    # config round trip
+    cfg2 = ModelConfig.from_hf_dict(cfg.to_hf_dict())
+    assert cfg2.mrope_interleaved and cfg2.mrope_section == [3, 3, 2] and cfg2.extra["vision_config"]["deepstack_visual_indexes"] == [0, 2]

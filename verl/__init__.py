@@ -119,6 +119,7 @@ _MOVED = {
     "verl.models.mcore.qwen2_5_vl.rope_utils": "verl_b200.models.vision",
     "verl.models.transformers.tiled_mlp": "verl_b200.models.tiled_mlp",
     "verl.models.transformers.qwen2_vl": "verl_b200.models.vision",
+    "verl.models.transformers.qwen3_vl": "verl_b200.models.vision",
     "verl.models.transformers.qwen2": "verl_b200.models.transformer",
     "verl.models.transformers.llama": "verl_b200.models.transformer",
     "verl.models.transformers.apertus": "verl_b200.models.transformer",

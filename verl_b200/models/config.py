@@ -19,14 +19,16 @@ _ARCH_TO_TYPE = {
     "ApertusForCausalLM": "apertus",
     "Qwen2VLForConditionalGeneration": "qwen2_vl",
     "Qwen2_5_VLForConditionalGeneration": "qwen2_5_vl",
+    "Qwen3VLForConditionalGeneration": "qwen3_vl",
     "LlamaForTokenClassification": "llama",
     "Qwen2ForTokenClassification": "qwen2",
     "Qwen3ForTokenClassification": "qwen3",
 }
 _TYPE_TO_ARCH = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                  "qwen3_moe": "Qwen3MoeForCausalLM", "qwen2_vl": "Qwen2VLForConditionalGeneration",
-                 "qwen2_5_vl": "Qwen2_5_VLForConditionalGeneration", "apertus": "ApertusForCausalLM"}
-_VL_TYPES = ("qwen2_vl", "qwen2_5_vl")
+                 "qwen2_5_vl": "Qwen2_5_VLForConditionalGeneration", "apertus": "ApertusForCausalLM",
+                 "qwen3_vl": "Qwen3VLForConditionalGeneration"}
+_VL_TYPES = ("qwen2_vl", "qwen2_5_vl", "qwen3_vl")
 
 
 @dataclass
@@ -64,9 +66,9 @@ class ModelConfig:
         if self.head_dim is None:
             self.head_dim = self.hidden_size // self.num_attention_heads
         if self.attention_bias is None:
-            self.attention_bias = self.model_type in ("qwen2",) + _VL_TYPES
+            self.attention_bias = self.model_type in ("qwen2", "qwen2_vl", "qwen2_5_vl")
         if self.qk_norm is None:
-            self.qk_norm = self.model_type in ("qwen3", "qwen3_moe", "apertus")
+            self.qk_norm = self.model_type in ("qwen3", "qwen3_moe", "apertus", "qwen3_vl")
         if self.hidden_act is None:
             self.hidden_act = "xielu" if self.model_type == "apertus" else "silu"
 
@@ -88,6 +90,12 @@ class ModelConfig:
     @property
     def mrope_section(self):
         return self.extra.get("mrope_section")
+
+    @property
+    def mrope_interleaved(self) -> bool:
+        """Qwen3-VL: the frequencies of the three axes alternate (T H W T H W ... T T) instead of lying in three
+        consecutive sections."""
+        return bool(self.extra.get("mrope_interleaved", False))
 
     @property
     def image_token_id(self) -> int:
@@ -132,6 +140,8 @@ class ModelConfig:
             flat["model_type"] = mt
             extra_vl = {"vision_config": dict(d.get("vision_config") or {}),
                         "mrope_section": list(rope.get("mrope_section") or []) or None}
+            if rope.get("mrope_interleaved") or mt == "qwen3_vl":
+                extra_vl["mrope_interleaved"] = True
             if "rope_theta" not in flat and rope.get("rope_theta"):
                 flat["rope_theta"] = rope["rope_theta"]
             for k in ("image_token_id", "video_token_id", "vision_start_token_id", "vision_end_token_id"):
@@ -181,6 +191,9 @@ class ModelConfig:
                                                             "norm_topk_prob", "router_aux_loss_coef", "num_labels")}
             text["model_type"] = self.model_type + "_text"
             text["rope_scaling"] = {"type": "mrope", "mrope_section": list(extra.get("mrope_section") or [])}
+            if self.model_type == "qwen3_vl":
+                text["rope_scaling"] = {"rope_type": "default", "mrope_section": list(extra.get("mrope_section") or []),
+                                        "mrope_interleaved": True, "rope_theta": self.rope_theta}
             out = {"architectures": [_TYPE_TO_ARCH[self.model_type]], "model_type": self.model_type, "torch_dtype": "bfloat16",
                    "text_config": text, "vision_config": dict(extra.get("vision_config") or {}),
                    "tie_word_embeddings": self.tie_word_embeddings}
@@ -244,6 +257,24 @@ PRESETS: dict[str, dict] = {
                                                          hidden_act="silu"),
                                    "mrope_section": [8, 12, 12], "image_token_id": 2000, "video_token_id": 2001,
                                    "vision_start_token_id": 2002}),
+    "tiny-qwen3-vl": dict(model_type="qwen3_vl", vocab_size=2048, hidden_size=256, intermediate_size=512,
+                          num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64, rope_theta=5e6,
+                          eos_token_id=2,
+                          extra={"vision_config": dict(depth=4, hidden_size=64, out_hidden_size=256, intermediate_size=96,
+                                                       num_heads=2, in_channels=3, patch_size=4, spatial_merge_size=2,
+                                                       temporal_patch_size=2, num_position_embeddings=64,
+                                                       deepstack_visual_indexes=[0, 2], hidden_act="gelu_pytorch_tanh"),
+                                 "mrope_section": [12, 10, 10], "mrope_interleaved": True, "image_token_id": 2000,
+                                 "video_token_id": 2001, "vision_start_token_id": 2002}),
+    "qwen3-vl-8b": dict(model_type="qwen3_vl", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
+                        num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=5e6,
+                        eos_token_id=151645, max_position_embeddings=262144,
+                        extra={"vision_config": dict(depth=27, hidden_size=1152, out_hidden_size=4096, intermediate_size=4304,
+                                                     num_heads=16, in_channels=3, patch_size=16, spatial_merge_size=2,
+                                                     temporal_patch_size=2, num_position_embeddings=2304,
+                                                     deepstack_visual_indexes=[8, 16, 24], hidden_act="gelu_pytorch_tanh"),
+                               "mrope_section": [24, 20, 20], "mrope_interleaved": True, "image_token_id": 151655,
+                               "video_token_id": 151656, "vision_start_token_id": 151652}),
     "qwen2.5-vl-7b": dict(model_type="qwen2_5_vl", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
                           num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, rope_theta=1e6,
                           eos_token_id=151645,

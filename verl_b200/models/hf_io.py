@@ -24,6 +24,37 @@ _VIS_HF_TO_NATIVE = (("attn.qkv.", "qkv."), ("attn.proj.", "proj."), ("mlp.fc1."
                      ("patch_embed.proj.", "patch_embed."))
 
 
+# Qwen3-VL names its MLP and merger linears differently and adds a position table and the deepstack mergers
+_VIS3_HF_TO_NATIVE = (("attn.qkv.", "qkv."), ("attn.proj.", "proj."), ("mlp.linear_fc1.", "fc1."), ("mlp.linear_fc2.", "fc2."),
+                      ("visual.merger.norm.", "visual.ln_q."), ("visual.merger.linear_fc1.", "visual.merge_fc1."),
+                      ("visual.merger.linear_fc2.", "visual.merge_fc2."), ("deepstack_merger_list.", "deepstack."),
+                      ("patch_embed.proj.", "patch_embed."))
+
+
+def _vis3_hf_to_native(name: str) -> str:
+    for a, b in _VIS3_HF_TO_NATIVE:
+        name = name.replace(a, b)
+    if name.startswith("visual.deepstack."):
+        name = name.replace(".linear_fc1.", ".fc1.").replace(".linear_fc2.", ".fc2.")
+    return name
+
+
+def _vis3_native_to_hf(name: str) -> str:
+    if name.startswith("visual.deepstack."):
+        return name.replace("visual.deepstack.", "visual.deepstack_merger_list.").replace(".fc1.", ".linear_fc1.").replace(
+            ".fc2.", ".linear_fc2.")
+    for hf, nat in (("visual.merger.norm.", "visual.ln_q."), ("visual.merger.linear_fc1.", "visual.merge_fc1."),
+                    ("visual.merger.linear_fc2.", "visual.merge_fc2."), ("visual.patch_embed.proj.", "visual.patch_embed.")):
+        if name.startswith(nat):
+            return hf + name[len(nat):]
+    if name.startswith("visual.blocks."):
+        for hf, nat in ((".attn.qkv.", ".qkv."), (".attn.proj.", ".proj."), (".mlp.linear_fc1.", ".fc1."),
+                        (".mlp.linear_fc2.", ".fc2.")):
+            if nat in name:
+                return name.replace(nat, hf)
+    return name
+
+
 def _normalise_vl_keys(hf_sd: dict) -> dict:
     """Vision-language checkpoints: ``model.language_model.*`` (recent HF) or ``model.*`` (original release) for the
     decoder, ``model.visual.*`` or ``visual.*`` for the tower -> ``model.*`` and ``visual.*``."""
@@ -46,8 +77,11 @@ def hf_to_native_state_dict(cfg: ModelConfig, hf_sd: dict[str, torch.Tensor]) ->
             if not k.startswith("visual."):
                 continue
             n = k
-            for a, b in _VIS_HF_TO_NATIVE:
-                n = n.replace(a, b)
+            if cfg.model_type == "qwen3_vl":
+                n = _vis3_hf_to_native(n)
+            else:
+                for a, b in _VIS_HF_TO_NATIVE:
+                    n = n.replace(a, b)
             out[n] = v.reshape(v.shape[0], -1) if n == "visual.patch_embed.weight" else v
     g = lambda k: hf_sd[k]  # noqa: E731
     out["embed_tokens.weight"] = g("model.embed_tokens.weight")
@@ -95,6 +129,13 @@ def native_to_hf_items(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tensor
     vl = cfg.is_vl
     lm = "model.language_model." if vl else "model."
     for name, t in named:
+        if name.startswith("visual.") and cfg.model_type == "qwen3_vl":
+            if name == "visual.patch_embed.weight":
+                vc = cfg.extra["vision_config"]
+                t = t.reshape(t.shape[0], vc.get("in_channels", 3), vc.get("temporal_patch_size", 2), vc.get("patch_size", 16),
+                              vc.get("patch_size", 16))
+            yield "model." + _vis3_native_to_hf(name), t
+            continue
         if name.startswith("visual."):
             n = _vis_native_to_hf(name, gated=(cfg.extra.get("vision_config") or {}).get("intermediate_size") is not None
                                   or cfg.model_type == "qwen2_5_vl")

@@ -318,7 +318,8 @@ class Attention(nn.Module):
             q, _ = ops.rmsnorm(q.reshape(T * Hq, D), qw, cfg.rms_norm_eps)
             k, _ = ops.rmsnorm(k.reshape(T * Hk, D), kw, cfg.rms_norm_eps)
             qkv = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v], dim=-1)
-        qkv = ops.rope_qkv(qkv, batch.position_ids, rope[0], rope[1], Hq, Hk, D, mrope_section=cfg.mrope_section)
+        qkv = ops.rope_qkv(qkv, batch.position_ids, rope[0], rope[1], Hq, Hk, D, mrope_section=cfg.mrope_section,
+                           mrope_interleaved=cfg.mrope_interleaved)
         q = qkv[:, : cfg.q_size].view(T, Hq, D)
         k = qkv[:, cfg.q_size : cfg.q_size + cfg.kv_size].view(T, Hk, D)
         v = qkv[:, cfg.q_size + cfg.kv_size :].view(T, Hk, D)
@@ -412,17 +413,44 @@ class CausalLM(nn.Module):
         return ops.rope_tables(c.head_dim, c.max_position_embeddings, c.rope_theta, device, c.extra.get("rope_scaling"))
 
     # --------------------------------------------------------------- forward
-    def embed(self, batch: PackedBatch) -> torch.Tensor:
+    @property
+    def num_deepstack(self) -> int:
+        """Qwen3-VL: how many of the first decoder layers get a deepstack feature of the vision tower added to the hidden
+        states of the image tokens after them."""
+        return self.visual.num_deepstack if self.visual is not None else 0
+
+    def embed(self, batch: PackedBatch, with_deepstack: bool = False):
+        """Token embeddings ``[T, H]`` with the vision tower's outputs at the image placeholder tokens.
+        ``with_deepstack``: a tuple ``(embeddings, feature_0, ..., feature_{n-1})`` with ``n = num_deepstack``; feature i
+        (``[number of image tokens, H]``, zero rows when the batch has no image) is for :meth:`add_deepstack` after
+        decoder layer i."""
+        n_ds = self.num_deepstack if with_deepstack else 0
         if batch.inputs_embeds is not None:
-            return batch.inputs_embeds.to(self.embed_tokens.weight.dtype)
+            h = batch.inputs_embeds.to(self.embed_tokens.weight.dtype)
+            return (h,) + tuple(h.new_zeros(0, h.shape[1]) for _ in range(n_ds)) if with_deepstack else h
         h = ops.embedding(batch.input_ids, self.embed_tokens.weight)
+        taps = [h.new_zeros(0, h.shape[1]) for _ in range(n_ds)]
         if self.visual is not None and batch.pixel_values is not None and batch.pixel_values.numel():
             # the vision tower's outputs replace the embeddings of the image placeholder tokens, in order
-            img = self.visual(batch.pixel_values, batch.image_grid_thw).to(h.dtype)
+            if self.visual.num_deepstack:
+                img, feats = self.visual(batch.pixel_values, batch.image_grid_thw, return_deepstack=True)
+                if with_deepstack:
+                    taps = [f.to(h.dtype) for f in feats]
+            else:
+                img = self.visual(batch.pixel_values, batch.image_grid_thw)
+            img = img.to(h.dtype)
             where = torch.nonzero(batch.input_ids == self.cfg.image_token_id, as_tuple=True)[0]
             assert where.numel() == img.shape[0], f"{where.numel()} image tokens but {img.shape[0]} image embeddings"
             h = h.index_put((where,), img)
-        return h
+        return (h, *taps) if with_deepstack else h
+
+    def add_deepstack(self, hidden: torch.Tensor, batch: PackedBatch, feature: torch.Tensor) -> torch.Tensor:
+        """``hidden`` with ``feature`` added at the rows of the image placeholder tokens (the residual stream of a layer
+        is ``hidden + residual``, so adding to ``hidden`` adds to the stream)."""
+        if feature.shape[0] == 0:
+            return hidden
+        where = torch.nonzero(batch.input_ids == self.cfg.image_token_id, as_tuple=True)[0]
+        return hidden.index_add(0, where, feature.to(hidden.dtype))
 
     def final_norm(self, hidden, residual) -> torch.Tensor:
         out, _ = ops.rmsnorm(hidden, self.norm.weight, self.cfg.rms_norm_eps, residual)
@@ -430,15 +458,17 @@ class CausalLM(nn.Module):
 
     def forward_hidden(self, batch: PackedBatch) -> torch.Tensor:
         """Final-norm hidden states [T,H] of a packed batch."""
-        hidden = self.embed(batch)
+        hidden, *taps = self.embed(batch, with_deepstack=True)
         residual = None
         rope = self.rope(hidden.device)
-        for layer in self.layers:
+        for i, layer in enumerate(self.layers):
             if self.gradient_checkpointing and torch.is_grad_enabled():
                 hidden, residual = torch.utils.checkpoint.checkpoint(layer, hidden, residual, batch, rope,
                                                                      use_reentrant=False)
             else:
                 hidden, residual = layer(hidden, residual, batch, rope)
+            if i < len(taps):
+                hidden = self.add_deepstack(hidden, batch, taps[i])
         return self.final_norm(hidden, residual)
 
     def logprob_entropy(self, hidden: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0):

@@ -1,5 +1,5 @@
-"""Vision side of the Qwen2-VL family: ViT tower with 2-D rotary attention and the 2 x 2 patch merger, multimodal RoPE
-position ids, and the merge of image embeddings into the token stream.
+"""Vision side of the Qwen2-VL / Qwen2.5-VL / Qwen3-VL families: ViT tower with 2-D rotary attention and the 2 x 2 patch
+merger, multimodal RoPE position ids, and the merge of image embeddings into the token stream.
 
 The reference takes these models from ``transformers`` and patches their forward for packed inputs and mrope
 (verl/models/transformers/qwen2_vl.py:1-548; position ids: ``get_rope_index`` there and
@@ -38,11 +38,23 @@ class VisionConfig:
     intermediate_size: int = 0
     window_size: int = 112
     fullatt_block_indexes: tuple = (7, 15, 23, 31)
+    # Qwen3-VL (verl/models/transformers/qwen3_vl.py): LayerNorm blocks with a two-matrix tanh-GELU MLP and full
+    # attention, a learned position table of ``num_position_embeddings`` entries (a square grid, interpolated to the
+    # image's patch grid) added to the patch embeddings, and "deepstack" mergers that read the hidden states after the
+    # blocks ``deepstack_visual_indexes``; their outputs are added to the language model's hidden states
+    num_position_embeddings: int = 2304
+    deepstack_visual_indexes: tuple = ()
 
     @classmethod
     def from_dict(cls, d: dict) -> "VisionConfig":
         d = dict(d)
-        if "out_hidden_size" in d or d.get("variant") == "qwen2_5_vl":
+        if "deepstack_visual_indexes" in d or d.get("variant") == "qwen3_vl":
+            if "out_hidden_size" in d:
+                d["embed_dim"], d["hidden_size"] = d["hidden_size"], d.pop("out_hidden_size")
+            d["variant"] = "qwen3_vl"
+            d["deepstack_visual_indexes"] = tuple(d.get("deepstack_visual_indexes") or ())
+            d.setdefault("hidden_act", "gelu_pytorch_tanh")
+        elif "out_hidden_size" in d or d.get("variant") == "qwen2_5_vl":
             # the HF Qwen2.5-VL vision config calls the tower's width ``hidden_size`` and the language model's width
             # ``out_hidden_size``
             if "out_hidden_size" in d:
@@ -120,7 +132,7 @@ class VisionBlock(nn.Module):
             self.fc_up = _Lin(c.embed_dim, hid, True, dtype, device)
             self.fc1 = None
         else:
-            hid = int(c.embed_dim * c.mlp_ratio)
+            hid = int(c.intermediate_size) if c.variant == "qwen3_vl" else int(c.embed_dim * c.mlp_ratio)
             self.fc1 = _Lin(c.embed_dim, hid, True, dtype, device)
         self.fc2 = _Lin(hid, c.embed_dim, True, dtype, device)
 
@@ -139,8 +151,25 @@ class VisionBlock(nn.Module):
             h = F.silu(self.fc_gate(y)) * self.fc_up(y)
         else:
             h = self.fc1(y)
-            h = h * torch.sigmoid(1.702 * h) if c.hidden_act == "quick_gelu" else F.gelu(h)
+            if c.hidden_act == "quick_gelu":
+                h = h * torch.sigmoid(1.702 * h)
+            else:
+                h = F.gelu(h, approximate="tanh" if c.hidden_act == "gelu_pytorch_tanh" else "none")
         return x + self.fc2(h)
+
+
+class _DeepstackMerger(nn.Module):
+    """Merger of a deepstack tap: LayerNorm over the concatenated 2 x 2 unit, two linears with a GELU between."""
+
+    def __init__(self, c: VisionConfig, dtype, device):
+        super().__init__()
+        wide = c.embed_dim * c.spatial_merge_size ** 2
+        self.norm = _LayerNormW(wide, dtype, device)
+        self.fc1 = _Lin(wide, wide, True, dtype, device)
+        self.fc2 = _Lin(wide, c.hidden_size, True, dtype, device)
+
+    def forward(self, x):
+        return self.fc2(F.gelu(self.fc1(self.norm(x.view(-1, self.norm.weight.shape[0])))))
 
 
 class VisionTower(nn.Module):
@@ -150,12 +179,42 @@ class VisionTower(nn.Module):
     def __init__(self, c: VisionConfig, dtype=torch.bfloat16, device="cpu"):
         super().__init__()
         self.c = c
-        self.patch_embed = _Lin(c.patch_dim, c.embed_dim, False, dtype, device)  # the Conv3d of the reference, as a GEMM
+        # the Conv3d of the reference, as a GEMM
+        self.patch_embed = _Lin(c.patch_dim, c.embed_dim, c.variant == "qwen3_vl", dtype, device)
         self.blocks = nn.ModuleList([VisionBlock(c, dtype, device) for _ in range(c.depth)])
         self.ln_q = (_RMSNormW if c.variant == "qwen2_5_vl" else _LayerNormW)(c.embed_dim, dtype, device)
         m2 = c.spatial_merge_size ** 2
         self.merge_fc1 = _Lin(c.embed_dim * m2, c.embed_dim * m2, True, dtype, device)
         self.merge_fc2 = _Lin(c.embed_dim * m2, c.hidden_size, True, dtype, device)
+        self.pos_embed = self.deepstack = None
+        if c.variant == "qwen3_vl":
+            self.pos_embed = nn.Embedding(c.num_position_embeddings, c.embed_dim, dtype=dtype, device=device)
+            self.deepstack = nn.ModuleList([_DeepstackMerger(c, dtype, device) for _ in c.deepstack_visual_indexes])
+
+    @property
+    def num_deepstack(self) -> int:
+        return len(self.deepstack) if self.deepstack is not None else 0
+
+    def interpolated_pos_embed(self, grid_thw: torch.Tensor) -> torch.Tensor:
+        """Qwen3-VL: bilinear interpolation of the learned ``side x side`` position table to every image's ``h x w``
+        patch grid (corners aligned), repeated for every frame, in the merge-block order of the patches."""
+        c = self.c
+        side = int(c.num_position_embeddings ** 0.5)
+        m = c.spatial_merge_size
+        table = self.pos_embed.weight
+        out = []
+        for t, h, w in grid_thw.tolist():
+            ys = torch.linspace(0, side - 1, h, device=table.device)
+            xs = torch.linspace(0, side - 1, w, device=table.device)
+            y0, x0 = ys.long(), xs.long()
+            y1, x1 = (y0 + 1).clamp(max=side - 1), (x0 + 1).clamp(max=side - 1)
+            dy, dx = (ys - y0).to(table.dtype), (xs - x0).to(table.dtype)
+            pick = lambda yy, xx: table[(yy[:, None] * side + xx[None, :]).reshape(-1)].view(h, w, -1)  # noqa: E731
+            wy0, wy1, wx0, wx1 = (1 - dy)[:, None, None], dy[:, None, None], (1 - dx)[None, :, None], dx[None, :, None]
+            pe = pick(y0, x0) * wy0 * wx0 + pick(y0, x1) * wy0 * wx1 + pick(y1, x0) * wy1 * wx0 + pick(y1, x1) * wy1 * wx1
+            pe = pe.view(h // m, m, w // m, m, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
+            out.append(pe.repeat(t, 1))
+        return torch.cat(out, 0)
 
     def init_weights(self, seed: int = 0):
         g = torch.Generator(device=self.patch_embed.weight.device)
@@ -208,9 +267,12 @@ class VisionTower(nn.Module):
             base += t * gh * gw
         return torch.cat(order), torch.tensor(bounds, dtype=torch.int32)
 
-    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor, return_deepstack: bool = False):
+        """``return_deepstack`` (Qwen3-VL): also the list of deepstack features, each ``[N / merge^2, hidden_size]``."""
         c = self.c
         x = self.patch_embed(pixel_values.to(self.patch_embed.weight.dtype))
+        if self.pos_embed is not None:
+            x = x + self.interpolated_pos_embed(grid_thw).to(x.dtype)
         cos, sin = self.rot_pos(grid_thw)
         per_frame = (grid_thw[:, 1] * grid_thw[:, 2]).repeat_interleave(grid_thw[:, 0])
         cu = F.pad(per_frame.cumsum(0), (1, 0)).to(torch.int32)
@@ -230,15 +292,19 @@ class VisionTower(nn.Module):
             x = self.ln_q(x).view(-1, c.embed_dim * m2)
             out = self.merge_fc2(F.gelu(self.merge_fc1(x)))
             return out[torch.argsort(order)]
-        for blk in self.blocks:
+        taps = []
+        for i, blk in enumerate(self.blocks):
             x = blk(x, cu, max_len, cos, sin)
+            if self.deepstack is not None and i in c.deepstack_visual_indexes:
+                taps.append(self.deepstack[c.deepstack_visual_indexes.index(i)](x))
         x = self.ln_q(x).view(-1, c.embed_dim * m2)
-        return self.merge_fc2(F.gelu(self.merge_fc1(x)))
+        out = self.merge_fc2(F.gelu(self.merge_fc1(x)))
+        return (out, taps) if return_deepstack else out
 
 
 def get_rope_index(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tensor], image_token_id: int,
                    spatial_merge_size: int = 2, video_grid_thw: Optional[torch.Tensor] = None,
-                   video_token_id: Optional[int] = None) -> tuple[torch.Tensor, int]:
+                   video_token_id: Optional[int] = None, split_video_frames: bool = False) -> tuple[torch.Tensor, int]:
     """Multimodal RoPE positions of ONE sequence of token ids (no padding): ``[3, L]`` (temporal, height, width) and
     the delta to add to a text position after the sequence (``max position + 1 - L``). Text tokens advance all three
     axes together; the placeholder tokens of an image take (frame, row, column) of their merged patch, offset by the
@@ -250,6 +316,9 @@ def get_rope_index(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tenso
     if image_grid_thw is not None:
         grids += [(image_token_id, g) for g in image_grid_thw.tolist()]
     vids = [(video_token_id, g) for g in video_grid_thw.tolist()] if video_grid_thw is not None else []
+    if split_video_frames:
+        # Qwen3-VL: timestamps separate the frames of a video in the prompt, so every frame is a grid of its own
+        vids = [(tok, [1, h, w]) for tok, (t, h, w) in vids for _ in range(t)]
     if not grids and not vids:
         p = torch.arange(L, device=dev)
         return torch.stack([p, p, p]), 0

@@ -120,11 +120,19 @@ def _rope_ref(t, pos, cos_t, sin_t, n_heads, D, sign=1.0):
     return torch.cat([a * c - b * s, b * c + a * s], -1).reshape(T, n_heads * D).to(t.dtype)
 
 
-def _mrope_cos_sin(pos3, cos_t, sin_t, sections):
+def _mrope_cos_sin(pos3, cos_t, sin_t, sections, interleaved: bool = False):
     """Per-token cos / sin [T, D/2] of multimodal RoPE: frequency j follows the temporal / height / width position
-    according to ``sections`` (numbers of frequencies per axis)."""
+    according to ``sections`` (numbers of frequencies per axis): three consecutive runs (Qwen2-VL), or, ``interleaved``
+    (Qwen3-VL), frequency j follows height if j % 3 == 1 and j < 3 * sections[1], width if j % 3 == 2 and
+    j < 3 * sections[2], the temporal position otherwise (T H W T H W ... T T)."""
     half = cos_t.shape[1]
-    axis = torch.repeat_interleave(torch.arange(3, device=pos3.device), torch.tensor(list(sections), device=pos3.device))
+    if interleaved:
+        j = torch.arange(half, device=pos3.device)
+        axis = torch.zeros(half, dtype=torch.long, device=pos3.device)
+        axis[(j % 3 == 1) & (j < 3 * int(sections[1]))] = 1
+        axis[(j % 3 == 2) & (j < 3 * int(sections[2]))] = 2
+    else:
+        axis = torch.repeat_interleave(torch.arange(3, device=pos3.device), torch.tensor(list(sections), device=pos3.device))
     axis = axis[:half]
     j = torch.arange(half, device=pos3.device)
     p = pos3[axis]                      # [half, T]: the position each frequency uses
@@ -167,19 +175,22 @@ class _RopeFn(torch.autograd.Function):
 
 
 def rope_qkv(qkv: torch.Tensor, pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor, Hq: int, Hk: int, D: int,
-             mrope_section=None):
+             mrope_section=None, mrope_interleaved: bool = False):
     """Apply rotate-half RoPE to the q and k parts of packed ``qkv`` ([T, (Hq+2Hk)*D]); v is untouched. With
     ``mrope_section = (t, h, w)`` (frequencies per axis, sum D / 2) ``pos`` is ``[3, T]`` (multimodal RoPE of the
-    Qwen2-VL family, verl/models/transformers/qwen2_vl.py)."""
+    Qwen2-VL family, verl/models/transformers/qwen2_vl.py; ``mrope_interleaved``: the layout of Qwen3-VL,
+    verl/models/transformers/qwen3_vl.py, which takes the per-token-table path below: the kernel knows the sectioned
+    layout only)."""
     if pos.dim() == 2 and mrope_section is None:
         pos = pos[0]
     if pos.dim() == 1:
         mrope_section = None
-    if qkv.is_cuda and (mrope_section is None or all(int(x) % 8 == 0 for x in mrope_section[:2])):
+    if qkv.is_cuda and (mrope_section is None or
+                        (not mrope_interleaved and all(int(x) % 8 == 0 for x in mrope_section[:2]))):
         return _RopeFn.apply(qkv, pos.contiguous(), cos_t, sin_t, Hq, Hk, D,
                              None if mrope_section is None else tuple(int(x) for x in mrope_section))
     if mrope_section is not None:
-        c, s_ = _mrope_cos_sin(pos, cos_t, sin_t, mrope_section)
+        c, s_ = _mrope_cos_sin(pos, cos_t, sin_t, mrope_section, mrope_interleaved)
         q = _rope_apply(qkv[:, : Hq * D], c, s_, Hq, D)
         k = _rope_apply(qkv[:, Hq * D : (Hq + Hk) * D], c, s_, Hk, D)
         return torch.cat([q, k, qkv[:, (Hq + Hk) * D :]], dim=-1)

@@ -373,7 +373,13 @@ class NativeRolloutEngine:
             raise ValueError("multi_modal_inputs were given but the model has no vision tower")
         pv = inputs["pixel_values"].to(self.device)
         grid = inputs["image_grid_thw"].to(self.device)
-        emb = self.model.visual(pv, grid).to(self.dtype)
+        taps = []
+        if self.model.visual.num_deepstack:  # Qwen3-VL: features for the image tokens' hidden states after the first layers
+            emb, taps = self.model.visual(pv, grid, return_deepstack=True)
+            taps = [t.to(self.dtype) for t in taps]
+        else:
+            emb = self.model.visual(pv, grid)
+        emb = emb.to(self.dtype)
         ids = torch.tensor(prompt_ids, dtype=torch.long)
         where = torch.nonzero(ids == cfg.image_token_id, as_tuple=True)[0]
         if where.numel() != emb.shape[0]:
@@ -385,7 +391,7 @@ class NativeRolloutEngine:
         sched = list(prompt_ids)
         for j, w in enumerate(where.tolist()):
             sched[w] = cfg.vocab_size + (salt + 7919 * j) % room
-        return {"emb": emb, "where": where.numpy(), "pos3": pos3.numpy(), "delta": int(delta)}, sched
+        return {"emb": emb, "taps": taps, "where": where.numpy(), "pos3": pos3.numpy(), "delta": int(delta)}, sched
 
     def _finish(self, sid: int, reason: str) -> TokenOutput:
         req = self.requests.pop(sid)
@@ -425,7 +431,8 @@ class NativeRolloutEngine:
             qkv = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v], dim=-1)
         rope = self.model.rope(self.device)
         qkv = ops.rope_qkv(qkv, positions, rope[0], rope[1], c.num_attention_heads, c.num_key_value_heads, c.head_dim,
-                           mrope_section=c.mrope_section if positions.dim() == 2 else None)
+                           mrope_section=c.mrope_section if positions.dim() == 2 else None,
+                           mrope_interleaved=bool(getattr(c, "mrope_interleaved", False)))
         q = qkv[:, : c.q_size].view(T, c.num_attention_heads, c.head_dim)
         k = qkv[:, c.q_size : c.q_size + c.kv_size].view(T, c.num_key_value_heads, c.head_dim)
         v = qkv[:, c.q_size + c.kv_size :].view(T, c.num_key_value_heads, c.head_dim)
@@ -497,11 +504,12 @@ class NativeRolloutEngine:
         dist.all_reduce(partial, group=self.tp_group)
         return ops.rmsnorm(partial, norm_w, eps, residual)
 
-    def _forward_layers(self, h, attend, path: int):
+    def _forward_layers(self, h, attend, path: int, inject: Optional[dict] = None):
         """Decoder stack on embedded tokens ``h [T, H]``; ``attend(li, layer, x)`` returns the attention output of the
         layer's (local) heads for the normalised input ``x``. Returns the final-norm hidden states. Every RMSNorm after
         the first one is fused with the residual add (and, under tensor parallelism, with the all-reduce of the
-        preceding row-parallel GEMM)."""
+        preceding row-parallel GEMM). ``inject[li] = (rows, values)``: added to the hidden states of ``rows`` after
+        layer ``li`` (the deepstack vision features of Qwen3-VL)."""
         c = self.cfg
         layers = self.model.layers
         T = h.shape[0]
@@ -515,6 +523,9 @@ class NativeRolloutEngine:
             else:
                 d = self._mm_partial(ops.swiglu(self._mm(x, layer.mlp.gate_up_proj.weight)), layer.mlp.down_proj.weight,
                                      1, path)
+            if inject and li in inject and (self.tp == 1 or self.tp_rank == 0):
+                # ``d`` is this rank's partial sum under tensor parallelism: one rank adds the (replicated) values
+                d.index_add_(0, inject[li][0], inject[li][1].to(d.dtype))
             nw = layers[li + 1].input_layernorm.weight if li + 1 < len(layers) else self.model.norm.weight
             x, residual = self._reduce_norm(d, nw, residual)
         return x
@@ -686,6 +697,7 @@ class NativeRolloutEngine:
             cu_k_t = torch.tensor(cu_k, dtype=torch.int32, device=dev)
             max_k = max(b - a for a, b in zip(cu_k[:-1], cu_k[1:]))
         vl = bool(self.full_cfg.is_vl)
+        inject = None
         if vl:
             # salted placeholder ids (>= vocabulary) look up row 0; their embeddings are replaced below
             ids = torch.where(ids < self.full_cfg.vocab_size, ids, torch.zeros_like(ids))
@@ -694,6 +706,7 @@ class NativeRolloutEngine:
             # multimodal RoPE: [3, T] positions; a request with images takes them from its table (its text after the
             # images is offset by the request's delta), the others advance all three axes together
             pos3 = pos.unsqueeze(0).repeat(3, 1)
+            ds_rows, ds_vals = [], []
             for j, i in enumerate(seq_idx):
                 mm = self._mmreq.get(int(sc.seq_ids[i]))
                 if mm is None:
@@ -708,7 +721,13 @@ class NativeRolloutEngine:
                     k0 = int(np.searchsorted(mm["where"], st))
                     rows_ = torch.from_numpy(mm["where"][hit] - st + cu[j]).to(dev)
                     h = h.index_put((rows_,), mm["emb"][k0 : k0 + int(hit.sum())])
+                    if mm.get("taps"):
+                        ds_rows.append(rows_)
+                        ds_vals.append([t[k0 : k0 + int(hit.sum())] for t in mm["taps"]])
             pos = pos3
+            if ds_rows:
+                rows_all = torch.cat(ds_rows)
+                inject = {li: (rows_all, torch.cat([v[li] for v in ds_vals])) for li in range(len(ds_vals[0]))}
 
         def attend(li, layer, x):
             q, k, v = self._layer_attn_in(layer, x, pos)
@@ -719,7 +738,7 @@ class NativeRolloutEngine:
             v_all = torch.cat([self.v_cache[li][blk, :, off], v], dim=0)[order_t]
             return _varlen_attention_kv(q, k_all, v_all, cu_q, cu_k_t, max_q, max_k)
 
-        x = self._forward_layers(h, attend, 1)
+        x = self._forward_layers(h, attend, 1, inject)
         last = torch.tensor([b - 1 for b in cu[1:]], dtype=torch.long, device=dev)
         return self._final_logits(x[last])
 

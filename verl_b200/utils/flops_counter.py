@@ -174,7 +174,8 @@ class FlopsCounter:
         merge = _get(v, "spatial_merge_size", 2) ** 2
         out = _get(v, "out_hidden_size", None) or _get(_text(self.config), "hidden_size")  # width of the language model
         patch = _get(v, "in_channels", _get(v, "in_chans", 3)) * _get(v, "temporal_patch_size", 2) * _get(v, "patch_size", 14) ** 2
-        per_patch = (4 * d * d + mlp) * depth + patch * d + (d * merge * d * merge + d * merge * out) / merge
+        mergers = 1 + len(_get(v, "deepstack_visual_indexes", None) or ())  # Qwen3-VL: one more merger per deepstack tap
+        per_patch = (4 * d * d + mlp) * depth + patch * d + mergers * (d * merge * d * merge + d * merge * out) / merge
         tokens = sum(images_seqlens)
         heads_dim = d  # heads x head_dim
         return 6 * per_patch * tokens + 12 * sum(s * s for s in images_seqlens) * heads_dim * depth

@@ -531,11 +531,18 @@ class NativeEngine(BaseEngine):
             cp_inv = torch.full((T,), -1, dtype=torch.long, device=idx.device)
             cp_inv[idx[held]] = torch.nonzero(held, as_tuple=True)[0]
             batch = PackedBatch(ids_l, pos_l, cu_chunk, int((cu_chunk[1:] - cu_chunk[:-1]).max()), total_tokens=T)
+        taps = ()
         if self.pp_rank > 0:
             from ...parallel.pipeline import pipe_recv
 
             hidden = pipe_recv(self.pp_prev, (batch.input_ids.shape[0], self.model_config.hidden_size), self.work_dtype,
                                self.device, need_grad=self.trainable)
+        elif m.num_deepstack:
+            # Qwen3-VL: the vision tower's deepstack features come out of the embedding unit with the embeddings and are
+            # added to the image tokens' hidden states after the first layers
+            if self.sp_size > 1 or self.cp_size > 1 or self.pp_size > 1:
+                raise NotImplementedError("deepstack vision features (Qwen3-VL) with sequence, context or pipeline parallelism")
+            hidden, *taps = unit_call(z, self._embed_unit, lambda: m.embed(batch, with_deepstack=True))
         else:
             hidden = unit_call(z, self._embed_unit, lambda: m.embed(batch))
         residual = None
@@ -545,6 +552,8 @@ class NativeEngine(BaseEngine):
             # the LAST n_keep layers keep their activations: their memory is the first to be freed in the backward
             hidden, residual = unit_call(z, unit, lambda h, r, layer=layer: layer(h, r, batch, rope), hidden, residual,
                                          keep_activations=i >= n_layers - n_keep)
+            if i < len(taps):
+                hidden = m.add_deepstack(hidden, batch, taps[i])
         if cp_inv is not None:
             all_rows = rows if rows is not None else torch.arange(batch.total_tokens, device=hidden.device)
             loc = cp_inv[all_rows]
