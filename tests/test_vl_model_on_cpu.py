@@ -127,7 +127,7 @@ def test_vl_batch_through_engine_and_actor(name):
     assert all(not torch.equal(before[k], after[k]) for k in before), "a part of the vision tower did not train"
 
 
-@pytest.mark.parametrize("name", ["tiny-qwen2-vl", "tiny-qwen3-vl"])
+@pytest.mark.parametrize("name", ["tiny-qwen2-vl", "tiny-qwen3-vl", "tiny-qwen3-vl-moe"])
 def test_vl_rollout_with_images_matches_full_recompute(name):
     """The paged engine with multimodal requests (vision tower at admission, placeholder embeddings and [3, T] positions
     in prefill, offset positions in burst decode) generates greedily what a full forward over the growing sequence
@@ -315,3 +315,52 @@ def test_qwen3_vl_matches_hf():
     # config round trip
     cfg2 = ModelConfig.from_hf_dict(cfg.to_hf_dict())
     assert cfg2.mrope_interleaved and cfg2.mrope_section == [3, 3, 2] and cfg2.extra["vision_config"]["deepstack_visual_indexes"] == [0, 2]
+
+
+def test_qwen3_vl_moe_matches_hf():
+    """Qwen3-VL with a mixture-of-experts decoder (experts stored as stacked tensors): logits of a sequence with an image
+    against ``transformers``; names round-trip."""
+    pytest.importorskip("transformers")
+    try:
+        from transformers import Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration
+    except ImportError:
+        pytest.skip("this transformers version has no Qwen3-VL-MoE")
+
+    hf_cfg = Qwen3VLMoeConfig(
+        text_config=dict(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=16, max_position_embeddings=512, num_experts=4, num_experts_per_tok=2,
+                         moe_intermediate_size=32, decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [3, 3, 2],
+                                          "mrope_interleaved": True}),
+        vision_config=dict(depth=2, hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, in_channels=3,
+                           patch_size=4, spatial_merge_size=2, temporal_patch_size=2, num_position_embeddings=16,
+                           deepstack_visual_indexes=[1], hidden_act="gelu_pytorch_tanh"),
+        image_token_id=500, video_token_id=501, vision_start_token_id=502, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = Qwen3VLMoeForConditionalGeneration(hf_cfg).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "experts" in n or n.endswith("gate.weight"):
+                p.normal_(0.0, 0.05)  # the experts' tensors start uninitialised, the router at zero
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict())
+    assert cfg.is_vl and cfg.is_moe and cfg.model_type == "qwen3_vl_moe" and cfg.num_experts == 4 and cfg.mrope_interleaved
+    native = hf_to_native_state_dict(cfg, dict(hf.state_dict()))
+    model = CausalLM(cfg, dtype=torch.float32)
+    missing, unexpected = model.load_state_dict(native, strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    grid = torch.tensor([[1, 4, 8]])
+    pixels = torch.randn(32, 3 * 2 * 4 * 4, generator=torch.Generator().manual_seed(1))
+    ids = torch.tensor([5, 502] + [500] * 8 + [7, 9, 11, 13])
+    pos3, _ = get_rope_index(ids, grid, image_token_id=500, spatial_merge_size=2)
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None], pixel_values=pixels, image_grid_thw=grid, attention_mask=torch.ones(1, ids.numel(), dtype=torch.long),
+                 mm_token_type_ids=(ids == 500).int()[None])
+        logits = model(PackedBatch(ids, pos3, torch.tensor([0, ids.numel()], dtype=torch.int32), ids.numel(), pixel_values=pixels,
+                                   image_grid_thw=grid))
+    torch.testing.assert_close(logits, ref.logits[0], atol=3e-4, rtol=3e-4)
+    back = native_to_hf_state_dict(cfg, native)
+    ref_sd = dict(hf.state_dict())
+    assert set(back) == set(ref_sd), (set(back) ^ set(ref_sd))
+    for k in ref_sd:
+        assert torch.equal(back[k], ref_sd[k]), k
+    assert ModelConfig.from_hf_dict(cfg.to_hf_dict()).num_experts == 4

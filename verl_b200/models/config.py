@@ -20,6 +20,7 @@ _ARCH_TO_TYPE = {
     "Qwen2VLForConditionalGeneration": "qwen2_vl",
     "Qwen2_5_VLForConditionalGeneration": "qwen2_5_vl",
     "Qwen3VLForConditionalGeneration": "qwen3_vl",
+    "Qwen3VLMoeForConditionalGeneration": "qwen3_vl_moe",
     "LlamaForTokenClassification": "llama",
     "Qwen2ForTokenClassification": "qwen2",
     "Qwen3ForTokenClassification": "qwen3",
@@ -27,8 +28,8 @@ _ARCH_TO_TYPE = {
 _TYPE_TO_ARCH = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                  "qwen3_moe": "Qwen3MoeForCausalLM", "qwen2_vl": "Qwen2VLForConditionalGeneration",
                  "qwen2_5_vl": "Qwen2_5_VLForConditionalGeneration", "apertus": "ApertusForCausalLM",
-                 "qwen3_vl": "Qwen3VLForConditionalGeneration"}
-_VL_TYPES = ("qwen2_vl", "qwen2_5_vl", "qwen3_vl")
+                 "qwen3_vl": "Qwen3VLForConditionalGeneration", "qwen3_vl_moe": "Qwen3VLMoeForConditionalGeneration"}
+_VL_TYPES = ("qwen2_vl", "qwen2_5_vl", "qwen3_vl", "qwen3_vl_moe")
 
 
 @dataclass
@@ -68,7 +69,7 @@ class ModelConfig:
         if self.attention_bias is None:
             self.attention_bias = self.model_type in ("qwen2", "qwen2_vl", "qwen2_5_vl")
         if self.qk_norm is None:
-            self.qk_norm = self.model_type in ("qwen3", "qwen3_moe", "apertus", "qwen3_vl")
+            self.qk_norm = self.model_type in ("qwen3", "qwen3_moe", "apertus", "qwen3_vl", "qwen3_vl_moe")
         if self.hidden_act is None:
             self.hidden_act = "xielu" if self.model_type == "apertus" else "silu"
 
@@ -140,7 +141,7 @@ class ModelConfig:
             flat["model_type"] = mt
             extra_vl = {"vision_config": dict(d.get("vision_config") or {}),
                         "mrope_section": list(rope.get("mrope_section") or []) or None}
-            if rope.get("mrope_interleaved") or mt == "qwen3_vl":
+            if rope.get("mrope_interleaved") or mt in ("qwen3_vl", "qwen3_vl_moe"):
                 extra_vl["mrope_interleaved"] = True
             if "rope_theta" not in flat and rope.get("rope_theta"):
                 flat["rope_theta"] = rope["rope_theta"]
@@ -172,6 +173,9 @@ class ModelConfig:
         if isinstance(eos, list):
             kw["eos_token_id"] = eos[0]
         cfg = cls(**kw)
+        if cfg.is_moe and (d.get("mlp_only_layers") or int(d.get("decoder_sparse_step") or 1) != 1):
+            raise NotImplementedError("mixture-of-experts stacks with dense layers in between (mlp_only_layers, "
+                                      "decoder_sparse_step != 1) are not supported: every layer is sparse here")
         cfg.extra = {k: v for k, v in d.items() if k not in known and k != "_vl_extra"}
         cfg.extra.update(d.get("_vl_extra") or {})
         return cfg
@@ -187,11 +191,12 @@ class ModelConfig:
         d = asdict(self)
         extra = d.pop("extra")
         if self.model_type in _VL_TYPES:
-            text = {k: v for k, v in d.items() if k not in ("num_experts", "num_experts_per_tok", "moe_intermediate_size",
-                                                            "norm_topk_prob", "router_aux_loss_coef", "num_labels")}
+            moe_keys = () if self.is_moe else ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob",
+                                               "router_aux_loss_coef")
+            text = {k: v for k, v in d.items() if k not in moe_keys + ("num_labels",)}
             text["model_type"] = self.model_type + "_text"
             text["rope_scaling"] = {"type": "mrope", "mrope_section": list(extra.get("mrope_section") or [])}
-            if self.model_type == "qwen3_vl":
+            if self.model_type in ("qwen3_vl", "qwen3_vl_moe"):
                 text["rope_scaling"] = {"rope_type": "default", "mrope_section": list(extra.get("mrope_section") or []),
                                         "mrope_interleaved": True, "rope_theta": self.rope_theta}
             out = {"architectures": [_TYPE_TO_ARCH[self.model_type]], "model_type": self.model_type, "torch_dtype": "bfloat16",
@@ -266,6 +271,26 @@ PRESETS: dict[str, dict] = {
                                                        deepstack_visual_indexes=[0, 2], hidden_act="gelu_pytorch_tanh"),
                                  "mrope_section": [12, 10, 10], "mrope_interleaved": True, "image_token_id": 2000,
                                  "video_token_id": 2001, "vision_start_token_id": 2002}),
+    "tiny-qwen3-vl-moe": dict(model_type="qwen3_vl_moe", vocab_size=2048, hidden_size=256, intermediate_size=512,
+                              num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=64, rope_theta=5e6,
+                              num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, eos_token_id=2,
+                              extra={"vision_config": dict(depth=3, hidden_size=64, out_hidden_size=256, intermediate_size=96,
+                                                           num_heads=2, in_channels=3, patch_size=4, spatial_merge_size=2,
+                                                           temporal_patch_size=2, num_position_embeddings=64,
+                                                           deepstack_visual_indexes=[0, 1], hidden_act="gelu_pytorch_tanh"),
+                                     "mrope_section": [12, 10, 10], "mrope_interleaved": True, "image_token_id": 2000,
+                                     "video_token_id": 2001, "vision_start_token_id": 2002}),
+    "qwen3-vl-30b-a3b": dict(model_type="qwen3_vl_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                             num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4, head_dim=128, rope_theta=5e6,
+                             num_experts=128, num_experts_per_tok=8, moe_intermediate_size=768, eos_token_id=151645,
+                             max_position_embeddings=262144,
+                             extra={"vision_config": dict(depth=27, hidden_size=1152, out_hidden_size=2048,
+                                                          intermediate_size=4304, num_heads=16, in_channels=3, patch_size=16,
+                                                          spatial_merge_size=2, temporal_patch_size=2,
+                                                          num_position_embeddings=2304, deepstack_visual_indexes=[8, 16, 24],
+                                                          hidden_act="gelu_pytorch_tanh"),
+                                    "mrope_section": [24, 20, 20], "mrope_interleaved": True, "image_token_id": 151655,
+                                    "video_token_id": 151656, "vision_start_token_id": 151652}),
     "qwen3-vl-8b": dict(model_type="qwen3_vl", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
                         num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=5e6,
                         eos_token_id=151645, max_position_embeddings=262144,

@@ -77,7 +77,7 @@ def hf_to_native_state_dict(cfg: ModelConfig, hf_sd: dict[str, torch.Tensor]) ->
             if not k.startswith("visual."):
                 continue
             n = k
-            if cfg.model_type == "qwen3_vl":
+            if cfg.model_type in ("qwen3_vl", "qwen3_vl_moe"):
                 n = _vis3_hf_to_native(n)
             else:
                 for a, b in _VIS_HF_TO_NATIVE:
@@ -104,7 +104,12 @@ def hf_to_native_state_dict(cfg: ModelConfig, hf_sd: dict[str, torch.Tensor]) ->
         if cfg.qk_norm:
             out[n + "self_attn.q_norm.weight"] = g(p + "self_attn.q_norm.weight")
             out[n + "self_attn.k_norm.weight"] = g(p + "self_attn.k_norm.weight")
-        if cfg.is_moe:
+        if cfg.is_moe and (p + "mlp.experts.gate_up_proj") in hf_sd:
+            # experts stored as stacked tensors [E, 2I, H] / [E, H, I] (Qwen3-VL-MoE): the native layout
+            out[n + "mlp.gate.weight"] = g(p + "mlp.gate.weight")
+            out[n + "mlp.gate_up_proj"] = g(p + "mlp.experts.gate_up_proj")
+            out[n + "mlp.down_proj"] = g(p + "mlp.experts.down_proj")
+        elif cfg.is_moe:
             out[n + "mlp.gate.weight"] = g(p + "mlp.gate.weight")
             out[n + "mlp.gate_up_proj"] = torch.stack([
                 torch.cat([g(p + f"mlp.experts.{e}.gate_proj.weight"), g(p + f"mlp.experts.{e}.up_proj.weight")], 0)
@@ -129,7 +134,7 @@ def native_to_hf_items(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tensor
     vl = cfg.is_vl
     lm = "model.language_model." if vl else "model."
     for name, t in named:
-        if name.startswith("visual.") and cfg.model_type == "qwen3_vl":
+        if name.startswith("visual.") and cfg.model_type in ("qwen3_vl", "qwen3_vl_moe"):
             if name == "visual.patch_embed.weight":
                 vc = cfg.extra["vision_config"]
                 t = t.reshape(t.shape[0], vc.get("in_channels", 3), vc.get("temporal_patch_size", 2), vc.get("patch_size", 16),
@@ -178,6 +183,8 @@ def native_to_hf_items(cfg: ModelConfig, named: Iterable[tuple[str, torch.Tensor
                 gte, up = t.chunk(2, dim=0)
                 yield p + "mlp.gate_proj.weight", gte
                 yield p + "mlp.up_proj.weight", up
+            elif rest in ("mlp.gate_up_proj", "mlp.down_proj") and cfg.model_type == "qwen3_vl_moe":
+                yield p + "mlp.experts." + rest[len("mlp."):], t
             elif rest == "mlp.gate_up_proj":
                 for e in range(t.shape[0]):
                     gte, up = t[e].chunk(2, dim=0)
