@@ -65,3 +65,35 @@ def test_sft_dataset_masks(tmp_path):
     it = mt[0]
     assert it["input_ids"].numel() == it["loss_mask"].numel() < 128
     assert 0 < int(it["loss_mask"].sum()) < it["loss_mask"].numel()
+
+
+def test_controller_driven_sft_trains_validates_and_resumes(tmp_path):
+    """The single-controller SFT trainer: two TrainingWorker processes (gloo) behind a worker group, one no-padding
+    TensorDict per step, checkpoints through the CheckpointHandler; a second trainer resumes at the saved step with the
+    sampler's position and ends with the same loss as an uninterrupted run."""
+    from verl_b200.trainer.sft_trainer_ray import SFTTrainer, StatefulBatchSampler
+
+    s = StatefulBatchSampler(20, 4, 2, shuffle=True, seed=1)
+    first = [b for _, b in zip(range(3), s)]
+    s2 = StatefulBatchSampler(20, 4, 2, shuffle=True, seed=1)
+    s2.load_state_dict(s.state_dict())
+    rest, full = list(s2), list(StatefulBatchSampler(20, 4, 2, shuffle=True, seed=1))
+    assert first + rest == full and len(full) == 10 and sorted(sum(full[:5], [])) == list(range(20))
+
+    def run(sub, **over):
+        cfg = _config(tmp_path / sub, **{"trainer.n_gpus_per_node": 2, "data.pad_mode": "no_padding", **over})
+        tr = SFTTrainer(cfg, tokenizer=IntTokenizer(256))
+        try:
+            return tr, tr.fit()
+        finally:
+            tr.shutdown()
+
+    ref, out_ref = run("a", **{"trainer.total_training_steps": 6, "trainer.save_freq": -1})
+    assert ref.global_step == 6 and out_ref["val/loss"] > 0 and out_ref["train/grad_norm"] > 0
+    tr1, out1 = run("b", **{"trainer.total_training_steps": 3})
+    assert tr1.global_step == 3 and os.path.isdir(tmp_path / "b" / "ckpt" / "global_step_3")
+    assert os.path.exists(tmp_path / "b" / "ckpt" / "global_step_3" / "data_0.pt")
+    tr2, out2 = run("b", **{"trainer.total_training_steps": 6})
+    assert tr2.resume_global_step == 3 and tr2.global_step == 6
+    assert abs(out2["train/loss"] - out_ref["train/loss"]) < 2e-3, (out2["train/loss"], out_ref["train/loss"])
+    assert out2["train/loss"] < out1["train/loss"] + 0.5

@@ -37,7 +37,7 @@ _MOVED = {
     "verl.trainer.config.algorithm": "verl_b200.trainer.config",
     "verl.trainer.config.config": "verl_b200.trainer.config",
     "verl.trainer.fsdp_sft_trainer": "verl_b200.trainer.sft_trainer",
-    "verl.trainer.sft_trainer_ray": "verl_b200.trainer.sft_trainer",
+    "verl.trainer.sft_trainer_ray": "verl_b200.trainer.sft_trainer_ray",
     "verl.utils.dataset.multiturn_sft_dataset": "verl_b200.utils.dataset.sft_dataset",
     "verl.utils.dataset.rm_dataset": "verl_b200.utils.dataset.sft_dataset",
     "verl.utils.checkpoint.fsdp_checkpoint_manager": "verl_b200.utils.checkpoint.native_checkpoint",

@@ -638,7 +638,7 @@ class DataProtoFuture:
 
                 resolved.append(ray.get(f))
         for o in resolved:
-            assert isinstance(o, DataProto)
+            assert isinstance(o, DataProto) or type(o).__name__ == "TensorDict", type(o)
         out = self.collect_fn(resolved)
         if self.dispatch_fn is not None:
             out = self.dispatch_fn(out)

@@ -89,16 +89,24 @@ for _n in ("ALL", "RANK_ZERO"):
 
 
 # ------------------------------------------------------------------- split helpers
+def _is_tensordict(x) -> bool:
+    from ...utils.tensordict_lite import TensorDict
+
+    return isinstance(x, TensorDict)
+
+
+def _chunk(x, chunks: int):
+    """Equal shares of a DataProto / future / TensorDict (the no-padding batches of the engine workers)."""
+    if _is_tensordict(x):
+        from ...utils.tensordict_utils import chunk_tensordict
+
+        return chunk_tensordict(x, chunks)
+    assert isinstance(x, (DataProto, DataProtoFuture)), f"cannot split argument of type {type(x)}"
+    return x.chunk(chunks=chunks)
+
+
 def _split_args_kwargs_data_proto(chunks: int, *args, **kwargs):
-    s_args = []
-    for a in args:
-        assert isinstance(a, (DataProto, DataProtoFuture)), f"cannot split argument of type {type(a)}"
-        s_args.append(a.chunk(chunks=chunks))
-    s_kwargs = {}
-    for k, v in kwargs.items():
-        assert isinstance(v, (DataProto, DataProtoFuture)), f"cannot split argument {k} of type {type(v)}"
-        s_kwargs[k] = v.chunk(chunks=chunks)
-    return s_args, s_kwargs
+    return [_chunk(a, chunks) for a in args], {k: _chunk(v, chunks) for k, v in kwargs.items()}
 
 
 def _split_args_kwargs_data_proto_with_auto_padding(chunks: int, *args, **kwargs):
@@ -108,6 +116,8 @@ def _split_args_kwargs_data_proto_with_auto_padding(chunks: int, *args, **kwargs
 
     def prep(x):
         nonlocal pad_size
+        if _is_tensordict(x):
+            return _chunk(x, chunks)
         assert isinstance(x, (DataProto, DataProtoFuture))
         if isinstance(x, DataProto) and x.is_padding_enabled():
             if pad_size is None:
@@ -130,10 +140,11 @@ def _concat_data_proto_or_future(outputs: list):
     if isinstance(o, DataProto):
         return DataProto.concat(outputs)
     if isinstance(o, DataProtoFuture) or hasattr(o, "result"):
-        return DataProtoFuture.concat(outputs)
-    from ...utils.tensordict_lite import TensorDict
+        # resolved later: the workers' results may be DataProtos or TensorDicts
+        return DataProtoFuture(collect_fn=_concat_data_proto_or_future, futures=outputs)
+    if _is_tensordict(o):
+        from ...utils.tensordict_lite import TensorDict
 
-    if isinstance(o, TensorDict):
         return TensorDict.cat(outputs, dim=0)
     raise NotImplementedError(type(o))
 

@@ -347,6 +347,9 @@ class TensorDict:
                 new._data[k] = torch.nested.as_nested_tensor(rows, layout=torch.jagged)
             else:
                 new._data[k] = torch.cat(vals, dim=0)
+        if len(tds[0]._batch_size) == 0:  # no batch dimension (results that carry only batch-level data)
+            new._batch_size = torch.Size(())
+            return new
         total = sum(t._batch_size[0] for t in tds)
         new._batch_size = torch.Size((total,) + tuple(tds[0]._batch_size[1:]))
         return new
