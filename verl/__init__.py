@@ -41,6 +41,7 @@ _MOVED = {
     "verl.utils.dataset.multiturn_sft_dataset": "verl_b200.utils.dataset.sft_dataset",
     "verl.utils.dataset.rm_dataset": "verl_b200.utils.dataset.sft_dataset",
     "verl.utils.checkpoint.fsdp_checkpoint_manager": "verl_b200.utils.checkpoint.native_checkpoint",
+    "verl.utils.debug.performance": "verl_b200.utils.profiler.performance",
     "verl.utils.profiler.nvtx_profile": "verl_b200.utils.profiler.profile",
     "verl.utils.profiler.torch_profile": "verl_b200.utils.profiler.profile",
     "verl.utils.kernel.linear_cross_entropy": "verl_b200.ops.lmhead",

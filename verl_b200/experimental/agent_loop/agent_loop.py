@@ -167,7 +167,11 @@ class AgentLoopWorker:
             p = list(o.prompt_ids)[-P:]
             prompts[i, P - len(p):] = torch.tensor(p, dtype=torch.long)
             pmask[i, P - len(p):] = 1
-            shells.append(TokenOutput(token_ids=list(o.response_ids)[:R], log_probs=o.response_logprobs))
+            rec = o.routed_experts
+            if rec is not None:
+                # the record of ONE generation call covers its prompt and its response; cut it like the prompt
+                rec = rec[len(o.prompt_ids) - len(p):] if len(rec) == len(o.prompt_ids) + len(o.response_ids) else None
+            shells.append(TokenOutput(token_ids=list(o.response_ids)[:R], log_probs=o.response_logprobs, routed_experts=rec))
         has_lp = all(o.response_logprobs is not None for o in outputs)
         out = assemble_rollout_batch(prompts, pmask, shells, R, pad, with_logprobs=has_lp,
                                      response_masks=[o.response_mask for o in outputs])

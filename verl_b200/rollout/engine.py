@@ -202,7 +202,7 @@ class NativeRolloutEngine:
                  gpu_memory_utilization: float = 0.5, enable_prefix_caching: bool = True, enforce_eager: bool = False,
                  seed: int = 0, eos_token_id: Optional[int] = None, cudagraph_capture_sizes: Optional[list] = None,
                  quantization: Optional[str] = None, tp_group=None, tp_comm=None, full_config: Optional[ModelConfig] = None,
-                 decode_burst: int = 16):
+                 decode_burst: int = 16, record_routing: bool = False):
         """``model``: the whole model, or (tensor parallelism) this rank's slice of it as laid out by
         :func:`verl_b200.parallel.reshard.tp_model_config`, with ``tp_group`` the replica's process group, ``tp_comm``
         its peer-memory communicator (CUDA) and ``full_config`` the architecture of the whole model. Every rank of a
@@ -234,6 +234,13 @@ class NativeRolloutEngine:
         self.max_num_batched_tokens = max(max_num_batched_tokens, 16)
         self.block_size = block_size
         self.enable_prefix_caching = enable_prefix_caching
+        # mixture-of-experts models: keep, per request, the experts every INPUT token was routed to in every layer
+        # (``TokenOutput.routed_experts [prompt + response tokens, layers, top-k]``; the trainer replays them, router
+        # replay mode R3). Tokens served from the prefix cache are never routed, so the cache is off while recording.
+        self.record_routing = bool(record_routing) and self.cfg.is_moe
+        self._routing: dict[int, np.ndarray] = {}
+        if self.record_routing:
+            self.enable_prefix_caching = False
         self.enforce_eager = enforce_eager or not self.on_gpu
         self.seed = seed
         self.eos = self.cfg.eos_token_id if eos_token_id is None else eos_token_id
@@ -357,6 +364,9 @@ class NativeRolloutEngine:
             raise ValueError(f"request {request_id}: prompt of {len(prompt_ids)} tokens does not fit (code {rc})")
         self.requests[sid] = _Request(request_id, sid, sp, len(prompt_ids))
         self.by_rid[request_id] = sid
+        if self.record_routing:
+            self._routing[sid] = np.zeros((len(prompt_ids) + max(max_new, 0), self.cfg.num_hidden_layers,
+                                           self.cfg.num_experts_per_tok), np.int16)
         if mm is not None:
             self._mmreq[sid] = mm
 
@@ -401,7 +411,13 @@ class NativeRolloutEngine:
         pre = self.sched.preempt_count(sid)
         self.sched.remove(sid)
         lps = req.logprobs[: len(toks)] if req.params.logprobs else None
-        return TokenOutput(token_ids=toks, log_probs=lps, stop_reason=reason, num_preempted=max(pre, 0), request_id=req.rid)
+        routed = self._routing.pop(sid, None)
+        if routed is not None:
+            routed = routed[: req.prompt_len + len(toks)]
+            if len(toks):
+                routed[-1] = 0  # the last token was never an input (a burst that ran past the end may have fed it)
+        return TokenOutput(token_ids=toks, log_probs=lps, routed_experts=routed, stop_reason=reason,
+                           num_preempted=max(pre, 0), request_id=req.rid)
 
     def abort_request(self, request_id: str) -> Optional[TokenOutput]:
         """Stop a request; the partial output is returned with ``stop_reason="aborted"``."""
@@ -530,6 +546,16 @@ class NativeRolloutEngine:
             x, residual = self._reduce_norm(d, nw, residual)
         return x
 
+    def _routing_snapshot(self) -> torch.Tensor:
+        """[tokens of the latest forward, layers, top-k] expert ids (int16, on the device)."""
+        return torch.stack([layer.mlp.last_routing for layer in self.model.layers], dim=1).to(torch.int16)
+
+    def _routing_store(self, sid: int, start: int, rows: np.ndarray) -> None:
+        buf = self._routing.get(sid)
+        if buf is not None and start < buf.shape[0]:
+            n = min(rows.shape[0], buf.shape[0] - start)
+            buf[start : start + n] = rows[:n]
+
     def _final_logits(self, x):
         w = self.model.lm_head_weight
         logits = ops.gemm(x, w, out_dtype=torch.float32) if self.on_gpu else x.float() @ w.float().t()
@@ -608,6 +634,10 @@ class NativeRolloutEngine:
         st["host_lp"] = out_host.numpy()[K * B * 8 :].view(np.float32).reshape(K, B)
         st["tok"] = torch.zeros(B, dtype=torch.int64, device=dev)
         st["lp"] = torch.zeros(B, dtype=torch.float32, device=dev)
+        if self.record_routing:  # the burst's routing records: row s = step s of the burst
+            shape = (K, B, c.num_hidden_layers, c.num_experts_per_tok)
+            st["ring_rt"] = torch.zeros(shape, dtype=torch.int16, device=dev)
+            st["rt_host"] = torch.zeros(shape, dtype=torch.int16, pin_memory=pin)
         splits, work = ops.decode_workspace(B, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
                                             self.max_model_len, dev)
         st["splits"], st["work"] = splits, work
@@ -615,6 +645,8 @@ class NativeRolloutEngine:
 
         def run():
             logits = self._decode_forward(st["ids"], st["pos"], st["slots"], st["bt"], st["lens"], splits, work)
+            if self.record_routing:  # before decode_advance moves the burst position on
+                st["ring_rt"].index_copy_(0, st["bpos"].long(), self._routing_snapshot().unsqueeze(0))
             ops.sample(logits, temperature=st["temp"], top_k=st["topk"], top_p=st["topp"], seed=self.seed,
                        step=self.step_counter, out_tokens=st["tok"], out_logprobs=st["lp"])
             ops.decode_advance(st["tok"], st["lp"], st["ids"], st["pos"], st["slots"], st["lens"], st["bt"],
@@ -739,6 +771,10 @@ class NativeRolloutEngine:
             return _varlen_attention_kv(q, k_all, v_all, cu_q, cu_k_t, max_q, max_k)
 
         x = self._forward_layers(h, attend, 1, inject)
+        if self.record_routing:
+            rt = self._routing_snapshot().cpu().numpy()
+            for j, i in enumerate(seq_idx):
+                self._routing_store(int(sc.seq_ids[i]), int(sc.seq_start[i]), rt[cu[j] : cu[j + 1]])
         last = torch.tensor([b - 1 for b in cu[1:]], dtype=torch.long, device=dev)
         return self._final_logits(x[last])
 
@@ -798,9 +834,17 @@ class NativeRolloutEngine:
                 else:
                     run()
             st["out_host"].copy_(st["out_dev"], non_blocking=True)
+            if self.record_routing:
+                st["rt_host"].copy_(st["ring_rt"], non_blocking=True)
             t_wait = time.perf_counter()
             if dev.type == "cuda":
                 torch.cuda.current_stream(dev).synchronize()
+            if self.record_routing:
+                # step s of the burst read the token at text position (position of the first step) + s; rows past a
+                # sequence's end are cut off when the request finishes
+                rt = st["rt_host"].numpy()
+                for j, sid in enumerate(sids_d.tolist()):
+                    self._routing_store(int(sid), int(sc.positions[t_idx[j]]), rt[:k, j])
             self.stats["decode_wait_s"] += time.perf_counter() - t_wait
             self.stats["decode_steps"] += k
             if k > 1:

@@ -46,4 +46,22 @@ def assemble_rollout_batch(prompt_ids: torch.Tensor, prompt_mask: torch.Tensor, 
                "position_ids": position_ids, "response_mask": rmask}
     if with_logprobs:
         tensors["rollout_log_probs"] = lps
+    first = next((o for o in outputs if getattr(o, "routed_experts", None) is not None), None)
+    if first is not None:
+        # mixture-of-experts rollouts that record their routing: [B, P + R, layers, top-k] aligned with input_ids (zeros
+        # where a token was never an input of the model: padding, and the last token of a response)
+        import numpy as np
+
+        routed = torch.zeros((B, P + R) + tuple(first.routed_experts.shape[1:]), dtype=torch.int16)
+        for i, o in enumerate(outputs):
+            rec = getattr(o, "routed_experts", None)
+            if rec is None:
+                continue
+            rec = torch.from_numpy(np.ascontiguousarray(rec))
+            n_p = int(prompt_mask[i].sum())
+            n_r = min(rec.shape[0] - n_p, R)
+            routed[i, P - n_p : P] = rec[:n_p]
+            if n_r > 0:
+                routed[i, P : P + n_r] = rec[n_p : n_p + n_r]
+        tensors["routed_experts"] = routed
     return DataProto.from_dict(tensors=tensors)

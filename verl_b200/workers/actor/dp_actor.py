@@ -38,6 +38,19 @@ class DataParallelPPOActor(BasePPOActor):
         # forward-only passes evaluate every distinct prompt of a micro-batch once (trainer/ppo/prefix_grouper_utils.py)
         self.use_prefix_grouper = bool(_cfg(config, "use_prefix_grouper", False))
         self.last_prefix_saving = 0.0
+        # router replay for mixture-of-experts models (verl/utils/megatron/router_replay_patch.py): "R2" records the
+        # experts every token was routed to during compute_log_prob and routes the same way in the update, so the old
+        # and the new log-probs of a token come from the same experts; "R3" takes the record from the rollout
+        # (``routed_experts`` in the batch) and replays it in compute_log_prob and in the update
+        self.router_replay = str(_cfg(_cfg(config, "router_replay", None), "mode", "disabled") or "disabled")
+        self.last_routed_experts = None
+        self.record_routing = True  # a reference policy built on this class switches it off: nothing reads its record
+        if self.router_replay != "disabled":
+            if not getattr(engine.model_config, "is_moe", False):
+                raise ValueError("actor.router_replay needs a mixture-of-experts model")
+            if getattr(engine, "sp_size", 1) > 1 or getattr(engine, "cp_size", 1) > 1 or getattr(engine, "pp_size", 1) > 1:
+                raise NotImplementedError("actor.router_replay with sequence, context or pipeline parallelism")
+            self.use_prefix_grouper = False  # the record is laid out by the plain packing of a micro-batch
 
     # ------------------------------------------------------------------ forward
     def _forward_micro_batch(self, micro: DataProto, temperature: float, calculate_entropy: bool):
@@ -70,14 +83,40 @@ class DataParallelPPOActor(BasePPOActor):
             if inputs.get("pixel_values") is not None:
                 packed.pixel_values = inputs["pixel_values"].to(self.device)
                 packed.image_grid_thw = inputs["image_grid_thw"].to(self.device)
+        replay = record = False
+        if self.router_replay != "disabled":
+            flat = torch.nonzero(mask.reshape(-1).bool(), as_tuple=True)[0]  # packed token t sits at (b, s) = flat[t]
+            moe = [layer.mlp for layer in self.engine.model.layers]
+            if "routed_experts" in b.keys():
+                # [b, S, layers, top-k] -> per layer the [T, top-k] ids of the packed tokens; stays set through the
+                # backward (recomputed layers must route the same way) until update_policy clears it
+                rec = b["routed_experts"].to(self.device).reshape(-1, *b["routed_experts"].shape[2:])[flat].long()
+                for li, m in enumerate(moe):
+                    m.replay_routing = rec[:, li].contiguous()
+                replay = True
+            elif self.router_replay == "R2" and self.record_routing and not torch.is_grad_enabled():
+                record = True
         lp, ent = self.engine.forward_logprob(packed, rows, labels, temperature)
         B = input_ids.shape[0]
+        if record:
+            S = input_ids.shape[1]
+            rec = torch.stack([m.last_routing for m in moe], dim=1)  # [T, layers, top-k]
+            full = torch.zeros(B * S, *rec.shape[1:], dtype=torch.int16, device=self.device)
+            full[flat] = rec.to(torch.int16)
+            self._recorded.append(full.view(B, S, *rec.shape[1:]).cpu())
+        if replay and not torch.is_grad_enabled():
+            self._clear_replay()
         log_probs = torch.zeros(B, R, dtype=torch.float32, device=self.device)
         entropy = torch.zeros(B, R, dtype=torch.float32, device=self.device)
         log_probs = log_probs.index_put((bj[:, 0], bj[:, 1]), lp)
         if calculate_entropy:
             entropy = entropy.index_put((bj[:, 0], bj[:, 1]), ent)
         return log_probs, (entropy if calculate_entropy else None)
+
+    def _clear_replay(self):
+        for layer in self.engine.model.layers:
+            if hasattr(layer.mlp, "replay_routing"):
+                layer.mlp.replay_routing = None
 
     def _micro_batches_by_group(self, data: DataProto, max_token_len: int):
         """Token-budget micro-batches for the shared-prefix layout: the samples of one prompt stay together (a group
@@ -131,11 +170,14 @@ class DataParallelPPOActor(BasePPOActor):
         micro_batch_size | (max_token_len, use_dynamic_bsz). Returns (log_probs [B,R], entropys | None)."""
         temperature = data.meta_info["temperature"]
         use_dyn = data.meta_info.get("use_dynamic_bsz", False)
-        sel = data.select(batch_keys=[k for k in ("responses", "input_ids", "attention_mask", "position_ids")
-                                      if k in data.batch.keys()])
+        keys = ["responses", "input_ids", "attention_mask", "position_ids"]
+        if self.router_replay == "R3":
+            keys.append("routed_experts")  # recorded by the rollout
+        sel = data.select(batch_keys=[k for k in keys if k in data.batch.keys()])
         micros, idx = self._micro_batches(sel, data.meta_info.get("max_token_len"),
                                           data.meta_info.get("micro_batch_size"), use_dyn)
         lps, ents = [], []
+        self._recorded, self.last_routed_experts = [], None
         for mb in micros:
             lp, ent = self._forward_micro_batch(mb, temperature, calculate_entropy)
             lps.append(lp)
@@ -147,6 +189,10 @@ class DataParallelPPOActor(BasePPOActor):
             log_probs = restore_dynamic_batch(log_probs, idx)
             if calculate_entropy:
                 entropys = restore_dynamic_batch(entropys, idx)
+        if self._recorded:
+            rec = torch.cat(self._recorded, dim=0)
+            self.last_routed_experts = restore_dynamic_batch(rec, idx) if use_dyn else rec
+            self._recorded = []
         return log_probs, entropys
 
     # -------------------------------------------------------------------- update
@@ -166,6 +212,10 @@ class DataParallelPPOActor(BasePPOActor):
         for opt_key in ("ref_log_prob", "rollout_is_weights", "rollout_log_probs"):
             if opt_key in data.batch.keys():
                 keys.append(opt_key)
+        if self.router_replay != "disabled":
+            assert "routed_experts" in data.batch.keys(), \
+                "actor.router_replay: the batch has no routed_experts (R2: from compute_log_prob, R3: from the rollout)"
+            keys.append("routed_experts")
         keys = [k for k in keys if k in data.batch.keys()]
         data = data.select(batch_keys=keys)
         mini_bsz = min(int(cfg.ppo_mini_batch_size), len(data))
@@ -235,6 +285,8 @@ class DataParallelPPOActor(BasePPOActor):
                             acc["actor/kl_loss"] += kl_loss.detach().item()
                             mb_metrics["actor/kl_coef"] = float(cfg.kl_loss_coef)
                         loss.backward()
+                    if self.router_replay != "disabled":
+                        self._clear_replay()
                     append_to_dict(metrics, mb_metrics)
                 grad_norm = engine.optimizer_step()
                 mini_metrics = {"actor/grad_norm": float(grad_norm), "actor/pg_loss": acc["actor/pg_loss"]}

@@ -216,6 +216,7 @@ class ActorRolloutRefWorker(_WorkerBase):
             self.ref_engine = NativeEngine(model_cfg, ref_eng_cfg, None, device=str(self.device), group=group, seed=seed,
                                            state_dict=state, trainable=False, comm=comm).initialize()
             self.ref_policy = DataParallelPPOActor(self.ref_cfg or self.actor_cfg, self.ref_engine)
+            self.ref_policy.record_routing = False
             if self.actor_cfg is not None:  # the reference policy evaluates the same batches: same layout choice
                 self.ref_policy.use_prefix_grouper = bool(_cfg(self.actor_cfg, "use_prefix_grouper", False))
         if self._is_rollout:
@@ -325,6 +326,7 @@ class ActorRolloutRefWorker(_WorkerBase):
             self.rollout_model, max_num_seqs=rc.max_num_seqs, max_model_len=max_len,
             max_num_batched_tokens=max(rc.max_num_batched_tokens, rc.prompt_length),
             gpu_memory_utilization=rc.gpu_memory_utilization, enable_prefix_caching=rc.enable_prefix_caching,
+            record_routing=bool(_cfg(rc, "enable_rollout_routing_replay", False)),
             enforce_eager=rc.enforce_eager, seed=seed + 1000 * (self.dp_rank // tp),
             cudagraph_capture_sizes=rc.cudagraph_capture_sizes, quantization=_cfg(rc, "quantization", None),
             tp_group=self.tp_group, tp_comm=self.tp_comm, full_config=model_cfg, **kw)
@@ -423,8 +425,10 @@ class ActorRolloutRefWorker(_WorkerBase):
         data, pooled = sp_pool(data, self.actor_engine)
         with self.actor_engine.eval_mode():
             lp, ent = self.actor.compute_log_prob(data, calculate_entropy=True)
-        out = DataProto.from_dict(tensors={"old_log_probs": lp.cpu(), "entropys": ent.cpu()},
-                                  meta_info={"temperature": data.meta_info["temperature"]})
+        tensors = {"old_log_probs": lp.cpu(), "entropys": ent.cpu()}
+        if self.actor.last_routed_experts is not None:  # router replay R2: the experts this pass routed every token to
+            tensors["routed_experts"] = self.actor.last_routed_experts
+        out = DataProto.from_dict(tensors=tensors, meta_info={"temperature": data.meta_info["temperature"]})
         return sp_unpool(out, pooled)
 
     @register(dispatch_mode=make_nd_compute_dataproto_dispatch_fn("ref"))

@@ -273,8 +273,16 @@ class NativeAsyncServer:
         @app.post("/generate")
         async def generate(body: dict):
             out = await server.generate(body["prompt_ids"], body.get("sampling_params"), body.get("request_id"))
-            return {"token_ids": out.token_ids, "log_probs": out.log_probs, "stop_reason": out.stop_reason,
-                    "num_preempted": out.num_preempted}
+            res = {"token_ids": out.token_ids, "log_probs": out.log_probs, "stop_reason": out.stop_reason,
+                   "num_preempted": out.num_preempted}
+            if out.routed_experts is not None:  # int16 [tokens, layers, top-k], as bytes
+                import base64
+
+                import numpy as np
+
+                rec = np.ascontiguousarray(out.routed_experts, dtype=np.int16)
+                res["routed_experts"] = {"shape": list(rec.shape), "data": base64.b64encode(rec.tobytes()).decode("ascii")}
+            return res
 
         @app.post("/v1/completions")
         async def completions(body: dict):
@@ -387,8 +395,16 @@ class HttpServerHandle:
         sp = {k: v for k, v in (sampling_params or {}).items() if isinstance(v, (int, float, bool, str, list, type(None)))}
         body = await self._post("/generate", {"prompt_ids": [int(t) for t in prompt_ids], "sampling_params": sp,
                                               "request_id": request_id})
-        return TokenOutput(token_ids=body["token_ids"], log_probs=body.get("log_probs"), stop_reason=body.get("stop_reason"),
-                           num_preempted=int(body.get("num_preempted", 0) or 0), request_id=request_id)
+        routed = body.get("routed_experts")
+        if routed is not None:
+            import base64
+
+            import numpy as np
+
+            routed = np.frombuffer(base64.b64decode(routed["data"]), dtype=np.int16).reshape(routed["shape"]).copy()
+        return TokenOutput(token_ids=body["token_ids"], log_probs=body.get("log_probs"), routed_experts=routed,
+                           stop_reason=body.get("stop_reason"), num_preempted=int(body.get("num_preempted", 0) or 0),
+                           request_id=request_id)
 
     async def abort_request(self, request_id: str, reset_prefix_cache: bool = False):
         return await self._post("/abort_request", {"request_id": request_id})
