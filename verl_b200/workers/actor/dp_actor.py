@@ -45,6 +45,9 @@ class DataParallelPPOActor(BasePPOActor):
         self.router_replay = str(_cfg(_cfg(config, "router_replay", None), "mode", "disabled") or "disabled")
         self.last_routed_experts = None
         self.record_routing = True  # a reference policy built on this class switches it off: nothing reads its record
+        # optimal-token-baseline estimators: compute_log_prob also returns sum_v pi(v)^2 per response token
+        self.calculate_sum_pi_squared = bool(_cfg(config, "calculate_sum_pi_squared", False))
+        self._want_spp, self._spp, self.last_sum_pi_squared = False, [], None
         if self.router_replay != "disabled":
             if not getattr(engine.model_config, "is_moe", False):
                 raise ValueError("actor.router_replay needs a mixture-of-experts model")
@@ -96,8 +99,14 @@ class DataParallelPPOActor(BasePPOActor):
                 replay = True
             elif self.router_replay == "R2" and self.record_routing and not torch.is_grad_enabled():
                 record = True
-        lp, ent = self.engine.forward_logprob(packed, rows, labels, temperature)
+        want_spp = self._want_spp and not torch.is_grad_enabled()
+        if want_spp:
+            lp, ent, spp = self.engine.forward_logprob(packed, rows, labels, temperature, sum_pi_squared=True)
+        else:
+            lp, ent = self.engine.forward_logprob(packed, rows, labels, temperature)
         B = input_ids.shape[0]
+        if want_spp:
+            self._spp.append(torch.zeros(B, R, dtype=torch.float32, device=self.device).index_put((bj[:, 0], bj[:, 1]), spp))
         if record:
             S = input_ids.shape[1]
             rec = torch.stack([m.last_routing for m in moe], dim=1)  # [T, layers, top-k]
@@ -178,6 +187,9 @@ class DataParallelPPOActor(BasePPOActor):
                                           data.meta_info.get("micro_batch_size"), use_dyn)
         lps, ents = [], []
         self._recorded, self.last_routed_experts = [], None
+        self._want_spp, self._spp, self.last_sum_pi_squared = self.calculate_sum_pi_squared and self.record_routing, [], None
+        if self._want_spp and self.use_prefix_grouper:
+            raise NotImplementedError("calculate_sum_pi_squared with use_prefix_grouper")
         for mb in micros:
             lp, ent = self._forward_micro_batch(mb, temperature, calculate_entropy)
             lps.append(lp)
@@ -189,6 +201,10 @@ class DataParallelPPOActor(BasePPOActor):
             log_probs = restore_dynamic_batch(log_probs, idx)
             if calculate_entropy:
                 entropys = restore_dynamic_batch(entropys, idx)
+        if self._spp:
+            spp = torch.cat(self._spp, dim=0)
+            self.last_sum_pi_squared = restore_dynamic_batch(spp, idx) if use_dyn else spp
+        self._want_spp, self._spp = False, []
         if self._recorded:
             rec = torch.cat(self._recorded, dim=0)
             self.last_routed_experts = restore_dynamic_batch(rec, idx) if use_dyn else rec

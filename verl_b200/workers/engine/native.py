@@ -653,18 +653,32 @@ class NativeEngine(BaseEngine):
             torch.cuda.empty_cache()
             return self._forward_hidden_rows(batch, rows)
 
-    def forward_logprob(self, batch: PackedBatch, rows: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0):
-        """Log-prob of ``labels[i]`` predicted at packed position ``rows[i]`` (+ entropy), both fp32."""
+    def forward_logprob(self, batch: PackedBatch, rows: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0,
+                        sum_pi_squared: bool = False):
+        """Log-prob of ``labels[i]`` predicted at packed position ``rows[i]`` (+ entropy), both fp32.
+        ``sum_pi_squared`` (forward-only passes of the optimal-token-baseline estimators): a third output, the sum over
+        the vocabulary of the squared token probabilities at every row, from logits materialised 1024 rows at a time."""
         m, z = self.model, self.zero
         hidden, residual = self._forward_hidden_rows_safe(batch, rows)
         if isinstance(hidden, str):  # an earlier pipeline stage: the residual stream went to the next stage
-            return self._pp_share((0, 0), residual, rows.numel())
+            return self._pp_share((0, 0, 0) if sum_pi_squared else (0, 0), residual, rows.numel())
 
         if self.sp_size > 1 or self.cp_size > 1:
             labels = labels[self._sp_sel[0]]
 
         def head(h, r):
-            return m.logprob_entropy(m.final_norm(h, r), labels, temperature)
+            x = m.final_norm(h, r)
+            out = m.logprob_entropy(x, labels, temperature)
+            if not sum_pi_squared:
+                return out
+            assert m.tp_group is None or m.lm_head is None or m.lm_head.weight.shape[0] == m.cfg.vocab_size, \
+                "sum_pi_squared with a vocabulary-parallel lm_head is not supported"
+            spp = []
+            with torch.no_grad():
+                for lo in range(0, x.shape[0], 1024):
+                    p = torch.softmax(m.logits(x[lo : lo + 1024]).float() / temperature, dim=-1)
+                    spp.append((p * p).sum(-1))
+            return (*out, torch.cat(spp) if spp else x.new_zeros(0, dtype=torch.float32))
 
         out = self._sp_merge(unit_call(z, self._head_unit, head, hidden, residual))
         return self._pp_share(out, None, rows.numel()) if self.pp_size > 1 else out

@@ -428,6 +428,8 @@ class ActorRolloutRefWorker(_WorkerBase):
         tensors = {"old_log_probs": lp.cpu(), "entropys": ent.cpu()}
         if self.actor.last_routed_experts is not None:  # router replay R2: the experts this pass routed every token to
             tensors["routed_experts"] = self.actor.last_routed_experts
+        if self.actor.last_sum_pi_squared is not None:  # actor.calculate_sum_pi_squared (optimal token baseline)
+            tensors["sum_pi_squared"] = self.actor.last_sum_pi_squared.cpu()
         out = DataProto.from_dict(tensors=tensors, meta_info={"temperature": data.meta_info["temperature"]})
         return sp_unpool(out, pooled)
 
