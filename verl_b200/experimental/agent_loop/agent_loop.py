@@ -131,6 +131,27 @@ class AgentLoopWorker:
         self.reward_fn = reward_fn
         from . import single_turn_agent_loop, tool_agent_loop  # noqa: F401  (registers the built-in loops)
 
+        agent = config.actor_rollout_ref.rollout.agent
+        path = agent.get("agent_loop_config_path", None) if hasattr(agent, "get") else getattr(agent, "agent_loop_config_path", None)
+        if path:
+            # a YAML list of ``{name, _target_: package.module.Class, **constructor arguments}``: user-defined loops
+            import importlib
+            import os
+
+            import yaml
+
+            for entry in yaml.safe_load(open(os.path.expanduser(str(path)))) or []:
+                entry = dict(entry)
+                name, target = entry.pop("name"), entry.pop("_target_")
+                mod, _, cls = str(target).rpartition(".")
+                _agent_loop_registry[name] = (getattr(importlib.import_module(mod), cls), entry)
+        model = config.actor_rollout_ref.model
+        template = model.get("custom_chat_template", None) if hasattr(model, "get") else getattr(model, "custom_chat_template", None)
+        if template is not None:
+            for obj in (self.tokenizer, self.processor):
+                if obj is not None:
+                    obj.chat_template = template
+
     async def generate_sequences(self, batch: DataProto) -> DataProto:
         rc = self.config.actor_rollout_ref.rollout
         sp = dict(temperature=rc.temperature, top_p=rc.top_p, top_k=rc.top_k, repetition_penalty=1.0,
@@ -143,7 +164,7 @@ class AgentLoopWorker:
         names = batch.non_tensor_batch.get("agent_name", np.array([default] * n, dtype=object))
         tasks = []
         for i in range(n):
-            kwargs = {k: v[i] for k, v in batch.non_tensor_batch.items()}
+            kwargs = {k: v[i] for k, v in batch.non_tensor_batch.items() if k != "agent_name"}
             if "raw_prompt" not in kwargs and "raw_prompt_ids" in kwargs:
                 kwargs["raw_prompt"] = kwargs["raw_prompt_ids"]
             tasks.append(asyncio.create_task(self._run_agent_loop(str(names[i] or default), dict(sp), **kwargs)))
@@ -152,8 +173,10 @@ class AgentLoopWorker:
 
     async def _run_agent_loop(self, agent_name: str, sampling_params: dict, **kwargs) -> AgentLoopOutput:
         assert agent_name in _agent_loop_registry, f"Agent loop {agent_name} not registered, registered agent loops: {list(_agent_loop_registry)}"
-        loop = _agent_loop_registry[agent_name](trainer_config=self.config, server_manager=self.server_manager,
-                                                tokenizer=self.tokenizer, processor=self.processor)
+        entry = _agent_loop_registry[agent_name]
+        cls, extra = entry if isinstance(entry, tuple) else (entry, {})
+        loop = cls(trainer_config=self.config, server_manager=self.server_manager, tokenizer=self.tokenizer,
+                   processor=self.processor, **extra)
         return await loop.run(sampling_params, **kwargs)
 
     def _postprocess(self, outputs: list[AgentLoopOutput], rc) -> DataProto:

@@ -64,7 +64,10 @@ def build_tokenizer(config, model_config=None):
         "trust_remote_code", False)
     path = os.path.expanduser(str(model.path))
     if os.path.isdir(path) and any(os.path.exists(os.path.join(path, f)) for f in ("tokenizer.json", "tokenizer_config.json")):
-        return hf_tokenizer(model.get("tokenizer_path") or path, trust_remote_code=trust)
+        tok = hf_tokenizer(model.get("tokenizer_path") or path, trust_remote_code=trust)
+        if model.get("custom_chat_template", None) is not None:  # model.custom_chat_template replaces the checkpoint's
+            tok.chat_template = model.get("custom_chat_template")
+        return tok
     mc = model_config if model_config is not None else resolve_model_config(model)[0]
     return IntTokenizer(mc.vocab_size, eos_token_id=mc.eos_token_id if mc.eos_token_id is not None else 2)
 

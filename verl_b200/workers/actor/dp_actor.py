@@ -236,6 +236,8 @@ class DataParallelPPOActor(BasePPOActor):
         data = data.select(batch_keys=keys)
         mini_bsz = min(int(cfg.ppo_mini_batch_size), len(data))
         mini_batches = data.split(mini_bsz)
+        shuffle = bool(_cfg(cfg, "shuffle", False))
+        self._epochs_done = getattr(self, "_epochs_done", 0)
         on_policy = len(mini_batches) == 1 and cfg.ppo_epochs == 1
         loss_mode = _cfg(cfg.policy_loss, "loss_mode", "vanilla")
         entropy_coeff = float(cfg.entropy_coeff)
@@ -244,6 +246,12 @@ class DataParallelPPOActor(BasePPOActor):
         metrics: dict = {}
         engine = self.engine
         for _ in range(cfg.ppo_epochs):
+            if shuffle:
+                # actor.shuffle: a fresh order of this rank's samples every epoch, reproducible from
+                # actor.data_loader_seed (the same on every rank: ranks of a model-parallel group hold the same samples)
+                g = torch.Generator().manual_seed(int(_cfg(cfg, "data_loader_seed", 42) or 42) + self._epochs_done)
+                mini_batches = data.select_idxs(torch.randperm(len(data), generator=g)).split(mini_bsz)
+            self._epochs_done += 1
             for mini in mini_batches:
                 n_tok, n_seq = self._global_counts(mini)
                 micros, _ = self._micro_batches(mini, int(cfg.ppo_max_token_len_per_gpu),

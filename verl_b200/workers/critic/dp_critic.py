@@ -63,10 +63,16 @@ class DataParallelPPOCritic(BasePPOCritic):
         keys = [k for k in ("input_ids", "responses", "response_mask", "attention_mask", "position_ids", "values", "returns")
                 if k in data.batch.keys()]
         data = data.select(batch_keys=keys)
-        mini_batches = data.split(min(int(cfg.ppo_mini_batch_size), len(data)))
+        mini_bsz = min(int(cfg.ppo_mini_batch_size), len(data))
+        mini_batches = data.split(mini_bsz)
         metrics: dict = {}
         eng = self.engine
+        self._epochs_done = getattr(self, "_epochs_done", 0)
         for _ in range(cfg.ppo_epochs):
+            if bool(_cfg(cfg, "shuffle", False)):  # critic.shuffle / critic.data_loader_seed, as in the actor
+                g = torch.Generator().manual_seed(int(_cfg(cfg, "data_loader_seed", 42) or 42) + self._epochs_done)
+                mini_batches = data.select_idxs(torch.randperm(len(data), generator=g)).split(mini_bsz)
+            self._epochs_done += 1
             for mini in mini_batches:
                 n_tok = torch.tensor([float(mini.batch["response_mask"].sum())], dtype=torch.float64, device=self.device)
                 if eng.world > 1:

@@ -89,6 +89,13 @@ class NativeEngine(BaseEngine):
         self.work_dtype = _DTYPES[_cfg(engine_config, "dtype", "bfloat16")] if self.device.type == "cuda" else torch.float32
         self.step_count = 0
         self.lr_step = 0
+        # gradient-norm clip of the role that owns this engine (``actor.grad_clip`` / ``critic.grad_clip`` of the
+        # reference's FSDP workers) when it is to replace ``optim.clip_grad``
+        self.clip_grad_override: Optional[float] = None
+        if _cfg(engine_config, "full_determinism", False):
+            from .utils import enable_full_determinism
+
+            enable_full_determinism(int(seed))
         self.model: Optional[CausalLM] = None
         self.zero: Optional[ZeroShardedParams] = None
         self._offloaded = False
@@ -840,7 +847,7 @@ class NativeEngine(BaseEngine):
         """Sum the adapter gradients over the data-parallel group, clip by their global norm, AdamW. A non-finite
         norm skips the update."""
         oc = self.optimizer_config
-        clip = float(_cfg(oc, "clip_grad", 1.0))
+        clip = float(_cfg(oc, "clip_grad", 1.0) if self.clip_grad_override is None else self.clip_grad_override)
         grads = [p.grad if p.grad is not None else torch.zeros_like(p) for p in self._lora_params]
         flat = torch.cat([g.reshape(-1) for g in grads])
         if self.dp_world > 1:
@@ -913,7 +920,7 @@ class NativeEngine(BaseEngine):
         if self._lora_params:
             return self._lora_optimizer_step()
         z, oc = self.zero, self.optimizer_config
-        clip = float(_cfg(oc, "clip_grad", 1.0))
+        clip = float(_cfg(oc, "clip_grad", 1.0) if self.clip_grad_override is None else self.clip_grad_override)
         lr = self._lr()
         betas = tuple(_cfg(oc, "betas", (0.9, 0.999)))
         wd = float(_cfg(oc, "weight_decay", 0.01))

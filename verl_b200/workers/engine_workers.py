@@ -57,6 +57,15 @@ def resolve_model_config(model_cfg) -> tuple[ModelConfig, Optional[dict]]:
     raise FileNotFoundError(f"model path {path!r}: expected an HF directory or 'preset:<name>'")
 
 
+def _role_clip(role_cfg):
+    """``actor.grad_clip`` / ``critic.grad_clip`` (the knob of the reference's FSDP workers) replaces ``optim.clip_grad``
+    (the knob of its engine workers) when only the former was changed from the common default of 1.0."""
+    role, optim = _cfg(role_cfg, "grad_clip", None), _cfg(_cfg(role_cfg, "optim", None), "clip_grad", 1.0)
+    if role is not None and float(role) != 1.0 and float(optim) == 1.0:
+        return float(role)
+    return None
+
+
 def _init_dist(device_name: str, timeout_s: int = 600):
     if dist.is_initialized():
         return
@@ -210,6 +219,10 @@ class ActorRolloutRefWorker(_WorkerBase):
                                              device=str(self.device), group=group, seed=seed, state_dict=state,
                                              comm=comm, gradient_checkpointing=gc, tiled_mlp_shards=tiled,
                                              lora=lora).initialize()
+            self.actor_engine.clip_grad_override = _role_clip(self.actor_cfg)
+            if _cfg(self.actor_cfg, "freeze_vision_tower", False):
+                raise NotImplementedError("actor.freeze_vision_tower: the vision tower trains with the embedding unit; "
+                                          "freezing a part of a ZeRO unit is not supported")
             self.actor = DataParallelPPOActor(self.actor_cfg, self.actor_engine)
         if self._is_ref and not (self._lora and self._is_actor):  # LoRA: the reference is the actor with adapters off
             ref_eng_cfg = self.ref_cfg.fsdp_config if self.ref_cfg is not None else None
@@ -571,6 +584,7 @@ class CriticWorker(_WorkerBase):
                                    group=group, seed=int(_cfg(eng_cfg, "seed", 42)), state_dict=state,
                                    gradient_checkpointing=bool(_cfg(self.critic_cfg.model, "enable_gradient_checkpointing", True))
                                    ).initialize()
+        self.engine.clip_grad_override = _role_clip(self.critic_cfg)
         self.critic = DataParallelPPOCritic(self.critic_cfg, self.engine)
         self.model_config = model_cfg
 
