@@ -117,3 +117,15 @@ def test_custom_agent_loops_from_a_config_file(tmp_path):
 def test_freezing_the_vision_tower_is_refused_not_ignored():
     src = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "verl_b200", "workers", "engine_workers.py")).read()
     assert "freeze_vision_tower" in src and "NotImplementedError" in src
+
+
+def test_checkpoint_engine_from_its_config_section():
+    from verl_b200.checkpoint_engine import build_checkpoint_engine
+    from verl_b200.workers.config import CheckpointEngineConfig
+
+    e = build_checkpoint_engine(CheckpointEngineConfig(backend="nccl", update_weights_bucket_megabytes=3,
+                                                       engine_kwargs={"nccl": {"src": 1}}), is_master=False)
+    assert type(e).__name__ == "NCCLCheckpointEngine" and e.bucket_size == 3 << 20 and e.src == 1
+    assert build_checkpoint_engine({"backend": "naive"}).bucket_size == 2048 << 20
+    with pytest.raises(ValueError, match="Unknown checkpoint engine backend"):
+        build_checkpoint_engine({"backend": "nixl2"})

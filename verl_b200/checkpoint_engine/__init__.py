@@ -1,7 +1,8 @@
 from .base import (CheckpointEngine, CheckpointEngineManager, CheckpointEngineRegistry, CheckpointEngineWithCache,
-                   ColocatedCheckpointEngine, NCCLCheckpointEngine, NVLinkCheckpointEngine, TensorMeta)
+                   ColocatedCheckpointEngine, NCCLCheckpointEngine, NVLinkCheckpointEngine, TensorMeta,
+                   build_checkpoint_engine)
 from .pinned_bucket import PinnedBucketEngine, plan_buckets
 
 __all__ = ["CheckpointEngine", "CheckpointEngineManager", "CheckpointEngineRegistry", "CheckpointEngineWithCache",
            "ColocatedCheckpointEngine", "NCCLCheckpointEngine", "NVLinkCheckpointEngine", "PinnedBucketEngine",
-           "TensorMeta", "plan_buckets"]
+           "TensorMeta", "build_checkpoint_engine", "plan_buckets"]

@@ -51,6 +51,16 @@ class CheckpointEngineRegistry:
         return cls.get(backend)(*args, **kwargs)
 
 
+def build_checkpoint_engine(config, **kwargs) -> "CheckpointEngine":
+    """Engine of ``rollout.checkpoint_engine`` (``backend``, ``update_weights_bucket_megabytes``,
+    ``engine_kwargs[backend]``); ``kwargs`` are the call site's own arguments (process group, role, device)."""
+    get = config.get if hasattr(config, "get") else (lambda k, d=None: getattr(config, k, d))
+    backend = get("backend", "naive") or "naive"
+    extra = dict((get("engine_kwargs", None) or {}).get(backend, None) or {})
+    mb = int(get("update_weights_bucket_megabytes", 2048) or 2048)
+    return CheckpointEngineRegistry.new(backend, **{"bucket_size": mb << 20, **extra, **kwargs})
+
+
 class CheckpointEngine(ABC):
     """One side (trainer or rollout) of a weight transfer."""
 
