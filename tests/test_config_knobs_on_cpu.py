@@ -114,9 +114,43 @@ def test_custom_agent_loops_from_a_config_file(tmp_path):
         sys.modules.pop("my_loops", None)
 
 
-def test_freezing_the_vision_tower_is_refused_not_ignored():
-    src = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "verl_b200", "workers", "engine_workers.py")).read()
-    assert "freeze_vision_tower" in src and "NotImplementedError" in src
+def test_frozen_vision_tower_stays_bit_identical_while_the_decoder_trains():
+    from verl_b200.models.vision import get_rope_index
+    import numpy as np
+
+    cfg = preset("tiny-qwen2-vl")
+    eng = NativeEngine(cfg, C(), C(lr=1e-2, clip_grad=1.0, weight_decay=0.1), device="cpu", seed=3,
+                       frozen_prefixes=("visual.",)).initialize()
+    actor = DataParallelPPOActor(FSDPActorConfig(ppo_mini_batch_size=2, ppo_micro_batch_size_per_gpu=1, use_kl_loss=False), eng)
+    g = torch.Generator().manual_seed(2)
+    P, R, B, tok = 12, 6, 2, cfg.image_token_id
+    grid = torch.tensor([[1, 4, 4]])
+    ids = torch.zeros(B, P + R, dtype=torch.long)
+    mask = torch.zeros(B, P + R, dtype=torch.long)
+    pos = torch.zeros(B, 4, P + R, dtype=torch.long)
+    mm = []
+    for i in range(B):
+        seq = torch.tensor([5 + i, 2002] + [tok] * 4 + [9, 11, 13] + torch.randint(3, 1900, (R,), generator=g).tolist())
+        lo = P - 9
+        ids[i, lo : lo + len(seq)], mask[i, lo : lo + len(seq)] = seq, 1
+        pos[i, 1:, lo : lo + len(seq)] = get_rope_index(seq, grid, tok, 2)[0]
+        pos[i, 0, lo : lo + len(seq)] = torch.arange(len(seq))
+        mm.append({"pixel_values": torch.randn(16, 96, generator=g), "image_grid_thw": grid})
+    data = DataProto.from_dict({"input_ids": ids, "attention_mask": mask, "position_ids": pos, "responses": ids[:, P:],
+                                "response_mask": mask[:, P:], "old_log_probs": -torch.rand(B, R, generator=g),
+                                "advantages": torch.randn(B, R, generator=g)},
+                               non_tensors={"multi_modal_inputs": np.array(mm, dtype=object)}, meta_info={"temperature": 1.0})
+    before = {k: v.clone() for k, v in eng.zero.named_full_tensors()}
+    with eng.train_mode():
+        for _ in range(2):
+            out = actor.update_policy(data)
+    assert out["actor/grad_norm"][0] > 0
+    after = dict(eng.zero.named_full_tensors())
+    vis = [k for k in before if k.startswith("visual.")]
+    assert vis and all(torch.equal(before[k], after[k]) for k in vis)
+    assert not torch.equal(before["layers.0.self_attn.qkv_proj.weight"], after["layers.0.self_attn.qkv_proj.weight"])
+    with pytest.raises(ValueError, match="no parameter name starts with"):
+        NativeEngine(preset("tiny-qwen2"), C(), C(lr=1e-3), device="cpu", seed=1, frozen_prefixes=("visual.",)).initialize()
 
 
 def test_checkpoint_engine_from_its_config_section():

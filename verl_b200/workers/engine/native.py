@@ -65,8 +65,11 @@ class NativeEngine(BaseEngine):
     def __init__(self, model_config: ModelConfig, engine_config=None, optimizer_config=None, *, value_head: bool = False,
                  device: Optional[str] = None, trainable: bool = True, group=None, seed: int = 0,
                  state_dict: Optional[dict] = None, comm=None, gradient_checkpointing: bool = True,
-                 tiled_mlp_shards: int = 0, lora: Optional[dict] = None):
+                 tiled_mlp_shards: int = 0, lora: Optional[dict] = None, frozen_prefixes: tuple = ()):
         self.model_config = model_config
+        # parameters whose name starts with one of these stay as loaded (``("visual.",)``: a frozen vision tower)
+        self.frozen_prefixes = tuple(frozen_prefixes or ())
+        self._frozen: list = []
         self.tiled_mlp_shards = int(tiled_mlp_shards)
         # LoRA (``{"rank", "alpha", "target_modules", "exclude_modules"}``): the base weights are frozen and keep no
         # optimizer state; the adapters are replicated fp32 tensors trained by their own AdamW
@@ -176,6 +179,8 @@ class NativeEngine(BaseEngine):
                 for layer in m.layers:
                     layer.mlp.ep_group = self.shard_group
         self.zero.frozen_grad = bool(self._lora_params)
+        if self.frozen_prefixes and self.trainable and not self._lora_params:
+            self._freeze(self.frozen_prefixes)
         self._setup_sequence_parallel()
         self._setup_context_parallel()
         n0 = 1 if (first or tied) else 0
@@ -914,6 +919,26 @@ class NativeEngine(BaseEngine):
         self.lr_step += 1
         return self._lr()
 
+    def _freeze(self, prefixes: tuple) -> None:
+        """No gradient for the named parameters, and their slices of this rank's master / working shards are put back
+        after every optimizer step (with zero gradients AdamW itself leaves them alone, the decoupled weight decay
+        does not)."""
+        z = self.zero
+        for u in z.units:
+            if u.local:
+                continue
+            lo, hi = z.rank * u.shard, (z.rank + 1) * u.shard
+            for name, p, n, o in zip(u.names, u.params, u.numels, u.offsets):
+                if not name.startswith(prefixes):
+                    continue
+                p.requires_grad_(False)
+                s_, e_ = max(o, lo), min(o + n, hi)
+                if s_ < e_:
+                    a, b = u.offset + s_ - lo, u.offset + e_ - lo
+                    self._frozen.append((a, b, z.master[a:b].clone()))
+        if not any(not p.requires_grad for u in z.units for p in u.params):
+            raise ValueError(f"no parameter name starts with {prefixes}")
+
     def optimizer_step(self) -> float:
         """Global grad-norm, clip, fused AdamW on the shards. Returns the (pre-clip) gradient norm; a
         non-finite norm skips the update (verl/workers/actor/dp_actor.py:391-415)."""
@@ -967,6 +992,9 @@ class NativeEngine(BaseEngine):
                 z.shard16.copy_(z.master.to(z.shard16.dtype))
             else:
                 self.step_count -= 1
+        for a, b, saved in self._frozen:
+            z.master[a:b].copy_(saved)
+            z.shard16[a:b].copy_(saved.to(z.shard16.dtype))
         z.zero_grad()
         return norm
 

@@ -217,12 +217,10 @@ class ActorRolloutRefWorker(_WorkerBase):
         if self._is_actor:
             self.actor_engine = NativeEngine(model_cfg, self.actor_cfg.fsdp_config, self.actor_cfg.optim,
                                              device=str(self.device), group=group, seed=seed, state_dict=state,
-                                             comm=comm, gradient_checkpointing=gc, tiled_mlp_shards=tiled,
-                                             lora=lora).initialize()
+                                             comm=comm, gradient_checkpointing=gc, tiled_mlp_shards=tiled, lora=lora,
+                                             frozen_prefixes=("visual.",) if _cfg(self.actor_cfg, "freeze_vision_tower", False)
+                                             else ()).initialize()
             self.actor_engine.clip_grad_override = _role_clip(self.actor_cfg)
-            if _cfg(self.actor_cfg, "freeze_vision_tower", False):
-                raise NotImplementedError("actor.freeze_vision_tower: the vision tower trains with the embedding unit; "
-                                          "freezing a part of a ZeRO unit is not supported")
             self.actor = DataParallelPPOActor(self.actor_cfg, self.actor_engine)
         if self._is_ref and not (self._lora and self._is_actor):  # LoRA: the reference is the actor with adapters off
             ref_eng_cfg = self.ref_cfg.fsdp_config if self.ref_cfg is not None else None
