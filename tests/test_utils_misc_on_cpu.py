@@ -139,3 +139,25 @@ def test_kernel_breakdown_interval_arithmetic_and_classes():
     assert classify("void vb::peer_reduce_scatter_add_kernel<8, 2>") == "comm"
     assert classify("vb::adamw_kernel") == "optimizer"
     assert classify("at::native::vectorized_elementwise_kernel") == "other_torch"
+
+
+def test_communicator_found_by_name_between_unrelated_processes(tmp_path):
+    """Three processes with nothing in common but a group name and a registry directory build a process group; the
+    late starters find the endpoint that rank 0 published."""
+    import subprocess
+    import sys
+    import time
+
+    from verl_b200.utils.rendezvous import lookup_endpoint
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    assert lookup_endpoint("nobody", str(tmp_path), max_retries=2, interval_s=0.01) is None
+    procs = []
+    for rank in (2, 1, 0):  # rank 0 last: the others poll until it has published
+        procs.append(subprocess.Popen([sys.executable, os.path.join(here, "_rendezvous_worker.py"), str(rank), "3", "sync-group",
+                                       str(tmp_path)], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+        time.sleep(0.3)
+    outs = [p.communicate(timeout=300) for p in procs]
+    assert all(p.returncode == 0 for p in procs), [o[1][-1500:] for o in outs]
+    assert sorted(o[0].strip() for o in outs) == ["RENDEZVOUS_OK 0", "RENDEZVOUS_OK 1", "RENDEZVOUS_OK 2"]
+    assert not os.path.exists(tmp_path / "sync-group.json")

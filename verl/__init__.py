@@ -167,6 +167,8 @@ _MOVED = {
     "verl.experimental.one_step_off_policy.utils": "verl_b200.trainer.ppo.utils",
     "verl.experimental.vla.dp_rob": "verl_b200.workers.actor.dp_actor",
     "verl.experimental.vla.fsdp_workers": "verl_b200.workers.engine_workers",
+    "verl.utils.rendezvous": "verl_b200.utils.rendezvous",
+    "verl.utils.rendezvous.ray_backend": "verl_b200.utils.rendezvous",
     "verl.utils.checkpoint.checkpoint_handler": "verl_b200.utils.checkpoint.checkpoint_handler",
 }
 
