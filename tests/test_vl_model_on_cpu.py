@@ -165,8 +165,8 @@ def test_vl_rollout_with_images_matches_full_recompute(name):
     assert len(done["text"]) == 7
 
 
-@pytest.mark.parametrize("name", ["tiny-qwen2-vl", "tiny-qwen3-vl"])
-def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch, name):
+@pytest.mark.parametrize("name,frames", [("tiny-qwen2-vl", 0), ("tiny-qwen3-vl", 0), ("tiny-qwen3-vl", 4)])
+def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch, name, frames):
     """The trainer path for images: dataset rows with pixels and grids (native image -> patch processing, placeholder
     expansion, [4, S] position ids), rollout with images, multimodal RoPE positions of the generated sequences, actor
     and reference log-probs, one update. Two steps of GRPO on the tiny Qwen2-VL preset with synthetic images."""
@@ -183,7 +183,8 @@ def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch, name)
         f"trainer.default_local_dir={tmp_path}/ckpt", "trainer.save_freq=-1", "trainer.test_freq=-1",
         "trainer.project_name=cpu_e2e", "trainer.experiment_name=vl",
         "data.train_files=synthetic:16:6:10:16:1900:0", "data.synthetic_image_size=16", "data.val_files=null",
-        "data.train_batch_size=4", "data.max_prompt_length=32", "data.max_response_length=12", "data.shuffle=false",
+        f"data.synthetic_video_frames={frames}",  # > 0: a video (frame pairs, deepstack features at its tokens) per prompt
+        "data.train_batch_size=4", "data.max_prompt_length=48", "data.max_response_length=12", "data.shuffle=false",
         "algorithm.adv_estimator=grpo", "actor_rollout_ref.rollout.n=2", "actor_rollout_ref.rollout.max_num_seqs=8",
         "actor_rollout_ref.rollout.max_num_batched_tokens=128", "actor_rollout_ref.rollout.tensor_model_parallel_size=1",
         "actor_rollout_ref.rollout.log_prob_micro_batch_size_per_gpu=4", "actor_rollout_ref.ref.log_prob_micro_batch_size_per_gpu=4",
@@ -364,3 +365,73 @@ def test_qwen3_vl_moe_matches_hf():
     for k in ref_sd:
         assert torch.equal(back[k], ref_sd[k]), k
     assert ModelConfig.from_hf_dict(cfg.to_hf_dict()).num_experts == 4
+
+
+def test_video_inputs_match_hf_and_the_rollout_engine():
+    """A prompt with an image AND a video: the patches of frame pairs, the placeholder expansion and the multimodal
+    RoPE positions (temporal axis advancing per frame group) give the logits of ``transformers``' Qwen2-VL; the rollout
+    engine with the same inputs generates greedily what the full forward predicts."""
+    pytest.importorskip("transformers")
+    import numpy as np
+    from transformers import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+
+    from verl_b200.rollout import NativeRolloutEngine, SamplingParams
+    from verl_b200.utils.dataset.vision_utils import VLProcessor, videos_to_patches
+
+    hf_cfg = Qwen2VLConfig(
+        text_config=dict(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]},
+                         max_position_embeddings=512, tie_word_embeddings=False, rope_theta=10000.0),
+        vision_config=dict(depth=2, embed_dim=32, hidden_size=64, num_heads=2, mlp_ratio=2, in_channels=3, patch_size=4,
+                           spatial_merge_size=2, temporal_patch_size=2),
+        image_token_id=500, video_token_id=501, vision_start_token_id=502, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    hf = Qwen2VLForConditionalGeneration(hf_cfg).float().eval()
+    cfg = ModelConfig.from_hf_dict(hf_cfg.to_dict())
+    model = CausalLM(cfg, dtype=torch.float32)
+    missing, unexpected = model.load_state_dict(hf_to_native_state_dict(cfg, dict(hf.state_dict())), strict=False)
+    assert not missing and not unexpected
+    rng = np.random.default_rng(0)
+    video = rng.integers(0, 256, (5, 16, 24, 3), dtype=np.uint8)      # 5 frames -> 3 frame groups (the last frame repeated)
+    image = rng.integers(0, 256, (16, 16, 3), dtype=np.uint8)
+    pvv, vgrid = videos_to_patches([video], 4, 2, 2)
+    assert vgrid.tolist() == [[3, 4, 6]] and pvv.shape == (72, 3 * 2 * 4 * 4)
+    # frame group 1, first patch of its first merge block = pixels [0:4, 0:4] of frames 2 and 3
+    from verl_b200.utils.dataset.vision_utils import _CLIP_MEAN, _CLIP_STD
+
+    want = (torch.from_numpy(video[2:4, :4, :4].astype(np.float32) / 255.0) - torch.tensor(_CLIP_MEAN)) / torch.tensor(_CLIP_STD)
+    torch.testing.assert_close(pvv[24].view(3, 2, 4, 4), want.permute(3, 0, 1, 2))
+    proc = VLProcessor.from_model_config(cfg)
+    assert proc.video_token_id == 501
+    prompt = [5, 502, 500, 7, 502, 501, 9, 11]
+    ids, mm, pos3 = proc(prompt, [image], [video])
+    assert ids.count(500) == 4 and ids.count(501) == 18 and set(mm) == {"pixel_values", "image_grid_thw", "pixel_values_videos", "video_grid_thw"}
+    ids_t = torch.tensor(ids)
+    with torch.no_grad():
+        mmt = torch.zeros(1, len(ids), dtype=torch.int32)
+        mmt[0, ids_t == 500], mmt[0, ids_t == 501] = 1, 2
+        ref = hf(input_ids=ids_t[None], pixel_values=mm["pixel_values"], image_grid_thw=mm["image_grid_thw"],
+                 pixel_values_videos=mm["pixel_values_videos"], video_grid_thw=mm["video_grid_thw"],
+                 attention_mask=torch.ones(1, len(ids), dtype=torch.long), mm_token_type_ids=mmt, position_ids=pos3[:, None])
+        batch = PackedBatch(ids_t, pos3, torch.tensor([0, len(ids)], dtype=torch.int32), len(ids), pixel_values=mm["pixel_values"],
+                            image_grid_thw=mm["image_grid_thw"], pixel_values_videos=mm["pixel_values_videos"],
+                            video_grid_thw=mm["video_grid_thw"])
+        logits = model(batch)
+    torch.testing.assert_close(logits, ref.logits[0], atol=3e-4, rtol=3e-4)
+    # temporal axis: the video's three frame groups sit at consecutive temporal positions
+    vid_t = pos3[0][ids_t == 501]
+    assert vid_t.unique().numel() == 3 and int(vid_t.max() - vid_t.min()) == 2
+
+    eng = NativeRolloutEngine(model, max_num_seqs=2, max_model_len=64, max_num_batched_tokens=16, num_blocks=16, decode_burst=2)
+    out = eng.generate([ids], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True), multi_modal_inputs=[mm])[0]
+    seq = list(ids)
+    for _ in range(5):
+        t = torch.tensor(seq)
+        p3, _ = get_rope_index(t, mm["image_grid_thw"], 500, 2, video_grid_thw=mm["video_grid_thw"], video_token_id=501)
+        with torch.no_grad():
+            lg = model(PackedBatch(t, p3, torch.tensor([0, len(seq)], dtype=torch.int32), len(seq), pixel_values=mm["pixel_values"],
+                                   image_grid_thw=mm["image_grid_thw"], pixel_values_videos=mm["pixel_values_videos"],
+                                   video_grid_thw=mm["video_grid_thw"]))
+        lg[:, [500, 501]] = float("-inf")  # the engine never samples a placeholder id
+        seq.append(int(lg[-1].argmax()))
+    assert out.token_ids == seq[len(ids):], (out.token_ids, seq[len(ids):])

@@ -40,6 +40,10 @@ class PackedBatch:
     # then [3, T] (multimodal RoPE)
     pixel_values: Optional[torch.Tensor] = None
     image_grid_thw: Optional[torch.Tensor] = None
+    # the same for videos (grids with t > 1: one attention segment per frame group); their outputs fill the video
+    # placeholder tokens
+    pixel_values_videos: Optional[torch.Tensor] = None
+    video_grid_thw: Optional[torch.Tensor] = None
     # embeddings computed by the caller ([T, H]; vision-language-action models splice projected image patches and
     # action placeholders into the token stream themselves): used instead of the embedding lookup
     inputs_embeds: Optional[torch.Tensor] = None
@@ -430,27 +434,40 @@ class CausalLM(nn.Module):
             return (h,) + tuple(h.new_zeros(0, h.shape[1]) for _ in range(n_ds)) if with_deepstack else h
         h = ops.embedding(batch.input_ids, self.embed_tokens.weight)
         taps = [h.new_zeros(0, h.shape[1]) for _ in range(n_ds)]
-        if self.visual is not None and batch.pixel_values is not None and batch.pixel_values.numel():
-            # the vision tower's outputs replace the embeddings of the image placeholder tokens, in order
+        has_img = batch.pixel_values is not None and batch.pixel_values.numel() > 0
+        has_vid = batch.pixel_values_videos is not None and batch.pixel_values_videos.numel() > 0
+        if self.visual is not None and (has_img or has_vid):
+            # the vision tower's outputs replace the embeddings of the placeholder tokens, in order: one call over the
+            # images' patches followed by the videos' (every image / frame group is its own attention segment)
+            pixels = [p for p, on in ((batch.pixel_values, has_img), (batch.pixel_values_videos, has_vid)) if on]
+            grids = [g for g, on in ((batch.image_grid_thw, has_img), (batch.video_grid_thw, has_vid)) if on]
+            pixels, grids = torch.cat(pixels, 0), torch.cat(grids, 0)
             if self.visual.num_deepstack:
-                img, feats = self.visual(batch.pixel_values, batch.image_grid_thw, return_deepstack=True)
+                vis, feats = self.visual(pixels, grids, return_deepstack=True)
                 if with_deepstack:
                     taps = [f.to(h.dtype) for f in feats]
             else:
-                img = self.visual(batch.pixel_values, batch.image_grid_thw)
-            img = img.to(h.dtype)
-            where = torch.nonzero(batch.input_ids == self.cfg.image_token_id, as_tuple=True)[0]
-            assert where.numel() == img.shape[0], f"{where.numel()} image tokens but {img.shape[0]} image embeddings"
-            h = h.index_put((where,), img)
+                vis = self.visual(pixels, grids)
+            where = self._vision_rows(batch)
+            assert where.numel() == vis.shape[0], f"{where.numel()} placeholder tokens but {vis.shape[0]} vision embeddings"
+            h = h.index_put((where,), vis.to(h.dtype))
         return (h, *taps) if with_deepstack else h
 
+    def _vision_rows(self, batch: PackedBatch) -> torch.Tensor:
+        """Rows of the image placeholder tokens followed by the rows of the video placeholder tokens: the order of the
+        vision tower's outputs."""
+        where = torch.nonzero(batch.input_ids == self.cfg.image_token_id, as_tuple=True)[0]
+        vid = self.cfg.extra.get("video_token_id")
+        if vid is not None and batch.pixel_values_videos is not None and batch.pixel_values_videos.numel():
+            where = torch.cat([where, torch.nonzero(batch.input_ids == int(vid), as_tuple=True)[0]])
+        return where
+
     def add_deepstack(self, hidden: torch.Tensor, batch: PackedBatch, feature: torch.Tensor) -> torch.Tensor:
-        """``hidden`` with ``feature`` added at the rows of the image placeholder tokens (the residual stream of a layer
+        """``hidden`` with ``feature`` added at the rows of the vision placeholder tokens (the residual stream of a layer
         is ``hidden + residual``, so adding to ``hidden`` adds to the stream)."""
         if feature.shape[0] == 0:
             return hidden
-        where = torch.nonzero(batch.input_ids == self.cfg.image_token_id, as_tuple=True)[0]
-        return hidden.index_add(0, where, feature.to(hidden.dtype))
+        return hidden.index_add(0, self._vision_rows(batch), feature.to(hidden.dtype))
 
     def final_norm(self, hidden, residual) -> torch.Tensor:
         out, _ = ops.rmsnorm(hidden, self.norm.weight, self.cfg.rms_norm_eps, residual)

@@ -357,7 +357,8 @@ class NativeRolloutEngine:
         self._next_sid += 1
         sched_ids = list(prompt_ids)
         mm = None
-        if multi_modal_inputs and multi_modal_inputs.get("pixel_values") is not None:
+        if multi_modal_inputs and (multi_modal_inputs.get("pixel_values") is not None
+                                   or multi_modal_inputs.get("pixel_values_videos") is not None):
             mm, sched_ids = self._prepare_multimodal(prompt_ids, multi_modal_inputs)
         rc = self.sched.add(sid, sched_ids, max_new)
         if rc != 0:
@@ -381,8 +382,12 @@ class NativeRolloutEngine:
         cfg = self.full_cfg
         if getattr(self.model, "visual", None) is None:
             raise ValueError("multi_modal_inputs were given but the model has no vision tower")
-        pv = inputs["pixel_values"].to(self.device)
-        grid = inputs["image_grid_thw"].to(self.device)
+        img_grid = inputs["image_grid_thw"] if inputs.get("pixel_values") is not None else None
+        vid_grid = inputs["video_grid_thw"] if inputs.get("pixel_values_videos") is not None else None
+        # one tower call over the images' patches followed by the videos' (as the training forward does)
+        pv = torch.cat([inputs[k] for k, g in (("pixel_values", img_grid), ("pixel_values_videos", vid_grid))
+                        if g is not None], 0).to(self.device)
+        grid = torch.cat([g for g in (img_grid, vid_grid) if g is not None], 0).to(self.device)
         taps = []
         if self.model.visual.num_deepstack:  # Qwen3-VL: features for the image tokens' hidden states after the first layers
             emb, taps = self.model.visual(pv, grid, return_deepstack=True)
@@ -391,11 +396,20 @@ class NativeRolloutEngine:
             emb = self.model.visual(pv, grid)
         emb = emb.to(self.dtype)
         ids = torch.tensor(prompt_ids, dtype=torch.long)
-        where = torch.nonzero(ids == cfg.image_token_id, as_tuple=True)[0]
+        vid_tok = cfg.extra.get("video_token_id")
+        where = torch.nonzero(ids == cfg.image_token_id, as_tuple=True)[0] if img_grid is not None else ids.new_zeros(0)
+        if vid_grid is not None:
+            where = torch.cat([where, torch.nonzero(ids == int(vid_tok), as_tuple=True)[0]])
         if where.numel() != emb.shape[0]:
-            raise ValueError(f"{where.numel()} image placeholder tokens but {emb.shape[0]} image embeddings")
+            raise ValueError(f"{where.numel()} vision placeholder tokens but {emb.shape[0]} vision embeddings")
+        # prefill looks rows up by position: keep them (and their embeddings) in prompt order
+        where, order = torch.sort(where)
+        emb = emb[order.to(emb.device)]
+        taps = [t[order.to(t.device)] for t in taps]
         merge = int(cfg.extra["vision_config"].get("spatial_merge_size", 2))
-        pos3, delta = get_rope_index(ids, grid.cpu(), cfg.image_token_id, merge)
+        pos3, delta = get_rope_index(ids, img_grid.cpu() if img_grid is not None else None, cfg.image_token_id, merge,
+                                     video_grid_thw=vid_grid.cpu() if vid_grid is not None else None,
+                                     video_token_id=None if vid_tok is None else int(vid_tok))
         salt = int(pv.float().sum().item() * 1000003) & 0x3FFFFFFF
         room = (1 << 31) - 1 - cfg.vocab_size
         sched = list(prompt_ids)
@@ -565,6 +579,8 @@ class NativeRolloutEngine:
             # sampled one would be taken for an image by every later consumer of the sequence)
             c = self.full_cfg
             ids = [c.image_token_id] if getattr(c, "is_vl", False) and c.image_token_id is not None else []
+            if ids and c.extra.get("video_token_id") is not None:
+                ids.append(int(c.extra["video_token_id"]))
             ban = self._banned_ids = torch.tensor(ids, dtype=torch.long, device=self.device)
         if ban.numel():
             logits.index_fill_(1, ban, float("-inf"))

@@ -33,7 +33,8 @@ def create_rl_dataset(data_paths, data_config, tokenizer, processor=None, is_tra
         gt = int(parts[8]) if len(parts) > 8 else None
         return SyntheticPromptDataset(num, lo, hi, id_lo, id_hi, data_config.max_prompt_length, seed, source,
                                       getattr(tokenizer, "pad_token_id", 0) or 0, gt, processor=processor,
-                                      image_size=int(data_config.get("synthetic_image_size", 0) or 0))
+                                      image_size=int(data_config.get("synthetic_image_size", 0) or 0),
+                                      video_frames=int(data_config.get("synthetic_video_frames", 0) or 0))
     return RLHFDataset(data_paths, tokenizer, data_config, processor, max_samples)
 
 

@@ -96,11 +96,13 @@ class RLHFDataset(Dataset):
         messages = row.pop(self.prompt_key)
         toks = self._tokenize(messages)
         images = row.pop(self.config.get("image_key", "images"), None)
+        videos = row.pop(self.config.get("video_key", "videos"), None)
         pos3 = None
-        if images is not None and len(images) and self.processor is not None:
+        has_img, has_vid = images is not None and len(images) > 0, videos is not None and len(videos) > 0
+        if (has_img or has_vid) and self.processor is not None:
             # vision-language prompt: placeholders expanded to one token per merged patch, pixels and grids travel
             # with the row, rows 1..3 of position_ids carry the multimodal RoPE positions
-            toks, mm, pos3 = self.processor(toks, list(images))
+            toks, mm, pos3 = self.processor(toks, list(images) if has_img else None, list(videos) if has_vid else None)
             row["multi_modal_inputs"] = mm
         ids = torch.tensor([toks], dtype=torch.long)
         mask = torch.ones_like(ids)
@@ -141,9 +143,10 @@ class SyntheticPromptDataset(Dataset):
 
     def __init__(self, num_prompts: int, min_len: int, max_len: int, id_lo: int, id_hi: int, max_prompt_length: int,
                  seed: int = 0, data_source: str = "synthetic/even_fraction", pad_token_id: int = 0, ground_truth=None,
-                 processor=None, image_size: int = 0):
+                 processor=None, image_size: int = 0, video_frames: int = 0):
         """``processor`` + ``image_size`` > 0: every prompt starts with one random RGB image of that size (vision-
-        language models); the text length is then in addition to the image placeholders."""
+        language models); the text length is then in addition to the image placeholders. ``video_frames`` > 0: a random
+        video of that many frames of the same size instead of the image."""
         g = torch.Generator().manual_seed(seed)
         self.items = []
         for i in range(num_prompts):
@@ -151,8 +154,12 @@ class SyntheticPromptDataset(Dataset):
             toks = torch.randint(id_lo, id_hi, (n,), generator=g)
             extra_row, pos3 = {}, None
             if processor is not None and image_size > 0:
-                img = torch.randint(0, 256, (image_size, image_size, 3), generator=g, dtype=torch.uint8).numpy()
-                tl, mm, pos3 = processor(toks.tolist(), [img])
+                if video_frames > 0:
+                    vid = torch.randint(0, 256, (video_frames, image_size, image_size, 3), generator=g, dtype=torch.uint8).numpy()
+                    tl, mm, pos3 = processor(toks.tolist(), None, [vid])
+                else:
+                    img = torch.randint(0, 256, (image_size, image_size, 3), generator=g, dtype=torch.uint8).numpy()
+                    tl, mm, pos3 = processor(toks.tolist(), [img])
                 toks = torch.tensor(tl, dtype=torch.long)
                 n = toks.numel()
                 assert n <= max_prompt_length, f"prompt of {n} tokens (with image placeholders) exceeds max_prompt_length"

@@ -85,6 +85,36 @@ def images_to_patches(images, patch_size: int = 14, merge_size: int = 2, tempora
     return torch.cat(pvs, 0), torch.tensor(grids, dtype=torch.long)
 
 
+def videos_to_patches(videos, patch_size: int = 14, merge_size: int = 2, temporal_patch_size: int = 2,
+                      mean=_CLIP_MEAN, std=_CLIP_STD):
+    """Videos (each a list / array of frames ``[T, H, W, 3]``, or a dict with ``frames``) -> ``pixel_values_videos
+    [sum(t * h * w), C * temporal_patch_size * P * P]`` and ``video_grid_thw [n_videos, 3]``: every frame resized as a
+    still image is, ``temporal_patch_size`` consecutive frames share a patch (the last frame is repeated to fill the
+    last one), patches in 2 x 2 merge-block order frame group by frame group (what transformers'
+    ``Qwen2VLVideoProcessor`` produces; verl/utils/dataset/vision_utils.py ``process_video``)."""
+    import torch
+
+    pvs, grids = [], []
+    for video in videos:
+        frames = process_video(video, patch_size)
+        xs = []
+        for im in frames:
+            x = torch.from_numpy(np.asarray(im, dtype=np.float32) / 255.0)
+            xs.append(((x - torch.tensor(mean)) / torch.tensor(std)).permute(2, 0, 1))
+        x = torch.stack(xs)                                                         # [T, 3, H, W]
+        pad = (-x.shape[0]) % temporal_patch_size
+        if pad:
+            x = torch.cat([x, x[-1:].repeat(pad, 1, 1, 1)], 0)
+        T, C, H, W = x.shape
+        gt, gh, gw, m = T // temporal_patch_size, H // patch_size, W // patch_size, merge_size
+        x = x.reshape(gt, temporal_patch_size, C, gh // m, m, patch_size, gw // m, m, patch_size)
+        # -> (gt, gh/m, gw/m, m, m) patch order, each patch flattened as (C, T, P, P)
+        x = x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8).reshape(gt * gh * gw, C * temporal_patch_size * patch_size * patch_size)
+        pvs.append(x)
+        grids.append([gt, gh, gw])
+    return torch.cat(pvs, 0), torch.tensor(grids, dtype=torch.long)
+
+
 def expand_image_placeholders(ids: list[int], grids, image_token_id: int, merge_size: int = 2,
                               vision_start_id: int | None = None, vision_end_id: int | None = None) -> list[int]:
     """Every image placeholder token of ``ids`` becomes ``t * h * w / merge^2`` copies (one per merged patch), image by
@@ -122,10 +152,11 @@ class VLProcessor:
     verl/utils/dataset/rl_dataset.py)."""
 
     def __init__(self, image_token_id: int, patch_size: int = 14, merge_size: int = 2, temporal_patch_size: int = 2,
-                 vision_start_id: int | None = None, vision_end_id: int | None = None):
+                 vision_start_id: int | None = None, vision_end_id: int | None = None, video_token_id: int | None = None):
         self.image_token_id, self.patch_size, self.merge_size = int(image_token_id), int(patch_size), int(merge_size)
         self.temporal_patch_size = int(temporal_patch_size)
         self.vision_start_id, self.vision_end_id = vision_start_id, vision_end_id
+        self.video_token_id = None if video_token_id is None else int(video_token_id)
 
     @classmethod
     def from_model_config(cls, cfg):
@@ -133,21 +164,35 @@ class VLProcessor:
             return None
         v = cfg.extra.get("vision_config") or {}
         return cls(cfg.image_token_id, v.get("patch_size", 14), v.get("spatial_merge_size", 2), v.get("temporal_patch_size", 2),
-                   cfg.extra.get("vision_start_token_id"), cfg.extra.get("vision_end_token_id"))
+                   cfg.extra.get("vision_start_token_id"), cfg.extra.get("vision_end_token_id"), cfg.extra.get("video_token_id"))
 
-    def __call__(self, prompt_ids: list[int], images):
-        """-> (prompt ids with expanded placeholders, multi_modal_inputs dict, mrope positions [3, L])."""
+    def __call__(self, prompt_ids: list[int], images=None, videos=None):
+        """-> (prompt ids with expanded placeholders, multi_modal_inputs dict, mrope positions [3, L]). A video's
+        placeholder run stands for the whole video (one token per merged patch of every frame group); its temporal RoPE
+        position advances by one per frame group (the Qwen2-VL rule; the per-second scaling of Qwen2.5-VL and the
+        timestamp text between the frames of Qwen3-VL prompts are not modelled)."""
         from ...models.vision import get_rope_index
         import torch
 
-        pv, grid = images_to_patches(images, self.patch_size, self.merge_size, self.temporal_patch_size)
-        ids = expand_image_placeholders(list(prompt_ids), grid, self.image_token_id, self.merge_size, self.vision_start_id,
-                                        self.vision_end_id)
-        pos3, _ = get_rope_index(torch.tensor(ids), grid, self.image_token_id, self.merge_size)
-        return ids, {"pixel_values": pv, "image_grid_thw": grid}, pos3
+        ids, mm, grid, vgrid = list(prompt_ids), {}, None, None
+        if videos is not None and len(videos):
+            assert self.video_token_id is not None, "this model has no video placeholder token"
+            pvv, vgrid = videos_to_patches(videos, self.patch_size, self.merge_size, self.temporal_patch_size)
+            ids = expand_image_placeholders(ids, vgrid, self.video_token_id, self.merge_size, self.vision_start_id,
+                                            self.vision_end_id)
+            mm.update(pixel_values_videos=pvv, video_grid_thw=vgrid)
+        if images is not None and len(images):
+            pv, grid = images_to_patches(images, self.patch_size, self.merge_size, self.temporal_patch_size)
+            ids = expand_image_placeholders(ids, grid, self.image_token_id, self.merge_size, self.vision_start_id,
+                                            self.vision_end_id)
+            mm.update(pixel_values=pv, image_grid_thw=grid)
+        pos3, _ = get_rope_index(torch.tensor(ids), grid, self.image_token_id, self.merge_size, video_grid_thw=vgrid,
+                                 video_token_id=self.video_token_id)
+        return ids, mm, pos3
 
 
-def vl_position_ids(input_ids, attention_mask, multi_modal_inputs, image_token_id: int, merge_size: int = 2):
+def vl_position_ids(input_ids, attention_mask, multi_modal_inputs, image_token_id: int, merge_size: int = 2,
+                    video_token_id: int | None = None):
     """[B, 4, S] position ids of padded sequences: row 0 = text positions, rows 1..3 = multimodal RoPE (temporal,
     height, width) from the unpadded tokens of every row and its image grid (verl/utils/dataset/rl_dataset.py and
     verl/models/transformers/qwen2_vl.py ``get_rope_index``)."""
@@ -163,6 +208,8 @@ def vl_position_ids(input_ids, attention_mask, multi_modal_inputs, image_token_i
         m = attention_mask[b].bool()
         mm = multi_modal_inputs[b] if multi_modal_inputs is not None else None
         grid = mm.get("image_grid_thw") if isinstance(mm, dict) else None
-        p3, _ = get_rope_index(input_ids[b][m], grid, image_token_id, merge_size)
+        vgrid = mm.get("video_grid_thw") if isinstance(mm, dict) else None
+        p3, _ = get_rope_index(input_ids[b][m], grid, image_token_id, merge_size, video_grid_thw=vgrid,
+                               video_token_id=video_token_id)
         out[b, 1:, m] = p3
     return out

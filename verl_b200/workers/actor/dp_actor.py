@@ -86,6 +86,9 @@ class DataParallelPPOActor(BasePPOActor):
             if inputs.get("pixel_values") is not None:
                 packed.pixel_values = inputs["pixel_values"].to(self.device)
                 packed.image_grid_thw = inputs["image_grid_thw"].to(self.device)
+            if inputs.get("pixel_values_videos") is not None:
+                packed.pixel_values_videos = inputs["pixel_values_videos"].to(self.device)
+                packed.video_grid_thw = inputs["video_grid_thw"].to(self.device)
         replay = record = False
         if self.router_replay != "disabled":
             flat = torch.nonzero(mask.reshape(-1).bool(), as_tuple=True)[0]  # packed token t sits at (b, s) = flat[t]

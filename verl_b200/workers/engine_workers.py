@@ -405,7 +405,8 @@ class ActorRolloutRefWorker(_WorkerBase):
             v = self.model_config.extra.get("vision_config") or {}
             out.batch["position_ids"] = vl_position_ids(out.batch["input_ids"], out.batch["attention_mask"],
                                                         prompts.non_tensor_batch.get("multi_modal_inputs"),
-                                                        self.model_config.image_token_id, int(v.get("spatial_merge_size", 2)))
+                                                        self.model_config.image_token_id, int(v.get("spatial_merge_size", 2)),
+                                                        video_token_id=self.model_config.extra.get("video_token_id"))
         gen_time = time.perf_counter() - t0
         out.non_tensor_batch.update(prompts.non_tensor_batch)
         n_tok = int(out.batch["response_mask"].sum())
