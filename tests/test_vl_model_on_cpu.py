@@ -165,8 +165,9 @@ def test_vl_rollout_with_images_matches_full_recompute(name):
     assert len(done["text"]) == 7
 
 
-@pytest.mark.parametrize("name,frames", [("tiny-qwen2-vl", 0), ("tiny-qwen3-vl", 0), ("tiny-qwen3-vl", 4)])
-def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch, name, frames):
+@pytest.mark.parametrize("name,frames,agent", [("tiny-qwen2-vl", 0, False), ("tiny-qwen3-vl", 0, False), ("tiny-qwen3-vl", 4, False),
+                                               ("tiny-qwen2-vl", 0, True), ("tiny-qwen3-vl", 4, True)])
+def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch, name, frames, agent):
     """The trainer path for images: dataset rows with pixels and grids (native image -> patch processing, placeholder
     expansion, [4, S] position ids), rollout with images, multimodal RoPE positions of the generated sequences, actor
     and reference log-probs, one update. Two steps of GRPO on the tiny Qwen2-VL preset with synthetic images."""
@@ -189,9 +190,11 @@ def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch, name,
         "actor_rollout_ref.rollout.max_num_batched_tokens=128", "actor_rollout_ref.rollout.tensor_model_parallel_size=1",
         "actor_rollout_ref.rollout.log_prob_micro_batch_size_per_gpu=4", "actor_rollout_ref.ref.log_prob_micro_batch_size_per_gpu=4",
         "actor_rollout_ref.actor.ppo_mini_batch_size=4", "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=4",
-        "actor_rollout_ref.actor.use_kl_loss=true", "actor_rollout_ref.actor.optim.lr=1e-5"])
+        "actor_rollout_ref.actor.use_kl_loss=true", "actor_rollout_ref.actor.optim.lr=1e-5"] + (
+        # server mode: the single-turn agent loop sends the sample's patches and grids with its request (over HTTP)
+        ["actor_rollout_ref.rollout.agent.use_agent_loop=true", "actor_rollout_ref.rollout.agent.num_workers=2"] if agent else []))
     trainer = run_ppo(cfg, spmd=True)
-    assert trainer.global_steps == 2
+    assert trainer.global_steps == 2 and bool(trainer.async_rollout_mode) == agent
     m = [json.loads(l) for l in open(tmp_path / "logs" / "cpu_e2e" / "vl.jsonl")][-1]["data"]
     for key in ("actor/pg_loss", "actor/grad_norm", "actor/kl_loss", "response_length/mean", "training/rollout_probs_diff_mean"):
         assert key in m and math.isfinite(m[key]), key

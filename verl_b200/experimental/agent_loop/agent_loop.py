@@ -67,8 +67,8 @@ class AsyncLLMServerManager:
     async def generate(self, request_id: str, *, prompt_ids: list[int], sampling_params: dict[str, Any],
                        image_data=None, video_data=None) -> TokenOutput:
         server = self._choose_server(request_id)
-        return await server.generate(prompt_ids=prompt_ids, sampling_params=sampling_params,
-                                     request_id=uuid4().hex)
+        kw = {} if image_data is None and video_data is None else {"image_data": image_data, "video_data": video_data}
+        return await server.generate(prompt_ids=prompt_ids, sampling_params=sampling_params, request_id=uuid4().hex, **kw)
 
     async def generate_for_partial(self, request_id: str, *, prompt_ids: list[int], sampling_params: dict[str, Any],
                                    image_data=None, video_data=None) -> tuple[list[int], list[float], bool]:
@@ -198,6 +198,14 @@ class AgentLoopWorker:
         has_lp = all(o.response_logprobs is not None for o in outputs)
         out = assemble_rollout_batch(prompts, pmask, shells, R, pad, with_logprobs=has_lp,
                                      response_masks=[o.response_mask for o in outputs])
+        mms = [(o.multi_modal_data or {}).get("multi_modal_inputs") for o in outputs]
+        if self.processor is not None and any(m is not None for m in mms):
+            # vision-language samples: [B, 4, S] position ids (text positions + multimodal RoPE of prompt and response)
+            from ...utils.dataset.vision_utils import vl_position_ids
+
+            out.batch["position_ids"] = vl_position_ids(out.batch["input_ids"], out.batch["attention_mask"], mms,
+                                                        self.processor.image_token_id, self.processor.merge_size,
+                                                        video_token_id=getattr(self.processor, "video_token_id", None))
         scores = [o.reward_score for o in outputs]
         if all(s is not None for s in scores):
             rm = torch.zeros(B, R)

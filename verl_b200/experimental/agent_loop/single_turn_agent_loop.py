@@ -22,10 +22,15 @@ class SingleTurnAgentLoop(AgentLoopBase):
         # the output is cut to response_length below: do not let the server spend the unused prompt budget on it
         sampling_params = dict(sampling_params)
         sampling_params["max_tokens"] = min(int(sampling_params.get("max_tokens", self.response_length)), self.response_length)
-        out = await self.server_manager.generate(uuid4().hex, prompt_ids=prompt_ids, sampling_params=sampling_params)
+        # vision-language samples: the dataset's patches and grids go with the request (the prompt ids already hold one
+        # placeholder token per merged patch)
+        mm = kwargs.get("multi_modal_inputs")
+        out = await self.server_manager.generate(uuid4().hex, prompt_ids=prompt_ids, sampling_params=sampling_params,
+                                                 image_data=mm if isinstance(mm, dict) and mm else None)
         dt = time.perf_counter() - t0
         ids = out.token_ids[: self.response_length]
         return AgentLoopOutput(prompt_ids=prompt_ids, response_ids=ids, response_mask=[1] * len(ids),
                                response_logprobs=out.log_probs[: self.response_length] if out.log_probs else None,
                                routed_experts=out.routed_experts, num_turns=2,
+                               multi_modal_data={"multi_modal_inputs": mm} if isinstance(mm, dict) and mm else None,
                                metrics=AgentLoopMetrics(generate_sequences=dt, num_preempted=out.num_preempted))

@@ -98,9 +98,9 @@ class NativeAsyncServer:
                     done.set_exception(e)
             if self.tp_group is not None and (inbox or aborts):
                 self._bcast({"add": inbox, "abort": aborts})
-            for rid, prompt, sp in inbox:
+            for rid, prompt, sp, mm in inbox:
                 try:
-                    eng.add_request(rid, prompt, sp)
+                    eng.add_request(rid, prompt, sp, multi_modal_inputs=mm)
                 except Exception as e:
                     fut = self._pending.pop(rid, None)
                     if fut is not None:
@@ -148,9 +148,9 @@ class NativeAsyncServer:
             return "stop"
         for name, args in cmd.get("ctrl", ()):
             getattr(eng, name)(*args)
-        for rid, prompt, sp in cmd.get("add", ()):
+        for rid, prompt, sp, mm in cmd.get("add", ()):
             try:
-                eng.add_request(rid, prompt, sp)
+                eng.add_request(rid, prompt, sp, multi_modal_inputs=mm)
             except Exception:
                 pass  # the leader saw the same error and failed the request
         for rid in cmd.get("abort", ()):
@@ -175,7 +175,28 @@ class NativeAsyncServer:
         return done
 
     # ------------------------------------------------------------------ public
-    def submit(self, prompt_ids: list[int], sampling_params: Optional[dict] = None, request_id: Optional[str] = None) -> Future:
+    def _multi_modal_inputs(self, image_data, video_data) -> Optional[dict]:
+        """What a request brings for its vision placeholders (already expanded in ``prompt_ids``, one token per merged
+        patch): a ``multi_modal_inputs`` dict of patches and grids as the datasets make them, or raw images / videos,
+        which are cut into patches here with the model's geometry (role of the ``multi_modal_data`` that
+        verl/workers/rollout/vllm_rollout/vllm_async_server.py:445-547 hands to the inference engine)."""
+        if isinstance(image_data, dict) and ("pixel_values" in image_data or "pixel_values_videos" in image_data):
+            return image_data
+        if not image_data and not video_data:
+            return None
+        from ...utils.dataset.vision_utils import images_to_patches, videos_to_patches
+
+        v = self.engine.full_cfg.extra.get("vision_config") or {}
+        geo = (int(v.get("patch_size", 14)), int(v.get("spatial_merge_size", 2)), int(v.get("temporal_patch_size", 2)))
+        mm = {}
+        if image_data:
+            mm["pixel_values"], mm["image_grid_thw"] = images_to_patches(list(image_data), *geo)
+        if video_data:
+            mm["pixel_values_videos"], mm["video_grid_thw"] = videos_to_patches(list(video_data), *geo)
+        return mm
+
+    def submit(self, prompt_ids: list[int], sampling_params: Optional[dict] = None, request_id: Optional[str] = None,
+               multi_modal_inputs: Optional[dict] = None) -> Future:
         sp = dict(sampling_params or {})
         if "max_tokens" not in sp and "max_new_tokens" not in sp:
             sp["max_tokens"] = self.response_length + self.prompt_length - len(prompt_ids)
@@ -186,13 +207,13 @@ class NativeAsyncServer:
         fut: Future = Future()
         with self._lock:
             self._pending[rid] = fut
-            self._inbox.append((rid, list(prompt_ids), SamplingParams.from_dict(sp)))
+            self._inbox.append((rid, list(prompt_ids), SamplingParams.from_dict(sp), multi_modal_inputs))
         self._wake.set()
         return fut
 
     async def generate(self, prompt_ids: list[int], sampling_params: Optional[dict] = None, request_id: Optional[str] = None,
                        image_data=None, video_data=None, priority: int = 0) -> TokenOutput:
-        fut = self.submit(prompt_ids, sampling_params, request_id)
+        fut = self.submit(prompt_ids, sampling_params, request_id, self._multi_modal_inputs(image_data, video_data))
         return await asyncio.wrap_future(fut)
 
     async def abort_request(self, request_id: str, reset_prefix_cache: bool = False) -> dict[str, Any]:
@@ -272,7 +293,8 @@ class NativeAsyncServer:
 
         @app.post("/generate")
         async def generate(body: dict):
-            out = await server.generate(body["prompt_ids"], body.get("sampling_params"), body.get("request_id"))
+            out = await server.generate(body["prompt_ids"], body.get("sampling_params"), body.get("request_id"),
+                                        image_data=_decode_tensors(body.get("multi_modal_inputs")))
             res = {"token_ids": out.token_ids, "log_probs": out.log_probs, "stop_reason": out.stop_reason,
                    "num_preempted": out.num_preempted}
             if out.routed_experts is not None:  # int16 [tokens, layers, top-k], as bytes
@@ -343,6 +365,34 @@ class NativeAsyncServer:
 from .utils import run_unvicorn  # noqa: E402,F401  (historical import location)
 
 
+def _encode_tensors(d: Optional[dict]) -> Optional[dict]:
+    """Tensors of a ``multi_modal_inputs`` dict as JSON fields (dtype, shape, base64 bytes)."""
+    if d is None:
+        return None
+    import base64
+
+    import torch
+
+    out = {}
+    for k, t in d.items():
+        t = torch.as_tensor(t).contiguous().cpu()
+        out[k] = {"dtype": str(t.dtype).replace("torch.", ""), "shape": list(t.shape),
+                  "data": base64.b64encode(t.numpy().tobytes()).decode("ascii")}
+    return out
+
+
+def _decode_tensors(d: Optional[dict]) -> Optional[dict]:
+    if d is None:
+        return None
+    import base64
+
+    import numpy as np
+    import torch
+
+    return {k: torch.from_numpy(np.frombuffer(base64.b64decode(v["data"]), dtype=np.dtype(v["dtype"])).reshape(v["shape"]).copy())
+            for k, v in d.items()}
+
+
 def serve_in_thread(server: NativeAsyncServer, address: str = "127.0.0.1") -> str:
     """Serve ``server.build_app()`` from a background thread of this process (its own event loop); returns
     ``host:port``. Used by worker processes, whose main thread belongs to the worker group's command loop."""
@@ -393,8 +443,13 @@ class HttpServerHandle:
     async def generate(self, prompt_ids: list[int], sampling_params: Optional[dict] = None, request_id: Optional[str] = None,
                        image_data=None, video_data=None, priority: int = 0) -> TokenOutput:
         sp = {k: v for k, v in (sampling_params or {}).items() if isinstance(v, (int, float, bool, str, list, type(None)))}
-        body = await self._post("/generate", {"prompt_ids": [int(t) for t in prompt_ids], "sampling_params": sp,
-                                              "request_id": request_id})
+        req = {"prompt_ids": [int(t) for t in prompt_ids], "sampling_params": sp, "request_id": request_id}
+        if image_data is not None or video_data is not None:
+            if not (isinstance(image_data, dict) and video_data is None):
+                raise NotImplementedError("over HTTP the vision inputs travel as a multi_modal_inputs dict of patches and "
+                                          "grids (VLProcessor / the datasets make it); raw images stay in-process")
+            req["multi_modal_inputs"] = _encode_tensors(image_data)
+        body = await self._post("/generate", req)
         routed = body.get("routed_experts")
         if routed is not None:
             import base64
