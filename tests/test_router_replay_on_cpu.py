@@ -172,7 +172,7 @@ def test_rollout_records_the_routing_of_every_input_token():
 import pytest
 
 
-@pytest.mark.parametrize("agent", [False, True])
+@pytest.mark.parametrize("agent", [False, True, "tool"])
 def test_grpo_with_r3_replay_end_to_end(tmp_path, monkeypatch, agent):
     """R3: the rollout's record is replayed in compute_log_prob and in the update (batch generation, and the server
     path of the single-turn agent loop, where the record travels with the HTTP response)."""
@@ -191,6 +191,9 @@ def test_grpo_with_r3_replay_end_to_end(tmp_path, monkeypatch, agent):
     if agent:
         extra += ["actor_rollout_ref.rollout.agent.use_agent_loop=true", "actor_rollout_ref.rollout.agent.num_workers=2",
                   "data.return_raw_chat=true"]
+    if agent == "tool":  # the tool-calling state machine: the latest generation call's record is the sequence's record
+        extra += ["actor_rollout_ref.rollout.multi_turn.enable=true", "actor_rollout_ref.rollout.multi_turn.max_assistant_turns=2",
+                  "actor_rollout_ref.rollout.agent.default_agent_loop=tool_agent"]
     trainer = run_ppo(compose("ppo_trainer", _overrides(tmp_path, extra)), spmd=True)
     assert trainer.global_steps == 2 and "routed_experts" in trainer._last_batch.batch.keys()
     m = [json.loads(l) for l in open(tmp_path / "logs" / "cpu_e2e" / "r3.jsonl")][-1]["data"]

@@ -49,6 +49,7 @@ class AgentData:
     metrics: dict = field(default_factory=lambda: {"generate_sequences": 0.0, "tool_calls": 0.0, "num_preempted": 0})
     interaction: Any = None
     mid_turn: bool = False  # the current assistant turn was cut by an abort and continues in the next generation
+    routed_experts: Any = None  # mixture-of-experts rollouts that record their routing: the latest call's record
 
 
 _TOOLS_CACHE: dict = {}
@@ -116,10 +117,19 @@ class ToolAgentLoop(AgentLoopBase):
         extra = {"turn_scores": data.turn_scores, "tool_rewards": data.tool_rewards}
         if cancelled:
             extra.update(is_cancel=True, agent_data=data)
+        routed = data.routed_experts
+        if routed is not None:
+            # tokens appended after the last call (a final tool response) were never routed: zero rows, like padding
+            import numpy as np
+
+            total = len(data.prompt_ids) + len(ids)
+            full = np.zeros((total,) + tuple(routed.shape[1:]), routed.dtype)
+            full[: min(total, routed.shape[0])] = routed[:total]
+            routed = full
         return AgentLoopOutput(
             prompt_ids=data.prompt_ids, response_ids=ids, response_mask=data.response_mask[: self.response_length],
             response_logprobs=data.response_logprobs[: self.response_length] if data.response_logprobs else None,
-            num_turns=data.user_turns + data.assistant_turns + 1,
+            routed_experts=routed, num_turns=data.user_turns + data.assistant_turns + 1,
             metrics=AgentLoopMetrics(**data.metrics), extra_fields=extra)
 
     # ------------------------------------------------------------------ states
@@ -131,6 +141,10 @@ class ToolAgentLoop(AgentLoopBase):
         out = await self.server_manager.generate(data.request_id, prompt_ids=ctx, sampling_params=sp)
         data.metrics["generate_sequences"] += time.perf_counter() - t0
         data.metrics["num_preempted"] += max(out.num_preempted, 0)
+        if out.routed_experts is not None:
+            # router replay R3: the record of a call covers its whole context (prompt, earlier turns, tool responses)
+            # and its own tokens, so the latest call's record is the record of the sequence so far
+            data.routed_experts = out.routed_experts
         return await self._after_generation(data, list(out.token_ids), list(out.log_probs or []))
 
     async def _after_generation(self, data: AgentData, token_ids: list, log_probs: list, turn_complete: bool = True) -> AgentState:
