@@ -82,3 +82,25 @@ def test_sum_pi_squared_matches_dense_softmax():
         assert bool((spp[i, n:] == 0).all())
     with eng.train_mode():  # the update does not ask for it
         assert actor._want_spp is False
+
+
+@pytest.mark.parametrize("mode", ["token_is", "seq_is", "token_rs", "bypass"])
+def test_rollout_correction_example_modes_train_a_step(tmp_path, monkeypatch, mode):
+    from test_e2e_grpo_on_cpu import _overrides
+
+    from verl_b200.trainer.main_ppo import run_ppo
+    from verl_b200.utils.config import compose
+
+    script = os.path.join(ROOT, "examples", "rollout_correction", "run_qwen2_5-7b_rollout_correction.sh")
+    out = subprocess.run(["bash", script], env={**os.environ, "MODE": mode, "DRY_RUN": "1"}, capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
+    base = _overrides(tmp_path, ["trainer.n_gpus_per_node=1", "trainer.total_training_steps=1", "trainer.save_freq=-1",
+                                 f"trainer.experiment_name={mode}", "data.max_response_length=16", "data.train_batch_size=4",
+                                 "actor_rollout_ref.actor.ppo_mini_batch_size=4", "actor_rollout_ref.rollout.calculate_log_probs=true"])
+    trainer = run_ppo(compose("ppo_trainer", base + out.stdout.split()), spmd=True)
+    assert trainer.global_steps == 1
+    m = [json.loads(l) for l in open(tmp_path / "logs" / "cpu_e2e" / f"{mode}.jsonl")][-1]["data"]
+    assert math.isfinite(m["actor/pg_loss"]) and math.isfinite(m["actor/grad_norm"])
+    if mode != "bypass":  # bypass: the rollout's log-probs ARE the old log-probs, there is no separate pass to compare with
+        assert any(k.startswith("rollout_corr/") for k in m), sorted(m)[:40]
