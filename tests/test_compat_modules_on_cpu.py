@@ -158,3 +158,38 @@ def test_base_interfaces_and_redirected_paths():
     lp, ent = FusedLinearForPPO()(h, w, ids)
     ls = torch.log_softmax(h @ w.T, -1)
     torch.testing.assert_close(lp, ls.gather(-1, ids[:, None])[:, 0]) and torch.testing.assert_close(ent, -(ls.exp() * ls).sum(-1))
+
+
+def test_checkpoint_manager_contents_retention_and_rng(tmp_path):
+    import random
+
+    import numpy as np
+
+    from verl_b200.models import preset
+    from verl_b200.utils.checkpoint.checkpoint_manager import BaseCheckpointManager, NativeCheckpointManager
+    from verl_b200.workers.engine.native import NativeEngine
+
+    class C(dict):
+        __getattr__ = dict.get
+
+    m = BaseCheckpointManager(model=None, checkpoint_config={"save_contents": ["model", "hf_model"], "load_contents": ["model"]})
+    assert m.should_save_model and m.should_save_hf_model and not m.should_save_optimizer and not m.should_save_extra
+    assert m.should_load_model and not m.should_load_optimizer
+    with pytest.raises(NotImplementedError):
+        m.save_checkpoint("x")
+    assert BaseCheckpointManager.checkpath("a", None) == (True, "a") and BaseCheckpointManager.checkpath(None, "h") == (False, "h")
+    st = BaseCheckpointManager.get_rng_state()
+    a = (random.random(), float(np.random.rand()), float(torch.rand(1)))
+    BaseCheckpointManager.load_rng_state(st)
+    assert a == (random.random(), float(np.random.rand()), float(torch.rand(1)))
+
+    # the engine's own saves: at most two folders stay, the weights of the newest come back
+    eng = NativeEngine(preset("tiny-qwen2"), C(), C(lr=1e-3), device="cpu", seed=1).initialize()
+    for step in (1, 2, 3):
+        eng.save_checkpoint(str(tmp_path / f"global_step_{step}"), global_step=step, max_ckpt_to_keep=2)
+    assert sorted(os.listdir(tmp_path)) == ["global_step_2", "global_step_3"]
+    eng2 = NativeEngine(preset("tiny-qwen2"), C(), C(lr=1e-3), device="cpu", seed=9).initialize()
+    mgr = NativeCheckpointManager(eng2, checkpoint_config={"load_contents": ["model"]})
+    mgr.load_checkpoint(str(tmp_path / "global_step_3"))
+    for (k, a_), (_, b_) in zip(eng.zero.named_full_tensors(), eng2.zero.named_full_tensors()):
+        assert torch.equal(a_, b_), k

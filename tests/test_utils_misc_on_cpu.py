@@ -161,3 +161,46 @@ def test_communicator_found_by_name_between_unrelated_processes(tmp_path):
     assert all(p.returncode == 0 for p in procs), [o[1][-1500:] for o in outs]
     assert sorted(o[0].strip() for o in outs) == ["RENDEZVOUS_OK 0", "RENDEZVOUS_OK 1", "RENDEZVOUS_OK 2"]
     assert not os.path.exists(tmp_path / "sync-group.json")
+
+
+def test_small_helpers_with_the_reference_names(tmp_path):
+    from verl_b200.protocol import deserialize_tensordict, serialize_tensordict
+    from verl_b200.utils import tensordict_utils as tu
+    from verl_b200.utils import torch_functional as F_
+    from verl_b200.utils.fs import verify_copy
+    from verl_b200.utils.import_utils import load_class_from_fqn, load_module
+    from verl_b200.utils.memory_utils import MemorySnapshotSampler, reset_memory_stats
+
+    # tensors as bytes: dense (bf16 too) and jagged entries survive the round trip
+    rows = [torch.arange(n, dtype=torch.int64) for n in (3, 1, 4)]
+    td = tu.get_tensordict({"a": torch.randn(3, 5).to(torch.bfloat16), "ids": torch.nested.as_nested_tensor(rows, layout=torch.jagged)})
+    back = deserialize_tensordict(serialize_tensordict(td))
+    assert torch.equal(back["a"], td["a"]) and [r.tolist() for r in back["ids"].unbind()] == [r.tolist() for r in rows]
+    assert tuple(back.batch_size) == (3,)
+    # packed and padded log-prob helpers agree with a dense log-softmax
+    g = torch.Generator().manual_seed(0)
+    ids, logits = torch.randint(0, 17, (3, 9), generator=g), torch.randn(3, 9, 17, generator=g)
+    mask = torch.ones(3, 9, dtype=torch.long)
+    mask[0, :3] = 0
+    want = torch.log_softmax(logits, -1)[:, :-1].gather(-1, ids[:, 1:, None])[..., 0][:, -4:]
+    torch.testing.assert_close(F_.log_probs_from_logits_response(ids, logits, 4), want)
+    idx, cu, longest = F_.get_unpad_data(mask)
+    assert cu.tolist() == [0, 6, 15, 24] and longest == 9
+    torch.testing.assert_close(F_.log_probs_from_logits_response_rmpad(ids, mask, logits.reshape(-1, 17)[idx], 4), want)
+    lin = torch.nn.Linear(3, 2)
+    lin(torch.ones(1, 3)).sum().backward()
+    assert abs(F_.compute_grad_norm(lin) - (6.0 + 2.0)) < 1e-6
+    # files and modules
+    (tmp_path / "src" / "d").mkdir(parents=True)
+    (tmp_path / "src" / "d" / "f.txt").write_text("abc")
+    import shutil
+
+    shutil.copytree(tmp_path / "src", tmp_path / "dst")
+    assert verify_copy(str(tmp_path / "src"), str(tmp_path / "dst"))
+    (tmp_path / "dst" / "d" / "f.txt").write_text("abcd")
+    assert not verify_copy(str(tmp_path / "src"), str(tmp_path / "dst"))
+    (tmp_path / "m.py").write_text("VALUE = 41\n")
+    assert load_module(str(tmp_path / "m.py")).VALUE == 41 and load_module("pkg://json").dumps([1]) == "[1]"
+    assert load_class_from_fqn("collections.OrderedDict").__name__ == "OrderedDict"
+    reset_memory_stats()
+    assert MemorySnapshotSampler(str(tmp_path / "snaps")).dump_memory_snapshot().endswith("periodic_00000.pickle")

@@ -599,6 +599,51 @@ class DataProto:
         return "\n".join(lines)
 
 
+# ------------------------------------------------------------------ tensors as plain bytes
+# A copy-free wire format for tensors and TensorDicts (bytes + dtype name + shape; nested tensors row by row), for
+# transports that move buffers rather than pickles (verl/protocol.py:252-304).
+def serialize_single_tensor(obj: torch.Tensor):
+    """-> (dtype name, shape, uint8 numpy view of the tensor's bytes)."""
+    t = obj.detach().cpu().contiguous()
+    return str(t.dtype).removeprefix("torch."), tuple(t.shape), t.flatten().view(torch.uint8).numpy()
+
+
+def deserialize_single_tensor(arr) -> torch.Tensor:
+    dtype, shape, data = arr
+    torch_dtype = getattr(torch, dtype)
+    assert isinstance(torch_dtype, torch.dtype), dtype
+    raw = torch.frombuffer(bytearray(data), dtype=torch.uint8) if len(data) else torch.empty(0, dtype=torch.uint8)
+    return raw.view(torch_dtype).view(tuple(shape))
+
+
+def serialize_tensordict(batch: TensorDict):
+    """-> (batch size, device name or None, {key: encoded tensor | (layout name, [encoded rows])}). Tensor entries only."""
+    items = {}
+    for k, v in batch.items():
+        if not isinstance(v, torch.Tensor):
+            raise TypeError(f"serialize_tensordict takes tensor entries only, got {type(v).__name__} for {k!r}")
+        if v.is_nested:
+            items[k] = (str(v.layout).removeprefix("torch."), [serialize_single_tensor(r) for r in v.unbind()])
+        else:
+            items[k] = serialize_single_tensor(v)
+    dev = getattr(batch, "device", None)
+    return tuple(batch.batch_size), (str(dev) if dev is not None else None), items
+
+
+def deserialize_tensordict(arr) -> TensorDict:
+    batch_size, _device, items = arr
+    out = {}
+    for k, v in items.items():
+        if len(v) == 3:
+            out[k] = deserialize_single_tensor(v)
+        elif len(v) == 2:
+            layout, rows = v
+            out[k] = torch.nested.as_nested_tensor([deserialize_single_tensor(r) for r in rows], layout=getattr(torch, layout))
+        else:
+            raise ValueError(f"Invalid tensor encoding format, expected length 2 or 3, got {len(v)}")
+    return TensorDict(out, batch_size=tuple(batch_size))
+
+
 @dataclass
 class DataProtoFuture:
     """Lazy handle on per-worker results (verl/protocol.py:1184-1239).

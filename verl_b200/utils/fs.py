@@ -54,3 +54,28 @@ def copy_to_local(src: str, cache_dir: Optional[str] = None, filelock: str = ".f
 def local_mkdir_safe(path: str) -> str:
     os.makedirs(os.path.expanduser(path), exist_ok=True)
     return path
+
+
+def verify_copy(src: str, dest: str) -> bool:
+    """True when ``dest`` looks like a complete copy of ``src``: the same kind, the same relative file tree, the same
+    file sizes."""
+    if not (os.path.exists(src) and os.path.exists(dest)) or os.path.isfile(src) != os.path.isfile(dest):
+        return False
+    if os.path.isfile(src):
+        return os.path.getsize(src) == os.path.getsize(dest)
+
+    def tree(root):
+        out = {}
+        for d, _, files in os.walk(root):
+            for f in files:
+                p = os.path.join(d, f)
+                out[os.path.relpath(p, root)] = os.path.getsize(p)
+        return out
+
+    return tree(src) == tree(dest)
+
+
+def copy_local_path_from_hdfs(src: str, cache_dir: Optional[str] = None, filelock: str = ".file.lock", verbose: bool = False,
+                              always_recopy: bool = False) -> str:
+    """Historical name of :func:`copy_to_local`."""
+    return copy_to_local(src, cache_dir=cache_dir, filelock=filelock, verbose=verbose, always_recopy=always_recopy)

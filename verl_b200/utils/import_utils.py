@@ -77,3 +77,41 @@ def is_transformers_version_in_range(min_version: Optional[str] = None, max_vers
 
 def is_version_ge(pkg: str = "transformers", minver: str = "0") -> bool:
     return is_version_in_range(pkg, min_version=minver)
+
+
+def load_module(module_path: str, module_name: Optional[str] = None):
+    """A module from a file path (``pkg://a.b`` or a dotted name imports a module by name)."""
+    if not module_path:
+        return None
+    if module_path.startswith("pkg://"):
+        return importlib.import_module(module_path[len("pkg://"):])
+    import os
+    import sys
+
+    if not os.path.exists(module_path):
+        return importlib.import_module(module_path)
+    name = module_name or f"custom_module_{abs(hash(os.path.abspath(module_path)))}"
+    spec = importlib.util.spec_from_file_location(name, module_path)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def load_class_from_fqn(fqn: str, description: str = "class"):
+    """``package.module.Class`` -> the class object."""
+    mod, _, name = str(fqn).rpartition(".")
+    if not mod:
+        raise ValueError(f"Invalid {description} name {fqn!r}: expected package.module.Name")
+    try:
+        return getattr(importlib.import_module(mod), name)
+    except (ImportError, AttributeError) as e:
+        raise ImportError(f"Cannot load {description} {fqn!r}: {e}") from e
+
+
+def is_nvtx_available() -> bool:
+    return is_package_available("nvtx")
+
+
+def is_trl_available() -> bool:
+    return is_package_available("trl")

@@ -44,3 +44,31 @@ def enable_memory_visualize(trace_alloc_max_entries: int = 200_000, stack_depth:
 def dump_memory_snapshot(path: str) -> None:
     if torch.cuda.is_available():
         torch.cuda.memory._dump_snapshot(path)
+
+
+def reset_memory_stats() -> None:
+    """Reset the allocator's peak counters (before a phase whose peak is to be measured)."""
+    import torch
+
+    if torch.cuda.is_available():
+        torch.cuda.reset_peak_memory_stats()
+        torch.cuda.reset_accumulated_memory_stats()
+
+
+class MemorySnapshotSampler:
+    """Allocator snapshots of a run, one file per call, numbered, under ``out_dir/<tag>`` (viewable with
+    pytorch.org/memory_viz; verl/utils/memory_utils.py ``MemorySnapshotSampler``). ``enable_memory_visualize`` must have
+    switched the allocator's history on."""
+
+    def __init__(self, out_dir: str = "./mem_snapshots", tag: str = "periodic"):
+        self.out_dir, self.tag, self.count = out_dir, tag, 0
+
+    def dump_memory_snapshot(self, out_dir: str | None = None, tag: str | None = None, sub_dir: str | None = None) -> str:
+        import os
+
+        d = os.path.join(out_dir or self.out_dir, sub_dir or "")
+        os.makedirs(d, exist_ok=True)
+        path = os.path.join(d, f"{tag or self.tag}_{self.count:05d}.pickle")
+        self.count += 1
+        dump_memory_snapshot(path)
+        return path

@@ -56,6 +56,13 @@ def concat_tensordict(data: list[TensorDict]) -> TensorDict:
     return TensorDict.cat(data, 0)
 
 
+def concat_tensordict_with_none_bsz(data: list[TensorDict]) -> TensorDict:
+    """Results without a batch dimension (only batch-level data, e.g. per-worker metrics): the first one stands for all."""
+    for d in data:
+        assert len(d.batch_size) == 0, "concat_tensordict_with_none_bsz takes TensorDicts without a batch dimension"
+    return data[0]
+
+
 def chunk_tensordict(td: TensorDict, chunks: int) -> list[TensorDict]:
     n = td.batch_size[0]
     assert n % chunks == 0, f"expecting td with length divisible by chunks, but got {n} and {chunks}"

@@ -222,3 +222,91 @@ def distributed_masked_mean(local: torch.Tensor, mask: torch.Tensor) -> torch.Te
     dist.all_reduce(s)
     dist.all_reduce(n)
     return (s / n).to(local.dtype).squeeze()
+
+
+# ----------------------------------------------------- log-probs from materialised logits (padded / packed layouts)
+def gather_from_labels(data: torch.Tensor, label: torch.Tensor) -> torch.Tensor:
+    """``data[..., label]``: the entry of the last dimension that ``label`` names, per position."""
+    return torch.gather(data, -1, label.unsqueeze(-1)).squeeze(-1)
+
+
+def logprobs_from_logits_naive(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    return gather_from_labels(torch.log_softmax(logits, dim=-1), labels)
+
+
+def post_process_logits(input_ids, logits: torch.Tensor, temperature: float, top_k=None, top_p=None) -> torch.Tensor:
+    """Temperature scaling in place (top-k / top-p warping changes the policy's support and is left to the sampler)."""
+    return logits.div_(temperature) if temperature != 1.0 else logits
+
+
+def log_probs_from_logits_response(input_ids: torch.Tensor, logits: torch.Tensor, response_length: int) -> torch.Tensor:
+    """``logits = model(input_ids)`` ``[B, S, V]`` -> log-probs of the last ``response_length`` tokens ``[B, R]``
+    (position t predicts token t + 1)."""
+    return logprobs_from_logits(logits[:, -response_length - 1 : -1], input_ids[:, -response_length:])
+
+
+def get_unpad_data(attention_mask: torch.Tensor):
+    """(flat indices of the kept tokens, cu_seqlens int32 [B + 1], longest sequence) of a padded batch."""
+    lens = attention_mask.sum(dim=-1, dtype=torch.int32)
+    idx = torch.nonzero(attention_mask.flatten(), as_tuple=False).flatten()
+    cu = torch.nn.functional.pad(torch.cumsum(lens, 0, dtype=torch.int32), (1, 0))
+    return idx, cu, int(lens.max().item())
+
+
+def log_probs_from_logits_all_rmpad(input_ids_rmpad: torch.Tensor, logits_rmpad: torch.Tensor, indices: torch.Tensor,
+                                    batch_size: int, seqlen: int, response_length: int) -> torch.Tensor:
+    """Packed ids ``[1, nnz]`` (or ``[nnz]``) and packed logits ``[nnz, V]`` with the flat ``indices`` of the packed
+    tokens in the ``[B, S]`` layout -> response log-probs ``[B, R]`` (zeros at padding). Within the packed stream token
+    t + 1 is the label of position t; the roll's wrap-around at a sequence's last token lands on a position that is
+    never a response row of the padded layout."""
+    ids = input_ids_rmpad.reshape(-1)
+    lp = logprobs_from_logits(logits_rmpad, torch.roll(ids, -1, 0))
+    full = torch.zeros(batch_size * seqlen, dtype=lp.dtype, device=lp.device)
+    full[indices] = lp
+    return full.view(batch_size, seqlen)[:, -response_length - 1 : -1]
+
+
+def log_probs_from_logits_response_rmpad(input_ids: torch.Tensor, attention_mask: torch.Tensor, logits_rmpad: torch.Tensor,
+                                         response_length: int) -> torch.Tensor:
+    """Padded ids / mask ``[B, S]`` and packed logits ``[nnz, V]`` -> response log-probs ``[B, R]``."""
+    b, s = input_ids.shape
+    idx, _, _ = get_unpad_data(attention_mask)
+    return log_probs_from_logits_all_rmpad(input_ids.reshape(-1)[idx], logits_rmpad, idx, b, s, response_length)
+
+
+def compute_grad_norm(model) -> float:
+    """SUM OF SQUARES of all gradients of ``model`` (take the square root for the L2 norm)."""
+    return float(sum(torch.sum(torch.square(p.grad.detach().float())) for p in model.parameters() if p.grad is not None))
+
+
+def broadcast_dict_tensor(tensors, src: int, group) -> None:
+    import torch.distributed as dist
+
+    for key in sorted(tensors.keys()):
+        dist.broadcast(tensors[key], src=src, group=group)
+
+
+def split_dict_tensor_into_batches(tensors, batch_size: int) -> list:
+    n = tensors.batch_size[0]
+    assert n % batch_size == 0, f"input data batch size: {n}, split batch size: {batch_size}"
+    return tensors.split(batch_size)
+
+
+def expand_as_nested(tensor: torch.Tensor, nested_tensor: torch.Tensor) -> torch.Tensor:
+    """``tensor [B]`` -> a jagged tensor shaped like ``nested_tensor [B, j]`` whose row i repeats ``tensor[i]``."""
+    assert nested_tensor.is_nested, "nested_tensor must be nested"
+    assert tensor.shape[0] == nested_tensor.shape[0], f"The batch shape must be the same. Got {tensor.shape[0]} vs {nested_tensor.shape[0]}"
+    offsets = nested_tensor.offsets()
+    return torch.nested.nested_tensor_from_jagged(torch.repeat_interleave(tensor, offsets.diff()), offsets=offsets)
+
+
+def prepare_decoder_attention_mask(attention_mask: Optional[torch.Tensor], input_shape, inputs_embeds: torch.Tensor) -> torch.Tensor:
+    """Additive ``[B, 1, T, T]`` mask of a decoder: causal, and the most negative value at padded keys."""
+    b, t = input_shape
+    neg = torch.finfo(inputs_embeds.dtype).min
+    mask = torch.zeros(b, 1, t, t, dtype=inputs_embeds.dtype, device=inputs_embeds.device)
+    if t > 1:
+        mask = mask.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool, device=mask.device), 1), neg)
+    if attention_mask is not None:
+        mask = mask.masked_fill(~attention_mask.bool()[:, None, None, :].to(mask.device), neg)
+    return mask

@@ -182,3 +182,18 @@ def ulysses_pad_and_slice_inputs(input_ids: torch.Tensor, position_ids: Optional
     if pos is not None:
         pos = slice_input_tensor(pos, -1, padding=False, group=group)
     return ids, pos, pad
+
+
+def all_gather_tensor(local_tensor: torch.Tensor, gather_dim: int, group=None) -> torch.Tensor:
+    """All ranks' ``local_tensor`` concatenated along ``gather_dim`` (no gradient; see :func:`gather_outputs_and_unpad`
+    for the differentiable form)."""
+    group = get_ulysses_sequence_parallel_group() if group is None else group
+    world = dist.get_world_size(group) if group is not None else 1
+    if world == 1:
+        return local_tensor
+    parts = [torch.empty_like(local_tensor) for _ in range(world)]
+    dist.all_gather(parts, local_tensor.contiguous(), group=group)
+    return torch.cat(parts, dim=gather_dim)
+
+
+gather_outpus_and_unpad = gather_outputs_and_unpad  # the reference's historical spelling

@@ -1100,9 +1100,15 @@ class NativeEngine(BaseEngine):
                         save_contents=("model", "optimizer", "extra"), **kwargs):
         """verl FSDP layout: ``model_world_size_{W}_rank_{r}.pt``, ``optim_...``, ``extra_state_...``,
         ``fsdp_config.json``, ``huggingface/`` (verl/utils/checkpoint/fsdp_checkpoint_manager.py:56-362)."""
-        from ...utils.checkpoint.native_checkpoint import save_engine_checkpoint
+        from ...utils.checkpoint.checkpoint_manager import NativeCheckpointManager
 
-        save_engine_checkpoint(self, local_path, global_step=global_step, save_contents=save_contents)
+        # the manager keeps the list of folders this engine has written: ``max_ckpt_to_keep`` removes the oldest before
+        # a new save, ``hdfs_path`` receives a copy of the finished folder
+        mgr = getattr(self, "_ckpt_manager", None)
+        if mgr is None:
+            mgr = self._ckpt_manager = NativeCheckpointManager(self)
+        mgr.checkpoint_save_contents = list(save_contents)
+        mgr.save_checkpoint(local_path, hdfs_path, global_step=global_step, max_ckpt_to_keep=max_ckpt_to_keep)
 
     def load_checkpoint(self, local_path: str, hdfs_path=None, del_local_after_load: bool = False,
                         load_contents=("model", "optimizer", "extra"), **kwargs):
