@@ -117,3 +117,53 @@ def extract_multi_modal_inputs(batch_data: list[dict], indices=None) -> dict:
         vals = [d[k] for d in picked if d and k in d]
         out[k] = torch.cat(vals, dim=0) if all(isinstance(v, torch.Tensor) for v in vals) else vals
     return out
+
+
+def check_exclude_modules(config, key: str) -> bool:
+    """True when the module named ``key`` is excluded by an adapter config's ``exclude_modules`` (a regular expression
+    given as a string, or a list of module names / name suffixes)."""
+    excl = getattr(config, "exclude_modules", None) if not isinstance(config, dict) else config.get("exclude_modules")
+    if not excl:
+        return False
+    if isinstance(excl, str):
+        import re
+
+        return re.fullmatch(excl, key) is not None
+    return key in excl or any(key.endswith(f".{e}") for e in excl)
+
+
+def get_generation_config(model: str, trust_remote_code: bool = False):
+    """``generation_config.json`` of a checkpoint directory (or the defaults derived from its ``config.json``); None when
+    neither is there."""
+    try:
+        from transformers import AutoConfig, GenerationConfig
+    except ImportError:
+        return None
+    try:
+        return GenerationConfig.from_pretrained(model)
+    except (OSError, ValueError):
+        try:
+            return GenerationConfig.from_model_config(AutoConfig.from_pretrained(model, trust_remote_code=trust_remote_code))
+        except (OSError, ValueError):
+            return None
+
+
+def get_hf_model_path(config) -> str:
+    """Local directory of ``config.model.path`` (remote paths are fetched first)."""
+    from .fs import copy_to_local, is_non_local
+
+    path = config.model.path
+    return copy_to_local(path, use_shm=bool(config.model.get("use_shm", False))) if is_non_local(path) else path
+
+
+class LambdaLayer(nn.Module):
+    def __init__(self, fn):
+        super().__init__()
+        self.fn = fn
+
+    def forward(self, *args, **kwargs):
+        return self.fn(*args, **kwargs)
+
+
+def squeeze(x: torch.Tensor) -> torch.Tensor:
+    return torch.squeeze(x, dim=-1)
