@@ -193,3 +193,45 @@ def test_checkpoint_manager_contents_retention_and_rng(tmp_path):
     mgr.load_checkpoint(str(tmp_path / "global_step_3"))
     for (k, a_), (_, b_) in zip(eng.zero.named_full_tensors(), eng2.zero.named_full_tensors()):
         assert torch.equal(a_, b_), k
+
+
+def test_dataset_split_metric_chain_profiler_predicates_and_worker_dispatch_info(tmp_path):
+    import json
+
+    from verl_b200.single_controller.base import Worker
+    from verl_b200.utils.dataset.rl_dataset import RLHFDataset, get_dataset_class
+    from verl_b200.utils.metric import AggregationType, Metric
+    from verl_b200.utils.profiler.profile import DistProfiler, mark_annotate
+    from verl_b200.utils.tokenizer import IntTokenizer
+
+    f = tmp_path / "p.jsonl"
+    f.write_text("\n".join(json.dumps({"prompt": " ".join(str(3 + j) for j in range(2 + i)), "data_source": "x"}) for i in range(7)))
+    ds = RLHFDataset(str(f), IntTokenizer(64), {"max_prompt_length": 6, "filter_overlong_prompts": False})
+    parts = ds.split(3)
+    assert [len(p) for p in parts] == [3, 2, 2] and parts[1][0]["raw_prompt_ids"] == ds[3]["raw_prompt_ids"]
+    with pytest.raises(ValueError):
+        ds.split(0)
+    ds.filter_overlong_prompts = True
+    assert len(ds.maybe_filter_out_long_prompts()) == 5  # prompts of 2..6 tokens fit
+    assert get_dataset_class({"custom_cls": {"path": None, "name": None}}) is RLHFDataset
+    (tmp_path / "mine.py").write_text("class D:\n    def __len__(self):\n        return 0\n    def __getitem__(self, i):\n        raise IndexError\nX = 3\n")
+    assert get_dataset_class({"custom_cls": {"path": str(tmp_path / "mine.py"), "name": "D"}}).__name__ == "D"
+    with pytest.raises(TypeError):
+        get_dataset_class({"custom_cls": {"path": str(tmp_path / "mine.py"), "name": "X"}})
+
+    m = Metric.chain([Metric("max", [1, 5]), Metric("max", 3)])
+    assert m.aggregation == AggregationType.MAX and m.aggregate() == 5.0 and Metric.chain([]).aggregation == AggregationType.MEAN
+
+    p = DistProfiler(1, {"enable": True, "ranks": [1], "tool": "none"})
+    assert p.check_enable() and p.check_this_rank() and not p.check_this_step() and not p.is_discrete_mode()
+    p.start()
+    assert p.check_this_step()
+    p.stop()
+    assert not p.check_this_step() and not DistProfiler(0, {"enable": True, "ranks": [1]}).check_this_rank()
+    assert mark_annotate("phase")(lambda a, b=1: a + b)(2, b=3) == 5
+
+    w = Worker()
+    w._register_dispatch_collect_info("actor", 3, True)
+    assert w.get_dispatch_collect() == {"dispatch_dp_rank": {"actor": 3}, "collect_dp_rank": {"actor": True}}
+    w.set_dispatch_collect("ref", {"actor": 3}, {"actor": True})
+    assert w._query_dispatch_info("ref") == 3 and w.query_collect_info("ref")

@@ -287,3 +287,33 @@ class AgentLoopManager:
     def sleep(self):
         for r in self.rollout_replicas:
             asyncio.run(r.sleep())
+
+    def _run_all(self, coros: list) -> list:
+        async def run_all():
+            return await asyncio.gather(*coros)
+
+        return asyncio.run(run_all()) if coros else []
+
+    def _targets(self) -> list:
+        """The replicas when there are any, else the server handles themselves (the colocated layout)."""
+        return list(self.rollout_replicas) or list(self.server_handles)
+
+    def clear_kv_cache(self):
+        """Drop all cached keys / values (prefix cache included) of every replica without putting it to sleep."""
+        self._run_all([t.clear_kv_cache() for t in self._targets() if hasattr(t, "clear_kv_cache")])
+
+    def start_profile(self, **kwargs):
+        self._run_all([t.start_profile(**kwargs) for t in self._targets() if hasattr(t, "start_profile")])
+
+    def stop_profile(self):
+        self._run_all([t.stop_profile() for t in self._targets() if hasattr(t, "stop_profile")])
+
+
+async def get_trajectory_info(step: int, index: list, validate: bool) -> list[dict]:
+    """One record per sample for rollout traces: the trainer step, the dataset index of the sample's prompt and the
+    number of the sample among the consecutive samples of the same prompt."""
+    out, n = [], 0
+    for i, idx in enumerate(index):
+        n = n + 1 if i > 0 and index[i - 1] == idx else 0
+        out.append({"step": step, "sample_index": idx, "rollout_n": n, "validate": validate})
+    return out

@@ -79,6 +79,20 @@ for _n in ("RANK_ZERO", "ONE_TO_ALL", "ALL_TO_ALL", "DP_COMPUTE", "DP_COMPUTE_PR
     Dispatch.register(_n)
 
 
+def init_predefined_dispatch_mode():
+    """(Re-)register the built-in dispatch modes (after a test removed or shadowed one)."""
+    for n in ("RANK_ZERO", "ONE_TO_ALL", "ALL_TO_ALL", "DP_COMPUTE", "DP_COMPUTE_PROTO", "DP_COMPUTE_PROTO_WITH_FUNC",
+              "DP_COMPUTE_METRIC", "DIRECT_ROLLOUT_METHOD"):
+        if Dispatch.from_name(n) is None:
+            Dispatch.register(n)
+
+
+def init_predefined_execute_mode():
+    for n in ("ALL", "RANK_ZERO"):
+        if Execute.from_name(n) is None:
+            Execute.register(n)
+
+
 class Execute(DynamicEnum):
     _registry = {}
     _next_value = 0

@@ -90,6 +90,26 @@ class Worker(WorkerHelper):
         assert mesh_name in self.__collect_dp_rank, f"{mesh_name} is not registered in {self.__class__.__name__}"
         return self.__collect_dp_rank[mesh_name]
 
+    def query_collect_info(self, mesh_name: str) -> bool:
+        """Whether this worker's output is collected for ``mesh_name`` (plain method: for callers inside the worker)."""
+        assert mesh_name in self.__collect_dp_rank, f"{mesh_name} is not registered in {self.__class__.__name__}"
+        return self.__collect_dp_rank[mesh_name]
+
+    @register(dispatch_mode=Dispatch.ONE_TO_ALL)
+    def get_dispatch_collect(self) -> dict:
+        """All registered meshes: ``{"dispatch_dp_rank": {mesh: dp rank}, "collect_dp_rank": {mesh: bool}}``."""
+        return {"dispatch_dp_rank": dict(self.__dispatch_dp_rank), "collect_dp_rank": dict(self.__collect_dp_rank)}
+
+    @register(dispatch_mode=Dispatch.ALL_TO_ALL)
+    def set_dispatch_collect(self, mesh_name: str, dispatch_dp_rank: dict, collect_dp_rank: dict) -> None:
+        """Give ``mesh_name`` the registration of another mesh's layout on this worker: the dictionaries are those of
+        :meth:`get_dispatch_collect` of the worker that should be mirrored (a role that shares another role's
+        data-parallel layout without building an engine of its own)."""
+        assert mesh_name not in self.__dispatch_dp_rank, f"{mesh_name} is already registered"
+        src = next(iter(dispatch_dp_rank)) if len(dispatch_dp_rank) == 1 else mesh_name
+        self.__dispatch_dp_rank[mesh_name] = dispatch_dp_rank[src]
+        self.__collect_dp_rank[mesh_name] = collect_dp_rank[src]
+
     def get_fused_worker_by_name(self, worker_name: str):
         return self.fused_worker_dict.get(worker_name, None)
 

@@ -91,6 +91,29 @@ class RLHFDataset(Dataset):
     def __len__(self):
         return len(self.rows)
 
+    def split(self, num_splits: int) -> list["RLHFDataset"]:
+        """``num_splits`` datasets over consecutive, near-equal parts of the rows (the first ``len % num_splits`` parts
+        hold one row more); they share the tokenizer, the processor and the configuration (the per-rollouter shares
+        of the fully asynchronous pipeline; verl/utils/dataset/rl_dataset.py:398-447)."""
+        if not isinstance(num_splits, int) or num_splits <= 0:
+            raise ValueError(f"num_splits must be a positive integer, got {num_splits}")
+        base, extra = divmod(len(self.rows), num_splits)
+        out, lo = [], 0
+        for i in range(num_splits):
+            hi = lo + base + (1 if i < extra else 0)
+            part = copy.copy(self)
+            part.rows = self.rows[lo:hi]
+            out.append(part)
+            lo = hi
+        return out
+
+    def maybe_filter_out_long_prompts(self, rows: Optional[list] = None) -> list:
+        """The rows whose tokenised prompt fits ``max_prompt_length`` (all rows when ``filter_overlong_prompts`` is off)."""
+        rows = self.rows if rows is None else rows
+        if not self.filter_overlong_prompts:
+            return rows
+        return [r for r in rows if len(self._tokenize(r[self.prompt_key])) <= self.max_prompt_length]
+
     def __getitem__(self, item):
         row = dict(self.rows[item])
         messages = row.pop(self.prompt_key)
@@ -180,3 +203,19 @@ class SyntheticPromptDataset(Dataset):
 
     def __getitem__(self, i):
         return dict(self.items[i])
+
+
+def get_dataset_class(data_config):
+    """``data.custom_cls`` (``path`` + ``name``: a ``torch.utils.data.Dataset`` subclass, or any class with ``__len__`` and
+    ``__getitem__``, from a user's file) or :class:`RLHFDataset`."""
+    from ..py_functional import load_extern_object
+
+    cc = data_config.get("custom_cls") if hasattr(data_config, "get") else getattr(data_config, "custom_cls", None)
+    path = (cc.get("path") if hasattr(cc, "get") else getattr(cc, "path", None)) if cc else None
+    if not path:
+        return RLHFDataset
+    cls = load_extern_object(path, cc.get("name") if hasattr(cc, "get") else cc.name)
+    if not (isinstance(cls, type) and hasattr(cls, "__len__") and hasattr(cls, "__getitem__")):
+        raise TypeError(f"The custom dataset class '{getattr(cls, '__name__', cls)}' from '{path}' must be a dataset class "
+                        "(__len__ and __getitem__)")
+    return cls

@@ -67,6 +67,14 @@ class Metric:
         return float(fn(self.values))
 
     @classmethod
+    def chain(cls, metric_lists: list["Metric"]) -> "Metric":
+        """One metric holding the values of all (same aggregation); an empty list gives an empty mean metric."""
+        out = cls(metric_lists[0].aggregation if metric_lists else AggregationType.MEAN)
+        for m in metric_lists:
+            out.extend(m)
+        return out
+
+    @classmethod
     def aggregate_dp(cls, metric_lists: list["Metric"]) -> float:
         vals = [v for m in metric_lists for v in m.values]
         return cls(metric_lists[0].aggregation, vals).aggregate()

@@ -45,6 +45,21 @@ def mark_end_range(range_id=None):
         torch.cuda.nvtx.range_pop()
 
 
+def mark_annotate(message: Optional[str] = None, color: Optional[str] = None, domain: Optional[str] = None,
+                  category: Optional[str] = None) -> Callable:
+    """Decorator: the function runs inside an NVTX range named ``message`` (or after the function)."""
+
+    def decorator(fn):
+        @functools.wraps(fn)
+        def wrapper(*args, **kw):
+            with nvtx_range(message or fn.__name__, color):
+                return fn(*args, **kw)
+
+        return wrapper
+
+    return decorator
+
+
 class DistProfiler:
     """Per-rank profiler chosen by ``config.tool``; inactive ranks are no-ops."""
 
@@ -59,10 +74,27 @@ class DistProfiler:
         self.tool_config = tool_config or _get(config, "tool_config", None)
         self._prof = None
         self._step = None
+        self._enable, self._this_rank, self._this_step = enable, self.active, False
+        # discrete mode: every annotated phase is a capture of its own instead of one capture per step
+        self._discrete = bool(_get(self.tool_config, "discrete", False))
+
+    def check_enable(self) -> bool:
+        return self._enable
+
+    def check_this_rank(self) -> bool:
+        return self._this_rank
+
+    def check_this_step(self) -> bool:
+        """True between ``start`` and ``stop`` on a rank that profiles."""
+        return self._this_step
+
+    def is_discrete_mode(self) -> bool:
+        return self._discrete
 
     def start(self, role: Optional[str] = None, profile_step: Optional[str] = None, **kwargs):
         if not self.active:
             return
+        self._this_step = True
         self._step = profile_step
         if self.tool == "nsys":
             torch.cuda.profiler.start()
@@ -79,6 +111,7 @@ class DistProfiler:
     def stop(self):
         if not self.active:
             return
+        self._this_step = False
         if self.tool == "nsys":
             torch.cuda.profiler.stop()
         elif self.tool == "torch" and self._prof is not None:
