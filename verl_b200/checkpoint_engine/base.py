@@ -221,6 +221,35 @@ class NCCLCheckpointEngine(CheckpointEngineWithCache):
                 break
 
 
+class CheckpointEngineWorker:
+    """The rollout side of a weight transfer as a worker: owns a checkpoint engine built from
+    ``rollout.checkpoint_engine`` and a rollout adapter (anything with ``update_weights(iterator of (name, tensor))``);
+    ``update_weights`` receives what the trainer side sends and hands it to the adapter
+    (verl/checkpoint_engine/base.py:244-280). Worker groups call its two methods on every replica process."""
+
+    def __init__(self, rollout_config, model_config=None, server_adapter=None, **engine_kwargs):
+        self.rollout_config, self.model_config, self.server_adapter = rollout_config, model_config, server_adapter
+        get = rollout_config.get if hasattr(rollout_config, "get") else (lambda k, d=None: getattr(rollout_config, k, d))
+        self.checkpoint_engine = build_checkpoint_engine(get("checkpoint_engine", None) or {}, **engine_kwargs)
+
+    async def update_weights(self):
+        async def feed(items):
+            res = self.server_adapter.update_weights(items)
+            if asyncio.iscoroutine(res):
+                await res
+
+        weights = self.checkpoint_engine.receive_weights()
+        if hasattr(weights, "__aiter__"):
+            # tensors are views of a bucket that the next bucket overwrites: the adapter takes each one as it arrives
+            async for item in weights:
+                await feed(iter([item]))
+        else:
+            await feed(weights)
+
+    def execute_checkpoint_engine(self, method: str, *args, **kwargs):
+        return getattr(self.checkpoint_engine, method)(*args, **kwargs)
+
+
 class CheckpointEngineManager:
     """Drives a weight sync: trainer worker group -> rollout replicas (verl/checkpoint_engine/base.py:286-410)."""
 

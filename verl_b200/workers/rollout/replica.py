@@ -45,6 +45,20 @@ class RolloutReplica(ABC):
         self.workers = list(getattr(worker_group, "workers", []))[ws * self.replica_rank : ws * (self.replica_rank + 1)]
         await self.launch_servers()
 
+    async def init_hybrid_colocated(self, worker_group, resource_pool):
+        """The trainer's worker processes serve (as in :meth:`init_hybrid`) and the replica remembers the resource pool
+        those processes live in, for helpers that are placed beside them."""
+        self.resource_pool = resource_pool
+        await self.init_hybrid(worker_group)
+        self.rollout_mode = RolloutMode.HYBRID
+
+    def get_ray_class_with_init_args(self):
+        """Worker class (+ constructor arguments) of a replica that starts its own processes (COLOCATED / STANDALONE)."""
+        raise NotImplementedError
+
+    def rollout_worker_use_gpu(self) -> bool:
+        return True
+
     async def init_colocated(self, resource_pool):
         self.rollout_mode = RolloutMode.COLOCATED
         self.resource_pool = resource_pool
