@@ -53,9 +53,15 @@ class RewardLoopWorker:
         rm = self.config.get("reward_model") or {}
         if self.custom_fn is None and rm.get("enable", False) and self.reward_model_manager is not None:
             # discriminative reward model; a generative one needs a custom reward function that calls the router
-            score = await self.reward_model_manager.score(data)
-            return {"reward_score": float(score), "reward_extra_info": {}}
+            return await self.compute_score_disrm(data)
         return await self.reward_loop.run_single(data)
+
+    async def compute_score_disrm(self, data: DataProto) -> dict:
+        """Score of a discriminative reward model (a value head on the last valid token) for one sample; the manager
+        batches concurrent requests into one forward."""
+        assert self.reward_model_manager is not None, "no reward model manager was given to this worker"
+        score = await self.reward_model_manager.score(data)
+        return {"reward_score": float(score), "reward_extra_info": {}}
 
 
 class RewardLoopManager:
