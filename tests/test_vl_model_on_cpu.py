@@ -192,7 +192,8 @@ def test_grpo_on_a_vision_language_model_end_to_end(tmp_path, monkeypatch, name,
         "actor_rollout_ref.actor.ppo_mini_batch_size=4", "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=4",
         "actor_rollout_ref.actor.use_kl_loss=true", "actor_rollout_ref.actor.optim.lr=1e-5"] + (
         # server mode: the single-turn agent loop sends the sample's patches and grids with its request (over HTTP)
-        ["actor_rollout_ref.rollout.agent.use_agent_loop=true", "actor_rollout_ref.rollout.agent.num_workers=2"] if agent else []))
+        ["actor_rollout_ref.rollout.agent.use_agent_loop=true", "actor_rollout_ref.rollout.agent.num_workers=2",
+         "data.return_raw_chat=true"] if agent else []))
     trainer = run_ppo(cfg, spmd=True)
     assert trainer.global_steps == 2 and bool(trainer.async_rollout_mode) == agent
     m = [json.loads(l) for l in open(tmp_path / "logs" / "cpu_e2e" / "vl.jsonl")][-1]["data"]

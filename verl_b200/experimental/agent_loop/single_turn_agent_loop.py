@@ -17,14 +17,19 @@ class SingleTurnAgentLoop(AgentLoopBase):
         self.prompt_length, self.response_length = int(rc.prompt_length), int(rc.response_length)
 
     async def run(self, sampling_params: dict[str, Any], **kwargs) -> AgentLoopOutput:
-        prompt_ids = await self.apply_chat_template(kwargs["raw_prompt"])
+        mm = kwargs.get("multi_modal_inputs")
+        if isinstance(mm, dict) and mm and kwargs.get("raw_prompt_ids") is not None:
+            # vision-language sample: the dataset's ids already hold one placeholder token per merged patch of the
+            # sample's images / videos; re-tokenising the chat messages would lose that expansion
+            prompt_ids = [int(t) for t in kwargs["raw_prompt_ids"]]
+        else:
+            prompt_ids = await self.apply_chat_template(kwargs["raw_prompt"])
         t0 = time.perf_counter()
         # the output is cut to response_length below: do not let the server spend the unused prompt budget on it
         sampling_params = dict(sampling_params)
         sampling_params["max_tokens"] = min(int(sampling_params.get("max_tokens", self.response_length)), self.response_length)
         # vision-language samples: the dataset's patches and grids go with the request (the prompt ids already hold one
         # placeholder token per merged patch)
-        mm = kwargs.get("multi_modal_inputs")
         out = await self.server_manager.generate(uuid4().hex, prompt_ids=prompt_ids, sampling_params=sampling_params,
                                                  image_data=mm if isinstance(mm, dict) and mm else None)
         dt = time.perf_counter() - t0
