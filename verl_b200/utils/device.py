@@ -57,3 +57,13 @@ def auto_set_device(config) -> None:
 
 def local_rank() -> int:
     return int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def is_torch_npu_available() -> bool:
+    """This framework targets NVIDIA B200 only."""
+    return False
+
+
+def get_resource_name() -> str:
+    """Name of the accelerator resource a scheduler hands out per worker."""
+    return "GPU" if is_cuda_available() else "CPU"

@@ -65,3 +65,14 @@ def stateless_init_process_group(master_address: str, master_port: int, rank: in
         opts = dist.ProcessGroupNCCL.Options()
         pg = dist.ProcessGroupNCCL(prefix, rank, world_size, opts)
     return pg
+
+
+def initialize_global_process_group_ray(timeout_second: Optional[int] = None, backend: Optional[str] = None) -> None:
+    """Default process group of a worker that a controller started with RANK / WORLD_SIZE / MASTER_* in its environment
+    (the worker groups of this framework set them); ``backend`` such as ``"cpu:gloo,cuda:nccl"`` or ``"cpu:gloo"``."""
+    if dist.is_initialized():
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    kw = {"timeout": datetime.timedelta(seconds=timeout_second)} if timeout_second is not None else {}
+    dist.init_process_group(backend=backend or get_nccl_backend(), rank=int(os.environ.get("RANK", 0)),
+                            world_size=int(os.environ.get("WORLD_SIZE", 1)), **kw)
