@@ -163,3 +163,52 @@ def test_checkpoint_engine_from_its_config_section():
     assert build_checkpoint_engine({"backend": "naive"}).bucket_size == 2048 << 20
     with pytest.raises(ValueError, match="Unknown checkpoint engine backend"):
         build_checkpoint_engine({"backend": "nixl2"})
+
+
+def test_megatron_strategy_command_lines_map_onto_the_native_engine(capsys):
+    from verl_b200.utils.config import compose, translate_megatron_overrides
+
+    ov = ["actor_rollout_ref.actor.strategy=megatron", "actor_rollout_ref.actor.megatron.tensor_model_parallel_size=2",
+          "actor_rollout_ref.actor.megatron.pipeline_model_parallel_size=2", "actor_rollout_ref.actor.megatron.param_offload=true",
+          "actor_rollout_ref.ref.megatron.tensor_model_parallel_size=2", "critic.strategy=megatron",
+          "critic.megatron.expert_model_parallel_size=4", "actor_rollout_ref.actor.megatron.use_mbridge=true",
+          "+actor_rollout_ref.actor.megatron.override_transformer_config.recompute_granularity=full",
+          "actor_rollout_ref.actor.optim.lr_decay_style=cosine", "actor_rollout_ref.actor.optim.lr=2e-6",
+          "actor_rollout_ref.model.path=preset:tiny-qwen2"]
+    out, dropped = translate_megatron_overrides(ov)
+    assert "actor_rollout_ref.actor.fsdp_config.tensor_model_parallel_size=2" in out and "critic.model.fsdp_config.expert_model_parallel_size=4" in out
+    assert len(dropped) == 2 and all("megatron" not in o for o in out)
+    cfg = compose("ppo_megatron_trainer", ov)
+    a = cfg.actor_rollout_ref.actor
+    assert a.strategy == "fsdp" and a.fsdp_config.tensor_model_parallel_size == 2 and a.fsdp_config.pipeline_model_parallel_size == 2
+    assert a.fsdp_config.param_offload is True and a.optim.lr_scheduler_type == "cosine" and a.optim.lr == 2e-6
+    assert cfg.actor_rollout_ref.ref.fsdp_config.tensor_model_parallel_size == 2
+    assert cfg.critic.strategy == "fsdp" and cfg.critic.model.fsdp_config.expert_model_parallel_size == 4
+    assert "left out" in capsys.readouterr().out
+    with pytest.raises(NotImplementedError, match="virtual pipeline"):
+        translate_megatron_overrides(["actor_rollout_ref.actor.megatron.virtual_pipeline_model_parallel_size=2"])
+    with pytest.raises(NotImplementedError, match="lr_decay_style"):
+        translate_megatron_overrides(["actor_rollout_ref.actor.optim.lr_decay_style=inverse-square-root"])
+
+
+def test_megatron_style_command_line_trains_with_tensor_parallelism(tmp_path, monkeypatch):
+    """The reference's Megatron launch flags, end to end: two gloo workers, the actor sharded over a tensor-parallel
+    group of two as ``actor.megatron.tensor_model_parallel_size=2`` asks."""
+    import json
+    import math
+
+    from test_e2e_grpo_on_cpu import _overrides
+
+    from verl_b200.trainer.main_ppo import run_ppo
+    from verl_b200.utils.config import compose
+
+    monkeypatch.setenv("VERL_FILE_LOGGER_ROOT", str(tmp_path / "logs"))
+    extra = ["actor_rollout_ref.actor.strategy=megatron", "actor_rollout_ref.actor.megatron.tensor_model_parallel_size=2",
+             "actor_rollout_ref.ref.strategy=megatron", "actor_rollout_ref.ref.megatron.tensor_model_parallel_size=2",
+             "actor_rollout_ref.actor.megatron.use_distributed_optimizer=true", "trainer.experiment_name=mcore",
+             "trainer.save_freq=-1", "trainer.total_training_steps=1", "data.max_response_length=16"]
+    trainer = run_ppo(compose("ppo_megatron_trainer", _overrides(tmp_path, extra)), spmd=False)
+    assert trainer.global_steps == 1
+    assert trainer.config.actor_rollout_ref.actor.fsdp_config.tensor_model_parallel_size == 2
+    m = [json.loads(l) for l in open(tmp_path / "logs" / "cpu_e2e" / "mcore.jsonl")][-1]["data"]
+    assert math.isfinite(m["actor/pg_loss"]) and m["actor/grad_norm"] > 0

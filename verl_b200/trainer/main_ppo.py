@@ -185,12 +185,19 @@ def run_ppo(config, spmd: Optional[bool] = None, trainer_cls=None, run_fit: bool
 
 def main(argv=None):
     argv = list(sys.argv[1:] if argv is None else argv)
-    name = "ppo_trainer"
-    for a in list(argv):
-        if a.startswith("--config-name="):
-            name = a.split("=", 1)[1]
-            argv.remove(a)
-    config = compose(name, argv)
+    name, rest, it = "ppo_trainer", [], iter(argv)
+    for a in it:
+        # Hydra's launcher flags: --config-name[=]NAME[.yaml] (ppo_megatron_trainer maps onto the one engine, see
+        # utils.config.translate_megatron_overrides); --config-path is not needed (the tree ships with the package)
+        if a.startswith("--config-name"):
+            name = (a.split("=", 1)[1] if "=" in a else next(it)).strip("'\"")
+            name = name[: -len(".yaml")] if name.endswith(".yaml") else name
+        elif a.startswith("--config-path"):
+            if "=" not in a:
+                next(it, None)
+        else:
+            rest.append(a)
+    config = compose(name, rest)
     run_ppo(config)
 
 

@@ -299,6 +299,54 @@ def _compose_file(config_dir: Path, name: str, group_choice: dict[str, str]) -> 
     return out
 
 
+# engine keys of the reference's Megatron strategy that name something the one native engine has
+_MEGATRON_ENGINE_KEYS = {"tensor_model_parallel_size", "pipeline_model_parallel_size", "expert_model_parallel_size",
+                         "context_parallel_size", "param_offload", "optimizer_offload", "grad_offload", "seed", "forward_only",
+                         "full_determinism"}
+_MEGATRON_LR_STYLE = {"constant": "constant", "cosine": "cosine", "WSD": "wsd", "wsd": "wsd"}
+
+
+def translate_megatron_overrides(overrides: Iterable[str]) -> tuple[list[str], list[str]]:
+    """Command lines written for the reference's Megatron strategy (``--config-name ppo_megatron_trainer``,
+    ``<role>.strategy=megatron``, ``<role>.megatron.tensor_model_parallel_size=2`` ...,
+    verl/trainer/config/ppo_megatron_trainer.yaml) onto this framework's one engine: the parallel sizes, offload switches
+    and the seed go to ``<role>.fsdp_config`` (``critic.model.fsdp_config`` for the critic), the strategy becomes the
+    native one, ``optim.lr_decay_style`` becomes ``optim.lr_scheduler_type``. Keys that configure Megatron-core itself
+    (transformer overrides, distributed optimizer, dist checkpointing, mbridge) have no counterpart: they are returned
+    in the second list and left out. Virtual pipeline stages are refused."""
+    out, dropped = [], []
+    for ov in overrides:
+        m = _OVERRIDE.match(ov)
+        key = m.group("key").strip() if m else ""
+        val = m.group("value") if m else None
+        pre = (m.group("prefix") or "") if m else ""
+        if key.endswith(".strategy") and val == "megatron":
+            out.append(f"{pre}{key}=fsdp")
+            continue
+        if ".megatron." in key:
+            role, leaf = key.split(".megatron.", 1)
+            if leaf == "virtual_pipeline_model_parallel_size" and val not in (None, "null", "None", "1"):
+                raise NotImplementedError("virtual pipeline stages (virtual_pipeline_model_parallel_size) are not supported")
+            if leaf in _MEGATRON_ENGINE_KEYS:
+                home = f"{role}.model.fsdp_config" if role == "critic" else f"{role}.fsdp_config"
+                out.append(f"{home}.{leaf}={val}")
+            else:
+                dropped.append(ov)
+            continue
+        if key.endswith(".optim.lr_decay_style"):
+            if val not in _MEGATRON_LR_STYLE:
+                raise NotImplementedError(f"optim.lr_decay_style={val}: supported are {sorted(set(_MEGATRON_LR_STYLE))}")
+            out.append(f"{pre}{key[: -len('lr_decay_style')]}lr_scheduler_type={_MEGATRON_LR_STYLE[val]}")
+            continue
+        if key.endswith((".optim.use_checkpoint_opt_param_scheduler", ".optim.lr_warmup_init", ".optim.lr_decay_steps",
+                         ".optim.weight_decay_incr_style", ".optim.lr_wsd_decay_style", ".optim.lr_wsd_decay_steps",
+                         ".optim.min_lr", ".load_weight")):
+            dropped.append(ov)
+            continue
+        out.append(ov)
+    return out, dropped
+
+
 def compose(config_name: str, overrides: Optional[Iterable[str]] = None, config_dir: str | Path | None = None,
             resolve_interpolations: bool = True) -> ConfigDict:
     """Load ``config_name`` (with its ``defaults:`` tree) from ``config_dir``, apply CLI-style overrides."""
@@ -306,6 +354,12 @@ def compose(config_name: str, overrides: Optional[Iterable[str]] = None, config_
         config_dir = Path(__file__).resolve().parent.parent / "trainer" / "config"
     config_dir = Path(config_dir)
     overrides = list(overrides or [])
+    if config_name == "ppo_megatron_trainer" or any(".megatron." in o or o.endswith("strategy=megatron") for o in overrides):
+        overrides, dropped = translate_megatron_overrides(overrides)
+        if config_name == "ppo_megatron_trainer":
+            config_name = "ppo_trainer"
+        if dropped:
+            print(f"[config] Megatron-core options without a counterpart here were left out: {dropped}")
     group_choice, value_overrides = {}, []
     for ov in overrides:
         m = _OVERRIDE.match(ov)
