@@ -97,3 +97,14 @@ def test_controller_driven_sft_trains_validates_and_resumes(tmp_path):
     assert tr2.resume_global_step == 3 and tr2.global_step == 6
     assert abs(out2["train/loss"] - out_ref["train/loss"]) < 2e-3, (out2["train/loss"], out_ref["train/loss"])
     assert out2["train/loss"] < out1["train/loss"] + 0.5
+
+
+def test_sft_with_the_megatron_engine_and_optimizer_choices(tmp_path):
+    """``engine=megatron optim=megatron`` (the reference's group choices) compose and train on the native engine."""
+    from verl_b200.trainer.sft_trainer import SFTTrainer
+
+    cfg = _config(tmp_path, **{"engine": "megatron", "optim": "megatron", "optim.lr_decay_style": "cosine", "optim.lr": "3e-3",
+                               "trainer.total_training_steps": 3, "trainer.save_freq": -1, "trainer.test_freq": -1})
+    assert cfg.engine.strategy == "megatron" and cfg.optim.lr_scheduler_type == "cosine"
+    out = SFTTrainer(cfg, tokenizer=IntTokenizer(256)).fit()
+    assert out["train/loss"] > 0 and out["train/grad_norm"] > 0

@@ -333,7 +333,7 @@ def translate_megatron_overrides(overrides: Iterable[str]) -> tuple[list[str], l
             else:
                 dropped.append(ov)
             continue
-        if key.endswith(".optim.lr_decay_style"):
+        if key.endswith(".optim.lr_decay_style") or key == "optim.lr_decay_style":
             if val not in _MEGATRON_LR_STYLE:
                 raise NotImplementedError(f"optim.lr_decay_style={val}: supported are {sorted(set(_MEGATRON_LR_STYLE))}")
             out.append(f"{pre}{key[: -len('lr_decay_style')]}lr_scheduler_type={_MEGATRON_LR_STYLE[val]}")
@@ -354,7 +354,8 @@ def compose(config_name: str, overrides: Optional[Iterable[str]] = None, config_
         config_dir = Path(__file__).resolve().parent.parent / "trainer" / "config"
     config_dir = Path(config_dir)
     overrides = list(overrides or [])
-    if config_name == "ppo_megatron_trainer" or any(".megatron." in o or o.endswith("strategy=megatron") for o in overrides):
+    if config_name == "ppo_megatron_trainer" or any(".megatron." in o or o.endswith("strategy=megatron") or
+                                                    "lr_decay_style=" in o for o in overrides):
         overrides, dropped = translate_megatron_overrides(overrides)
         if config_name == "ppo_megatron_trainer":
             config_name = "ppo_trainer"
