@@ -15,7 +15,7 @@ from ...utils.profiler.config import ProfilerConfig
 
 __all__ = [
     "OptimizerConfig", "FSDPOptimizerConfig", "McoreOptimizerConfig", "EngineConfig", "FSDPEngineConfig",
-    "McoreEngineConfig", "TrainingWorkerConfig", "PolicyLossConfig", "RouterReplayConfig", "ActorConfig",
+    "McoreEngineConfig", "McoreCriticConfig", "TrainingWorkerConfig", "PolicyLossConfig", "RouterReplayConfig", "ActorConfig",
     "FSDPActorConfig", "McoreActorConfig", "MtpConfig", "HFModelConfig", "CriticConfig", "FSDPCriticConfig",
     "FSDPCriticModelCfg", "SamplingConfig", "MultiTurnConfig", "CustomAsyncServerConfig", "AgentLoopConfig",
     "TraceConfig", "ServerConfig", "PrometheusConfig", "CheckpointEngineConfig", "RolloutConfig",
@@ -398,6 +398,17 @@ class FSDPCriticConfig(CriticConfig):
     ulysses_sequence_parallel_size: int = 1
     grad_clip: float = 1.0
     optim: FSDPOptimizerConfig = field(default_factory=lambda: FSDPOptimizerConfig(lr=1e-5))
+
+
+@dataclass
+class McoreCriticConfig(CriticConfig):
+    """Critic section with the reference's Megatron key names; the parallel sizes of ``megatron`` are served by the one
+    native engine (``utils.config.translate_megatron_overrides`` moves them to ``model.fsdp_config``)."""
+
+    strategy: str = "megatron"
+    nccl_timeout: int = 600
+    megatron: McoreEngineConfig = field(default_factory=McoreEngineConfig)
+    load_weight: bool = True
 
 
 # ----------------------------------------------------------------------------- rollout
